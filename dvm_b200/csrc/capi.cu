@@ -1,0 +1,298 @@
+// C ABI over the C++ builder (include/dvm_c.h).  Exceptions never cross this boundary: they are turned
+// into an error return plus a thread-local message.
+#include <cuda_runtime.h>
+
+#include <chrono>
+#include <cstring>
+#include <exception>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/dvm.h"
+#include "../../include/dvm_c.h"
+#include "graph.h"
+#include "runtime.h"
+
+struct dvm_int_array {
+  std::vector<int64_t> data;
+  dvm::IntArrayRef ref;
+  void sync() {
+    ref.data = data.data();
+    ref.size = data.size();
+  }
+};
+
+struct dvm_scalar {
+  dvm::ScalarRef ref;
+};
+
+struct dvm_kernel {
+  dvm::Kernel kernel;
+  double last_jit_us = 0.0;
+};
+
+namespace {
+
+thread_local std::string g_error;
+
+template <typename F>
+auto Guard(F &&f, decltype(f()) fail) -> decltype(f()) {
+  try {
+    g_error.clear();
+    return f();
+  } catch (const std::exception &e) {
+    g_error = e.what();
+  } catch (...) {
+    g_error = "unknown error";
+  }
+  return fail;
+}
+
+inline dvm::NDObject *N(dvm_object *o) { return reinterpret_cast<dvm::NDObject *>(o); }
+inline dvm_object *O(dvm::NDObject *n) { return reinterpret_cast<dvm_object *>(n); }
+
+struct CallbackAlloc : dvm::WsAllocator {
+  dvm_ws_alloc_fn fn;
+  void *user;
+  void *Alloc(size_t size) override { return fn ? fn(size, user) : nullptr; }
+};
+
+int CudaCheck(cudaError_t e, const char *what) {
+  if (e == cudaSuccess) return 0;
+  g_error = std::string(what) + ": " + cudaGetErrorString(e);
+  return static_cast<int>(e);
+}
+
+template <typename S>
+dvm::NDObject *BinaryScalarDispatch(dvm::Kernel &k, int op, dvm::NDObject *x, S v, bool scalar_is_lhs) {
+  return scalar_is_lhs ? k.Binary(op, v, x) : k.Binary(op, x, v);
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *dvm_last_error(void) { return g_error.c_str(); }
+const char *dvm_version(void) { return "dvm-b200 0.1 (sm_100a)"; }
+
+dvm_int_array *dvm_int_array_new(const int64_t *data, size_t size) {
+  auto a = new dvm_int_array();
+  if (size) a->data.assign(data, data + size);
+  a->sync();
+  return a;
+}
+int dvm_int_array_update(dvm_int_array *a, const int64_t *data, size_t size) {
+  a->data.assign(data, data + size);
+  a->sync();
+  return 0;
+}
+size_t dvm_int_array_size(const dvm_int_array *a) { return a->data.size(); }
+const int64_t *dvm_int_array_data(const dvm_int_array *a) { return a->data.data(); }
+void dvm_int_array_free(dvm_int_array *a) { delete a; }
+
+dvm_scalar *dvm_scalar_new(void) {
+  auto s = new dvm_scalar();
+  s->ref.type = dvm::kDataTypeEnd;
+  s->ref.i64 = 0;
+  return s;
+}
+void dvm_scalar_set_f32(dvm_scalar *s, float v) { s->ref = v; }
+void dvm_scalar_set_i64(dvm_scalar *s, int64_t v) { s->ref = v; }
+void dvm_scalar_free(dvm_scalar *s) { delete s; }
+
+dvm_kernel *dvm_kernel_new(int kernel_type, uint32_t flags) {
+  return Guard(
+    [&]() {
+      auto k = std::make_unique<dvm_kernel>();
+      k->kernel.Reset(static_cast<dvm::KernelType>(kernel_type), flags);
+      return k.release();
+    },
+    static_cast<dvm_kernel *>(nullptr));
+}
+int dvm_kernel_reset(dvm_kernel *k, int kernel_type, uint32_t flags) {
+  return Guard([&]() { k->kernel.Reset(static_cast<dvm::KernelType>(kernel_type), flags); return 0; }, 1);
+}
+void dvm_kernel_free(dvm_kernel *k) { delete k; }
+int dvm_set_name_hint(dvm_kernel *k, const char *name) {
+  return Guard([&]() { k->kernel.SetNameHint(name, name); return 0; }, 1);
+}
+
+#define DVM_OBJ_GUARD(EXPR) Guard([&]() { return O(EXPR); }, static_cast<dvm_object *>(nullptr))
+
+dvm_object *dvm_load(dvm_kernel *k, void *addr, dvm_int_array *shape, int dtype) {
+  return DVM_OBJ_GUARD(k->kernel.Load(addr, &shape->ref, static_cast<dvm::DataType>(dtype)));
+}
+dvm_object *dvm_store(dvm_kernel *k, void *addr, dvm_object *input) { return DVM_OBJ_GUARD(k->kernel.Store(addr, N(input))); }
+dvm_object *dvm_unary(dvm_kernel *k, int unary_type, dvm_object *input) {
+  return DVM_OBJ_GUARD(k->kernel.Unary(unary_type, N(input)));
+}
+dvm_object *dvm_binary(dvm_kernel *k, int binary_type, dvm_object *lhs, dvm_object *rhs) {
+  return DVM_OBJ_GUARD(k->kernel.Binary(binary_type, N(lhs), N(rhs)));
+}
+dvm_object *dvm_binary_f32(dvm_kernel *k, int binary_type, dvm_object *x, float v, int scalar_is_lhs) {
+  return DVM_OBJ_GUARD(BinaryScalarDispatch(k->kernel, binary_type, N(x), v, scalar_is_lhs != 0));
+}
+dvm_object *dvm_binary_i64(dvm_kernel *k, int binary_type, dvm_object *x, int64_t v, int scalar_is_lhs) {
+  return DVM_OBJ_GUARD(BinaryScalarDispatch(k->kernel, binary_type, N(x), v, scalar_is_lhs != 0));
+}
+dvm_object *dvm_binary_ref(dvm_kernel *k, int binary_type, dvm_object *x, dvm_scalar *v, int scalar_is_lhs) {
+  return DVM_OBJ_GUARD(BinaryScalarDispatch(k->kernel, binary_type, N(x), &v->ref, scalar_is_lhs != 0));
+}
+dvm_object *dvm_reduce(dvm_kernel *k, int reduce_type, dvm_object *input, dvm_int_array *dims, int keepdims) {
+  return DVM_OBJ_GUARD(k->kernel.Reduce(reduce_type, N(input), &dims->ref, keepdims != 0));
+}
+dvm_object *dvm_select(dvm_kernel *k, dvm_object *cond, dvm_object *lhs, dvm_object *rhs) {
+  return DVM_OBJ_GUARD(k->kernel.Select(N(cond), N(lhs), N(rhs)));
+}
+dvm_object *dvm_cast(dvm_kernel *k, dvm_object *input, int dtype) {
+  return DVM_OBJ_GUARD(k->kernel.Cast(N(input), static_cast<dvm::DataType>(dtype)));
+}
+dvm_object *dvm_broadcast(dvm_kernel *k, dvm_object *input, dvm_int_array *shape) {
+  return DVM_OBJ_GUARD(k->kernel.Broadcast(N(input), &shape->ref));
+}
+dvm_object *dvm_full_f32(dvm_kernel *k, float v, dvm_int_array *shape, int dtype) {
+  return DVM_OBJ_GUARD(k->kernel.Broadcast(v, &shape->ref, static_cast<dvm::DataType>(dtype)));
+}
+dvm_object *dvm_full_i64(dvm_kernel *k, int64_t v, dvm_int_array *shape, int dtype) {
+  return DVM_OBJ_GUARD(k->kernel.Broadcast(v, &shape->ref, static_cast<dvm::DataType>(dtype)));
+}
+dvm_object *dvm_full_ref(dvm_kernel *k, dvm_scalar *v, dvm_int_array *shape, int dtype) {
+  return DVM_OBJ_GUARD(k->kernel.Broadcast(&v->ref, &shape->ref, static_cast<dvm::DataType>(dtype)));
+}
+dvm_object *dvm_reshape(dvm_kernel *k, dvm_object *input, dvm_int_array *shape) {
+  return DVM_OBJ_GUARD(k->kernel.Reshape(N(input), &shape->ref));
+}
+dvm_object *dvm_copy(dvm_kernel *k, dvm_object *input) { return DVM_OBJ_GUARD(k->kernel.Copy(N(input))); }
+dvm_object *dvm_matmul(dvm_kernel *k, dvm_object *lhs, dvm_object *rhs, int trans_a, int trans_b, dvm_object *bias) {
+  return DVM_OBJ_GUARD(k->kernel.MatMul(N(lhs), N(rhs), trans_a != 0, trans_b != 0, bias ? N(bias) : nullptr));
+}
+
+int dvm_normalize(dvm_kernel *k) {
+  return Guard([&]() { k->kernel.Normalize(); return 0; }, 1);
+}
+
+int dvm_pre_codegen(dvm_kernel *k, size_t *workspace_bytes) {
+  return Guard(
+    [&]() {
+      auto t0 = std::chrono::steady_clock::now();
+      size_t ws = k->kernel.PreCodeGen();
+      k->last_jit_us = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count();
+      if (workspace_bytes) *workspace_bytes = ws;
+      return 0;
+    },
+    1);
+}
+
+int dvm_codegen(dvm_kernel *k, const dvm_reloc *relocs, size_t reloc_size, dvm_ws_alloc_fn alloc, void *user) {
+  return Guard(
+    [&]() {
+      static_assert(sizeof(dvm_reloc) == sizeof(dvm::RelocEntry), "dvm_reloc must match dvm::RelocEntry");
+      CallbackAlloc cb;
+      cb.fn = alloc;
+      cb.user = user;
+      auto t0 = std::chrono::steady_clock::now();
+      k->kernel.Normalize();
+      k->kernel.CodeGen(reinterpret_cast<const dvm::RelocEntry *>(relocs), reloc_size, &cb);
+      k->last_jit_us = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count();
+      return 0;
+    },
+    1);
+}
+
+int dvm_launch(dvm_kernel *k, void *stream) {
+  return Guard([&]() { return k->kernel.Launch(stream); }, -1);
+}
+
+int dvm_launch_reloc(dvm_kernel *k, const dvm_reloc *relocs, size_t reloc_size, void *workspace, void *stream) {
+  return Guard(
+    [&]() { return k->kernel.Launch(reinterpret_cast<const dvm::RelocEntry *>(relocs), reloc_size, workspace, stream); },
+    -1);
+}
+
+double dvm_last_jit_us(const dvm_kernel *k) { return k->last_jit_us; }
+
+int dvm_object_rank(const dvm_object *o) { return reinterpret_cast<const dvm::NDObject *>(o)->shape.rank; }
+int64_t dvm_object_dim(const dvm_object *o, int i) { return reinterpret_cast<const dvm::NDObject *>(o)->shape.d[i]; }
+int dvm_object_dtype(const dvm_object *o) { return reinterpret_cast<const dvm::NDObject *>(o)->dtype; }
+
+const char *dvm_dump(dvm_kernel *k) { return Guard([&]() { return k->kernel.Dump(); }, ""); }
+const char *dvm_dump_r(dvm_kernel *k) { return Guard([&]() { return k->kernel.DumpR(); }, ""); }
+const char *dvm_das(dvm_kernel *k) { return Guard([&]() { return k->kernel.Das(); }, ""); }
+const char *dvm_inspect(dvm_kernel *k) { return Guard([&]() { return k->kernel.Inspect(); }, ""); }
+
+int dvm_rt_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+int dvm_rt_set_device(int dev) { return CudaCheck(cudaSetDevice(dev), "cudaSetDevice"); }
+int dvm_rt_sm_count(void) {
+  return Guard(
+    [&]() {
+      dvmb::Runtime::Get().EnsureInit();
+      return dvmb::Runtime::Get().sm_count();
+    },
+    0);
+}
+void *dvm_rt_malloc(size_t bytes) {
+  void *p = nullptr;
+  if (CudaCheck(cudaMalloc(&p, bytes ? bytes : 1), "cudaMalloc") != 0) return nullptr;
+  return p;
+}
+int dvm_rt_free(void *p) { return CudaCheck(cudaFree(p), "cudaFree"); }
+int dvm_rt_memcpy_h2d(void *dst, const void *src, size_t bytes, void *stream) {
+  return CudaCheck(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)), "H2D copy");
+}
+int dvm_rt_memcpy_d2h(void *dst, const void *src, size_t bytes, void *stream) {
+  return CudaCheck(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)), "D2H copy");
+}
+int dvm_rt_memset(void *dst, int value, size_t bytes, void *stream) {
+  return CudaCheck(cudaMemsetAsync(dst, value, bytes, static_cast<cudaStream_t>(stream)), "memset");
+}
+int dvm_rt_sync(void *stream) { return CudaCheck(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)), "stream sync"); }
+void *dvm_rt_host_alloc(size_t bytes) {
+  void *p = nullptr;
+  if (CudaCheck(cudaMallocHost(&p, bytes ? bytes : 1), "cudaMallocHost") != 0) return nullptr;
+  return p;
+}
+int dvm_rt_host_free(void *p) { return CudaCheck(cudaFreeHost(p), "cudaFreeHost"); }
+
+int dvm_perf(dvm_kernel *k, int warmup, int reps, void *stream, float *min_us, float *max_us, float *mean_us) {
+  return Guard(
+    [&]() {
+      cudaStream_t s = static_cast<cudaStream_t>(stream);
+      cudaEvent_t e0, e1;
+      if (CudaCheck(cudaEventCreate(&e0), "event") || CudaCheck(cudaEventCreate(&e1), "event")) return 1;
+      for (int i = 0; i < warmup; ++i) {
+        int rc = k->kernel.Launch(stream);
+        if (rc != 0) return rc;
+      }
+      float lo = 1e30f, hi = 0.0f, sum = 0.0f;
+      for (int i = 0; i < reps; ++i) {
+        cudaEventRecord(e0, s);
+        int rc = k->kernel.Launch(stream);
+        cudaEventRecord(e1, s);
+        if (rc != 0) return rc;
+        if (CudaCheck(cudaEventSynchronize(e1), "event sync")) return 1;
+        float ms = 0.0f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        float us = ms * 1000.0f;
+        lo = us < lo ? us : lo;
+        hi = us > hi ? us : hi;
+        sum += us;
+      }
+      cudaEventDestroy(e0);
+      cudaEventDestroy(e1);
+      if (min_us) *min_us = lo;
+      if (max_us) *max_us = hi;
+      if (mean_us) *mean_us = reps > 0 ? sum / reps : 0.0f;
+      return 0;
+    },
+    1);
+}
+
+}  // extern "C"

@@ -1,0 +1,131 @@
+// Operator graph of one dvm::Kernel: node type, shape inference, stage plans and launch.
+//
+// Replaces the reference's NDObject class family (src/ops.h:30-77, 444-554) and its kernel models
+// (src/kernel.h:52-104, src/xkernel.h) with one node struct and one compile pipeline aimed at the
+// sm_100a interpreters.
+#ifndef DVM_B200_GRAPH_H_
+#define DVM_B200_GRAPH_H_
+
+#include <cstdint>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/dvm.h"
+#include "isa.h"
+
+namespace dvm {
+
+constexpr int kMaxRank = 8;
+
+struct Shape {
+  int64_t d[kMaxRank];
+  int rank = 0;
+  int64_t numel() const {
+    int64_t n = 1;
+    for (int i = 0; i < rank; ++i) n *= d[i];
+    return n;
+  }
+  bool operator==(const Shape &o) const {
+    if (rank != o.rank) return false;
+    for (int i = 0; i < rank; ++i)
+      if (d[i] != o.d[i]) return false;
+    return true;
+  }
+};
+
+enum NodeKind : uint8_t {
+  N_LOAD = 0,
+  N_STORE,
+  N_UNARY,      // sub = UnaryType
+  N_BINARY,     // sub = BinaryType (arithmetic / logical / pow), two tensor operands
+  N_BINARY_S,   // sub = ScalarBin, tensor (in[0]) op scalar
+  N_COMPARE,    // sub = BinaryType (< kAdd), two tensor operands; result is 1/0 in the operand dtype
+  N_COMPARE_S,  // tensor (in[0]) cmp scalar
+  N_SELECT,     // in[0] cond (same dtype as data), in[1], in[2]
+  N_CAST,       // one direct conversion step
+  N_BROADCAST,  // tensor -> shape
+  N_BROADCAST_S,  // scalar -> shape
+  N_RESHAPE,
+  N_COPY,
+  N_REDUCE,     // sub = ReduceType
+  N_MATMUL,
+};
+
+// Scalar-operand arithmetic kinds (the reference's BinaryScalarOp opcodes ADDS/MULS/DIVS/SDIV/MAXS/MINS,
+// src/vm_gpu.cu:1178-1297).
+enum ScalarBin : uint8_t { SB_ADD = 0, SB_MUL, SB_DIV, SB_SDIV, SB_MAX, SB_MIN };
+
+class NDObject {
+ public:
+  NodeKind kind;
+  DataType dtype;
+  uint8_t sub = 0;
+  bool noloss_cast = false;   // cast inserted by the dtype-promotion rules (may be peeled again)
+  bool keepdims = false;
+  bool trans_a = false, trans_b = false;
+  bool store_temp = false;
+  int id = 0;
+  NDObject *in[3] = {nullptr, nullptr, nullptr};
+  // scalar operand: fixed code (already encoded in `dtype`, widened to the 32-bit register form) or a
+  // borrowed ScalarRef re-read at code generation
+  uint32_t scalar_bits = 0;
+  ScalarRef *scalar_ref = nullptr;
+  IntArrayRef *shape_ref = nullptr;   // Load/Broadcast/Reshape target shape, Reduce dims (borrowed)
+  void *addr = nullptr;               // Load/Store device address
+  // results of Normalize()
+  Shape shape;
+  IntArrayRef out_ref;                // view of `shape` handed out by Kernel::GetShape
+};
+
+// One launch of the vector interpreter.
+struct VectorStage {
+  dvmb::VmParam param;
+  uint32_t grid = 0, threads = 0;
+  bool idle = false;                       // zero-size domain: nothing to launch
+  std::vector<NDObject *> slot_obj;        // tensor slot -> load/store node (relocation sites)
+  std::vector<int64_t> slot_ws_off;        // >= 0: slot is a workspace temporary at this byte offset
+  uint64_t algo_bytes = 0;
+};
+
+class VKernel {
+ public:
+  VKernel(KernelType type, uint32_t flags) : type_(type), flags_(flags) {}
+  ~VKernel();
+
+  NDObject *NewNode(NodeKind kind, DataType dtype);
+  void Normalize();
+  size_t Compile();   // build stages for the current shapes; returns workspace bytes
+  void Bind(const RelocEntry *relocs, size_t n, void *workspace);
+  int Launch(void *stream);
+
+  const char *Dump();
+  const char *DumpR();
+  const char *Das();
+  const char *Inspect();
+
+  KernelType type_;
+  uint32_t flags_;
+  std::vector<NDObject *> nodes_;          // append (= topological) order
+  std::vector<VectorStage> stages_;
+  size_t ws_bytes_ = 0;
+  void *workspace_ = nullptr;
+  bool normalized_ = false;
+  bool compiled_ = false;
+  std::string text_;
+  std::string name_;
+  double last_jit_us_ = 0.0;               // host time of the last Normalize+Compile+Bind
+};
+
+// vcompile.cc
+bool CompileVectorStage(const std::vector<NDObject *> &ops, VectorStage *out, std::string *why);
+std::string DisassembleStage(const VectorStage &st);
+
+// normalize.cc
+void InferShape(NDObject *n);
+int ItemSize(DataType t);
+const char *DTypeName(DataType t);
+
+}  // namespace dvm
+
+#endif  // DVM_B200_GRAPH_H_

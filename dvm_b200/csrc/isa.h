@@ -1,0 +1,147 @@
+// Tile bytecode for the sm_100a vector interpreter (shared by the host compiler and the device VM).
+//
+// Execution model.  A launch walks an iteration space of `num_groups` groups, each holding
+// `group_elems` elements.  A reduce-free graph is one group spanning the whole (coalesced) domain and its
+// chunks are dealt round-robin to the CTAs ("flat" mode).  A graph with reductions makes one group per
+// kept (non-reduced) coordinate; a CTA, or a power-of-two slice of a warp, owns a group and loops over
+// its chunks ("group" mode).  A chunk is `8 * tg` consecutive elements of a group: thread `t` of the
+// group owns two 4-element granules at `4*t` and `4*tg + 4*t` inside the chunk, so every global access
+// is a coalesced 16-byte (fp32), 8-byte (fp16/bf16) or 4-byte (bool) vector.
+//
+// The machine is an accumulator machine whose state lives in registers: an 8-lane accumulator, eight
+// 8-lane named vector registers, and a scalar side (accumulator + 12 named scalars) for values that are
+// constant inside a group (reduce results, per-channel parameters).  The program is cut into sections
+// PRO_0, BODY_0, PRO_1, BODY_1, ... : PRO_p runs once per group on the scalar side (it finalises the
+// reductions accumulated by BODY_{p-1}); BODY_p runs once per chunk on the vector side.
+//
+// This plays the role of the reference's instruction set header (src/isa.h:59-228 opcodes,
+// src/isa.h:261-299 instruction head, src/isa.h:2388-2451 entry word); the encoding is new.
+#ifndef DVM_B200_ISA_H_
+#define DVM_B200_ISA_H_
+
+#include <cstdint>
+
+namespace dvmb {
+
+constexpr int kMaxTensors = 16;
+constexpr int kMaxCodeWords = 288;
+constexpr int kMaxKept = 3;
+constexpr int kMaxEnum = 4;
+constexpr int kNumVRegs = 6;
+constexpr int kNumSRegs = 12;
+constexpr int kNumRSlots = 4;
+constexpr int kMaxPhases = 4;        // BODY sections
+constexpr int kLanes = 8;            // elements per thread per vector register
+constexpr int kAccIdx = 15;          // `dst` value meaning "the accumulator"
+
+// Element types as stored in global memory (same numbering as dvm::DataType).
+enum : uint32_t { T_BOOL = 0, T_F16 = 1, T_BF16 = 2, T_F32 = 3, T_I32 = 4, T_I64 = 5 };
+
+enum Opcode : uint32_t {
+  OP_END = 0,
+  OP_LD,     // acc|reg[dst] <- tensor[sub]
+  OP_ST,     // tensor[sub] <- acc
+  OP_COPY,   // acc <- operand
+  OP_MOV,    // reg[dst] <- acc
+  OP_UN,     // acc <- unary[sub](acc)
+  OP_BIN,    // acc <- binary[sub](acc, operand)
+  OP_CMP,    // acc <- cmp[sub](acc, operand) ? 1 : 0   (in the operand representation)
+  OP_SEL,    // acc <- acc != 0 ? operand : operand2
+  OP_CVT,    // acc <- convert[sub](acc)
+  OP_RACC,   // partial[sub&3] (op)= lanes of acc        (vector side only)
+  OP_RFIN,   // sacc <- reduce over the group of partial[sub&3]; partial reset   (scalar side only)
+  OP_RINIT,  // partial[sub&3] <- identity
+  OP_COUNT
+};
+
+enum UnKind : uint32_t { U_SQRT = 0, U_ABS, U_LOG, U_EXP, U_ROUND, U_FLOOR, U_CEIL, U_TRUNC, U_ISFINITE, U_ABS_I, U_NOP };
+
+enum BinKind : uint32_t {
+  B_ADD = 0, B_SUB, B_MUL, B_DIV, B_MAX, B_MIN, B_POW, B_RSUB, B_RDIV,
+  B_ADD_I, B_SUB_I, B_MUL_I, B_MAX_I, B_MIN_I, B_RSUB_I,
+  B_COUNT
+};
+
+enum CmpKind : uint32_t { C_EQ = 0, C_NE, C_GT, C_GE, C_LT, C_LE };
+
+enum CvtKind : uint32_t {
+  V_F2I = 0,   // float -> int32, truncation toward zero (C cast semantics)
+  V_I2F,       // int32 -> float
+  V_NEZ_F,     // float != 0 -> int 0/1
+  V_NEZ_I,     // int   != 0 -> int 0/1
+  V_RND        // no arithmetic: only the rounding field applies (fp32 -> fp16/bf16 precision)
+};
+
+enum RedKind : uint32_t { R_SUM = 0, R_MAX, R_MIN };
+
+enum OperandKind : uint32_t { K_VREG = 0, K_SREG = 1, K_IMM = 2, K_ACC = 3 };
+
+enum Rounding : uint32_t { RN_NONE = 0, RN_F16 = 1, RN_BF16 = 2 };
+
+// Instruction word (64 bit):
+//   [31:0] imm32  [39:32] opcode  [47:40] sub  [51:48] operand kind  [55:52] operand index
+//   [59:56] dst   [61:60] rounding  [62] integer representation flag  [63] scalar-side flag
+// OP_SEL packs its second operand into sub: kind in sub[7:4], index in sub[3:0] (never an immediate).
+struct Insn {
+  static constexpr uint64_t make(uint32_t opc, uint32_t sub, uint32_t okind, uint32_t oidx, uint32_t dst,
+                                 uint32_t rnd, uint32_t isint, uint32_t scalar, uint32_t imm) {
+    return (uint64_t)imm | ((uint64_t)(opc & 0xff) << 32) | ((uint64_t)(sub & 0xff) << 40) |
+           ((uint64_t)(okind & 0xf) << 48) | ((uint64_t)(oidx & 0xf) << 52) | ((uint64_t)(dst & 0xf) << 56) |
+           ((uint64_t)(rnd & 0x3) << 60) | ((uint64_t)(isint & 1) << 62) | ((uint64_t)(scalar & 1) << 63);
+  }
+};
+
+#define DVMB_IMM(w) ((uint32_t)(w))
+#define DVMB_OPC(w) ((uint32_t)((w) >> 32) & 0xffu)
+#define DVMB_SUB(w) ((uint32_t)((w) >> 40) & 0xffu)
+#define DVMB_OKIND(w) ((uint32_t)((w) >> 48) & 0xfu)
+#define DVMB_OIDX(w) ((uint32_t)((w) >> 52) & 0xfu)
+#define DVMB_DST(w) ((uint32_t)((w) >> 56) & 0xfu)
+#define DVMB_RND(w) ((uint32_t)((w) >> 60) & 0x3u)
+#define DVMB_ISINT(w) ((uint32_t)((w) >> 62) & 0x1u)
+#define DVMB_SCALAR(w) ((uint32_t)((w) >> 63) & 0x1u)
+
+// How a tensor's element offset is derived from (group, element-in-group).
+enum AddrMode : uint32_t {
+  AM_DENSE = 0,    // offset = kept part + element index (contiguous over the enumerated axes)
+  AM_GRANULE = 1,  // innermost enumerated size % 4 == 0: one coordinate split per 4-element granule
+  AM_ELEMENT = 2,  // coordinate split per element
+  AM_SCALAR = 3    // constant inside a group (all enumerated strides are 0)
+};
+
+struct TensorDesc {
+  uint64_t ptr;                // device address (the relocation site; see code.h:56-76 in the reference)
+  uint32_t kstride[kMaxKept];  // element strides along the kept axes (outer -> inner)
+  uint32_t estride[kMaxEnum];  // element strides along the enumerated axes, right-aligned (index 3 = innermost)
+  uint8_t dtype;
+  uint8_t mode;
+  uint8_t vec_ok;              // granules are contiguous and aligned to 4 elements
+  uint8_t pad;
+};
+// Element offsets are 32-bit: a tensor bound to the vector interpreter holds fewer than 2^31 elements.
+
+enum VmMode : uint32_t { VM_FLAT = 0, VM_GROUP = 1 };
+
+struct VmParam {
+  uint32_t mode;
+  uint32_t num_groups;
+  uint32_t group_elems;
+  uint32_t tg;               // threads cooperating on one group
+  uint32_t groups_per_cta;   // blockDim.x / tg
+  uint32_t chunks;           // chunks per group
+  uint32_t kept_size[kMaxKept];
+  uint32_t enum_size[kMaxEnum];   // right-aligned, unused outer slots are 1
+  uint32_t need_coords;      // some tensor uses AM_GRANULE
+  uint32_t num_body;         // number of BODY sections
+  uint16_t sec[2 * kMaxPhases + 2];  // word offset of PRO_0, BODY_0, PRO_1, ..., PRO_n (each ends with OP_END)
+  uint32_t n_tensors;
+  uint32_t n_code;
+  TensorDesc tensor[kMaxTensors];
+  uint64_t code[kMaxCodeWords];
+};
+
+static_assert(sizeof(VmParam) <= 4096, "VmParam must fit the 4 KB kernel parameter space");
+
+}  // namespace dvmb
+
+#endif  // DVM_B200_ISA_H_

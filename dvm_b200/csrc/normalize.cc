@@ -1,0 +1,140 @@
+// Shape inference for graph nodes (the counterpart of the NDObject::Normalize family in the reference:
+// Load src/ops.cc:1117-1123, binary broadcast 2398-2464, Select 2578-2622, Broadcast 2683-2695,
+// Reduce 3080-3123, Reshape 1799-1827, MatMul src/ops_m.cc:271-305).  Shapes are kept in API order
+// (outermost first); NumPy right-aligned broadcasting rules apply.
+#include <string>
+
+#include "graph.h"
+
+namespace dvm {
+
+int ItemSize(DataType t) {
+  switch (t) {
+    case kBool: return 1;
+    case kFloat16:
+    case kBFloat16: return 2;
+    case kFloat32:
+    case kInt32: return 4;
+    default: return 8;
+  }
+}
+
+const char *DTypeName(DataType t) {
+  static const char *names[] = {"bool", "fp16", "bf16", "fp32", "int32", "int64"};
+  return t >= 0 && t < kDataTypeEnd ? names[t] : "?";
+}
+
+namespace {
+
+[[noreturn]] void Fail(const NDObject *n, const char *what) {
+  std::string msg = "shape inference failed at op #" + std::to_string(n->id) + ": " + what;
+  DvmException(msg.c_str());
+}
+
+Shape FromRef(const NDObject *n, const IntArrayRef *ref) {
+  if (ref == nullptr || (ref->size > 0 && ref->data == nullptr)) Fail(n, "missing shape");
+  if (ref->size > static_cast<size_t>(kMaxRank)) Fail(n, "rank above 8");
+  Shape s;
+  s.rank = static_cast<int>(ref->size);
+  for (int i = 0; i < s.rank; ++i) s.d[i] = ref->data[i];
+  return s;
+}
+
+Shape BroadcastShapes(const NDObject *n, const Shape &a, const Shape &b) {
+  Shape o;
+  o.rank = a.rank > b.rank ? a.rank : b.rank;
+  for (int p = 0; p < o.rank; ++p) {   // p counts from the innermost dim
+    int64_t da = p < a.rank ? a.d[a.rank - 1 - p] : 1;
+    int64_t db = p < b.rank ? b.d[b.rank - 1 - p] : 1;
+    if (da != db && da != 1 && db != 1) Fail(n, "operands are not broadcast-compatible");
+    o.d[o.rank - 1 - p] = da == 1 ? db : da;
+  }
+  return o;
+}
+
+}  // namespace
+
+void InferShape(NDObject *n) {
+  switch (n->kind) {
+    case N_LOAD:
+      n->shape = FromRef(n, n->shape_ref);
+      for (int i = 0; i < n->shape.rank; ++i)
+        if (n->shape.d[i] < 0) Fail(n, "negative dimension");
+      break;
+    case N_STORE:
+    case N_UNARY:
+    case N_BINARY_S:
+    case N_COMPARE_S:
+    case N_CAST:
+    case N_COPY: n->shape = n->in[0]->shape; break;
+    case N_BINARY:
+    case N_COMPARE: n->shape = BroadcastShapes(n, n->in[0]->shape, n->in[1]->shape); break;
+    case N_SELECT:
+      n->shape = BroadcastShapes(n, BroadcastShapes(n, n->in[0]->shape, n->in[1]->shape), n->in[2]->shape);
+      break;
+    case N_BROADCAST: {
+      Shape t = FromRef(n, n->shape_ref);
+      const Shape &s = n->in[0]->shape;
+      if (t.rank < s.rank) Fail(n, "broadcast target has lower rank than its input");
+      for (int i = 0; i < t.rank; ++i) {
+        int si = i - (t.rank - s.rank);
+        int64_t in_dim = si >= 0 ? s.d[si] : 1;
+        if (t.d[i] == -1) t.d[i] = in_dim;   // -1 keeps the input dimension
+        if (in_dim != 1 && in_dim != t.d[i]) Fail(n, "broadcast target does not match its input");
+      }
+      n->shape = t;
+      break;
+    }
+    case N_BROADCAST_S: n->shape = n->in[0] ? n->in[0]->shape : FromRef(n, n->shape_ref); break;
+    case N_RESHAPE: {
+      Shape t = FromRef(n, n->shape_ref);
+      if (t.numel() != n->in[0]->shape.numel()) Fail(n, "reshape changes the element count");
+      n->shape = t;
+      break;
+    }
+    case N_REDUCE: {
+      const Shape &s = n->in[0]->shape;
+      bool red[kMaxRank] = {false};
+      if (n->shape_ref == nullptr) Fail(n, "missing reduce dims");
+      for (size_t i = 0; i < n->shape_ref->size; ++i) {
+        int64_t d = n->shape_ref->data[i];
+        if (d < 0) d += s.rank;
+        if (d < 0 || d >= s.rank) Fail(n, "reduce dim out of range");
+        red[d] = true;
+      }
+      Shape o;
+      o.rank = 0;
+      for (int i = 0; i < s.rank; ++i) {
+        if (red[i]) {
+          if (n->keepdims) o.d[o.rank++] = 1;
+        } else {
+          o.d[o.rank++] = s.d[i];
+        }
+      }
+      n->shape = o;
+      break;
+    }
+    case N_MATMUL: {
+      const Shape &a = n->in[0]->shape, &b = n->in[1]->shape;
+      if (a.rank < 2 || b.rank < 2) Fail(n, "matmul operands need rank >= 2");
+      int64_t m = n->trans_a ? a.d[a.rank - 1] : a.d[a.rank - 2];
+      int64_t ka = n->trans_a ? a.d[a.rank - 2] : a.d[a.rank - 1];
+      int64_t kb = n->trans_b ? b.d[b.rank - 1] : b.d[b.rank - 2];
+      int64_t nn = n->trans_b ? b.d[b.rank - 2] : b.d[b.rank - 1];
+      if (ka != kb) Fail(n, "matmul inner dimensions differ");
+      Shape ba, bb;
+      ba.rank = a.rank - 2;
+      bb.rank = b.rank - 2;
+      for (int i = 0; i < ba.rank; ++i) ba.d[i] = a.d[i];
+      for (int i = 0; i < bb.rank; ++i) bb.d[i] = b.d[i];
+      Shape o = BroadcastShapes(n, ba, bb);
+      if (o.rank > 2) Fail(n, "matmul supports at most two batch dims");
+      o.d[o.rank++] = m;
+      o.d[o.rank++] = nn;
+      n->shape = o;
+      break;
+    }
+  }
+}
+
+}  // namespace dvm

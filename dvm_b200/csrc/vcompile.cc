@@ -1,0 +1,1067 @@
+// Host JIT for one fused vector stage: operator list -> VmParam (geometry, tensor table, bytecode).
+//
+// This is the new-backend counterpart of the reference's vector scheduling and emission path
+// (VectorKernel::BuildDomain/ShapeTiling/ApplyTiling src/kernel.cc:765-1194, GPU CodeGenHelper::Generate
+// src/kernel.cc:206-257, op emitters src/ops.cc:769-3171).  The strategy is different: instead of tiling
+// into shared-memory slots, every op of the stage is evaluated over one iteration domain by an
+// accumulator machine held in registers; reductions split the program into phases and values needed
+// after a reduction are recomputed from the (cache-resident) inputs instead of being parked on chip.
+#include <algorithm>
+#include <cstring>
+#include <string>
+#include <unordered_map>
+
+#include "graph.h"
+#include "runtime.h"
+#include "vm_launch.h"
+
+namespace dvm {
+
+uint32_t EncodeScalarRefNow(const ScalarRef *ref, DataType dtype);
+
+namespace {
+
+using namespace dvmb;
+
+struct Fail {
+  std::string why;
+};
+
+bool IsIntRepr(DataType t) { return t == kInt32 || t == kBool; }
+
+struct Info {
+  int axis[kMaxRank];        // domain axis of each API dim
+  int64_t asz[kMaxRank];     // size per domain axis (1 where absent or broadcast)
+  bool scalar_space = false;
+  int level = 0;
+  NDObject *canon = nullptr;  // value this node aliases (itself for real ops)
+  int slot = -1;              // tensor slot (loads / stores)
+  int rslot = -1;             // reduce partial slot
+  int sreg = -1;              // scalar register while live
+  int last_section = -1;      // last section index reading this scalar-space value
+};
+
+enum LocKind { L_NONE, L_ACC, L_REG, L_IMM };
+
+struct Compiler {
+  const std::vector<NDObject *> &ops;
+  VectorStage *out;
+  std::unordered_map<const NDObject *, int> index;
+  std::vector<Info> info;
+  int R = 0;                       // domain rank
+  int64_t dom[kMaxRank];
+  bool reduced[kMaxRank];
+  bool has_reduce = false;
+  std::vector<int> kept_axes, enum_axes;   // domain axes, outer -> inner
+  // coalesced geometry
+  struct CoAxis {
+    int64_t size;
+    std::vector<int> members;   // domain axes merged into this one (outer -> inner)
+  };
+  std::vector<CoAxis> ckept, cenum;
+  int num_body = 0;
+  std::vector<uint64_t> code;
+  std::vector<NDObject *> slot_nodes;
+
+  Compiler(const std::vector<NDObject *> &o, VectorStage *st) : ops(o), out(st) {}
+
+  Info &I(const NDObject *n) { return info[index.at(n)]; }
+
+  // ---- step 1: align every node's dims to domain axes -------------------------------------------
+  void AlignAxes() {
+    R = 0;
+    for (auto n : ops) R = std::max(R, n->shape.rank);
+    if (R > kMaxRank) throw Fail{"domain rank above 8"};
+    for (auto n : ops) {
+      Info &fi = I(n);
+      const int r = n->shape.rank;
+      auto right_align = [&]() {
+        for (int i = 0; i < r; ++i) fi.axis[i] = R - r + i;
+      };
+      switch (n->kind) {
+        case N_LOAD:
+        case N_BROADCAST_S: right_align(); break;
+        case N_REDUCE: {
+          const NDObject *src = n->in[0];
+          const Info &si = I(src);
+          bool red[kMaxRank] = {false};
+          for (size_t i = 0; i < n->shape_ref->size; ++i) {
+            int64_t d = n->shape_ref->data[i];
+            if (d < 0) d += src->shape.rank;
+            red[d] = true;
+          }
+          int o = 0;
+          for (int i = 0; i < src->shape.rank; ++i) {
+            if (red[i] && !n->keepdims) continue;
+            fi.axis[o++] = si.axis[i];
+          }
+          break;
+        }
+        case N_RESHAPE: {
+          // Supported in-stage only when it inserts or removes unit dims: non-unit dims keep their axes.
+          const NDObject *src = n->in[0];
+          const Info &si = I(src);
+          std::vector<int> src_axes;
+          std::vector<int64_t> src_sizes;
+          for (int i = 0; i < src->shape.rank; ++i)
+            if (src->shape.d[i] != 1) {
+              src_axes.push_back(si.axis[i]);
+              src_sizes.push_back(src->shape.d[i]);
+            }
+          size_t j = 0;
+          right_align();
+          // unit dims of the result sit on their right-aligned axis only if that axis is not claimed
+          for (int i = 0; i < r; ++i) {
+            if (n->shape.d[i] == 1) continue;
+            if (j >= src_axes.size() || src_sizes[j] != n->shape.d[i]) throw Fail{"general reshape inside a stage"};
+            fi.axis[i] = src_axes[j++];
+          }
+          if (j != src_axes.size()) throw Fail{"general reshape inside a stage"};
+          // give unit dims any axis that keeps the list strictly increasing; fall back to -1 (ignored)
+          for (int i = 0; i < r; ++i)
+            if (n->shape.d[i] == 1) fi.axis[i] = -1;
+          break;
+        }
+        case N_BROADCAST: {
+          const NDObject *src = n->in[0];
+          const Info &si = I(src);
+          right_align();
+          for (int i = 0; i < src->shape.rank; ++i) {
+            int oi = i + (r - src->shape.rank);
+            if (si.axis[i] >= 0) fi.axis[oi] = si.axis[i];
+          }
+          break;
+        }
+        case N_BINARY:
+        case N_COMPARE:
+        case N_SELECT: {
+          right_align();
+          bool fixed[kMaxRank] = {false};
+          int nin = n->kind == N_SELECT ? 3 : 2;
+          for (int k = 0; k < nin; ++k) {
+            NDObject *src = n->in[k];
+            Info &si = I(src);
+            const int sr = src->shape.rank;
+            for (int i = 0; i < sr; ++i) {
+              int oi = i + (r - sr);
+              if (src->shape.d[i] == 1 || si.axis[i] < 0) continue;
+              if (!fixed[oi]) {
+                fi.axis[oi] = si.axis[i];
+                fixed[oi] = true;
+              } else if (fi.axis[oi] != si.axis[i]) {
+                // a plain input can simply be re-anchored onto the axes its partner uses
+                if (src->kind == N_LOAD || src->kind == N_BROADCAST_S) {
+                  si.axis[i] = fi.axis[oi];
+                } else {
+                  throw Fail{"operands iterate different axes"};
+                }
+              }
+            }
+          }
+          break;
+        }
+        default: {
+          const Info &si = I(n->in[0]);
+          for (int i = 0; i < r; ++i) fi.axis[i] = si.axis[i];
+          break;
+        }
+      }
+    }
+    // domain sizes
+    for (int a = 0; a < R; ++a) dom[a] = 1;
+    for (auto n : ops) {
+      Info &fi = I(n);
+      for (int a = 0; a < R; ++a) fi.asz[a] = 1;
+      for (int i = 0; i < n->shape.rank; ++i) {
+        int a = fi.axis[i];
+        if (a < 0) continue;
+        if (a >= R) throw Fail{"axis out of range"};
+        if (n->shape.d[i] != 1) {
+          fi.asz[a] = n->shape.d[i];
+          if (dom[a] != 1 && dom[a] != n->shape.d[i]) throw Fail{"ops disagree on a domain extent"};
+          dom[a] = n->shape.d[i];
+        }
+      }
+    }
+  }
+
+  // ---- step 2: reductions, spaces, levels ---------------------------------------------------------
+  void Classify() {
+    for (int a = 0; a < R; ++a) reduced[a] = false;
+    bool first = true;
+    for (auto n : ops) {
+      if (n->kind != N_REDUCE) continue;
+      const NDObject *src = n->in[0];
+      const Info &si = I(src);
+      bool mine[kMaxRank] = {false};
+      for (size_t i = 0; i < n->shape_ref->size; ++i) {
+        int64_t d = n->shape_ref->data[i];
+        if (d < 0) d += src->shape.rank;
+        int a = si.axis[d];
+        if (a >= 0 && dom[a] != 1) mine[a] = true;
+      }
+      if (first) {
+        for (int a = 0; a < R; ++a) reduced[a] = mine[a];
+        first = false;
+      } else {
+        for (int a = 0; a < R; ++a)
+          if (reduced[a] != mine[a]) throw Fail{"reductions over different axes in one stage"};
+      }
+      has_reduce = true;
+    }
+    int nred = 0;
+    for (int a = 0; a < R; ++a) nred += reduced[a] ? 1 : 0;
+    if (has_reduce && nred == 0) has_reduce = false;   // every reduced axis has extent 1: plain copies
+    for (auto n : ops) {
+      Info &fi = I(n);
+      bool varies = false;
+      for (int a = 0; a < R; ++a) {
+        if (fi.asz[a] == 1) continue;
+        if (!has_reduce || reduced[a]) varies = true;
+      }
+      fi.scalar_space = !varies;
+      // canonical value
+      fi.canon = n;
+      switch (n->kind) {
+        case N_BROADCAST:
+        case N_RESHAPE:
+        case N_COPY: fi.canon = I(n->in[0]).canon; break;
+        case N_CAST:
+          if ((n->in[0]->dtype == kFloat16 || n->in[0]->dtype == kBFloat16) && n->dtype == kFloat32)
+            fi.canon = I(n->in[0]).canon;
+          break;
+        case N_REDUCE:
+          if (!has_reduce) fi.canon = I(n->in[0]).canon;
+          break;
+        default: break;
+      }
+      int lvl = 0;
+      for (int k = 0; k < 3; ++k)
+        if (n->in[k]) lvl = std::max(lvl, I(n->in[k]).level);
+      if (n->kind == N_REDUCE && has_reduce) {
+        if (I(n->in[0]).scalar_space) throw Fail{"reduction of a value that does not vary along the reduced axes"};
+        lvl += 1;
+      }
+      fi.level = lvl;
+      if (n->kind == N_REDUCE && has_reduce && !fi.scalar_space) throw Fail{"partial reduction result is not group-constant"};
+    }
+  }
+
+  // ---- step 3: geometry ---------------------------------------------------------------------------
+  // Element stride of tensor node `n` (contiguous in its own API shape) along domain axis `a`.
+  int64_t StrideOn(const NDObject *n, int a) {
+    const Info &fi = I(n);
+    int64_t st = 1;
+    for (int i = n->shape.rank - 1; i >= 0; --i) {
+      if (fi.axis[i] == a && n->shape.d[i] != 1) return st;
+      st *= n->shape.d[i];
+    }
+    return 0;
+  }
+
+  void Coalesce(const std::vector<int> &axes, std::vector<CoAxis> *outv, bool vector_only) {
+    outv->clear();
+    for (int a : axes) {
+      if (dom[a] == 1) continue;
+      if (!outv->empty()) {
+        CoAxis &prev = outv->back();
+        int pa = prev.members.back();   // innermost member of the previous (outer) group
+        bool ok = true;
+        for (auto n : slot_nodes) {
+          if (vector_only && I(n).scalar_space) continue;
+          // merging requires stride(outer) == stride(inner) * size(inner) for every tensor
+          int64_t so = StrideOn(n, pa), si = StrideOn(n, a);
+          if (so != si * dom[a]) {
+            ok = false;
+            break;
+          }
+        }
+        if (ok) {
+          prev.size *= dom[a];
+          prev.members.push_back(a);
+          continue;
+        }
+      }
+      outv->push_back(CoAxis{dom[a], {a}});
+    }
+  }
+
+  void Geometry() {
+    for (auto n : ops)
+      if (n->kind == N_LOAD || n->kind == N_STORE) {
+        I(n).slot = static_cast<int>(slot_nodes.size());
+        slot_nodes.push_back(n);
+      }
+    if (slot_nodes.size() > static_cast<size_t>(kMaxTensors)) throw Fail{"more than 16 tensors in one stage"};
+    kept_axes.clear();
+    enum_axes.clear();
+    for (int a = 0; a < R; ++a) {
+      if (has_reduce && !reduced[a]) {
+        kept_axes.push_back(a);
+      } else {
+        enum_axes.push_back(a);
+      }
+    }
+    Coalesce(kept_axes, &ckept, false);
+    Coalesce(enum_axes, &cenum, true);
+    if (ckept.size() > static_cast<size_t>(kMaxKept)) throw Fail{"more than 3 kept axes after coalescing"};
+    if (cenum.size() > static_cast<size_t>(kMaxEnum)) throw Fail{"more than 4 iterated axes after coalescing"};
+  }
+
+  // ---- step 4: code emission ----------------------------------------------------------------------
+  uint32_t RoundOf(const NDObject *n) {
+    return n->dtype == kFloat16 ? RN_F16 : (n->dtype == kBFloat16 ? RN_BF16 : RN_NONE);
+  }
+
+  uint32_t ScalarBits(const NDObject *n) {
+    return n->scalar_ref ? EncodeScalarRefNow(n->scalar_ref, n->dtype) : n->scalar_bits;
+  }
+
+  struct Operand {
+    uint32_t kind, idx, imm;
+  };
+
+  // One section's accumulator-machine emitter.  Vector side: values live in acc / vregs for the section
+  // only.  Scalar side: values live in sacc / sregs and persist across sections (Info::sreg).
+  struct Side {
+    Compiler *c;
+    bool scalar;
+    int section;
+    const NDObject *acc_val = nullptr;
+    std::vector<const NDObject *> reg_val;
+    std::unordered_map<const NDObject *, int> uses;      // remaining uses inside this section
+    std::unordered_map<const NDObject *, int> vreg_of;   // vector side only
+
+    void Push(uint32_t opc, uint32_t sub, Operand o, uint32_t dst, uint32_t rnd, uint32_t isint) {
+      c->code.push_back(Insn::make(opc, sub, o.kind, o.idx, dst, rnd, isint, scalar ? 1 : 0, o.imm));
+    }
+    void Push0(uint32_t opc, uint32_t sub, uint32_t dst = 0, uint32_t rnd = 0, uint32_t isint = 0) {
+      Push(opc, sub, Operand{0, 0, 0}, dst, rnd, isint);
+    }
+
+    int RegOf(const NDObject *v) {
+      if (scalar) return c->I(v).sreg;
+      auto it = vreg_of.find(v);
+      return it == vreg_of.end() ? -1 : it->second;
+    }
+
+    bool NeededLater(const NDObject *v) {
+      auto it = uses.find(v);
+      if (it != uses.end() && it->second > 0) return true;
+      if (scalar && c->I(v).last_section > section) return true;
+      return false;
+    }
+
+    int AllocReg(const NDObject *v) {
+      const int n = scalar ? kNumSRegs : kNumVRegs;
+      if (static_cast<int>(reg_val.size()) < n) reg_val.resize(n, nullptr);
+      for (int i = 0; i < n; ++i) {
+        if (reg_val[i] == nullptr) {
+          reg_val[i] = v;
+          if (scalar) {
+            c->I(v).sreg = i;
+          } else {
+            vreg_of[v] = i;
+          }
+          return i;
+        }
+      }
+      throw Fail{scalar ? "out of scalar registers" : "out of vector registers"};
+    }
+
+    void FreeIfDead(const NDObject *v) {
+      if (NeededLater(v)) return;
+      int r = RegOf(v);
+      if (r >= 0) {
+        reg_val[r] = nullptr;
+        if (scalar) {
+          c->I(v).sreg = -1;
+        } else {
+          vreg_of.erase(v);
+        }
+      }
+    }
+
+    // Keep the accumulator's value alive in a register if something still needs it.
+    void SaveAcc() {
+      if (acc_val == nullptr) return;
+      if (RegOf(acc_val) >= 0) return;
+      if (!NeededLater(acc_val)) return;
+      int r = AllocReg(acc_val);
+      Push0(OP_MOV, 0, r);
+    }
+
+    // The accumulator is about to be overwritten by an op that reads it: park its value if later ops
+    // still need it (call after Consume()).
+    void ParkAccIfNeeded() { SaveAcc(); }
+
+    int AllocTemp() {
+      const int n = scalar ? kNumSRegs : kNumVRegs;
+      if (static_cast<int>(reg_val.size()) < n) reg_val.resize(n, nullptr);
+      static const NDObject kTempMarker{};
+      for (int i = 0; i < n; ++i)
+        if (reg_val[i] == nullptr) {
+          reg_val[i] = &kTempMarker;
+          return i;
+        }
+      throw Fail{scalar ? "out of scalar registers" : "out of vector registers"};
+    }
+    void FreeTemp(int r) { reg_val[r] = nullptr; }
+
+    // Location of a value as a non-accumulator operand; loads it into a register if it is an input
+    // that has not been fetched yet.
+    Operand OperandOf(const NDObject *v) {
+      if (v->kind == N_BROADCAST_S) return Operand{K_IMM, 0, c->ScalarBits(v)};
+      const Info &vi = c->I(v);
+      if (!scalar && vi.scalar_space) {
+        if (vi.sreg < 0) throw Fail{"internal: group-constant value has no scalar register"};
+        return Operand{K_SREG, static_cast<uint32_t>(vi.sreg), 0};
+      }
+      int r = RegOf(v);
+      if (r >= 0) return Operand{scalar ? K_SREG : K_VREG, static_cast<uint32_t>(r), 0};
+      if (acc_val == v) return Operand{K_ACC, 0, 0};
+      if (v->kind == N_LOAD) {
+        r = AllocReg(v);
+        Push0(OP_LD, vi.slot, r);
+        return Operand{scalar ? K_SREG : K_VREG, static_cast<uint32_t>(r), 0};
+      }
+      throw Fail{"internal: operand value is not available"};
+    }
+
+    // Bring `v` into the accumulator.
+    void ToAcc(const NDObject *v) {
+      if (acc_val == v) return;
+      SaveAcc();
+      if (v->kind == N_LOAD && RegOf(v) < 0 && (scalar || !c->I(v).scalar_space)) {
+        Push0(OP_LD, c->I(v).slot, kAccIdx);
+      } else {
+        Operand o = OperandOf(v);
+        Push(OP_COPY, 0, o, 0, 0, 0);
+      }
+      acc_val = v;
+    }
+
+    void Consume(const NDObject *v) {
+      auto it = uses.find(v);
+      if (it != uses.end() && it->second > 0) --it->second;
+    }
+
+    void Release(const NDObject *v) {
+      if (v->kind == N_BROADCAST_S) return;
+      if (!scalar && c->I(v).scalar_space) return;
+      FreeIfDead(v);
+    }
+  };
+
+  const NDObject *Canon(const NDObject *n) { return I(n).canon; }
+
+  // Emit the computation of canonical node `n` on `s`; the value ends in the accumulator.
+  // Protocol: operands are located (loading inputs on demand) while their use counts still include
+  // this op, so anything the accumulator must give up is parked in a register first; then the uses are
+  // consumed, the accumulator operand is parked if later ops still read it, and the op is pushed.
+  void EmitNode(Side &s, const NDObject *n) {
+    const uint32_t rnd = RoundOf(n);
+    const bool isint = IsIntRepr(n->dtype);
+    auto finish_unary_like = [&](const NDObject *x) {
+      s.Consume(x);
+      s.ParkAccIfNeeded();
+    };
+    switch (n->kind) {
+      case N_LOAD:
+      case N_BROADCAST_S: return;   // fetched on demand / immediate
+      case N_UNARY: {
+        const NDObject *x = Canon(n->in[0]);
+        s.ToAcc(x);
+        finish_unary_like(x);
+        static const uint32_t map[] = {U_SQRT, U_ABS, U_LOG, U_EXP, U_NOP, U_ISFINITE, U_NOP, U_ROUND, U_FLOOR, U_CEIL, U_TRUNC};
+        uint32_t kind = map[n->sub];
+        if (n->sub == kAbs && isint) kind = U_ABS_I;
+        const bool exact = n->sub == kAbs || n->sub == kIsFinite || n->sub >= kRound;
+        s.Push0(OP_UN, kind, 0, exact ? RN_NONE : rnd);
+        s.acc_val = n;
+        s.Release(x);
+        return;
+      }
+      case N_CAST: {
+        const NDObject *x = Canon(n->in[0]);
+        s.ToAcc(x);
+        finish_unary_like(x);
+        const DataType from = n->in[0]->dtype, to = n->dtype;
+        const bool from_int = IsIntRepr(from), to_int = IsIntRepr(to);
+        uint32_t kind = V_RND, r = RN_NONE;
+        if (to == kBool) {
+          kind = from_int ? V_NEZ_I : V_NEZ_F;
+        } else if (from_int && !to_int) {
+          kind = V_I2F;
+          r = rnd;
+        } else if (!from_int && to_int) {
+          kind = V_F2I;
+        } else if (!from_int) {
+          r = rnd;   // float narrowing; bool -> int32 keeps its bits
+        }
+        s.Push0(OP_CVT, kind, 0, r);
+        s.acc_val = n;
+        s.Release(x);
+        return;
+      }
+      case N_BINARY_S:
+      case N_COMPARE_S: {
+        const NDObject *x = Canon(n->in[0]);
+        s.ToAcc(x);
+        finish_unary_like(x);
+        Operand o{K_IMM, 0, ScalarBits(n)};
+        if (n->kind == N_COMPARE_S) {
+          s.Push(OP_CMP, n->sub, o, 0, 0, isint);
+        } else {
+          static const uint32_t fmap[] = {B_ADD, B_MUL, B_DIV, B_RDIV, B_MAX, B_MIN};
+          static const uint32_t imap[] = {B_ADD_I, B_MUL_I, B_COUNT, B_COUNT, B_MAX_I, B_MIN_I};
+          uint32_t kind = isint ? imap[n->sub] : fmap[n->sub];
+          if (kind == B_COUNT) throw Fail{"integer division is not supported"};
+          const bool exact = n->sub == SB_MAX || n->sub == SB_MIN;
+          s.Push(OP_BIN, kind, o, 0, exact ? RN_NONE : rnd, 0);
+        }
+        s.acc_val = n;
+        s.Release(x);
+        return;
+      }
+      case N_BINARY:
+      case N_COMPARE: {
+        const NDObject *x = Canon(n->in[0]);
+        const NDObject *y = Canon(n->in[1]);
+        uint32_t kind = 0, rkind = B_COUNT;   // rkind: the same op with its operands swapped
+        bool exact = false;
+        if (n->kind == N_BINARY) {
+          switch (n->sub) {
+            case kAdd: kind = rkind = isint ? B_ADD_I : B_ADD; break;
+            case kMul: kind = rkind = isint ? B_MUL_I : B_MUL; break;
+            case kSub: kind = isint ? B_SUB_I : B_SUB; rkind = isint ? B_RSUB_I : B_RSUB; break;
+            case kDiv:
+              if (isint) throw Fail{"integer division is not supported"};
+              kind = B_DIV; rkind = B_RDIV; break;
+            case kPow:
+              if (isint) throw Fail{"integer pow is not supported"};
+              kind = B_POW; break;
+            // float max/min are `a > b ? a : b`: not symmetric for NaN and signed zero, so never mirrored
+            case kMaximum: case kLogicalOr: kind = isint ? B_MAX_I : B_MAX; exact = true; if (isint) rkind = kind; break;
+            case kMinimum: case kLogicalAnd: kind = isint ? B_MIN_I : B_MIN; exact = true; if (isint) rkind = kind; break;
+            default: throw Fail{"unknown binary op"};
+          }
+        } else {
+          static const uint32_t mirrored[] = {C_EQ, C_NE, C_LT, C_LE, C_GT, C_GE};
+          kind = n->sub;
+          rkind = mirrored[n->sub];
+        }
+        Operand o;
+        bool swapped = false;
+        if (x == y) {
+          s.ToAcc(x);
+          o = Operand{K_ACC, 0, 0};
+        } else if (s.acc_val == y && rkind != B_COUNT) {
+          swapped = true;
+          o = s.OperandOf(x);
+        } else {
+          s.ToAcc(x);          // parks y first if y sat in the accumulator
+          o = s.OperandOf(y);
+        }
+        s.Consume(x);
+        s.Consume(y);
+        s.ParkAccIfNeeded();
+        if (n->kind == N_COMPARE) {
+          s.Push(OP_CMP, swapped ? rkind : kind, o, 0, 0, IsIntRepr(n->in[0]->dtype));
+        } else {
+          s.Push(OP_BIN, swapped ? rkind : kind, o, 0, exact ? RN_NONE : rnd, 0);
+        }
+        s.acc_val = n;
+        s.Release(x);
+        if (y != x) s.Release(y);
+        return;
+      }
+      case N_SELECT: {
+        const NDObject *cnd = Canon(n->in[0]);
+        const NDObject *a = Canon(n->in[1]);
+        const NDObject *b = Canon(n->in[2]);
+        // The instruction takes one free-form operand (register / scalar / immediate / accumulator) and
+        // one register-or-scalar operand; `inv` makes the free-form one the "false" alternative.
+        auto reg_like = [&](const NDObject *v) {
+          if (v->kind == N_BROADCAST_S) return false;
+          if (!s.scalar && I(v).scalar_space) return true;
+          return v != cnd;   // anything else can be given a register
+        };
+        bool inv = false;
+        const NDObject *free_v = a, *reg_v = b;
+        if (!reg_like(b)) {
+          if (!reg_like(a)) {
+            // both alternatives are immediates (or the condition itself): materialise b in a register
+            s.SaveAcc();
+            s.Push(OP_COPY, 0, s.OperandOf(b), 0, 0, 0);
+            int r = s.AllocTemp();
+            s.Push0(OP_MOV, 0, r);
+            s.acc_val = nullptr;
+            s.ToAcc(cnd);
+            Operand oa = a == cnd ? Operand{K_ACC, 0, 0} : s.OperandOf(a);
+            s.Consume(cnd); s.Consume(a); s.Consume(b);
+            s.ParkAccIfNeeded();
+            s.Push(OP_SEL, ((s.scalar ? K_SREG : K_VREG) << 4) | r, oa, 0, 0, IsIntRepr(n->in[0]->dtype));
+            s.FreeTemp(r);
+            s.acc_val = n;
+            s.Release(cnd); s.Release(a); s.Release(b);
+            return;
+          }
+          inv = true;
+          free_v = b;
+          reg_v = a;
+        }
+        // reg_v needs a register (or scalar register) location before the condition takes the accumulator
+        if (s.acc_val == reg_v && s.RegOf(reg_v) < 0 && !(!s.scalar && I(reg_v).scalar_space)) {
+          int r = s.AllocReg(reg_v);
+          s.Push0(OP_MOV, 0, r);
+        }
+        Operand orr = s.OperandOf(reg_v);
+        s.ToAcc(cnd);
+        if (orr.kind == K_ACC) throw Fail{"internal: select alternative lost its register"};
+        Operand of = free_v == cnd ? Operand{K_ACC, 0, 0} : s.OperandOf(free_v);
+        s.Consume(cnd); s.Consume(a); s.Consume(b);
+        s.ParkAccIfNeeded();
+        s.Push(OP_SEL, (orr.kind << 4) | orr.idx, of, inv ? 1 : 0, 0, IsIntRepr(n->in[0]->dtype));
+        s.acc_val = n;
+        s.Release(cnd); s.Release(a); s.Release(b);
+        return;
+      }
+      default: throw Fail{"op kind cannot run inside a vector stage"};
+    }
+  }
+
+  // Nodes (canonical, in program order) the vector body of level `q` must evaluate.
+  std::vector<const NDObject *> BodyNeeds(int q, std::vector<const NDObject *> *roots) {
+    std::vector<char> need(ops.size(), 0);
+    roots->clear();
+    for (auto n : ops) {
+      if (n->kind == N_STORE && !I(n).scalar_space && I(n).level == q) roots->push_back(n);
+      if (n->kind == N_REDUCE && has_reduce && I(n->in[0]).level == q) roots->push_back(n);
+    }
+    std::vector<const NDObject *> stack;
+    for (auto r : *roots) stack.push_back(Canon(r->in[0]));
+    while (!stack.empty()) {
+      const NDObject *v = stack.back();
+      stack.pop_back();
+      if (I(v).scalar_space || v->kind == N_BROADCAST_S) continue;
+      int idx = index.at(v);
+      if (need[idx]) continue;
+      need[idx] = 1;
+      for (int k = 0; k < 3; ++k)
+        if (v->in[k]) stack.push_back(Canon(v->in[k]));
+    }
+    std::vector<const NDObject *> order;
+    for (size_t i = 0; i < ops.size(); ++i)
+      if (need[i]) order.push_back(ops[i]);
+    return order;
+  }
+
+  void CountUses(Side &s, const std::vector<const NDObject *> &order, const std::vector<const NDObject *> &roots) {
+    for (auto v : order)
+      for (int k = 0; k < 3; ++k)
+        if (v->in[k]) s.uses[Canon(v->in[k])]++;
+    for (auto r : roots) s.uses[Canon(r->in[0])]++;
+  }
+
+  void Emit() {
+    // levels present
+    int max_vec_level = -1, max_level = 0;
+    for (auto n : ops) {
+      const Info &fi = I(n);
+      max_level = std::max(max_level, fi.level);
+      if (n->kind == N_STORE && !fi.scalar_space) max_vec_level = std::max(max_vec_level, fi.level);
+      if (n->kind == N_REDUCE && has_reduce) max_vec_level = std::max(max_vec_level, I(n->in[0]).level);
+    }
+    num_body = max_vec_level + 1;
+    if (num_body > kMaxPhases) throw Fail{"more than 4 dependent reduction phases"};
+    // reduce slots
+    int nslots = 0;
+    for (auto n : ops)
+      if (n->kind == N_REDUCE && has_reduce) {
+        if (nslots >= kNumRSlots) throw Fail{"more than 4 reductions in one stage"};
+        I(n).rslot = nslots++;
+      }
+    // body plans first: they define how long group-constant values must stay in scalar registers
+    std::vector<std::vector<const NDObject *>> body_order(num_body), body_roots(num_body);
+    for (int q = 0; q < num_body; ++q) body_order[q] = BodyNeeds(q, &body_roots[q]);
+    auto touch = [&](const NDObject *v, int section) {
+      Info &vi = I(v);
+      if (vi.scalar_space) vi.last_section = std::max(vi.last_section, section);
+    };
+    for (int q = 0; q < num_body; ++q) {
+      for (auto v : body_order[q])
+        for (int k = 0; k < 3; ++k)
+          if (v->in[k]) touch(Canon(v->in[k]), 2 * q + 1);
+      for (auto r : body_roots[q]) touch(Canon(r->in[0]), 2 * q + 1);
+    }
+    // scalar-side plans
+    if (max_level > num_body) throw Fail{"internal: scalar work beyond the last phase"};
+    const int num_pro = num_body + 1;
+    std::vector<std::vector<const NDObject *>> pro_order(num_pro);
+    for (auto n : ops) {
+      const Info &fi = I(n);
+      if (!fi.scalar_space) continue;
+      if (n->kind == N_STORE) {
+        pro_order[fi.level].push_back(n);
+        touch(Canon(n->in[0]), 2 * fi.level);
+        continue;
+      }
+      if (fi.canon != n || n->kind == N_BROADCAST_S) continue;
+      pro_order[fi.level].push_back(n);
+      if (n->kind == N_REDUCE) continue;
+      for (int k = 0; k < 3; ++k)
+        if (n->in[k]) touch(Canon(n->in[k]), 2 * fi.level);
+    }
+    // emit
+    VmParam &P = out->param;
+    std::vector<const NDObject *> sreg_val(kNumSRegs, nullptr);
+    for (int p = 0; p <= num_body; ++p) {
+      // ---- PRO_p
+      P.sec[2 * p] = static_cast<uint16_t>(code.size());
+      Side ss{this, true, 2 * p};
+      ss.reg_val = sreg_val;
+      if (p == 0) {
+        for (auto n : ops)
+          if (n->kind == N_REDUCE && has_reduce) ss.Push0(OP_RINIT, I(n).rslot | (n->sub << 4));
+      }
+      // free scalar registers whose value is dead by now
+      for (int i = 0; i < kNumSRegs; ++i)
+        if (ss.reg_val[i] && I(ss.reg_val[i]).last_section < 2 * p) {
+          I(ss.reg_val[i]).sreg = -1;
+          ss.reg_val[i] = nullptr;
+        }
+      for (auto n : pro_order[p])
+        for (int k = 0; k < 3; ++k)
+          if (n->in[k] && n->kind != N_REDUCE) ss.uses[Canon(n->in[k])]++;
+      for (auto n : pro_order[p]) {
+        if (n->kind == N_STORE) {
+          const NDObject *v = Canon(n->in[0]);
+          ss.Consume(v);
+          ss.ToAcc(v);
+          ss.Push0(OP_ST, I(n).slot);
+          ss.Release(v);
+          continue;
+        }
+        if (n->kind == N_REDUCE) {
+          ss.SaveAcc();
+          ss.Push0(OP_RFIN, I(n).rslot | (n->sub << 4));
+          ss.acc_val = n;
+        } else if (n->kind == N_LOAD) {
+          int r = ss.AllocReg(n);
+          ss.Push0(OP_LD, I(n).slot, r);
+          continue;
+        } else {
+          EmitNode(ss, n);
+        }
+        // a group-constant value read by a later section lives in a scalar register; values consumed
+        // inside this section stay in the accumulator until something else needs it
+        if (I(n).last_section > ss.section && ss.RegOf(n) < 0) {
+          int r = ss.AllocReg(n);
+          ss.Push0(OP_MOV, 0, r);
+        }
+      }
+      ss.Push0(OP_END, 0);
+      sreg_val = ss.reg_val;
+      if (p == num_body) break;
+      // ---- BODY_p
+      P.sec[2 * p + 1] = static_cast<uint16_t>(code.size());
+      Side vs{this, false, 2 * p + 1};
+      CountUses(vs, body_order[p], body_roots[p]);
+      // issue the input fetches first so that every load of the chunk is in flight together
+      {
+        std::vector<const NDObject *> loads;
+        for (auto v : body_order[p])
+          if (v->kind == N_LOAD) loads.push_back(v);
+        // the value the first op (or, with no ops, the first store/reduction) consumes through the
+        // accumulator is fetched straight into it
+        const NDObject *first_x = nullptr;
+        bool any_op = false;
+        for (auto v : body_order[p]) {
+          if (v->kind == N_LOAD || v->kind == N_BROADCAST_S) continue;
+          const NDObject *x = Canon(v->in[0]);
+          if (x->kind == N_LOAD && !I(x).scalar_space && vs.uses[x] == 1) first_x = x;
+          any_op = true;
+          break;
+        }
+        if (!any_op && !body_roots[p].empty()) {
+          const NDObject *x = Canon(body_roots[p][0]->in[0]);
+          if (x->kind == N_LOAD && !I(x).scalar_space) first_x = x;
+        }
+        if (static_cast<int>(loads.size()) <= kNumVRegs - 2 + (first_x ? 1 : 0)) {
+          for (auto v : loads) {
+            if (v == first_x) continue;
+            int r = vs.AllocReg(v);
+            vs.Push0(OP_LD, I(v).slot, r);
+          }
+          if (first_x) {
+            vs.Push0(OP_LD, I(first_x).slot, kAccIdx);
+            vs.acc_val = first_x;
+          }
+        }
+      }
+      // roots are interleaved in program order: emit each as soon as its value exists
+      std::vector<const NDObject *> pending = body_roots[p];
+      auto flush_roots = [&](const NDObject *just_made) {
+        for (auto &r : pending) {
+          if (r == nullptr) continue;
+          const NDObject *v = Canon(r->in[0]);
+          if (v != just_made) continue;
+          vs.Consume(v);
+          vs.ToAcc(v);
+          if (r->kind == N_STORE) {
+            vs.Push0(OP_ST, I(r).slot);
+          } else {
+            vs.Push0(OP_RACC, I(r).rslot | (r->sub << 4));
+          }
+          vs.Release(v);
+          r = nullptr;
+        }
+      };
+      for (auto v : body_order[p]) {
+        if (v->kind != N_LOAD && v->kind != N_BROADCAST_S) EmitNode(vs, v);
+        flush_roots(v);
+      }
+      for (auto r : pending)
+        if (r != nullptr) throw Fail{"internal: a store or reduction lost its value"};
+      vs.Push0(OP_END, 0);
+    }
+    if (code.size() > static_cast<size_t>(kMaxCodeWords)) throw Fail{"program exceeds the bytecode capacity"};
+  }
+
+  // ---- step 5: fill VmParam -----------------------------------------------------------------------
+  void Fill() {
+    VmParam &P = out->param;
+    P.num_body = num_body;
+    P.n_code = static_cast<uint32_t>(code.size());
+    std::memcpy(P.code, code.data(), code.size() * sizeof(uint64_t));
+    int64_t K = 1, G = 1;
+    for (auto &a : ckept) K *= a.size;
+    for (auto &a : cenum) G *= a.size;
+    if (G >= (1ll << 31) || K >= (1ll << 31)) throw Fail{"iteration domain above 2^31 elements"};
+    for (int j = 0; j < kMaxKept; ++j) P.kept_size[j] = 1;
+    for (int j = 0; j < kMaxEnum; ++j) P.enum_size[j] = 1;
+    for (size_t j = 0; j < ckept.size(); ++j)
+      P.kept_size[kMaxKept - ckept.size() + j] = static_cast<uint32_t>(ckept[j].size);
+    for (size_t j = 0; j < cenum.size(); ++j)
+      P.enum_size[kMaxEnum - cenum.size() + j] = static_cast<uint32_t>(cenum[j].size);
+    P.num_groups = static_cast<uint32_t>(K);
+    P.group_elems = static_cast<uint32_t>(G);
+    const int sms = Runtime::Get().sm_count_or_default();
+    bool zero = false;
+    for (auto n : ops)
+      if (n->shape.numel() == 0) zero = true;
+    out->idle = zero;
+    if (!has_reduce) {
+      P.mode = VM_FLAT;
+      P.tg = kVmMaxThreads;
+      P.groups_per_cta = 1;
+      P.chunks = static_cast<uint32_t>((G + 8 * P.tg - 1) / (8 * P.tg));
+      out->threads = P.tg;
+      out->grid = std::max<uint32_t>(1u, std::min<uint32_t>(P.chunks, sms * kVmMinBlocks * 2));
+      if (num_body == 0) out->grid = 1;
+    } else {
+      P.mode = VM_GROUP;
+      if (G <= 8 * 32) {
+        uint32_t tg = 1;
+        while (8 * tg < G) tg <<= 1;
+        P.tg = tg;
+        P.groups_per_cta = kVmMaxThreads / tg;
+        P.chunks = 1;
+        out->threads = kVmMaxThreads;
+      } else {
+        uint32_t chunks = static_cast<uint32_t>((G + 8 * kVmMaxThreads - 1) / (8 * kVmMaxThreads));
+        uint32_t per = static_cast<uint32_t>((G + 8ll * chunks - 1) / (8ll * chunks));
+        uint32_t tg = ((per + 31) / 32) * 32;
+        P.tg = tg;
+        P.groups_per_cta = 1;
+        P.chunks = static_cast<uint32_t>((G + 8ll * tg - 1) / (8ll * tg));
+        out->threads = tg;
+      }
+      uint32_t ngb = (P.num_groups + P.groups_per_cta - 1) / P.groups_per_cta;
+      out->grid = std::max<uint32_t>(1u, std::min<uint32_t>(ngb, sms * kVmMinBlocks * 2));
+    }
+    // tensors
+    P.n_tensors = static_cast<uint32_t>(slot_nodes.size());
+    P.need_coords = 0;
+    out->slot_obj.assign(slot_nodes.begin(), slot_nodes.end());
+    out->algo_bytes = 0;
+    for (size_t sidx = 0; sidx < slot_nodes.size(); ++sidx) {
+      NDObject *n = slot_nodes[sidx];
+      TensorDesc &td = P.tensor[sidx];
+      std::memset(&td, 0, sizeof(td));
+      td.ptr = reinterpret_cast<uint64_t>(n->addr);
+      td.dtype = static_cast<uint8_t>(n->dtype);
+      if (n->dtype == kInt64) throw Fail{"int64 tensors are not supported by the vector interpreter"};
+      if (n->shape.numel() >= (1ll << 31)) throw Fail{"tensor above 2^31 elements"};
+      out->algo_bytes += static_cast<uint64_t>(n->shape.numel()) * ItemSize(n->dtype);
+      bool layout_vec = true;
+      for (size_t j = 0; j < ckept.size(); ++j) {
+        int64_t st = StrideOn(n, ckept[j].members.back());
+        td.kstride[kMaxKept - ckept.size() + j] = static_cast<uint32_t>(st);
+        if (st % 4 != 0) layout_vec = false;
+      }
+      if (I(n).scalar_space) {
+        td.mode = AM_SCALAR;
+        td.vec_ok = 0;
+        continue;
+      }
+      bool dense = true;
+      int64_t expect = 1;
+      for (int j = static_cast<int>(cenum.size()) - 1; j >= 0; --j) {
+        int64_t st = StrideOn(n, cenum[j].members.back());
+        td.estride[kMaxEnum - cenum.size() + j] = static_cast<uint32_t>(st);
+        if (st != expect) dense = false;
+        if (j != static_cast<int>(cenum.size()) - 1 && st % 4 != 0) layout_vec = false;
+        expect *= cenum[j].size;
+      }
+      const int64_t inner = cenum.empty() ? 1 : cenum.back().size;
+      const int64_t inner_stride = cenum.empty() ? 1 : StrideOn(n, cenum.back().members.back());
+      if (dense) {
+        td.mode = AM_DENSE;
+      } else if (inner % 4 == 0) {
+        td.mode = AM_GRANULE;
+        P.need_coords = 1;
+      } else {
+        td.mode = AM_ELEMENT;
+        layout_vec = false;
+      }
+      if (inner_stride != 1) layout_vec = false;
+      // pad doubles as "layout allows vector access"; vec_ok is finalised when the address is bound
+      td.pad = layout_vec ? 1 : 0;
+      td.vec_ok = 0;
+    }
+  }
+
+  void Run() {
+    for (size_t i = 0; i < ops.size(); ++i) index[ops[i]] = static_cast<int>(i);
+    info.assign(ops.size(), Info());
+    for (auto n : ops)
+      if (n->kind == N_MATMUL) throw Fail{"MatMul inside a vector stage"};
+    AlignAxes();
+    Classify();
+    Geometry();
+    Emit();
+    Fill();
+  }
+};
+
+const char *kOpNames[] = {"end", "ld", "st", "copy", "mov", "un", "bin", "cmp", "sel", "cvt", "racc", "rfin", "rinit"};
+const char *kUnNames[] = {"Sqrt", "Abs", "Log", "Exp", "Round", "Floor", "Ceil", "Trunc", "IsFinite", "Abs", "Nop"};
+const char *kBinNames[] = {"Add", "Sub", "Mul", "Div", "Max", "Min", "Pow", "RSub", "RDiv",
+                           "Add", "Sub", "Mul", "Max", "Min", "RSub"};
+const char *kCmpNames[] = {"Eq", "Ne", "Gt", "Ge", "Lt", "Le"};
+const char *kCvtNames[] = {"F2I", "I2F", "NeZ", "NeZ", "Round"};
+const char *kRedNames[] = {"Sum", "Max", "Min"};
+const char *kModeNames[] = {"dense", "granule", "element", "scalar"};
+
+}  // namespace
+
+bool CompileVectorStage(const std::vector<NDObject *> &ops, VectorStage *out, std::string *why) {
+  try {
+    std::memset(&out->param, 0, sizeof(out->param));
+    Compiler c(ops, out);
+    c.Run();
+    return true;
+  } catch (const Fail &f) {
+    if (why) *why = f.why;
+    return false;
+  }
+}
+
+// Text form of a stage's bytecode (the counterpart of the reference's disassembler, src/code.cc:1093-1498).
+// One line per instruction: "<pc>: <Name>.<type> <dst>, <operands>"; loads and stores print as
+// "load.<dtype> <dst>, <gm address>" / "store.<dtype> <gm address>, acc".
+std::string DisassembleStage(const VectorStage &st) {
+  using namespace dvmb;
+  const VmParam &P = st.param;
+  std::string o;
+  char buf[256];
+  snprintf(buf, sizeof(buf), "vmain.sm100(mode=%s, groups=%u, group_elems=%u, tg=%u, chunks=%u, grid=%u, threads=%u) {\n",
+           P.mode == VM_FLAT ? "flat" : "group", P.num_groups, P.group_elems, P.tg, P.chunks, st.grid, st.threads);
+  o += buf;
+  for (uint32_t t = 0; t < P.n_tensors; ++t) {
+    const TensorDesc &td = P.tensor[t];
+    snprintf(buf, sizeof(buf), "  // t%u: %s %s vec=%d kstride=[%u,%u,%u] estride=[%u,%u,%u,%u] @0x%llx\n", t,
+             DTypeName(static_cast<DataType>(td.dtype)), kModeNames[td.mode], td.vec_ok, td.kstride[0], td.kstride[1],
+             td.kstride[2], td.estride[0], td.estride[1], td.estride[2], td.estride[3],
+             static_cast<unsigned long long>(td.ptr));
+    o += buf;
+  }
+  auto operand = [&](uint64_t w) -> std::string {
+    char b[48];
+    switch (DVMB_OKIND(w)) {
+      case K_VREG: snprintf(b, sizeof(b), "v%u", DVMB_OIDX(w)); break;
+      case K_SREG: snprintf(b, sizeof(b), "s%u", DVMB_OIDX(w)); break;
+      case K_IMM: snprintf(b, sizeof(b), "#0x%08x", DVMB_IMM(w)); break;
+      default: snprintf(b, sizeof(b), "acc"); break;
+    }
+    return b;
+  };
+  static const char *rnd_names[] = {"", ".rn_f16", ".rn_bf16", ""};
+  for (uint32_t pc = 0; pc < P.n_code; ++pc) {
+    for (uint32_t sidx = 0; sidx <= 2 * P.num_body; ++sidx)
+      if (P.sec[sidx] == pc) {
+        snprintf(buf, sizeof(buf), " %s_%u:\n", (sidx & 1) ? "body" : "pro", sidx / 2);
+        o += buf;
+      }
+    const uint64_t w = P.code[pc];
+    const uint32_t opc = DVMB_OPC(w), sub = DVMB_SUB(w), dst = DVMB_DST(w);
+    const bool sc = DVMB_SCALAR(w);
+    const char *acc = sc ? "sacc" : "acc";
+    const char *rp = sc ? "s" : "v";
+    const char *ty = DVMB_ISINT(w) ? "int32" : "fp32";
+    switch (opc) {
+      case OP_END: snprintf(buf, sizeof(buf), "  %u: end\n", pc); break;
+      case OP_LD: {
+        const TensorDesc &td = P.tensor[sub];
+        char d[16];
+        if (dst == kAccIdx) snprintf(d, sizeof(d), "%s", acc); else snprintf(d, sizeof(d), "%s%u", rp, dst);
+        snprintf(buf, sizeof(buf), "  %u: load.%s %s, 0x%llx // t%u\n", pc, DTypeName(static_cast<DataType>(td.dtype)), d,
+                 static_cast<unsigned long long>(td.ptr), sub);
+        break;
+      }
+      case OP_ST: {
+        const TensorDesc &td = P.tensor[sub];
+        snprintf(buf, sizeof(buf), "  %u: store.%s 0x%llx, %s // t%u\n", pc, DTypeName(static_cast<DataType>(td.dtype)),
+                 static_cast<unsigned long long>(td.ptr), acc, sub);
+        break;
+      }
+      case OP_COPY: snprintf(buf, sizeof(buf), "  %u: copy %s, %s\n", pc, acc, operand(w).c_str()); break;
+      case OP_MOV: snprintf(buf, sizeof(buf), "  %u: mov %s%u, %s\n", pc, rp, dst, acc); break;
+      case OP_UN:
+        snprintf(buf, sizeof(buf), "  %u: %s.%s%s %s, %s\n", pc, kUnNames[sub], sub == U_ABS_I ? "int32" : "fp32",
+                 rnd_names[DVMB_RND(w)], acc, acc);
+        break;
+      case OP_BIN:
+        snprintf(buf, sizeof(buf), "  %u: %s.%s%s %s, %s, %s\n", pc, kBinNames[sub], sub >= B_ADD_I ? "int32" : "fp32",
+                 rnd_names[DVMB_RND(w)], acc, acc, operand(w).c_str());
+        break;
+      case OP_CMP:
+        snprintf(buf, sizeof(buf), "  %u: Cmp%s.%s %s, %s, %s\n", pc, kCmpNames[sub], ty, acc, acc, operand(w).c_str());
+        break;
+      case OP_SEL: {
+        char second[16];
+        snprintf(second, sizeof(second), "%s%u", (sub >> 4) == K_SREG ? "s" : "v", sub & 15u);
+        if (dst & 1u) {
+          snprintf(buf, sizeof(buf), "  %u: Select.%s %s, %s ? %s : %s\n", pc, ty, acc, acc, second, operand(w).c_str());
+        } else {
+          snprintf(buf, sizeof(buf), "  %u: Select.%s %s, %s ? %s : %s\n", pc, ty, acc, acc, operand(w).c_str(), second);
+        }
+        break;
+      }
+      case OP_CVT:
+        snprintf(buf, sizeof(buf), "  %u: Cvt%s%s %s, %s\n", pc, kCvtNames[sub], rnd_names[DVMB_RND(w)], acc, acc);
+        break;
+      case OP_RACC: snprintf(buf, sizeof(buf), "  %u: Reduce%s.acc p%u, acc\n", pc, kRedNames[sub >> 4], sub & 3u); break;
+      case OP_RFIN: snprintf(buf, sizeof(buf), "  %u: Reduce%s.fin sacc, p%u // bar\n", pc, kRedNames[sub >> 4], sub & 3u); break;
+      case OP_RINIT: snprintf(buf, sizeof(buf), "  %u: Reduce%s.init p%u\n", pc, kRedNames[sub >> 4], sub & 3u); break;
+      default: snprintf(buf, sizeof(buf), "  %u: ?\n", pc); break;
+    }
+    o += buf;
+  }
+  o += "}\n";
+  return o;
+}
+
+}  // namespace dvm

@@ -1,0 +1,192 @@
+// VKernel: owns the graph of one dvm::Kernel, runs shape inference, plans the launches and runs them.
+// Counterpart of the reference's VKernel / VKernelS lifecycle (Normalize/CodeGen/CodeGenR/Launch,
+// src/kernel.cc:104-156, 2113-2209) for the sm_100a interpreters.
+#include <chrono>
+#include <cstring>
+#include <string>
+
+#include "graph.h"
+#include "runtime.h"
+#include "vm_launch.h"
+
+namespace dvm {
+
+VKernel::~VKernel() {
+  for (auto n : nodes_) delete n;
+}
+
+NDObject *VKernel::NewNode(NodeKind kind, DataType dtype) {
+  auto n = new NDObject();
+  n->kind = kind;
+  n->dtype = dtype;
+  n->id = static_cast<int>(nodes_.size());
+  nodes_.push_back(n);
+  normalized_ = false;
+  compiled_ = false;
+  return n;
+}
+
+void VKernel::Normalize() {
+  for (auto n : nodes_) InferShape(n);
+  normalized_ = true;
+  compiled_ = false;
+}
+
+// Drop ops that no store depends on (the reference's dead-code pass, src/pass.cc:838-849).
+static std::vector<NDObject *> LiveOps(const std::vector<NDObject *> &nodes) {
+  std::vector<char> live(nodes.size(), 0);
+  for (size_t i = nodes.size(); i-- > 0;) {
+    NDObject *n = nodes[i];
+    if (n->kind == N_STORE) live[i] = 1;
+    if (!live[i]) continue;
+    for (int k = 0; k < 3; ++k)
+      if (n->in[k]) live[n->in[k]->id] = 1;
+  }
+  std::vector<NDObject *> out;
+  for (size_t i = 0; i < nodes.size(); ++i)
+    if (live[i]) out.push_back(nodes[i]);
+  return out;
+}
+
+size_t VKernel::Compile() {
+  if (!normalized_) Normalize();
+  stages_.clear();
+  ws_bytes_ = 0;
+  std::vector<NDObject *> ops = LiveOps(nodes_);
+  if (ops.empty()) {
+    compiled_ = true;
+    return 0;
+  }
+  stages_.emplace_back();
+  std::string why;
+  if (!CompileVectorStage(ops, &stages_.back(), &why)) {
+    stages_.clear();
+    std::string msg = "cannot fuse this graph into one launch: " + why;
+    DvmException(msg.c_str());
+  }
+  compiled_ = true;
+  return ws_bytes_;
+}
+
+void VKernel::Bind(const RelocEntry *relocs, size_t n, void *workspace) {
+  workspace_ = workspace;
+  for (size_t i = 0; i < n; ++i) relocs[i].io->addr = relocs[i].addr;
+  for (auto &st : stages_) {
+    for (size_t s = 0; s < st.slot_obj.size(); ++s) {
+      dvmb::TensorDesc &td = st.param.tensor[s];
+      td.ptr = reinterpret_cast<uint64_t>(st.slot_obj[s]->addr);
+      const uint64_t align = 4ull * ItemSize(static_cast<DataType>(td.dtype));
+      td.vec_ok = (td.pad && td.ptr != 0 && td.ptr % align == 0) ? 1 : 0;
+    }
+  }
+}
+
+int VKernel::Launch(void *stream) {
+  if (!compiled_) DvmException("Launch before CodeGen");
+  dvmb::Runtime::Get().EnsureInit();
+  for (auto &st : stages_) {
+    if (st.idle) continue;
+    for (size_t s = 0; s < st.slot_obj.size(); ++s)
+      if (st.param.tensor[s].ptr == 0) DvmException("Launch with an unbound tensor address");
+    int err = dvmb::LaunchVector(st.param, st.grid, st.threads, stream);
+    if (err != 0) return err;
+  }
+  return 0;
+}
+
+// ---- text dumps -------------------------------------------------------------------------------------
+static const char *KindName(const NDObject *n) {
+  static const char *un[] = {"Sqrt", "Abs", "Log", "Exp", "Reciprocal", "IsFinite", "LogicalNot", "Round", "Floor", "Ceil", "Trunc"};
+  static const char *bin[] = {"Equal", "NotEqual", "Greater", "GreaterEqual", "Less", "LessEqual", "Add", "Sub", "Mul",
+                              "Div", "Pow", "Maximum", "Minimum", "LogicalAnd", "LogicalOr"};
+  static const char *sb[] = {"Adds", "Muls", "Divs", "SDiv", "Maxs", "Mins"};
+  static const char *red[] = {"ReduceSum", "ReduceMax", "ReduceMin"};
+  switch (n->kind) {
+    case N_LOAD: return "Load";
+    case N_STORE: return "Store";
+    case N_UNARY: return un[n->sub];
+    case N_BINARY: return bin[n->sub];
+    case N_BINARY_S: return sb[n->sub];
+    case N_COMPARE: return bin[n->sub];
+    case N_COMPARE_S: return bin[n->sub];
+    case N_SELECT: return "Select";
+    case N_CAST: return "Cast";
+    case N_BROADCAST: return "Broadcast";
+    case N_BROADCAST_S: return "BroadcastS";
+    case N_RESHAPE: return "Reshape";
+    case N_COPY: return "Copy";
+    case N_REDUCE: return red[n->sub];
+    default: return "MatMul";
+  }
+}
+
+static std::string GraphText(const std::vector<NDObject *> &nodes, bool with_shapes) {
+  std::string o;
+  char buf[160];
+  for (auto n : nodes) {
+    snprintf(buf, sizeof(buf), "%%%d = %s.%s(", n->id, KindName(n), DTypeName(n->dtype));
+    o += buf;
+    bool first = true;
+    for (int k = 0; k < 3; ++k)
+      if (n->in[k]) {
+        snprintf(buf, sizeof(buf), "%s%%%d", first ? "" : ", ", n->in[k]->id);
+        o += buf;
+        first = false;
+      }
+    if (n->kind == N_BINARY_S || n->kind == N_COMPARE_S || n->kind == N_BROADCAST_S) {
+      snprintf(buf, sizeof(buf), "%s%s", first ? "" : ", ", n->scalar_ref ? "<scalar ref>" : "");
+      o += buf;
+      if (!n->scalar_ref) {
+        snprintf(buf, sizeof(buf), "#0x%08x", n->scalar_bits);
+        o += buf;
+      }
+    }
+    o += ")";
+    if (with_shapes) {
+      o += " [";
+      for (int i = 0; i < n->shape.rank; ++i) {
+        snprintf(buf, sizeof(buf), "%s%lld", i ? "," : "", static_cast<long long>(n->shape.d[i]));
+        o += buf;
+      }
+      o += "]";
+    }
+    o += "\n";
+  }
+  return o;
+}
+
+const char *VKernel::DumpR() {
+  text_ = GraphText(nodes_, normalized_);
+  return text_.c_str();
+}
+
+const char *VKernel::Dump() {
+  if (!normalized_) Normalize();
+  text_ = GraphText(LiveOps(nodes_), true);
+  return text_.c_str();
+}
+
+const char *VKernel::Das() {
+  if (!compiled_) Compile();
+  text_.clear();
+  for (auto &st : stages_) text_ += DisassembleStage(st);
+  return text_.c_str();
+}
+
+const char *VKernel::Inspect() {
+  if (!compiled_) Compile();
+  char buf[256];
+  text_.clear();
+  int i = 0;
+  for (auto &st : stages_) {
+    snprintf(buf, sizeof(buf), "stage %d: grid=%u threads=%u code_words=%u tensors=%u algorithmic_bytes=%llu%s\n", i++,
+             st.grid, st.threads, st.param.n_code, st.param.n_tensors, static_cast<unsigned long long>(st.algo_bytes),
+             st.idle ? " (idle: zero-size domain)" : "");
+    text_ += buf;
+  }
+  snprintf(buf, sizeof(buf), "workspace_bytes=%zu last_jit_us=%.2f\n", ws_bytes_, last_jit_us_);
+  text_ += buf;
+  return text_.c_str();
+}
+
+}  // namespace dvm

@@ -1,0 +1,97 @@
+"""Test harness over PyKernel, with the surface of the reference's Tester (python/dvm/tester.py:70-299):
+``load`` takes a NumPy array (uploading it) or a shape for dynamic kernels, ``store_expect`` records an
+expectation, ``run_check`` runs and compares with ``np.allclose(rtol=eps, atol=eps, equal_nan=True)`` using
+the reference's default tolerances (1e-5 fp32, 1e-3 fp16, 0 otherwise).
+"""
+import inspect
+import os
+
+import numpy as np
+
+from .frontend import DataType, PyKernel, dvm_dtype_of, _BF16
+
+
+def _normalize_dtype(dtype):
+    if isinstance(dtype, DataType):
+        return dtype
+    if isinstance(dtype, str):
+        names = {"bool": DataType.bool, "float16": DataType.float16, "bfloat16": DataType.bfloat16,
+                 "float32": DataType.float32, "int32": DataType.int32, "int64": DataType.int64}
+        return names[dtype]
+    return dvm_dtype_of(dtype)
+
+
+class Tester(PyKernel):
+    __test__ = False
+
+    def __init__(self, ker_type="", use_pass_opt=False, run_mode="dev"):
+        dev_conf = os.getenv("DEVICE_ID")
+        PyKernel.__init__(self, ker_type, run_mode, int(dev_conf) if dev_conf else 0)
+        self.is_dyn = "dyn" in ker_type
+        self.is_codegen = False
+        self.expects = []  # [store op, expectation, eps]
+
+    def load(self, shape_arr, dtype=None):
+        if not isinstance(shape_arr, np.ndarray):
+            return PyKernel.load(self, shape_arr, _normalize_dtype(dtype))   # dynamic-shape declaration
+        dtype_id = _normalize_dtype(shape_arr.dtype if dtype is None else dtype)
+        if dtype_id == DataType.bfloat16 and (_BF16 is None or shape_arr.dtype != _BF16):
+            shape_arr = PyKernel.convert_to_bf16(shape_arr)
+        op = PyKernel.load(self, list(shape_arr.shape), dtype_id)
+        self.input(op, shape_arr)
+        return op
+
+    def cast(self, x, dtype):
+        return PyKernel.cast(self, x, _normalize_dtype(dtype))
+
+    def full(self, scalar, shape, dtype=None):
+        return PyKernel.full(self, scalar, shape, _normalize_dtype(dtype))
+
+    def store_expect(self, x, e, eps=None):
+        op = PyKernel.store(self, x)
+        self.expects.append([op, e, eps])
+        return op
+
+    def codegen(self, verbose=False):
+        if self.is_codegen:
+            return
+        PyKernel.codegen(self, None)
+        if verbose:
+            print(self.dump_r())
+            print(self.das())
+        if not self.is_dyn:
+            self.is_codegen = True
+
+    def run(self, verbose=False):
+        self.codegen(verbose)
+        PyKernel.run(self)
+
+    def bare_run(self):
+        PyKernel.run(self)
+
+    def check(self, store, expect, eps=None, verbose=False):
+        out = self.output(store)
+        if store.dtype() == DataType.bfloat16:
+            out = PyKernel.convert_from_bf16(out)
+        if inspect.isfunction(expect):
+            return bool(expect(out))
+        if eps is None:
+            eps = 1e-5 if out.dtype == np.float32 else (1e-3 if out.dtype == np.float16 else 0)
+        expect = np.asarray(expect)
+        if _BF16 is not None and expect.dtype == _BF16:
+            expect = expect.astype(np.float32)
+        ok = np.allclose(out, expect, rtol=eps, atol=eps, equal_nan=True)
+        if not ok and verbose:
+            bad = ~np.isclose(out, expect, rtol=eps, atol=eps, equal_nan=True)
+            idx = np.argwhere(bad)[:8]
+            for i in idx:
+                print("mismatch at", tuple(i), "expect", expect[tuple(i)], "got", out[tuple(i)])
+        return bool(ok)
+
+    def run_check(self, verbose=False):
+        self.run(verbose)
+        return all(self.check(op, e, eps, verbose) for op, e, eps in self.expects)
+
+    def run_perf(self):
+        self.codegen()
+        return self.perf()

@@ -1,0 +1,126 @@
+/* dvm-b200 C ABI: the drop-in boundary of the fused-operator path.
+ *
+ * Plain C entry points (opaque handles, pointers and sizes only) over the C++ builder in dvm.h.  These are
+ * the functions a foreign-function binding of the reference's operator path would bind: each one cites the
+ * reference interface it replaces, either the C++ builder (`include/dvm.h:<line>` of mindspore-ai/dvm) or
+ * the method of its Python extension module (`src/pybind_api.cc:<line>`, `include/dvm_py.h:<line>`).
+ *
+ * Error convention: functions returning a pointer return NULL on failure, functions returning int return
+ * 0 on success and non-zero on failure; dvm_last_error() then gives the message of the DvmException that
+ * was raised (thread-local).  A NULL result from dvm_reduce() with an empty error string mirrors the
+ * reference's "unsupported dtype" null result (src/dvm.cc:1538-1540).
+ *
+ * There is no CPU execution path behind this ABI: compute entry points fail when no sm_100 device is
+ * usable.
+ */
+#ifndef DVM_B200_DVM_C_H_
+#define DVM_B200_DVM_C_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DVM_C_API __attribute__((visibility("default")))
+
+typedef struct dvm_kernel dvm_kernel;         /* a dvm::Kernel plus what it borrowed through this ABI */
+typedef struct dvm_object dvm_object;         /* dvm::NDObject, owned by its kernel */
+typedef struct dvm_int_array dvm_int_array;   /* owning int64 array with a stable dvm::IntArrayRef */
+typedef struct dvm_scalar dvm_scalar;         /* owning dvm::ScalarRef */
+
+/* (load/store object, device address): same layout as dvm::RelocEntry (include/dvm.h:201-206). */
+typedef struct dvm_reloc {
+  dvm_object *io;
+  void *addr;
+} dvm_reloc;
+
+/* Workspace callback, the C form of dvm::WsAllocator (include/dvm.h:208-210). */
+typedef void *(*dvm_ws_alloc_fn)(size_t size, void *user);
+
+DVM_C_API const char *dvm_last_error(void);
+DVM_C_API const char *dvm_version(void);
+
+/* ---- borrowed shape / scalar holders (IntArrayRefPy and ScalarRefPy, include/dvm_py.h:40-92) ---- */
+DVM_C_API dvm_int_array *dvm_int_array_new(const int64_t *data, size_t size);
+DVM_C_API int dvm_int_array_update(dvm_int_array *a, const int64_t *data, size_t size);
+DVM_C_API size_t dvm_int_array_size(const dvm_int_array *a);
+DVM_C_API const int64_t *dvm_int_array_data(const dvm_int_array *a);
+DVM_C_API void dvm_int_array_free(dvm_int_array *a);
+DVM_C_API dvm_scalar *dvm_scalar_new(void);
+DVM_C_API void dvm_scalar_set_f32(dvm_scalar *s, float v);
+DVM_C_API void dvm_scalar_set_i64(dvm_scalar *s, int64_t v);
+DVM_C_API void dvm_scalar_free(dvm_scalar *s);
+
+/* ---- kernel lifecycle: Kernel::Kernel / Reset / ~Kernel (include/dvm.h:238-252) ---- */
+DVM_C_API dvm_kernel *dvm_kernel_new(int kernel_type, uint32_t flags);
+DVM_C_API int dvm_kernel_reset(dvm_kernel *k, int kernel_type, uint32_t flags);
+DVM_C_API void dvm_kernel_free(dvm_kernel *k);
+DVM_C_API int dvm_set_name_hint(dvm_kernel *k, const char *name);               /* include/dvm.h:266 */
+
+/* ---- graph building ---- */
+DVM_C_API dvm_object *dvm_load(dvm_kernel *k, void *addr, dvm_int_array *shape, int dtype);  /* dvm.h:276 */
+DVM_C_API dvm_object *dvm_store(dvm_kernel *k, void *addr, dvm_object *input);               /* dvm.h:331 */
+DVM_C_API dvm_object *dvm_unary(dvm_kernel *k, int unary_type, dvm_object *input);           /* dvm.h:372 */
+DVM_C_API dvm_object *dvm_binary(dvm_kernel *k, int binary_type, dvm_object *lhs, dvm_object *rhs); /* dvm.h:381 */
+/* tensor (op) scalar; scalar_is_lhs selects `scalar op tensor` (KernelPy::Binary, include/dvm_py.h:113-133) */
+DVM_C_API dvm_object *dvm_binary_f32(dvm_kernel *k, int binary_type, dvm_object *x, float v, int scalar_is_lhs);
+DVM_C_API dvm_object *dvm_binary_i64(dvm_kernel *k, int binary_type, dvm_object *x, int64_t v, int scalar_is_lhs);
+DVM_C_API dvm_object *dvm_binary_ref(dvm_kernel *k, int binary_type, dvm_object *x, dvm_scalar *v, int scalar_is_lhs);
+DVM_C_API dvm_object *dvm_reduce(dvm_kernel *k, int reduce_type, dvm_object *input, dvm_int_array *dims,
+                                 int keepdims);                                               /* dvm.h:391 */
+DVM_C_API dvm_object *dvm_select(dvm_kernel *k, dvm_object *cond, dvm_object *lhs, dvm_object *rhs); /* dvm.h:401 */
+DVM_C_API dvm_object *dvm_cast(dvm_kernel *k, dvm_object *input, int dtype);                  /* dvm.h:409 */
+DVM_C_API dvm_object *dvm_broadcast(dvm_kernel *k, dvm_object *input, dvm_int_array *shape);  /* dvm.h:417 */
+/* scalar -> tensor (KernelPy::Full, include/dvm_py.h:146-162; dvm.h:426) */
+DVM_C_API dvm_object *dvm_full_f32(dvm_kernel *k, float v, dvm_int_array *shape, int dtype);
+DVM_C_API dvm_object *dvm_full_i64(dvm_kernel *k, int64_t v, dvm_int_array *shape, int dtype);
+DVM_C_API dvm_object *dvm_full_ref(dvm_kernel *k, dvm_scalar *v, dvm_int_array *shape, int dtype);
+DVM_C_API dvm_object *dvm_reshape(dvm_kernel *k, dvm_object *input, dvm_int_array *shape);    /* dvm.h:434 */
+DVM_C_API dvm_object *dvm_copy(dvm_kernel *k, dvm_object *input);                             /* dvm.h:466 */
+DVM_C_API dvm_object *dvm_matmul(dvm_kernel *k, dvm_object *lhs, dvm_object *rhs, int trans_a, int trans_b,
+                                 dvm_object *bias);                                           /* dvm.h:509 */
+
+/* ---- shape inference, code generation, launch ---- */
+DVM_C_API int dvm_normalize(dvm_kernel *k);                                                   /* dvm.h:566 */
+DVM_C_API int dvm_pre_codegen(dvm_kernel *k, size_t *workspace_bytes);                        /* dvm.h:590 */
+DVM_C_API int dvm_codegen(dvm_kernel *k, const dvm_reloc *relocs, size_t reloc_size, dvm_ws_alloc_fn alloc,
+                          void *user);                                                        /* dvm.h:572 */
+DVM_C_API int dvm_launch(dvm_kernel *k, void *stream);                                        /* dvm.h:578 */
+DVM_C_API int dvm_launch_reloc(dvm_kernel *k, const dvm_reloc *relocs, size_t reloc_size, void *workspace,
+                               void *stream);                                                 /* dvm.h:599 */
+/* Host microseconds spent by the last dvm_codegen / dvm_pre_codegen (shape inference + planning + emission). */
+DVM_C_API double dvm_last_jit_us(const dvm_kernel *k);
+
+/* ---- introspection (NDObjectPy::GetShape/GetDType include/dvm_py.h:28-38; Dump/DumpR/Das/Inspect dvm.h:619-637) ---- */
+DVM_C_API int dvm_object_rank(const dvm_object *o);
+DVM_C_API int64_t dvm_object_dim(const dvm_object *o, int i);
+DVM_C_API int dvm_object_dtype(const dvm_object *o);
+DVM_C_API const char *dvm_dump(dvm_kernel *k);
+DVM_C_API const char *dvm_dump_r(dvm_kernel *k);
+DVM_C_API const char *dvm_das(dvm_kernel *k);
+DVM_C_API const char *dvm_inspect(dvm_kernel *k);
+
+/* ---- device runtime used by the Python runner (DevRunner, src/pybind_api.cc:195-271; Device, :1100-1116) ---- */
+DVM_C_API int dvm_rt_device_count(void);
+DVM_C_API int dvm_rt_set_device(int dev);
+DVM_C_API int dvm_rt_sm_count(void);
+DVM_C_API void *dvm_rt_malloc(size_t bytes);
+DVM_C_API int dvm_rt_free(void *p);
+DVM_C_API int dvm_rt_memcpy_h2d(void *dst, const void *src, size_t bytes, void *stream);
+DVM_C_API int dvm_rt_memcpy_d2h(void *dst, const void *src, size_t bytes, void *stream);
+DVM_C_API int dvm_rt_memset(void *dst, int value, size_t bytes, void *stream);
+DVM_C_API int dvm_rt_sync(void *stream);
+DVM_C_API void *dvm_rt_host_alloc(size_t bytes);   /* pinned host memory */
+DVM_C_API int dvm_rt_host_free(void *p);
+/* warmup launches, then `reps` launches timed one by one with device events on `stream`
+ * (RtKernelPy::Perf, src/pybind_api.cc:751-767: 1 warm-up + 10 timed runs, min/max/mean in us). */
+DVM_C_API int dvm_perf(dvm_kernel *k, int warmup, int reps, void *stream, float *min_us, float *max_us,
+                       float *mean_us);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* DVM_B200_DVM_C_H_ */
