@@ -14,6 +14,8 @@ from .frontend import DataType, PyKernel, dvm_dtype_of, _BF16
 def _normalize_dtype(dtype):
     if isinstance(dtype, DataType):
         return dtype
+    if isinstance(dtype, (int, np.integer)) and not isinstance(dtype, bool):
+        return DataType(int(dtype))
     if isinstance(dtype, str):
         names = {"bool": DataType.bool, "float16": DataType.float16, "bfloat16": DataType.bfloat16,
                  "float32": DataType.float32, "int32": DataType.int32, "int64": DataType.int64}
