@@ -81,7 +81,8 @@ class NDObject {
 // One launch of the vector interpreter.
 struct VectorStage {
   dvmb::VmParam param;
-  uint32_t grid = 0, threads = 0;
+  uint32_t grid = 0, threads = 0, smem_bytes = 0;
+  uint32_t body_tensor_mask[dvmb::kMaxPhases] = {0, 0, 0, 0};   // tensor slots each BODY reads
   bool idle = false;                       // zero-size domain: nothing to launch
   std::vector<NDObject *> slot_obj;        // tensor slot -> load/store node (relocation sites)
   std::vector<int64_t> slot_ws_off;        // >= 0: slot is a workspace temporary at this byte offset

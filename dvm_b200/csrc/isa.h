@@ -8,9 +8,12 @@
 // group owns two 4-element granules at `4*t` and `4*tg + 4*t` inside the chunk, so every global access
 // is a coalesced 16-byte (fp32), 8-byte (fp16/bf16) or 4-byte (bool) vector.
 //
-// The machine is an accumulator machine whose state lives in registers: an 8-lane accumulator, eight
-// 8-lane named vector registers, and a scalar side (accumulator + 12 named scalars) for values that are
-// constant inside a group (reduce results, per-channel parameters).  The program is cut into sections
+// The machine is an accumulator machine.  The 8-lane accumulator is the only vector state in registers;
+// every other operand is read where it already lives: an input tensor's chunk in the shared-memory ring
+// that a producer warp fills with bulk async copies (cp.async.bulk + mbarrier), a thread-private
+// shared-memory temporary, a scalar register, or an immediate.  The scalar side (accumulator + 12 named
+// scalars) holds values that are constant inside a group (reduce results, per-channel parameters).  The
+// program is cut into sections
 // PRO_0, BODY_0, PRO_1, BODY_1, ... : PRO_p runs once per group on the scalar side (it finalises the
 // reductions accumulated by BODY_{p-1}); BODY_p runs once per chunk on the vector side.
 //
@@ -27,7 +30,7 @@ constexpr int kMaxTensors = 16;
 constexpr int kMaxCodeWords = 288;
 constexpr int kMaxKept = 3;
 constexpr int kMaxEnum = 4;
-constexpr int kNumVRegs = 6;
+constexpr int kNumTemps = 6;            // thread-private 8-lane temporaries in shared memory
 constexpr int kNumSRegs = 12;
 constexpr int kNumRSlots = 4;
 constexpr int kMaxPhases = 4;        // BODY sections
@@ -39,10 +42,10 @@ enum : uint32_t { T_BOOL = 0, T_F16 = 1, T_BF16 = 2, T_F32 = 3, T_I32 = 4, T_I64
 
 enum Opcode : uint32_t {
   OP_END = 0,
-  OP_LD,     // acc|reg[dst] <- tensor[sub]
+  OP_LD,     // unused (inputs are operands of kind K_TENSOR)
   OP_ST,     // tensor[sub] <- acc
   OP_COPY,   // acc <- operand
-  OP_MOV,    // reg[dst] <- acc
+  OP_MOV,    // temp[dst] <- acc (vector side) / sreg[dst] <- sacc (scalar side)
   OP_UN,     // acc <- unary[sub](acc)
   OP_BIN,    // acc <- binary[sub](acc, operand)
   OP_CMP,    // acc <- cmp[sub](acc, operand) ? 1 : 0   (in the operand representation)
@@ -74,7 +77,9 @@ enum CvtKind : uint32_t {
 
 enum RedKind : uint32_t { R_SUM = 0, R_MAX, R_MIN };
 
-enum OperandKind : uint32_t { K_VREG = 0, K_SREG = 1, K_IMM = 2, K_ACC = 3 };
+// K_TENSOR: chunk of input tensor `idx`, converted to the 32-bit register form on read.
+// K_TEMP: thread-private temporary `idx`.
+enum OperandKind : uint32_t { K_TENSOR = 0, K_SREG = 1, K_IMM = 2, K_ACC = 3, K_TEMP = 4 };
 
 enum Rounding : uint32_t { RN_NONE = 0, RN_F16 = 1, RN_BF16 = 2 };
 
@@ -116,8 +121,12 @@ struct TensorDesc {
   uint8_t dtype;
   uint8_t mode;
   uint8_t vec_ok;              // granules are contiguous and aligned to 4 elements
-  uint8_t pad;
+  uint8_t layout_vec;          // the layout permits vector access (vec_ok = layout_vec && aligned address)
+  uint32_t ring_off;           // byte offset of this tensor's chunk inside a ring stage, or kNoRing
+  uint8_t ring_layout;         // the layout permits bulk staging (ring_off is set when the address is aligned)
+  uint8_t pad[3];
 };
+constexpr uint32_t kNoRing = 0xffffffffu;
 // Element offsets are 32-bit: a tensor bound to the vector interpreter holds fewer than 2^31 elements.
 
 enum VmMode : uint32_t { VM_FLAT = 0, VM_GROUP = 1 };
@@ -129,9 +138,15 @@ struct VmParam {
   uint32_t tg;               // threads cooperating on one group
   uint32_t groups_per_cta;   // blockDim.x / tg
   uint32_t chunks;           // chunks per group
+  uint32_t chunk_elems;      // elements per chunk (<= 8 * tg; threads past the end idle)
+  uint32_t stage_bytes;      // bytes of one ring stage (0: no bulk staging in this launch)
+  uint32_t num_stages;
+  uint32_t body_ring_mask[kMaxPhases];  // per BODY section: tensor slots the producer stages
+  uint32_t num_temps;        // shared-memory temporaries in use
+  uint32_t num_sregs;        // scalar registers in use
   uint32_t kept_size[kMaxKept];
   uint32_t enum_size[kMaxEnum];   // right-aligned, unused outer slots are 1
-  uint32_t need_coords;      // some tensor uses AM_GRANULE
+  uint32_t need_coords;      // some tensor uses AM_GRANULE or is staged per segment
   uint32_t num_body;         // number of BODY sections
   uint16_t sec[2 * kMaxPhases + 2];  // word offset of PRO_0, BODY_0, PRO_1, ..., PRO_n (each ends with OP_END)
   uint32_t n_tensors;

@@ -62,6 +62,12 @@ struct Compiler {
   int num_body = 0;
   std::vector<uint64_t> code;
   std::vector<NDObject *> slot_nodes;
+  int max_temp = 0, max_sreg = 0;
+  uint32_t body_tensor_mask[kMaxPhases] = {0, 0, 0, 0};   // tensor slots each BODY reads as operands
+
+  void NoteTensorUse(int section, int slot) {
+    if (section & 1) body_tensor_mask[section / 2] |= 1u << slot;
+  }
 
   Compiler(const std::vector<NDObject *> &o, VectorStage *st) : ops(o), out(st) {}
 
@@ -353,15 +359,17 @@ struct Compiler {
     }
 
     int AllocReg(const NDObject *v) {
-      const int n = scalar ? kNumSRegs : kNumVRegs;
+      const int n = scalar ? kNumSRegs : kNumTemps;
       if (static_cast<int>(reg_val.size()) < n) reg_val.resize(n, nullptr);
       for (int i = 0; i < n; ++i) {
         if (reg_val[i] == nullptr) {
           reg_val[i] = v;
           if (scalar) {
             c->I(v).sreg = i;
+            c->max_sreg = std::max(c->max_sreg, i + 1);
           } else {
             vreg_of[v] = i;
+            c->max_temp = std::max(c->max_temp, i + 1);
           }
           return i;
         }
@@ -386,6 +394,7 @@ struct Compiler {
     void SaveAcc() {
       if (acc_val == nullptr) return;
       if (RegOf(acc_val) >= 0) return;
+      if (!scalar && acc_val->kind == N_LOAD) return;   // an input is simply read again where it lives
       if (!NeededLater(acc_val)) return;
       int r = AllocReg(acc_val);
       Push0(OP_MOV, 0, r);
@@ -396,20 +405,21 @@ struct Compiler {
     void ParkAccIfNeeded() { SaveAcc(); }
 
     int AllocTemp() {
-      const int n = scalar ? kNumSRegs : kNumVRegs;
+      const int n = scalar ? kNumSRegs : kNumTemps;
       if (static_cast<int>(reg_val.size()) < n) reg_val.resize(n, nullptr);
       static const NDObject kTempMarker{};
       for (int i = 0; i < n; ++i)
         if (reg_val[i] == nullptr) {
           reg_val[i] = &kTempMarker;
+          if (scalar) c->max_sreg = std::max(c->max_sreg, i + 1); else c->max_temp = std::max(c->max_temp, i + 1);
           return i;
         }
       throw Fail{scalar ? "out of scalar registers" : "out of vector registers"};
     }
     void FreeTemp(int r) { reg_val[r] = nullptr; }
 
-    // Location of a value as a non-accumulator operand; loads it into a register if it is an input
-    // that has not been fetched yet.
+    // Location of a value as a non-accumulator operand.  Inputs are read in place: a tensor operand names
+    // the tensor slot (the interpreter takes it from the shared-memory ring or from global memory).
     Operand OperandOf(const NDObject *v) {
       if (v->kind == N_BROADCAST_S) return Operand{K_IMM, 0, c->ScalarBits(v)};
       const Info &vi = c->I(v);
@@ -418,12 +428,11 @@ struct Compiler {
         return Operand{K_SREG, static_cast<uint32_t>(vi.sreg), 0};
       }
       int r = RegOf(v);
-      if (r >= 0) return Operand{scalar ? K_SREG : K_VREG, static_cast<uint32_t>(r), 0};
+      if (r >= 0) return Operand{scalar ? K_SREG : K_TEMP, static_cast<uint32_t>(r), 0};
       if (acc_val == v) return Operand{K_ACC, 0, 0};
       if (v->kind == N_LOAD) {
-        r = AllocReg(v);
-        Push0(OP_LD, vi.slot, r);
-        return Operand{scalar ? K_SREG : K_VREG, static_cast<uint32_t>(r), 0};
+        c->NoteTensorUse(section, vi.slot);
+        return Operand{K_TENSOR, static_cast<uint32_t>(vi.slot), 0};
       }
       throw Fail{"internal: operand value is not available"};
     }
@@ -432,12 +441,8 @@ struct Compiler {
     void ToAcc(const NDObject *v) {
       if (acc_val == v) return;
       SaveAcc();
-      if (v->kind == N_LOAD && RegOf(v) < 0 && (scalar || !c->I(v).scalar_space)) {
-        Push0(OP_LD, c->I(v).slot, kAccIdx);
-      } else {
-        Operand o = OperandOf(v);
-        Push(OP_COPY, 0, o, 0, 0, 0);
-      }
+      Operand o = OperandOf(v);
+      Push(OP_COPY, 0, o, 0, 0, 0);
       acc_val = v;
     }
 
@@ -585,7 +590,8 @@ struct Compiler {
         auto reg_like = [&](const NDObject *v) {
           if (v->kind == N_BROADCAST_S) return false;
           if (!s.scalar && I(v).scalar_space) return true;
-          return v != cnd;   // anything else can be given a register
+          if (s.scalar && v->kind == N_LOAD) return false;   // the scalar side reads tensors only as the free operand
+          return v != cnd;   // anything else sits in (or can be given) a register, or is an input read in place
         };
         bool inv = false;
         const NDObject *free_v = a, *reg_v = b;
@@ -601,7 +607,7 @@ struct Compiler {
             Operand oa = a == cnd ? Operand{K_ACC, 0, 0} : s.OperandOf(a);
             s.Consume(cnd); s.Consume(a); s.Consume(b);
             s.ParkAccIfNeeded();
-            s.Push(OP_SEL, ((s.scalar ? K_SREG : K_VREG) << 4) | r, oa, 0, 0, IsIntRepr(n->in[0]->dtype));
+            s.Push(OP_SEL, ((s.scalar ? K_SREG : K_TEMP) << 4) | r, oa, 0, 0, IsIntRepr(n->in[0]->dtype));
             s.FreeTemp(r);
             s.acc_val = n;
             s.Release(cnd); s.Release(a); s.Release(b);
@@ -748,9 +754,7 @@ struct Compiler {
           ss.Push0(OP_RFIN, I(n).rslot | (n->sub << 4));
           ss.acc_val = n;
         } else if (n->kind == N_LOAD) {
-          int r = ss.AllocReg(n);
-          ss.Push0(OP_LD, I(n).slot, r);
-          continue;
+          ss.ToAcc(n);
         } else {
           EmitNode(ss, n);
         }
@@ -768,38 +772,6 @@ struct Compiler {
       P.sec[2 * p + 1] = static_cast<uint16_t>(code.size());
       Side vs{this, false, 2 * p + 1};
       CountUses(vs, body_order[p], body_roots[p]);
-      // issue the input fetches first so that every load of the chunk is in flight together
-      {
-        std::vector<const NDObject *> loads;
-        for (auto v : body_order[p])
-          if (v->kind == N_LOAD) loads.push_back(v);
-        // the value the first op (or, with no ops, the first store/reduction) consumes through the
-        // accumulator is fetched straight into it
-        const NDObject *first_x = nullptr;
-        bool any_op = false;
-        for (auto v : body_order[p]) {
-          if (v->kind == N_LOAD || v->kind == N_BROADCAST_S) continue;
-          const NDObject *x = Canon(v->in[0]);
-          if (x->kind == N_LOAD && !I(x).scalar_space && vs.uses[x] == 1) first_x = x;
-          any_op = true;
-          break;
-        }
-        if (!any_op && !body_roots[p].empty()) {
-          const NDObject *x = Canon(body_roots[p][0]->in[0]);
-          if (x->kind == N_LOAD && !I(x).scalar_space) first_x = x;
-        }
-        if (static_cast<int>(loads.size()) <= kNumVRegs - 2 + (first_x ? 1 : 0)) {
-          for (auto v : loads) {
-            if (v == first_x) continue;
-            int r = vs.AllocReg(v);
-            vs.Push0(OP_LD, I(v).slot, r);
-          }
-          if (first_x) {
-            vs.Push0(OP_LD, I(first_x).slot, kAccIdx);
-            vs.acc_val = first_x;
-          }
-        }
-      }
       // roots are interleaved in program order: emit each as soon as its value exists
       std::vector<const NDObject *> pending = body_roots[p];
       auto flush_roots = [&](const NDObject *just_made) {
@@ -852,58 +824,84 @@ struct Compiler {
     for (auto n : ops)
       if (n->shape.numel() == 0) zero = true;
     out->idle = zero;
+
+    // ---- thread / chunk geometry
+    const int64_t inner = cenum.empty() ? 1 : cenum.back().size;
+    const uint32_t kChunkCap = 8 * kVmFlatThreads;   // elements
+    bool chunk_in_inner = false;   // every chunk lies inside one run of the innermost iterated axis
+    bool packed = false;           // several small groups share a CTA
     if (!has_reduce) {
       P.mode = VM_FLAT;
-      P.tg = kVmMaxThreads;
+      P.tg = kVmFlatThreads;
       P.groups_per_cta = 1;
-      P.chunks = static_cast<uint32_t>((G + 8 * P.tg - 1) / (8 * P.tg));
-      out->threads = P.tg;
-      out->grid = std::max<uint32_t>(1u, std::min<uint32_t>(P.chunks, sms * kVmMinBlocks * 2));
-      if (num_body == 0) out->grid = 1;
+      P.chunk_elems = 8 * P.tg;
+      P.chunks = static_cast<uint32_t>((G + P.chunk_elems - 1) / P.chunk_elems);
+      chunk_in_inner = cenum.size() <= 1 || (inner % P.chunk_elems == 0);
     } else {
       P.mode = VM_GROUP;
       if (G <= 8 * 32) {
         uint32_t tg = 1;
         while (8 * tg < G) tg <<= 1;
         P.tg = tg;
-        P.groups_per_cta = kVmMaxThreads / tg;
+        P.groups_per_cta = kVmFlatThreads / tg;
+        P.chunk_elems = 8 * tg;
         P.chunks = 1;
-        out->threads = kVmMaxThreads;
+        packed = true;
       } else {
-        uint32_t chunks = static_cast<uint32_t>((G + 8 * kVmMaxThreads - 1) / (8 * kVmMaxThreads));
-        uint32_t per = static_cast<uint32_t>((G + 8ll * chunks - 1) / (8ll * chunks));
-        uint32_t tg = ((per + 31) / 32) * 32;
-        P.tg = tg;
         P.groups_per_cta = 1;
-        P.chunks = static_cast<uint32_t>((G + 8ll * tg - 1) / (8ll * tg));
-        out->threads = tg;
+        uint32_t ce = 0;
+        if (cenum.size() >= 2 && inner % 4 == 0) {
+          // cut the innermost axis into equal chunks so that a chunk never straddles two runs
+          for (int64_t parts = (inner + kChunkCap - 1) / kChunkCap; parts <= inner / 32 && parts < 4096; ++parts)
+            if (inner % parts == 0 && (inner / parts) % 8 == 0) {
+              ce = static_cast<uint32_t>(inner / parts);
+              break;
+            }
+        }
+        if (ce != 0) {
+          P.chunk_elems = ce;
+          P.tg = ((ce + 7) / 8 + 31) / 32 * 32;
+          chunk_in_inner = true;
+        } else {
+          const uint32_t chunks = static_cast<uint32_t>((G + kChunkCap - 1) / kChunkCap);
+          const uint32_t per = static_cast<uint32_t>((G + 8ll * chunks - 1) / (8ll * chunks));
+          P.tg = (per + 31) / 32 * 32;
+          P.chunk_elems = 8 * P.tg;
+          chunk_in_inner = cenum.size() <= 1;
+        }
+        P.chunks = static_cast<uint32_t>((G + P.chunk_elems - 1) / P.chunk_elems);
       }
-      uint32_t ngb = (P.num_groups + P.groups_per_cta - 1) / P.groups_per_cta;
-      out->grid = std::max<uint32_t>(1u, std::min<uint32_t>(ngb, sms * kVmMinBlocks * 2));
     }
-    // tensors
+    const uint32_t T = P.tg * P.groups_per_cta;
+
+    // ---- tensors
     P.n_tensors = static_cast<uint32_t>(slot_nodes.size());
     P.need_coords = 0;
     out->slot_obj.assign(slot_nodes.begin(), slot_nodes.end());
     out->algo_bytes = 0;
+    uint32_t stage_bytes = 0;
+    uint32_t read_mask = 0;
+    for (int q = 0; q < num_body; ++q) read_mask |= body_tensor_mask[q];
     for (size_t sidx = 0; sidx < slot_nodes.size(); ++sidx) {
       NDObject *n = slot_nodes[sidx];
       TensorDesc &td = P.tensor[sidx];
       std::memset(&td, 0, sizeof(td));
+      td.ring_off = kNoRing;
       td.ptr = reinterpret_cast<uint64_t>(n->addr);
       td.dtype = static_cast<uint8_t>(n->dtype);
       if (n->dtype == kInt64) throw Fail{"int64 tensors are not supported by the vector interpreter"};
       if (n->shape.numel() >= (1ll << 31)) throw Fail{"tensor above 2^31 elements"};
       out->algo_bytes += static_cast<uint64_t>(n->shape.numel()) * ItemSize(n->dtype);
-      bool layout_vec = true;
+      const int isz = ItemSize(n->dtype);
+      bool layout_vec = true, layout_bulk = true;
       for (size_t j = 0; j < ckept.size(); ++j) {
         int64_t st = StrideOn(n, ckept[j].members.back());
         td.kstride[kMaxKept - ckept.size() + j] = static_cast<uint32_t>(st);
         if (st % 4 != 0) layout_vec = false;
+        if ((st * isz) % 16 != 0) layout_bulk = false;
       }
       if (I(n).scalar_space) {
         td.mode = AM_SCALAR;
-        td.vec_ok = 0;
         continue;
       }
       bool dense = true;
@@ -912,10 +910,12 @@ struct Compiler {
         int64_t st = StrideOn(n, cenum[j].members.back());
         td.estride[kMaxEnum - cenum.size() + j] = static_cast<uint32_t>(st);
         if (st != expect) dense = false;
-        if (j != static_cast<int>(cenum.size()) - 1 && st % 4 != 0) layout_vec = false;
+        if (j != static_cast<int>(cenum.size()) - 1) {
+          if (st % 4 != 0) layout_vec = false;
+          if ((st * isz) % 16 != 0) layout_bulk = false;
+        }
         expect *= cenum[j].size;
       }
-      const int64_t inner = cenum.empty() ? 1 : cenum.back().size;
       const int64_t inner_stride = cenum.empty() ? 1 : StrideOn(n, cenum.back().members.back());
       if (dense) {
         td.mode = AM_DENSE;
@@ -927,10 +927,53 @@ struct Compiler {
         layout_vec = false;
       }
       if (inner_stride != 1) layout_vec = false;
-      // pad doubles as "layout allows vector access"; vec_ok is finalised when the address is bound
-      td.pad = layout_vec ? 1 : 0;
-      td.vec_ok = 0;
+      td.layout_vec = layout_vec ? 1 : 0;
+      // bulk staging: the chunk must be one contiguous, 16-byte aligned run of this tensor
+      const bool contiguous_chunk = inner_stride == 1 && (dense || (td.mode == AM_GRANULE && chunk_in_inner));
+      const bool is_input = n->kind == N_LOAD && ((read_mask >> sidx) & 1u);
+      if (is_input && !packed && contiguous_chunk && layout_bulk && (static_cast<int64_t>(P.chunk_elems) * isz) % 16 == 0 &&
+          (dense ? true : chunk_in_inner)) {
+        td.ring_layout = 1;
+        td.ring_off = stage_bytes;   // provisional; Bind() drops it when the address is not 16-byte aligned
+        stage_bytes += (P.chunk_elems * isz + 127u) & ~127u;
+      }
     }
+    // a dense tensor whose chunks straddle runs of a multi-axis iteration is still contiguous; a granule-mode
+    // one needs coordinates for its bulk source too
+    if (stage_bytes != 0 && cenum.size() >= 2) P.need_coords = P.need_coords;
+
+    // ---- shared memory plan
+    P.num_temps = static_cast<uint32_t>(max_temp);
+    P.num_sregs = static_cast<uint32_t>(max_sreg);
+    const uint32_t fixed = kVmSmemStages + P.num_temps * T * 32u + P.num_sregs * T * 4u;
+    uint32_t stages = 0;
+    if (stage_bytes != 0) {
+      const uint32_t budget = 72 * 1024;   // three CTAs of this size fit one SM
+      stages = fixed + 2 * stage_bytes > budget ? 2 : std::min<uint32_t>(kVmMaxStages, (budget - fixed) / stage_bytes);
+      if (fixed + stages * stage_bytes > kVmMaxSmemBytes) {
+        // too large to stage even twice: fall back to direct global loads
+        stage_bytes = 0;
+        stages = 0;
+        for (uint32_t t = 0; t < P.n_tensors; ++t) {
+          P.tensor[t].ring_layout = 0;
+          P.tensor[t].ring_off = kNoRing;
+        }
+      }
+    }
+    P.stage_bytes = stage_bytes;
+    P.num_stages = stages;
+    for (int q = 0; q < kMaxPhases; ++q) P.body_ring_mask[q] = 0;
+    out->smem_bytes = fixed + stages * stage_bytes;
+    if (out->smem_bytes > kVmMaxSmemBytes) throw Fail{"stage needs more shared memory than one SM has"};
+    for (int q = 0; q < num_body; ++q) out->body_tensor_mask[q] = body_tensor_mask[q];
+    out->threads = T + (stage_bytes != 0 ? 32u : 0u);
+
+    // ---- grid: persistent CTAs, as many as fit per SM
+    uint32_t per_sm = std::max<uint32_t>(1u, std::min<uint32_t>(3u, (220u * 1024u) / std::max<uint32_t>(out->smem_bytes, 1u)));
+    if (T > static_cast<uint32_t>(kVmFlatThreads)) per_sm = 1;
+    const uint32_t work = P.mode == VM_FLAT ? P.chunks : (P.num_groups + P.groups_per_cta - 1) / P.groups_per_cta;
+    out->grid = std::max<uint32_t>(1u, std::min<uint32_t>(work, sms * per_sm));
+    if (num_body == 0) out->grid = 1;
   }
 
   void Run() {
@@ -977,27 +1020,36 @@ std::string DisassembleStage(const VectorStage &st) {
   const VmParam &P = st.param;
   std::string o;
   char buf[256];
-  snprintf(buf, sizeof(buf), "vmain.sm100(mode=%s, groups=%u, group_elems=%u, tg=%u, chunks=%u, grid=%u, threads=%u) {\n",
-           P.mode == VM_FLAT ? "flat" : "group", P.num_groups, P.group_elems, P.tg, P.chunks, st.grid, st.threads);
+  snprintf(buf, sizeof(buf),
+           "vmain.sm100(mode=%s, groups=%u, group_elems=%u, tg=%u, groups_per_cta=%u, chunk_elems=%u, chunks=%u, grid=%u, "
+           "threads=%u, smem=%u, stages=%u x %u B) {\n",
+           P.mode == VM_FLAT ? "flat" : "group", P.num_groups, P.group_elems, P.tg, P.groups_per_cta, P.chunk_elems, P.chunks,
+           st.grid, st.threads, st.smem_bytes, P.num_stages, P.stage_bytes);
   o += buf;
   for (uint32_t t = 0; t < P.n_tensors; ++t) {
     const TensorDesc &td = P.tensor[t];
-    snprintf(buf, sizeof(buf), "  // t%u: %s %s vec=%d kstride=[%u,%u,%u] estride=[%u,%u,%u,%u] @0x%llx\n", t,
-             DTypeName(static_cast<DataType>(td.dtype)), kModeNames[td.mode], td.vec_ok, td.kstride[0], td.kstride[1],
+    snprintf(buf, sizeof(buf), "  // t%u: %s %s vec=%d ring=%d kstride=[%u,%u,%u] estride=[%u,%u,%u,%u] @0x%llx\n", t,
+             DTypeName(static_cast<DataType>(td.dtype)), kModeNames[td.mode], td.vec_ok, td.ring_off != kNoRing ? 1 : 0,
+             td.kstride[0], td.kstride[1],
              td.kstride[2], td.estride[0], td.estride[1], td.estride[2], td.estride[3],
              static_cast<unsigned long long>(td.ptr));
     o += buf;
   }
-  auto operand = [&](uint64_t w) -> std::string {
-    char b[48];
-    switch (DVMB_OKIND(w)) {
-      case K_VREG: snprintf(b, sizeof(b), "v%u", DVMB_OIDX(w)); break;
-      case K_SREG: snprintf(b, sizeof(b), "s%u", DVMB_OIDX(w)); break;
-      case K_IMM: snprintf(b, sizeof(b), "#0x%08x", DVMB_IMM(w)); break;
+  auto operand_text = [&](uint32_t kind, uint32_t idx, uint32_t imm) -> std::string {
+    char b[64];
+    switch (kind) {
+      case K_TENSOR:
+        snprintf(b, sizeof(b), "load.%s(0x%llx)", DTypeName(static_cast<DataType>(P.tensor[idx].dtype)),
+                 static_cast<unsigned long long>(P.tensor[idx].ptr));
+        break;
+      case K_TEMP: snprintf(b, sizeof(b), "v%u", idx); break;
+      case K_SREG: snprintf(b, sizeof(b), "s%u", idx); break;
+      case K_IMM: snprintf(b, sizeof(b), "#0x%08x", imm); break;
       default: snprintf(b, sizeof(b), "acc"); break;
     }
     return b;
   };
+  auto operand = [&](uint64_t w) -> std::string { return operand_text(DVMB_OKIND(w), DVMB_OIDX(w), DVMB_IMM(w)); };
   static const char *rnd_names[] = {"", ".rn_f16", ".rn_bf16", ""};
   for (uint32_t pc = 0; pc < P.n_code; ++pc) {
     for (uint32_t sidx = 0; sidx <= 2 * P.num_body; ++sidx)
@@ -1013,14 +1065,6 @@ std::string DisassembleStage(const VectorStage &st) {
     const char *ty = DVMB_ISINT(w) ? "int32" : "fp32";
     switch (opc) {
       case OP_END: snprintf(buf, sizeof(buf), "  %u: end\n", pc); break;
-      case OP_LD: {
-        const TensorDesc &td = P.tensor[sub];
-        char d[16];
-        if (dst == kAccIdx) snprintf(d, sizeof(d), "%s", acc); else snprintf(d, sizeof(d), "%s%u", rp, dst);
-        snprintf(buf, sizeof(buf), "  %u: load.%s %s, 0x%llx // t%u\n", pc, DTypeName(static_cast<DataType>(td.dtype)), d,
-                 static_cast<unsigned long long>(td.ptr), sub);
-        break;
-      }
       case OP_ST: {
         const TensorDesc &td = P.tensor[sub];
         snprintf(buf, sizeof(buf), "  %u: store.%s 0x%llx, %s // t%u\n", pc, DTypeName(static_cast<DataType>(td.dtype)),
@@ -1041,12 +1085,11 @@ std::string DisassembleStage(const VectorStage &st) {
         snprintf(buf, sizeof(buf), "  %u: Cmp%s.%s %s, %s, %s\n", pc, kCmpNames[sub], ty, acc, acc, operand(w).c_str());
         break;
       case OP_SEL: {
-        char second[16];
-        snprintf(second, sizeof(second), "%s%u", (sub >> 4) == K_SREG ? "s" : "v", sub & 15u);
+        std::string second = operand_text(sub >> 4, sub & 15u, 0);
         if (dst & 1u) {
-          snprintf(buf, sizeof(buf), "  %u: Select.%s %s, %s ? %s : %s\n", pc, ty, acc, acc, second, operand(w).c_str());
+          snprintf(buf, sizeof(buf), "  %u: Select.%s %s, %s ? %s : %s\n", pc, ty, acc, acc, second.c_str(), operand(w).c_str());
         } else {
-          snprintf(buf, sizeof(buf), "  %u: Select.%s %s, %s ? %s : %s\n", pc, ty, acc, acc, operand(w).c_str(), second);
+          snprintf(buf, sizeof(buf), "  %u: Select.%s %s, %s ? %s : %s\n", pc, ty, acc, acc, operand(w).c_str(), second.c_str());
         }
         break;
       }

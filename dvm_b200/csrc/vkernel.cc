@@ -72,12 +72,21 @@ void VKernel::Bind(const RelocEntry *relocs, size_t n, void *workspace) {
   workspace_ = workspace;
   for (size_t i = 0; i < n; ++i) relocs[i].io->addr = relocs[i].addr;
   for (auto &st : stages_) {
+    dvmb::VmParam &P = st.param;
+    uint32_t staged = 0;
     for (size_t s = 0; s < st.slot_obj.size(); ++s) {
-      dvmb::TensorDesc &td = st.param.tensor[s];
+      dvmb::TensorDesc &td = P.tensor[s];
       td.ptr = reinterpret_cast<uint64_t>(st.slot_obj[s]->addr);
       const uint64_t align = 4ull * ItemSize(static_cast<DataType>(td.dtype));
-      td.vec_ok = (td.pad && td.ptr != 0 && td.ptr % align == 0) ? 1 : 0;
+      td.vec_ok = (td.layout_vec && td.ptr != 0 && td.ptr % align == 0) ? 1 : 0;
+      // a tensor planned for bulk staging keeps its ring slot only if its address is 16-byte aligned
+      if (td.ring_layout && td.ptr % 16 == 0) {
+        staged |= 1u << s;
+      } else if (td.ring_layout) {
+        td.ring_off = dvmb::kNoRing;
+      }
     }
+    for (uint32_t q = 0; q < P.num_body; ++q) P.body_ring_mask[q] = st.body_tensor_mask[q] & staged;
   }
 }
 
@@ -88,7 +97,7 @@ int VKernel::Launch(void *stream) {
     if (st.idle) continue;
     for (size_t s = 0; s < st.slot_obj.size(); ++s)
       if (st.param.tensor[s].ptr == 0) DvmException("Launch with an unbound tensor address");
-    int err = dvmb::LaunchVector(st.param, st.grid, st.threads, stream);
+    int err = dvmb::LaunchVector(st.param, st.grid, st.threads, st.smem_bytes, stream);
     if (err != 0) return err;
   }
   return 0;

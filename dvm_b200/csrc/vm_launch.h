@@ -9,11 +9,20 @@
 
 namespace dvmb {
 
-constexpr int kVmMaxThreads = 256;
-constexpr int kVmMinBlocks = 2;
+constexpr int kVmMaxThreads = 512;            // consumer threads per CTA (a producer warp is added on top)
+constexpr int kVmMinBlocks = 1;
+constexpr int kVmFlatThreads = 256;           // consumer threads of a reduce-free launch
+constexpr uint32_t kVmMaxSmemBytes = 200 * 1024;
+// dynamic shared memory layout: mbarriers, reduce scratch, then ring stages, temporaries, scalar registers
+constexpr uint32_t kVmSmemBarriers = 0;       // full[8] at +0, empty[8] at +64
+constexpr uint32_t kVmSmemRed = 128;          // float[2][32]
+constexpr uint32_t kVmSmemStages = 512;
+constexpr uint32_t kVmMaxStages = 8;
 
 // Enqueue the vector interpreter. Returns the cudaError_t of the launch (0 = ok).
-int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, void *stream);
+int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, uint32_t smem_bytes, void *stream);
+// Device status word (0 = ok); reading clears it.
+unsigned int ReadVectorStatus();
 
 }  // namespace dvmb
 

@@ -1,11 +1,17 @@
-// Persistent register-resident bytecode interpreter for fused vector graphs on sm_100a.
+// Persistent bytecode interpreter for fused vector graphs on sm_100a.
 //
-// One kernel executes every fused elementwise / broadcast / reduce graph the host compiler emits
-// (the role of dvm_vm_gpu in the reference, src/vm_gpu.cu:1552-1617, whose operands live in shared
-// memory; here every intermediate stays in registers and a fused graph touches HBM once per tensor).
+// One kernel executes every fused elementwise / broadcast / reduce graph the host compiler emits (the role
+// of dvm_vm_gpu in the reference, src/vm_gpu.cu:1552-1617).  Differences in kind, not in degree:
+//   * a producer warp streams the input chunks of upcoming tiles into a shared-memory ring with bulk async
+//     copies (cp.async.bulk, completion on mbarriers), so HBM latency is hidden by the ring depth and not
+//     by occupancy; the consumer warps read each operand straight from the ring, converting on the fly;
+//   * the running value of the fused chain stays in registers (an 8-lane accumulator); nothing is written
+//     back to shared memory between ops except values with several later uses (thread-private temporaries);
+//   * results leave the SM once, as 16-byte (fp32) / 8-byte (16-bit) coalesced stores.
 // Per-op arithmetic follows the reference's device functors (src/vm_gpu.cu:198-329): IEEE fp32 math,
 // fp16/bf16 values rounded to storage precision after every op, float->int by truncation, compares
 // yielding 1/0 in the operand representation, max/min as `a > b ? a : b` / `a < b ? a : b`.
+// Every wait on an mbarrier is bounded: on expiry the thread records a status code and leaves.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <math_constants.h>
@@ -16,6 +22,8 @@
 #include "vm_launch.h"
 
 namespace dvmb {
+
+__device__ unsigned int g_vm_status = 0;   // 0 = ok; else (code << 24 | blockIdx)
 
 namespace {
 
@@ -30,6 +38,12 @@ __device__ __forceinline__ float round_bf16(float v) {
   u += 0x7fffu + ((u >> 16) & 1u);
   return u2f(u & 0xffff0000u);
 }
+// Two floats -> packed bf16x2 (lo in bits 0..15), hardware round-to-nearest-even, NaN preserved.
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
 
 template <int N>
 __device__ __forceinline__ void apply_round(uint32_t rnd, uint32_t (&a)[N]) {
@@ -37,8 +51,17 @@ __device__ __forceinline__ void apply_round(uint32_t rnd, uint32_t (&a)[N]) {
 #pragma unroll
     for (int i = 0; i < N; ++i) a[i] = f2u(round_f16(u2f(a[i])));
   } else if (rnd == RN_BF16) {
+    if constexpr (N % 2 == 0) {
 #pragma unroll
-    for (int i = 0; i < N; ++i) a[i] = f2u(round_bf16(u2f(a[i])));
+      for (int i = 0; i < N; i += 2) {
+        uint32_t p = pack_bf16x2(u2f(a[i]), u2f(a[i + 1]));
+        a[i] = p << 16;
+        a[i + 1] = p & 0xffff0000u;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < N; ++i) a[i] = f2u(round_bf16(u2f(a[i])));
+    }
   }
 }
 
@@ -71,19 +94,30 @@ __device__ __forceinline__ void apply_un(uint32_t kind, uint32_t (&a)[N]) {
   }
 }
 
+// Second operands come either as a per-lane vector or as one value for all lanes.
+template <int N>
+struct VecOperand {
+  const uint32_t (&v)[N];
+  __device__ __forceinline__ uint32_t operator()(int i) const { return v[i]; }
+};
+struct SplatOperand {
+  uint32_t v;
+  __device__ __forceinline__ uint32_t operator()(int) const { return v; }
+};
+
 #define DVMB_BIN_F(EXPR)                   \
   _Pragma("unroll") for (int i = 0; i < N; ++i) { \
-    float x = u2f(a[i]), y = u2f(b[i]);    \
+    float x = u2f(a[i]), y = u2f(b(i));    \
     a[i] = f2u(EXPR);                      \
   }
 #define DVMB_BIN_I(EXPR)                   \
   _Pragma("unroll") for (int i = 0; i < N; ++i) { \
-    int32_t x = (int32_t)a[i], y = (int32_t)b[i]; \
+    int32_t x = (int32_t)a[i], y = (int32_t)b(i); \
     a[i] = (uint32_t)(EXPR);               \
   }
 
-template <int N>
-__device__ __forceinline__ void apply_bin(uint32_t kind, uint32_t (&a)[N], const uint32_t (&b)[N]) {
+template <int N, class B>
+__device__ __forceinline__ void apply_bin(uint32_t kind, uint32_t (&a)[N], const B &b) {
   switch (kind) {
     case B_ADD: DVMB_BIN_F(x + y) break;
     case B_SUB: DVMB_BIN_F(x - y) break;
@@ -116,26 +150,26 @@ __device__ __forceinline__ bool cmp_value(uint32_t kind, T x, T y) {
   }
 }
 
-template <int N>
-__device__ __forceinline__ void apply_cmp(uint32_t kind, uint32_t isint, uint32_t (&a)[N], const uint32_t (&b)[N]) {
+template <int N, class B>
+__device__ __forceinline__ void apply_cmp(uint32_t kind, uint32_t isint, uint32_t (&a)[N], const B &b) {
   if (isint) {
 #pragma unroll
-    for (int i = 0; i < N; ++i) a[i] = cmp_value<int32_t>(kind, (int32_t)a[i], (int32_t)b[i]) ? 1u : 0u;
+    for (int i = 0; i < N; ++i) a[i] = cmp_value<int32_t>(kind, (int32_t)a[i], (int32_t)b(i)) ? 1u : 0u;
   } else {
 #pragma unroll
-    for (int i = 0; i < N; ++i) a[i] = cmp_value<float>(kind, u2f(a[i]), u2f(b[i])) ? 0x3f800000u : 0u;
+    for (int i = 0; i < N; ++i) a[i] = cmp_value<float>(kind, u2f(a[i]), u2f(b(i))) ? 0x3f800000u : 0u;
   }
 }
 
 // a <- cond(a) ? b : c; `inv` swaps the alternatives (the free-form operand b is then the false value).
-template <int N>
-__device__ __forceinline__ void apply_sel(uint32_t isint, uint32_t inv, uint32_t (&a)[N], const uint32_t (&b)[N],
+template <int N, class B>
+__device__ __forceinline__ void apply_sel(uint32_t isint, uint32_t inv, uint32_t (&a)[N], const B &b,
                                           const uint32_t (&c)[N]) {
 #pragma unroll
   for (int i = 0; i < N; ++i) {
     bool t = isint ? (a[i] != 0u) : (u2f(a[i]) != 0.0f);
     if (inv) t = !t;
-    a[i] = t ? b[i] : c[i];
+    a[i] = t ? b(i) : c[i];
   }
 }
 
@@ -169,7 +203,7 @@ __device__ __forceinline__ float red_combine(uint32_t kind, float x, float y) {
   return kind == R_SUM ? x + y : (kind == R_MAX ? (x > y ? x : y) : (x < y ? x : y));
 }
 
-// ---- global memory access -------------------------------------------------------------------------
+// ---- element conversion ---------------------------------------------------------------------------
 
 __device__ __forceinline__ uint32_t widen(uint32_t dtype, uint32_t raw) {
   switch (dtype) {
@@ -207,35 +241,55 @@ __device__ __forceinline__ void store_elem(uint32_t dtype, uint8_t *base, uint32
   }
 }
 
-__device__ __forceinline__ void load_vec4(uint32_t dtype, const uint8_t *base, uint32_t off, uint32_t *out) {
+// Unpack one raw 4-element granule (16 / 8 / 4 bytes by dtype) into register form.
+__device__ __forceinline__ void unpack4(uint32_t dtype, uint4 raw, uint32_t *out) {
   switch (dtype) {
     case T_F32:
-    case T_I32: {
-      uint4 v = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const uint32_t *>(base) + off));
-      out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
-      break;
-    }
+    case T_I32: out[0] = raw.x; out[1] = raw.y; out[2] = raw.z; out[3] = raw.w; break;
     case T_F16: {
-      uint2 v = __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const unsigned short *>(base) + off));
-      float2 lo = __half22float2(*reinterpret_cast<__half2 *>(&v.x));
-      float2 hi = __half22float2(*reinterpret_cast<__half2 *>(&v.y));
+      float2 lo = __half22float2(*reinterpret_cast<__half2 *>(&raw.x));
+      float2 hi = __half22float2(*reinterpret_cast<__half2 *>(&raw.y));
       out[0] = f2u(lo.x); out[1] = f2u(lo.y); out[2] = f2u(hi.x); out[3] = f2u(hi.y);
       break;
     }
-    case T_BF16: {
-      uint2 v = __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const unsigned short *>(base) + off));
-      out[0] = v.x << 16; out[1] = v.x & 0xffff0000u; out[2] = v.y << 16; out[3] = v.y & 0xffff0000u;
+    case T_BF16:
+      out[0] = raw.x << 16; out[1] = raw.x & 0xffff0000u; out[2] = raw.y << 16; out[3] = raw.y & 0xffff0000u;
       break;
-    }
-    default: {
-      uint32_t v = __ldg(reinterpret_cast<const uint32_t *>(base + off));
-      out[0] = v & 0xffu; out[1] = (v >> 8) & 0xffu; out[2] = (v >> 16) & 0xffu; out[3] = v >> 24;
+    default:
+      out[0] = raw.x & 0xffu; out[1] = (raw.x >> 8) & 0xffu; out[2] = (raw.x >> 16) & 0xffu; out[3] = raw.x >> 24;
       break;
-    }
   }
 }
 
-__device__ __forceinline__ void store_vec4(uint32_t dtype, uint8_t *base, uint32_t off, const uint32_t *v) {
+__device__ __forceinline__ uint4 gload4(uint32_t dtype, const uint8_t *base, uint32_t off) {
+  uint4 r = make_uint4(0, 0, 0, 0);
+  switch (dtype) {
+    case T_F32:
+    case T_I32: r = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const uint32_t *>(base) + off)); break;
+    case T_F16:
+    case T_BF16: {
+      uint2 v = __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const unsigned short *>(base) + off));
+      r.x = v.x; r.y = v.y;
+      break;
+    }
+    default: r.x = __ldg(reinterpret_cast<const uint32_t *>(base + off)); break;
+  }
+  return r;
+}
+
+__device__ __forceinline__ uint4 sload4(uint32_t dtype, uint32_t saddr) {
+  uint4 r = make_uint4(0, 0, 0, 0);
+  switch (dtype) {
+    case T_F32:
+    case T_I32: asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(saddr)); break;
+    case T_F16:
+    case T_BF16: asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "r"(saddr)); break;
+    default: asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r.x) : "r"(saddr)); break;
+  }
+  return r;
+}
+
+__device__ __forceinline__ void gstore4(uint32_t dtype, uint8_t *base, uint32_t off, const uint32_t *v) {
   switch (dtype) {
     case T_F32:
     case T_I32:
@@ -252,8 +306,8 @@ __device__ __forceinline__ void store_vec4(uint32_t dtype, uint8_t *base, uint32
     }
     case T_BF16: {
       uint2 p;
-      p.x = (f2u(round_bf16(u2f(v[0]))) >> 16) | (f2u(round_bf16(u2f(v[1]))) & 0xffff0000u);
-      p.y = (f2u(round_bf16(u2f(v[2]))) >> 16) | (f2u(round_bf16(u2f(v[3]))) & 0xffff0000u);
+      p.x = pack_bf16x2(u2f(v[0]), u2f(v[1]));
+      p.y = pack_bf16x2(u2f(v[2]), u2f(v[3]));
       *reinterpret_cast<uint2 *>(reinterpret_cast<unsigned short *>(base) + off) = p;
       break;
     }
@@ -264,12 +318,68 @@ __device__ __forceinline__ void store_vec4(uint32_t dtype, uint8_t *base, uint32
   }
 }
 
+__device__ __forceinline__ uint32_t item_shift(uint32_t dtype) {
+  return dtype == T_BOOL ? 0u : ((dtype == T_F16 || dtype == T_BF16) ? 1u : 2u);
+}
+
+// ---- mbarrier / bulk copy -------------------------------------------------------------------------
+
+__device__ __forceinline__ void mbar_init(uint32_t addr, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(addr), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t addr) {
+  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(addr) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t addr, uint32_t bytes) {
+  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(addr), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t addr, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+    "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+    : "=r"(ok)
+    : "r"(addr), "r"(parity)
+    : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after about two seconds and records `code` in the status word.  Once any wait
+// of the launch has expired every later wait returns at once, so the kernel always runs to its end (with
+// wrong results, which the host reports through the status word) instead of hanging.
+__device__ __noinline__ void mbar_wait_slow(uint32_t addr, uint32_t parity, uint32_t code) {
+  unsigned long long t0, t1;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (;;) {
+    if (*reinterpret_cast<volatile unsigned int *>(&g_vm_status) != 0u) return;
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(addr, parity)) return;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    if (t1 - t0 > 2000000000ull) {
+      atomicCAS(&g_vm_status, 0u, (code << 24) | (blockIdx.x & 0xffffffu));
+      return;
+    }
+  }
+}
+__device__ __forceinline__ void mbar_wait(uint32_t addr, uint32_t parity, uint32_t code) {
+  if (mbar_try_wait(addr, parity)) return;
+  mbar_wait_slow(addr, parity, code);
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t mbar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+               "l"(src), "r"(bytes), "r"(mbar)
+               : "memory");
+}
+
+// ---- addressing -----------------------------------------------------------------------------------
+
 // Per-thread position inside the iteration space.
 struct Pos {
-  uint32_t k[kMaxKept];   // kept coordinates of this thread's group
-  uint32_t e0[2];         // first element (inside the group) of each granule
-  int32_t nv[2];          // valid elements of each granule (0..4)
+  uint32_t k[kMaxKept];      // kept coordinates of this thread's group
+  uint32_t e0[2];            // first element (inside the group) of each granule
+  int32_t nv[2];             // valid elements of each granule (0..4)
   uint32_t ec[2][kMaxEnum];  // enumerated coordinates of each granule's first element (AM_GRANULE)
+  uint32_t in_chunk[2];      // element index of each granule inside its chunk
+  uint32_t chunk_valid;      // valid elements of the current chunk
   bool gvalid;
 };
 
@@ -284,10 +394,10 @@ __device__ __forceinline__ void split_enum(const VmParam &P, uint32_t e, uint32_
   c[0] = e;
 }
 
-__device__ __forceinline__ uint32_t kept_offset(const TensorDesc &td, const Pos &pos) {
+__device__ __forceinline__ uint32_t kept_offset(const TensorDesc &td, const uint32_t (&k)[kMaxKept]) {
   uint32_t off = 0;
 #pragma unroll
-  for (int j = 0; j < kMaxKept; ++j) off += pos.k[j] * td.kstride[j];
+  for (int j = 0; j < kMaxKept; ++j) off += k[j] * td.kstride[j];
   return off;
 }
 
@@ -298,15 +408,26 @@ __device__ __forceinline__ uint32_t enum_offset(const TensorDesc &td, const uint
   return off;
 }
 
-__device__ __forceinline__ void load_tile(const VmParam &P, uint32_t slot, const Pos &pos, uint32_t (&out)[kLanes]) {
+// Fetch the 8 lanes of tensor `slot` for this thread: from the ring stage when the tensor is staged and the
+// granule lies inside the bulk-copied part, else straight from global memory.
+__device__ __forceinline__ void fetch_tensor(const VmParam &P, uint32_t slot, const Pos &pos, uint32_t stage_saddr,
+                                             uint32_t (&out)[kLanes]) {
   const TensorDesc &td = P.tensor[slot];
-  const uint8_t *base = reinterpret_cast<const uint8_t *>(td.ptr);
   const uint32_t dtype = td.dtype, mode = td.mode;
-  const uint32_t koff = kept_offset(td, pos);
+  const uint32_t sh = item_shift(dtype);
+  const bool staged = td.ring_off != kNoRing;
+  // elements of the chunk that the bulk copy delivered (whole 16-byte units)
+  const uint32_t bulk_elems = staged ? (((pos.chunk_valid << sh) & ~15u) >> sh) : 0u;
+  const uint8_t *base = reinterpret_cast<const uint8_t *>(td.ptr);
+  const uint32_t koff = kept_offset(td, pos.k);
 #pragma unroll
   for (int g = 0; g < 2; ++g) {
-    const int nv = pos.gvalid ? pos.nv[g] : 0;
     uint32_t *o = &out[4 * g];
+    if (staged && pos.in_chunk[g] + 4 <= bulk_elems) {
+      unpack4(dtype, sload4(dtype, stage_saddr + td.ring_off + (pos.in_chunk[g] << sh)), o);
+      continue;
+    }
+    const int nv = pos.gvalid ? pos.nv[g] : 0;
     if (mode == AM_ELEMENT) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -330,7 +451,7 @@ __device__ __forceinline__ void load_tile(const VmParam &P, uint32_t slot, const
       istride = 0;
     }
     if (td.vec_ok && nv == 4) {
-      load_vec4(dtype, base, off, o);
+      unpack4(dtype, gload4(dtype, base, off), o);
     } else {
 #pragma unroll
       for (int i = 0; i < 4; ++i) o[i] = i < nv ? load_elem(dtype, base, off + i * istride) : 0u;
@@ -338,12 +459,12 @@ __device__ __forceinline__ void load_tile(const VmParam &P, uint32_t slot, const
   }
 }
 
-__device__ __forceinline__ void store_tile(const VmParam &P, uint32_t slot, const Pos &pos,
-                                           const uint32_t (&val)[kLanes]) {
+__device__ __forceinline__ void store_tensor(const VmParam &P, uint32_t slot, const Pos &pos,
+                                             const uint32_t (&val)[kLanes]) {
   const TensorDesc &td = P.tensor[slot];
   uint8_t *base = reinterpret_cast<uint8_t *>(td.ptr);
   const uint32_t dtype = td.dtype, mode = td.mode;
-  const uint32_t koff = kept_offset(td, pos);
+  const uint32_t koff = kept_offset(td, pos.k);
 #pragma unroll
   for (int g = 0; g < 2; ++g) {
     const int nv = pos.gvalid ? pos.nv[g] : 0;
@@ -370,7 +491,7 @@ __device__ __forceinline__ void store_tile(const VmParam &P, uint32_t slot, cons
       istride = 0;
     }
     if (td.vec_ok && nv == 4) {
-      store_vec4(dtype, base, off, v);
+      gstore4(dtype, base, off, v);
     } else {
 #pragma unroll
       for (int i = 0; i < 4; ++i)
@@ -378,32 +499,6 @@ __device__ __forceinline__ void store_tile(const VmParam &P, uint32_t slot, cons
     }
   }
 }
-
-#define DVMB_VREG_CASES(IDX, STMT) \
-  switch (IDX) {                   \
-    case 0: { constexpr int J = 0; STMT } break; \
-    case 1: { constexpr int J = 1; STMT } break; \
-    case 2: { constexpr int J = 2; STMT } break; \
-    case 3: { constexpr int J = 3; STMT } break; \
-    case 4: { constexpr int J = 4; STMT } break; \
-    default: { constexpr int J = 5; STMT } break; \
-  }
-
-#define DVMB_SREG_CASES(IDX, STMT) \
-  switch (IDX) {                   \
-    case 0: { constexpr int J = 0; STMT } break; \
-    case 1: { constexpr int J = 1; STMT } break; \
-    case 2: { constexpr int J = 2; STMT } break; \
-    case 3: { constexpr int J = 3; STMT } break; \
-    case 4: { constexpr int J = 4; STMT } break; \
-    case 5: { constexpr int J = 5; STMT } break; \
-    case 6: { constexpr int J = 6; STMT } break; \
-    case 7: { constexpr int J = 7; STMT } break; \
-    case 8: { constexpr int J = 8; STMT } break; \
-    case 9: { constexpr int J = 9; STMT } break; \
-    case 10: { constexpr int J = 10; STMT } break; \
-    default: { constexpr int J = 11; STMT } break; \
-  }
 
 #define DVMB_PART_CASES(IDX, STMT) \
   switch (IDX) {                   \
@@ -413,52 +508,118 @@ __device__ __forceinline__ void store_tile(const VmParam &P, uint32_t slot, cons
     default: { constexpr int J = 3; STMT } break; \
   }
 
+__device__ __forceinline__ void decompose_group(const VmParam &P, uint32_t gi, uint32_t (&k)[kMaxKept]) {
+#pragma unroll
+  for (int j = kMaxKept - 1; j > 0; --j) {
+    uint32_t sz = P.kept_size[j];
+    uint32_t q = gi / sz;
+    k[j] = gi - q * sz;
+    gi = q;
+  }
+  k[0] = gi;
+}
+
 }  // namespace
 
-__global__ void __launch_bounds__(kVmMaxThreads, kVmMinBlocks) dvm_b200_vm_vector(const __grid_constant__ VmParam P) {
-  __shared__ float red_buf[2][32];
+namespace {
+__device__ __forceinline__ void vm_vector_body(const VmParam &P) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  const uint32_t tid = threadIdx.x;
+  const uint32_t T = P.tg * P.groups_per_cta;   // consumer threads
+  const bool flat = P.mode == VM_FLAT;
+  const uint32_t S = P.num_stages;
+  const bool ring = P.stage_bytes != 0;
+  const uint32_t ngb = flat ? 1u : (P.num_groups + P.groups_per_cta - 1) / P.groups_per_cta;
+  const uint32_t gb_begin = flat ? 0u : blockIdx.x, gb_step = flat ? 1u : gridDim.x;
+  const uint32_t ch_begin = flat ? blockIdx.x : 0u, ch_step = flat ? gridDim.x : 1u;
+
+  if (ring) {
+    if (tid == 0) {
+      for (uint32_t s = 0; s < S; ++s) {
+        mbar_init(smem_base + kVmSmemBarriers + 8 * s, 1);        // full: one arrival (the producer) + tx bytes
+        mbar_init(smem_base + kVmSmemBarriers + 64 + 8 * s, T);   // empty: every consumer thread
+      }
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+  }
+
+  // =============================== producer warp ===============================
+  if (tid >= T) {
+    if (tid != T) return;
+    uint32_t seq = 0;
+    for (uint32_t gb = gb_begin; gb < ngb; gb += gb_step) {
+      uint32_t k[kMaxKept];
+      decompose_group(P, gb, k);   // groups_per_cta == 1 whenever the ring is on
+      for (uint32_t ph = 0; ph < P.num_body; ++ph) {
+        const uint32_t mask = P.body_ring_mask[ph];
+        if (mask == 0) continue;
+        for (uint32_t ch = ch_begin; ch < P.chunks; ch += ch_step, ++seq) {
+          const uint32_t stage = seq % S, use = seq / S;
+          const uint32_t full = smem_base + kVmSmemBarriers + 8 * stage;
+          mbar_wait(full + 64, (use & 1u) ^ 1u, 1);
+          const uint32_t e_start = ch * P.chunk_elems;
+          const uint32_t valid = min(P.chunk_elems, P.group_elems - e_start);
+          uint32_t c[kMaxEnum];
+          split_enum(P, e_start, c);
+          uint32_t total = 0;
+          for (uint32_t m = mask; m; m &= m - 1) {
+            const TensorDesc &td = P.tensor[__ffs(m) - 1];
+            total += (valid << item_shift(td.dtype)) & ~15u;
+          }
+          if (total == 0) {
+            mbar_arrive(full);
+            continue;
+          }
+          mbar_arrive_expect_tx(full, total);
+          const uint32_t stage_saddr = smem_base + kVmSmemStages + stage * P.stage_bytes;
+          for (uint32_t m = mask; m; m &= m - 1) {
+            const TensorDesc &td = P.tensor[__ffs(m) - 1];
+            const uint32_t sh = item_shift(td.dtype);
+            const uint32_t bytes = (valid << sh) & ~15u;
+            if (bytes == 0) continue;
+            const uint32_t off = kept_offset(td, k) + enum_offset(td, c);
+            bulk_g2s(stage_saddr + td.ring_off, reinterpret_cast<const uint8_t *>(td.ptr) + ((size_t)off << sh), bytes, full);
+          }
+        }
+      }
+    }
+    return;
+  }
+
+  // =============================== consumer warps ===============================
+  float *red_buf = reinterpret_cast<float *>(smem + kVmSmemRed);
+  const uint32_t temps_saddr = smem_base + kVmSmemStages + S * P.stage_bytes;
+  const uint32_t sregs_saddr = temps_saddr + P.num_temps * T * 32u;
+  const uint32_t tg = P.tg;
+  const uint32_t lane_in_group = flat ? tid : tid % tg;
+  const uint32_t group_in_cta = flat ? 0 : tid / tg;
 
   uint32_t acc[kLanes];
-  uint32_t r[kNumVRegs][kLanes];
-  uint32_t s[kNumSRegs];
   uint32_t sacc[1] = {0};
   float part[kNumRSlots];
 #pragma unroll
   for (int i = 0; i < kLanes; ++i) acc[i] = 0;
 #pragma unroll
-  for (int j = 0; j < kNumVRegs; ++j)
-#pragma unroll
-    for (int i = 0; i < kLanes; ++i) r[j][i] = 0;
-#pragma unroll
-  for (int j = 0; j < kNumSRegs; ++j) s[j] = 0;
-#pragma unroll
   for (int j = 0; j < kNumRSlots; ++j) part[j] = 0.0f;
-
-  const uint32_t tid = threadIdx.x;
-  const uint32_t tg = P.tg;
-  const bool flat = P.mode == VM_FLAT;
-  const uint32_t lane_in_group = flat ? tid : tid % tg;
-  const uint32_t group_in_cta = flat ? 0 : tid / tg;
-  const uint32_t ngb = flat ? 1u : (P.num_groups + P.groups_per_cta - 1) / P.groups_per_cta;
-  const uint32_t gb_begin = flat ? 0u : blockIdx.x, gb_step = flat ? 1u : gridDim.x;
-  const uint32_t ch_begin = flat ? blockIdx.x : 0u, ch_step = flat ? gridDim.x : 1u;
   uint32_t red_par = 0;
-
+  uint32_t seq = 0;
   Pos pos;
+
+  auto temp_addr = [&](uint32_t k, uint32_t g) { return temps_saddr + ((k * 2 + g) * T + tid) * 16u; };
+  auto sreg_addr = [&](uint32_t k) { return sregs_saddr + (k * T + tid) * 4u; };
+  auto lds32 = [](uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+  };
 
   for (uint32_t gb = gb_begin; gb < ngb; gb += gb_step) {
     {
       uint32_t gi = gb * P.groups_per_cta + group_in_cta;
       pos.gvalid = gi < P.num_groups;
-      if (!pos.gvalid) gi = 0;
-#pragma unroll
-      for (int j = kMaxKept - 1; j > 0; --j) {
-        uint32_t sz = P.kept_size[j];
-        uint32_t q = gi / sz;
-        pos.k[j] = gi - q * sz;
-        gi = q;
-      }
-      pos.k[0] = gi;
+      decompose_group(P, pos.gvalid ? gi : 0u, pos.k);
     }
     for (uint32_t ph = 0; ph <= P.num_body; ++ph) {
       // ---------------- scalar side: PRO_ph ----------------
@@ -467,53 +628,37 @@ __global__ void __launch_bounds__(kVmMaxThreads, kVmMinBlocks) dvm_b200_vm_vecto
         const uint32_t opc = DVMB_OPC(w);
         if (opc == OP_END) break;
         const uint32_t sub = DVMB_SUB(w);
-        uint32_t b[1] = {0};
+        uint32_t b = 0;
         if (opc == OP_COPY || opc == OP_BIN || opc == OP_CMP || opc == OP_SEL) {
           const uint32_t okind = DVMB_OKIND(w), oidx = DVMB_OIDX(w);
           if (okind == K_SREG) {
-            DVMB_SREG_CASES(oidx, b[0] = s[J];)
+            b = lds32(sreg_addr(oidx));
           } else if (okind == K_IMM) {
-            b[0] = DVMB_IMM(w);
+            b = DVMB_IMM(w);
+          } else if (okind == K_TENSOR) {
+            const TensorDesc &td = P.tensor[oidx];
+            b = load_elem(td.dtype, reinterpret_cast<const uint8_t *>(td.ptr), kept_offset(td, pos.k));
           } else {
-            b[0] = sacc[0];
+            b = sacc[0];
           }
         }
+        const SplatOperand bo{b};
         switch (opc) {
-          case OP_LD: {
-            const TensorDesc &td = P.tensor[sub];
-            uint32_t v = load_elem(td.dtype, reinterpret_cast<const uint8_t *>(td.ptr), kept_offset(td, pos));
-            const uint32_t dst = DVMB_DST(w);
-            if (dst == kAccIdx) {
-              sacc[0] = v;
-            } else {
-              DVMB_SREG_CASES(dst, s[J] = v;)
-            }
-            break;
-          }
           case OP_ST: {
             const TensorDesc &td = P.tensor[sub];
             if (lane_in_group == 0 && pos.gvalid && (!flat || blockIdx.x == 0))
-              store_elem(td.dtype, reinterpret_cast<uint8_t *>(td.ptr), kept_offset(td, pos), sacc[0]);
+              store_elem(td.dtype, reinterpret_cast<uint8_t *>(td.ptr), kept_offset(td, pos.k), sacc[0]);
             break;
           }
-          case OP_COPY: sacc[0] = b[0]; break;
-          case OP_MOV: {
-            const uint32_t dst = DVMB_DST(w);
-            DVMB_SREG_CASES(dst, s[J] = sacc[0];)
-            break;
-          }
+          case OP_COPY: sacc[0] = b; break;
+          case OP_MOV: asm volatile("st.shared.u32 [%0], %1;" ::"r"(sreg_addr(DVMB_DST(w))), "r"(sacc[0]) : "memory"); break;
           case OP_UN: apply_un<1>(sub, sacc); apply_round<1>(DVMB_RND(w), sacc); break;
-          case OP_BIN: apply_bin<1>(sub, sacc, b); apply_round<1>(DVMB_RND(w), sacc); break;
-          case OP_CMP: apply_cmp<1>(sub, DVMB_ISINT(w), sacc, b); break;
+          case OP_BIN: apply_bin<1>(sub, sacc, bo); apply_round<1>(DVMB_RND(w), sacc); break;
+          case OP_CMP: apply_cmp<1>(sub, DVMB_ISINT(w), sacc, bo); break;
           case OP_SEL: {
-            uint32_t c[1] = {0};
-            const uint32_t k2 = sub >> 4, i2 = sub & 15u;
-            if (k2 == K_SREG) {
-              DVMB_SREG_CASES(i2, c[0] = s[J];)
-            } else {
-              c[0] = sacc[0];
-            }
-            apply_sel<1>(DVMB_ISINT(w), DVMB_DST(w) & 1u, sacc, b, c);
+            uint32_t c[1];
+            c[0] = lds32(sreg_addr(sub & 15u));
+            apply_sel<1>(DVMB_ISINT(w), DVMB_DST(w) & 1u, sacc, bo, c);
             break;
           }
           case OP_CVT: apply_cvt<1>(sub, sacc); apply_round<1>(DVMB_RND(w), sacc); break;
@@ -531,11 +676,11 @@ __global__ void __launch_bounds__(kVmMaxThreads, kVmMinBlocks) dvm_b200_vm_vecto
             } else {
 #pragma unroll
               for (uint32_t o = 16; o > 0; o >>= 1) v = red_combine(kind, v, __shfl_xor_sync(0xffffffffu, v, o));
-              if ((tid & 31u) == 0) red_buf[red_par][tid >> 5] = v;
-              __syncthreads();
-              const uint32_t nw = blockDim.x >> 5;
-              v = red_buf[red_par][0];
-              for (uint32_t wi = 1; wi < nw; ++wi) v = red_combine(kind, v, red_buf[red_par][wi]);
+              if ((tid & 31u) == 0) red_buf[red_par * 32 + (tid >> 5)] = v;
+              asm volatile("bar.sync 1, %0;" ::"r"(T) : "memory");   // consumer warps only
+              const uint32_t nw = T >> 5;
+              v = red_buf[red_par * 32];
+              for (uint32_t wi = 1; wi < nw; ++wi) v = red_combine(kind, v, red_buf[red_par * 32 + wi]);
               red_par ^= 1u;
             }
             sacc[0] = f2u(v);
@@ -547,78 +692,101 @@ __global__ void __launch_bounds__(kVmMaxThreads, kVmMinBlocks) dvm_b200_vm_vecto
       if (ph == P.num_body) break;
       // ---------------- vector side: BODY_ph over the chunks ----------------
       const uint32_t body_pc = P.sec[2 * ph + 1];
+      const bool staged_body = ring && P.body_ring_mask[ph] != 0;
       for (uint32_t ch = ch_begin; ch < P.chunks; ch += ch_step) {
+        const uint32_t e_start = ch * P.chunk_elems;
+        pos.chunk_valid = min(P.chunk_elems, P.group_elems - e_start);
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
-          // 64-bit so that a chunk past the end of a 2^31-element group cannot wrap
-          const uint64_t e = (uint64_t)ch * (8ull * tg) + (uint64_t)g * 4ull * tg + 4ull * lane_in_group;
-          const int64_t left = (int64_t)P.group_elems - (int64_t)e;
-          pos.nv[g] = left >= 4 ? 4 : (left > 0 ? (int32_t)left : 0);
-          pos.e0[g] = (uint32_t)e;
+          const uint32_t ic = (uint32_t)g * 4u * tg + 4u * lane_in_group;
+          const int32_t left = (int32_t)pos.chunk_valid - (int32_t)ic;
+          pos.in_chunk[g] = ic;
+          pos.nv[g] = left >= 4 ? 4 : (left > 0 ? left : 0);
+          pos.e0[g] = e_start + ic;
           if (P.need_coords) split_enum(P, pos.nv[g] > 0 ? pos.e0[g] : 0u, pos.ec[g]);
+        }
+        uint32_t stage_saddr = 0, empty_bar = 0;
+        if (staged_body) {
+          const uint32_t stage = seq % S, use = seq / S;
+          ++seq;
+          stage_saddr = smem_base + kVmSmemStages + stage * P.stage_bytes;
+          empty_bar = smem_base + kVmSmemBarriers + 64 + 8 * stage;
+          mbar_wait(smem_base + kVmSmemBarriers + 8 * stage, use & 1u, 2);
         }
         for (uint32_t pc = body_pc;;) {
           const uint64_t w = P.code[pc++];
           const uint32_t opc = DVMB_OPC(w);
           if (opc == OP_END) break;
           const uint32_t sub = DVMB_SUB(w);
+          const uint32_t okind = DVMB_OKIND(w), oidx = DVMB_OIDX(w);
+          const bool has_operand = opc == OP_COPY || opc == OP_BIN || opc == OP_CMP || opc == OP_SEL;
+          const bool splat = okind == K_SREG || okind == K_IMM;
           uint32_t b[kLanes];
-          if (opc == OP_COPY || opc == OP_BIN || opc == OP_CMP || opc == OP_SEL) {
-            const uint32_t okind = DVMB_OKIND(w), oidx = DVMB_OIDX(w);
-            if (okind == K_VREG) {
-              DVMB_VREG_CASES(oidx, _Pragma("unroll") for (int i = 0; i < kLanes; ++i) b[i] = r[J][i];)
+          uint32_t bs = DVMB_IMM(w);
+          if (has_operand) {
+            if (okind == K_TENSOR) {
+              fetch_tensor(P, oidx, pos, stage_saddr, b);
+            } else if (okind == K_TEMP) {
+#pragma unroll
+              for (int g = 0; g < 2; ++g)
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(b[4 * g]), "=r"(b[4 * g + 1]), "=r"(b[4 * g + 2]), "=r"(b[4 * g + 3])
+                             : "r"(temp_addr(oidx, g)));
+            } else if (okind == K_SREG) {
+              bs = lds32(sreg_addr(oidx));
             } else if (okind == K_ACC) {
 #pragma unroll
               for (int i = 0; i < kLanes; ++i) b[i] = acc[i];
-            } else {
-              uint32_t v = DVMB_IMM(w);
-              if (okind == K_SREG) {
-                DVMB_SREG_CASES(oidx, v = s[J];)
-              }
-#pragma unroll
-              for (int i = 0; i < kLanes; ++i) b[i] = v;
             }
           }
+          const VecOperand<kLanes> bv{b};
+          const SplatOperand bo{bs};
           switch (opc) {
-            case OP_LD: {
-              const uint32_t dst = DVMB_DST(w);
-              if (dst == kAccIdx) {
-                load_tile(P, sub, pos, acc);
-              } else {
-                uint32_t t[kLanes];
-                load_tile(P, sub, pos, t);
-                DVMB_VREG_CASES(dst, _Pragma("unroll") for (int i = 0; i < kLanes; ++i) r[J][i] = t[i];)
-              }
-              break;
-            }
-            case OP_ST: store_tile(P, sub, pos, acc); break;
+            case OP_ST: store_tensor(P, sub, pos, acc); break;
             case OP_COPY:
+              if (splat) {
 #pragma unroll
-              for (int i = 0; i < kLanes; ++i) acc[i] = b[i];
+                for (int i = 0; i < kLanes; ++i) acc[i] = bs;
+              } else {
+#pragma unroll
+                for (int i = 0; i < kLanes; ++i) acc[i] = b[i];
+              }
               break;
             case OP_MOV: {
               const uint32_t dst = DVMB_DST(w);
-              DVMB_VREG_CASES(dst, _Pragma("unroll") for (int i = 0; i < kLanes; ++i) r[J][i] = acc[i];)
+#pragma unroll
+              for (int g = 0; g < 2; ++g)
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(temp_addr(dst, g)), "r"(acc[4 * g]),
+                             "r"(acc[4 * g + 1]), "r"(acc[4 * g + 2]), "r"(acc[4 * g + 3])
+                             : "memory");
               break;
             }
             case OP_UN: apply_un<kLanes>(sub, acc); apply_round<kLanes>(DVMB_RND(w), acc); break;
-            case OP_BIN: apply_bin<kLanes>(sub, acc, b); apply_round<kLanes>(DVMB_RND(w), acc); break;
-            case OP_CMP: apply_cmp<kLanes>(sub, DVMB_ISINT(w), acc, b); break;
+            case OP_BIN:
+              if (splat) apply_bin<kLanes>(sub, acc, bo); else apply_bin<kLanes>(sub, acc, bv);
+              apply_round<kLanes>(DVMB_RND(w), acc);
+              break;
+            case OP_CMP:
+              if (splat) apply_cmp<kLanes>(sub, DVMB_ISINT(w), acc, bo); else apply_cmp<kLanes>(sub, DVMB_ISINT(w), acc, bv);
+              break;
             case OP_SEL: {
               uint32_t c[kLanes];
               const uint32_t k2 = sub >> 4, i2 = sub & 15u;
-              if (k2 == K_VREG) {
-                DVMB_VREG_CASES(i2, _Pragma("unroll") for (int i = 0; i < kLanes; ++i) c[i] = r[J][i];)
-              } else if (k2 == K_SREG) {
-                uint32_t v = 0;
-                DVMB_SREG_CASES(i2, v = s[J];)
+              if (k2 == K_TENSOR) {
+                fetch_tensor(P, i2, pos, stage_saddr, c);
+              } else if (k2 == K_TEMP) {
+#pragma unroll
+                for (int g = 0; g < 2; ++g)
+                  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                               : "=r"(c[4 * g]), "=r"(c[4 * g + 1]), "=r"(c[4 * g + 2]), "=r"(c[4 * g + 3])
+                               : "r"(temp_addr(i2, g)));
+              } else {
+                const uint32_t v = lds32(sreg_addr(i2));
 #pragma unroll
                 for (int i = 0; i < kLanes; ++i) c[i] = v;
-              } else {
-#pragma unroll
-                for (int i = 0; i < kLanes; ++i) c[i] = acc[i];
               }
-              apply_sel<kLanes>(DVMB_ISINT(w), DVMB_DST(w) & 1u, acc, b, c);
+              if (splat) apply_sel<kLanes>(DVMB_ISINT(w), DVMB_DST(w) & 1u, acc, bo, c);
+              else apply_sel<kLanes>(DVMB_ISINT(w), DVMB_DST(w) & 1u, acc, bv, c);
               break;
             }
             case OP_CVT: apply_cvt<kLanes>(sub, acc); apply_round<kLanes>(DVMB_RND(w), acc); break;
@@ -634,14 +802,47 @@ __global__ void __launch_bounds__(kVmMaxThreads, kVmMinBlocks) dvm_b200_vm_vecto
             default: break;
           }
         }
+        if (staged_body) mbar_arrive(empty_bar);
       }
     }
   }
 }
+}  // namespace
 
-int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, void *stream) {
-  dvm_b200_vm_vector<<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(param);
+// Two register budgets of the same interpreter: up to 256 consumer threads with three CTAs per SM (the
+// streaming shapes), and up to 512 consumer threads (long reduction rows) with one.
+__global__ void __launch_bounds__(kVmFlatThreads + 32, 3) dvm_b200_vm_vector(const __grid_constant__ VmParam P) {
+  vm_vector_body(P);
+}
+__global__ void __launch_bounds__(kVmMaxThreads + 32, 1) dvm_b200_vm_vector_wide(const __grid_constant__ VmParam P) {
+  vm_vector_body(P);
+}
+
+int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, uint32_t smem_bytes, void *stream) {
+  static bool attr_set[64] = {false};   // the attribute is per device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(dvm_b200_vm_vector, cudaFuncAttributeMaxDynamicSharedMemorySize, kVmMaxSmemBytes);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(dvm_b200_vm_vector_wide, cudaFuncAttributeMaxDynamicSharedMemorySize, kVmMaxSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set[dev] = true;
+  }
+  if (threads <= kVmFlatThreads + 32) {
+    dvm_b200_vm_vector<<<grid, threads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(param);
+  } else {
+    dvm_b200_vm_vector_wide<<<grid, threads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(param);
+  }
   return static_cast<int>(cudaGetLastError());
+}
+
+// Read (and clear) the device status word of the vector interpreter; 0 means every bounded wait succeeded.
+unsigned int ReadVectorStatus() {
+  unsigned int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_vm_status, sizeof(v)) != cudaSuccess) return 0xffffffffu;
+  if (v != 0) cudaMemcpyToSymbol(g_vm_status, &zero, sizeof(zero));
+  return v;
 }
 
 }  // namespace dvmb
