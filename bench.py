@@ -179,10 +179,10 @@ def run_reference(args, rank):
 class DeviceWorkload:
     """One compiled fused graph with its inputs resident on the device."""
 
-    def __init__(self, name, seed_offset=0):
+    def __init__(self, name, seed_offset=0, scale=1.0):
         import dvm_b200 as dvm
         self.name = name
-        self.arrays = make_inputs(name, seed_offset)
+        self.arrays = make_inputs(name, seed_offset, scale)
         ktype = "vector:spec,dyn" if name == "c3" else "vector"
         self.k = dvm.PyKernel(ktype, "dev", int(os.environ.get("LOCAL_RANK", "0")))
         self.loads = [self.k.load(list(a.shape), dvm.frontend.dvm_dtype_of(a.dtype)) for a in self.arrays]
@@ -276,6 +276,8 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the other workloads, e2e and the CPU baseline")
+    ap.add_argument("--scale", type=float, default=1.0,
+                    help="fraction of the workload's leading dimension (profiling captures use a small case)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -295,7 +297,7 @@ def main():
         dist = td
 
     name = args.workload
-    wl = DeviceWorkload(name, seed_offset=1000 * rank)
+    wl = DeviceWorkload(name, seed_offset=1000 * rank, scale=args.scale)
     nbytes = algo_bytes(name, wl.arrays, [np.empty(s.shape(), wl.k.output(s).dtype) for s in wl.stores])
 
     with ClockSampler(local_rank) as clocks:
@@ -310,7 +312,8 @@ def main():
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": DTYPE[name], "data": "synthetic",
         "config": {"workload": WORKLOADS[name], "algorithmic_bytes_per_step_per_gpu": nbytes,
-                   "l2": "inputs larger than L2 (no flush)", "sharding": "each rank runs a full-size shard (batch x N)"},
+                   "l2": "inputs larger than L2 (no flush)", "sharding": "each rank runs a full-size shard (batch x N)",
+                   "scale": args.scale},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "peak_source": peak_src, "kernel": "dvm_b200_vm_vector",
                      "us_per_launch": {"min": lo, "mean": mean, "max": hi},

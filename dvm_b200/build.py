@@ -27,6 +27,9 @@ SOURCES = [
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
+    # the interpreters dispatch through dense switches: let ptxas build jump tables (the default threshold
+    # of 101 % never does)
+    "--jump-table-density=20",
     "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall,-Wno-unused-function",
 ]
 

@@ -84,6 +84,8 @@ struct VectorStage {
   uint32_t grid = 0, threads = 0, smem_bytes = 0;
   uint32_t body_tensor_mask[dvmb::kMaxPhases] = {0, 0, 0, 0};   // tensor slots each BODY reads
   bool idle = false;                       // zero-size domain: nothing to launch
+  std::vector<uint64_t> bytecode;          // instruction words of every section (what Das() prints)
+  uint16_t bsec[2 * dvmb::kMaxPhases + 2] = {0};   // section offsets inside `bytecode`
   std::vector<NDObject *> slot_obj;        // tensor slot -> load/store node (relocation sites)
   std::vector<int64_t> slot_ws_off;        // >= 0: slot is a workspace temporary at this byte offset
   uint64_t algo_bytes = 0;
@@ -121,6 +123,9 @@ class VKernel {
 // vcompile.cc
 bool CompileVectorStage(const std::vector<NDObject *> &ops, VectorStage *out, std::string *why);
 std::string DisassembleStage(const VectorStage &st);
+// Turn the stage's instruction words into the launch program (scalar sections + micro-ops) for the tensor
+// addresses now in the descriptors; called whenever addresses are (re)bound.
+void LowerStage(VectorStage *st);
 
 // normalize.cc
 void InferShape(NDObject *n);

@@ -27,7 +27,7 @@
 namespace dvmb {
 
 constexpr int kMaxTensors = 16;
-constexpr int kMaxCodeWords = 288;
+constexpr int kMaxCodeWords = 288;   // words of the program a launch carries (scalar sections + micro-ops)
 constexpr int kMaxKept = 3;
 constexpr int kMaxEnum = 4;
 constexpr int kNumTemps = 6;            // thread-private 8-lane temporaries in shared memory
@@ -106,6 +106,50 @@ struct Insn {
 #define DVMB_ISINT(w) ((uint32_t)((w) >> 62) & 0x1u)
 #define DVMB_SCALAR(w) ((uint32_t)((w) >> 63) & 0x1u)
 
+// ---- micro-ops ------------------------------------------------------------------------------------
+// BODY sections are not executed from the instruction words above but from micro-ops the host lowers them
+// to once the tensor addresses are known: one flat, dense handler id per word, every parameter resolved
+// (ring offset, register index, immediate), no tensor-descriptor reads on the fast paths.
+//   [7:0] handler   [15:8] aux   [31:16] arg16   [63:32] imm32
+enum UopHandler : uint32_t {
+  UH_END = 0,
+  // operand fetches; aux[1:0] = destination (UD_B / UD_ACC / UD_C), aux[5:2] = tensor slot
+  UH_LDR_F32, UH_LDR_F16, UH_LDR_BF16, UH_LDR_U8,   // from the ring stage, arg16 = ring offset / 16
+  UH_LDG,                                           // from global memory through the tensor descriptor
+  UH_LDT,                                           // thread-private temporary arg16
+  UH_LDS,                                           // scalar register arg16, splat
+  UH_LDI,                                           // imm32, splat
+  UH_MOVA,                                          // destination <- acc
+  UH_STT,                                           // temporary arg16 <- acc
+  // acc <- op(acc, b)
+  UH_BINV_FIRST,
+  UH_BINV_LAST = UH_BINV_FIRST + B_COUNT - 1,
+  // acc <- op(acc, scalar); aux bit0: scalar register arg16, else imm32
+  UH_BINS_FIRST,
+  UH_BINS_LAST = UH_BINS_FIRST + B_COUNT - 1,
+  UH_UN_FIRST,
+  UH_UN_LAST = UH_UN_FIRST + U_NOP,
+  UH_RND_F16, UH_RND_BF16,
+  // compares: aux[2:0] = CmpKind; the _S forms take aux bit7 = scalar register arg16, else imm32
+  UH_CMP_F_V, UH_CMP_F_S, UH_CMP_I_V, UH_CMP_I_S,
+  UH_SEL_F, UH_SEL_I,                               // acc <- cond(acc) ? b : c
+  UH_CVT_F2I, UH_CVT_I2F, UH_CVT_NEZ_F, UH_CVT_NEZ_I,
+  UH_RACC_SUM, UH_RACC_MAX, UH_RACC_MIN,            // arg16 = partial slot
+  UH_ST_F32, UH_ST_F16, UH_ST_BF16, UH_ST_U8,       // dense, aligned tensor arg16: vector stores
+  UH_STG,                                           // any tensor arg16
+  UH_COUNT
+};
+enum UopDest : uint32_t { UD_B = 0, UD_ACC = 1, UD_C = 2 };
+
+constexpr uint64_t MakeUop(uint32_t handler, uint32_t aux, uint32_t arg16, uint32_t imm) {
+  return (uint64_t)(handler & 0xff) | ((uint64_t)(aux & 0xff) << 8) | ((uint64_t)(arg16 & 0xffff) << 16) |
+         ((uint64_t)imm << 32);
+}
+#define DVMB_UH(u) ((uint32_t)(u) & 0xffu)
+#define DVMB_UAUX(u) (((uint32_t)(u) >> 8) & 0xffu)
+#define DVMB_UARG(u) ((uint32_t)(u) >> 16)
+#define DVMB_UIMM(u) ((uint32_t)((u) >> 32))
+
 // How a tensor's element offset is derived from (group, element-in-group).
 enum AddrMode : uint32_t {
   AM_DENSE = 0,    // offset = kept part + element index (contiguous over the enumerated axes)
@@ -148,7 +192,9 @@ struct VmParam {
   uint32_t enum_size[kMaxEnum];   // right-aligned, unused outer slots are 1
   uint32_t need_coords;      // some tensor uses AM_GRANULE or is staged per segment
   uint32_t num_body;         // number of BODY sections
-  uint16_t sec[2 * kMaxPhases + 2];  // word offset of PRO_0, BODY_0, PRO_1, ..., PRO_n (each ends with OP_END)
+  // word offset of PRO_0, BODY_0, PRO_1, ..., PRO_n in code[]: PRO sections hold instruction words ending
+  // with OP_END, BODY sections hold micro-ops ending with UH_END
+  uint16_t sec[2 * kMaxPhases + 2];
   uint32_t n_tensors;
   uint32_t n_code;
   TensorDesc tensor[kMaxTensors];

@@ -724,7 +724,7 @@ struct Compiler {
     std::vector<const NDObject *> sreg_val(kNumSRegs, nullptr);
     for (int p = 0; p <= num_body; ++p) {
       // ---- PRO_p
-      P.sec[2 * p] = static_cast<uint16_t>(code.size());
+      out->bsec[2 * p] = static_cast<uint16_t>(code.size());
       Side ss{this, true, 2 * p};
       ss.reg_val = sreg_val;
       if (p == 0) {
@@ -769,7 +769,7 @@ struct Compiler {
       sreg_val = ss.reg_val;
       if (p == num_body) break;
       // ---- BODY_p
-      P.sec[2 * p + 1] = static_cast<uint16_t>(code.size());
+      out->bsec[2 * p + 1] = static_cast<uint16_t>(code.size());
       Side vs{this, false, 2 * p + 1};
       CountUses(vs, body_order[p], body_roots[p]);
       // roots are interleaved in program order: emit each as soon as its value exists
@@ -799,14 +799,17 @@ struct Compiler {
       vs.Push0(OP_END, 0);
     }
     if (code.size() > static_cast<size_t>(kMaxCodeWords)) throw Fail{"program exceeds the bytecode capacity"};
+    // worst case of the lowered program: two micro-ops per operand-taking instruction plus a rounding one
+    size_t worst = 0;
+    for (uint64_t w : code) worst += DVMB_SCALAR(w) ? 1 : 4;
+    if (worst > static_cast<size_t>(kMaxCodeWords)) throw Fail{"program exceeds the micro-op capacity"};
   }
 
   // ---- step 5: fill VmParam -----------------------------------------------------------------------
   void Fill() {
     VmParam &P = out->param;
     P.num_body = num_body;
-    P.n_code = static_cast<uint32_t>(code.size());
-    std::memcpy(P.code, code.data(), code.size() * sizeof(uint64_t));
+    out->bytecode = code;
     int64_t K = 1, G = 1;
     for (auto &a : ckept) K *= a.size;
     for (auto &a : cenum) G *= a.size;
@@ -1012,6 +1015,107 @@ bool CompileVectorStage(const std::vector<NDObject *> &ops, VectorStage *out, st
   }
 }
 
+void LowerStage(VectorStage *st) {
+  using namespace dvmb;
+  VmParam &P = st->param;
+  uint32_t n = 0;
+  auto push = [&](uint64_t w) {
+    if (n >= static_cast<uint32_t>(kMaxCodeWords)) DvmException("lowered program exceeds the launch capacity");
+    P.code[n++] = w;
+  };
+  // fetch of an operand into destination `dest`
+  auto fetch = [&](uint32_t kind, uint32_t idx, uint32_t imm, uint32_t dest) {
+    switch (kind) {
+      case K_TENSOR: {
+        const TensorDesc &td = P.tensor[idx];
+        const uint32_t aux = dest | (idx << 2);
+        if (td.ring_off != kNoRing) {
+          static const uint32_t by_dtype[] = {UH_LDR_U8, UH_LDR_F16, UH_LDR_BF16, UH_LDR_F32, UH_LDR_F32};
+          push(MakeUop(by_dtype[td.dtype], aux, td.ring_off >> 4, 0));
+        } else {
+          push(MakeUop(UH_LDG, aux, 0, 0));
+        }
+        break;
+      }
+      case K_TEMP: push(MakeUop(UH_LDT, dest, idx, 0)); break;
+      case K_SREG: push(MakeUop(UH_LDS, dest, idx, 0)); break;
+      case K_IMM: push(MakeUop(UH_LDI, dest, 0, imm)); break;
+      default:
+        if (dest != UD_ACC) push(MakeUop(UH_MOVA, dest, 0, 0));
+        break;
+    }
+  };
+  auto round = [&](uint32_t rnd) {
+    if (rnd == RN_F16) push(MakeUop(UH_RND_F16, 0, 0, 0));
+    if (rnd == RN_BF16) push(MakeUop(UH_RND_BF16, 0, 0, 0));
+  };
+  for (uint32_t sidx = 0; sidx <= 2 * P.num_body; ++sidx) {
+    P.sec[sidx] = static_cast<uint16_t>(n);
+    const bool body = (sidx & 1u) != 0;
+    for (uint32_t pc = st->bsec[sidx];; ++pc) {
+      const uint64_t w = st->bytecode[pc];
+      const uint32_t opc = DVMB_OPC(w), sub = DVMB_SUB(w), okind = DVMB_OKIND(w), oidx = DVMB_OIDX(w);
+      if (!body) {   // scalar sections run from the instruction words as they are
+        push(w);
+        if (opc == OP_END) break;
+        continue;
+      }
+      if (opc == OP_END) {
+        push(MakeUop(UH_END, 0, 0, 0));
+        break;
+      }
+      const bool splat = okind == K_SREG || okind == K_IMM;
+      switch (opc) {
+        case OP_COPY: fetch(okind, oidx, DVMB_IMM(w), UD_ACC); break;
+        case OP_MOV: push(MakeUop(UH_STT, 0, DVMB_DST(w), 0)); break;
+        case OP_UN:
+          push(MakeUop(UH_UN_FIRST + sub, 0, 0, 0));
+          round(DVMB_RND(w));
+          break;
+        case OP_BIN:
+          if (splat) {
+            push(MakeUop(UH_BINS_FIRST + sub, okind == K_SREG ? 1 : 0, oidx, DVMB_IMM(w)));
+          } else {
+            fetch(okind, oidx, 0, UD_B);
+            push(MakeUop(UH_BINV_FIRST + sub, 0, 0, 0));
+          }
+          round(DVMB_RND(w));
+          break;
+        case OP_CMP:
+          if (splat) {
+            push(MakeUop(DVMB_ISINT(w) ? UH_CMP_I_S : UH_CMP_F_S, sub | (okind == K_SREG ? 0x80u : 0u), oidx, DVMB_IMM(w)));
+          } else {
+            fetch(okind, oidx, 0, UD_B);
+            push(MakeUop(DVMB_ISINT(w) ? UH_CMP_I_V : UH_CMP_F_V, sub, 0, 0));
+          }
+          break;
+        case OP_SEL: {
+          const bool inv = (DVMB_DST(w) & 1u) != 0;
+          fetch(okind, oidx, DVMB_IMM(w), inv ? UD_C : UD_B);   // the free-form alternative
+          fetch(sub >> 4, sub & 15u, 0, inv ? UD_B : UD_C);      // the register-like alternative
+          push(MakeUop(DVMB_ISINT(w) ? UH_SEL_I : UH_SEL_F, 0, 0, 0));
+          break;
+        }
+        case OP_CVT: {
+          static const uint32_t by_kind[] = {UH_CVT_F2I, UH_CVT_I2F, UH_CVT_NEZ_F, UH_CVT_NEZ_I};
+          if (sub != V_RND) push(MakeUop(by_kind[sub], 0, 0, 0));
+          round(DVMB_RND(w));
+          break;
+        }
+        case OP_RACC: push(MakeUop(UH_RACC_SUM + (sub >> 4), 0, sub & 3u, 0)); break;
+        case OP_ST: {
+          const TensorDesc &td = P.tensor[sub];
+          static const uint32_t by_dtype[] = {UH_ST_U8, UH_ST_F16, UH_ST_BF16, UH_ST_F32, UH_ST_F32};
+          push(MakeUop(td.mode == AM_DENSE && td.vec_ok ? by_dtype[td.dtype] : UH_STG, 0, sub, 0));
+          break;
+        }
+        default: break;
+      }
+    }
+  }
+  P.n_code = n;
+}
+
 // Text form of a stage's bytecode (the counterpart of the reference's disassembler, src/code.cc:1093-1498).
 // One line per instruction: "<pc>: <Name>.<type> <dst>, <operands>"; loads and stores print as
 // "load.<dtype> <dst>, <gm address>" / "store.<dtype> <gm address>, acc".
@@ -1051,13 +1155,13 @@ std::string DisassembleStage(const VectorStage &st) {
   };
   auto operand = [&](uint64_t w) -> std::string { return operand_text(DVMB_OKIND(w), DVMB_OIDX(w), DVMB_IMM(w)); };
   static const char *rnd_names[] = {"", ".rn_f16", ".rn_bf16", ""};
-  for (uint32_t pc = 0; pc < P.n_code; ++pc) {
+  for (uint32_t pc = 0; pc < st.bytecode.size(); ++pc) {
     for (uint32_t sidx = 0; sidx <= 2 * P.num_body; ++sidx)
-      if (P.sec[sidx] == pc) {
+      if (st.bsec[sidx] == pc) {
         snprintf(buf, sizeof(buf), " %s_%u:\n", (sidx & 1) ? "body" : "pro", sidx / 2);
         o += buf;
       }
-    const uint64_t w = P.code[pc];
+    const uint64_t w = st.bytecode[pc];
     const uint32_t opc = DVMB_OPC(w), sub = DVMB_SUB(w), dst = DVMB_DST(w);
     const bool sc = DVMB_SCALAR(w);
     const char *acc = sc ? "sacc" : "acc";

@@ -87,6 +87,7 @@ void VKernel::Bind(const RelocEntry *relocs, size_t n, void *workspace) {
       }
     }
     for (uint32_t q = 0; q < P.num_body; ++q) P.body_ring_mask[q] = st.body_tensor_mask[q] & staged;
+    LowerStage(&st);
   }
 }
 

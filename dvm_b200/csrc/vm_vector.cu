@@ -347,11 +347,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t addr, uint32_t parity) {
 // of the launch has expired every later wait returns at once, so the kernel always runs to its end (with
 // wrong results, which the host reports through the status word) instead of hanging.
 __device__ __noinline__ void mbar_wait_slow(uint32_t addr, uint32_t parity, uint32_t code) {
+  for (int i = 0; i < 4096; ++i)
+    if (mbar_try_wait(addr, parity)) return;
   unsigned long long t0, t1;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
   for (;;) {
     if (*reinterpret_cast<volatile unsigned int *>(&g_vm_status) != 0u) return;
-    for (int i = 0; i < 64; ++i)
+    for (int i = 0; i < 1024; ++i)
       if (mbar_try_wait(addr, parity)) return;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
     if (t1 - t0 > 2000000000ull) {
@@ -596,11 +598,11 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
   const uint32_t lane_in_group = flat ? tid : tid % tg;
   const uint32_t group_in_cta = flat ? 0 : tid / tg;
 
-  uint32_t acc[kLanes];
+  uint32_t acc[kLanes], b[kLanes], c[kLanes];
   uint32_t sacc[1] = {0};
   float part[kNumRSlots];
 #pragma unroll
-  for (int i = 0; i < kLanes; ++i) acc[i] = 0;
+  for (int i = 0; i < kLanes; ++i) acc[i] = b[i] = c[i] = 0;
 #pragma unroll
   for (int j = 0; j < kNumRSlots; ++j) part[j] = 0.0f;
   uint32_t red_par = 0;
@@ -628,21 +630,21 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
         const uint32_t opc = DVMB_OPC(w);
         if (opc == OP_END) break;
         const uint32_t sub = DVMB_SUB(w);
-        uint32_t b = 0;
+        uint32_t sb = 0;
         if (opc == OP_COPY || opc == OP_BIN || opc == OP_CMP || opc == OP_SEL) {
           const uint32_t okind = DVMB_OKIND(w), oidx = DVMB_OIDX(w);
           if (okind == K_SREG) {
-            b = lds32(sreg_addr(oidx));
+            sb = lds32(sreg_addr(oidx));
           } else if (okind == K_IMM) {
-            b = DVMB_IMM(w);
+            sb = DVMB_IMM(w);
           } else if (okind == K_TENSOR) {
             const TensorDesc &td = P.tensor[oidx];
-            b = load_elem(td.dtype, reinterpret_cast<const uint8_t *>(td.ptr), kept_offset(td, pos.k));
+            sb = load_elem(td.dtype, reinterpret_cast<const uint8_t *>(td.ptr), kept_offset(td, pos.k));
           } else {
-            b = sacc[0];
+            sb = sacc[0];
           }
         }
-        const SplatOperand bo{b};
+        const SplatOperand bo{sb};
         switch (opc) {
           case OP_ST: {
             const TensorDesc &td = P.tensor[sub];
@@ -650,15 +652,15 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
               store_elem(td.dtype, reinterpret_cast<uint8_t *>(td.ptr), kept_offset(td, pos.k), sacc[0]);
             break;
           }
-          case OP_COPY: sacc[0] = b; break;
+          case OP_COPY: sacc[0] = sb; break;
           case OP_MOV: asm volatile("st.shared.u32 [%0], %1;" ::"r"(sreg_addr(DVMB_DST(w))), "r"(sacc[0]) : "memory"); break;
           case OP_UN: apply_un<1>(sub, sacc); apply_round<1>(DVMB_RND(w), sacc); break;
           case OP_BIN: apply_bin<1>(sub, sacc, bo); apply_round<1>(DVMB_RND(w), sacc); break;
           case OP_CMP: apply_cmp<1>(sub, DVMB_ISINT(w), sacc, bo); break;
           case OP_SEL: {
-            uint32_t c[1];
-            c[0] = lds32(sreg_addr(sub & 15u));
-            apply_sel<1>(DVMB_ISINT(w), DVMB_DST(w) & 1u, sacc, bo, c);
+            uint32_t sc[1];
+            sc[0] = lds32(sreg_addr(sub & 15u));
+            apply_sel<1>(DVMB_ISINT(w), DVMB_DST(w) & 1u, sacc, bo, sc);
             break;
           }
           case OP_CVT: apply_cvt<1>(sub, sacc); apply_round<1>(DVMB_RND(w), sacc); break;
@@ -713,93 +715,230 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
           empty_bar = smem_base + kVmSmemBarriers + 64 + 8 * stage;
           mbar_wait(smem_base + kVmSmemBarriers + 8 * stage, use & 1u, 2);
         }
-        for (uint32_t pc = body_pc;;) {
-          const uint64_t w = P.code[pc++];
-          const uint32_t opc = DVMB_OPC(w);
-          if (opc == OP_END) break;
-          const uint32_t sub = DVMB_SUB(w);
-          const uint32_t okind = DVMB_OKIND(w), oidx = DVMB_OIDX(w);
-          const bool has_operand = opc == OP_COPY || opc == OP_BIN || opc == OP_CMP || opc == OP_SEL;
-          const bool splat = okind == K_SREG || okind == K_IMM;
-          uint32_t b[kLanes];
-          uint32_t bs = DVMB_IMM(w);
-          if (has_operand) {
-            if (okind == K_TENSOR) {
-              fetch_tensor(P, oidx, pos, stage_saddr, b);
-            } else if (okind == K_TEMP) {
-#pragma unroll
-              for (int g = 0; g < 2; ++g)
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(b[4 * g]), "=r"(b[4 * g + 1]), "=r"(b[4 * g + 2]), "=r"(b[4 * g + 3])
-                             : "r"(temp_addr(oidx, g)));
-            } else if (okind == K_SREG) {
-              bs = lds32(sreg_addr(oidx));
-            } else if (okind == K_ACC) {
-#pragma unroll
-              for (int i = 0; i < kLanes; ++i) b[i] = acc[i];
+        const bool full_tile = pos.chunk_valid == P.chunk_elems && pos.gvalid;
+        const uint32_t ring_lane = stage_saddr;   // + offset + (in_chunk << shift) per fetch
+        for (uint32_t pc = body_pc;; ++pc) {
+          const uint64_t u = P.code[pc];
+          const uint32_t uh = DVMB_UH(u);
+          const uint32_t aux = DVMB_UAUX(u);
+          const uint32_t arg = DVMB_UARG(u);
+          if (uh == UH_END) break;
+          uint32_t slot;
+#define DVMB_TO_DEST(FN)                       \
+  {                                            \
+    const uint32_t d_ = aux & 3u;              \
+    if (d_ == UD_ACC) { FN(acc) } else if (d_ == UD_B) { FN(b) } else { FN(c) } \
+  }
+#define DVMB_BINV(K, TYPE, CONV_IN, CONV_OUT, EXPR)              \
+  case UH_BINV_FIRST + K: {                                      \
+    _Pragma("unroll") for (int i = 0; i < kLanes; ++i) {         \
+      TYPE x = CONV_IN(acc[i]), y = CONV_IN(b[i]);               \
+      acc[i] = CONV_OUT(EXPR);                                   \
+    }                                                            \
+    continue;                                                    \
+  }                                                              \
+  case UH_BINS_FIRST + K: {                                      \
+    const uint32_t sv_ = (aux & 1u) ? lds32(sreg_addr(arg)) : DVMB_UIMM(u); \
+    const TYPE y = CONV_IN(sv_);                                 \
+    _Pragma("unroll") for (int i = 0; i < kLanes; ++i) {         \
+      TYPE x = CONV_IN(acc[i]);                                  \
+      acc[i] = CONV_OUT(EXPR);                                   \
+    }                                                            \
+    continue;                                                    \
+  }
+#define DVMB_UNOP(K, EXPR)                                       \
+  case UH_UN_FIRST + K: {                                        \
+    _Pragma("unroll") for (int i = 0; i < kLanes; ++i) {         \
+      float x = u2f(acc[i]);                                     \
+      acc[i] = f2u(EXPR);                                        \
+    }                                                            \
+    continue;                                                    \
+  }
+#define DVMB_AS_INT(v) ((int32_t)(v))
+#define DVMB_AS_U32(v) ((uint32_t)(v))
+          switch (uh) {
+            // ---------------- operand fetches ----------------
+            case UH_LDR_F32: {
+              slot = aux >> 2;
+              if (!full_tile) goto fetch_generic;
+              const uint32_t a0 = ring_lane + (arg << 4) + (pos.in_chunk[0] << 2);
+              const uint32_t a1 = a0 + ((4u * tg) << 2);
+#define DVMB_FN(V)                                                                                                  \
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(V[0]), "=r"(V[1]), "=r"(V[2]), "=r"(V[3]) : "r"(a0)); \
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(V[4]), "=r"(V[5]), "=r"(V[6]), "=r"(V[7]) : "r"(a1));
+              DVMB_TO_DEST(DVMB_FN)
+#undef DVMB_FN
+              continue;
             }
-          }
-          const VecOperand<kLanes> bv{b};
-          const SplatOperand bo{bs};
-          switch (opc) {
-            case OP_ST: store_tensor(P, sub, pos, acc); break;
-            case OP_COPY:
-              if (splat) {
+            case UH_LDR_F16:
+            case UH_LDR_BF16: {
+              slot = aux >> 2;
+              if (!full_tile) goto fetch_generic;
+              const uint32_t a0 = ring_lane + (arg << 4) + (pos.in_chunk[0] << 1);
+              const uint32_t a1 = a0 + ((4u * tg) << 1);
+              uint2 r0, r1;
+              asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(r0.x), "=r"(r0.y) : "r"(a0));
+              asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(r1.x), "=r"(r1.y) : "r"(a1));
+              if (uh == UH_LDR_BF16) {
+#define DVMB_FN(V)                                                                                      \
+  V[0] = r0.x << 16; V[1] = r0.x & 0xffff0000u; V[2] = r0.y << 16; V[3] = r0.y & 0xffff0000u;           \
+  V[4] = r1.x << 16; V[5] = r1.x & 0xffff0000u; V[6] = r1.y << 16; V[7] = r1.y & 0xffff0000u;
+                DVMB_TO_DEST(DVMB_FN)
+#undef DVMB_FN
+              } else {
+#define DVMB_FN(V)                                                           \
+  {                                                                          \
+    float2 f0 = __half22float2(*reinterpret_cast<__half2 *>(&r0.x));         \
+    float2 f1 = __half22float2(*reinterpret_cast<__half2 *>(&r0.y));         \
+    float2 f2 = __half22float2(*reinterpret_cast<__half2 *>(&r1.x));         \
+    float2 f3 = __half22float2(*reinterpret_cast<__half2 *>(&r1.y));         \
+    V[0] = f2u(f0.x); V[1] = f2u(f0.y); V[2] = f2u(f1.x); V[3] = f2u(f1.y);  \
+    V[4] = f2u(f2.x); V[5] = f2u(f2.y); V[6] = f2u(f3.x); V[7] = f2u(f3.y);  \
+  }
+                DVMB_TO_DEST(DVMB_FN)
+#undef DVMB_FN
+              }
+              continue;
+            }
+            case UH_LDR_U8: {
+              slot = aux >> 2;
+              if (!full_tile) goto fetch_generic;
+              const uint32_t a0 = ring_lane + (arg << 4) + pos.in_chunk[0];
+              const uint32_t r0 = lds32(a0), r1 = lds32(a0 + 4u * tg);
+#define DVMB_FN(V)                                                                                \
+  V[0] = r0 & 0xffu; V[1] = (r0 >> 8) & 0xffu; V[2] = (r0 >> 16) & 0xffu; V[3] = r0 >> 24;        \
+  V[4] = r1 & 0xffu; V[5] = (r1 >> 8) & 0xffu; V[6] = (r1 >> 16) & 0xffu; V[7] = r1 >> 24;
+              DVMB_TO_DEST(DVMB_FN)
+#undef DVMB_FN
+              continue;
+            }
+            case UH_LDG: {
+              slot = aux >> 2;
+            fetch_generic:
+#define DVMB_FN(V) fetch_tensor(P, slot, pos, stage_saddr, V);
+              DVMB_TO_DEST(DVMB_FN)
+#undef DVMB_FN
+              continue;
+            }
+            case UH_LDT: {
+#define DVMB_FN(V)                                                                                              \
+  _Pragma("unroll") for (int g = 0; g < 2; ++g)                                                                  \
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"                                                         \
+                 : "=r"(V[4 * g]), "=r"(V[4 * g + 1]), "=r"(V[4 * g + 2]), "=r"(V[4 * g + 3])                    \
+                 : "r"(temp_addr(arg, g)));
+              DVMB_TO_DEST(DVMB_FN)
+#undef DVMB_FN
+              continue;
+            }
+            case UH_LDS:
+            case UH_LDI: {
+              const uint32_t v = uh == UH_LDS ? lds32(sreg_addr(arg)) : DVMB_UIMM(u);
+#define DVMB_FN(V) _Pragma("unroll") for (int i = 0; i < kLanes; ++i) V[i] = v;
+              DVMB_TO_DEST(DVMB_FN)
+#undef DVMB_FN
+              continue;
+            }
+            case UH_MOVA: {
+              if ((aux & 3u) == UD_B) {
 #pragma unroll
-                for (int i = 0; i < kLanes; ++i) acc[i] = bs;
+                for (int i = 0; i < kLanes; ++i) b[i] = acc[i];
               } else {
 #pragma unroll
-                for (int i = 0; i < kLanes; ++i) acc[i] = b[i];
+                for (int i = 0; i < kLanes; ++i) c[i] = acc[i];
               }
-              break;
-            case OP_MOV: {
-              const uint32_t dst = DVMB_DST(w);
+              continue;
+            }
+            case UH_STT: {
 #pragma unroll
               for (int g = 0; g < 2; ++g)
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(temp_addr(dst, g)), "r"(acc[4 * g]),
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(temp_addr(arg, g)), "r"(acc[4 * g]),
                              "r"(acc[4 * g + 1]), "r"(acc[4 * g + 2]), "r"(acc[4 * g + 3])
                              : "memory");
-              break;
+              continue;
             }
-            case OP_UN: apply_un<kLanes>(sub, acc); apply_round<kLanes>(DVMB_RND(w), acc); break;
-            case OP_BIN:
-              if (splat) apply_bin<kLanes>(sub, acc, bo); else apply_bin<kLanes>(sub, acc, bv);
-              apply_round<kLanes>(DVMB_RND(w), acc);
-              break;
-            case OP_CMP:
-              if (splat) apply_cmp<kLanes>(sub, DVMB_ISINT(w), acc, bo); else apply_cmp<kLanes>(sub, DVMB_ISINT(w), acc, bv);
-              break;
-            case OP_SEL: {
-              uint32_t c[kLanes];
-              const uint32_t k2 = sub >> 4, i2 = sub & 15u;
-              if (k2 == K_TENSOR) {
-                fetch_tensor(P, i2, pos, stage_saddr, c);
-              } else if (k2 == K_TEMP) {
+            // ---------------- arithmetic ----------------
+            DVMB_BINV(B_ADD, float, u2f, f2u, x + y)
+            DVMB_BINV(B_SUB, float, u2f, f2u, x - y)
+            DVMB_BINV(B_MUL, float, u2f, f2u, x * y)
+            DVMB_BINV(B_DIV, float, u2f, f2u, x / y)
+            DVMB_BINV(B_MAX, float, u2f, f2u, (x > y ? x : y))
+            DVMB_BINV(B_MIN, float, u2f, f2u, (x < y ? x : y))
+            DVMB_BINV(B_POW, float, u2f, f2u, powf(x, y))
+            DVMB_BINV(B_RSUB, float, u2f, f2u, y - x)
+            DVMB_BINV(B_RDIV, float, u2f, f2u, y / x)
+            DVMB_BINV(B_ADD_I, uint32_t, DVMB_AS_U32, DVMB_AS_U32, x + y)
+            DVMB_BINV(B_SUB_I, uint32_t, DVMB_AS_U32, DVMB_AS_U32, x - y)
+            DVMB_BINV(B_MUL_I, uint32_t, DVMB_AS_U32, DVMB_AS_U32, x * y)
+            DVMB_BINV(B_MAX_I, int32_t, DVMB_AS_INT, DVMB_AS_U32, (x > y ? x : y))
+            DVMB_BINV(B_MIN_I, int32_t, DVMB_AS_INT, DVMB_AS_U32, (x < y ? x : y))
+            DVMB_BINV(B_RSUB_I, uint32_t, DVMB_AS_U32, DVMB_AS_U32, y - x)
+            DVMB_UNOP(U_SQRT, sqrtf(x))
+            DVMB_UNOP(U_ABS, fabsf(x))
+            DVMB_UNOP(U_LOG, logf(x))
+            DVMB_UNOP(U_EXP, expf(x))
+            DVMB_UNOP(U_ROUND, nearbyintf(x))
+            DVMB_UNOP(U_FLOOR, floorf(x))
+            DVMB_UNOP(U_CEIL, ceilf(x))
+            DVMB_UNOP(U_TRUNC, truncf(x))
+            DVMB_UNOP(U_ISFINITE, (isfinite(x) ? 1.0f : 0.0f))
+            case UH_UN_FIRST + U_ABS_I: {
 #pragma unroll
-                for (int g = 0; g < 2; ++g)
-                  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                               : "=r"(c[4 * g]), "=r"(c[4 * g + 1]), "=r"(c[4 * g + 2]), "=r"(c[4 * g + 3])
-                               : "r"(temp_addr(i2, g)));
-              } else {
-                const uint32_t v = lds32(sreg_addr(i2));
-#pragma unroll
-                for (int i = 0; i < kLanes; ++i) c[i] = v;
-              }
-              if (splat) apply_sel<kLanes>(DVMB_ISINT(w), DVMB_DST(w) & 1u, acc, bo, c);
-              else apply_sel<kLanes>(DVMB_ISINT(w), DVMB_DST(w) & 1u, acc, bv, c);
-              break;
+              for (int i = 0; i < kLanes; ++i) acc[i] = (int32_t)acc[i] < 0 ? (0u - acc[i]) : acc[i];
+              continue;
             }
-            case OP_CVT: apply_cvt<kLanes>(sub, acc); apply_round<kLanes>(DVMB_RND(w), acc); break;
-            case OP_RACC: {
-              const uint32_t kind = sub >> 4;
+            case UH_UN_FIRST + U_NOP: continue;
+            case UH_RND_F16: apply_round<kLanes>(RN_F16, acc); continue;
+            case UH_RND_BF16: apply_round<kLanes>(RN_BF16, acc); continue;
+            case UH_CMP_F_V: apply_cmp<kLanes>(aux & 7u, 0, acc, VecOperand<kLanes>{b}); continue;
+            case UH_CMP_I_V: apply_cmp<kLanes>(aux & 7u, 1, acc, VecOperand<kLanes>{b}); continue;
+            case UH_CMP_F_S:
+            case UH_CMP_I_S: {
+              const SplatOperand so{(aux & 0x80u) ? lds32(sreg_addr(arg)) : DVMB_UIMM(u)};
+              apply_cmp<kLanes>(aux & 7u, uh == UH_CMP_I_S ? 1u : 0u, acc, so);
+              continue;
+            }
+            case UH_SEL_F: apply_sel<kLanes>(0, 0, acc, VecOperand<kLanes>{b}, c); continue;
+            case UH_SEL_I: apply_sel<kLanes>(1, 0, acc, VecOperand<kLanes>{b}, c); continue;
+            case UH_CVT_F2I: apply_cvt<kLanes>(V_F2I, acc); continue;
+            case UH_CVT_I2F: apply_cvt<kLanes>(V_I2F, acc); continue;
+            case UH_CVT_NEZ_F: apply_cvt<kLanes>(V_NEZ_F, acc); continue;
+            case UH_CVT_NEZ_I: apply_cvt<kLanes>(V_NEZ_I, acc); continue;
+            case UH_RACC_SUM:
+            case UH_RACC_MAX:
+            case UH_RACC_MIN: {
+              const uint32_t kind = uh - UH_RACC_SUM;
               float v = red_identity(kind);
+              if (full_tile) {
 #pragma unroll
-              for (int i = 0; i < kLanes; ++i)
-                if (pos.gvalid && (i & 3) < pos.nv[i >> 2]) v = red_combine(kind, v, u2f(acc[i]));
-              DVMB_PART_CASES(sub & 3u, part[J] = red_combine(kind, part[J], v);)
-              break;
+                for (int i = 0; i < kLanes; ++i) v = red_combine(kind, v, u2f(acc[i]));
+              } else {
+#pragma unroll
+                for (int i = 0; i < kLanes; ++i)
+                  if (pos.gvalid && (i & 3) < pos.nv[i >> 2]) v = red_combine(kind, v, u2f(acc[i]));
+              }
+              DVMB_PART_CASES(arg & 3u, part[J] = red_combine(kind, part[J], v);)
+              continue;
             }
-            default: break;
+            // ---------------- stores ----------------
+            case UH_ST_F32:
+            case UH_ST_F16:
+            case UH_ST_BF16:
+            case UH_ST_U8: {
+              if (!full_tile) goto store_generic;
+              const TensorDesc &td = P.tensor[arg];
+              uint8_t *base = reinterpret_cast<uint8_t *>(td.ptr);
+              const uint32_t off0 = kept_offset(td, pos.k) + pos.e0[0];
+              const uint32_t off1 = off0 + 4u * tg;
+              gstore4(uh == UH_ST_F32 ? T_F32 : (uh == UH_ST_F16 ? T_F16 : (uh == UH_ST_BF16 ? T_BF16 : T_BOOL)), base, off0, &acc[0]);
+              gstore4(uh == UH_ST_F32 ? T_F32 : (uh == UH_ST_F16 ? T_F16 : (uh == UH_ST_BF16 ? T_BF16 : T_BOOL)), base, off1, &acc[4]);
+              continue;
+            }
+            case UH_STG: {
+            store_generic:
+              store_tensor(P, arg, pos, acc);
+              continue;
+            }
+            default: continue;
           }
         }
         if (staged_body) mbar_arrive(empty_bar);
