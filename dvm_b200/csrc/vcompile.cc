@@ -7,6 +7,7 @@
 // accumulator machine held in registers; reductions split the program into phases and values needed
 // after a reduction are recomputed from the (cache-resident) inputs instead of being parked on chip.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <unordered_map>
@@ -836,6 +837,7 @@ struct Compiler {
     if (!has_reduce) {
       P.mode = VM_FLAT;
       P.tg = kVmFlatThreads;
+      if (const char *env = getenv("DVM_B200_FLAT_THREADS")) P.tg = static_cast<uint32_t>(atoi(env));
       P.groups_per_cta = 1;
       P.chunk_elems = 8 * P.tg;
       P.chunks = static_cast<uint32_t>((G + P.chunk_elems - 1) / P.chunk_elems);
@@ -951,8 +953,10 @@ struct Compiler {
     const uint32_t fixed = kVmSmemStages + P.num_temps * T * 32u + P.num_sregs * T * 4u;
     uint32_t stages = 0;
     if (stage_bytes != 0) {
-      const uint32_t budget = 72 * 1024;   // three CTAs of this size fit one SM
+      uint32_t budget = 72 * 1024;   // three CTAs of this size fit one SM
+      if (const char *env = getenv("DVM_B200_RING_KB")) budget = static_cast<uint32_t>(atoi(env)) * 1024u;
       stages = fixed + 2 * stage_bytes > budget ? 2 : std::min<uint32_t>(kVmMaxStages, (budget - fixed) / stage_bytes);
+      if (const char *env = getenv("DVM_B200_STAGES")) stages = static_cast<uint32_t>(atoi(env));
       if (fixed + stages * stage_bytes > kVmMaxSmemBytes) {
         // too large to stage even twice: fall back to direct global loads
         stage_bytes = 0;
@@ -972,7 +976,9 @@ struct Compiler {
     out->threads = T + (stage_bytes != 0 ? 32u : 0u);
 
     // ---- grid: persistent CTAs, as many as fit per SM
-    uint32_t per_sm = std::max<uint32_t>(1u, std::min<uint32_t>(3u, (220u * 1024u) / std::max<uint32_t>(out->smem_bytes, 1u)));
+    uint32_t per_sm_cap = 3u;
+    if (const char *env = getenv("DVM_B200_CTAS_PER_SM")) per_sm_cap = static_cast<uint32_t>(atoi(env));
+    uint32_t per_sm = std::max<uint32_t>(1u, std::min<uint32_t>(per_sm_cap, (220u * 1024u) / std::max<uint32_t>(out->smem_bytes + 1024u, 1u)));
     if (T > static_cast<uint32_t>(kVmFlatThreads)) per_sm = 1;
     const uint32_t work = P.mode == VM_FLAT ? P.chunks : (P.num_groups + P.groups_per_cta - 1) / P.groups_per_cta;
     out->grid = std::max<uint32_t>(1u, std::min<uint32_t>(work, sms * per_sm));

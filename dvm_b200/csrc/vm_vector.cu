@@ -521,10 +521,78 @@ __device__ __forceinline__ void decompose_group(const VmParam &P, uint32_t gi, u
   k[0] = gi;
 }
 
+
+// ---- hidden vector registers ------------------------------------------------------------------------
+// va0..7 accumulator, vb0..7 / vc0..7 operands, vp0..3 reduction partials: PTX registers declared once at
+// the top of the kernel and named only inside inline assembly.
+#define DV_L8(M, ...) M(0, __VA_ARGS__) M(1, __VA_ARGS__) M(2, __VA_ARGS__) M(3, __VA_ARGS__) M(4, __VA_ARGS__) M(5, __VA_ARGS__) M(6, __VA_ARGS__) M(7, __VA_ARGS__)
+#define DV_BINV_LANE(i, OP) OP " va" #i ", va" #i ", vb" #i ";\n\t"
+#define DV_RBINV_LANE(i, OP) OP " va" #i ", vb" #i ", va" #i ";\n\t"
+#define DV_BINS_LANE(i, OP) OP " va" #i ", va" #i ", %0;\n\t"
+#define DV_RBINS_LANE(i, OP) OP " va" #i ", %0, va" #i ";\n\t"
+#define DV_PICKV_LANE(i, SETP) SETP " p, va" #i ", vb" #i ";\n\tselp.b32 va" #i ", va" #i ", vb" #i ", p;\n\t"
+#define DV_PICKS_LANE(i, SETP) SETP " p, va" #i ", %0;\n\tselp.b32 va" #i ", va" #i ", %0, p;\n\t"
+#define DV_UN_LANE(i, OP) OP " va" #i ", va" #i ";\n\t"
+#define DV_ISFIN_LANE(i, X) "testp.finite.f32 p, va" #i ";\n\tselp.b32 va" #i ", 0x3f800000, 0, p;\n\t"
+#define DV_RNDH_LANE(i, X) "cvt.rn.f16.f32 h, va" #i ";\n\tcvt.f32.f16 va" #i ", h;\n\t"
+#define DV_RNDB_PAIR(a, b) "cvt.rn.bf16x2.f32 t, va" b ", va" a ";\n\tshl.b32 va" a ", t, 16;\n\tand.b32 va" b ", t, 0xffff0000;\n\t"
+#define DV_CMPF_LANE(i, SETP) SETP " p, va" #i ", vb" #i ";\n\tselp.b32 va" #i ", 0x3f800000, 0, p;\n\t"
+#define DV_CMPI_LANE(i, SETP) SETP " p, va" #i ", vb" #i ";\n\tselp.b32 va" #i ", 1, 0, p;\n\t"
+#define DV_SEL_LANE(i, TEST, ZERO) TEST #i ZERO ";\n\tselp.b32 va" #i ", vb" #i ", vc" #i ", p;\n\t"
+#define DV_NEZ_LANE(i, TEST, ZERO) TEST #i ZERO ";\n\tselp.b32 va" #i ", 1, 0, p;\n\t"
+#define DV_MOV_LANE(i, D, S_) "mov.b32 " D #i ", " S_ #i ";\n\t"
+#define DV_GETLANE(i, R) "mov.b32 %" #i ", " R #i ";\n\t"
+#define DV_SETLANE(i, R) "mov.b32 " R #i ", %" #i ";\n\t"
+#define DV_SPLATLANE(i, R) "mov.b32 " R #i ", %0;\n\t"
+#define DV_GET(R, X) \
+  asm volatile(DV_L8(DV_GETLANE, R) : "=r"(X[0]), "=r"(X[1]), "=r"(X[2]), "=r"(X[3]), "=r"(X[4]), "=r"(X[5]), "=r"(X[6]), "=r"(X[7]));
+#define DV_SET(R, X) \
+  asm volatile(DV_L8(DV_SETLANE, R)::"r"(X[0]), "r"(X[1]), "r"(X[2]), "r"(X[3]), "r"(X[4]), "r"(X[5]), "r"(X[6]), "r"(X[7]));
+#define DV_SPLAT(R, V) asm volatile(DV_L8(DV_SPLATLANE, R)::"r"(V));
+#define DV_LDR32(R, A0, A1)                                                                          \
+  asm volatile("ld.shared.v4.b32 {" R "0," R "1," R "2," R "3}, [%0];\n\tld.shared.v4.b32 {" R "4," R "5," R "6," R "7}, [%1];" ::"r"(A0), \
+               "r"(A1)                                                                               \
+               : "memory");
+#define DV_BF16_HALF(R, a, b, c, d, T0, T1) \
+  "shl.b32 " R a ", " T0 ", 16;\n\tand.b32 " R b ", " T0 ", 0xffff0000;\n\tshl.b32 " R c ", " T1 ", 16;\n\tand.b32 " R d ", " T1 ", 0xffff0000;\n\t"
+#define DV_LDR_BF16(R, A0, A1)                                                                     \
+  asm volatile("{\n\t.reg .b32 t0, t1, t2, t3;\n\tld.shared.v2.b32 {t0,t1}, [%0];\n\tld.shared.v2.b32 {t2,t3}, [%1];\n\t" \
+               DV_BF16_HALF(R, "0", "1", "2", "3", "t0", "t1") DV_BF16_HALF(R, "4", "5", "6", "7", "t2", "t3") "}" ::"r"(A0), \
+               "r"(A1)                                                                             \
+               : "memory");
+#define DV_F16_PAIR(R, a, b, T) "mov.b32 {h0,h1}, " T ";\n\tcvt.f32.f16 " R a ", h0;\n\tcvt.f32.f16 " R b ", h1;\n\t"
+#define DV_LDR_F16(R, A0, A1)                                                                      \
+  asm volatile("{\n\t.reg .b32 t0, t1, t2, t3;\n\t.reg .b16 h0, h1;\n\tld.shared.v2.b32 {t0,t1}, [%0];\n\tld.shared.v2.b32 {t2,t3}, [%1];\n\t" \
+               DV_F16_PAIR(R, "0", "1", "t0") DV_F16_PAIR(R, "2", "3", "t1") DV_F16_PAIR(R, "4", "5", "t2") DV_F16_PAIR(R, "6", "7", "t3") "}" ::"r"(A0), \
+               "r"(A1)                                                                             \
+               : "memory");
+#define DV_U8_QUAD(R, a, b, c, d, T) \
+  "and.b32 " R a ", " T ", 255;\n\tbfe.u32 " R b ", " T ", 8, 8;\n\tbfe.u32 " R c ", " T ", 16, 8;\n\tshr.u32 " R d ", " T ", 24;\n\t"
+#define DV_LDR_U8(R, A0, A1)                                                                       \
+  asm volatile("{\n\t.reg .b32 t0, t1;\n\tld.shared.b32 t0, [%0];\n\tld.shared.b32 t1, [%1];\n\t"  \
+               DV_U8_QUAD(R, "0", "1", "2", "3", "t0") DV_U8_QUAD(R, "4", "5", "6", "7", "t1") "}" ::"r"(A0), \
+               "r"(A1)                                                                             \
+               : "memory");
+// run FN("va"| "vb" | "vc", args...) for destination code D
+#define DV_BY_DEST(D, FN, ...)                \
+  {                                           \
+    const uint32_t d_ = (D);                  \
+    if (d_ == UD_ACC) { FN("va", __VA_ARGS__) } else if (d_ == UD_B) { FN("vb", __VA_ARGS__) } else { FN("vc", __VA_ARGS__) } \
+  }
+#define DV_BIN_CASES(K, VLANE, SLANE, OP)                                      \
+  case UH_BINV_FIRST + K: asm volatile(DV_L8(VLANE, OP)); continue;            \
+  case UH_BINS_FIRST + K: {                                                    \
+    const uint32_t sv_ = (aux & 1u) ? lds32(sreg_addr(arg)) : DVMB_UIMM(u);    \
+    asm volatile(DV_L8(SLANE, OP)::"r"(sv_));                                  \
+    continue;                                                                  \
+  }
+
 }  // namespace
 
 namespace {
 __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
+  asm volatile(".reg .b32 va<8>, vb<8>, vc<8>, vp<4>;");
+  asm volatile(DV_L8(DV_SPLATLANE, "va") DV_L8(DV_SPLATLANE, "vb") DV_L8(DV_SPLATLANE, "vc") "mov.b32 vp0, %0;\n\tmov.b32 vp1, %0;\n\tmov.b32 vp2, %0;\n\tmov.b32 vp3, %0;" ::"r"(0u));
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
   const uint32_t tid = threadIdx.x;
@@ -591,6 +659,9 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
   }
 
   // =============================== consumer warps ===============================
+  // The vector state (accumulator va, operand registers vb / vc, reduction partials vp) lives in PTX
+  // registers that only inline assembly names.  The compiler therefore carries no vector state across
+  // the dispatch loop (nothing to copy at the switch merge), and ptxas keeps each one in a fixed register.
   float *red_buf = reinterpret_cast<float *>(smem + kVmSmemRed);
   const uint32_t temps_saddr = smem_base + kVmSmemStages + S * P.stage_bytes;
   const uint32_t sregs_saddr = temps_saddr + P.num_temps * T * 32u;
@@ -598,13 +669,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
   const uint32_t lane_in_group = flat ? tid : tid % tg;
   const uint32_t group_in_cta = flat ? 0 : tid / tg;
 
-  uint32_t acc[kLanes], b[kLanes], c[kLanes];
   uint32_t sacc[1] = {0};
-  float part[kNumRSlots];
-#pragma unroll
-  for (int i = 0; i < kLanes; ++i) acc[i] = b[i] = c[i] = 0;
-#pragma unroll
-  for (int j = 0; j < kNumRSlots; ++j) part[j] = 0.0f;
   uint32_t red_par = 0;
   uint32_t seq = 0;
   Pos pos;
@@ -615,6 +680,25 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
     uint32_t v;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
     return v;
+  };
+  auto get_part = [](uint32_t slot) {
+    uint32_t v;
+    switch (slot) {
+      case 0: asm volatile("mov.b32 %0, vp0;" : "=r"(v)); break;
+      case 1: asm volatile("mov.b32 %0, vp1;" : "=r"(v)); break;
+      case 2: asm volatile("mov.b32 %0, vp2;" : "=r"(v)); break;
+      default: asm volatile("mov.b32 %0, vp3;" : "=r"(v)); break;
+    }
+    return u2f(v);
+  };
+  auto set_part = [](uint32_t slot, float f) {
+    const uint32_t v = f2u(f);
+    switch (slot) {
+      case 0: asm volatile("mov.b32 vp0, %0;" ::"r"(v)); break;
+      case 1: asm volatile("mov.b32 vp1, %0;" ::"r"(v)); break;
+      case 2: asm volatile("mov.b32 vp2, %0;" ::"r"(v)); break;
+      default: asm volatile("mov.b32 vp3, %0;" ::"r"(v)); break;
+    }
   };
 
   for (uint32_t gb = gb_begin; gb < ngb; gb += gb_step) {
@@ -664,15 +748,11 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             break;
           }
           case OP_CVT: apply_cvt<1>(sub, sacc); apply_round<1>(DVMB_RND(w), sacc); break;
-          case OP_RINIT: {
-            const float id = red_identity(sub >> 4);
-            DVMB_PART_CASES(sub & 3u, part[J] = id;)
-            break;
-          }
+          case OP_RINIT: set_part(sub & 3u, red_identity(sub >> 4)); break;
           case OP_RFIN: {
             const uint32_t kind = sub >> 4;
-            float v = 0.0f;
-            DVMB_PART_CASES(sub & 3u, v = part[J]; part[J] = red_identity(kind);)
+            float v = get_part(sub & 3u);
+            set_part(sub & 3u, red_identity(kind));
             if (tg <= 32) {
               for (uint32_t o = tg >> 1; o > 0; o >>= 1) v = red_combine(kind, v, __shfl_xor_sync(0xffffffffu, v, o));
             } else {
@@ -716,7 +796,6 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
           mbar_wait(smem_base + kVmSmemBarriers + 8 * stage, use & 1u, 2);
         }
         const bool full_tile = pos.chunk_valid == P.chunk_elems && pos.gvalid;
-        const uint32_t ring_lane = stage_saddr;   // + offset + (in_chunk << shift) per fetch
         for (uint32_t pc = body_pc;; ++pc) {
           const uint64_t u = P.code[pc];
           const uint32_t uh = DVMB_UH(u);
@@ -724,218 +803,227 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
           const uint32_t arg = DVMB_UARG(u);
           if (uh == UH_END) break;
           uint32_t slot;
-#define DVMB_TO_DEST(FN)                       \
-  {                                            \
-    const uint32_t d_ = aux & 3u;              \
-    if (d_ == UD_ACC) { FN(acc) } else if (d_ == UD_B) { FN(b) } else { FN(c) } \
-  }
-#define DVMB_BINV(K, TYPE, CONV_IN, CONV_OUT, EXPR)              \
-  case UH_BINV_FIRST + K: {                                      \
-    _Pragma("unroll") for (int i = 0; i < kLanes; ++i) {         \
-      TYPE x = CONV_IN(acc[i]), y = CONV_IN(b[i]);               \
-      acc[i] = CONV_OUT(EXPR);                                   \
-    }                                                            \
-    continue;                                                    \
-  }                                                              \
-  case UH_BINS_FIRST + K: {                                      \
-    const uint32_t sv_ = (aux & 1u) ? lds32(sreg_addr(arg)) : DVMB_UIMM(u); \
-    const TYPE y = CONV_IN(sv_);                                 \
-    _Pragma("unroll") for (int i = 0; i < kLanes; ++i) {         \
-      TYPE x = CONV_IN(acc[i]);                                  \
-      acc[i] = CONV_OUT(EXPR);                                   \
-    }                                                            \
-    continue;                                                    \
-  }
-#define DVMB_UNOP(K, EXPR)                                       \
-  case UH_UN_FIRST + K: {                                        \
-    _Pragma("unroll") for (int i = 0; i < kLanes; ++i) {         \
-      float x = u2f(acc[i]);                                     \
-      acc[i] = f2u(EXPR);                                        \
-    }                                                            \
-    continue;                                                    \
-  }
-#define DVMB_AS_INT(v) ((int32_t)(v))
-#define DVMB_AS_U32(v) ((uint32_t)(v))
           switch (uh) {
             // ---------------- operand fetches ----------------
             case UH_LDR_F32: {
               slot = aux >> 2;
               if (!full_tile) goto fetch_generic;
-              const uint32_t a0 = ring_lane + (arg << 4) + (pos.in_chunk[0] << 2);
+              const uint32_t a0 = stage_saddr + (arg << 4) + (pos.in_chunk[0] << 2);
               const uint32_t a1 = a0 + ((4u * tg) << 2);
-#define DVMB_FN(V)                                                                                                  \
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(V[0]), "=r"(V[1]), "=r"(V[2]), "=r"(V[3]) : "r"(a0)); \
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(V[4]), "=r"(V[5]), "=r"(V[6]), "=r"(V[7]) : "r"(a1));
-              DVMB_TO_DEST(DVMB_FN)
-#undef DVMB_FN
+              DV_BY_DEST(aux & 3u, DV_LDR32, a0, a1)
               continue;
             }
-            case UH_LDR_F16:
+            case UH_LDR_F16: {
+              slot = aux >> 2;
+              if (!full_tile) goto fetch_generic;
+              const uint32_t a0 = stage_saddr + (arg << 4) + (pos.in_chunk[0] << 1);
+              const uint32_t a1 = a0 + ((4u * tg) << 1);
+              DV_BY_DEST(aux & 3u, DV_LDR_F16, a0, a1)
+              continue;
+            }
             case UH_LDR_BF16: {
               slot = aux >> 2;
               if (!full_tile) goto fetch_generic;
-              const uint32_t a0 = ring_lane + (arg << 4) + (pos.in_chunk[0] << 1);
+              const uint32_t a0 = stage_saddr + (arg << 4) + (pos.in_chunk[0] << 1);
               const uint32_t a1 = a0 + ((4u * tg) << 1);
-              uint2 r0, r1;
-              asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(r0.x), "=r"(r0.y) : "r"(a0));
-              asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(r1.x), "=r"(r1.y) : "r"(a1));
-              if (uh == UH_LDR_BF16) {
-#define DVMB_FN(V)                                                                                      \
-  V[0] = r0.x << 16; V[1] = r0.x & 0xffff0000u; V[2] = r0.y << 16; V[3] = r0.y & 0xffff0000u;           \
-  V[4] = r1.x << 16; V[5] = r1.x & 0xffff0000u; V[6] = r1.y << 16; V[7] = r1.y & 0xffff0000u;
-                DVMB_TO_DEST(DVMB_FN)
-#undef DVMB_FN
-              } else {
-#define DVMB_FN(V)                                                           \
-  {                                                                          \
-    float2 f0 = __half22float2(*reinterpret_cast<__half2 *>(&r0.x));         \
-    float2 f1 = __half22float2(*reinterpret_cast<__half2 *>(&r0.y));         \
-    float2 f2 = __half22float2(*reinterpret_cast<__half2 *>(&r1.x));         \
-    float2 f3 = __half22float2(*reinterpret_cast<__half2 *>(&r1.y));         \
-    V[0] = f2u(f0.x); V[1] = f2u(f0.y); V[2] = f2u(f1.x); V[3] = f2u(f1.y);  \
-    V[4] = f2u(f2.x); V[5] = f2u(f2.y); V[6] = f2u(f3.x); V[7] = f2u(f3.y);  \
-  }
-                DVMB_TO_DEST(DVMB_FN)
-#undef DVMB_FN
-              }
+              DV_BY_DEST(aux & 3u, DV_LDR_BF16, a0, a1)
               continue;
             }
             case UH_LDR_U8: {
               slot = aux >> 2;
               if (!full_tile) goto fetch_generic;
-              const uint32_t a0 = ring_lane + (arg << 4) + pos.in_chunk[0];
-              const uint32_t r0 = lds32(a0), r1 = lds32(a0 + 4u * tg);
-#define DVMB_FN(V)                                                                                \
-  V[0] = r0 & 0xffu; V[1] = (r0 >> 8) & 0xffu; V[2] = (r0 >> 16) & 0xffu; V[3] = r0 >> 24;        \
-  V[4] = r1 & 0xffu; V[5] = (r1 >> 8) & 0xffu; V[6] = (r1 >> 16) & 0xffu; V[7] = r1 >> 24;
-              DVMB_TO_DEST(DVMB_FN)
-#undef DVMB_FN
+              const uint32_t a0 = stage_saddr + (arg << 4) + pos.in_chunk[0];
+              const uint32_t a1 = a0 + 4u * tg;
+              DV_BY_DEST(aux & 3u, DV_LDR_U8, a0, a1)
               continue;
             }
             case UH_LDG: {
               slot = aux >> 2;
             fetch_generic:
-#define DVMB_FN(V) fetch_tensor(P, slot, pos, stage_saddr, V);
-              DVMB_TO_DEST(DVMB_FN)
-#undef DVMB_FN
+              uint32_t t[kLanes];
+              fetch_tensor(P, slot, pos, stage_saddr, t);
+              DV_BY_DEST(aux & 3u, DV_SET, t)
               continue;
             }
             case UH_LDT: {
-#define DVMB_FN(V)                                                                                              \
-  _Pragma("unroll") for (int g = 0; g < 2; ++g)                                                                  \
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"                                                         \
-                 : "=r"(V[4 * g]), "=r"(V[4 * g + 1]), "=r"(V[4 * g + 2]), "=r"(V[4 * g + 3])                    \
-                 : "r"(temp_addr(arg, g)));
-              DVMB_TO_DEST(DVMB_FN)
-#undef DVMB_FN
+              const uint32_t a0 = temp_addr(arg, 0), a1 = temp_addr(arg, 1);
+              DV_BY_DEST(aux & 3u, DV_LDR32, a0, a1)
               continue;
             }
             case UH_LDS:
             case UH_LDI: {
               const uint32_t v = uh == UH_LDS ? lds32(sreg_addr(arg)) : DVMB_UIMM(u);
-#define DVMB_FN(V) _Pragma("unroll") for (int i = 0; i < kLanes; ++i) V[i] = v;
-              DVMB_TO_DEST(DVMB_FN)
-#undef DVMB_FN
+              DV_BY_DEST(aux & 3u, DV_SPLAT, v)
               continue;
             }
-            case UH_MOVA: {
-              if ((aux & 3u) == UD_B) {
+            case UH_MOVA:
+              if ((aux & 3u) == UD_B) { asm volatile(DV_L8(DV_MOV_LANE, "vb", "va")); } else { asm volatile(DV_L8(DV_MOV_LANE, "vc", "va")); }
+              continue;
+            case UH_STT:
+              asm volatile("st.shared.v4.b32 [%0], {va0,va1,va2,va3};\n\tst.shared.v4.b32 [%1], {va4,va5,va6,va7};" ::"r"(
+                             temp_addr(arg, 0)),
+                           "r"(temp_addr(arg, 1))
+                           : "memory");
+              continue;
+            // ---------------- arithmetic: acc <- op(acc, vb) / op(acc, scalar) ----------------
+            DV_BIN_CASES(B_ADD, DV_BINV_LANE, DV_BINS_LANE, "add.f32")
+            DV_BIN_CASES(B_SUB, DV_BINV_LANE, DV_BINS_LANE, "sub.f32")
+            DV_BIN_CASES(B_MUL, DV_BINV_LANE, DV_BINS_LANE, "mul.f32")
+            DV_BIN_CASES(B_DIV, DV_BINV_LANE, DV_BINS_LANE, "div.rn.f32")
+            DV_BIN_CASES(B_RSUB, DV_RBINV_LANE, DV_RBINS_LANE, "sub.f32")
+            DV_BIN_CASES(B_RDIV, DV_RBINV_LANE, DV_RBINS_LANE, "div.rn.f32")
+            DV_BIN_CASES(B_ADD_I, DV_BINV_LANE, DV_BINS_LANE, "add.s32")
+            DV_BIN_CASES(B_SUB_I, DV_BINV_LANE, DV_BINS_LANE, "sub.s32")
+            DV_BIN_CASES(B_MUL_I, DV_BINV_LANE, DV_BINS_LANE, "mul.lo.s32")
+            DV_BIN_CASES(B_MAX_I, DV_BINV_LANE, DV_BINS_LANE, "max.s32")
+            DV_BIN_CASES(B_MIN_I, DV_BINV_LANE, DV_BINS_LANE, "min.s32")
+            DV_BIN_CASES(B_RSUB_I, DV_RBINV_LANE, DV_RBINS_LANE, "sub.s32")
+            // float max / min keep the reference's `a > b ? a : b` / `a < b ? a : b`
+            case UH_BINV_FIRST + B_MAX: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_PICKV_LANE, "setp.gt.f32") "}"); continue;
+            case UH_BINV_FIRST + B_MIN: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_PICKV_LANE, "setp.lt.f32") "}"); continue;
+            case UH_BINS_FIRST + B_MAX: {
+              const uint32_t sv = (aux & 1u) ? lds32(sreg_addr(arg)) : DVMB_UIMM(u);
+              asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_PICKS_LANE, "setp.gt.f32") "}" ::"r"(sv));
+              continue;
+            }
+            case UH_BINS_FIRST + B_MIN: {
+              const uint32_t sv = (aux & 1u) ? lds32(sreg_addr(arg)) : DVMB_UIMM(u);
+              asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_PICKS_LANE, "setp.lt.f32") "}" ::"r"(sv));
+              continue;
+            }
+            case UH_BINV_FIRST + B_POW:
+            case UH_BINS_FIRST + B_POW: {
+              uint32_t x[kLanes], y[kLanes];
+              DV_GET("va", x)
+              if (uh == UH_BINV_FIRST + B_POW) {
+                DV_GET("vb", y)
+              } else {
+                const uint32_t sv = (aux & 1u) ? lds32(sreg_addr(arg)) : DVMB_UIMM(u);
 #pragma unroll
-                for (int i = 0; i < kLanes; ++i) b[i] = acc[i];
+                for (int i = 0; i < kLanes; ++i) y[i] = sv;
+              }
+#pragma unroll
+              for (int i = 0; i < kLanes; ++i) x[i] = f2u(powf(u2f(x[i]), u2f(y[i])));
+              DV_SET("va", x)
+              continue;
+            }
+            // ---------------- unary ----------------
+            case UH_UN_FIRST + U_SQRT: asm volatile(DV_L8(DV_UN_LANE, "sqrt.rn.f32")); continue;
+            case UH_UN_FIRST + U_ABS: asm volatile(DV_L8(DV_UN_LANE, "abs.f32")); continue;
+            case UH_UN_FIRST + U_ROUND: asm volatile(DV_L8(DV_UN_LANE, "cvt.rni.f32.f32")); continue;
+            case UH_UN_FIRST + U_FLOOR: asm volatile(DV_L8(DV_UN_LANE, "cvt.rmi.f32.f32")); continue;
+            case UH_UN_FIRST + U_CEIL: asm volatile(DV_L8(DV_UN_LANE, "cvt.rpi.f32.f32")); continue;
+            case UH_UN_FIRST + U_TRUNC: asm volatile(DV_L8(DV_UN_LANE, "cvt.rzi.f32.f32")); continue;
+            case UH_UN_FIRST + U_ABS_I: asm volatile(DV_L8(DV_UN_LANE, "abs.s32")); continue;
+            case UH_UN_FIRST + U_ISFINITE:
+              asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_ISFIN_LANE, "") "}");
+              continue;
+            case UH_UN_FIRST + U_LOG:
+            case UH_UN_FIRST + U_EXP: {
+              uint32_t x[kLanes];
+              DV_GET("va", x)
+              if (uh == UH_UN_FIRST + U_EXP) {
+#pragma unroll
+                for (int i = 0; i < kLanes; ++i) x[i] = f2u(expf(u2f(x[i])));
               } else {
 #pragma unroll
-                for (int i = 0; i < kLanes; ++i) c[i] = acc[i];
+                for (int i = 0; i < kLanes; ++i) x[i] = f2u(logf(u2f(x[i])));
               }
-              continue;
-            }
-            case UH_STT: {
-#pragma unroll
-              for (int g = 0; g < 2; ++g)
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(temp_addr(arg, g)), "r"(acc[4 * g]),
-                             "r"(acc[4 * g + 1]), "r"(acc[4 * g + 2]), "r"(acc[4 * g + 3])
-                             : "memory");
-              continue;
-            }
-            // ---------------- arithmetic ----------------
-            DVMB_BINV(B_ADD, float, u2f, f2u, x + y)
-            DVMB_BINV(B_SUB, float, u2f, f2u, x - y)
-            DVMB_BINV(B_MUL, float, u2f, f2u, x * y)
-            DVMB_BINV(B_DIV, float, u2f, f2u, x / y)
-            DVMB_BINV(B_MAX, float, u2f, f2u, (x > y ? x : y))
-            DVMB_BINV(B_MIN, float, u2f, f2u, (x < y ? x : y))
-            DVMB_BINV(B_POW, float, u2f, f2u, powf(x, y))
-            DVMB_BINV(B_RSUB, float, u2f, f2u, y - x)
-            DVMB_BINV(B_RDIV, float, u2f, f2u, y / x)
-            DVMB_BINV(B_ADD_I, uint32_t, DVMB_AS_U32, DVMB_AS_U32, x + y)
-            DVMB_BINV(B_SUB_I, uint32_t, DVMB_AS_U32, DVMB_AS_U32, x - y)
-            DVMB_BINV(B_MUL_I, uint32_t, DVMB_AS_U32, DVMB_AS_U32, x * y)
-            DVMB_BINV(B_MAX_I, int32_t, DVMB_AS_INT, DVMB_AS_U32, (x > y ? x : y))
-            DVMB_BINV(B_MIN_I, int32_t, DVMB_AS_INT, DVMB_AS_U32, (x < y ? x : y))
-            DVMB_BINV(B_RSUB_I, uint32_t, DVMB_AS_U32, DVMB_AS_U32, y - x)
-            DVMB_UNOP(U_SQRT, sqrtf(x))
-            DVMB_UNOP(U_ABS, fabsf(x))
-            DVMB_UNOP(U_LOG, logf(x))
-            DVMB_UNOP(U_EXP, expf(x))
-            DVMB_UNOP(U_ROUND, nearbyintf(x))
-            DVMB_UNOP(U_FLOOR, floorf(x))
-            DVMB_UNOP(U_CEIL, ceilf(x))
-            DVMB_UNOP(U_TRUNC, truncf(x))
-            DVMB_UNOP(U_ISFINITE, (isfinite(x) ? 1.0f : 0.0f))
-            case UH_UN_FIRST + U_ABS_I: {
-#pragma unroll
-              for (int i = 0; i < kLanes; ++i) acc[i] = (int32_t)acc[i] < 0 ? (0u - acc[i]) : acc[i];
+              DV_SET("va", x)
               continue;
             }
             case UH_UN_FIRST + U_NOP: continue;
-            case UH_RND_F16: apply_round<kLanes>(RN_F16, acc); continue;
-            case UH_RND_BF16: apply_round<kLanes>(RN_BF16, acc); continue;
-            case UH_CMP_F_V: apply_cmp<kLanes>(aux & 7u, 0, acc, VecOperand<kLanes>{b}); continue;
-            case UH_CMP_I_V: apply_cmp<kLanes>(aux & 7u, 1, acc, VecOperand<kLanes>{b}); continue;
+            case UH_RND_F16: asm volatile("{\n\t.reg .b16 h;\n\t" DV_L8(DV_RNDH_LANE, "") "}"); continue;
+            case UH_RND_BF16:
+              asm volatile("{\n\t.reg .b32 t;\n\t" DV_RNDB_PAIR("0", "1") DV_RNDB_PAIR("2", "3") DV_RNDB_PAIR("4", "5") DV_RNDB_PAIR("6", "7") "}");
+              continue;
+            // ---------------- compare / select / convert ----------------
+            case UH_CMP_F_V:
             case UH_CMP_F_S:
+            case UH_CMP_I_V:
             case UH_CMP_I_S: {
-              const SplatOperand so{(aux & 0x80u) ? lds32(sreg_addr(arg)) : DVMB_UIMM(u)};
-              apply_cmp<kLanes>(aux & 7u, uh == UH_CMP_I_S ? 1u : 0u, acc, so);
+              const bool is_int = uh == UH_CMP_I_V || uh == UH_CMP_I_S;
+              if (uh == UH_CMP_F_S || uh == UH_CMP_I_S) {
+                const uint32_t sv = (aux & 0x80u) ? lds32(sreg_addr(arg)) : DVMB_UIMM(u);
+                DV_SPLAT("vb", sv)
+              }
+              switch ((aux & 7u) | (is_int ? 8u : 0u)) {
+                case C_EQ: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPF_LANE, "setp.eq.f32") "}"); break;
+                case C_NE: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPF_LANE, "setp.neu.f32") "}"); break;
+                case C_GT: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPF_LANE, "setp.gt.f32") "}"); break;
+                case C_GE: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPF_LANE, "setp.ge.f32") "}"); break;
+                case C_LT: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPF_LANE, "setp.lt.f32") "}"); break;
+                case C_LE: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPF_LANE, "setp.le.f32") "}"); break;
+                case 8 + C_EQ: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPI_LANE, "setp.eq.s32") "}"); break;
+                case 8 + C_NE: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPI_LANE, "setp.ne.s32") "}"); break;
+                case 8 + C_GT: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPI_LANE, "setp.gt.s32") "}"); break;
+                case 8 + C_GE: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPI_LANE, "setp.ge.s32") "}"); break;
+                case 8 + C_LT: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPI_LANE, "setp.lt.s32") "}"); break;
+                default: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPI_LANE, "setp.le.s32") "}"); break;
+              }
               continue;
             }
-            case UH_SEL_F: apply_sel<kLanes>(0, 0, acc, VecOperand<kLanes>{b}, c); continue;
-            case UH_SEL_I: apply_sel<kLanes>(1, 0, acc, VecOperand<kLanes>{b}, c); continue;
-            case UH_CVT_F2I: apply_cvt<kLanes>(V_F2I, acc); continue;
-            case UH_CVT_I2F: apply_cvt<kLanes>(V_I2F, acc); continue;
-            case UH_CVT_NEZ_F: apply_cvt<kLanes>(V_NEZ_F, acc); continue;
-            case UH_CVT_NEZ_I: apply_cvt<kLanes>(V_NEZ_I, acc); continue;
+            case UH_SEL_F: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_SEL_LANE, "setp.neu.f32 p, va", ", 0f00000000") "}"); continue;
+            case UH_SEL_I: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_SEL_LANE, "setp.ne.s32 p, va", ", 0") "}"); continue;
+            case UH_CVT_F2I: asm volatile(DV_L8(DV_UN_LANE, "cvt.rzi.s32.f32")); continue;
+            case UH_CVT_I2F: asm volatile(DV_L8(DV_UN_LANE, "cvt.rn.f32.s32")); continue;
+            case UH_CVT_NEZ_F: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_NEZ_LANE, "setp.neu.f32 p, va", ", 0f00000000") "}"); continue;
+            case UH_CVT_NEZ_I: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_NEZ_LANE, "setp.ne.s32 p, va", ", 0") "}"); continue;
+            // ---------------- reductions ----------------
             case UH_RACC_SUM:
             case UH_RACC_MAX:
             case UH_RACC_MIN: {
               const uint32_t kind = uh - UH_RACC_SUM;
+              uint32_t x[kLanes];
+              DV_GET("va", x)
               float v = red_identity(kind);
               if (full_tile) {
 #pragma unroll
-                for (int i = 0; i < kLanes; ++i) v = red_combine(kind, v, u2f(acc[i]));
+                for (int i = 0; i < kLanes; ++i) v = red_combine(kind, v, u2f(x[i]));
               } else {
 #pragma unroll
                 for (int i = 0; i < kLanes; ++i)
-                  if (pos.gvalid && (i & 3) < pos.nv[i >> 2]) v = red_combine(kind, v, u2f(acc[i]));
+                  if (pos.gvalid && (i & 3) < pos.nv[i >> 2]) v = red_combine(kind, v, u2f(x[i]));
               }
-              DVMB_PART_CASES(arg & 3u, part[J] = red_combine(kind, part[J], v);)
+              set_part(arg & 3u, red_combine(kind, get_part(arg & 3u), v));
               continue;
             }
             // ---------------- stores ----------------
-            case UH_ST_F32:
-            case UH_ST_F16:
-            case UH_ST_BF16:
-            case UH_ST_U8: {
+            case UH_ST_F32: {
               if (!full_tile) goto store_generic;
               const TensorDesc &td = P.tensor[arg];
-              uint8_t *base = reinterpret_cast<uint8_t *>(td.ptr);
-              const uint32_t off0 = kept_offset(td, pos.k) + pos.e0[0];
-              const uint32_t off1 = off0 + 4u * tg;
-              gstore4(uh == UH_ST_F32 ? T_F32 : (uh == UH_ST_F16 ? T_F16 : (uh == UH_ST_BF16 ? T_BF16 : T_BOOL)), base, off0, &acc[0]);
-              gstore4(uh == UH_ST_F32 ? T_F32 : (uh == UH_ST_F16 ? T_F16 : (uh == UH_ST_BF16 ? T_BF16 : T_BOOL)), base, off1, &acc[4]);
+              uint32_t *p0 = reinterpret_cast<uint32_t *>(td.ptr) + kept_offset(td, pos.k) + pos.e0[0];
+              asm volatile("st.global.v4.b32 [%0], {va0,va1,va2,va3};\n\tst.global.v4.b32 [%1], {va4,va5,va6,va7};" ::"l"(p0),
+                           "l"(p0 + 4u * tg)
+                           : "memory");
               continue;
             }
+            case UH_ST_F16:
+            case UH_ST_BF16: {
+              if (!full_tile) goto store_generic;
+              const TensorDesc &td = P.tensor[arg];
+              unsigned short *p0 = reinterpret_cast<unsigned short *>(td.ptr) + kept_offset(td, pos.k) + pos.e0[0];
+              if (uh == UH_ST_BF16) {
+                asm volatile("{\n\t.reg .b32 t0, t1;\n\t"
+                             "cvt.rn.bf16x2.f32 t0, va1, va0;\n\tcvt.rn.bf16x2.f32 t1, va3, va2;\n\tst.global.v2.b32 [%0], {t0,t1};\n\t"
+                             "cvt.rn.bf16x2.f32 t0, va5, va4;\n\tcvt.rn.bf16x2.f32 t1, va7, va6;\n\tst.global.v2.b32 [%1], {t0,t1};\n\t}" ::"l"(p0),
+                             "l"(p0 + 4u * tg)
+                             : "memory");
+              } else {
+                asm volatile("{\n\t.reg .b32 t0, t1;\n\t"
+                             "cvt.rn.f16x2.f32 t0, va1, va0;\n\tcvt.rn.f16x2.f32 t1, va3, va2;\n\tst.global.v2.b32 [%0], {t0,t1};\n\t"
+                             "cvt.rn.f16x2.f32 t0, va5, va4;\n\tcvt.rn.f16x2.f32 t1, va7, va6;\n\tst.global.v2.b32 [%1], {t0,t1};\n\t}" ::"l"(p0),
+                             "l"(p0 + 4u * tg)
+                             : "memory");
+              }
+              continue;
+            }
+            case UH_ST_U8:
             case UH_STG: {
             store_generic:
-              store_tensor(P, arg, pos, acc);
+              uint32_t x[kLanes];
+              DV_GET("va", x)
+              store_tensor(P, arg, pos, x);
               continue;
             }
             default: continue;
