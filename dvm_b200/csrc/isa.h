@@ -4,11 +4,11 @@
 // `group_elems` elements.  A reduce-free graph is one group spanning the whole (coalesced) domain and its
 // chunks are dealt round-robin to the CTAs ("flat" mode).  A graph with reductions makes one group per
 // kept (non-reduced) coordinate; a CTA, or a power-of-two slice of a warp, owns a group and loops over
-// its chunks ("group" mode).  A chunk is `8 * tg` consecutive elements of a group: thread `t` of the
-// group owns two 4-element granules at `4*t` and `4*tg + 4*t` inside the chunk, so every global access
+// its chunks ("group" mode).  A chunk is up to `16 * tg` consecutive elements of a group: thread `t` of the
+// group owns four 4-element granules at `4*t + g*4*tg` (g = 0..3) inside the chunk, so every global access
 // is a coalesced 16-byte (fp32), 8-byte (fp16/bf16) or 4-byte (bool) vector.
 //
-// The machine is an accumulator machine.  The 8-lane accumulator is the only vector state in registers;
+// The machine is an accumulator machine.  The 16-lane accumulator is the only vector state in registers;
 // every other operand is read where it already lives: an input tensor's chunk in the shared-memory ring
 // that a producer warp fills with bulk async copies (cp.async.bulk + mbarrier), a thread-private
 // shared-memory temporary, a scalar register, or an immediate.  The scalar side (accumulator + 12 named
@@ -34,7 +34,7 @@ constexpr int kNumTemps = 6;            // thread-private 8-lane temporaries in 
 constexpr int kNumSRegs = 12;
 constexpr int kNumRSlots = 4;
 constexpr int kMaxPhases = 4;        // BODY sections
-constexpr int kLanes = 8;            // elements per thread per vector register
+constexpr int kLanes = 16;           // elements per thread per vector register (four 4-element granules)
 constexpr int kAccIdx = 15;          // `dst` value meaning "the accumulator"
 
 // Element types as stored in global memory (same numbering as dvm::DataType).
@@ -182,7 +182,7 @@ struct VmParam {
   uint32_t tg;               // threads cooperating on one group
   uint32_t groups_per_cta;   // blockDim.x / tg
   uint32_t chunks;           // chunks per group
-  uint32_t chunk_elems;      // elements per chunk (<= 8 * tg; threads past the end idle)
+  uint32_t chunk_elems;      // elements per chunk (<= 16 * tg; threads past the end idle)
   uint32_t stage_bytes;      // bytes of one ring stage (0: no bulk staging in this launch)
   uint32_t num_stages;
   uint32_t body_ring_mask[kMaxPhases];  // per BODY section: tensor slots the producer stages

@@ -831,7 +831,7 @@ struct Compiler {
 
     // ---- thread / chunk geometry
     const int64_t inner = cenum.empty() ? 1 : cenum.back().size;
-    const uint32_t kChunkCap = 8 * kVmFlatThreads;   // elements
+    const uint32_t kChunkCap = kLanes * kVmFlatThreads;   // elements
     bool chunk_in_inner = false;   // every chunk lies inside one run of the innermost iterated axis
     bool packed = false;           // several small groups share a CTA
     if (!has_reduce) {
@@ -839,17 +839,17 @@ struct Compiler {
       P.tg = kVmFlatThreads;
       if (const char *env = getenv("DVM_B200_FLAT_THREADS")) P.tg = static_cast<uint32_t>(atoi(env));
       P.groups_per_cta = 1;
-      P.chunk_elems = 8 * P.tg;
+      P.chunk_elems = kLanes * P.tg;
       P.chunks = static_cast<uint32_t>((G + P.chunk_elems - 1) / P.chunk_elems);
       chunk_in_inner = cenum.size() <= 1 || (inner % P.chunk_elems == 0);
     } else {
       P.mode = VM_GROUP;
-      if (G <= 8 * 32) {
+      if (G <= kLanes * 32) {
         uint32_t tg = 1;
-        while (8 * tg < G) tg <<= 1;
+        while (kLanes * tg < G) tg <<= 1;
         P.tg = tg;
         P.groups_per_cta = kVmFlatThreads / tg;
-        P.chunk_elems = 8 * tg;
+        P.chunk_elems = kLanes * tg;
         P.chunks = 1;
         packed = true;
       } else {
@@ -865,13 +865,13 @@ struct Compiler {
         }
         if (ce != 0) {
           P.chunk_elems = ce;
-          P.tg = ((ce + 7) / 8 + 31) / 32 * 32;
+          P.tg = ((ce + kLanes - 1) / kLanes + 31) / 32 * 32;
           chunk_in_inner = true;
         } else {
           const uint32_t chunks = static_cast<uint32_t>((G + kChunkCap - 1) / kChunkCap);
-          const uint32_t per = static_cast<uint32_t>((G + 8ll * chunks - 1) / (8ll * chunks));
+          const uint32_t per = static_cast<uint32_t>((G + 1ll * kLanes * chunks - 1) / (1ll * kLanes * chunks));
           P.tg = (per + 31) / 32 * 32;
-          P.chunk_elems = 8 * P.tg;
+          P.chunk_elems = kLanes * P.tg;
           chunk_in_inner = cenum.size() <= 1;
         }
         P.chunks = static_cast<uint32_t>((G + P.chunk_elems - 1) / P.chunk_elems);
@@ -950,12 +950,15 @@ struct Compiler {
     // ---- shared memory plan
     P.num_temps = static_cast<uint32_t>(max_temp);
     P.num_sregs = static_cast<uint32_t>(max_sreg);
-    const uint32_t fixed = kVmSmemStages + P.num_temps * T * 32u + P.num_sregs * T * 4u;
+    const uint32_t fixed = kVmSmemStages + P.num_temps * T * (4u * kLanes) + P.num_sregs * T * 4u;
     uint32_t stages = 0;
     if (stage_bytes != 0) {
-      uint32_t budget = 72 * 1024;   // three CTAs of this size fit one SM
+      uint32_t budget = 100 * 1024;   // two CTAs of this size fit one SM
       if (const char *env = getenv("DVM_B200_RING_KB")) budget = static_cast<uint32_t>(atoi(env)) * 1024u;
-      stages = fixed + 2 * stage_bytes > budget ? 2 : std::min<uint32_t>(kVmMaxStages, (budget - fixed) / stage_bytes);
+      // enough stages to keep about 48 KB per CTA in flight (small tiles need a deep ring to cover the memory
+      // latency), at least three; beyond that deeper read-ahead measured slower on large tiles
+      const uint32_t want = std::max<uint32_t>(3u, (48u * 1024u + stage_bytes - 1) / stage_bytes + 1);
+      stages = fixed + 2 * stage_bytes > budget ? 2 : std::min<uint32_t>(std::min<uint32_t>(want, kVmMaxStages), (budget - fixed) / stage_bytes);
       if (const char *env = getenv("DVM_B200_STAGES")) stages = static_cast<uint32_t>(atoi(env));
       if (fixed + stages * stage_bytes > kVmMaxSmemBytes) {
         // too large to stage even twice: fall back to direct global loads
@@ -976,7 +979,7 @@ struct Compiler {
     out->threads = T + (stage_bytes != 0 ? 32u : 0u);
 
     // ---- grid: persistent CTAs, as many as fit per SM
-    uint32_t per_sm_cap = 3u;
+    uint32_t per_sm_cap = 2u;
     if (const char *env = getenv("DVM_B200_CTAS_PER_SM")) per_sm_cap = static_cast<uint32_t>(atoi(env));
     uint32_t per_sm = std::max<uint32_t>(1u, std::min<uint32_t>(per_sm_cap, (220u * 1024u) / std::max<uint32_t>(out->smem_bytes + 1024u, 1u)));
     if (T > static_cast<uint32_t>(kVmFlatThreads)) per_sm = 1;

@@ -20,6 +20,7 @@
 
 #include "isa.h"
 #include "vm_launch.h"
+#include "vm_vector_regs.h"
 
 namespace dvmb {
 
@@ -374,14 +375,16 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void *src, uin
 
 // ---- addressing -----------------------------------------------------------------------------------
 
-// Per-thread position inside the iteration space.
+constexpr int kGranules = kLanes / 4;
+
+// Per-thread position inside the iteration space.  Granule g of the thread starts `in_chunk0 + g * 4 * tg`
+// elements into the chunk.
 struct Pos {
-  uint32_t k[kMaxKept];      // kept coordinates of this thread's group
-  uint32_t e0[2];            // first element (inside the group) of each granule
-  int32_t nv[2];             // valid elements of each granule (0..4)
-  uint32_t ec[2][kMaxEnum];  // enumerated coordinates of each granule's first element (AM_GRANULE)
-  uint32_t in_chunk[2];      // element index of each granule inside its chunk
-  uint32_t chunk_valid;      // valid elements of the current chunk
+  uint32_t k[kMaxKept];   // kept coordinates of this thread's group
+  uint32_t e_start;       // first element (inside the group) of the current chunk
+  uint32_t in_chunk0;     // element index of granule 0 inside its chunk
+  uint32_t gstep;         // 4 * tg
+  uint32_t chunk_valid;   // valid elements of the current chunk
   bool gvalid;
 };
 
@@ -410,10 +413,27 @@ __device__ __forceinline__ uint32_t enum_offset(const TensorDesc &td, const uint
   return off;
 }
 
-// Fetch the 8 lanes of tensor `slot` for this thread: from the ring stage when the tensor is staged and the
-// granule lies inside the bulk-copied part, else straight from global memory.
-__device__ __forceinline__ void fetch_tensor(const VmParam &P, uint32_t slot, const Pos &pos, uint32_t stage_saddr,
-                                             uint32_t (&out)[kLanes]) {
+// Element offset and inner stride of a granule that starts at element `e0` of the group.
+__device__ __forceinline__ uint32_t granule_offset(const VmParam &P, const TensorDesc &td, uint32_t koff, uint32_t e0,
+                                                   uint32_t *istride) {
+  const uint32_t mode = td.mode;
+  *istride = 1;
+  if (mode == AM_DENSE) return koff + e0;
+  if (mode == AM_GRANULE) {
+    uint32_t c[kMaxEnum];
+    split_enum(P, e0, c);
+    *istride = td.estride[kMaxEnum - 1];
+    return koff + enum_offset(td, c);
+  }
+  *istride = 0;
+  return koff;
+}
+
+// General fetch of the 16 lanes of tensor `slot` for this thread: from the ring stage when the tensor is
+// staged and the granule lies inside the bulk-copied part, else straight from global memory, element by
+// element where the layout or a ragged tail needs it.
+__device__ __noinline__ void fetch_tensor(const VmParam &P, uint32_t slot, const Pos &pos, uint32_t stage_saddr,
+                                          uint32_t (&out)[kLanes]) {
   const TensorDesc &td = P.tensor[slot];
   const uint32_t dtype = td.dtype, mode = td.mode;
   const uint32_t sh = item_shift(dtype);
@@ -422,36 +442,31 @@ __device__ __forceinline__ void fetch_tensor(const VmParam &P, uint32_t slot, co
   const uint32_t bulk_elems = staged ? (((pos.chunk_valid << sh) & ~15u) >> sh) : 0u;
   const uint8_t *base = reinterpret_cast<const uint8_t *>(td.ptr);
   const uint32_t koff = kept_offset(td, pos.k);
-#pragma unroll
-  for (int g = 0; g < 2; ++g) {
+#pragma unroll 1
+  for (int g = 0; g < kGranules; ++g) {
     uint32_t *o = &out[4 * g];
-    if (staged && pos.in_chunk[g] + 4 <= bulk_elems) {
-      unpack4(dtype, sload4(dtype, stage_saddr + td.ring_off + (pos.in_chunk[g] << sh)), o);
+    const uint32_t ic = pos.in_chunk0 + (uint32_t)g * pos.gstep;
+    if (staged && ic + 4 <= bulk_elems) {
+      unpack4(dtype, sload4(dtype, stage_saddr + td.ring_off + (ic << sh)), o);
       continue;
     }
-    const int nv = pos.gvalid ? pos.nv[g] : 0;
+    const int32_t left = (int32_t)pos.chunk_valid - (int32_t)ic;
+    const int nv = !pos.gvalid ? 0 : (left >= 4 ? 4 : (left > 0 ? left : 0));
+    const uint32_t e0 = pos.e_start + ic;
     if (mode == AM_ELEMENT) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         o[i] = 0;
         if (i < nv) {
           uint32_t c[kMaxEnum];
-          split_enum(P, pos.e0[g] + i, c);
+          split_enum(P, e0 + i, c);
           o[i] = load_elem(dtype, base, koff + enum_offset(td, c));
         }
       }
       continue;
     }
-    uint32_t off = koff;
-    uint32_t istride = 1;
-    if (mode == AM_GRANULE) {
-      off += enum_offset(td, pos.ec[g]);
-      istride = td.estride[kMaxEnum - 1];
-    } else if (mode == AM_DENSE) {
-      off += pos.e0[g];
-    } else {
-      istride = 0;
-    }
+    uint32_t istride;
+    const uint32_t off = granule_offset(P, td, koff, nv > 0 ? e0 : 0u, &istride);
     if (td.vec_ok && nv == 4) {
       unpack4(dtype, gload4(dtype, base, off), o);
     } else {
@@ -461,37 +476,32 @@ __device__ __forceinline__ void fetch_tensor(const VmParam &P, uint32_t slot, co
   }
 }
 
-__device__ __forceinline__ void store_tensor(const VmParam &P, uint32_t slot, const Pos &pos,
-                                             const uint32_t (&val)[kLanes]) {
+__device__ __noinline__ void store_tensor(const VmParam &P, uint32_t slot, const Pos &pos,
+                                          const uint32_t (&val)[kLanes]) {
   const TensorDesc &td = P.tensor[slot];
   uint8_t *base = reinterpret_cast<uint8_t *>(td.ptr);
   const uint32_t dtype = td.dtype, mode = td.mode;
   const uint32_t koff = kept_offset(td, pos.k);
-#pragma unroll
-  for (int g = 0; g < 2; ++g) {
-    const int nv = pos.gvalid ? pos.nv[g] : 0;
+#pragma unroll 1
+  for (int g = 0; g < kGranules; ++g) {
+    const uint32_t ic = pos.in_chunk0 + (uint32_t)g * pos.gstep;
+    const int32_t left = (int32_t)pos.chunk_valid - (int32_t)ic;
+    const int nv = !pos.gvalid ? 0 : (left >= 4 ? 4 : (left > 0 ? left : 0));
+    const uint32_t e0 = pos.e_start + ic;
     const uint32_t *v = &val[4 * g];
     if (mode == AM_ELEMENT) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         if (i < nv) {
           uint32_t c[kMaxEnum];
-          split_enum(P, pos.e0[g] + i, c);
+          split_enum(P, e0 + i, c);
           store_elem(dtype, base, koff + enum_offset(td, c), v[i]);
         }
       }
       continue;
     }
-    uint32_t off = koff;
-    uint32_t istride = 1;
-    if (mode == AM_GRANULE) {
-      off += enum_offset(td, pos.ec[g]);
-      istride = td.estride[kMaxEnum - 1];
-    } else if (mode == AM_DENSE) {
-      off += pos.e0[g];
-    } else {
-      istride = 0;
-    }
+    uint32_t istride;
+    const uint32_t off = granule_offset(P, td, koff, nv > 0 ? e0 : 0u, &istride);
     if (td.vec_ok && nv == 4) {
       gstore4(dtype, base, off, v);
     } else {
@@ -501,14 +511,6 @@ __device__ __forceinline__ void store_tensor(const VmParam &P, uint32_t slot, co
     }
   }
 }
-
-#define DVMB_PART_CASES(IDX, STMT) \
-  switch (IDX) {                   \
-    case 0: { constexpr int J = 0; STMT } break; \
-    case 1: { constexpr int J = 1; STMT } break; \
-    case 2: { constexpr int J = 2; STMT } break; \
-    default: { constexpr int J = 3; STMT } break; \
-  }
 
 __device__ __forceinline__ void decompose_group(const VmParam &P, uint32_t gi, uint32_t (&k)[kMaxKept]) {
 #pragma unroll
@@ -521,78 +523,13 @@ __device__ __forceinline__ void decompose_group(const VmParam &P, uint32_t gi, u
   k[0] = gi;
 }
 
-
-// ---- hidden vector registers ------------------------------------------------------------------------
-// va0..7 accumulator, vb0..7 / vc0..7 operands, vp0..3 reduction partials: PTX registers declared once at
-// the top of the kernel and named only inside inline assembly.
-#define DV_L8(M, ...) M(0, __VA_ARGS__) M(1, __VA_ARGS__) M(2, __VA_ARGS__) M(3, __VA_ARGS__) M(4, __VA_ARGS__) M(5, __VA_ARGS__) M(6, __VA_ARGS__) M(7, __VA_ARGS__)
-#define DV_BINV_LANE(i, OP) OP " va" #i ", va" #i ", vb" #i ";\n\t"
-#define DV_RBINV_LANE(i, OP) OP " va" #i ", vb" #i ", va" #i ";\n\t"
-#define DV_BINS_LANE(i, OP) OP " va" #i ", va" #i ", %0;\n\t"
-#define DV_RBINS_LANE(i, OP) OP " va" #i ", %0, va" #i ";\n\t"
-#define DV_PICKV_LANE(i, SETP) SETP " p, va" #i ", vb" #i ";\n\tselp.b32 va" #i ", va" #i ", vb" #i ", p;\n\t"
-#define DV_PICKS_LANE(i, SETP) SETP " p, va" #i ", %0;\n\tselp.b32 va" #i ", va" #i ", %0, p;\n\t"
-#define DV_UN_LANE(i, OP) OP " va" #i ", va" #i ";\n\t"
-#define DV_ISFIN_LANE(i, X) "testp.finite.f32 p, va" #i ";\n\tselp.b32 va" #i ", 0x3f800000, 0, p;\n\t"
-#define DV_RNDH_LANE(i, X) "cvt.rn.f16.f32 h, va" #i ";\n\tcvt.f32.f16 va" #i ", h;\n\t"
-#define DV_RNDB_PAIR(a, b) "cvt.rn.bf16x2.f32 t, va" b ", va" a ";\n\tshl.b32 va" a ", t, 16;\n\tand.b32 va" b ", t, 0xffff0000;\n\t"
-#define DV_CMPF_LANE(i, SETP) SETP " p, va" #i ", vb" #i ";\n\tselp.b32 va" #i ", 0x3f800000, 0, p;\n\t"
-#define DV_CMPI_LANE(i, SETP) SETP " p, va" #i ", vb" #i ";\n\tselp.b32 va" #i ", 1, 0, p;\n\t"
-#define DV_SEL_LANE(i, TEST, ZERO) TEST #i ZERO ";\n\tselp.b32 va" #i ", vb" #i ", vc" #i ", p;\n\t"
-#define DV_NEZ_LANE(i, TEST, ZERO) TEST #i ZERO ";\n\tselp.b32 va" #i ", 1, 0, p;\n\t"
-#define DV_MOV_LANE(i, D, S_) "mov.b32 " D #i ", " S_ #i ";\n\t"
-#define DV_GETLANE(i, R) "mov.b32 %" #i ", " R #i ";\n\t"
-#define DV_SETLANE(i, R) "mov.b32 " R #i ", %" #i ";\n\t"
-#define DV_SPLATLANE(i, R) "mov.b32 " R #i ", %0;\n\t"
-#define DV_GET(R, X) \
-  asm volatile(DV_L8(DV_GETLANE, R) : "=r"(X[0]), "=r"(X[1]), "=r"(X[2]), "=r"(X[3]), "=r"(X[4]), "=r"(X[5]), "=r"(X[6]), "=r"(X[7]));
-#define DV_SET(R, X) \
-  asm volatile(DV_L8(DV_SETLANE, R)::"r"(X[0]), "r"(X[1]), "r"(X[2]), "r"(X[3]), "r"(X[4]), "r"(X[5]), "r"(X[6]), "r"(X[7]));
-#define DV_SPLAT(R, V) asm volatile(DV_L8(DV_SPLATLANE, R)::"r"(V));
-#define DV_LDR32(R, A0, A1)                                                                          \
-  asm volatile("ld.shared.v4.b32 {" R "0," R "1," R "2," R "3}, [%0];\n\tld.shared.v4.b32 {" R "4," R "5," R "6," R "7}, [%1];" ::"r"(A0), \
-               "r"(A1)                                                                               \
-               : "memory");
-#define DV_BF16_HALF(R, a, b, c, d, T0, T1) \
-  "shl.b32 " R a ", " T0 ", 16;\n\tand.b32 " R b ", " T0 ", 0xffff0000;\n\tshl.b32 " R c ", " T1 ", 16;\n\tand.b32 " R d ", " T1 ", 0xffff0000;\n\t"
-#define DV_LDR_BF16(R, A0, A1)                                                                     \
-  asm volatile("{\n\t.reg .b32 t0, t1, t2, t3;\n\tld.shared.v2.b32 {t0,t1}, [%0];\n\tld.shared.v2.b32 {t2,t3}, [%1];\n\t" \
-               DV_BF16_HALF(R, "0", "1", "2", "3", "t0", "t1") DV_BF16_HALF(R, "4", "5", "6", "7", "t2", "t3") "}" ::"r"(A0), \
-               "r"(A1)                                                                             \
-               : "memory");
-#define DV_F16_PAIR(R, a, b, T) "mov.b32 {h0,h1}, " T ";\n\tcvt.f32.f16 " R a ", h0;\n\tcvt.f32.f16 " R b ", h1;\n\t"
-#define DV_LDR_F16(R, A0, A1)                                                                      \
-  asm volatile("{\n\t.reg .b32 t0, t1, t2, t3;\n\t.reg .b16 h0, h1;\n\tld.shared.v2.b32 {t0,t1}, [%0];\n\tld.shared.v2.b32 {t2,t3}, [%1];\n\t" \
-               DV_F16_PAIR(R, "0", "1", "t0") DV_F16_PAIR(R, "2", "3", "t1") DV_F16_PAIR(R, "4", "5", "t2") DV_F16_PAIR(R, "6", "7", "t3") "}" ::"r"(A0), \
-               "r"(A1)                                                                             \
-               : "memory");
-#define DV_U8_QUAD(R, a, b, c, d, T) \
-  "and.b32 " R a ", " T ", 255;\n\tbfe.u32 " R b ", " T ", 8, 8;\n\tbfe.u32 " R c ", " T ", 16, 8;\n\tshr.u32 " R d ", " T ", 24;\n\t"
-#define DV_LDR_U8(R, A0, A1)                                                                       \
-  asm volatile("{\n\t.reg .b32 t0, t1;\n\tld.shared.b32 t0, [%0];\n\tld.shared.b32 t1, [%1];\n\t"  \
-               DV_U8_QUAD(R, "0", "1", "2", "3", "t0") DV_U8_QUAD(R, "4", "5", "6", "7", "t1") "}" ::"r"(A0), \
-               "r"(A1)                                                                             \
-               : "memory");
-// run FN("va"| "vb" | "vc", args...) for destination code D
-#define DV_BY_DEST(D, FN, ...)                \
-  {                                           \
-    const uint32_t d_ = (D);                  \
-    if (d_ == UD_ACC) { FN("va", __VA_ARGS__) } else if (d_ == UD_B) { FN("vb", __VA_ARGS__) } else { FN("vc", __VA_ARGS__) } \
-  }
-#define DV_BIN_CASES(K, VLANE, SLANE, OP)                                      \
-  case UH_BINV_FIRST + K: asm volatile(DV_L8(VLANE, OP)); continue;            \
-  case UH_BINS_FIRST + K: {                                                    \
-    const uint32_t sv_ = (aux & 1u) ? lds32(sreg_addr(arg)) : DVMB_UIMM(u);    \
-    asm volatile(DV_L8(SLANE, OP)::"r"(sv_));                                  \
-    continue;                                                                  \
-  }
-
 }  // namespace
 
 namespace {
 __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
-  asm volatile(".reg .b32 va<8>, vb<8>, vc<8>, vp<4>;");
-  asm volatile(DV_L8(DV_SPLATLANE, "va") DV_L8(DV_SPLATLANE, "vb") DV_L8(DV_SPLATLANE, "vc") "mov.b32 vp0, %0;\n\tmov.b32 vp1, %0;\n\tmov.b32 vp2, %0;\n\tmov.b32 vp3, %0;" ::"r"(0u));
+  asm volatile(DV_DECLARE);
+  asm volatile(DV_LN(DV_SPLATLANE, "va") DV_LN(DV_SPLATLANE, "vb") DV_LN(DV_SPLATLANE, "vc")
+               "mov.b32 vp0, %0;\n\tmov.b32 vp1, %0;\n\tmov.b32 vp2, %0;\n\tmov.b32 vp3, %0;" ::"r"(0u));
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
   const uint32_t tid = threadIdx.x;
@@ -618,17 +555,21 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
   // =============================== producer warp ===============================
   if (tid >= T) {
     if (tid != T) return;
-    uint32_t seq = 0;
+    uint32_t pstage = 0, pparity = 0;
     for (uint32_t gb = gb_begin; gb < ngb; gb += gb_step) {
       uint32_t k[kMaxKept];
       decompose_group(P, gb, k);   // groups_per_cta == 1 whenever the ring is on
       for (uint32_t ph = 0; ph < P.num_body; ++ph) {
         const uint32_t mask = P.body_ring_mask[ph];
         if (mask == 0) continue;
-        for (uint32_t ch = ch_begin; ch < P.chunks; ch += ch_step, ++seq) {
-          const uint32_t stage = seq % S, use = seq / S;
+        for (uint32_t ch = ch_begin; ch < P.chunks; ch += ch_step) {
+          const uint32_t stage = pstage;
           const uint32_t full = smem_base + kVmSmemBarriers + 8 * stage;
-          mbar_wait(full + 64, (use & 1u) ^ 1u, 1);
+          mbar_wait(full + 64, pparity ^ 1u, 1);
+          if (++pstage == S) {
+            pstage = 0;
+            pparity ^= 1u;
+          }
           const uint32_t e_start = ch * P.chunk_elems;
           const uint32_t valid = min(P.chunk_elems, P.group_elems - e_start);
           uint32_t c[kMaxEnum];
@@ -664,17 +605,19 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
   // the dispatch loop (nothing to copy at the switch merge), and ptxas keeps each one in a fixed register.
   float *red_buf = reinterpret_cast<float *>(smem + kVmSmemRed);
   const uint32_t temps_saddr = smem_base + kVmSmemStages + S * P.stage_bytes;
-  const uint32_t sregs_saddr = temps_saddr + P.num_temps * T * 32u;
+  const uint32_t sregs_saddr = temps_saddr + P.num_temps * T * (4u * kLanes);
   const uint32_t tg = P.tg;
   const uint32_t lane_in_group = flat ? tid : tid % tg;
   const uint32_t group_in_cta = flat ? 0 : tid / tg;
 
   uint32_t sacc[1] = {0};
   uint32_t red_par = 0;
-  uint32_t seq = 0;
+  uint32_t ring_stage = 0, ring_parity = 0;
   Pos pos;
+  pos.gstep = 4u * tg;
+  pos.in_chunk0 = 4u * lane_in_group;
 
-  auto temp_addr = [&](uint32_t k, uint32_t g) { return temps_saddr + ((k * 2 + g) * T + tid) * 16u; };
+  auto temp_addr = [&](uint32_t k, uint32_t g) { return temps_saddr + ((k * kGranules + g) * T + tid) * 16u; };
   auto sreg_addr = [&](uint32_t k) { return sregs_saddr + (k * T + tid) * 4u; };
   auto lds32 = [](uint32_t a) {
     uint32_t v;
@@ -776,24 +719,17 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
       const uint32_t body_pc = P.sec[2 * ph + 1];
       const bool staged_body = ring && P.body_ring_mask[ph] != 0;
       for (uint32_t ch = ch_begin; ch < P.chunks; ch += ch_step) {
-        const uint32_t e_start = ch * P.chunk_elems;
-        pos.chunk_valid = min(P.chunk_elems, P.group_elems - e_start);
-#pragma unroll
-        for (int g = 0; g < 2; ++g) {
-          const uint32_t ic = (uint32_t)g * 4u * tg + 4u * lane_in_group;
-          const int32_t left = (int32_t)pos.chunk_valid - (int32_t)ic;
-          pos.in_chunk[g] = ic;
-          pos.nv[g] = left >= 4 ? 4 : (left > 0 ? left : 0);
-          pos.e0[g] = e_start + ic;
-          if (P.need_coords) split_enum(P, pos.nv[g] > 0 ? pos.e0[g] : 0u, pos.ec[g]);
-        }
+        pos.e_start = ch * P.chunk_elems;
+        pos.chunk_valid = min(P.chunk_elems, P.group_elems - pos.e_start);
         uint32_t stage_saddr = 0, empty_bar = 0;
         if (staged_body) {
-          const uint32_t stage = seq % S, use = seq / S;
-          ++seq;
-          stage_saddr = smem_base + kVmSmemStages + stage * P.stage_bytes;
-          empty_bar = smem_base + kVmSmemBarriers + 64 + 8 * stage;
-          mbar_wait(smem_base + kVmSmemBarriers + 8 * stage, use & 1u, 2);
+          stage_saddr = smem_base + kVmSmemStages + ring_stage * P.stage_bytes;
+          empty_bar = smem_base + kVmSmemBarriers + 64 + 8 * ring_stage;
+          mbar_wait(smem_base + kVmSmemBarriers + 8 * ring_stage, ring_parity, 2);
+          if (++ring_stage == S) {
+            ring_stage = 0;
+            ring_parity ^= 1u;
+          }
         }
         const bool full_tile = pos.chunk_valid == P.chunk_elems && pos.gvalid;
         for (uint32_t pc = body_pc;; ++pc) {
@@ -808,33 +744,29 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             case UH_LDR_F32: {
               slot = aux >> 2;
               if (!full_tile) goto fetch_generic;
-              const uint32_t a0 = stage_saddr + (arg << 4) + (pos.in_chunk[0] << 2);
-              const uint32_t a1 = a0 + ((4u * tg) << 2);
-              DV_BY_DEST(aux & 3u, DV_LDR32, a0, a1)
+              const uint32_t a0 = stage_saddr + (arg << 4) + (pos.in_chunk0 << 2), gs = pos.gstep << 2;
+              DV_BY_DEST(aux & 3u, DV_LDR32, a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)
               continue;
             }
             case UH_LDR_F16: {
               slot = aux >> 2;
               if (!full_tile) goto fetch_generic;
-              const uint32_t a0 = stage_saddr + (arg << 4) + (pos.in_chunk[0] << 1);
-              const uint32_t a1 = a0 + ((4u * tg) << 1);
-              DV_BY_DEST(aux & 3u, DV_LDR_F16, a0, a1)
+              const uint32_t a0 = stage_saddr + (arg << 4) + (pos.in_chunk0 << 1), gs = pos.gstep << 1;
+              DV_BY_DEST(aux & 3u, DV_LDR_F16, a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)
               continue;
             }
             case UH_LDR_BF16: {
               slot = aux >> 2;
               if (!full_tile) goto fetch_generic;
-              const uint32_t a0 = stage_saddr + (arg << 4) + (pos.in_chunk[0] << 1);
-              const uint32_t a1 = a0 + ((4u * tg) << 1);
-              DV_BY_DEST(aux & 3u, DV_LDR_BF16, a0, a1)
+              const uint32_t a0 = stage_saddr + (arg << 4) + (pos.in_chunk0 << 1), gs = pos.gstep << 1;
+              DV_BY_DEST(aux & 3u, DV_LDR_BF16, a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)
               continue;
             }
             case UH_LDR_U8: {
               slot = aux >> 2;
               if (!full_tile) goto fetch_generic;
-              const uint32_t a0 = stage_saddr + (arg << 4) + pos.in_chunk[0];
-              const uint32_t a1 = a0 + 4u * tg;
-              DV_BY_DEST(aux & 3u, DV_LDR_U8, a0, a1)
+              const uint32_t a0 = stage_saddr + (arg << 4) + pos.in_chunk0, gs = pos.gstep;
+              DV_BY_DEST(aux & 3u, DV_LDR_U8, a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)
               continue;
             }
             case UH_LDG: {
@@ -846,8 +778,8 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
               continue;
             }
             case UH_LDT: {
-              const uint32_t a0 = temp_addr(arg, 0), a1 = temp_addr(arg, 1);
-              DV_BY_DEST(aux & 3u, DV_LDR32, a0, a1)
+              const uint32_t a0 = temp_addr(arg, 0), gs = T * 16u;
+              DV_BY_DEST(aux & 3u, DV_LDR32, a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)
               continue;
             }
             case UH_LDS:
@@ -857,14 +789,16 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
               continue;
             }
             case UH_MOVA:
-              if ((aux & 3u) == UD_B) { asm volatile(DV_L8(DV_MOV_LANE, "vb", "va")); } else { asm volatile(DV_L8(DV_MOV_LANE, "vc", "va")); }
+              if ((aux & 3u) == UD_B) { asm volatile(DV_LN(DV_MOV_LANE, "vb", "va")); } else { asm volatile(DV_LN(DV_MOV_LANE, "vc", "va")); }
               continue;
-            case UH_STT:
-              asm volatile("st.shared.v4.b32 [%0], {va0,va1,va2,va3};\n\tst.shared.v4.b32 [%1], {va4,va5,va6,va7};" ::"r"(
-                             temp_addr(arg, 0)),
-                           "r"(temp_addr(arg, 1))
+            case UH_STT: {
+              const uint32_t a0 = temp_addr(arg, 0), gs = T * 16u;
+              asm volatile("st.shared.v4.b32 [%0], {va0,va1,va2,va3};\n\tst.shared.v4.b32 [%1], {va4,va5,va6,va7};\n\t"
+                           "st.shared.v4.b32 [%2], {va8,va9,va10,va11};\n\tst.shared.v4.b32 [%3], {va12,va13,va14,va15};" ::"r"(a0),
+                           "r"(a0 + gs), "r"(a0 + 2u * gs), "r"(a0 + 3u * gs)
                            : "memory");
               continue;
+            }
             // ---------------- arithmetic: acc <- op(acc, vb) / op(acc, scalar) ----------------
             DV_BIN_CASES(B_ADD, DV_BINV_LANE, DV_BINS_LANE, "add.f32")
             DV_BIN_CASES(B_SUB, DV_BINV_LANE, DV_BINS_LANE, "sub.f32")
@@ -879,16 +813,16 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             DV_BIN_CASES(B_MIN_I, DV_BINV_LANE, DV_BINS_LANE, "min.s32")
             DV_BIN_CASES(B_RSUB_I, DV_RBINV_LANE, DV_RBINS_LANE, "sub.s32")
             // float max / min keep the reference's `a > b ? a : b` / `a < b ? a : b`
-            case UH_BINV_FIRST + B_MAX: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_PICKV_LANE, "setp.gt.f32") "}"); continue;
-            case UH_BINV_FIRST + B_MIN: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_PICKV_LANE, "setp.lt.f32") "}"); continue;
+            case UH_BINV_FIRST + B_MAX: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_PICKV_LANE, "setp.gt.f32") "}"); continue;
+            case UH_BINV_FIRST + B_MIN: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_PICKV_LANE, "setp.lt.f32") "}"); continue;
             case UH_BINS_FIRST + B_MAX: {
               const uint32_t sv = (aux & 1u) ? lds32(sreg_addr(arg)) : DVMB_UIMM(u);
-              asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_PICKS_LANE, "setp.gt.f32") "}" ::"r"(sv));
+              asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_PICKS_LANE, "setp.gt.f32") "}" ::"r"(sv));
               continue;
             }
             case UH_BINS_FIRST + B_MIN: {
               const uint32_t sv = (aux & 1u) ? lds32(sreg_addr(arg)) : DVMB_UIMM(u);
-              asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_PICKS_LANE, "setp.lt.f32") "}" ::"r"(sv));
+              asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_PICKS_LANE, "setp.lt.f32") "}" ::"r"(sv));
               continue;
             }
             case UH_BINV_FIRST + B_POW:
@@ -908,15 +842,15 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
               continue;
             }
             // ---------------- unary ----------------
-            case UH_UN_FIRST + U_SQRT: asm volatile(DV_L8(DV_UN_LANE, "sqrt.rn.f32")); continue;
-            case UH_UN_FIRST + U_ABS: asm volatile(DV_L8(DV_UN_LANE, "abs.f32")); continue;
-            case UH_UN_FIRST + U_ROUND: asm volatile(DV_L8(DV_UN_LANE, "cvt.rni.f32.f32")); continue;
-            case UH_UN_FIRST + U_FLOOR: asm volatile(DV_L8(DV_UN_LANE, "cvt.rmi.f32.f32")); continue;
-            case UH_UN_FIRST + U_CEIL: asm volatile(DV_L8(DV_UN_LANE, "cvt.rpi.f32.f32")); continue;
-            case UH_UN_FIRST + U_TRUNC: asm volatile(DV_L8(DV_UN_LANE, "cvt.rzi.f32.f32")); continue;
-            case UH_UN_FIRST + U_ABS_I: asm volatile(DV_L8(DV_UN_LANE, "abs.s32")); continue;
+            case UH_UN_FIRST + U_SQRT: asm volatile(DV_LN(DV_UN_LANE, "sqrt.rn.f32")); continue;
+            case UH_UN_FIRST + U_ABS: asm volatile(DV_LN(DV_UN_LANE, "abs.f32")); continue;
+            case UH_UN_FIRST + U_ROUND: asm volatile(DV_LN(DV_UN_LANE, "cvt.rni.f32.f32")); continue;
+            case UH_UN_FIRST + U_FLOOR: asm volatile(DV_LN(DV_UN_LANE, "cvt.rmi.f32.f32")); continue;
+            case UH_UN_FIRST + U_CEIL: asm volatile(DV_LN(DV_UN_LANE, "cvt.rpi.f32.f32")); continue;
+            case UH_UN_FIRST + U_TRUNC: asm volatile(DV_LN(DV_UN_LANE, "cvt.rzi.f32.f32")); continue;
+            case UH_UN_FIRST + U_ABS_I: asm volatile(DV_LN(DV_UN_LANE, "abs.s32")); continue;
             case UH_UN_FIRST + U_ISFINITE:
-              asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_ISFIN_LANE, "") "}");
+              asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_ISFIN_LANE, "") "}");
               continue;
             case UH_UN_FIRST + U_LOG:
             case UH_UN_FIRST + U_EXP: {
@@ -933,9 +867,9 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
               continue;
             }
             case UH_UN_FIRST + U_NOP: continue;
-            case UH_RND_F16: asm volatile("{\n\t.reg .b16 h;\n\t" DV_L8(DV_RNDH_LANE, "") "}"); continue;
+            case UH_RND_F16: asm volatile("{\n\t.reg .b16 h;\n\t" DV_LN(DV_RNDH_LANE, "") "}"); continue;
             case UH_RND_BF16:
-              asm volatile("{\n\t.reg .b32 t;\n\t" DV_RNDB_PAIR("0", "1") DV_RNDB_PAIR("2", "3") DV_RNDB_PAIR("4", "5") DV_RNDB_PAIR("6", "7") "}");
+              asm volatile("{\n\t.reg .b32 t;\n\t" DV_PAIRS(DV_RNDB_PAIR, "") "}");
               continue;
             // ---------------- compare / select / convert ----------------
             case UH_CMP_F_V:
@@ -948,42 +882,53 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
                 DV_SPLAT("vb", sv)
               }
               switch ((aux & 7u) | (is_int ? 8u : 0u)) {
-                case C_EQ: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPF_LANE, "setp.eq.f32") "}"); break;
-                case C_NE: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPF_LANE, "setp.neu.f32") "}"); break;
-                case C_GT: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPF_LANE, "setp.gt.f32") "}"); break;
-                case C_GE: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPF_LANE, "setp.ge.f32") "}"); break;
-                case C_LT: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPF_LANE, "setp.lt.f32") "}"); break;
-                case C_LE: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPF_LANE, "setp.le.f32") "}"); break;
-                case 8 + C_EQ: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPI_LANE, "setp.eq.s32") "}"); break;
-                case 8 + C_NE: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPI_LANE, "setp.ne.s32") "}"); break;
-                case 8 + C_GT: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPI_LANE, "setp.gt.s32") "}"); break;
-                case 8 + C_GE: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPI_LANE, "setp.ge.s32") "}"); break;
-                case 8 + C_LT: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPI_LANE, "setp.lt.s32") "}"); break;
-                default: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_CMPI_LANE, "setp.le.s32") "}"); break;
+                case C_EQ: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_CMPF_LANE, "setp.eq.f32") "}"); break;
+                case C_NE: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_CMPF_LANE, "setp.neu.f32") "}"); break;
+                case C_GT: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_CMPF_LANE, "setp.gt.f32") "}"); break;
+                case C_GE: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_CMPF_LANE, "setp.ge.f32") "}"); break;
+                case C_LT: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_CMPF_LANE, "setp.lt.f32") "}"); break;
+                case C_LE: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_CMPF_LANE, "setp.le.f32") "}"); break;
+                case 8 + C_EQ: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_CMPI_LANE, "setp.eq.s32") "}"); break;
+                case 8 + C_NE: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_CMPI_LANE, "setp.ne.s32") "}"); break;
+                case 8 + C_GT: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_CMPI_LANE, "setp.gt.s32") "}"); break;
+                case 8 + C_GE: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_CMPI_LANE, "setp.ge.s32") "}"); break;
+                case 8 + C_LT: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_CMPI_LANE, "setp.lt.s32") "}"); break;
+                default: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_CMPI_LANE, "setp.le.s32") "}"); break;
               }
               continue;
             }
-            case UH_SEL_F: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_SEL_LANE, "setp.neu.f32 p, va", ", 0f00000000") "}"); continue;
-            case UH_SEL_I: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_SEL_LANE, "setp.ne.s32 p, va", ", 0") "}"); continue;
-            case UH_CVT_F2I: asm volatile(DV_L8(DV_UN_LANE, "cvt.rzi.s32.f32")); continue;
-            case UH_CVT_I2F: asm volatile(DV_L8(DV_UN_LANE, "cvt.rn.f32.s32")); continue;
-            case UH_CVT_NEZ_F: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_NEZ_LANE, "setp.neu.f32 p, va", ", 0f00000000") "}"); continue;
-            case UH_CVT_NEZ_I: asm volatile("{\n\t.reg .pred p;\n\t" DV_L8(DV_NEZ_LANE, "setp.ne.s32 p, va", ", 0") "}"); continue;
+            case UH_SEL_F: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_SEL_LANE, "setp.neu.f32 p, va", ", 0f00000000") "}"); continue;
+            case UH_SEL_I: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_SEL_LANE, "setp.ne.s32 p, va", ", 0") "}"); continue;
+            case UH_CVT_F2I: asm volatile(DV_LN(DV_UN_LANE, "cvt.rzi.s32.f32")); continue;
+            case UH_CVT_I2F: asm volatile(DV_LN(DV_UN_LANE, "cvt.rn.f32.s32")); continue;
+            case UH_CVT_NEZ_F: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_NEZ_LANE, "setp.neu.f32 p, va", ", 0f00000000") "}"); continue;
+            case UH_CVT_NEZ_I: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_NEZ_LANE, "setp.ne.s32 p, va", ", 0") "}"); continue;
             // ---------------- reductions ----------------
             case UH_RACC_SUM:
             case UH_RACC_MAX:
             case UH_RACC_MIN: {
               const uint32_t kind = uh - UH_RACC_SUM;
-              uint32_t x[kLanes];
-              DV_GET("va", x)
-              float v = red_identity(kind);
+              float v;
               if (full_tile) {
-#pragma unroll
-                for (int i = 0; i < kLanes; ++i) v = red_combine(kind, v, u2f(x[i]));
+                // reduce the 16 lanes in registers, in lane order
+                uint32_t r;
+                if (kind == R_SUM) {
+                  asm volatile("{\n\t.reg .b32 s;\n\tmov.b32 s, 0;\n\t" DV_LN(DV_SUMLANE, "") "mov.b32 %0, s;\n\t}" : "=r"(r));
+                } else if (kind == R_MAX) {
+                  asm volatile("{\n\t.reg .b32 s;\n\t.reg .pred p;\n\tmov.b32 s, 0xff800000;\n\t" DV_LN(DV_MAXLANE, "") "mov.b32 %0, s;\n\t}" : "=r"(r));
+                } else {
+                  asm volatile("{\n\t.reg .b32 s;\n\t.reg .pred p;\n\tmov.b32 s, 0x7f800000;\n\t" DV_LN(DV_MINLANE, "") "mov.b32 %0, s;\n\t}" : "=r"(r));
+                }
+                v = u2f(r);
               } else {
+                uint32_t x[kLanes];
+                DV_GET("va", x)
+                v = red_identity(kind);
 #pragma unroll
-                for (int i = 0; i < kLanes; ++i)
-                  if (pos.gvalid && (i & 3) < pos.nv[i >> 2]) v = red_combine(kind, v, u2f(x[i]));
+                for (int i = 0; i < kLanes; ++i) {
+                  const int32_t left = (int32_t)pos.chunk_valid - (int32_t)(pos.in_chunk0 + (uint32_t)(i >> 2) * pos.gstep);
+                  if (pos.gvalid && (i & 3) < left) v = red_combine(kind, v, u2f(x[i]));
+                }
               }
               set_part(arg & 3u, red_combine(kind, get_part(arg & 3u), v));
               continue;
@@ -992,9 +937,11 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             case UH_ST_F32: {
               if (!full_tile) goto store_generic;
               const TensorDesc &td = P.tensor[arg];
-              uint32_t *p0 = reinterpret_cast<uint32_t *>(td.ptr) + kept_offset(td, pos.k) + pos.e0[0];
-              asm volatile("st.global.v4.b32 [%0], {va0,va1,va2,va3};\n\tst.global.v4.b32 [%1], {va4,va5,va6,va7};" ::"l"(p0),
-                           "l"(p0 + 4u * tg)
+              uint32_t *p0 = reinterpret_cast<uint32_t *>(td.ptr) + kept_offset(td, pos.k) + pos.e_start + pos.in_chunk0;
+              const uint32_t gs = pos.gstep;
+              asm volatile("st.global.v4.b32 [%0], {va0,va1,va2,va3};\n\tst.global.v4.b32 [%1], {va4,va5,va6,va7};\n\t"
+                           "st.global.v4.b32 [%2], {va8,va9,va10,va11};\n\tst.global.v4.b32 [%3], {va12,va13,va14,va15};" ::"l"(p0),
+                           "l"(p0 + gs), "l"(p0 + 2u * gs), "l"(p0 + 3u * gs)
                            : "memory");
               continue;
             }
@@ -1002,20 +949,22 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             case UH_ST_BF16: {
               if (!full_tile) goto store_generic;
               const TensorDesc &td = P.tensor[arg];
-              unsigned short *p0 = reinterpret_cast<unsigned short *>(td.ptr) + kept_offset(td, pos.k) + pos.e0[0];
+              unsigned short *p0 = reinterpret_cast<unsigned short *>(td.ptr) + kept_offset(td, pos.k) + pos.e_start + pos.in_chunk0;
+              const uint32_t gs = pos.gstep;
+#define DV_ST16(CVT)                                                                                          \
+  asm volatile("{\n\t.reg .b32 t0, t1;\n\t"                                                                   \
+               CVT " t0, va1, va0;\n\t" CVT " t1, va3, va2;\n\tst.global.v2.b32 [%0], {t0,t1};\n\t"           \
+               CVT " t0, va5, va4;\n\t" CVT " t1, va7, va6;\n\tst.global.v2.b32 [%1], {t0,t1};\n\t"           \
+               CVT " t0, va9, va8;\n\t" CVT " t1, va11, va10;\n\tst.global.v2.b32 [%2], {t0,t1};\n\t"         \
+               CVT " t0, va13, va12;\n\t" CVT " t1, va15, va14;\n\tst.global.v2.b32 [%3], {t0,t1};\n\t}" ::"l"(p0), \
+               "l"(p0 + gs), "l"(p0 + 2u * gs), "l"(p0 + 3u * gs)                                            \
+               : "memory");
               if (uh == UH_ST_BF16) {
-                asm volatile("{\n\t.reg .b32 t0, t1;\n\t"
-                             "cvt.rn.bf16x2.f32 t0, va1, va0;\n\tcvt.rn.bf16x2.f32 t1, va3, va2;\n\tst.global.v2.b32 [%0], {t0,t1};\n\t"
-                             "cvt.rn.bf16x2.f32 t0, va5, va4;\n\tcvt.rn.bf16x2.f32 t1, va7, va6;\n\tst.global.v2.b32 [%1], {t0,t1};\n\t}" ::"l"(p0),
-                             "l"(p0 + 4u * tg)
-                             : "memory");
+                DV_ST16("cvt.rn.bf16x2.f32")
               } else {
-                asm volatile("{\n\t.reg .b32 t0, t1;\n\t"
-                             "cvt.rn.f16x2.f32 t0, va1, va0;\n\tcvt.rn.f16x2.f32 t1, va3, va2;\n\tst.global.v2.b32 [%0], {t0,t1};\n\t"
-                             "cvt.rn.f16x2.f32 t0, va5, va4;\n\tcvt.rn.f16x2.f32 t1, va7, va6;\n\tst.global.v2.b32 [%1], {t0,t1};\n\t}" ::"l"(p0),
-                             "l"(p0 + 4u * tg)
-                             : "memory");
+                DV_ST16("cvt.rn.f16x2.f32")
               }
+#undef DV_ST16
               continue;
             }
             case UH_ST_U8:
@@ -1036,9 +985,9 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
 }
 }  // namespace
 
-// Two register budgets of the same interpreter: up to 256 consumer threads with three CTAs per SM (the
+// Two register budgets of the same interpreter: up to 256 consumer threads with two CTAs per SM (the
 // streaming shapes), and up to 512 consumer threads (long reduction rows) with one.
-__global__ void __launch_bounds__(kVmFlatThreads + 32, 3) dvm_b200_vm_vector(const __grid_constant__ VmParam P) {
+__global__ void __launch_bounds__(kVmFlatThreads + 32, 2) dvm_b200_vm_vector(const __grid_constant__ VmParam P) {
   vm_vector_body(P);
 }
 __global__ void __launch_bounds__(kVmMaxThreads + 32, 1) dvm_b200_vm_vector_wide(const __grid_constant__ VmParam P) {

@@ -1,0 +1,109 @@
+// Inline-PTX building blocks of the vector interpreter's hidden register file.
+//
+// The vector state of a consumer thread - accumulator va0..15, operand registers vb0..15 / vc0..15 and the
+// reduction partials vp0..3 - is held in PTX registers that are declared once at the top of the kernel and
+// are named only inside inline assembly.  The C++ compiler therefore carries no vector value across the
+// dispatch loop (nothing to copy where the handlers' control flow merges) and ptxas keeps each register
+// in place for the whole kernel.  Lane i of a register belongs to granule i / 4 of the thread (four
+// consecutive elements); granule g sits 4 * tg elements after granule g - 1 inside a chunk.
+#ifndef DVM_B200_VM_VECTOR_REGS_H_
+#define DVM_B200_VM_VECTOR_REGS_H_
+
+#define DV_LN(M, ...)                                                                                             \
+  M(0, __VA_ARGS__) M(1, __VA_ARGS__) M(2, __VA_ARGS__) M(3, __VA_ARGS__) M(4, __VA_ARGS__) M(5, __VA_ARGS__)     \
+  M(6, __VA_ARGS__) M(7, __VA_ARGS__) M(8, __VA_ARGS__) M(9, __VA_ARGS__) M(10, __VA_ARGS__) M(11, __VA_ARGS__)   \
+  M(12, __VA_ARGS__) M(13, __VA_ARGS__) M(14, __VA_ARGS__) M(15, __VA_ARGS__)
+// pairs (a, b) of neighbouring lanes
+#define DV_PAIRS(M, ...)                                                                              \
+  M("0", "1", __VA_ARGS__) M("2", "3", __VA_ARGS__) M("4", "5", __VA_ARGS__) M("6", "7", __VA_ARGS__) \
+  M("8", "9", __VA_ARGS__) M("10", "11", __VA_ARGS__) M("12", "13", __VA_ARGS__) M("14", "15", __VA_ARGS__)
+
+#define DV_DECLARE ".reg .b32 va<16>, vb<16>, vc<16>, vp<4>;"
+
+// ---- lane templates ----------------------------------------------------------------------------------
+#define DV_BINV_LANE(i, OP) OP " va" #i ", va" #i ", vb" #i ";\n\t"
+#define DV_RBINV_LANE(i, OP) OP " va" #i ", vb" #i ", va" #i ";\n\t"
+#define DV_BINS_LANE(i, OP) OP " va" #i ", va" #i ", %0;\n\t"
+#define DV_RBINS_LANE(i, OP) OP " va" #i ", %0, va" #i ";\n\t"
+#define DV_PICKV_LANE(i, SETP) SETP " p, va" #i ", vb" #i ";\n\tselp.b32 va" #i ", va" #i ", vb" #i ", p;\n\t"
+#define DV_PICKS_LANE(i, SETP) SETP " p, va" #i ", %0;\n\tselp.b32 va" #i ", va" #i ", %0, p;\n\t"
+#define DV_UN_LANE(i, OP) OP " va" #i ", va" #i ";\n\t"
+#define DV_ISFIN_LANE(i, X) "testp.finite.f32 p, va" #i ";\n\tselp.b32 va" #i ", 0x3f800000, 0, p;\n\t"
+#define DV_RNDH_LANE(i, X) "cvt.rn.f16.f32 h, va" #i ";\n\tcvt.f32.f16 va" #i ", h;\n\t"
+#define DV_RNDB_PAIR(a, b, X) "cvt.rn.bf16x2.f32 t, va" b ", va" a ";\n\tshl.b32 va" a ", t, 16;\n\tand.b32 va" b ", t, 0xffff0000;\n\t"
+#define DV_CMPF_LANE(i, SETP) SETP " p, va" #i ", vb" #i ";\n\tselp.b32 va" #i ", 0x3f800000, 0, p;\n\t"
+#define DV_CMPI_LANE(i, SETP) SETP " p, va" #i ", vb" #i ";\n\tselp.b32 va" #i ", 1, 0, p;\n\t"
+#define DV_SEL_LANE(i, TEST, ZERO) TEST #i ZERO ";\n\tselp.b32 va" #i ", vb" #i ", vc" #i ", p;\n\t"
+#define DV_NEZ_LANE(i, TEST, ZERO) TEST #i ZERO ";\n\tselp.b32 va" #i ", 1, 0, p;\n\t"
+#define DV_MOV_LANE(i, D, S_) "mov.b32 " D #i ", " S_ #i ";\n\t"
+#define DV_GETLANE(i, R) "mov.b32 %" #i ", " R #i ";\n\t"
+#define DV_SETLANE(i, R) "mov.b32 " R #i ", %" #i ";\n\t"
+#define DV_SPLATLANE(i, R) "mov.b32 " R #i ", %0;\n\t"
+#define DV_SUMLANE(i, X) "add.f32 s, s, va" #i ";\n\t"
+#define DV_MAXLANE(i, X) "setp.gt.f32 p, s, va" #i ";\n\tselp.b32 s, s, va" #i ", p;\n\t"
+#define DV_MINLANE(i, X) "setp.lt.f32 p, s, va" #i ";\n\tselp.b32 s, s, va" #i ", p;\n\t"
+
+// ---- whole-register operations ---------------------------------------------------------------------------
+#define DV_OUT16(X)                                                                                                   \
+  "=r"(X[0]), "=r"(X[1]), "=r"(X[2]), "=r"(X[3]), "=r"(X[4]), "=r"(X[5]), "=r"(X[6]), "=r"(X[7]), "=r"(X[8]),         \
+    "=r"(X[9]), "=r"(X[10]), "=r"(X[11]), "=r"(X[12]), "=r"(X[13]), "=r"(X[14]), "=r"(X[15])
+#define DV_IN16(X)                                                                                                    \
+  "r"(X[0]), "r"(X[1]), "r"(X[2]), "r"(X[3]), "r"(X[4]), "r"(X[5]), "r"(X[6]), "r"(X[7]), "r"(X[8]), "r"(X[9]),       \
+    "r"(X[10]), "r"(X[11]), "r"(X[12]), "r"(X[13]), "r"(X[14]), "r"(X[15])
+#define DV_GET(R, X) asm volatile(DV_LN(DV_GETLANE, R) : DV_OUT16(X));
+#define DV_SET(R, X) asm volatile(DV_LN(DV_SETLANE, R)::DV_IN16(X));
+#define DV_SPLAT(R, V) asm volatile(DV_LN(DV_SPLATLANE, R)::"r"(V));
+
+// four 16-byte granules from shared memory (fp32 / int32 tensors, temporaries)
+#define DV_LDR32(R, A0, A1, A2, A3)                                                \
+  asm volatile("ld.shared.v4.b32 {" R "0," R "1," R "2," R "3}, [%0];\n\t"         \
+               "ld.shared.v4.b32 {" R "4," R "5," R "6," R "7}, [%1];\n\t"         \
+               "ld.shared.v4.b32 {" R "8," R "9," R "10," R "11}, [%2];\n\t"       \
+               "ld.shared.v4.b32 {" R "12," R "13," R "14," R "15}, [%3];" ::"r"(A0), \
+               "r"(A1), "r"(A2), "r"(A3)                                           \
+               : "memory");
+#define DV_LD16_RAW                                                                                       \
+  "ld.shared.v2.b32 {t0,t1}, [%0];\n\tld.shared.v2.b32 {t2,t3}, [%1];\n\tld.shared.v2.b32 {t4,t5}, [%2];\n\t" \
+  "ld.shared.v2.b32 {t6,t7}, [%3];\n\t"
+#define DV_BF16_PAIR(R, a, b, T) "shl.b32 " R a ", " T ", 16;\n\tand.b32 " R b ", " T ", 0xffff0000;\n\t"
+#define DV_LDR_BF16(R, A0, A1, A2, A3)                                                                          \
+  asm volatile("{\n\t.reg .b32 t0, t1, t2, t3, t4, t5, t6, t7;\n\t" DV_LD16_RAW                                 \
+               DV_BF16_PAIR(R, "0", "1", "t0") DV_BF16_PAIR(R, "2", "3", "t1") DV_BF16_PAIR(R, "4", "5", "t2")   \
+               DV_BF16_PAIR(R, "6", "7", "t3") DV_BF16_PAIR(R, "8", "9", "t4") DV_BF16_PAIR(R, "10", "11", "t5") \
+               DV_BF16_PAIR(R, "12", "13", "t6") DV_BF16_PAIR(R, "14", "15", "t7") "}" ::"r"(A0),                \
+               "r"(A1), "r"(A2), "r"(A3)                                                                        \
+               : "memory");
+#define DV_F16_PAIR(R, a, b, T) "mov.b32 {h0,h1}, " T ";\n\tcvt.f32.f16 " R a ", h0;\n\tcvt.f32.f16 " R b ", h1;\n\t"
+#define DV_LDR_F16(R, A0, A1, A2, A3)                                                                          \
+  asm volatile("{\n\t.reg .b32 t0, t1, t2, t3, t4, t5, t6, t7;\n\t.reg .b16 h0, h1;\n\t" DV_LD16_RAW            \
+               DV_F16_PAIR(R, "0", "1", "t0") DV_F16_PAIR(R, "2", "3", "t1") DV_F16_PAIR(R, "4", "5", "t2")     \
+               DV_F16_PAIR(R, "6", "7", "t3") DV_F16_PAIR(R, "8", "9", "t4") DV_F16_PAIR(R, "10", "11", "t5")   \
+               DV_F16_PAIR(R, "12", "13", "t6") DV_F16_PAIR(R, "14", "15", "t7") "}" ::"r"(A0),                 \
+               "r"(A1), "r"(A2), "r"(A3)                                                                       \
+               : "memory");
+#define DV_U8_QUAD(R, a, b, c, d, T) \
+  "and.b32 " R a ", " T ", 255;\n\tbfe.u32 " R b ", " T ", 8, 8;\n\tbfe.u32 " R c ", " T ", 16, 8;\n\tshr.u32 " R d ", " T ", 24;\n\t"
+#define DV_LDR_U8(R, A0, A1, A2, A3)                                                                             \
+  asm volatile("{\n\t.reg .b32 t0, t1, t2, t3;\n\tld.shared.b32 t0, [%0];\n\tld.shared.b32 t1, [%1];\n\t"         \
+               "ld.shared.b32 t2, [%2];\n\tld.shared.b32 t3, [%3];\n\t"                                          \
+               DV_U8_QUAD(R, "0", "1", "2", "3", "t0") DV_U8_QUAD(R, "4", "5", "6", "7", "t1")                   \
+               DV_U8_QUAD(R, "8", "9", "10", "11", "t2") DV_U8_QUAD(R, "12", "13", "14", "15", "t3") "}" ::"r"(A0), \
+               "r"(A1), "r"(A2), "r"(A3)                                                                         \
+               : "memory");
+
+// run FN("va" | "vb" | "vc", args...) for destination code D
+#define DV_BY_DEST(D, FN, ...)                \
+  {                                           \
+    const uint32_t d_ = (D);                  \
+    if (d_ == UD_ACC) { FN("va", __VA_ARGS__) } else if (d_ == UD_B) { FN("vb", __VA_ARGS__) } else { FN("vc", __VA_ARGS__) } \
+  }
+#define DV_BIN_CASES(K, VLANE, SLANE, OP)                                      \
+  case UH_BINV_FIRST + K: asm volatile(DV_LN(VLANE, OP)); continue;            \
+  case UH_BINS_FIRST + K: {                                                    \
+    const uint32_t sv_ = (aux & 1u) ? lds32(sreg_addr(arg)) : DVMB_UIMM(u);    \
+    asm volatile(DV_LN(SLANE, OP)::"r"(sv_));                                  \
+    continue;                                                                  \
+  }
+#define DV_CMP_ASM(LANE, SETP) asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(LANE, SETP) "}")
+
+#endif  // DVM_B200_VM_VECTOR_REGS_H_
