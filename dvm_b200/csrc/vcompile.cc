@@ -943,10 +943,6 @@ struct Compiler {
         stage_bytes += (P.chunk_elems * isz + 127u) & ~127u;
       }
     }
-    // a dense tensor whose chunks straddle runs of a multi-axis iteration is still contiguous; a granule-mode
-    // one needs coordinates for its bulk source too
-    if (stage_bytes != 0 && cenum.size() >= 2) P.need_coords = P.need_coords;
-
     // ---- shared memory plan
     P.num_temps = static_cast<uint32_t>(max_temp);
     P.num_sregs = static_cast<uint32_t>(max_sreg);

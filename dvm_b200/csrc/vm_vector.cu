@@ -553,27 +553,33 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
   }
 
   // =============================== producer warp ===============================
+  // Lane j of the producer warp owns ring stage j: it walks the same tile sequence as the consumers and
+  // serves every S-th tile, so the address arithmetic of S tiles proceeds in parallel.
   if (tid >= T) {
-    if (tid != T) return;
-    uint32_t pstage = 0, pparity = 0;
+    const uint32_t plane = tid - T;
+    if (plane >= S) return;
+    const uint32_t full = smem_base + kVmSmemBarriers + 8 * plane;
+    const uint32_t stage_saddr = smem_base + kVmSmemStages + plane * P.stage_bytes;
+    uint32_t next = plane, seq = 0, parity = 1;   // first wait on a fresh "empty" barrier passes at once
     for (uint32_t gb = gb_begin; gb < ngb; gb += gb_step) {
       uint32_t k[kMaxKept];
-      decompose_group(P, gb, k);   // groups_per_cta == 1 whenever the ring is on
+      bool have_k = false;
       for (uint32_t ph = 0; ph < P.num_body; ++ph) {
         const uint32_t mask = P.body_ring_mask[ph];
         if (mask == 0) continue;
-        for (uint32_t ch = ch_begin; ch < P.chunks; ch += ch_step) {
-          const uint32_t stage = pstage;
-          const uint32_t full = smem_base + kVmSmemBarriers + 8 * stage;
-          mbar_wait(full + 64, pparity ^ 1u, 1);
-          if (++pstage == S) {
-            pstage = 0;
-            pparity ^= 1u;
+        for (uint32_t ch = ch_begin; ch < P.chunks; ch += ch_step, ++seq) {
+          if (seq != next) continue;
+          next += S;
+          if (!have_k) {
+            decompose_group(P, gb, k);   // groups_per_cta == 1 whenever the ring is on
+            have_k = true;
           }
+          mbar_wait(full + 64, parity, 1);
+          parity ^= 1u;
           const uint32_t e_start = ch * P.chunk_elems;
           const uint32_t valid = min(P.chunk_elems, P.group_elems - e_start);
-          uint32_t c[kMaxEnum];
-          split_enum(P, e_start, c);
+          uint32_t c[kMaxEnum] = {0, 0, 0, e_start};
+          if (P.need_coords) split_enum(P, e_start, c);
           uint32_t total = 0;
           for (uint32_t m = mask; m; m &= m - 1) {
             const TensorDesc &td = P.tensor[__ffs(m) - 1];
@@ -584,7 +590,6 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             continue;
           }
           mbar_arrive_expect_tx(full, total);
-          const uint32_t stage_saddr = smem_base + kVmSmemStages + stage * P.stage_bytes;
           for (uint32_t m = mask; m; m &= m - 1) {
             const TensorDesc &td = P.tensor[__ffs(m) - 1];
             const uint32_t sh = item_shift(td.dtype);
