@@ -19,9 +19,12 @@ SOURCES = [
     "normalize.cc",
     "vcompile.cc",
     "vkernel.cc",
+    "partition.cc",
     "runtime.cu",
     "capi.cu",
     "vm_vector.cu",
+    "mm_tcgen05.cu",
+    "attn_tcgen05.cu",
 ]
 
 NVCC_FLAGS = [

@@ -13,6 +13,8 @@
 #include "../../include/dvm_c.h"
 #include "graph.h"
 #include "runtime.h"
+#include "vm_launch.h"
+#include "mm_launch.h"
 
 struct dvm_int_array {
   std::vector<int64_t> data;
@@ -253,7 +255,20 @@ int dvm_rt_memcpy_d2h(void *dst, const void *src, size_t bytes, void *stream) {
 int dvm_rt_memset(void *dst, int value, size_t bytes, void *stream) {
   return CudaCheck(cudaMemsetAsync(dst, value, bytes, static_cast<cudaStream_t>(stream)), "memset");
 }
-int dvm_rt_sync(void *stream) { return CudaCheck(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)), "stream sync"); }
+// Waits for the stream, then reads the status words of the device interpreters: a bounded device wait that
+// expired (the kernel then ran to its end with wrong results) is reported here as an error.
+int dvm_rt_sync(void *stream) {
+  int rc = CudaCheck(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)), "stream sync");
+  if (rc != 0) return rc;
+  const unsigned int sv = dvmb::ReadVectorStatus(), sm = dvmb::ReadMatMulStatus(), sa = dvmb::ReadAttentionStatus();
+  if ((sv | sm | sa) != 0) {
+    char buf[160];
+    snprintf(buf, sizeof(buf), "a bounded device wait expired (vector 0x%08x, matmul 0x%08x, attention 0x%08x)", sv, sm, sa);
+    g_error = buf;
+    return -1;
+  }
+  return 0;
+}
 void *dvm_rt_host_alloc(size_t bytes) {
   void *p = nullptr;
   if (CudaCheck(cudaMallocHost(&p, bytes ? bytes : 1), "cudaMallocHost") != 0) return nullptr;

@@ -13,6 +13,7 @@
 
 #include "../../include/dvm.h"
 #include "isa.h"
+#include "mm_launch.h"
 
 namespace dvm {
 
@@ -73,6 +74,10 @@ class NDObject {
   ScalarRef *scalar_ref = nullptr;
   IntArrayRef *shape_ref = nullptr;   // Load/Broadcast/Reshape target shape, Reduce dims (borrowed)
   void *addr = nullptr;               // Load/Store device address
+  // nodes the stage planner makes: a clone of a user's Load/Store (`origin` supplies the address) or a
+  // temporary in the kernel's workspace (`ws_off` >= 0, bytes from the workspace base)
+  NDObject *origin = nullptr;
+  int64_t ws_off = -1;
   // results of Normalize()
   Shape shape;
   IntArrayRef out_ref;                // view of `shape` handed out by Kernel::GetShape
@@ -91,9 +96,38 @@ struct VectorStage {
   uint64_t algo_bytes = 0;
 };
 
+// One launch of the tensor-core MatMul with its fused post-ops.
+struct MatMulStage {
+  dvmb::MmParam param;
+  NDObject *a = nullptr, *b = nullptr, *bias = nullptr;   // nodes whose addresses feed the operands
+  std::vector<NDObject *> slot_obj;     // post-fusion tensor slot -> node (nullptr for the product itself)
+  std::vector<uint64_t> bytecode;       // the post-fusion program (what Das() prints)
+  bool idle = false;
+  uint64_t algo_bytes = 0, flops = 0;
+};
+
+// One launch of the fused attention kernel.
+struct AttnStage {
+  dvmb::AttnParam param;
+  NDObject *q = nullptr, *k = nullptr, *v = nullptr, *o = nullptr;
+  bool idle = false;
+  uint64_t algo_bytes = 0, flops = 0;
+};
+
+enum StageKind : uint8_t { STAGE_VECTOR = 0, STAGE_MATMUL, STAGE_ATTENTION };
+
+struct Stage {
+  StageKind kind = STAGE_VECTOR;
+  VectorStage vec;
+  MatMulStage mm;
+  AttnStage attn;
+};
+
 class VKernel {
  public:
   VKernel(KernelType type, uint32_t flags) : type_(type), flags_(flags) {}
+  void ClearStages();
+  void PlanStages(const std::vector<NDObject *> &ops);   // partition.cc: general multi-stage planner
   ~VKernel();
 
   NDObject *NewNode(NodeKind kind, DataType dtype);
@@ -110,7 +144,8 @@ class VKernel {
   KernelType type_;
   uint32_t flags_;
   std::vector<NDObject *> nodes_;          // append (= topological) order
-  std::vector<VectorStage> stages_;
+  std::vector<std::unique_ptr<Stage>> stages_;
+  std::vector<NDObject *> synth_;          // planner-made nodes (clones, workspace temporaries), owned
   size_t ws_bytes_ = 0;
   void *workspace_ = nullptr;
   bool normalized_ = false;
@@ -122,6 +157,10 @@ class VKernel {
 
 // vcompile.cc
 bool CompileVectorStage(const std::vector<NDObject *> &ops, VectorStage *out, std::string *why);
+// Compile `ops` (a pseudo-load `mma_src` standing for the MatMul product, the fused elementwise ops, stores) into
+// the post-fusion program of a MatMul stage.
+bool CompileEpilogue(const std::vector<NDObject *> &ops, const NDObject *mma_src, MatMulStage *out, std::string *why);
+std::string DisassembleEpilogue(const MatMulStage &st);
 std::string DisassembleStage(const VectorStage &st);
 // Turn the stage's instruction words into the launch program (scalar sections + micro-ops) for the tensor
 // addresses now in the descriptors; called whenever addresses are (re)bound.

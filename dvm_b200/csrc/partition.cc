@@ -1,0 +1,565 @@
+// Stage planner: cuts an operator graph that does not fit one vector launch into a sequence of launches -
+// vector stages, MatMul stages with their fused post-ops, fused attention - handing values from one stage to
+// the next through the kernel's workspace in global memory.
+//
+// Plays the role of the reference's graph splitter (_SplitKernel::Append/Split/Exchange/AppendCube/BuildKernel,
+// src/xkernel.cc:1960-2301) and of the mix kernel's post-fusion collection (MixKernelBase::Append,
+// src/xkernel.cc:157-209).  The policy is different: a vector area keeps growing for as long as the vector
+// compiler can still fuse it into one launch (reductions followed by elementwise ops stay together), a MatMul
+// takes every following elementwise op of its own shape into its epilogue, and the
+// MatMul -> softmax -> MatMul pattern becomes one attention launch.
+#include <algorithm>
+#include <cstring>
+#include <string>
+#include <unordered_map>
+#include <unordered_set>
+
+#include "graph.h"
+#include "runtime.h"
+
+namespace dvm {
+
+uint32_t EncodeScalarRefNow(const ScalarRef *ref, DataType dtype);
+
+namespace {
+
+bool IsElementwise(NodeKind k) {
+  switch (k) {
+    case N_UNARY:
+    case N_BINARY:
+    case N_BINARY_S:
+    case N_COMPARE:
+    case N_COMPARE_S:
+    case N_SELECT:
+    case N_CAST:
+    case N_COPY: return true;
+    default: return false;
+  }
+}
+
+// Ops that never get a stage of their own: consumers re-create them from what they read.
+bool IsLazy(const NDObject *n) { return n->kind == N_LOAD || n->kind == N_BROADCAST_S || n->kind == N_BROADCAST; }
+
+struct Planner {
+  VKernel *vk;
+  const std::vector<NDObject *> &ops;
+  std::unordered_map<const NDObject *, std::vector<NDObject *>> users;
+  std::unordered_map<const NDObject *, int> pos;
+  std::unordered_set<const NDObject *> done;
+  // where a computed value lives in memory once its stage has run: a planner-made Load
+  std::unordered_map<const NDObject *, NDObject *> mem;
+  std::vector<NDObject *> cur;   // open vector area, program order
+  std::unordered_set<const NDObject *> in_cur;
+  size_t ws_top = 0;
+
+  Planner(VKernel *k, const std::vector<NDObject *> &o) : vk(k), ops(o) {
+    for (size_t i = 0; i < ops.size(); ++i) {
+      pos[ops[i]] = static_cast<int>(i);
+      for (int j = 0; j < 3; ++j)
+        if (ops[i]->in[j]) users[ops[i]->in[j]].push_back(ops[i]);
+    }
+  }
+
+  NDObject *Synth(const NDObject *like) {
+    auto n = new NDObject(*like);
+    n->origin = nullptr;
+    n->ws_off = -1;
+    vk->synth_.push_back(n);
+    return n;
+  }
+
+  NDObject *SynthLoad(const NDObject *value, const Shape &shape) {
+    auto n = new NDObject();
+    n->kind = N_LOAD;
+    n->dtype = value->dtype;
+    n->shape = shape;
+    n->id = value->id;
+    vk->synth_.push_back(n);
+    return n;
+  }
+
+  size_t AllocWs(const NDObject *value) {
+    const size_t bytes = static_cast<size_t>(value->shape.numel()) * ItemSize(value->dtype);
+    const size_t off = ws_top;
+    ws_top = (ws_top + bytes + 255) & ~static_cast<size_t>(255);
+    return off;
+  }
+
+  // True when `n` is already addressable in global memory (a user's Load, a view of one, a stored temporary).
+  bool InMemory(const NDObject *n) const { return n->kind == N_LOAD || mem.count(n) != 0; }
+
+  // A Load node (planner-made) reading value `n`, which must be InMemory().
+  NDObject *MemLoad(const NDObject *n) {
+    if (n->kind == N_LOAD) {
+      NDObject *c = Synth(n);
+      c->origin = n->origin ? n->origin : const_cast<NDObject *>(n);
+      c->ws_off = n->ws_off;
+      return c;
+    }
+    NDObject *where = mem.at(n);
+    NDObject *c = Synth(where);
+    c->origin = where->origin;
+    c->ws_off = where->ws_off;
+    return c;
+  }
+
+  // ---- building the op list of one stage out of clones ---------------------------------------------------
+  struct Build {
+    std::vector<NDObject *> list;
+    std::unordered_map<const NDObject *, NDObject *> clone;
+    std::vector<std::pair<const NDObject *, NDObject *>> temps;   // (value, planner-made store) to publish in `mem`
+  };
+
+  NDObject *InputFor(Build &b, NDObject *v) {
+    auto it = b.clone.find(v);
+    if (it != b.clone.end()) return it->second;
+    NDObject *c = nullptr;
+    if (InMemory(v)) {
+      c = MemLoad(v);
+    } else if (v->kind == N_BROADCAST_S) {
+      c = Synth(v);
+      c->in[0] = nullptr;
+    } else if (v->kind == N_BROADCAST) {
+      NDObject *src = InputFor(b, v->in[0]);
+      c = Synth(v);
+      c->in[0] = src;
+    } else {
+      DvmException("stage planner: a value is used before the stage that computes it");
+    }
+    b.clone[v] = c;
+    b.list.push_back(c);
+    return c;
+  }
+
+  NDObject *CloneOp(Build &b, NDObject *n) {
+    NDObject *in[3] = {nullptr, nullptr, nullptr};
+    for (int j = 0; j < 3; ++j)
+      if (n->in[j]) in[j] = InputFor(b, n->in[j]);
+    NDObject *c = Synth(n);
+    for (int j = 0; j < 3; ++j) c->in[j] = in[j];
+    if (n->kind == N_STORE) c->origin = n;
+    b.clone[n] = c;
+    b.list.push_back(c);
+    return c;
+  }
+
+  bool HasOutsideUser(const NDObject *n, const std::unordered_set<const NDObject *> &area) const {
+    auto it = users.find(n);
+    if (it == users.end()) return false;
+    for (auto u : it->second) {
+      if (u->kind == N_STORE && !IsLazy(n)) continue;   // stores travel with their value
+      if (u->kind == N_BROADCAST) {
+        if (HasOutsideUser(u, area)) return true;
+        continue;
+      }
+      if (!area.count(u)) return true;
+    }
+    return false;
+  }
+
+  // Clone `nodes` (program order) with their stores; values read outside `area` get a workspace store.
+  // With `commit` the workspace is really allocated.
+  void CloneArea(Build &b, const std::vector<NDObject *> &nodes, const std::unordered_set<const NDObject *> &area,
+                 bool commit) {
+    for (auto n : nodes) {
+      NDObject *c = b.clone.count(n) ? b.clone.at(n) : CloneOp(b, n);
+      if (n->kind == N_STORE) continue;
+      auto it = users.find(n);
+      if (it != users.end())
+        for (auto u : it->second)
+          if (u->kind == N_STORE && !area.count(u)) {
+            CloneOp(b, u);
+            if (commit) done.insert(u);
+          }
+      if (HasOutsideUser(n, area)) {
+        auto st = new NDObject();
+        vk->synth_.push_back(st);
+        st->kind = N_STORE;
+        st->dtype = n->dtype;
+        st->shape = n->shape;
+        st->in[0] = c;
+        st->id = n->id;
+        st->ws_off = commit ? static_cast<int64_t>(AllocWs(n)) : 0;
+        b.list.push_back(st);
+        b.temps.emplace_back(n, st);
+      }
+    }
+  }
+
+  void Publish(const Build &b) {
+    for (auto &t : b.temps) {
+      NDObject *ld = SynthLoad(t.first, t.first->shape);
+      ld->ws_off = t.second->ws_off;
+      mem[t.first] = ld;
+    }
+  }
+
+  // ---- vector areas ----------------------------------------------------------------------------------------
+  bool TryVector(const std::vector<NDObject *> &nodes, bool commit, std::string *why) {
+    std::unordered_set<const NDObject *> area(nodes.begin(), nodes.end());
+    const size_t synth_mark = vk->synth_.size();
+    const size_t ws_mark = ws_top;
+    Build b;
+    CloneArea(b, nodes, area, commit);
+    auto st = std::make_unique<Stage>();
+    st->kind = STAGE_VECTOR;
+    const bool ok = CompileVectorStage(b.list, &st->vec, why);
+    if (ok && commit) {
+      Publish(b);
+      vk->stages_.push_back(std::move(st));
+      return true;
+    }
+    // a trial (or a failure): drop the clones again
+    for (size_t i = synth_mark; i < vk->synth_.size(); ++i) delete vk->synth_[i];
+    vk->synth_.resize(synth_mark);
+    ws_top = ws_mark;
+    return ok;
+  }
+
+  void CloseCur() {
+    if (cur.empty()) return;
+    std::string why;
+    if (!TryVector(cur, true, &why)) {
+      std::string msg = "cannot compile a vector stage: " + why;
+      DvmException(msg.c_str());
+    }
+    for (auto n : cur) done.insert(n);
+    cur.clear();
+    in_cur.clear();
+  }
+
+  void AddVector(NDObject *n) {
+    cur.push_back(n);
+    std::string why;
+    if (TryVector(cur, false, &why)) {
+      in_cur.insert(n);
+      return;
+    }
+    cur.pop_back();
+    CloseCur();
+    cur.push_back(n);
+    if (!TryVector(cur, false, &why)) {
+      std::string msg = "op #" + std::to_string(n->id) + " cannot run on this backend: " + why;
+      DvmException(msg.c_str());
+    }
+    in_cur.insert(n);
+  }
+
+  // Make sure `v` is addressable in memory before a tensor-core stage reads it.
+  void RequireInMemory(NDObject *v, const char *what) {
+    if (InMemory(v)) return;
+    if (in_cur.count(v)) {
+      CloseCur();
+      if (InMemory(v)) return;
+    }
+    std::string msg = std::string(what) + " must be a tensor in memory (a Load or a computed value)";
+    DvmException(msg.c_str());
+  }
+
+  // ---- MatMul stages ---------------------------------------------------------------------------------------
+  static void BatchOf(const Shape &s, uint32_t *b0, uint32_t *b1) {
+    *b1 = s.rank >= 3 ? static_cast<uint32_t>(s.d[s.rank - 3]) : 1u;
+    *b0 = s.rank >= 4 ? static_cast<uint32_t>(s.d[s.rank - 4]) : 1u;
+  }
+
+  bool ExternalOk(const NDObject *x, const NDObject *m) const {
+    if (x->kind == N_LOAD || x->kind == N_BROADCAST_S) return true;
+    if (x->kind == N_BROADCAST) return ExternalOk(x->in[0], m);
+    if (mem.count(x)) return true;
+    return in_cur.count(x) != 0;   // computed before the MatMul; its area is closed first
+  }
+
+  void PlaceMatMul(NDObject *m) {
+    for (int j = 0; j < 3; ++j)
+      if (m->in[j]) RequireInMemory(m->in[j], j == 2 ? "MatMul bias" : "MatMul operand");
+    // post-fusion area: elementwise ops of the product's own shape that depend on it
+    std::vector<NDObject *> area_nodes;
+    std::unordered_set<const NDObject *> area{m};
+    for (size_t i = pos.at(m) + 1; i < ops.size(); ++i) {
+      NDObject *v = ops[i];
+      if (done.count(v) || !IsElementwise(v->kind) || !(v->shape == m->shape)) continue;
+      bool touches = false, ok = true;
+      for (int j = 0; j < 3; ++j) {
+        if (!v->in[j]) continue;
+        if (area.count(v->in[j])) {
+          touches = true;
+        } else if (!ExternalOk(v->in[j], m)) {
+          ok = false;
+        }
+      }
+      if (!touches || !ok) continue;
+      area.insert(v);
+      area_nodes.push_back(v);
+    }
+    for (int attempt = 0; attempt < 2; ++attempt) {
+      if (attempt == 1) {
+        area_nodes.clear();
+        area = {m};
+      }
+      bool need_close = false;
+      for (auto v : area_nodes)
+        for (int j = 0; j < 3; ++j) {
+          const NDObject *x = v->in[j];
+          while (x && x->kind == N_BROADCAST) x = x->in[0];
+          if (x && in_cur.count(x)) need_close = true;
+        }
+      if (need_close) CloseCur();
+      const size_t synth_mark = vk->synth_.size();
+      const size_t ws_mark = ws_top;
+      Build b;
+      NDObject *src = SynthLoad(m, m->shape);
+      b.clone[m] = src;
+      b.list.push_back(src);
+      std::vector<NDObject *> nodes{m};
+      nodes.insert(nodes.end(), area_nodes.begin(), area_nodes.end());
+      CloneArea(b, nodes, area, true);
+      auto st = std::make_unique<Stage>();
+      st->kind = STAGE_MATMUL;
+      std::memset(&st->mm.param, 0, sizeof(st->mm.param));
+      std::string why;
+      if (!CompileEpilogue(b.list, src, &st->mm, &why)) {
+        for (size_t i = synth_mark; i < vk->synth_.size(); ++i) delete vk->synth_[i];
+        vk->synth_.resize(synth_mark);
+        ws_top = ws_mark;
+        if (attempt == 1) {
+          std::string msg = "cannot compile the MatMul epilogue: " + why;
+          DvmException(msg.c_str());
+        }
+        continue;
+      }
+      FillMatMul(m, &st->mm);
+      Publish(b);
+      vk->stages_.push_back(std::move(st));
+      done.insert(m);
+      for (auto v : area_nodes) {
+        done.insert(v);
+      }
+      for (auto v : nodes) {
+        auto it = users.find(v);
+        if (it != users.end())
+          for (auto u : it->second)
+            if (u->kind == N_STORE) done.insert(u);
+      }
+      return;
+    }
+  }
+
+  void FillMatMul(NDObject *m, MatMulStage *mm) {
+    dvmb::MmParam &P = mm->param;
+    const Shape &a = m->in[0]->shape, &bs = m->in[1]->shape, &o = m->shape;
+    P.M = static_cast<uint32_t>(o.d[o.rank - 2]);
+    P.N = static_cast<uint32_t>(o.d[o.rank - 1]);
+    P.K = static_cast<uint32_t>(m->trans_a ? a.d[a.rank - 2] : a.d[a.rank - 1]);
+    BatchOf(o, &P.batch0, &P.batch1);
+    P.a_mmajor = m->trans_a ? 1 : 0;
+    P.b_kmajor = m->trans_b ? 1 : 0;
+    P.in_dtype = static_cast<uint32_t>(m->dtype);
+    uint32_t ab0, ab1, bb0, bb1;
+    BatchOf(a, &ab0, &ab1);
+    BatchOf(bs, &bb0, &bb1);
+    P.a_mul1 = ab1 > 1 ? 1 : 0;
+    P.a_mul0 = ab0 > 1 ? ab1 : 0;
+    P.a_batches = ab0 * ab1;
+    P.b_mul1 = bb1 > 1 ? 1 : 0;
+    P.b_mul0 = bb0 > 1 ? bb1 : 0;
+    P.b_batches = bb0 * bb1;
+    mm->a = MemLoad(m->in[0]);
+    mm->b = MemLoad(m->in[1]);
+    mm->bias = m->in[2] ? MemLoad(m->in[2]) : nullptr;
+    if (m->in[2]) {
+      P.bias_dtype = static_cast<uint32_t>(m->in[2]->dtype);
+      if (m->in[2]->shape.numel() != static_cast<int64_t>(P.N)) DvmException("MatMul bias must hold one value per result column");
+    }
+    mm->idle = o.numel() == 0;
+    mm->flops = 2ull * P.M * P.N * P.K * P.batch0 * P.batch1;
+    mm->algo_bytes += static_cast<uint64_t>(a.numel() + bs.numel()) * 2 + (m->in[2] ? m->in[2]->shape.numel() * ItemSize(m->in[2]->dtype) : 0);
+  }
+
+  // ---- attention -------------------------------------------------------------------------------------------
+  std::vector<NDObject *> RealUsers(const NDObject *n) const {
+    auto it = users.find(n);
+    return it == users.end() ? std::vector<NDObject *>() : it->second;
+  }
+
+  static bool ReducesLastDimKeep(const NDObject *r, int kind) {
+    if (r->kind != N_REDUCE || r->sub != kind || !r->keepdims || r->shape_ref == nullptr || r->shape_ref->size != 1) return false;
+    int64_t d = r->shape_ref->data[0];
+    if (d < 0) d += r->in[0]->shape.rank;
+    return d == r->in[0]->shape.rank - 1;
+  }
+
+  bool TryAttention(NDObject *m1) {
+    if (m1->trans_a || !m1->trans_b || m1->in[2]) return false;
+    const Shape &qs = m1->in[0]->shape, &ks = m1->in[1]->shape;
+    if (qs.rank != ks.rank || qs.rank < 2 || qs.rank > 4) return false;
+    for (int i = 0; i < qs.rank - 2; ++i)
+      if (qs.d[i] != ks.d[i]) return false;
+    std::vector<NDObject *> chain{m1};
+    NDObject *x = m1;
+    uint32_t scale_bits = 0x3f800000u, round2 = 0;
+    auto single_user = [&](NDObject *n) -> NDObject * {
+      auto u = RealUsers(n);
+      return u.size() == 1 ? u[0] : nullptr;
+    };
+    NDObject *u = single_user(x);
+    if (u && u->kind == N_BINARY_S && u->sub == SB_MUL) {
+      scale_bits = u->scalar_ref ? EncodeScalarRefNow(u->scalar_ref, u->dtype) : u->scalar_bits;
+      round2 = (u->dtype == kFloat16 || u->dtype == kBFloat16) ? 1 : 0;
+      chain.push_back(u);
+      x = u;
+      u = single_user(x);
+    }
+    if (u && u->kind == N_CAST && u->dtype == kFloat32) {
+      chain.push_back(u);
+      x = u;
+    }
+    if (x->dtype != kFloat32) return false;
+    if (x->kind == N_CAST) {
+      // an fp32 scale after the cast
+      NDObject *u2 = single_user(x);
+      if (u2 && u2->kind == N_BINARY_S && u2->sub == SB_MUL && scale_bits == 0x3f800000u) {
+        scale_bits = u2->scalar_ref ? EncodeScalarRefNow(u2->scalar_ref, u2->dtype) : u2->scalar_bits;
+        chain.push_back(u2);
+        x = u2;
+      }
+    }
+    auto ux = RealUsers(x);
+    if (ux.size() != 2) return false;
+    NDObject *rmax = nullptr, *sub = nullptr;
+    for (auto c : ux) {
+      if (ReducesLastDimKeep(c, kMax)) rmax = c;
+      if (c->kind == N_BINARY && c->sub == kSub && c->in[0] == x) sub = c;
+    }
+    if (!rmax || !sub || sub->in[1] != rmax || RealUsers(rmax).size() != 1) return false;
+    NDObject *e = single_user(sub);
+    if (!e || e->kind != N_UNARY || e->sub != kExp) return false;
+    auto ue = RealUsers(e);
+    if (ue.size() != 2) return false;
+    NDObject *rsum = nullptr, *div = nullptr;
+    for (auto c : ue) {
+      if (ReducesLastDimKeep(c, kSum)) rsum = c;
+      if (c->kind == N_BINARY && c->sub == kDiv && c->in[0] == e) div = c;
+    }
+    if (!rsum || !div || div->in[1] != rsum || RealUsers(rsum).size() != 1) return false;
+    NDObject *p = single_user(div);
+    if (!p) return false;
+    chain.insert(chain.end(), {rmax, sub, e, rsum, div});
+    if (p->kind == N_CAST && p->dtype == m1->dtype) {
+      chain.push_back(p);
+      NDObject *m2 = single_user(p);
+      if (!m2) return false;
+      p = m2;
+    } else {
+      return false;
+    }
+    NDObject *m2 = p;
+    if (m2->kind != N_MATMUL || m2->in[0] != chain.back() || m2->trans_a || m2->trans_b || m2->in[2]) return false;
+    const Shape &vs = m2->in[1]->shape;
+    if (vs.rank != ks.rank) return false;
+    for (int i = 0; i < ks.rank - 1; ++i)
+      if (vs.d[i] != ks.d[i]) return false;
+    if (vs.d[vs.rank - 1] != qs.d[qs.rank - 1]) return false;
+    dvmb::AttnParam ap;
+    std::memset(&ap, 0, sizeof(ap));
+    uint32_t b0, b1;
+    BatchOf(qs, &b0, &b1);
+    ap.batch = b0 * b1;
+    ap.sq = static_cast<uint32_t>(qs.d[qs.rank - 2]);
+    ap.skv = static_cast<uint32_t>(ks.d[ks.rank - 2]);
+    ap.d = static_cast<uint32_t>(qs.d[qs.rank - 1]);
+    ap.dtype = static_cast<uint32_t>(m1->dtype);
+    ap.scale_bits = scale_bits;
+    ap.scale_first = round2;
+    if (!dvmb::AttentionSupported(ap)) return false;
+    // every operand must be addressable; only then commit
+    NDObject *ins[3] = {m1->in[0], m1->in[1], m2->in[1]};
+    for (auto v : ins)
+      if (!InMemory(v) && !in_cur.count(v)) return false;
+    for (auto v : ins) RequireInMemory(v, "attention operand");
+    auto st = std::make_unique<Stage>();
+    st->kind = STAGE_ATTENTION;
+    st->attn.param = ap;
+    st->attn.q = MemLoad(ins[0]);
+    st->attn.k = MemLoad(ins[1]);
+    st->attn.v = MemLoad(ins[2]);
+    auto outs = RealUsers(m2);
+    if (outs.size() == 1 && outs[0]->kind == N_STORE) {
+      NDObject *o = Synth(outs[0]);
+      o->origin = outs[0];
+      o->in[0] = nullptr;
+      st->attn.o = o;
+      done.insert(outs[0]);
+    } else {
+      NDObject *o = SynthLoad(m2, m2->shape);
+      o->ws_off = static_cast<int64_t>(AllocWs(m2));
+      st->attn.o = o;
+      mem[m2] = o;
+    }
+    st->attn.idle = m2->shape.numel() == 0;
+    st->attn.flops = 4ull * ap.batch * ap.sq * ap.skv * ap.d;
+    st->attn.algo_bytes = 2ull * ap.batch * (2ull * ap.sq * ap.d + 2ull * ap.skv * ap.d);
+    vk->stages_.push_back(std::move(st));
+    for (auto n : chain) done.insert(n);
+    done.insert(m2);
+    return true;
+  }
+
+  // ---- driver ------------------------------------------------------------------------------------------------
+  void Run() {
+    for (auto n : ops) {
+      if (done.count(n)) continue;
+      switch (n->kind) {
+        case N_LOAD:
+        case N_BROADCAST_S:
+        case N_BROADCAST: break;
+        case N_STORE: {
+          NDObject *v = n->in[0];
+          if (IsLazy(v) || mem.count(v)) AddVector(n);   // a plain copy of something already in memory
+          break;
+        }
+        case N_RESHAPE: {
+          NDObject *src = n->in[0];
+          if (in_cur.count(src)) {
+            // try the reshape inside the open area (it can stay there when it only adds or drops unit dims)
+            cur.push_back(n);
+            std::string why;
+            if (TryVector(cur, false, &why)) {
+              in_cur.insert(n);
+              break;
+            }
+            cur.pop_back();
+            CloseCur();
+          }
+          if (!InMemory(src)) {
+            if (src->kind == N_BROADCAST || src->kind == N_BROADCAST_S) {
+              AddVector(n);
+              break;
+            }
+            DvmException("stage planner: reshape of a value that is not in memory");
+          }
+          // a view of memory: same bytes, new shape
+          NDObject *ld = MemLoad(src);
+          ld->shape = n->shape;
+          mem[n] = ld;
+          done.insert(n);
+          break;
+        }
+        case N_MATMUL:
+          if (!TryAttention(n)) PlaceMatMul(n);
+          break;
+        default: AddVector(n); break;
+      }
+    }
+    CloseCur();
+  }
+};
+
+}  // namespace
+
+void VKernel::PlanStages(const std::vector<NDObject *> &ops) {
+  Planner p(this, ops);
+  p.Run();
+  ws_bytes_ = p.ws_top;
+}
+
+}  // namespace dvm

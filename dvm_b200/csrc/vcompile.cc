@@ -65,6 +65,8 @@ struct Compiler {
   std::vector<NDObject *> slot_nodes;
   int max_temp = 0, max_sreg = 0;
   uint32_t body_tensor_mask[kMaxPhases] = {0, 0, 0, 0};   // tensor slots each BODY reads as operands
+  bool epilogue = false;           // compiling the post-fusion program of a MatMul stage
+  const NDObject *mma_src = nullptr;
 
   void NoteTensorUse(int section, int slot) {
     if (section & 1) body_tensor_mask[section / 2] |= 1u << slot;
@@ -198,6 +200,7 @@ struct Compiler {
     bool first = true;
     for (auto n : ops) {
       if (n->kind != N_REDUCE) continue;
+      if (epilogue) throw Fail{"reduction inside a MatMul epilogue"};
       const NDObject *src = n->in[0];
       const Info &si = I(src);
       bool mine[kMaxRank] = {false};
@@ -226,7 +229,7 @@ struct Compiler {
         if (fi.asz[a] == 1) continue;
         if (!has_reduce || reduced[a]) varies = true;
       }
-      fi.scalar_space = !varies;
+      fi.scalar_space = epilogue ? false : !varies;
       // canonical value
       fi.canon = n;
       switch (n->kind) {
@@ -300,6 +303,7 @@ struct Compiler {
         slot_nodes.push_back(n);
       }
     if (slot_nodes.size() > static_cast<size_t>(kMaxTensors)) throw Fail{"more than 16 tensors in one stage"};
+    if (epilogue) return;
     kept_axes.clear();
     enum_axes.clear();
     for (int a = 0; a < R; ++a) {
@@ -984,7 +988,48 @@ struct Compiler {
     if (num_body == 0) out->grid = 1;
   }
 
-  void Run() {
+  // ---- step 5 (MatMul epilogue): tensor table addressed by (batch0, batch1, row, column) -------------
+  void FillEpilogue(MatMulStage *mm) {
+    MmParam &P = mm->param;
+    if (R < 2 || R > 4) throw Fail{"MatMul result rank outside 2..4"};
+    if (slot_nodes.size() > static_cast<size_t>(kMmMaxEpiTensors)) throw Fail{"more than 8 tensors in a MatMul epilogue"};
+    if (max_temp > kNumTemps) throw Fail{"out of vector registers"};
+    // scalar sections must be empty
+    for (int p = 0; p <= num_body; ++p)
+      if (DVMB_OPC(code[out->bsec[2 * p]]) != OP_END) throw Fail{"group-constant work inside a MatMul epilogue"};
+    if (num_body != 1) throw Fail{"MatMul epilogue needs exactly one body"};
+    mm->bytecode.clear();
+    for (size_t pc = out->bsec[1];; ++pc) {
+      mm->bytecode.push_back(code[pc]);
+      if (DVMB_OPC(code[pc]) == OP_END) break;
+    }
+    if (mm->bytecode.size() > static_cast<size_t>(kMmMaxEpilogueWords)) throw Fail{"MatMul epilogue exceeds the program capacity"};
+    std::memcpy(P.epilogue, mm->bytecode.data(), mm->bytecode.size() * sizeof(uint64_t));
+    P.n_tensors = static_cast<uint32_t>(slot_nodes.size());
+    P.num_temps = static_cast<uint32_t>(max_temp);
+    P.mma_slot = 0xffffffffu;
+    mm->slot_obj.assign(slot_nodes.begin(), slot_nodes.end());
+    mm->algo_bytes = 0;
+    for (size_t s = 0; s < slot_nodes.size(); ++s) {
+      NDObject *n = slot_nodes[s];
+      EpiTensor &t = P.tensor[s];
+      std::memset(&t, 0, sizeof(t));
+      t.dtype = static_cast<uint32_t>(n->dtype);
+      if (n->dtype == kInt64) throw Fail{"int64 tensors are not supported"};
+      if (n == mma_src) {
+        P.mma_slot = static_cast<uint32_t>(s);
+        mm->slot_obj[s] = nullptr;
+        continue;
+      }
+      mm->algo_bytes += static_cast<uint64_t>(n->shape.numel()) * ItemSize(n->dtype);
+      t.sn = static_cast<int32_t>(StrideOn(n, R - 1));
+      t.sm = StrideOn(n, R - 2);
+      t.sb1 = R >= 3 ? StrideOn(n, R - 3) : 0;
+      t.sb0 = R >= 4 ? StrideOn(n, R - 4) : 0;
+    }
+  }
+
+  void Run(MatMulStage *mm = nullptr) {
     for (size_t i = 0; i < ops.size(); ++i) index[ops[i]] = static_cast<int>(i);
     info.assign(ops.size(), Info());
     for (auto n : ops)
@@ -993,7 +1038,11 @@ struct Compiler {
     Classify();
     Geometry();
     Emit();
-    Fill();
+    if (epilogue) {
+      FillEpilogue(mm);
+    } else {
+      Fill();
+    }
   }
 };
 
@@ -1013,6 +1062,20 @@ bool CompileVectorStage(const std::vector<NDObject *> &ops, VectorStage *out, st
     std::memset(&out->param, 0, sizeof(out->param));
     Compiler c(ops, out);
     c.Run();
+    return true;
+  } catch (const Fail &f) {
+    if (why) *why = f.why;
+    return false;
+  }
+}
+
+bool CompileEpilogue(const std::vector<NDObject *> &ops, const NDObject *mma_src, MatMulStage *mm, std::string *why) {
+  try {
+    VectorStage scratch;
+    Compiler c(ops, &scratch);
+    c.epilogue = true;
+    c.mma_src = mma_src;
+    c.Run(mm);
     return true;
   } catch (const Fail &f) {
     if (why) *why = f.why;
@@ -1121,6 +1184,74 @@ void LowerStage(VectorStage *st) {
   P.n_code = n;
 }
 
+
+namespace {
+// One line of disassembly per instruction word; `dt(slot)` / `ptr(slot)` describe the tensor table.
+template <class DT, class PT>
+std::string InsnLine(uint32_t pc, uint64_t w, DT dt, PT ptr) {
+  using namespace dvmb;
+  char buf[256];
+  auto operand_text = [&](uint32_t kind, uint32_t idx, uint32_t imm) -> std::string {
+    char b[64];
+    switch (kind) {
+      case K_TENSOR:
+        snprintf(b, sizeof(b), "load.%s(0x%llx)", DTypeName(static_cast<DataType>(dt(idx))),
+                 static_cast<unsigned long long>(ptr(idx)));
+        break;
+      case K_TEMP: snprintf(b, sizeof(b), "v%u", idx); break;
+      case K_SREG: snprintf(b, sizeof(b), "s%u", idx); break;
+      case K_IMM: snprintf(b, sizeof(b), "#0x%08x", imm); break;
+      default: snprintf(b, sizeof(b), "acc"); break;
+    }
+    return b;
+  };
+  auto operand = [&](uint64_t ww) -> std::string { return operand_text(DVMB_OKIND(ww), DVMB_OIDX(ww), DVMB_IMM(ww)); };
+  static const char *rnd_names[] = {"", ".rn_f16", ".rn_bf16", ""};
+  const uint32_t opc = DVMB_OPC(w), sub = DVMB_SUB(w), dst = DVMB_DST(w);
+  const bool sc = DVMB_SCALAR(w);
+  const char *acc = sc ? "sacc" : "acc";
+  const char *rp = sc ? "s" : "v";
+  const char *ty = DVMB_ISINT(w) ? "int32" : "fp32";
+  switch (opc) {
+    case OP_END: snprintf(buf, sizeof(buf), "  %u: end\n", pc); break;
+    case OP_ST:
+      snprintf(buf, sizeof(buf), "  %u: store.%s 0x%llx, %s // t%u\n", pc, DTypeName(static_cast<DataType>(dt(sub))),
+               static_cast<unsigned long long>(ptr(sub)), acc, sub);
+      break;
+    case OP_COPY: snprintf(buf, sizeof(buf), "  %u: copy %s, %s\n", pc, acc, operand(w).c_str()); break;
+    case OP_MOV: snprintf(buf, sizeof(buf), "  %u: mov %s%u, %s\n", pc, rp, dst, acc); break;
+    case OP_UN:
+      snprintf(buf, sizeof(buf), "  %u: %s.%s%s %s, %s\n", pc, kUnNames[sub], sub == U_ABS_I ? "int32" : "fp32",
+               rnd_names[DVMB_RND(w)], acc, acc);
+      break;
+    case OP_BIN:
+      snprintf(buf, sizeof(buf), "  %u: %s.%s%s %s, %s, %s\n", pc, kBinNames[sub], sub >= B_ADD_I ? "int32" : "fp32",
+               rnd_names[DVMB_RND(w)], acc, acc, operand(w).c_str());
+      break;
+    case OP_CMP:
+      snprintf(buf, sizeof(buf), "  %u: Cmp%s.%s %s, %s, %s\n", pc, kCmpNames[sub], ty, acc, acc, operand(w).c_str());
+      break;
+    case OP_SEL: {
+      std::string second = operand_text(sub >> 4, sub & 15u, 0);
+      if (dst & 1u) {
+        snprintf(buf, sizeof(buf), "  %u: Select.%s %s, %s ? %s : %s\n", pc, ty, acc, acc, second.c_str(), operand(w).c_str());
+      } else {
+        snprintf(buf, sizeof(buf), "  %u: Select.%s %s, %s ? %s : %s\n", pc, ty, acc, acc, operand(w).c_str(), second.c_str());
+      }
+      break;
+    }
+    case OP_CVT:
+      snprintf(buf, sizeof(buf), "  %u: Cvt%s%s %s, %s\n", pc, kCvtNames[sub], rnd_names[DVMB_RND(w)], acc, acc);
+      break;
+    case OP_RACC: snprintf(buf, sizeof(buf), "  %u: Reduce%s.acc p%u, acc\n", pc, kRedNames[sub >> 4], sub & 3u); break;
+    case OP_RFIN: snprintf(buf, sizeof(buf), "  %u: Reduce%s.fin sacc, p%u // bar\n", pc, kRedNames[sub >> 4], sub & 3u); break;
+    case OP_RINIT: snprintf(buf, sizeof(buf), "  %u: Reduce%s.init p%u\n", pc, kRedNames[sub >> 4], sub & 3u); break;
+    default: snprintf(buf, sizeof(buf), "  %u: ?\n", pc); break;
+  }
+  return buf;
+}
+}  // namespace
+
 // Text form of a stage's bytecode (the counterpart of the reference's disassembler, src/code.cc:1093-1498).
 // One line per instruction: "<pc>: <Name>.<type> <dst>, <operands>"; loads and stores print as
 // "load.<dtype> <dst>, <gm address>" / "store.<dtype> <gm address>, acc".
@@ -1144,74 +1275,53 @@ std::string DisassembleStage(const VectorStage &st) {
              static_cast<unsigned long long>(td.ptr));
     o += buf;
   }
-  auto operand_text = [&](uint32_t kind, uint32_t idx, uint32_t imm) -> std::string {
-    char b[64];
-    switch (kind) {
-      case K_TENSOR:
-        snprintf(b, sizeof(b), "load.%s(0x%llx)", DTypeName(static_cast<DataType>(P.tensor[idx].dtype)),
-                 static_cast<unsigned long long>(P.tensor[idx].ptr));
-        break;
-      case K_TEMP: snprintf(b, sizeof(b), "v%u", idx); break;
-      case K_SREG: snprintf(b, sizeof(b), "s%u", idx); break;
-      case K_IMM: snprintf(b, sizeof(b), "#0x%08x", imm); break;
-      default: snprintf(b, sizeof(b), "acc"); break;
-    }
-    return b;
-  };
-  auto operand = [&](uint64_t w) -> std::string { return operand_text(DVMB_OKIND(w), DVMB_OIDX(w), DVMB_IMM(w)); };
-  static const char *rnd_names[] = {"", ".rn_f16", ".rn_bf16", ""};
+  auto dt = [&](uint32_t slot) { return static_cast<uint32_t>(P.tensor[slot].dtype); };
+  auto ptr = [&](uint32_t slot) { return P.tensor[slot].ptr; };
   for (uint32_t pc = 0; pc < st.bytecode.size(); ++pc) {
     for (uint32_t sidx = 0; sidx <= 2 * P.num_body; ++sidx)
       if (st.bsec[sidx] == pc) {
         snprintf(buf, sizeof(buf), " %s_%u:\n", (sidx & 1) ? "body" : "pro", sidx / 2);
         o += buf;
       }
-    const uint64_t w = st.bytecode[pc];
-    const uint32_t opc = DVMB_OPC(w), sub = DVMB_SUB(w), dst = DVMB_DST(w);
-    const bool sc = DVMB_SCALAR(w);
-    const char *acc = sc ? "sacc" : "acc";
-    const char *rp = sc ? "s" : "v";
-    const char *ty = DVMB_ISINT(w) ? "int32" : "fp32";
-    switch (opc) {
-      case OP_END: snprintf(buf, sizeof(buf), "  %u: end\n", pc); break;
-      case OP_ST: {
-        const TensorDesc &td = P.tensor[sub];
-        snprintf(buf, sizeof(buf), "  %u: store.%s 0x%llx, %s // t%u\n", pc, DTypeName(static_cast<DataType>(td.dtype)),
-                 static_cast<unsigned long long>(td.ptr), acc, sub);
-        break;
-      }
-      case OP_COPY: snprintf(buf, sizeof(buf), "  %u: copy %s, %s\n", pc, acc, operand(w).c_str()); break;
-      case OP_MOV: snprintf(buf, sizeof(buf), "  %u: mov %s%u, %s\n", pc, rp, dst, acc); break;
-      case OP_UN:
-        snprintf(buf, sizeof(buf), "  %u: %s.%s%s %s, %s\n", pc, kUnNames[sub], sub == U_ABS_I ? "int32" : "fp32",
-                 rnd_names[DVMB_RND(w)], acc, acc);
-        break;
-      case OP_BIN:
-        snprintf(buf, sizeof(buf), "  %u: %s.%s%s %s, %s, %s\n", pc, kBinNames[sub], sub >= B_ADD_I ? "int32" : "fp32",
-                 rnd_names[DVMB_RND(w)], acc, acc, operand(w).c_str());
-        break;
-      case OP_CMP:
-        snprintf(buf, sizeof(buf), "  %u: Cmp%s.%s %s, %s, %s\n", pc, kCmpNames[sub], ty, acc, acc, operand(w).c_str());
-        break;
-      case OP_SEL: {
-        std::string second = operand_text(sub >> 4, sub & 15u, 0);
-        if (dst & 1u) {
-          snprintf(buf, sizeof(buf), "  %u: Select.%s %s, %s ? %s : %s\n", pc, ty, acc, acc, second.c_str(), operand(w).c_str());
-        } else {
-          snprintf(buf, sizeof(buf), "  %u: Select.%s %s, %s ? %s : %s\n", pc, ty, acc, acc, operand(w).c_str(), second.c_str());
-        }
-        break;
-      }
-      case OP_CVT:
-        snprintf(buf, sizeof(buf), "  %u: Cvt%s%s %s, %s\n", pc, kCvtNames[sub], rnd_names[DVMB_RND(w)], acc, acc);
-        break;
-      case OP_RACC: snprintf(buf, sizeof(buf), "  %u: Reduce%s.acc p%u, acc\n", pc, kRedNames[sub >> 4], sub & 3u); break;
-      case OP_RFIN: snprintf(buf, sizeof(buf), "  %u: Reduce%s.fin sacc, p%u // bar\n", pc, kRedNames[sub >> 4], sub & 3u); break;
-      case OP_RINIT: snprintf(buf, sizeof(buf), "  %u: Reduce%s.init p%u\n", pc, kRedNames[sub >> 4], sub & 3u); break;
-      default: snprintf(buf, sizeof(buf), "  %u: ?\n", pc); break;
+    o += InsnLine(pc, st.bytecode[pc], dt, ptr);
+  }
+  o += "}\n";
+  return o;
+}
+
+}  // namespace dvm
+
+namespace dvm {
+
+// Text form of a MatMul stage: the MatMul itself, then its post-fusion program.
+std::string DisassembleEpilogue(const MatMulStage &st) {
+  using namespace dvmb;
+  const MmParam &P = st.param;
+  std::string o;
+  char buf[320];
+  snprintf(buf, sizeof(buf),
+           "mmain.sm100(batch=%ux%u, m=%u, n=%u, k=%u, a=%s, b=%s, %s, engine=%s) {\n", P.batch0, P.batch1, P.M, P.N, P.K,
+           P.a_mmajor ? "[k,m]" : "[m,k]", P.b_kmajor ? "[n,k]" : "[k,n]", DTypeName(static_cast<DataType>(P.in_dtype)),
+           MatMulUsesTensorCores(P) ? "tcgen05" : "simt");
+  o += buf;
+  snprintf(buf, sizeof(buf), "  matmul.%s acc, load(0x%llx), load(0x%llx)%s\n", DTypeName(static_cast<DataType>(P.in_dtype)),
+           static_cast<unsigned long long>(P.a_ptr), static_cast<unsigned long long>(P.b_ptr), P.bias_ptr ? ", bias" : "");
+  o += buf;
+  for (uint32_t t = 0; t < P.n_tensors; ++t) {
+    const EpiTensor &td = P.tensor[t];
+    if (t == P.mma_slot) {
+      snprintf(buf, sizeof(buf), "  // t%u: the product\n", t);
+    } else {
+      snprintf(buf, sizeof(buf), "  // t%u: %s strides=[%lld,%lld,%lld,%d] @0x%llx\n", t, DTypeName(static_cast<DataType>(td.dtype)),
+               static_cast<long long>(td.sb0), static_cast<long long>(td.sb1), static_cast<long long>(td.sm), td.sn,
+               static_cast<unsigned long long>(td.ptr));
     }
     o += buf;
   }
+  auto dt = [&](uint32_t slot) { return P.tensor[slot].dtype; };
+  auto ptr = [&](uint32_t slot) { return P.tensor[slot].ptr; };
+  o += " post:\n";
+  for (uint32_t pc = 0; pc < st.bytecode.size(); ++pc) o += InsnLine(pc, st.bytecode[pc], dt, ptr);
   o += "}\n";
   return o;
 }

@@ -8,11 +8,26 @@
 #include "graph.h"
 #include "runtime.h"
 #include "vm_launch.h"
+#include "mm_launch.h"
 
 namespace dvm {
 
 VKernel::~VKernel() {
+  ClearStages();
   for (auto n : nodes_) delete n;
+}
+
+void VKernel::ClearStages() {
+  stages_.clear();
+  for (auto n : synth_) delete n;
+  synth_.clear();
+}
+
+// Device address of a load/store node: a workspace temporary, a clone of a user's node, or the node itself.
+static void *AddrOf(const NDObject *n, void *workspace) {
+  if (n->ws_off >= 0) return workspace ? static_cast<char *>(workspace) + n->ws_off : nullptr;
+  if (n->origin) return n->origin->addr;
+  return n->addr;
 }
 
 NDObject *VKernel::NewNode(NodeKind kind, DataType dtype) {
@@ -50,20 +65,26 @@ static std::vector<NDObject *> LiveOps(const std::vector<NDObject *> &nodes) {
 
 size_t VKernel::Compile() {
   if (!normalized_) Normalize();
-  stages_.clear();
+  ClearStages();
   ws_bytes_ = 0;
   std::vector<NDObject *> ops = LiveOps(nodes_);
   if (ops.empty()) {
     compiled_ = true;
     return 0;
   }
-  stages_.emplace_back();
-  std::string why;
-  if (!CompileVectorStage(ops, &stages_.back(), &why)) {
-    stages_.clear();
-    std::string msg = "cannot fuse this graph into one launch: " + why;
-    DvmException(msg.c_str());
+  bool has_matmul = false;
+  for (auto n : ops) has_matmul |= n->kind == N_MATMUL;
+  if (!has_matmul) {
+    // the common case: the whole graph is one launch of the vector interpreter
+    auto st = std::make_unique<Stage>();
+    std::string why;
+    if (CompileVectorStage(ops, &st->vec, &why)) {
+      stages_.push_back(std::move(st));
+      compiled_ = true;
+      return 0;
+    }
   }
+  PlanStages(ops);
   compiled_ = true;
   return ws_bytes_;
 }
@@ -71,12 +92,30 @@ size_t VKernel::Compile() {
 void VKernel::Bind(const RelocEntry *relocs, size_t n, void *workspace) {
   workspace_ = workspace;
   for (size_t i = 0; i < n; ++i) relocs[i].io->addr = relocs[i].addr;
-  for (auto &st : stages_) {
+  for (auto &stp : stages_) {
+    if (stp->kind == STAGE_MATMUL) {
+      MatMulStage &mm = stp->mm;
+      mm.param.a_ptr = reinterpret_cast<uint64_t>(AddrOf(mm.a, workspace));
+      mm.param.b_ptr = reinterpret_cast<uint64_t>(AddrOf(mm.b, workspace));
+      mm.param.bias_ptr = mm.bias ? reinterpret_cast<uint64_t>(AddrOf(mm.bias, workspace)) : 0;
+      for (size_t s = 0; s < mm.slot_obj.size(); ++s)
+        if (mm.slot_obj[s]) mm.param.tensor[s].ptr = reinterpret_cast<uint64_t>(AddrOf(mm.slot_obj[s], workspace));
+      continue;
+    }
+    if (stp->kind == STAGE_ATTENTION) {
+      AttnStage &at = stp->attn;
+      at.param.q_ptr = reinterpret_cast<uint64_t>(AddrOf(at.q, workspace));
+      at.param.k_ptr = reinterpret_cast<uint64_t>(AddrOf(at.k, workspace));
+      at.param.v_ptr = reinterpret_cast<uint64_t>(AddrOf(at.v, workspace));
+      at.param.o_ptr = reinterpret_cast<uint64_t>(AddrOf(at.o, workspace));
+      continue;
+    }
+    VectorStage &st = stp->vec;
     dvmb::VmParam &P = st.param;
     uint32_t staged = 0;
     for (size_t s = 0; s < st.slot_obj.size(); ++s) {
       dvmb::TensorDesc &td = P.tensor[s];
-      td.ptr = reinterpret_cast<uint64_t>(st.slot_obj[s]->addr);
+      td.ptr = reinterpret_cast<uint64_t>(AddrOf(st.slot_obj[s], workspace));
       const uint64_t align = 4ull * ItemSize(static_cast<DataType>(td.dtype));
       td.vec_ok = (td.layout_vec && td.ptr != 0 && td.ptr % align == 0) ? 1 : 0;
       // a tensor planned for bulk staging keeps its ring slot only if its address is 16-byte aligned
@@ -94,7 +133,27 @@ void VKernel::Bind(const RelocEntry *relocs, size_t n, void *workspace) {
 int VKernel::Launch(void *stream) {
   if (!compiled_) DvmException("Launch before CodeGen");
   dvmb::Runtime::Get().EnsureInit();
-  for (auto &st : stages_) {
+  for (auto &stp : stages_) {
+    if (stp->kind == STAGE_MATMUL) {
+      MatMulStage &mm = stp->mm;
+      if (mm.idle) continue;
+      if (mm.param.a_ptr == 0 || mm.param.b_ptr == 0) DvmException("Launch with an unbound tensor address");
+      for (size_t s = 0; s < mm.slot_obj.size(); ++s)
+        if (mm.slot_obj[s] && mm.param.tensor[s].ptr == 0) DvmException("Launch with an unbound tensor address");
+      int err = dvmb::LaunchMatMul(mm.param, stream);
+      if (err != 0) return err;
+      continue;
+    }
+    if (stp->kind == STAGE_ATTENTION) {
+      AttnStage &at = stp->attn;
+      if (at.idle) continue;
+      if (!at.param.q_ptr || !at.param.k_ptr || !at.param.v_ptr || !at.param.o_ptr)
+        DvmException("Launch with an unbound tensor address");
+      int err = dvmb::LaunchAttention(at.param, stream);
+      if (err != 0) return err;
+      continue;
+    }
+    VectorStage &st = stp->vec;
     if (st.idle) continue;
     for (size_t s = 0; s < st.slot_obj.size(); ++s)
       if (st.param.tensor[s].ptr == 0) DvmException("Launch with an unbound tensor address");
@@ -179,7 +238,21 @@ const char *VKernel::Dump() {
 const char *VKernel::Das() {
   if (!compiled_) Compile();
   text_.clear();
-  for (auto &st : stages_) text_ += DisassembleStage(st);
+  for (auto &st : stages_) {
+    if (st->kind == STAGE_MATMUL) {
+      text_ += DisassembleEpilogue(st->mm);
+    } else if (st->kind == STAGE_ATTENTION) {
+      const dvmb::AttnParam &a = st->attn.param;
+      char buf[256];
+      snprintf(buf, sizeof(buf), "amain.sm100(batch=%u, sq=%u, skv=%u, d=%u, %s) {\n  attention 0x%llx, load(0x%llx), load(0x%llx), load(0x%llx)\n}\n",
+               a.batch, a.sq, a.skv, a.d, DTypeName(static_cast<DataType>(a.dtype)), static_cast<unsigned long long>(a.o_ptr),
+               static_cast<unsigned long long>(a.q_ptr), static_cast<unsigned long long>(a.k_ptr),
+               static_cast<unsigned long long>(a.v_ptr));
+      text_ += buf;
+    } else {
+      text_ += DisassembleStage(st->vec);
+    }
+  }
   return text_.c_str();
 }
 
@@ -188,10 +261,20 @@ const char *VKernel::Inspect() {
   char buf[256];
   text_.clear();
   int i = 0;
-  for (auto &st : stages_) {
-    snprintf(buf, sizeof(buf), "stage %d: grid=%u threads=%u code_words=%u tensors=%u algorithmic_bytes=%llu%s\n", i++,
-             st.grid, st.threads, st.param.n_code, st.param.n_tensors, static_cast<unsigned long long>(st.algo_bytes),
-             st.idle ? " (idle: zero-size domain)" : "");
+  for (auto &stp : stages_) {
+    if (stp->kind == STAGE_MATMUL) {
+      snprintf(buf, sizeof(buf), "stage %d: matmul flops=%llu algorithmic_bytes=%llu%s\n", i++,
+               static_cast<unsigned long long>(stp->mm.flops), static_cast<unsigned long long>(stp->mm.algo_bytes),
+               stp->mm.idle ? " (idle: zero-size result)" : "");
+    } else if (stp->kind == STAGE_ATTENTION) {
+      snprintf(buf, sizeof(buf), "stage %d: attention flops=%llu algorithmic_bytes=%llu\n", i++,
+               static_cast<unsigned long long>(stp->attn.flops), static_cast<unsigned long long>(stp->attn.algo_bytes));
+    } else {
+      VectorStage &st = stp->vec;
+      snprintf(buf, sizeof(buf), "stage %d: grid=%u threads=%u code_words=%u tensors=%u algorithmic_bytes=%llu%s\n", i++,
+               st.grid, st.threads, st.param.n_code, st.param.n_tensors, static_cast<unsigned long long>(st.algo_bytes),
+               st.idle ? " (idle: zero-size domain)" : "");
+    }
     text_ += buf;
   }
   snprintf(buf, sizeof(buf), "workspace_bytes=%zu last_jit_us=%.2f\n", ws_bytes_, last_jit_us_);

@@ -39,6 +39,10 @@ class Tester(PyKernel):
         dtype_id = _normalize_dtype(shape_arr.dtype if dtype is None else dtype)
         if dtype_id == DataType.bfloat16 and (_BF16 is None or shape_arr.dtype != _BF16):
             shape_arr = PyKernel.convert_to_bf16(shape_arr)
+        elif dtype_id == DataType.float16 and shape_arr.dtype != np.float16:
+            shape_arr = shape_arr.astype(np.float16)
+        elif dtype_id == DataType.float32 and shape_arr.dtype != np.float32:
+            shape_arr = shape_arr.astype(np.float32)
         op = PyKernel.load(self, list(shape_arr.shape), dtype_id)
         self.input(op, shape_arr)
         return op

@@ -129,6 +129,8 @@ class OracleKernel:
         dt = dtype_of_array(array) if dtype is None else int(dtype)
         if dt == BF16 and array.dtype == np.float32:
             array = round_bf16(array)
+        if dt == F16 and array.dtype == np.float32:
+            array = round_f16(array)
         return OVal(dt, from_storage(dt, array))
 
     def store(self, x, dtype=None):
