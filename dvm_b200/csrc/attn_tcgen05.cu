@@ -1,7 +1,389 @@
-// placeholder
+// Fused attention  O = softmax(scale * Q K^T) V  on the sm_100a tensor cores.
+//
+// The reference has no attention operator: its example (examples/03_attention.py:31-52) builds
+// MatMul -> scale -> softmax -> MatMul from API ops, which its splitter turns into several kernels with the full
+// score matrix in global memory (src/xkernel.cc:1980-2119).  Here the stage planner recognises that pattern and
+// runs it as one launch with the scores kept on chip (online softmax over key/value tiles).
+//
+// One CTA owns 256 query rows of one (batch, head): two tiles of 128 rows that take turns on the tensor core.
+//   warp 0      TMA producer: Q once, then K and V tiles of 128 keys through a 3-slot ring
+//   warp 1      MMA issuer: S_g = Q_g K^T into TMEM, O_g += P_g V; the two row tiles g = 0, 1 are interleaved so
+//               that one tile's softmax overlaps the other tile's MMAs
+//   warps 2-5   softmax of tile 0 (one thread per row), warps 6-9 softmax of tile 1: scores TMEM -> registers,
+//               running maximum, exp2, row sum, P as bf16/fp16 into shared memory (the A operand of P V)
+// The running maximum is only raised when a row's new maximum exceeds it by more than 8 (a factor e^8 of
+// head-room in P); only then is the accumulator in TMEM rescaled, which for typical inputs happens once.
+// Rounding follows the graph: the score is rounded to the operand type (the MatMul result), scaled (rounded
+// again when the scale was applied in the operand type), softmax in fp32, P rounded to the operand type.
+// Every mbarrier wait is bounded; on expiry a status word is set and the kernel runs to its end.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstring>
+
 #include "mm_launch.h"
+#include "sm100_sync.cuh"
+#include "vm_ops.cuh"
+
 namespace dvmb {
-int LaunchAttention(const AttnParam &, void *) { return -1; }
-bool AttentionSupported(const AttnParam &) { return false; }
-unsigned int ReadAttentionStatus() { return 0; }
+
+__device__ unsigned int g_attn_status = 0;
+
+namespace {
+
+constexpr uint32_t kTileQ = 128, kTileKV = 128;
+constexpr uint32_t kQTilesPerCta = 2;
+constexpr uint32_t kRingSlots = 3;
+constexpr uint32_t kTileBytes = 128 * 128 * 2;      // one [128 x 128] 16-bit tile (two 64-column halves)
+constexpr uint32_t kHalfBytes = 128 * 64 * 2;       // [128 rows x 64 elements], 128-byte swizzled rows
+constexpr uint32_t kThreads = 64 + 2 * 128;
+constexpr uint32_t kHeader = 1024;
+// shared memory: header | Q0 Q1 | P0 P1 | ring[3]
+constexpr uint32_t kOffQ = kHeader, kOffP = kOffQ + 2 * kTileBytes, kOffRing = kOffP + 2 * kTileBytes;
+constexpr uint32_t kSmemBytes = kOffRing + kRingSlots * kTileBytes + 1024;
+// tensor memory columns: S0 S1 O0 O1
+constexpr uint32_t kTmemS = 0, kTmemO = 256, kTmemCols = 512;
+constexpr float kRescaleThreshold = 8.0f;
+
+struct AttnMaps {
+  CUtensorMap q, k, v;
+};
+
+// barrier offsets inside the header
+constexpr uint32_t kBarQ = 0, kBarKvFull = 8, kBarKvEmpty = 32, kBarSFull = 56, kBarSFree = 72, kBarPReady = 88,
+                   kBarPvDone = 104, kTmemSlot = 128;
+
+__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+    "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+    "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+    "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+    "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+    "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+    "r"(r[31])
+    : "memory");
 }
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ uint32_t pack_pair(uint32_t dtype, float lo, float hi) {
+  if (dtype == T_BF16) return pack_bf16x2(lo, hi);
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+}  // namespace
+
+__global__ void __launch_bounds__(kThreads, 1) dvm_b200_attention(const __grid_constant__ AttnParam P,
+                                                                  const __grid_constant__ AttnMaps maps) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t *smem = smem_raw + (base - raw_addr);
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const uint32_t dhalves = P.d / 64;                  // 64-element halves of the head dimension (1 or 2)
+  const uint32_t qblocks = (P.sq + kTileQ * kQTilesPerCta - 1) / (kTileQ * kQTilesPerCta);
+  const uint32_t bz = blockIdx.x / qblocks, qb = blockIdx.x - bz * qblocks;
+  const uint32_t q_row0 = qb * kTileQ * kQTilesPerCta;
+  const uint32_t nkv = (P.skv + kTileKV - 1) / kTileKV;
+  const uint32_t tile_bytes = dhalves * kHalfBytes;   // bytes of one staged Q / K / V tile
+
+  if (threadIdx.x == 0) {
+    mbar_init(base + kBarQ, 1);
+    for (uint32_t s = 0; s < kRingSlots; ++s) {
+      mbar_init(base + kBarKvFull + 8 * s, 1);
+      mbar_init(base + kBarKvEmpty + 8 * s, 1);
+    }
+    for (uint32_t g = 0; g < 2; ++g) {
+      mbar_init(base + kBarSFull + 8 * g, 1);
+      mbar_init(base + kBarSFree + 8 * g, 4);
+      mbar_init(base + kBarPReady + 8 * g, 4);
+      mbar_init(base + kBarPvDone + 8 * g, 1);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(base + kTmemSlot, kTmemCols);
+    tmem_relinquish();
+  }
+  tcgen05_before_sync();
+  __syncthreads();
+  tcgen05_after_sync();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(smem + kTmemSlot);
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      mbar_expect_tx(base + kBarQ, 2 * tile_bytes);
+      for (uint32_t g = 0; g < 2; ++g)
+        for (uint32_t h = 0; h < dhalves; ++h)
+          tma_load_3d(base + kOffQ + g * kTileBytes + h * kHalfBytes, &maps.q, base + kBarQ, (int)(h * 64),
+                      (int)(q_row0 + g * kTileQ), (int)bz);
+      // ring order: K0 V0 K1 V1 ...
+      uint32_t slot = 0, parity = 1;
+      for (uint32_t i = 0; i < 2 * nkv; ++i) {
+        const uint32_t j = i >> 1;
+        const CUtensorMap *map = (i & 1u) ? &maps.v : &maps.k;
+        mbar_wait(base + kBarKvEmpty + 8 * slot, parity, 1, &g_attn_status);
+        mbar_expect_tx(base + kBarKvFull + 8 * slot, tile_bytes);
+        for (uint32_t h = 0; h < dhalves; ++h)
+          tma_load_3d(base + kOffRing + slot * kTileBytes + h * kHalfBytes, map, base + kBarKvFull + 8 * slot, (int)(h * 64),
+                      (int)(j * kTileKV), (int)bz);
+        if (++slot == kRingSlots) {
+          slot = 0;
+          parity ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      const uint32_t fmt = P.dtype == T_BF16 ? 1u : 0u;
+      // S = Q K^T: both operands have the head dimension innermost; M = 128, N = 128 keys
+      const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | ((kTileKV >> 3) << 17) | ((kTileQ >> 4) << 24);
+      // O += P V: V is stored [key][d] (the contraction axis outermost); N = d
+      const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((P.d >> 3) << 17) | ((kTileQ >> 4) << 24);
+      const uint32_t ksteps_s = P.d / 16;
+      uint32_t slot = 0, kv_parity = 0;   // ring position of the next tile to consume
+      auto advance = [&]() {
+        if (++slot == kRingSlots) {
+          slot = 0;
+          kv_parity ^= 1u;
+        }
+      };
+      auto issue_s = [&](uint32_t g, uint32_t kslot) {
+        const uint32_t qa = base + kOffQ + g * kTileBytes, kb = base + kOffRing + kslot * kTileBytes;
+        for (uint32_t kk = 0; kk < ksteps_s; ++kk) {
+          const uint32_t off = (kk >> 2) * kHalfBytes + (kk & 3u) * 32u;
+          umma_f16_cta1(tmem_base + kTmemS + g * 128, make_smem_desc(qa + off, 0, 1024), make_smem_desc(kb + off, 0, 1024), idesc_s,
+                        kk != 0 ? 1u : 0u);
+        }
+        umma_commit_cta1(base + kBarSFull + 8 * g);
+      };
+      auto issue_pv = [&](uint32_t g, uint32_t vslot, bool accumulate) {
+        const uint32_t pa = base + kOffP + g * kTileBytes, vb = base + kOffRing + vslot * kTileBytes;
+        for (uint32_t kk = 0; kk < kTileKV / 16; ++kk) {
+          const uint64_t da = make_smem_desc(pa + (kk >> 2) * kHalfBytes + (kk & 3u) * 32u, 0, 1024);
+          const uint64_t db = make_smem_desc(vb + kk * 2048, kHalfBytes, 1024);
+          umma_f16_cta1(tmem_base + kTmemO + g * 128, da, db, idesc_o, (accumulate || kk != 0) ? 1u : 0u);
+        }
+        umma_commit_cta1(base + kBarPvDone + 8 * g);
+      };
+      mbar_wait(base + kBarQ, 0, 2, &g_attn_status);
+      // prologue: scores of key tile 0 for both row tiles
+      mbar_wait(base + kBarKvFull + 8 * slot, kv_parity, 3, &g_attn_status);
+      tcgen05_after_sync();
+      issue_s(0, slot);
+      issue_s(1, slot);
+      umma_commit_cta1(base + kBarKvEmpty + 8 * slot);
+      advance();
+      for (uint32_t j = 0; j < nkv; ++j) {
+        const uint32_t vslot = slot, v_parity = kv_parity;
+        advance();
+        const uint32_t kslot = slot, k_parity = kv_parity;
+        const bool more = j + 1 < nkv;
+        if (more) advance();
+        for (uint32_t g = 0; g < 2; ++g) {
+          mbar_wait(base + kBarPReady + 8 * g, j & 1u, 4, &g_attn_status);
+          if (g == 0) mbar_wait(base + kBarKvFull + 8 * vslot, v_parity, 5, &g_attn_status);
+          tcgen05_after_sync();
+          issue_pv(g, vslot, j != 0);
+          if (g == 1) umma_commit_cta1(base + kBarKvEmpty + 8 * vslot);
+          if (more) {
+            if (g == 0) mbar_wait(base + kBarKvFull + 8 * kslot, k_parity, 6, &g_attn_status);
+            mbar_wait(base + kBarSFree + 8 * g, j & 1u, 7, &g_attn_status);
+            tcgen05_after_sync();
+            issue_s(g, kslot);
+            if (g == 1) umma_commit_cta1(base + kBarKvEmpty + 8 * kslot);
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------ softmax warps ------------------------------
+    const uint32_t g = (warp - 2) >> 2;          // row tile of this warp
+    const uint32_t quarter = warp & 3u;          // TMEM lane quarter this warp may access
+    const uint32_t r = quarter * 32 + lane;      // row inside the tile
+    const uint32_t row = q_row0 + g * kTileQ + r;
+    const uint32_t lane_base = (quarter * 32u) << 16;
+    const uint32_t t_s = tmem_base + lane_base + kTmemS + g * 128, t_o = tmem_base + lane_base + kTmemO + g * 128;
+    const float scale = __uint_as_float(P.scale_bits);
+    const float kLog2e = 1.4426950408889634f;
+    float m_used = -CUDART_INF_F, l = 0.0f;
+    const uint32_t p_row = base + kOffP + g * kTileBytes + (r >> 3) * 1024 + (r & 7u) * 128;
+    for (uint32_t j = 0; j < nkv; ++j) {
+      mbar_wait(base + kBarSFull + 8 * g, j & 1u, 8, &g_attn_status);
+      tcgen05_after_sync();
+      uint32_t s[128];
+      {
+        uint32_t t[32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          tmem_ld_32x32b_x32(t_s + c * 32, t);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) s[c * 32 + i] = t[i];
+        }
+      }
+      tcgen05_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(base + kBarSFree + 8 * g);
+      // score in the graph's precision, masked past the last key
+      const uint32_t kv_valid = min(kTileKV, P.skv - j * kTileKV);
+      float mx = -CUDART_INF_F;
+#pragma unroll
+      for (int i = 0; i < 128; ++i) {
+        float x = u2f(s[i]);
+        x = P.dtype == T_BF16 ? round_bf16(x) : round_f16(x);
+        x *= scale;
+        if (P.scale_first) x = P.dtype == T_BF16 ? round_bf16(x) : round_f16(x);
+        if ((uint32_t)i >= kv_valid) x = -CUDART_INF_F;
+        s[i] = f2u(x);
+        mx = fmaxf(mx, x);
+      }
+      float alpha = 1.0f;
+      bool rescale = false;
+      if (mx > m_used + kRescaleThreshold || m_used == -CUDART_INF_F) {
+        alpha = m_used == -CUDART_INF_F ? 0.0f : fast_exp2((m_used - mx) * kLog2e);
+        rescale = j != 0;
+        m_used = mx;
+        l *= alpha;
+      }
+      const float mneg = -m_used * kLog2e;
+      float sum = 0.0f;
+      uint32_t pk[64];
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        const float p0 = fast_exp2(fmaf(u2f(s[2 * i]), kLog2e, mneg));
+        const float p1 = fast_exp2(fmaf(u2f(s[2 * i + 1]), kLog2e, mneg));
+        sum += p0 + p1;
+        pk[i] = pack_pair(P.dtype, p0, p1);
+      }
+      l += sum;
+      // P_g and O_g are free once the previous P V of this tile has completed
+      if (j != 0) {
+        mbar_wait(base + kBarPvDone + 8 * g, (j - 1) & 1u, 9, &g_attn_status);
+        tcgen05_after_sync();
+      }
+      if (__any_sync(0xffffffffu, rescale)) {
+        for (uint32_t c = 0; c < P.d; c += 32) {
+          uint32_t t[32];
+          tmem_ld_32x32b_x32(t_o + c, t);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) t[i] = f2u(u2f(t[i]) * alpha);
+          tmem_st_32x32b_x32(t_o + c, t);
+        }
+        tmem_st_wait();
+      }
+      // P row -> shared memory in the 128-byte swizzled layout of an MMA A operand
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const uint32_t addr = p_row + (u >> 3) * kHalfBytes + (((uint32_t)(u & 7) ^ (r & 7u)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(pk[4 * u]), "r"(pk[4 * u + 1]), "r"(pk[4 * u + 2]),
+                     "r"(pk[4 * u + 3])
+                     : "memory");
+      }
+      fence_async_shared();
+      tcgen05_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(base + kBarPReady + 8 * g);
+    }
+    // ---- result: O / l, rounded to the operand type
+    mbar_wait(base + kBarPvDone + 8 * g, (nkv - 1) & 1u, 10, &g_attn_status);
+    tcgen05_after_sync();
+    const float inv = 1.0f / l;
+    uint8_t *orow = reinterpret_cast<uint8_t *>(P.o_ptr) + ((size_t)bz * P.sq + row) * P.d * 2;
+    for (uint32_t c = 0; c < P.d; c += 32) {
+      uint32_t t[32];
+      tmem_ld_32x32b_x32(t_o + c, t);
+      if (row < P.sq) {
+        uint32_t o[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[i] = pack_pair(P.dtype, u2f(t[2 * i]) * inv, u2f(t[2 * i + 1]) * inv);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          *reinterpret_cast<uint4 *>(orow + (size_t)c * 2 + u * 16) = make_uint4(o[4 * u], o[4 * u + 1], o[4 * u + 2], o[4 * u + 3]);
+      }
+    }
+  }
+  tcgen05_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+namespace {
+
+PFN_cuTensorMapEncodeTiled GetEncodeFn() {
+  static PFN_cuTensorMapEncodeTiled fn = nullptr;
+  if (fn == nullptr) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(p);
+  }
+  return fn;
+}
+
+// [batch, rows, d] row-major, box = [1, 128 rows, 64 elements], 128-byte swizzle
+int EncodeRows(CUtensorMap *map, uint64_t ptr, uint64_t d, uint64_t rows, uint64_t batch) {
+  auto encode = GetEncodeFn();
+  if (encode == nullptr) return -10;
+  cuuint64_t dims[3] = {d, rows, batch};
+  cuuint64_t strides[2] = {d * 2, d * rows * 2};
+  cuuint32_t box[3] = {64, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, reinterpret_cast<void *>(ptr), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -100 - static_cast<int>(r);
+}
+
+}  // namespace
+
+bool AttentionSupported(const AttnParam &p) {
+  if (p.d != 64 && p.d != 128) return false;
+  if (p.dtype != T_BF16 && p.dtype != T_F16) return false;
+  if (p.sq == 0 || p.skv == 0 || p.batch == 0) return false;
+  return true;
+}
+
+int LaunchAttention(const AttnParam &p, void *stream) {
+  if (!AttentionSupported(p)) return -1;
+  if ((p.q_ptr | p.k_ptr | p.v_ptr | p.o_ptr) & 15u) return -2;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  static bool attr_set[64] = {false};
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(dvm_b200_attention, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set[dev] = true;
+  }
+  AttnMaps maps;
+  int rc = EncodeRows(&maps.q, p.q_ptr, p.d, p.sq, p.batch);
+  if (rc == 0) rc = EncodeRows(&maps.k, p.k_ptr, p.d, p.skv, p.batch);
+  if (rc == 0) rc = EncodeRows(&maps.v, p.v_ptr, p.d, p.skv, p.batch);
+  if (rc != 0) return rc;
+  const uint32_t qblocks = (p.sq + kTileQ * kQTilesPerCta - 1) / (kTileQ * kQTilesPerCta);
+  dvm_b200_attention<<<p.batch * qblocks, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p, maps);
+  return static_cast<int>(cudaGetLastError());
+}
+
+unsigned int ReadAttentionStatus() {
+  unsigned int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_attn_status, sizeof(v)) != cudaSuccess) return 0xffffffffu;
+  if (v != 0) cudaMemcpyToSymbol(g_attn_status, &zero, sizeof(zero));
+  return v;
+}
+
+}  // namespace dvmb

@@ -58,11 +58,11 @@ def matmul_bias_gelu(k, a, b, bias):
     return k.cast(gelu_tanh(k, k.cast(c, F32)), BF16)
 
 
-def attention(k, q, kmat, v, scale):
-    """C4: softmax(Q K^T * scale) V, non-causal, fp32 softmax, bf16 result."""
+def attention(k, q, kmat, v, scale, dtype=BF16):
+    """C4: softmax(Q K^T * scale) V, non-causal, fp32 softmax, result in the operand type `dtype`."""
     s = k.mul(k.matmul(q, kmat, False, True), scale)
     s = k.cast(s, F32)
     m = k.max(s, (-1,), True)
     e = k.exp(k.sub(s, m))
     p = k.div(e, k.sum(e, (-1,), True))
-    return k.matmul(k.cast(p, BF16), v, False, False)
+    return k.matmul(k.cast(p, dtype), v, False, False)
