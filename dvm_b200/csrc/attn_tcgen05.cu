@@ -74,6 +74,21 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Round two fp32 values to the operand type's precision (hardware packed conversion, then widen again).
+template <uint32_t DT>
+__device__ __forceinline__ void round_pair(float &a, float &b) {
+  if (DT == T_BF16) {
+    const uint32_t d = pack_bf16x2(a, b);
+    a = __uint_as_float(d << 16);
+    b = __uint_as_float(d & 0xffff0000u);
+  } else {
+    const __half2 h = __floats2half2_rn(a, b);
+    const float2 f = __half22float2(h);
+    a = f.x;
+    b = f.y;
+  }
+}
+
 __device__ __forceinline__ uint32_t pack_pair(uint32_t dtype, float lo, float hi) {
   if (dtype == T_BF16) return pack_bf16x2(lo, hi);
   const __half2 h = __floats2half2_rn(lo, hi);
@@ -82,8 +97,9 @@ __device__ __forceinline__ uint32_t pack_pair(uint32_t dtype, float lo, float hi
 
 }  // namespace
 
-__global__ void __launch_bounds__(kThreads, 1) dvm_b200_attention(const __grid_constant__ AttnParam P,
-                                                                  const __grid_constant__ AttnMaps maps) {
+namespace {
+template <uint32_t DT, bool SCALE_FIRST>
+__device__ __forceinline__ void attention_body(const AttnParam &P, const AttnMaps &maps) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -146,7 +162,7 @@ __global__ void __launch_bounds__(kThreads, 1) dvm_b200_attention(const __grid_c
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
-      const uint32_t fmt = P.dtype == T_BF16 ? 1u : 0u;
+      const uint32_t fmt = DT == T_BF16 ? 1u : 0u;
       // S = Q K^T: both operands have the head dimension innermost; M = 128, N = 128 keys
       const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | ((kTileKV >> 3) << 17) | ((kTileQ >> 4) << 24);
       // O += P V: V is stored [key][d] (the contraction axis outermost); N = d
@@ -216,7 +232,7 @@ __global__ void __launch_bounds__(kThreads, 1) dvm_b200_attention(const __grid_c
     const uint32_t lane_base = (quarter * 32u) << 16;
     const uint32_t t_s = tmem_base + lane_base + kTmemS + g * 128, t_o = tmem_base + lane_base + kTmemO + g * 128;
     const float scale = __uint_as_float(P.scale_bits);
-    const float kLog2e = 1.4426950408889634f;
+    constexpr float kLog2e = 1.4426950408889634f;
     float m_used = -CUDART_INF_F, l = 0.0f;
     const uint32_t p_row = base + kOffP + g * kTileBytes + (r >> 3) * 1024 + (r & 7u) * 128;
     for (uint32_t j = 0; j < nkv; ++j) {
@@ -235,38 +251,48 @@ __global__ void __launch_bounds__(kThreads, 1) dvm_b200_attention(const __grid_c
       tcgen05_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(base + kBarSFree + 8 * g);
-      // score in the graph's precision, masked past the last key
+      // score in the graph's precision (rounded as the MatMul result, scaled), kept in the log2 domain
       const uint32_t kv_valid = min(kTileKV, P.skv - j * kTileKV);
+      const float c2 = SCALE_FIRST ? kLog2e : scale * kLog2e;
+#pragma unroll
+      for (int i = 0; i < 128; i += 2) {
+        float x0 = u2f(s[i]), x1 = u2f(s[i + 1]);
+        round_pair<DT>(x0, x1);
+        if (SCALE_FIRST) {
+          x0 *= scale;
+          x1 *= scale;
+          round_pair<DT>(x0, x1);
+        }
+        s[i] = f2u(x0 * c2);
+        s[i + 1] = f2u(x1 * c2);
+      }
+      if (kv_valid < kTileKV) {   // the last key tile: mask what lies past the sequence
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if ((uint32_t)i >= kv_valid) s[i] = 0xff800000u;
+      }
       float mx = -CUDART_INF_F;
 #pragma unroll
-      for (int i = 0; i < 128; ++i) {
-        float x = u2f(s[i]);
-        x = P.dtype == T_BF16 ? round_bf16(x) : round_f16(x);
-        x *= scale;
-        if (P.scale_first) x = P.dtype == T_BF16 ? round_bf16(x) : round_f16(x);
-        if ((uint32_t)i >= kv_valid) x = -CUDART_INF_F;
-        s[i] = f2u(x);
-        mx = fmaxf(mx, x);
-      }
+      for (int i = 0; i < 128; ++i) mx = fmaxf(mx, u2f(s[i]));
       float alpha = 1.0f;
       bool rescale = false;
-      if (mx > m_used + kRescaleThreshold || m_used == -CUDART_INF_F) {
-        alpha = m_used == -CUDART_INF_F ? 0.0f : fast_exp2((m_used - mx) * kLog2e);
+      if (mx > m_used + kRescaleThreshold * kLog2e || m_used == -CUDART_INF_F) {
+        alpha = m_used == -CUDART_INF_F ? 0.0f : fast_exp2(m_used - mx);
         rescale = j != 0;
         m_used = mx;
         l *= alpha;
       }
-      const float mneg = -m_used * kLog2e;
-      float sum = 0.0f;
+      float sum0 = 0.0f, sum1 = 0.0f;
       uint32_t pk[64];
 #pragma unroll
       for (int i = 0; i < 64; ++i) {
-        const float p0 = fast_exp2(fmaf(u2f(s[2 * i]), kLog2e, mneg));
-        const float p1 = fast_exp2(fmaf(u2f(s[2 * i + 1]), kLog2e, mneg));
-        sum += p0 + p1;
-        pk[i] = pack_pair(P.dtype, p0, p1);
+        const float p0 = fast_exp2(u2f(s[2 * i]) - m_used);
+        const float p1 = fast_exp2(u2f(s[2 * i + 1]) - m_used);
+        sum0 += p0;
+        sum1 += p1;
+        pk[i] = pack_pair(DT, p0, p1);
       }
-      l += sum;
+      l += sum0 + sum1;
       // P_g and O_g are free once the previous P V of this tile has completed
       if (j != 0) {
         mbar_wait(base + kBarPvDone + 8 * g, (j - 1) & 1u, 9, &g_attn_status);
@@ -306,7 +332,7 @@ __global__ void __launch_bounds__(kThreads, 1) dvm_b200_attention(const __grid_c
       if (row < P.sq) {
         uint32_t o[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) o[i] = pack_pair(P.dtype, u2f(t[2 * i]) * inv, u2f(t[2 * i + 1]) * inv);
+        for (int i = 0; i < 16; ++i) o[i] = pack_pair(DT, u2f(t[2 * i]) * inv, u2f(t[2 * i + 1]) * inv);
 #pragma unroll
         for (int u = 0; u < 4; ++u)
           *reinterpret_cast<uint4 *>(orow + (size_t)c * 2 + u * 16) = make_uint4(o[4 * u], o[4 * u + 1], o[4 * u + 2], o[4 * u + 3]);
@@ -320,6 +346,18 @@ __global__ void __launch_bounds__(kThreads, 1) dvm_b200_attention(const __grid_c
     tmem_dealloc(tmem_base, kTmemCols);
   }
 }
+}  // namespace
+
+#define DVMB_ATTN_KERNEL(NAME, DT, SF)                                                                              \
+  __global__ void __launch_bounds__(kThreads, 1) NAME(const __grid_constant__ AttnParam P,                          \
+                                                      const __grid_constant__ AttnMaps maps) {                      \
+    attention_body<DT, SF>(P, maps);                                                                                \
+  }
+DVMB_ATTN_KERNEL(dvm_b200_attention_bf16, T_BF16, false)
+DVMB_ATTN_KERNEL(dvm_b200_attention_bf16_sf, T_BF16, true)
+DVMB_ATTN_KERNEL(dvm_b200_attention_f16, T_F16, false)
+DVMB_ATTN_KERNEL(dvm_b200_attention_f16_sf, T_F16, true)
+#undef DVMB_ATTN_KERNEL
 
 namespace {
 
@@ -363,19 +401,25 @@ int LaunchAttention(const AttnParam &p, void *stream) {
   if ((p.q_ptr | p.k_ptr | p.v_ptr | p.o_ptr) & 15u) return -2;
   int dev = 0;
   cudaGetDevice(&dev);
+  using KernelFn = void (*)(const AttnParam, const AttnMaps);
+  static const KernelFn kernels[4] = {dvm_b200_attention_bf16, dvm_b200_attention_bf16_sf, dvm_b200_attention_f16,
+                                      dvm_b200_attention_f16_sf};
   static bool attr_set[64] = {false};
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(dvm_b200_attention, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e != cudaSuccess) return static_cast<int>(e);
+    for (auto fn : kernels) {
+      cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+      if (e != cudaSuccess) return static_cast<int>(e);
+    }
     attr_set[dev] = true;
   }
+  const KernelFn kernel = kernels[(p.dtype == T_BF16 ? 0 : 2) + (p.scale_first ? 1 : 0)];
   AttnMaps maps;
   int rc = EncodeRows(&maps.q, p.q_ptr, p.d, p.sq, p.batch);
   if (rc == 0) rc = EncodeRows(&maps.k, p.k_ptr, p.d, p.skv, p.batch);
   if (rc == 0) rc = EncodeRows(&maps.v, p.v_ptr, p.d, p.skv, p.batch);
   if (rc != 0) return rc;
   const uint32_t qblocks = (p.sq + kTileQ * kQTilesPerCta - 1) / (kTileQ * kQTilesPerCta);
-  dvm_b200_attention<<<p.batch * qblocks, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p, maps);
+  kernel<<<p.batch * qblocks, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p, maps);
   return static_cast<int>(cudaGetLastError());
 }
 
