@@ -33,9 +33,14 @@ WORKLOADS = {
     "c1": "fused elementwise exp(x)*y+0.5, fp32 [8192,8192]",
     "c2": "BatchNorm training-forward, fp16 NCHW [64,256,56,56], fp32 statistics",
     "c3": "residual-add + RMSNorm + SwiGLU, bf16 [16384,4096]",
+    "c4": "fused attention, bf16 Q/K/V [8,32,2048,128], fp32 softmax",
+    "c5": "MatMul + bias + tanh-GeLU post-fusion, bf16 [16384,8192]x[8192,8192], fp32 accumulate",
 }
-ALGO_BYTES = {"c1": 805306368, "c2": 205524992, "c3": 805314560}
-DTYPE = {"c1": "f32", "c2": "f16 storage / f32 math", "c3": "bf16 storage / f32 math"}
+ALGO_BYTES = {"c1": 805306368, "c2": 205524992, "c3": 805314560, "c4": 536870912, "c5": 671105024}
+ALGO_FLOPS = {"c4": 549755813888, "c5": 2199023255552}
+DTYPE = {"c1": "f32", "c2": "f16 storage / f32 math", "c3": "bf16 storage / f32 math", "c4": "bf16 operands / f32 accumulate",
+         "c5": "bf16 operands / f32 accumulate"}
+KTYPE = {"c1": "vector", "c2": "vector", "c3": "vector:spec,dyn", "c4": "split", "c5": "mix"}
 
 
 def make_inputs(name, seed_offset=0, scale=1.0):
@@ -59,6 +64,18 @@ def make_inputs(name, seed_offset=0, scale=1.0):
         h, r, g, u = (rng.standard_normal((t, 4096), dtype=np.float32).astype(bf) for _ in range(4))
         w = rng.normal(1, 0.02, (4096,)).astype(np.float32).astype(bf)
         return [h, r, w, g, u]
+    if name == "c4":
+        rng = np.random.default_rng(4 + seed_offset)
+        b = max(1, int(8 * scale))
+        return [rng.standard_normal((b, 32, 2048, 128), dtype=np.float32).astype(ml_dtypes.bfloat16) for _ in range(3)]
+    if name == "c5":
+        rng = np.random.default_rng(5 + seed_offset)
+        m = max(128, int(16384 * scale))
+        bf = ml_dtypes.bfloat16
+        a = (rng.standard_normal((m, 8192), dtype=np.float32) * 0.02).astype(bf)
+        b = (rng.standard_normal((8192, 8192), dtype=np.float32) * 0.02).astype(bf)
+        bias = (rng.standard_normal((8192,), dtype=np.float32) * 0.02).astype(bf)
+        return [a, b, bias]
     raise ValueError(name)
 
 
@@ -71,6 +88,10 @@ def build_graph(k, name, loaded, arrays):
         return list(W.batchnorm_train(k, *loaded, n * h * w))
     if name == "c3":
         return list(W.rmsnorm_swiglu(k, *loaded, 4096))
+    if name == "c4":
+        return [W.attention(k, *loaded, 1.0 / np.sqrt(128.0))]
+    if name == "c5":
+        return [W.matmul_bias_gelu(k, *loaded)]
     raise ValueError(name)
 
 
@@ -129,10 +150,50 @@ def cpu_eval(name, arrays):
     return [o.store(v) for v in build_graph(o, name, loaded, arrays)]
 
 
-def cpu_baseline(name, budget_s=12.0):
-    """Time the NumPy graph evaluation on a bounded sample of the workload (fraction of the leading dim)."""
+def cpu_sample(name):
+    """A bounded sample of the workload for the host-side evaluation: (arrays, description)."""
+    if name == "c4":
+        arrays = [a[:1, :2] for a in make_inputs("c4", scale=1.0 / 8)]
+        return arrays, "2 of the 256 (batch, head) slices of c4"
+    if name == "c5":
+        arrays = make_inputs("c5", scale=1.0 / 64)
+        return arrays, "256 of the 16384 rows of A (1/64 of c5)"
     scale = {"c1": 1.0 / 32, "c2": 1.0 / 16, "c3": 1.0 / 64}[name]
-    arrays = make_inputs(name, scale=scale)
+    return make_inputs(name, scale=scale), "1/%d of the leading dimension of %s" % (round(1 / scale), name)
+
+
+def work_of(name, arrays, outs):
+    """Units of the workload's metric in one evaluation: algorithmic bytes, or flops for the tensor-core graphs."""
+    if name == "c4":
+        b, h, s, d = arrays[0].shape
+        return 4.0 * b * h * s * s * d
+    if name == "c5":
+        return 2.0 * arrays[0].shape[0] * arrays[1].shape[0] * arrays[1].shape[1]
+    return float(algo_bytes(name, arrays, outs))
+
+
+def unit_of(name):
+    return "TFLOP/s" if name in ("c4", "c5") else "GB/s"
+
+
+def unit_scale(name):
+    return 1e12 if name in ("c4", "c5") else 1e9
+
+
+def metric_of(name):
+    return {"c4": "attention_tflops", "c5": "matmul_post_fusion_tflops"}.get(name, "fused_op_hbm_throughput")
+
+
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def cpu_baseline(name, budget_s=12.0):
+    """Time the NumPy graph evaluation (the oracle) on a bounded sample of the workload."""
+    arrays, what = cpu_sample(name)
     t0 = time.perf_counter()
     outs = cpu_eval(name, arrays)
     dt = time.perf_counter() - t0
@@ -143,18 +204,18 @@ def cpu_baseline(name, budget_s=12.0):
         cpu_eval(name, arrays)
         best = min(best, time.perf_counter() - t0)
         reps += 1
-    nbytes = algo_bytes(name, arrays, outs)
-    return {"value": nbytes / best / 1e9, "unit": "GB/s", "cores": 1, "kind": "port",
-            "sample": "%s of the leading dimension of %s (%d algorithmic bytes), best of %d NumPy evaluations"
-                      % ("1/%d" % round(1 / scale), name, nbytes, reps)}
+    work = work_of(name, arrays, outs)
+    # NumPy's elementwise and reduction loops are single-threaded; its fp32 matmul uses the BLAS threads
+    cores = host_threads() if name in ("c4", "c5") else 1
+    return {"value": work / best / unit_scale(name), "unit": unit_of(name), "cores": cores, "kind": "port",
+            "sample": "%s, best of %d NumPy evaluations" % (what, reps)}
 
 
 def run_reference(args, rank):
     if rank != 0:
         return
     name = args.workload
-    scale = {"c1": 1.0 / 32, "c2": 1.0 / 16, "c3": 1.0 / 64}[name]
-    arrays = make_inputs(name, scale=scale)
+    arrays, what = cpu_sample(name)
     outs = None
     for _ in range(args.warmup):
         outs = cpu_eval(name, arrays)
@@ -162,17 +223,16 @@ def run_reference(args, rank):
     for _ in range(args.steps):
         outs = cpu_eval(name, arrays)
     dt = time.perf_counter() - t0
-    nbytes = algo_bytes(name, arrays, outs)
-    v = nbytes * args.steps / dt / 1e9
-    sample = "1/%d of the leading dimension per step (%d algorithmic bytes)" % (round(1 / scale), nbytes)
+    v = work_of(name, arrays, outs) * args.steps / dt / unit_scale(name)
+    cores = host_threads() if name in ("c4", "c5") else 1
     print(json.dumps({
-        "impl": "reference", "metric": "fused_op_hbm_throughput", "value": v, "unit": "GB/s", "n_gpus": args.gpus,
+        "impl": "reference", "metric": metric_of(name), "value": v, "unit": unit_of(name), "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": DTYPE[name], "data": "synthetic",
         "config": {"workload": WORKLOADS[name], "note": "NumPy evaluation of the same graph on host cores; the "
                    "reference ships no CPU executor and its tests use NumPy as the evaluator"},
-        "cpu_baseline": {"value": v, "unit": "GB/s", "cores": 1, "kind": "port", "sample": sample},
-        "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "cpu_baseline": {"value": v, "unit": unit_of(name), "cores": cores, "kind": "port", "sample": what + " per step"},
+        "e2e": {"value": v, "unit": unit_of(name), "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
 
@@ -183,8 +243,7 @@ class DeviceWorkload:
         import dvm_b200 as dvm
         self.name = name
         self.arrays = make_inputs(name, seed_offset, scale)
-        ktype = "vector:spec,dyn" if name == "c3" else "vector"
-        self.k = dvm.PyKernel(ktype, "dev", int(os.environ.get("LOCAL_RANK", "0")))
+        self.k = dvm.PyKernel(KTYPE[name], "dev", int(os.environ.get("LOCAL_RANK", "0")))
         self.loads = [self.k.load(list(a.shape), dvm.frontend.dvm_dtype_of(a.dtype)) for a in self.arrays]
         for op, a in zip(self.loads, self.arrays):
             self.k.input(op, a)
@@ -192,7 +251,8 @@ class DeviceWorkload:
         self.stores = [self.k.store(v) for v in vals]
         self.k.codegen()
         self.jit_us = self.k.jit_us()
-        self.launches_per_step = self.k.das().count("vmain")
+        das = self.k.das()
+        self.launches_per_step = das.count("vmain") + das.count("mmain") + das.count("amain")
 
     def outputs(self):
         return [self.k.output(s) for s in self.stores]
@@ -258,14 +318,64 @@ def time_e2e(wl, steps, warmup, dist):
     return dt, h2d, d2h
 
 
-def measured_peak():
+def measured_peak(name):
+    """Roofline denominator for the workload's dominant kernel: measured HBM copy bandwidth or bf16 GEMM rate."""
+    key, fallback = ("bf16_tflops", 1590.0) if name in ("c4", "c5") else ("hbm_gbs", 6650.0)
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         try:
-            return float(json.load(open(path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+            return float(json.load(open(path))[key]), "measured (MEASURED_PEAKS.json %s)" % key
         except Exception:
             pass
-    return 6650.0, "fallback (earlier measurement on this pool)"
+    return fallback, "fallback (earlier measurement on this pool)"
+
+
+KERNEL_NAME = {"c1": "dvm_b200_vm_vector", "c2": "dvm_b200_vm_vector", "c3": "dvm_b200_vm_vector",
+               "c4": "dvm_b200_attention_bf16_sf", "c5": "dvm_b200_mm_tcgen05_pair"}
+
+
+def device_summary(name, reps=30):
+    """Per-launch figures of one workload on the current device (inputs resident, device events)."""
+    wl = DeviceWorkload(name)
+    outs = [np.empty(s.shape(), wl.k.output(s).dtype) for s in wl.stores]
+    work = work_of(name, wl.arrays, outs)
+    lo, hi, mean = wl.k.perf(warmup=3, reps=reps)
+    peak, _ = measured_peak(name)
+    rate = work / (mean * 1e-6) / unit_scale(name)
+    out = {"workload": WORKLOADS[name], "us_per_launch": mean, "us_min": lo, "rate": rate, "unit": unit_of(name),
+           "frac_of_measured_peak": rate / peak, "jit_us": wl.jit_us, "launches": wl.launches_per_step}
+    wl.k.release_io()
+    return out
+
+
+def dynamic_shape_jit():
+    """c3 as one dynamic-shape kernel stepped through its token counts in order: host microseconds from the new
+    shape to the finished program (compile + bind), and the kernel time at that shape."""
+    import ml_dtypes
+    import dvm_b200 as dvm
+    bf = ml_dtypes.bfloat16
+    k = dvm.PyKernel("vector:spec,dyn", "dev", int(os.environ.get("LOCAL_RANK", "0")))
+    t_ref = dvm.IntArrayRef([1, 4096])
+    w_ref = dvm.IntArrayRef([4096])
+    loads = [k.load(t_ref, dvm.bfloat16), k.load(t_ref, dvm.bfloat16), k.load(w_ref, dvm.bfloat16),
+             k.load(t_ref, dvm.bfloat16), k.load(t_ref, dvm.bfloat16)]
+    from dvm_b200 import workloads as W
+    stores = [k.store(v) for v in W.rmsnorm_swiglu(k, *loads, 4096)]
+    out = {}
+    for t in (1, 7, 128, 1000, 4096, 16384):
+        rng = np.random.default_rng(3 + 1000 * t)
+        t_ref.update([t, 4096])
+        arrs = [rng.standard_normal((t, 4096), dtype=np.float32).astype(bf) for _ in range(2)]
+        arrs.append(rng.normal(1, 0.02, (4096,)).astype(np.float32).astype(bf))
+        arrs += [rng.standard_normal((t, 4096), dtype=np.float32).astype(bf) for _ in range(2)]
+        for op, a in zip(loads, arrs):
+            k.input(op, a)
+        k.codegen()
+        jit = k.jit_us()
+        lo, hi, mean = k.perf(warmup=2, reps=10)
+        out[str(t)] = {"jit_us": jit, "kernel_us": mean}
+    k.release_io()
+    return out
 
 
 def main():
@@ -298,49 +408,50 @@ def main():
 
     name = args.workload
     wl = DeviceWorkload(name, seed_offset=1000 * rank, scale=args.scale)
-    nbytes = algo_bytes(name, wl.arrays, [np.empty(s.shape(), wl.k.output(s).dtype) for s in wl.stores])
+    outs = [np.empty(s.shape(), wl.k.output(s).dtype) for s in wl.stores]
+    work = work_of(name, wl.arrays, outs)
+    nbytes = algo_bytes(name, wl.arrays, outs)
 
     with ClockSampler(local_rank) as clocks:
         ms = time_steps(wl, args.steps, args.warmup, dist)
         # per-launch duration of the dominant kernel, device events on the launch stream
         lo, hi, mean = wl.k.perf(warmup=3, reps=max(20, min(args.steps, 200)))
-    value = nbytes * args.steps * world / (ms * 1e-3) / 1e9
-    peak, peak_src = measured_peak()
-    achieved = nbytes / (mean * 1e-6) / 1e9
+    value = work * args.steps * world / (ms * 1e-3) / unit_scale(name)
+    peak, peak_src = measured_peak(name)
+    achieved = work / (mean * 1e-6) / unit_scale(name)
+    tensor = name in ("c4", "c5")
     line = {
-        "metric": "fused_op_hbm_throughput", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "metric": metric_of(name), "value": value, "unit": unit_of(name), "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": DTYPE[name], "data": "synthetic",
         "config": {"workload": WORKLOADS[name], "algorithmic_bytes_per_step_per_gpu": nbytes,
                    "l2": "inputs larger than L2 (no flush)", "sharding": "each rank runs a full-size shard (batch x N)",
                    "scale": args.scale},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_source": peak_src, "kernel": "dvm_b200_vm_vector",
+        "roofline": {"bound": "tensor" if tensor else "hbm", "achieved": achieved, "peak": peak, "unit": unit_of(name),
+                     "frac": achieved / peak, "traffic": None, "peak_source": peak_src, "kernel": KERNEL_NAME[name],
                      "us_per_launch": {"min": lo, "mean": mean, "max": hi},
-                     "frac_of_nominal_8TBs": achieved / 8000.0},
+                     "frac_of_nominal": achieved / (2250.0 if tensor else 8000.0)},
         "gpu_launches": args.steps * wl.launches_per_step,
         "jit_us": wl.jit_us,
         "clocks": clocks.summary(),
     }
+    if tensor:
+        line["config"]["algorithmic_flops_per_step_per_gpu"] = work
     if not args.no_extras:
-        dt, h2d, d2h = time_e2e(wl, max(3, min(args.steps, 10)), 1, dist)
         e2e_steps = max(3, min(args.steps, 10))
-        line["e2e"] = {"value": nbytes * e2e_steps * world / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
-                       "d2h_bytes_per_step": d2h, "ms_per_step": dt / e2e_steps * 1e3}
+        dt, h2d, d2h = time_e2e(wl, e2e_steps, 1, dist)
+        line["e2e"] = {"value": work * e2e_steps * world / dt / unit_scale(name), "unit": unit_of(name),
+                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": dt / e2e_steps * 1e3}
         if rank == 0 and world == 1:
             line["cpu_baseline"] = cpu_baseline(name)
-            others = {}
+            wl.k.release_io()
             del wl
+            others = {}
             for other in sorted(WORKLOADS):
-                if other == name:
-                    continue
-                w2 = DeviceWorkload(other)
-                nb = algo_bytes(other, w2.arrays, [np.empty(s.shape(), w2.k.output(s).dtype) for s in w2.stores])
-                lo2, hi2, mean2 = w2.k.perf(warmup=3, reps=30)
-                others[other] = {"workload": WORKLOADS[other], "us_per_launch": mean2, "GBs": nb / (mean2 * 1e-6) / 1e9,
-                                 "frac_of_measured_peak": nb / (mean2 * 1e-6) / 1e9 / peak, "jit_us": w2.jit_us}
-                del w2
+                if other != name:
+                    others[other] = device_summary(other)
             line["other_workloads"] = others
+            line["dynamic_shape_jit_c3"] = dynamic_shape_jit()
     if rank == 0:
         print(json.dumps(line))
     if dist is not None:
