@@ -61,6 +61,8 @@ SIGNATURES = {
     "dvm_codegen": (c_int, [c_void_p, ctypes.POINTER(Reloc), c_size_t, WS_ALLOC_FN, c_void_p]),
     "dvm_launch": (c_int, [c_void_p, c_void_p]),
     "dvm_launch_reloc": (c_int, [c_void_p, ctypes.POINTER(Reloc), c_size_t, c_void_p, c_void_p]),
+    "dvm_launch_static_scratch": (c_int, [c_void_p, ctypes.POINTER(Reloc), c_size_t, c_void_p]),
+    "dvm_static_scratch_capacity": (c_size_t, []),
     "dvm_last_jit_us": (ctypes.c_double, [c_void_p]),
     "dvm_object_rank": (c_int, [c_void_p]),
     "dvm_object_dim": (c_int64, [c_void_p, c_int]),

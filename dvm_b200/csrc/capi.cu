@@ -32,6 +32,7 @@ struct dvm_scalar {
 struct dvm_kernel {
   dvm::Kernel kernel;
   double last_jit_us = 0.0;
+  size_t ws_bytes = 0;   // workspace the current program needs (set by dvm_pre_codegen / dvm_codegen)
 };
 
 namespace {
@@ -57,8 +58,19 @@ inline dvm_object *O(dvm::NDObject *n) { return reinterpret_cast<dvm_object *>(n
 struct CallbackAlloc : dvm::WsAllocator {
   dvm_ws_alloc_fn fn;
   void *user;
-  void *Alloc(size_t size) override { return fn ? fn(size, user) : nullptr; }
+  size_t asked = 0;
+  void *Alloc(size_t size) override {
+    asked = size;
+    return fn ? fn(size, user) : nullptr;
+  }
 };
+
+// Scratch for dvm_launch_static_scratch(): lives in the library's device image, so every GPU that loads the
+// library holds these bytes until the process exits.  Host code may not pass the symbol itself to a kernel;
+// the device address is looked up once per device with cudaGetSymbolAddress.
+constexpr size_t kStaticScratchBytes = 16u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+void *g_static_scratch_addr[64] = {nullptr};
 
 int CudaCheck(cudaError_t e, const char *what) {
   if (e == cudaSuccess) return 0;
@@ -180,6 +192,7 @@ int dvm_pre_codegen(dvm_kernel *k, size_t *workspace_bytes) {
       auto t0 = std::chrono::steady_clock::now();
       size_t ws = k->kernel.PreCodeGen();
       k->last_jit_us = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count();
+      k->ws_bytes = ws;
       if (workspace_bytes) *workspace_bytes = ws;
       return 0;
     },
@@ -197,6 +210,7 @@ int dvm_codegen(dvm_kernel *k, const dvm_reloc *relocs, size_t reloc_size, dvm_w
       k->kernel.Normalize();
       k->kernel.CodeGen(reinterpret_cast<const dvm::RelocEntry *>(relocs), reloc_size, &cb);
       k->last_jit_us = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count();
+      k->ws_bytes = cb.asked;
       return 0;
     },
     1);
@@ -209,6 +223,35 @@ int dvm_launch(dvm_kernel *k, void *stream) {
 int dvm_launch_reloc(dvm_kernel *k, const dvm_reloc *relocs, size_t reloc_size, void *workspace, void *stream) {
   return Guard(
     [&]() { return k->kernel.Launch(reinterpret_cast<const dvm::RelocEntry *>(relocs), reloc_size, workspace, stream); },
+    -1);
+}
+
+size_t dvm_static_scratch_capacity(void) { return kStaticScratchBytes; }
+
+int dvm_launch_static_scratch(dvm_kernel *k, const dvm_reloc *relocs, size_t reloc_size, void *stream) {
+  return Guard(
+    [&]() {
+      if (k->ws_bytes > kStaticScratchBytes) {
+        char buf[160];
+        snprintf(buf, sizeof(buf), "this kernel needs %zu bytes of workspace; the static scratch holds %zu", k->ws_bytes,
+                 kStaticScratchBytes);
+        g_error = buf;
+        return -2;
+      }
+      int dev = -1;
+      if (CudaCheck(cudaGetDevice(&dev), "cudaGetDevice") != 0) return -3;
+      if (dev < 0 || dev >= 64) {
+        g_error = "device index outside 0..63";
+        return -3;
+      }
+      if (g_static_scratch_addr[dev] == nullptr) {
+        // first call on this device: resolve the device address of the scratch array
+        void *p = nullptr;
+        if (CudaCheck(cudaGetSymbolAddress(&p, g_static_scratch), "cudaGetSymbolAddress(static scratch)") != 0) return -4;
+        g_static_scratch_addr[dev] = p;
+      }
+      return k->kernel.Launch(reinterpret_cast<const dvm::RelocEntry *>(relocs), reloc_size, g_static_scratch_addr[dev], stream);
+    },
     -1);
 }
 

@@ -90,6 +90,24 @@ DVM_C_API int dvm_codegen(dvm_kernel *k, const dvm_reloc *relocs, size_t reloc_s
 DVM_C_API int dvm_launch(dvm_kernel *k, void *stream);                                        /* dvm.h:578 */
 DVM_C_API int dvm_launch_reloc(dvm_kernel *k, const dvm_reloc *relocs, size_t reloc_size, void *workspace,
                                void *stream);                                                 /* dvm.h:599 */
+/* No counterpart in the reference.  Launch like dvm_launch_reloc(), but with the kernel's workspace (the
+ * global-memory temporaries that hand values from one stage of a split graph to the next) taken from a fixed
+ * array inside the library's device image instead of a buffer the caller allocates.  It is meant for callers
+ * that cannot call cudaMalloc at the point of launch: code running inside a framework's allocator hooks, inside a
+ * memory-pool region that forbids new allocations, or on a serving path where an allocation could stall the
+ * device.  The entry point itself calls no cudaMalloc/cudaFree and no allocating library routine.
+ *   - dvm_pre_codegen() or dvm_codegen() must have run for the current shapes; `relocs` supplies every input
+ *     and output address, exactly as for dvm_launch_reloc().
+ *   - Limit: kernels whose workspace exceeds dvm_static_scratch_capacity() bytes (16 MiB) are refused with a
+ *     non-zero return and a message in dvm_last_error(); nothing is launched.
+ *   - Every GPU that loads the library holds the array until the process exits.
+ *   - The first call on a device resolves the array's device address (cudaGetSymbolAddress, with that device
+ *     current); make that first call before starting any stream capture.
+ *   - All calls share the one array, which keeps whatever the last call left in it.  A kernel's temporaries are
+ *     always written before they are read, so nothing needs clearing; but two such launches that overlap on the
+ *     GPU (different streams) race on the array - serialise them. */
+DVM_C_API int dvm_launch_static_scratch(dvm_kernel *k, const dvm_reloc *relocs, size_t reloc_size, void *stream);
+DVM_C_API size_t dvm_static_scratch_capacity(void);
 /* Host microseconds spent by the last dvm_codegen / dvm_pre_codegen (shape inference + planning + emission). */
 DVM_C_API double dvm_last_jit_us(const dvm_kernel *k);
 
