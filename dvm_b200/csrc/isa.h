@@ -57,11 +57,14 @@ enum Opcode : uint32_t {
   OP_COUNT
 };
 
-enum UnKind : uint32_t { U_SQRT = 0, U_ABS, U_LOG, U_EXP, U_ROUND, U_FLOOR, U_CEIL, U_TRUNC, U_ISFINITE, U_ABS_I, U_NOP };
+enum UnKind : uint32_t { U_SQRT = 0, U_ABS, U_LOG, U_EXP, U_ROUND, U_FLOOR, U_CEIL, U_TRUNC, U_ISFINITE, U_ABS_I,
+                         U_EXP_FAST,   // exp through ex2.approx (relative error about 1e-6): values that never reach an exact-class op
+                         U_NOP };
 
 enum BinKind : uint32_t {
   B_ADD = 0, B_SUB, B_MUL, B_DIV, B_MAX, B_MIN, B_POW, B_RSUB, B_RDIV,
   B_ADD_I, B_SUB_I, B_MUL_I, B_MAX_I, B_MIN_I, B_RSUB_I,
+  B_DIV_FAST, B_RDIV_FAST,   // 2-ulp full-range division, same eligibility rule as U_EXP_FAST
   B_COUNT
 };
 
@@ -180,7 +183,8 @@ struct VmParam {
   uint32_t num_groups;
   uint32_t group_elems;
   uint32_t tg;               // threads cooperating on one group
-  uint32_t groups_per_cta;   // blockDim.x / tg
+  uint32_t groups_per_cta;   // groups a CTA works on at a time
+  uint32_t tcons;            // consumer threads of the CTA: tg * groups_per_cta rounded up to a multiple of 32
   uint32_t chunks;           // chunks per group
   uint32_t chunk_elems;      // elements per chunk (<= 16 * tg; threads past the end idle)
   uint32_t stage_bytes;      // bytes of one ring stage (0: no bulk staging in this launch)

@@ -65,6 +65,10 @@ struct Compiler {
   std::vector<NDObject *> slot_nodes;
   int max_temp = 0, max_sreg = 0;
   uint32_t body_tensor_mask[kMaxPhases] = {0, 0, 0, 0};   // tensor slots each BODY reads as operands
+  // nodes whose value can reach an op of the exact class (compare, select condition, cast to int / bool, rounding,
+  // IsFinite): those keep IEEE division and the accurate exp; every other float value may use the fast forms,
+  // whose error (2 ulp / about 1e-6 relative) is far inside the fp32 tolerance of the path
+  std::vector<char> exact;
   bool epilogue = false;           // compiling the post-fusion program of a MatMul stage
   const NDObject *mma_src = nullptr;
 
@@ -254,6 +258,31 @@ struct Compiler {
       }
       fi.level = lvl;
       if (n->kind == N_REDUCE && has_reduce && !fi.scalar_space) throw Fail{"partial reduction result is not group-constant"};
+    }
+  }
+
+  void MarkExact() {
+    exact.assign(ops.size(), 0);
+    static const bool off = getenv("DVM_B200_EXACT_MATH") != nullptr;
+    if (off) {
+      exact.assign(ops.size(), 1);
+      return;
+    }
+    for (size_t i = ops.size(); i-- > 0;) {
+      const NDObject *n = ops[i];
+      bool sink = false;   // this op needs exact inputs
+      switch (n->kind) {
+        case N_COMPARE:
+        case N_COMPARE_S: sink = true; break;
+        case N_CAST: sink = IsIntRepr(n->dtype); break;
+        case N_UNARY: sink = n->sub == kIsFinite || n->sub >= kRound; break;
+        default: break;
+      }
+      for (int k = 0; k < 3; ++k) {
+        if (!n->in[k]) continue;
+        const bool cond = n->kind == N_SELECT && k == 0;
+        if (sink || cond || exact[i]) exact[index.at(n->in[k])] = 1;
+      }
     }
   }
 
@@ -486,8 +515,9 @@ struct Compiler {
         static const uint32_t map[] = {U_SQRT, U_ABS, U_LOG, U_EXP, U_NOP, U_ISFINITE, U_NOP, U_ROUND, U_FLOOR, U_CEIL, U_TRUNC};
         uint32_t kind = map[n->sub];
         if (n->sub == kAbs && isint) kind = U_ABS_I;
-        const bool exact = n->sub == kAbs || n->sub == kIsFinite || n->sub >= kRound;
-        s.Push0(OP_UN, kind, 0, exact ? RN_NONE : rnd);
+        if (kind == U_EXP && !exact[index.at(n)]) kind = U_EXP_FAST;
+        const bool noround = n->sub == kAbs || n->sub == kIsFinite || n->sub >= kRound;
+        s.Push0(OP_UN, kind, 0, noround ? RN_NONE : rnd);
         s.acc_val = n;
         s.Release(x);
         return;
@@ -527,8 +557,9 @@ struct Compiler {
           static const uint32_t imap[] = {B_ADD_I, B_MUL_I, B_COUNT, B_COUNT, B_MAX_I, B_MIN_I};
           uint32_t kind = isint ? imap[n->sub] : fmap[n->sub];
           if (kind == B_COUNT) throw Fail{"integer division is not supported"};
-          const bool exact = n->sub == SB_MAX || n->sub == SB_MIN;
-          s.Push(OP_BIN, kind, o, 0, exact ? RN_NONE : rnd, 0);
+          if (!exact[index.at(n)]) kind = kind == B_DIV ? B_DIV_FAST : (kind == B_RDIV ? B_RDIV_FAST : kind);
+          const bool noround = n->sub == SB_MAX || n->sub == SB_MIN;
+          s.Push(OP_BIN, kind, o, 0, noround ? RN_NONE : rnd, 0);
         }
         s.acc_val = n;
         s.Release(x);
@@ -539,7 +570,7 @@ struct Compiler {
         const NDObject *x = Canon(n->in[0]);
         const NDObject *y = Canon(n->in[1]);
         uint32_t kind = 0, rkind = B_COUNT;   // rkind: the same op with its operands swapped
-        bool exact = false;
+        bool noround = false;
         if (n->kind == N_BINARY) {
           switch (n->sub) {
             case kAdd: kind = rkind = isint ? B_ADD_I : B_ADD; break;
@@ -547,13 +578,15 @@ struct Compiler {
             case kSub: kind = isint ? B_SUB_I : B_SUB; rkind = isint ? B_RSUB_I : B_RSUB; break;
             case kDiv:
               if (isint) throw Fail{"integer division is not supported"};
-              kind = B_DIV; rkind = B_RDIV; break;
+              kind = B_DIV; rkind = B_RDIV;
+              if (!exact[index.at(n)]) { kind = B_DIV_FAST; rkind = B_RDIV_FAST; }
+              break;
             case kPow:
               if (isint) throw Fail{"integer pow is not supported"};
               kind = B_POW; break;
             // float max/min are `a > b ? a : b`: not symmetric for NaN and signed zero, so never mirrored
-            case kMaximum: case kLogicalOr: kind = isint ? B_MAX_I : B_MAX; exact = true; if (isint) rkind = kind; break;
-            case kMinimum: case kLogicalAnd: kind = isint ? B_MIN_I : B_MIN; exact = true; if (isint) rkind = kind; break;
+            case kMaximum: case kLogicalOr: kind = isint ? B_MAX_I : B_MAX; noround = true; if (isint) rkind = kind; break;
+            case kMinimum: case kLogicalAnd: kind = isint ? B_MIN_I : B_MIN; noround = true; if (isint) rkind = kind; break;
             default: throw Fail{"unknown binary op"};
           }
         } else {
@@ -579,7 +612,7 @@ struct Compiler {
         if (n->kind == N_COMPARE) {
           s.Push(OP_CMP, swapped ? rkind : kind, o, 0, 0, IsIntRepr(n->in[0]->dtype));
         } else {
-          s.Push(OP_BIN, swapped ? rkind : kind, o, 0, exact ? RN_NONE : rnd, 0);
+          s.Push(OP_BIN, swapped ? rkind : kind, o, 0, noround ? RN_NONE : rnd, 0);
         }
         s.acc_val = n;
         s.Release(x);
@@ -869,7 +902,7 @@ struct Compiler {
         }
         if (ce != 0) {
           P.chunk_elems = ce;
-          P.tg = ((ce + kLanes - 1) / kLanes + 31) / 32 * 32;
+          P.tg = (ce + kLanes - 1) / kLanes;   // every thread of the group holds 16 lanes of the chunk
           chunk_in_inner = true;
         } else {
           const uint32_t chunks = static_cast<uint32_t>((G + kChunkCap - 1) / kChunkCap);
@@ -881,7 +914,8 @@ struct Compiler {
         P.chunks = static_cast<uint32_t>((G + P.chunk_elems - 1) / P.chunk_elems);
       }
     }
-    const uint32_t T = P.tg * P.groups_per_cta;
+    const uint32_t T = (P.tg * P.groups_per_cta + 31u) / 32u * 32u;
+    P.tcons = T;
 
     // ---- tensors
     P.n_tensors = static_cast<uint32_t>(slot_nodes.size());
@@ -1036,6 +1070,7 @@ struct Compiler {
       if (n->kind == N_MATMUL) throw Fail{"MatMul inside a vector stage"};
     AlignAxes();
     Classify();
+    MarkExact();
     Geometry();
     Emit();
     if (epilogue) {
@@ -1047,9 +1082,9 @@ struct Compiler {
 };
 
 const char *kOpNames[] = {"end", "ld", "st", "copy", "mov", "un", "bin", "cmp", "sel", "cvt", "racc", "rfin", "rinit"};
-const char *kUnNames[] = {"Sqrt", "Abs", "Log", "Exp", "Round", "Floor", "Ceil", "Trunc", "IsFinite", "Abs", "Nop"};
+const char *kUnNames[] = {"Sqrt", "Abs", "Log", "Exp", "Round", "Floor", "Ceil", "Trunc", "IsFinite", "Abs", "ExpFast", "Nop"};
 const char *kBinNames[] = {"Add", "Sub", "Mul", "Div", "Max", "Min", "Pow", "RSub", "RDiv",
-                           "Add", "Sub", "Mul", "Max", "Min", "RSub"};
+                           "Add", "Sub", "Mul", "Max", "Min", "RSub", "DivFast", "RDivFast"};
 const char *kCmpNames[] = {"Eq", "Ne", "Gt", "Ge", "Lt", "Le"};
 const char *kCvtNames[] = {"F2I", "I2F", "NeZ", "NeZ", "Round"};
 const char *kRedNames[] = {"Sum", "Max", "Min"};
@@ -1225,7 +1260,7 @@ std::string InsnLine(uint32_t pc, uint64_t w, DT dt, PT ptr) {
                rnd_names[DVMB_RND(w)], acc, acc);
       break;
     case OP_BIN:
-      snprintf(buf, sizeof(buf), "  %u: %s.%s%s %s, %s, %s\n", pc, kBinNames[sub], sub >= B_ADD_I ? "int32" : "fp32",
+      snprintf(buf, sizeof(buf), "  %u: %s.%s%s %s, %s, %s\n", pc, kBinNames[sub], (sub >= B_ADD_I && sub <= B_RSUB_I) ? "int32" : "fp32",
                rnd_names[DVMB_RND(w)], acc, acc, operand(w).c_str());
       break;
     case OP_CMP:

@@ -35,6 +35,20 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return r;
 }
 
+// exp through the hardware exp2 approximation: relative error about 1e-6 for |x| below 10, 5e-6 at the range ends.
+__device__ __forceinline__ float fast_exp(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x * 1.4426950408889634f));
+  return r;
+}
+
+// Full-range division with a 2-ulp bound (div.full.f32).
+__device__ __forceinline__ float fast_div(float a, float b) {
+  float r;
+  asm("div.full.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+
 template <int N>
 __device__ __forceinline__ void apply_round(uint32_t rnd, uint32_t (&a)[N]) {
   if (rnd == RN_F16) {
@@ -68,6 +82,7 @@ __device__ __forceinline__ void apply_un(uint32_t kind, uint32_t (&a)[N]) {
     case U_ABS: DVMB_UN_LOOP(fabsf(x)) break;
     case U_LOG: DVMB_UN_LOOP(logf(x)) break;
     case U_EXP: DVMB_UN_LOOP(expf(x)) break;
+    case U_EXP_FAST: DVMB_UN_LOOP(fast_exp(x)) break;
     case U_ROUND: DVMB_UN_LOOP(nearbyintf(x)) break;
     case U_FLOOR: DVMB_UN_LOOP(floorf(x)) break;
     case U_CEIL: DVMB_UN_LOOP(ceilf(x)) break;
@@ -118,6 +133,8 @@ __device__ __forceinline__ void apply_bin(uint32_t kind, uint32_t (&a)[N], const
     case B_POW: DVMB_BIN_F(powf(x, y)) break;
     case B_RSUB: DVMB_BIN_F(y - x) break;
     case B_RDIV: DVMB_BIN_F(y / x) break;
+    case B_DIV_FAST: DVMB_BIN_F(fast_div(x, y)) break;
+    case B_RDIV_FAST: DVMB_BIN_F(fast_div(y, x)) break;
     case B_ADD_I: DVMB_BIN_I((uint32_t)x + (uint32_t)y) break;
     case B_SUB_I: DVMB_BIN_I((uint32_t)x - (uint32_t)y) break;
     case B_MUL_I: DVMB_BIN_I((uint32_t)x * (uint32_t)y) break;

@@ -240,7 +240,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
   const uint32_t tid = threadIdx.x;
-  const uint32_t T = P.tg * P.groups_per_cta;   // consumer threads
+  const uint32_t T = P.tcons;   // consumer threads (a multiple of 32; threads past tg * groups_per_cta idle)
   const bool flat = P.mode == VM_FLAT;
   const uint32_t S = P.num_stages;
   const bool ring = P.stage_bytes != 0;
@@ -252,7 +252,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
     if (tid == 0) {
       for (uint32_t s = 0; s < S; ++s) {
         mbar_init(smem_base + kVmSmemBarriers + 8 * s, 1);        // full: one arrival (the producer) + tx bytes
-        mbar_init(smem_base + kVmSmemBarriers + 64 + 8 * s, T);   // empty: every consumer thread
+        mbar_init(smem_base + kVmSmemBarriers + 64 + 8 * s, T >> 5);   // empty: one arrival per consumer warp
       }
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -359,7 +359,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
   for (uint32_t gb = gb_begin; gb < ngb; gb += gb_step) {
     {
       uint32_t gi = gb * P.groups_per_cta + group_in_cta;
-      pos.gvalid = gi < P.num_groups;
+      pos.gvalid = gi < P.num_groups && group_in_cta < P.groups_per_cta && (flat || lane_in_group < tg);
       decompose_group(P, pos.gvalid ? gi : 0u, pos.k);
     }
     for (uint32_t ph = 0; ph <= P.num_body; ++ph) {
@@ -443,7 +443,8 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             ring_parity ^= 1u;
           }
         }
-        const bool full_tile = pos.chunk_valid == P.chunk_elems && pos.gvalid;
+        // every lane of this thread lies inside the chunk: the vector fast paths apply
+        const bool full_tile = pos.gvalid && pos.in_chunk0 + 3u * pos.gstep + 4u <= pos.chunk_valid;
         for (uint32_t pc = body_pc;; ++pc) {
           const uint64_t u = P.code[pc];
           const uint32_t uh = DVMB_UH(u);
@@ -518,6 +519,8 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             DV_BIN_CASES(B_DIV, DV_BINV_LANE, DV_BINS_LANE, "div.rn.f32")
             DV_BIN_CASES(B_RSUB, DV_RBINV_LANE, DV_RBINS_LANE, "sub.f32")
             DV_BIN_CASES(B_RDIV, DV_RBINV_LANE, DV_RBINS_LANE, "div.rn.f32")
+            DV_BIN_CASES(B_DIV_FAST, DV_BINV_LANE, DV_BINS_LANE, "div.full.f32")
+            DV_BIN_CASES(B_RDIV_FAST, DV_RBINV_LANE, DV_RBINS_LANE, "div.full.f32")
             DV_BIN_CASES(B_ADD_I, DV_BINV_LANE, DV_BINS_LANE, "add.s32")
             DV_BIN_CASES(B_SUB_I, DV_BINV_LANE, DV_BINS_LANE, "sub.s32")
             DV_BIN_CASES(B_MUL_I, DV_BINV_LANE, DV_BINS_LANE, "mul.lo.s32")
@@ -578,6 +581,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
               DV_SET("va", x)
               continue;
             }
+            case UH_UN_FIRST + U_EXP_FAST: asm volatile(DV_LN(DV_EXPF_LANE, "")); continue;
             case UH_UN_FIRST + U_NOP: continue;
             case UH_RND_F16: asm volatile("{\n\t.reg .b16 h;\n\t" DV_LN(DV_RNDH_LANE, "") "}"); continue;
             case UH_RND_BF16:
@@ -690,7 +694,10 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             default: continue;
           }
         }
-        if (staged_body) mbar_arrive(empty_bar);
+        if (staged_body) {
+          __syncwarp();
+          if ((tid & 31u) == 0) mbar_arrive(empty_bar);
+        }
       }
     }
   }

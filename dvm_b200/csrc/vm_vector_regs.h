@@ -28,6 +28,7 @@
 #define DV_PICKV_LANE(i, SETP) SETP " p, va" #i ", vb" #i ";\n\tselp.b32 va" #i ", va" #i ", vb" #i ", p;\n\t"
 #define DV_PICKS_LANE(i, SETP) SETP " p, va" #i ", %0;\n\tselp.b32 va" #i ", va" #i ", %0, p;\n\t"
 #define DV_UN_LANE(i, OP) OP " va" #i ", va" #i ";\n\t"
+#define DV_EXPF_LANE(i, X) "mul.f32 va" #i ", va" #i ", 0f3FB8AA3B;\n\tex2.approx.ftz.f32 va" #i ", va" #i ";\n\t"
 #define DV_ISFIN_LANE(i, X) "testp.finite.f32 p, va" #i ";\n\tselp.b32 va" #i ", 0x3f800000, 0, p;\n\t"
 #define DV_RNDH_LANE(i, X) "cvt.rn.f16.f32 h, va" #i ";\n\tcvt.f32.f16 va" #i ", h;\n\t"
 #define DV_RNDB_PAIR(a, b, X) "cvt.rn.bf16x2.f32 t, va" b ", va" a ";\n\tshl.b32 va" a ", t, 16;\n\tand.b32 va" b ", t, 0xffff0000;\n\t"

@@ -20,12 +20,17 @@ def test_fused_elementwise_shapes(shape):
 
 
 def test_config1_slice_bitwise_ops():
-    # add/mul/sub/div are IEEE-exact on both sides
+    # add/mul/sub are IEEE-exact on both sides; a division that feeds a compare stays IEEE-exact too, one that only
+    # feeds arithmetic and stores may use the 2-ulp fast form
     rng = np.random.default_rng(1)
     x = rng.uniform(-1, 1, (300, 1000)).astype(np.float32)
     y = rng.uniform(0.5, 2, (300, 1000)).astype(np.float32)
-    dev, ref, _ = run_both(lambda k, a, b: k.div(k.sub(k.mul(a, b), a), b), [x, y])
+    dev, ref, _ = run_both(lambda k, a, b: k.add(k.sub(k.mul(a, b), a), b), [x, y])
     assert_close(dev[0], ref[0], TOL_EXACT, "exact fp32 chain")
+    dev, ref, t = run_both(lambda k, a, b: (k.div(a, b), k.greater(k.div(a, b), 0.25)), [x, y])
+    assert "DivFast" in t.das() and "Div.fp32" in t.das()
+    assert_close(dev[0], ref[0], TOL_FP32, "fast division")
+    assert_close(dev[1], ref[1], TOL_EXACT, "compare of an exact division")
 
 
 @pytest.mark.parametrize("dt", [np.float16, "bf16", np.float32])
