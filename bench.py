@@ -378,12 +378,84 @@ def dynamic_shape_jit():
     return out
 
 
+def run_c5tp(args, rank, world, local_rank, dist):
+    """K-split tensor-parallel MatMul: every rank multiplies its K slice, the fp32 partial products are all-reduced
+    with NCCL, then the fused bias + GeLU kernel runs on the sum (strong scaling: the whole product is one unit)."""
+    import torch
+    import dvm_b200 as dvm
+    from dvm_b200 import sharding, workloads as W
+    a, b, bias = make_inputs("c5", scale=args.scale)
+    m, n, kdim = a.shape[0], b.shape[1], a.shape[1]
+    ar, br = sharding.ksplit_operands(a, b, rank, world)
+    del a, b
+    partial = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    k1 = dvm.PyKernel("mix", "dev", local_rank)
+    la, lb = k1.load(list(ar.shape), dvm.bfloat16), k1.load(list(br.shape), dvm.bfloat16)
+    k1.input(la, ar)
+    k1.input(lb, br)
+    s1 = k1.store(k1.cast(k1.matmul(la, lb, False, False), dvm.float32))
+    k1.bind_device(s1, partial.data_ptr(), partial.numel() * 4)
+    k1.codegen()
+    k2 = dvm.PyKernel("vector", "dev", local_rank)
+    lt, lbias = k2.load([m, n], dvm.float32), k2.load([n], dvm.bfloat16)
+    k2.bind_device(lt, partial.data_ptr(), partial.numel() * 4)
+    k2.input(lbias, bias)
+    s2 = k2.store(k2.cast(W.gelu_tanh(k2, k2.add(lt, k2.cast(lbias, dvm.float32))), dvm.bfloat16))
+    k2.codegen()
+
+    def step():
+        k1.launch()
+        if dist is not None:
+            dist.all_reduce(partial)
+        k2.launch()
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    flops = 2.0 * m * n * kdim
+    lo, hi, mean = k1.perf(warmup=2, reps=10)
+    peak, peak_src = measured_peak("c5")
+    achieved = flops / world / (mean * 1e-6) / 1e12
+    if rank == 0:
+        print(json.dumps({
+            "metric": "matmul_post_fusion_tflops", "value": flops * args.steps / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": DTYPE["c5"], "data": "synthetic",
+            "config": {"workload": WORKLOADS["c5"] + "; K split over %d ranks, fp32 partial products all-reduced with NCCL" % world,
+                       "l2": "inputs larger than L2 (no flush)", "exchange_bytes_per_rank": m * n * 4, "scale": args.scale},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": peak_src, "kernel": "dvm_b200_mm_tcgen05_pair",
+                         "us_per_launch": {"min": lo, "mean": mean, "max": hi}},
+            "gpu_launches": args.steps * 2, "clocks": clocks.summary(),
+        }))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c5tp"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the other workloads, e2e and the CPU baseline")
     ap.add_argument("--scale", type=float, default=1.0,
@@ -395,6 +467,8 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
+        if args.workload == "c5tp":
+            args.workload = "c5"
         run_reference(args, rank)
         return
 
@@ -407,6 +481,9 @@ def main():
         dist = td
 
     name = args.workload
+    if name == "c5tp":
+        run_c5tp(args, rank, world, local_rank, dist)
+        return
     wl = DeviceWorkload(name, seed_offset=1000 * rank, scale=args.scale)
     outs = [np.empty(s.shape(), wl.k.output(s).dtype) for s in wl.stores]
     work = work_of(name, wl.arrays, outs)

@@ -322,6 +322,17 @@ class _DevBuf:
             self.ptr = None
 
 
+class _ExternalBuf:
+    """Device memory owned by the caller (e.g. a torch tensor) bound to a load or store."""
+
+    def __init__(self, ptr, nbytes):
+        self.ptr = int(ptr)
+        self.nbytes = int(nbytes)
+
+    def free(self):
+        self.ptr = None
+
+
 class PyKernel(Kernel):
     """Kernel plus a device runner (RtKernelPy, src/pybind_api.h:27-119)."""
 
@@ -394,6 +405,18 @@ class PyKernel(Kernel):
         rec[2] = arr
         if arr.nbytes:
             check_rc(self._lib.dvm_rt_memcpy_h2d(rec[1].ptr, arr.ctypes.data, arr.nbytes, None), "H2D copy")
+
+    def bind_device(self, obj, ptr, nbytes):
+        """Use caller-owned device memory for a load or store (no counterpart in the reference's Python API, which
+        always copies through NumPy; the C++ API takes device pointers through RelocEntry, include/dvm.h:201-206)."""
+        for recs in (self._loads, self._stores):
+            for rec in recs:
+                if rec[0]._h == obj._h:
+                    if rec[1] is not None:
+                        rec[1].free()
+                    rec[1] = _ExternalBuf(ptr, nbytes)
+                    return
+        raise DvmError("bind_device: not a load or store of this kernel")
 
     def codegen(self, pass_names=None):
         check_rc(self._lib.dvm_normalize(self._k), "normalize")
