@@ -171,7 +171,8 @@ struct TensorDesc {
   uint8_t layout_vec;          // the layout permits vector access (vec_ok = layout_vec && aligned address)
   uint32_t ring_off;           // byte offset of this tensor's chunk inside a ring stage, or kNoRing
   uint8_t ring_layout;         // the layout permits bulk staging (ring_off is set when the address is aligned)
-  uint8_t pad[3];
+  uint8_t chunk_contig;        // every chunk is one contiguous run of this tensor (its start follows from the chunk's coordinates)
+  uint8_t pad[2];
 };
 constexpr uint32_t kNoRing = 0xffffffffu;
 // Element offsets are 32-bit: a tensor bound to the vector interpreter holds fewer than 2^31 elements.
@@ -189,6 +190,10 @@ struct VmParam {
   uint32_t chunk_elems;      // elements per chunk (<= 16 * tg; threads past the end idle)
   uint32_t stage_bytes;      // bytes of one ring stage (0: no bulk staging in this launch)
   uint32_t num_stages;
+  // resident groups: every chunk of a group keeps its own ring slot from the first phase to the last, so the
+  // group is read from global memory once; `cluster` CTAs share a group (cpc chunks each) and combine their
+  // reductions through distributed shared memory; `sets` slot sets let the next group load behind the current one
+  uint32_t resident, cluster, cpc, sets;
   uint32_t body_ring_mask[kMaxPhases];  // per BODY section: tensor slots the producer stages
   uint32_t num_temps;        // shared-memory temporaries in use
   uint32_t num_sregs;        // scalar registers in use

@@ -973,6 +973,7 @@ struct Compiler {
       td.layout_vec = layout_vec ? 1 : 0;
       // bulk staging: the chunk must be one contiguous, 16-byte aligned run of this tensor
       const bool contiguous_chunk = inner_stride == 1 && (dense || (td.mode == AM_GRANULE && chunk_in_inner));
+      td.chunk_contig = contiguous_chunk ? 1 : 0;
       const bool is_input = n->kind == N_LOAD && ((read_mask >> sidx) & 1u);
       if (is_input && !packed && contiguous_chunk && layout_bulk && (static_cast<int64_t>(P.chunk_elems) * isz) % 16 == 0 &&
           (dense ? true : chunk_in_inner)) {
@@ -1004,6 +1005,32 @@ struct Compiler {
         }
       }
     }
+    // ---- resident groups: give every chunk of a group its own slot so that later phases re-read shared memory
+    // instead of global memory; a group that does not fit one CTA is shared by a cluster of 2, 4 or 8
+    P.resident = 0;
+    P.cluster = 1;
+    P.cpc = P.chunks;
+    P.sets = 1;
+    static const bool no_resident = getenv("DVM_B200_NO_RESIDENT") != nullptr;
+    if (P.mode == VM_GROUP && !packed && stage_bytes != 0 && num_body >= 2 && !no_resident) {
+      const uint32_t budget2 = 106 * 1024, budget1 = 210 * 1024;   // shared memory of a CTA at two / one CTA per SM
+      for (uint32_t cl = 1; cl <= 8 && !P.resident; cl *= 2) {
+        const uint32_t cpc = (P.chunks + cl - 1) / cl;
+        if (cl > 1 && (P.chunks < cl || T > static_cast<uint32_t>(kVmFlatThreads))) break;
+        const uint64_t one = static_cast<uint64_t>(cpc) * stage_bytes;
+        uint32_t sets = 0;
+        if (fixed + 2 * one <= budget2) sets = 2;
+        else if (fixed + one <= budget2) sets = 1;
+        else if (cl == 1 && fixed + 2 * one <= budget1) sets = 2;
+        else if (cl >= 8 && fixed + one <= budget1) sets = 1;
+        if (sets == 0 || sets * cpc > kVmMaxSlots) continue;
+        P.resident = 1;
+        P.cluster = cl;
+        P.cpc = cpc;
+        P.sets = sets;
+        stages = sets * cpc;
+      }
+    }
     P.stage_bytes = stage_bytes;
     P.num_stages = stages;
     for (int q = 0; q < kMaxPhases; ++q) P.body_ring_mask[q] = 0;
@@ -1015,10 +1042,15 @@ struct Compiler {
     // ---- grid: persistent CTAs, as many as fit per SM
     uint32_t per_sm_cap = 2u;
     if (const char *env = getenv("DVM_B200_CTAS_PER_SM")) per_sm_cap = static_cast<uint32_t>(atoi(env));
-    uint32_t per_sm = std::max<uint32_t>(1u, std::min<uint32_t>(per_sm_cap, (220u * 1024u) / std::max<uint32_t>(out->smem_bytes + 1024u, 1u)));
+    uint32_t per_sm = std::max<uint32_t>(1u, std::min<uint32_t>(per_sm_cap, (226u * 1024u) / std::max<uint32_t>(out->smem_bytes + 1024u, 1u)));
     if (T > static_cast<uint32_t>(kVmFlatThreads)) per_sm = 1;
     const uint32_t work = P.mode == VM_FLAT ? P.chunks : (P.num_groups + P.groups_per_cta - 1) / P.groups_per_cta;
-    out->grid = std::max<uint32_t>(1u, std::min<uint32_t>(work, sms * per_sm));
+    if (P.cluster > 1) {
+      const uint32_t units = std::max<uint32_t>(1u, std::min<uint32_t>(work, sms * per_sm / P.cluster));
+      out->grid = units * P.cluster;
+    } else {
+      out->grid = std::max<uint32_t>(1u, std::min<uint32_t>(work, sms * per_sm));
+    }
     if (num_body == 0) out->grid = 1;
   }
 
@@ -1209,7 +1241,7 @@ void LowerStage(VectorStage *st) {
         case OP_ST: {
           const TensorDesc &td = P.tensor[sub];
           static const uint32_t by_dtype[] = {UH_ST_U8, UH_ST_F16, UH_ST_BF16, UH_ST_F32, UH_ST_F32};
-          push(MakeUop(td.mode == AM_DENSE && td.vec_ok ? by_dtype[td.dtype] : UH_STG, 0, sub, 0));
+          push(MakeUop(td.chunk_contig && td.vec_ok ? by_dtype[td.dtype] : UH_STG, 0, sub, 0));
           break;
         }
         default: break;
@@ -1297,9 +1329,9 @@ std::string DisassembleStage(const VectorStage &st) {
   char buf[256];
   snprintf(buf, sizeof(buf),
            "vmain.sm100(mode=%s, groups=%u, group_elems=%u, tg=%u, groups_per_cta=%u, chunk_elems=%u, chunks=%u, grid=%u, "
-           "threads=%u, smem=%u, stages=%u x %u B) {\n",
+           "threads=%u, smem=%u, stages=%u x %u B%s, cluster=%u) {\n",
            P.mode == VM_FLAT ? "flat" : "group", P.num_groups, P.group_elems, P.tg, P.groups_per_cta, P.chunk_elems, P.chunks,
-           st.grid, st.threads, st.smem_bytes, P.num_stages, P.stage_bytes);
+           st.grid, st.threads, st.smem_bytes, P.num_stages, P.stage_bytes, P.resident ? " resident" : "", P.cluster);
   o += buf;
   for (uint32_t t = 0; t < P.n_tensors; ++t) {
     const TensorDesc &td = P.tensor[t];

@@ -12,15 +12,19 @@ namespace dvmb {
 constexpr int kVmMaxThreads = 512;            // consumer threads per CTA (a producer warp is added on top)
 constexpr int kVmMinBlocks = 1;
 constexpr int kVmFlatThreads = 256;           // consumer threads of a reduce-free launch
-constexpr uint32_t kVmMaxSmemBytes = 200 * 1024;
+constexpr uint32_t kVmMaxSmemBytes = 216 * 1024;
 // dynamic shared memory layout: mbarriers, reduce scratch, then ring stages, temporaries, scalar registers
-constexpr uint32_t kVmSmemBarriers = 0;       // full[8] at +0, empty[8] at +64
-constexpr uint32_t kVmSmemRed = 128;          // float[2][32]
-constexpr uint32_t kVmSmemStages = 512;
-constexpr uint32_t kVmMaxStages = 8;
+constexpr uint32_t kVmMaxStages = 8;          // streaming ring depth
+constexpr uint32_t kVmMaxSlots = 64;          // resident slots (sets x chunks per CTA)
+constexpr uint32_t kVmSmemBarriers = 0;       // full[64] at +0, empty[64] at +512
+constexpr uint32_t kVmSmemEmpty = 512;
+constexpr uint32_t kVmSmemRed = 1024;         // float[2][32]: warp partials of a CTA-wide reduction
+constexpr uint32_t kVmSmemXPart = 1280;       // float[2]: this CTA's partial for the cluster-wide combine
+constexpr uint32_t kVmSmemXBar = 1296;        // mbarrier of the cluster-wide combine
+constexpr uint32_t kVmSmemStages = 1536;
 
 // Enqueue the vector interpreter. Returns the cudaError_t of the launch (0 = ok).
-int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, uint32_t smem_bytes, void *stream);
+int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, uint32_t smem_bytes, void *stream);   // param.cluster > 1 launches clusters
 // Device status word (0 = ok); reading clears it.
 unsigned int ReadVectorStatus();
 

@@ -80,6 +80,47 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void *src, uin
                : "memory");
 }
 
+// ---- cluster-wide combine (distributed shared memory) ------------------------------------------------
+__device__ __forceinline__ uint32_t map_shared_rank(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_remote_release(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t addr, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+    "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+    : "=r"(ok)
+    : "r"(addr), "r"(parity)
+    : "memory");
+  return ok != 0;
+}
+// Bounded like every other wait of the kernel (status code 3).
+__device__ __noinline__ void mbar_wait_cluster(uint32_t addr, uint32_t parity) {
+  for (int i = 0; i < 4096; ++i)
+    if (mbar_try_wait_cluster(addr, parity)) return;
+  unsigned long long t0, t1;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (;;) {
+    if (*reinterpret_cast<volatile unsigned int *>(&g_vm_status) != 0u) return;
+    for (int i = 0; i < 1024; ++i)
+      if (mbar_try_wait_cluster(addr, parity)) return;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    if (t1 - t0 > 2000000000ull) {
+      atomicCAS(&g_vm_status, 0u, (3u << 24) | (blockIdx.x & 0xffffffu));
+      return;
+    }
+  }
+}
+__device__ __forceinline__ float ld_shared_cluster_f32(uint32_t cluster_addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
+
 // ---- addressing -----------------------------------------------------------------------------------
 
 constexpr int kGranules = kLanes / 4;
@@ -245,17 +286,25 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
   const uint32_t S = P.num_stages;
   const bool ring = P.stage_bytes != 0;
   const uint32_t ngb = flat ? 1u : (P.num_groups + P.groups_per_cta - 1) / P.groups_per_cta;
-  const uint32_t gb_begin = flat ? 0u : blockIdx.x, gb_step = flat ? 1u : gridDim.x;
-  const uint32_t ch_begin = flat ? blockIdx.x : 0u, ch_step = flat ? gridDim.x : 1u;
+  // CTAs of a cluster share a group: CTA `rank` of unit `blockIdx.x / cluster` owns chunks [rank * cpc, ...)
+  const uint32_t cluster = P.cluster, rank = cluster > 1 ? blockIdx.x % cluster : 0u;
+  const bool resident = P.resident != 0;
+  const uint32_t gb_begin = flat ? 0u : blockIdx.x / cluster, gb_step = flat ? 1u : gridDim.x / cluster;
+  const uint32_t ch_begin = flat ? blockIdx.x : rank * P.cpc, ch_step = flat ? gridDim.x : 1u;
+  const uint32_t ch_end = flat ? P.chunks : min(P.chunks, (rank + 1u) * P.cpc);
 
-  if (ring) {
-    if (tid == 0) {
-      for (uint32_t s = 0; s < S; ++s) {
-        mbar_init(smem_base + kVmSmemBarriers + 8 * s, 1);        // full: one arrival (the producer) + tx bytes
-        mbar_init(smem_base + kVmSmemBarriers + 64 + 8 * s, T >> 5);   // empty: one arrival per consumer warp
-      }
-      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  if (tid == 0) {
+    for (uint32_t s = 0; s < S; ++s) {
+      mbar_init(smem_base + kVmSmemBarriers + 8 * s, 1);        // full: one arrival (the producer) + tx bytes
+      mbar_init(smem_base + kVmSmemEmpty + 8 * s, T >> 5);      // empty: one arrival per consumer warp
     }
+    mbar_init(smem_base + kVmSmemXBar, cluster);                 // one arrival per CTA of the cluster
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (cluster > 1) {
+    // every CTA's barriers exist before a peer signals them
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  } else {
     __syncthreads();
   }
 

@@ -129,7 +129,7 @@ def test_rmsnorm_swiglu(rows, cols):
     assert_close(dev[1], ref[1], TOL_HALF, "swiglu")
 
 
-@pytest.mark.parametrize("shape", [(4, 8, 6, 6), (16, 32, 14, 14), (8, 3, 5, 7)])
+@pytest.mark.parametrize("shape", [(4, 8, 6, 6), (16, 32, 14, 14), (8, 3, 5, 7), (32, 8, 56, 56), (42, 5, 56, 56), (70, 3, 56, 56)])
 def test_batchnorm(shape):
     rng = np.random.default_rng(2)
     n, c, hh, ww = shape
