@@ -17,6 +17,7 @@
 #include <math_constants.h>
 
 #include <cstdint>
+#include <cstring>
 
 #include "isa.h"
 #include "vm_launch.h"
@@ -133,6 +134,7 @@ struct Pos {
   uint32_t in_chunk0;     // element index of granule 0 inside its chunk
   uint32_t gstep;         // 4 * tg
   uint32_t chunk_valid;   // valid elements of the current chunk
+  uint32_t c[kMaxEnum];   // coordinates of the chunk's first element along the enumerated axes
   bool gvalid;
 };
 
@@ -313,6 +315,50 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
   // serves every S-th tile, so the address arithmetic of S tiles proceeds in parallel.
   if (tid >= T) {
     const uint32_t plane = tid - T;
+    if (resident) {
+      // Resident groups: slot set * cpc + ci holds chunk ci of this CTA for the whole group; lane (ci % 32) fills it
+      // once, when the previous occupant has been released in its last phase.
+      uint32_t mask = 0;
+      for (uint32_t ph = 0; ph < P.num_body; ++ph) mask |= P.body_ring_mask[ph];
+      uint32_t set = 0, use = 0;
+      for (uint32_t gb = gb_begin; gb < ngb; gb += gb_step) {
+        uint32_t k[kMaxKept];
+        decompose_group(P, gb, k);
+        for (uint32_t ch = ch_begin + plane; ch < ch_end; ch += 32u) {
+          const uint32_t slot = set * P.cpc + (ch - ch_begin);
+          const uint32_t full = smem_base + kVmSmemBarriers + 8 * slot;
+          mbar_wait(smem_base + kVmSmemEmpty + 8 * slot, (use & 1u) ^ 1u, 1);
+          const uint32_t e_start = ch * P.chunk_elems;
+          const uint32_t valid = min(P.chunk_elems, P.group_elems - e_start);
+          uint32_t c[kMaxEnum] = {0, 0, 0, e_start};
+          if (P.need_coords) split_enum(P, e_start, c);
+          uint32_t total = 0;
+          for (uint32_t m = mask; m; m &= m - 1) {
+            const TensorDesc &td = P.tensor[__ffs(m) - 1];
+            total += (valid << item_shift(td.dtype)) & ~15u;
+          }
+          if (total == 0) {
+            mbar_arrive(full);
+            continue;
+          }
+          mbar_arrive_expect_tx(full, total);
+          for (uint32_t m = mask; m; m &= m - 1) {
+            const TensorDesc &td = P.tensor[__ffs(m) - 1];
+            const uint32_t sh = item_shift(td.dtype);
+            const uint32_t bytes = (valid << sh) & ~15u;
+            if (bytes == 0) continue;
+            const uint32_t off = kept_offset(td, k) + enum_offset(td, c);
+            bulk_g2s(smem_base + kVmSmemStages + slot * P.stage_bytes + td.ring_off,
+                     reinterpret_cast<const uint8_t *>(td.ptr) + ((size_t)off << sh), bytes, full);
+          }
+        }
+        if (++set == P.sets) {
+          set = 0;
+          ++use;
+        }
+      }
+      return;
+    }
     if (plane >= S) return;
     const uint32_t full = smem_base + kVmSmemBarriers + 8 * plane;
     const uint32_t stage_saddr = smem_base + kVmSmemStages + plane * P.stage_bytes;
@@ -323,14 +369,14 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
       for (uint32_t ph = 0; ph < P.num_body; ++ph) {
         const uint32_t mask = P.body_ring_mask[ph];
         if (mask == 0) continue;
-        for (uint32_t ch = ch_begin; ch < P.chunks; ch += ch_step, ++seq) {
+        for (uint32_t ch = ch_begin; ch < ch_end; ch += ch_step, ++seq) {
           if (seq != next) continue;
           next += S;
           if (!have_k) {
             decompose_group(P, gb, k);   // groups_per_cta == 1 whenever the ring is on
             have_k = true;
           }
-          mbar_wait(full + 64, parity, 1);
+          mbar_wait(smem_base + kVmSmemEmpty + 8 * plane, parity, 1);
           parity ^= 1u;
           const uint32_t e_start = ch * P.chunk_elems;
           const uint32_t valid = min(P.chunk_elems, P.group_elems - e_start);
@@ -374,7 +420,11 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
   uint32_t sacc[1] = {0};
   uint32_t red_par = 0;
   uint32_t ring_stage = 0, ring_parity = 0;
+  uint32_t xphase = 0, xpar = 0;       // cluster-combine phase and buffer
+  uint32_t res_set = 0, res_use = 0;   // resident slot set of the current group and how often it was used
+  bool first_group = true;
   Pos pos;
+  pos.c[0] = pos.c[1] = pos.c[2] = pos.c[3] = 0;
   pos.gstep = 4u * tg;
   pos.in_chunk0 = 4u * lane_in_group;
 
@@ -406,6 +456,11 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
   };
 
   for (uint32_t gb = gb_begin; gb < ngb; gb += gb_step) {
+    if (!first_group && ++res_set == P.sets) {
+      res_set = 0;
+      ++res_use;
+    }
+    first_group = false;
     {
       uint32_t gi = gb * P.groups_per_cta + group_in_cta;
       pos.gvalid = gi < P.num_groups && group_in_cta < P.groups_per_cta && (flat || lane_in_group < tg);
@@ -436,7 +491,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
         switch (opc) {
           case OP_ST: {
             const TensorDesc &td = P.tensor[sub];
-            if (lane_in_group == 0 && pos.gvalid && (!flat || blockIdx.x == 0))
+            if (lane_in_group == 0 && pos.gvalid && rank == 0 && (!flat || blockIdx.x == 0))
               store_elem(td.dtype, reinterpret_cast<uint8_t *>(td.ptr), kept_offset(td, pos.k), sacc[0]);
             break;
           }
@@ -469,6 +524,20 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
               for (uint32_t wi = 1; wi < nw; ++wi) v = red_combine(kind, v, red_buf[red_par * 32 + wi]);
               red_par ^= 1u;
             }
+            if (cluster > 1) {
+              // combine the CTA totals of the cluster in rank order: publish ours, signal every CTA, read all
+              float *xpart = reinterpret_cast<float *>(smem + kVmSmemXPart);
+              if (tid == 0) {
+                xpart[xpar] = v;
+                for (uint32_t r = 0; r < cluster; ++r) mbar_arrive_remote_release(map_shared_rank(smem_base + kVmSmemXBar, r));
+              }
+              mbar_wait_cluster(smem_base + kVmSmemXBar, xphase);
+              xphase ^= 1u;
+              v = ld_shared_cluster_f32(map_shared_rank(smem_base + kVmSmemXPart + 4u * xpar, 0));
+              for (uint32_t r = 1; r < cluster; ++r)
+                v = red_combine(kind, v, ld_shared_cluster_f32(map_shared_rank(smem_base + kVmSmemXPart + 4u * xpar, r)));
+              xpar ^= 1u;
+            }
             sacc[0] = f2u(v);
             break;
           }
@@ -478,18 +547,41 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
       if (ph == P.num_body) break;
       // ---------------- vector side: BODY_ph over the chunks ----------------
       const uint32_t body_pc = P.sec[2 * ph + 1];
-      const bool staged_body = ring && P.body_ring_mask[ph] != 0;
-      for (uint32_t ch = ch_begin; ch < P.chunks; ch += ch_step) {
+      const bool staged_body = ring && (resident || P.body_ring_mask[ph] != 0);
+      const bool release_slots = !resident || ph + 1 == P.num_body;
+      for (uint32_t ch = ch_begin; ch < ch_end; ch += ch_step) {
         pos.e_start = ch * P.chunk_elems;
         pos.chunk_valid = min(P.chunk_elems, P.group_elems - pos.e_start);
+        if (!P.need_coords) {
+          pos.c[3] = pos.e_start;
+        } else if (ch == ch_begin) {
+          split_enum(P, pos.e_start, pos.c);
+        } else {
+          // chunks follow one another: advance the innermost coordinate and carry
+          pos.c[3] += ch_step * P.chunk_elems;
+#pragma unroll
+          for (int j = kMaxEnum - 1; j > 0; --j)
+            while (pos.c[j] >= P.enum_size[j]) {
+              pos.c[j] -= P.enum_size[j];
+              pos.c[j - 1] += 1u;
+            }
+        }
         uint32_t stage_saddr = 0, empty_bar = 0;
         if (staged_body) {
-          stage_saddr = smem_base + kVmSmemStages + ring_stage * P.stage_bytes;
-          empty_bar = smem_base + kVmSmemBarriers + 64 + 8 * ring_stage;
-          mbar_wait(smem_base + kVmSmemBarriers + 8 * ring_stage, ring_parity, 2);
-          if (++ring_stage == S) {
-            ring_stage = 0;
-            ring_parity ^= 1u;
+          if (resident) {
+            // the chunk's own slot: filled once per group, waited for in the first phase only
+            const uint32_t slot = res_set * P.cpc + (ch - ch_begin);
+            stage_saddr = smem_base + kVmSmemStages + slot * P.stage_bytes;
+            empty_bar = smem_base + kVmSmemEmpty + 8 * slot;
+            if (ph == 0) mbar_wait(smem_base + kVmSmemBarriers + 8 * slot, res_use & 1u, 2);
+          } else {
+            stage_saddr = smem_base + kVmSmemStages + ring_stage * P.stage_bytes;
+            empty_bar = smem_base + kVmSmemEmpty + 8 * ring_stage;
+            mbar_wait(smem_base + kVmSmemBarriers + 8 * ring_stage, ring_parity, 2);
+            if (++ring_stage == S) {
+              ring_stage = 0;
+              ring_parity ^= 1u;
+            }
           }
         }
         // every lane of this thread lies inside the chunk: the vector fast paths apply
@@ -499,7 +591,8 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
           const uint32_t uh = DVMB_UH(u);
           const uint32_t aux = DVMB_UAUX(u);
           const uint32_t arg = DVMB_UARG(u);
-          if (uh == UH_END) break;
+          // a thread without a single lane inside the chunk has nothing to fetch, add or store
+          if (uh == UH_END || !pos.gvalid || pos.in_chunk0 >= pos.chunk_valid) break;
           uint32_t slot;
           switch (uh) {
             // ---------------- operand fetches ----------------
@@ -702,7 +795,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             case UH_ST_F32: {
               if (!full_tile) goto store_generic;
               const TensorDesc &td = P.tensor[arg];
-              uint32_t *p0 = reinterpret_cast<uint32_t *>(td.ptr) + kept_offset(td, pos.k) + pos.e_start + pos.in_chunk0;
+              uint32_t *p0 = reinterpret_cast<uint32_t *>(td.ptr) + kept_offset(td, pos.k) + enum_offset(td, pos.c) + pos.in_chunk0;
               const uint32_t gs = pos.gstep;
               asm volatile("st.global.v4.b32 [%0], {va0,va1,va2,va3};\n\tst.global.v4.b32 [%1], {va4,va5,va6,va7};\n\t"
                            "st.global.v4.b32 [%2], {va8,va9,va10,va11};\n\tst.global.v4.b32 [%3], {va12,va13,va14,va15};" ::"l"(p0),
@@ -714,7 +807,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             case UH_ST_BF16: {
               if (!full_tile) goto store_generic;
               const TensorDesc &td = P.tensor[arg];
-              unsigned short *p0 = reinterpret_cast<unsigned short *>(td.ptr) + kept_offset(td, pos.k) + pos.e_start + pos.in_chunk0;
+              unsigned short *p0 = reinterpret_cast<unsigned short *>(td.ptr) + kept_offset(td, pos.k) + enum_offset(td, pos.c) + pos.in_chunk0;
               const uint32_t gs = pos.gstep;
 #define DV_ST16(CVT)                                                                                          \
   asm volatile("{\n\t.reg .b32 t0, t1;\n\t"                                                                   \
@@ -743,12 +836,18 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             default: continue;
           }
         }
-        if (staged_body) {
+        if (staged_body && release_slots) {
           __syncwarp();
           if ((tid & 31u) == 0) mbar_arrive(empty_bar);
         }
       }
     }
+  }
+  if (cluster > 1) {
+    // no CTA leaves while a peer may still read its partials
+    if (tid == 0)
+      for (uint32_t r = 0; r < cluster; ++r) mbar_arrive_remote_release(map_shared_rank(smem_base + kVmSmemXBar, r));
+    mbar_wait_cluster(smem_base + kVmSmemXBar, xphase);
   }
 }
 }  // namespace
@@ -773,11 +872,24 @@ int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, uint32_t
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set[dev] = true;
   }
-  if (threads <= kVmFlatThreads + 32) {
-    dvm_b200_vm_vector<<<grid, threads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(param);
-  } else {
-    dvm_b200_vm_vector_wide<<<grid, threads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(param);
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(threads, 1, 1);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  if (param.cluster > 1) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = param.cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
   }
+  cudaError_t le = threads <= kVmFlatThreads + 32 ? cudaLaunchKernelEx(&cfg, dvm_b200_vm_vector, param)
+                                                   : cudaLaunchKernelEx(&cfg, dvm_b200_vm_vector_wide, param);
+  if (le != cudaSuccess) return static_cast<int>(le);
   return static_cast<int>(cudaGetLastError());
 }
 
