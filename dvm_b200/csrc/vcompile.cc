@@ -1011,7 +1011,8 @@ struct Compiler {
     P.cluster = 1;
     P.cpc = P.chunks;
     P.sets = 1;
-    static const bool no_resident = getenv("DVM_B200_NO_RESIDENT") != nullptr;
+    // measured slower than re-streaming from L2 on the shapes tried so far: opt-in until the resident loop is leaner
+    static const bool no_resident = getenv("DVM_B200_RESIDENT") == nullptr;
     if (P.mode == VM_GROUP && !packed && stage_bytes != 0 && num_body >= 2 && !no_resident) {
       const uint32_t budget2 = 106 * 1024, budget1 = 210 * 1024;   // shared memory of a CTA at two / one CTA per SM
       for (uint32_t cl = 1; cl <= 8 && !P.resident; cl *= 2) {

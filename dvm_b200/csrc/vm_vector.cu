@@ -134,7 +134,6 @@ struct Pos {
   uint32_t in_chunk0;     // element index of granule 0 inside its chunk
   uint32_t gstep;         // 4 * tg
   uint32_t chunk_valid;   // valid elements of the current chunk
-  uint32_t c[kMaxEnum];   // coordinates of the chunk's first element along the enumerated axes
   bool gvalid;
 };
 
@@ -276,6 +275,7 @@ __device__ __forceinline__ void decompose_group(const VmParam &P, uint32_t gi, u
 }  // namespace
 
 namespace {
+template <bool kResident, bool kCoords>
 __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
   asm volatile(DV_DECLARE);
   asm volatile(DV_LN(DV_SPLATLANE, "va") DV_LN(DV_SPLATLANE, "vb") DV_LN(DV_SPLATLANE, "vc")
@@ -289,8 +289,9 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
   const bool ring = P.stage_bytes != 0;
   const uint32_t ngb = flat ? 1u : (P.num_groups + P.groups_per_cta - 1) / P.groups_per_cta;
   // CTAs of a cluster share a group: CTA `rank` of unit `blockIdx.x / cluster` owns chunks [rank * cpc, ...)
-  const uint32_t cluster = P.cluster, rank = cluster > 1 ? blockIdx.x % cluster : 0u;
-  const bool resident = P.resident != 0;
+  // (only the resident instantiation carries the cluster / slot bookkeeping: the streaming one keeps its registers)
+  const uint32_t cluster = kResident ? P.cluster : 1u, rank = cluster > 1 ? blockIdx.x % cluster : 0u;
+  const bool resident = kResident;
   const uint32_t gb_begin = flat ? 0u : blockIdx.x / cluster, gb_step = flat ? 1u : gridDim.x / cluster;
   const uint32_t ch_begin = flat ? blockIdx.x : rank * P.cpc, ch_step = flat ? gridDim.x : 1u;
   const uint32_t ch_end = flat ? P.chunks : min(P.chunks, (rank + 1u) * P.cpc);
@@ -424,7 +425,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
   uint32_t res_set = 0, res_use = 0;   // resident slot set of the current group and how often it was used
   bool first_group = true;
   Pos pos;
-  pos.c[0] = pos.c[1] = pos.c[2] = pos.c[3] = 0;
+  uint32_t cc[kMaxEnum] = {0, 0, 0, 0};   // coordinates of the chunk's first element (only when some tensor needs them)
   pos.gstep = 4u * tg;
   pos.in_chunk0 = 4u * lane_in_group;
 
@@ -552,19 +553,19 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
       for (uint32_t ch = ch_begin; ch < ch_end; ch += ch_step) {
         pos.e_start = ch * P.chunk_elems;
         pos.chunk_valid = min(P.chunk_elems, P.group_elems - pos.e_start);
-        if (!P.need_coords) {
-          pos.c[3] = pos.e_start;
-        } else if (ch == ch_begin) {
-          split_enum(P, pos.e_start, pos.c);
-        } else {
-          // chunks follow one another: advance the innermost coordinate and carry
-          pos.c[3] += ch_step * P.chunk_elems;
+        if (kCoords && P.need_coords) {
+          if (ch == ch_begin) {
+            split_enum(P, pos.e_start, cc);
+          } else {
+            // chunks follow one another: advance the innermost coordinate and carry
+            cc[3] += ch_step * P.chunk_elems;
 #pragma unroll
-          for (int j = kMaxEnum - 1; j > 0; --j)
-            while (pos.c[j] >= P.enum_size[j]) {
-              pos.c[j] -= P.enum_size[j];
-              pos.c[j - 1] += 1u;
-            }
+            for (int j = kMaxEnum - 1; j > 0; --j)
+              while (cc[j] >= P.enum_size[j]) {
+                cc[j] -= P.enum_size[j];
+                cc[j - 1] += 1u;
+              }
+          }
         }
         uint32_t stage_saddr = 0, empty_bar = 0;
         if (staged_body) {
@@ -586,13 +587,14 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
         }
         // every lane of this thread lies inside the chunk: the vector fast paths apply
         const bool full_tile = pos.gvalid && pos.in_chunk0 + 3u * pos.gstep + 4u <= pos.chunk_valid;
-        for (uint32_t pc = body_pc;; ++pc) {
+        // a thread without a single lane inside the chunk has nothing to fetch, add or store
+        const bool lane_active = pos.gvalid && 4u * lane_in_group < pos.chunk_valid;
+        for (uint32_t pc = lane_active ? body_pc : P.n_code - 1u;; ++pc) {
           const uint64_t u = P.code[pc];
           const uint32_t uh = DVMB_UH(u);
           const uint32_t aux = DVMB_UAUX(u);
           const uint32_t arg = DVMB_UARG(u);
-          // a thread without a single lane inside the chunk has nothing to fetch, add or store
-          if (uh == UH_END || !pos.gvalid || pos.in_chunk0 >= pos.chunk_valid) break;
+          if (uh == UH_END) break;
           uint32_t slot;
           switch (uh) {
             // ---------------- operand fetches ----------------
@@ -795,7 +797,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             case UH_ST_F32: {
               if (!full_tile) goto store_generic;
               const TensorDesc &td = P.tensor[arg];
-              uint32_t *p0 = reinterpret_cast<uint32_t *>(td.ptr) + kept_offset(td, pos.k) + enum_offset(td, pos.c) + pos.in_chunk0;
+              uint32_t *p0 = reinterpret_cast<uint32_t *>(td.ptr) + kept_offset(td, pos.k) + (!kCoords || td.mode == AM_DENSE ? pos.e_start : enum_offset(td, cc)) + pos.in_chunk0;
               const uint32_t gs = pos.gstep;
               asm volatile("st.global.v4.b32 [%0], {va0,va1,va2,va3};\n\tst.global.v4.b32 [%1], {va4,va5,va6,va7};\n\t"
                            "st.global.v4.b32 [%2], {va8,va9,va10,va11};\n\tst.global.v4.b32 [%3], {va12,va13,va14,va15};" ::"l"(p0),
@@ -807,7 +809,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             case UH_ST_BF16: {
               if (!full_tile) goto store_generic;
               const TensorDesc &td = P.tensor[arg];
-              unsigned short *p0 = reinterpret_cast<unsigned short *>(td.ptr) + kept_offset(td, pos.k) + enum_offset(td, pos.c) + pos.in_chunk0;
+              unsigned short *p0 = reinterpret_cast<unsigned short *>(td.ptr) + kept_offset(td, pos.k) + (!kCoords || td.mode == AM_DENSE ? pos.e_start : enum_offset(td, cc)) + pos.in_chunk0;
               const uint32_t gs = pos.gstep;
 #define DV_ST16(CVT)                                                                                          \
   asm volatile("{\n\t.reg .b32 t0, t1;\n\t"                                                                   \
@@ -854,21 +856,30 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
 
 // Two register budgets of the same interpreter: up to 256 consumer threads with two CTAs per SM (the
 // streaming shapes), and up to 512 consumer threads (long reduction rows) with one.
-__global__ void __launch_bounds__(kVmFlatThreads + 32, 2) dvm_b200_vm_vector(const __grid_constant__ VmParam P) {
-  vm_vector_body(P);
-}
-__global__ void __launch_bounds__(kVmMaxThreads + 32, 1) dvm_b200_vm_vector_wide(const __grid_constant__ VmParam P) {
-  vm_vector_body(P);
-}
+#define DVMB_VM_KERNEL(NAME, THREADS, BLOCKS, RES, COORDS)                                                       \
+  __global__ void __launch_bounds__(THREADS, BLOCKS) NAME(const __grid_constant__ VmParam P) {                    \
+    vm_vector_body<RES, COORDS>(P);                                                                                \
+  }
+// dense layouts (every chunk starts at group offset + element index)
+DVMB_VM_KERNEL(dvm_b200_vm_vector, kVmFlatThreads + 32, 2, false, false)
+DVMB_VM_KERNEL(dvm_b200_vm_vector_wide, kVmMaxThreads + 32, 1, false, false)
+// strided layouts: chunk starts follow from the chunk's coordinates along the iterated axes
+DVMB_VM_KERNEL(dvm_b200_vm_vector_nd, kVmFlatThreads + 32, 2, false, true)
+DVMB_VM_KERNEL(dvm_b200_vm_vector_nd_wide, kVmMaxThreads + 32, 1, false, true)
+// resident groups (and clusters): every chunk of a group keeps a shared-memory slot for all phases
+DVMB_VM_KERNEL(dvm_b200_vm_vector_res, kVmFlatThreads + 32, 2, true, true)
+DVMB_VM_KERNEL(dvm_b200_vm_vector_res_wide, kVmMaxThreads + 32, 1, true, true)
+#undef DVMB_VM_KERNEL
 
 int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, uint32_t smem_bytes, void *stream) {
   static bool attr_set[64] = {false};   // the attribute is per device
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(dvm_b200_vm_vector, cudaFuncAttributeMaxDynamicSharedMemorySize, kVmMaxSmemBytes);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(dvm_b200_vm_vector_wide, cudaFuncAttributeMaxDynamicSharedMemorySize, kVmMaxSmemBytes);
+    cudaError_t e = cudaSuccess;
+    for (auto fn : {dvm_b200_vm_vector, dvm_b200_vm_vector_wide, dvm_b200_vm_vector_nd, dvm_b200_vm_vector_nd_wide,
+                    dvm_b200_vm_vector_res, dvm_b200_vm_vector_res_wide})
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kVmMaxSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set[dev] = true;
   }
@@ -887,8 +898,14 @@ int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, uint32_t
     cfg.attrs = attr;
     cfg.numAttrs = 1;
   }
-  cudaError_t le = threads <= kVmFlatThreads + 32 ? cudaLaunchKernelEx(&cfg, dvm_b200_vm_vector, param)
-                                                   : cudaLaunchKernelEx(&cfg, dvm_b200_vm_vector_wide, param);
+  const bool narrow = threads <= kVmFlatThreads + 32;
+  auto kernel = narrow ? dvm_b200_vm_vector : dvm_b200_vm_vector_wide;
+  if (param.resident) {
+    kernel = narrow ? dvm_b200_vm_vector_res : dvm_b200_vm_vector_res_wide;
+  } else if (param.need_coords) {
+    kernel = narrow ? dvm_b200_vm_vector_nd : dvm_b200_vm_vector_nd_wide;
+  }
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, kernel, param);
   if (le != cudaSuccess) return static_cast<int>(le);
   return static_cast<int>(cudaGetLastError());
 }
