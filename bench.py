@@ -211,10 +211,70 @@ def cpu_baseline(name, budget_s=12.0):
             "sample": "%s, best of %d NumPy evaluations" % (what, reps)}
 
 
+def reference_cuda(name, scale=1.0):
+    """The same graph on the reference's own CUDA backend (oracle/_ref, built from the reference tree by
+    oracle/build_ref.py): returns (kernel builder, arrays, outputs) or None when the module is absent, no device is
+    usable, or the graph needs an op the reference's GPU backend lacks (MatMul, ReduceMax: src/system.cc:290-294)."""
+    if name not in ("c1", "c2", "c3"):
+        return None
+    try:
+        from oracle import ref_backend
+        if ref_backend.module() is None:
+            return None
+        arrays = make_inputs(name, scale=scale)
+        k = ref_backend.RefKernel("vector" if name == "c1" else "split")
+        loads = [k.load(a) for a in arrays]
+        stores = [k.store(v) for v in build_graph(k, name, loads, arrays)]
+        k.run()
+        outs = [k.output(s) for s in stores]
+        return k, arrays, outs
+    except Exception as e:   # an unusable reference must not take the benchmark down
+        sys.stderr.write("reference CUDA backend unavailable for %s: %s\n" % (name, e))
+        return None
+
+
+def run_reference_cuda(args, name):
+    """Reference arm on the reference's own CUDA backend: K launches of its kernels for the same graph and inputs."""
+    import torch
+    got = reference_cuda(name)
+    if got is None:
+        return False
+    k, arrays, outs = got
+    for _ in range(args.warmup):
+        k.k.run()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        k.k.run()   # launches every kernel of the split graph and waits for the stream
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    work = work_of(name, arrays, outs)
+    v = work * args.steps / dt / unit_scale(name)
+    lo, hi, mean = k.perf()
+    print(json.dumps({
+        "impl": "reference", "metric": metric_of(name), "value": v, "unit": unit_of(name), "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": DTYPE[name], "data": "synthetic",
+        "config": {"workload": WORKLOADS[name], "note": "the reference's own CUDA backend (src/vm_gpu.cu compiled for sm_100a "
+                   "from the reference tree), same graph through its Python module, inputs resident; kernel time by its perf(): "
+                   "%.1f us mean" % mean},
+        "cpu_baseline": {"value": v, "unit": unit_of(name), "cores": 1, "kind": "reference",
+                         "sample": "the full workload on the GPU through the reference's CUDA backend"},
+        "e2e": {"value": v, "unit": unit_of(name), "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+    return True
+
+
 def run_reference(args, rank):
     if rank != 0:
         return
     name = args.workload
+    try:
+        import torch
+        if torch.cuda.is_available() and run_reference_cuda(args, name):
+            return
+    except Exception as e:
+        sys.stderr.write("falling back to the NumPy evaluation: %s\n" % e)
     arrays, what = cpu_sample(name)
     outs = None
     for _ in range(args.warmup):
@@ -529,6 +589,17 @@ def main():
                     others[other] = device_summary(other)
             line["other_workloads"] = others
             line["dynamic_shape_jit_c3"] = dynamic_shape_jit()
+            # second comparison: the reference's own CUDA backend on the same GPU (kernel time by its perf())
+            ref = {}
+            for other in ("c1", "c2", "c3"):
+                got = reference_cuda(other)
+                if got is not None:
+                    lo_r, hi_r, mean_r = got[0].perf()
+                    ref[other] = {"us_per_run": mean_r, "rate": work_of(other, got[1], got[2]) / (mean_r * 1e-6) / unit_scale(other),
+                                  "unit": unit_of(other), "kernels": got[0].k.das().count("vmain")}
+                    got[0].k.release_io()
+                del got
+            line["reference_cuda_backend"] = ref or "not available"
     if rank == 0:
         print(json.dumps(line))
     if dist is not None:

@@ -1,6 +1,6 @@
 """Adapter over the reference's own `_dvm_py` module (built by oracle/build_ref.py into oracle/_ref/) so that the
 graph definitions of the parity tests can be evaluated by the reference's CUDA backend on the same GPU.
-Test infrastructure only: nothing in the product imports it."""
+Test and benchmark-baseline infrastructure only: nothing in the product imports it."""
 import glob
 import importlib.util
 import os
@@ -38,12 +38,16 @@ class RefKernel:
 
     def load(self, array, dtype=None):
         array = np.ascontiguousarray(array)
-        if dtype is None:
+        if dtype is None and str(array.dtype) == "bfloat16":
+            code = 2
+        elif dtype is None:
             code = {np.dtype(np.bool_): 0, np.dtype(np.float16): 1, np.dtype(np.float32): 3, np.dtype(np.int32): 4}[array.dtype]
         else:
             code = int(dtype)
         if code == 2 and array.dtype == np.float32:
             array = self.k.convert_to_bf16(array)
+        elif code == 2:
+            array = array.view(np.uint16)   # the reference moves bf16 as raw 16-bit words
         elif code == 1:
             array = array.astype(np.float16)
         op = self.k.load(list(array.shape), self._dt(code))

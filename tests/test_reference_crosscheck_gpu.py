@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 from dvm_b200 import workloads as W
-from tests import ref_backend
+from oracle import ref_backend
 from tests.util import TOL_EXACT, TOL_FP32, TOL_HALF, TOL_REDUCE, assert_close
 
 pytestmark = [pytest.mark.gpu, pytest.mark.skipif(ref_backend.module() is None, reason="oracle/_ref/_dvm_py was not built")]
