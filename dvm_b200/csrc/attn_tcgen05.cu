@@ -89,6 +89,34 @@ __device__ __forceinline__ void round_pair(float &a, float &b) {
   }
 }
 
+// Packed 2 x 16-bit arithmetic in the operand type: the product of two bf16 / fp16 values rounded once to that type
+// is exactly "multiply in fp32, round to the type", the graph's scaled score.
+template <uint32_t DT>
+__device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  if (DT == T_BF16) {
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  } else {
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  }
+  return r;
+}
+template <uint32_t DT>
+__device__ __forceinline__ uint32_t max2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  if (DT == T_BF16) {
+    asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  } else {
+    asm("max.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  }
+  return r;
+}
+template <uint32_t DT>
+__device__ __forceinline__ float2 unpack2(uint32_t p) {
+  if (DT == T_BF16) return make_float2(__uint_as_float(p << 16), __uint_as_float(p & 0xffff0000u));
+  return __half22float2(*reinterpret_cast<const __half2 *>(&p));
+}
+
 __device__ __forceinline__ uint32_t pack_pair(uint32_t dtype, float lo, float hi) {
   if (dtype == T_BF16) return pack_bf16x2(lo, hi);
   const __half2 h = __floats2half2_rn(lo, hi);
@@ -143,11 +171,14 @@ __device__ __forceinline__ void attention_body(const AttnParam &P, const AttnMap
         for (uint32_t h = 0; h < dhalves; ++h)
           tma_load_3d(base + kOffQ + g * kTileBytes + h * kHalfBytes, &maps.q, base + kBarQ, (int)(h * 64),
                       (int)(q_row0 + g * kTileQ), (int)bz);
-      // ring order: K0 V0 K1 V1 ...
+      // ring order = order of need: K0, then per key tile j: K(j+1) (its scores are issued early), V(j)
       uint32_t slot = 0, parity = 1;
-      for (uint32_t i = 0; i < 2 * nkv; ++i) {
-        const uint32_t j = i >> 1;
-        const CUtensorMap *map = (i & 1u) ? &maps.v : &maps.k;
+      const uint32_t ntiles = 2 * nkv;
+      for (uint32_t p = 0; p < ntiles; ++p) {
+        // position p holds: K0 at 0; K(j) at 2j - 1; V(j) at 2j + 2, except the last V at 2 nkv - 1
+        const bool is_v = p != 0 && ((p & 1u) == 0 || p == ntiles - 1);
+        const uint32_t j = p == 0 ? 0u : (is_v ? (p == ntiles - 1 ? nkv - 1 : (p - 2) / 2) : (p + 1) / 2);
+        const CUtensorMap *map = is_v ? &maps.v : &maps.k;
         mbar_wait(base + kBarKvEmpty + 8 * slot, parity, 1, &g_attn_status);
         mbar_expect_tx(base + kBarKvFull + 8 * slot, tile_bytes);
         for (uint32_t h = 0; h < dhalves; ++h)
@@ -168,13 +199,6 @@ __device__ __forceinline__ void attention_body(const AttnParam &P, const AttnMap
       // O += P V: V is stored [key][d] (the contraction axis outermost); N = d
       const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((P.d >> 3) << 17) | ((kTileQ >> 4) << 24);
       const uint32_t ksteps_s = P.d / 16;
-      uint32_t slot = 0, kv_parity = 0;   // ring position of the next tile to consume
-      auto advance = [&]() {
-        if (++slot == kRingSlots) {
-          slot = 0;
-          kv_parity ^= 1u;
-        }
-      };
       auto issue_s = [&](uint32_t g, uint32_t kslot) {
         const uint32_t qa = base + kOffQ + g * kTileBytes, kb = base + kOffRing + kslot * kTileBytes;
         for (uint32_t kk = 0; kk < ksteps_s; ++kk) {
@@ -193,34 +217,60 @@ __device__ __forceinline__ void attention_body(const AttnParam &P, const AttnMap
         }
         umma_commit_cta1(base + kBarPvDone + 8 * g);
       };
+      // ring position of K(j) / V(j) (see the producer) -> slot and phase parity
+      const uint32_t ntiles = 2 * nkv;
+      auto k_pos = [&](uint32_t j) { return j == 0 ? 0u : 2 * j - 1; };
+      auto v_pos = [&](uint32_t j) { return j + 1 < nkv ? 2 * j + 2 : ntiles - 1; };
+      auto full_ready = [&](uint32_t pos) { return mbar_try_wait(base + kBarKvFull + 8 * (pos % kRingSlots), (pos / kRingSlots) & 1u); };
+      auto release = [&](uint32_t pos) { umma_commit_cta1(base + kBarKvEmpty + 8 * (pos % kRingSlots)); };
       mbar_wait(base + kBarQ, 0, 2, &g_attn_status);
       // prologue: scores of key tile 0 for both row tiles
-      mbar_wait(base + kBarKvFull + 8 * slot, kv_parity, 3, &g_attn_status);
+      mbar_wait(base + kBarKvFull, 0, 3, &g_attn_status);
       tcgen05_after_sync();
-      issue_s(0, slot);
-      issue_s(1, slot);
-      umma_commit_cta1(base + kBarKvEmpty + 8 * slot);
-      advance();
-      for (uint32_t j = 0; j < nkv; ++j) {
-        const uint32_t vslot = slot, v_parity = kv_parity;
-        advance();
-        const uint32_t kslot = slot, k_parity = kv_parity;
-        const bool more = j + 1 < nkv;
-        if (more) advance();
+      issue_s(0, 0);
+      issue_s(1, 0);
+      release(0);
+      // Event-driven issue: the scores of the next key tile go out as soon as the softmax warps have taken the
+      // current ones into registers (so a tile's softmax never waits for its own scores), P V as soon as P is in
+      // shared memory.  Bounded: gives up after about two seconds without progress.
+      uint32_t s_issued[2] = {1, 1}, pv_issued[2] = {0, 0};
+      unsigned long long t_last;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_last));
+      uint32_t idle = 0;
+      while (pv_issued[0] < nkv || pv_issued[1] < nkv) {
+        bool progress = false;
+#pragma unroll
         for (uint32_t g = 0; g < 2; ++g) {
-          mbar_wait(base + kBarPReady + 8 * g, j & 1u, 4, &g_attn_status);
-          if (g == 0) mbar_wait(base + kBarKvFull + 8 * vslot, v_parity, 5, &g_attn_status);
-          tcgen05_after_sync();
-          issue_pv(g, vslot, j != 0);
-          if (g == 1) umma_commit_cta1(base + kBarKvEmpty + 8 * vslot);
-          if (more) {
-            if (g == 0) mbar_wait(base + kBarKvFull + 8 * kslot, k_parity, 6, &g_attn_status);
-            mbar_wait(base + kBarSFree + 8 * g, j & 1u, 7, &g_attn_status);
+          const uint32_t js = s_issued[g];
+          if (js < nkv && js <= pv_issued[g] + 1 && mbar_try_wait(base + kBarSFree + 8 * g, (js - 1) & 1u) && full_ready(k_pos(js))) {
             tcgen05_after_sync();
-            issue_s(g, kslot);
-            if (g == 1) umma_commit_cta1(base + kBarKvEmpty + 8 * kslot);
+            issue_s(g, k_pos(js) % kRingSlots);
+            s_issued[g] = js + 1;
+            if (s_issued[g ^ 1u] > js) release(k_pos(js));   // both row tiles have read K(js)
+            progress = true;
+          }
+          const uint32_t jp = pv_issued[g];
+          if (jp < nkv && jp < s_issued[g] && mbar_try_wait(base + kBarPReady + 8 * g, jp & 1u) && full_ready(v_pos(jp))) {
+            tcgen05_after_sync();
+            issue_pv(g, v_pos(jp) % kRingSlots, jp != 0);
+            pv_issued[g] = jp + 1;
+            if (pv_issued[g ^ 1u] > jp) release(v_pos(jp));
+            progress = true;
           }
         }
+        if (progress) {
+          idle = 0;
+        } else if (++idle >= 4096) {
+          idle = 0;
+          unsigned long long t_now;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_now));
+          if (*reinterpret_cast<volatile unsigned int *>(&g_attn_status) != 0u) break;
+          if (idle == 0 && t_now - t_last > 2000000000ull) {
+            atomicCAS(&g_attn_status, 0u, (11u << 24) | (blockIdx.x & 0xffffffu));
+            break;
+          }
+        }
+        if (progress) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_last));
       }
     }
   } else {
@@ -239,60 +289,94 @@ __device__ __forceinline__ void attention_body(const AttnParam &P, const AttnMap
       mbar_wait(base + kBarSFull + 8 * g, j & 1u, 8, &g_attn_status);
       tcgen05_after_sync();
       uint32_t s[128];
-      {
-        uint32_t t[32];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          tmem_ld_32x32b_x32(t_s + c * 32, t);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) s[c * 32 + i] = t[i];
-        }
-      }
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32_nowait(t_s + c * 32, &s[c * 32]);   // four loads in flight, one wait
+      tmem_ld_wait();
       tcgen05_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(base + kBarSFree + 8 * g);
-      // score in the graph's precision (rounded as the MatMul result, scaled), kept in the log2 domain
       const uint32_t kv_valid = min(kTileKV, P.skv - j * kTileKV);
-      const float c2 = SCALE_FIRST ? kLog2e : scale * kLog2e;
-#pragma unroll
-      for (int i = 0; i < 128; i += 2) {
-        float x0 = u2f(s[i]), x1 = u2f(s[i + 1]);
-        round_pair<DT>(x0, x1);
-        if (SCALE_FIRST) {
-          x0 *= scale;
-          x1 *= scale;
-          round_pair<DT>(x0, x1);
-        }
-        s[i] = f2u(x0 * c2);
-        s[i + 1] = f2u(x1 * c2);
-      }
-      if (kv_valid < kTileKV) {   // the last key tile: mask what lies past the sequence
-#pragma unroll
-        for (int i = 0; i < 128; ++i)
-          if ((uint32_t)i >= kv_valid) s[i] = 0xff800000u;
-      }
-      float mx = -CUDART_INF_F;
-#pragma unroll
-      for (int i = 0; i < 128; ++i) mx = fmaxf(mx, u2f(s[i]));
       float alpha = 1.0f;
       bool rescale = false;
-      if (mx > m_used + kRescaleThreshold * kLog2e || m_used == -CUDART_INF_F) {
-        alpha = m_used == -CUDART_INF_F ? 0.0f : fast_exp2(m_used - mx);
-        rescale = j != 0;
-        m_used = mx;
-        l *= alpha;
-      }
-      float sum0 = 0.0f, sum1 = 0.0f;
       uint32_t pk[64];
+      if (SCALE_FIRST) {
+        // The graph's order (score rounded to the operand type, scaled in that type) in packed 16-bit arithmetic:
+        // one conversion packs and rounds two scores, one packed multiply scales and rounds them again.
+        const uint32_t scale2 = pack_pair(DT, scale, scale);
+        const uint32_t ninf2 = DT == T_BF16 ? 0xff80ff80u : 0xfc00fc00u;
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const float p0 = fast_exp2(u2f(s[2 * i]) - m_used);
-        const float p1 = fast_exp2(u2f(s[2 * i + 1]) - m_used);
-        sum0 += p0;
-        sum1 += p1;
-        pk[i] = pack_pair(DT, p0, p1);
+        for (int i = 0; i < 64; ++i) pk[i] = mul2<DT>(pack_pair(DT, u2f(s[2 * i]), u2f(s[2 * i + 1])), scale2);
+        if (kv_valid < kTileKV) {   // the last key tile: mask what lies past the sequence
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            if ((uint32_t)(2 * i + 1) >= kv_valid) pk[i] = (pk[i] & 0x0000ffffu) | (ninf2 & 0xffff0000u);
+            if ((uint32_t)(2 * i) >= kv_valid) pk[i] = ninf2;
+          }
+        }
+        uint32_t m8[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) m8[c] = pk[c];
+#pragma unroll
+        for (int i = 8; i < 64; ++i) m8[i & 7] = max2<DT>(m8[i & 7], pk[i]);
+        const float2 mm = unpack2<DT>(max2<DT>(max2<DT>(max2<DT>(m8[0], m8[1]), max2<DT>(m8[2], m8[3])),
+                                               max2<DT>(max2<DT>(m8[4], m8[5]), max2<DT>(m8[6], m8[7]))));
+        const float mx = fmaxf(mm.x, mm.y) * kLog2e;   // running maximum kept in the log2 domain
+        if (mx > m_used + kRescaleThreshold * kLog2e || m_used == -CUDART_INF_F) {
+          alpha = m_used == -CUDART_INF_F ? 0.0f : fast_exp2(m_used - mx);
+          rescale = j != 0;
+          m_used = mx;
+          l *= alpha;
+        }
+        float sum8[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+        const float mneg = -m_used;
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const float2 x = unpack2<DT>(pk[i]);
+          const float p0 = fast_exp2(fmaf(x.x, kLog2e, mneg));
+          const float p1 = fast_exp2(fmaf(x.y, kLog2e, mneg));
+          sum8[(2 * i) & 7] += p0;
+          sum8[(2 * i + 1) & 7] += p1;
+          pk[i] = pack_pair(DT, p0, p1);
+        }
+        l += ((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7]));
+      } else {
+        // scale applied in fp32 after the cast: round the score once, keep it in the log2 domain
+        const float c2 = scale * kLog2e;
+#pragma unroll
+        for (int i = 0; i < 128; i += 2) {
+          float x0 = u2f(s[i]), x1 = u2f(s[i + 1]);
+          round_pair<DT>(x0, x1);
+          s[i] = f2u(x0 * c2);
+          s[i + 1] = f2u(x1 * c2);
+        }
+        if (kv_valid < kTileKV) {
+#pragma unroll
+          for (int i = 0; i < 128; ++i)
+            if ((uint32_t)i >= kv_valid) s[i] = 0xff800000u;
+        }
+        float mx8[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) mx8[c] = u2f(s[c]);
+#pragma unroll
+        for (int i = 8; i < 128; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], u2f(s[i]));
+        const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+        if (mx > m_used + kRescaleThreshold * kLog2e || m_used == -CUDART_INF_F) {
+          alpha = m_used == -CUDART_INF_F ? 0.0f : fast_exp2(m_used - mx);
+          rescale = j != 0;
+          m_used = mx;
+          l *= alpha;
+        }
+        float sum8[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const float p0 = fast_exp2(u2f(s[2 * i]) - m_used);
+          const float p1 = fast_exp2(u2f(s[2 * i + 1]) - m_used);
+          sum8[(2 * i) & 7] += p0;
+          sum8[(2 * i + 1) & 7] += p1;
+          pk[i] = pack_pair(DT, p0, p1);
+        }
+        l += ((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7]));
       }
-      l += sum0 + sum1;
       // P_g and O_g are free once the previous P V of this tile has completed
       if (j != 0) {
         mbar_wait(base + kBarPvDone + 8 * g, (j - 1) & 1u, 9, &g_attn_status);

@@ -39,7 +39,7 @@ struct MmParam {
   uint32_t n_tensors;
   uint32_t mma_slot;
   uint32_t num_temps;
-  uint32_t pad0;
+  uint32_t group_m;         // row blocks swept together over all column blocks (L2 reuse of the A panel); set by the launcher
   EpiTensor tensor[kMmMaxEpiTensors];
   uint64_t epilogue[kMmMaxEpilogueWords];
 };

@@ -71,12 +71,11 @@ __device__ __forceinline__ float round_operand_type(uint32_t dtype, float v) {
 
 // tile index -> (batch, m block, n block), grouped along M so that the A panel of a group stays in L2 while
 // the group sweeps over N
-__device__ __forceinline__ void tile_coords(uint32_t t, uint32_t mblocks, uint32_t nblocks, uint32_t &bz, uint32_t &mb,
-                                            uint32_t &nb) {
+__device__ __forceinline__ void tile_coords(uint32_t t, uint32_t mblocks, uint32_t nblocks, uint32_t kGroupM, uint32_t &bz,
+                                            uint32_t &mb, uint32_t &nb) {
   const uint32_t per_batch = mblocks * nblocks;
   bz = t / per_batch;
   t -= bz * per_batch;
-  constexpr uint32_t kGroupM = 8;
   const uint32_t group_tiles = kGroupM * nblocks;
   const uint32_t g = t / group_tiles;
   const uint32_t first_m = g * kGroupM;
@@ -152,7 +151,7 @@ __device__ __forceinline__ void mm_body(const MmParam &P, const MmMaps &maps) {
       uint32_t stage = 0, parity = 1;
       for (uint32_t t = unit; t < num_tiles; t += num_units) {
         uint32_t bz, mb, nb;
-        tile_coords(t, mblocks, nblocks, bz, mb, nb);
+        tile_coords(t, mblocks, nblocks, P.group_m, bz, mb, nb);
         const uint32_t b0 = bz / P.batch1, b1 = bz - b0 * P.batch1;
         const int za = (int)(b0 * P.a_mul0 + b1 * P.a_mul1), zb = (int)(b0 * P.b_mul0 + b1 * P.b_mul1);
         const int row0 = (int)((mb * CTAS + rank) * BM);
@@ -254,7 +253,7 @@ __device__ __forceinline__ void mm_body(const MmParam &P, const MmMaps &maps) {
     uint32_t acc = 0, acc_parity = 0;
     for (uint32_t t = unit; t < num_tiles; t += num_units) {
       uint32_t bz, mb, nb;
-      tile_coords(t, mblocks, nblocks, bz, mb, nb);
+      tile_coords(t, mblocks, nblocks, P.group_m, bz, mb, nb);
       mbar_wait(bar_tfull + 8 * acc, acc_parity, 4, &g_mm_status);
       tcgen05_after_sync();
       EpiPos pos;
@@ -395,7 +394,10 @@ bool MatMulUsesTensorCores(const MmParam &p) {
   return true;
 }
 
-int LaunchMatMul(const MmParam &p, void *stream) {
+int LaunchMatMul(const MmParam &p_in, void *stream) {
+  MmParam p = p_in;
+  static const int group_env = getenv("DVM_B200_MM_GROUP_M") ? atoi(getenv("DVM_B200_MM_GROUP_M")) : 0;
+  p.group_m = group_env > 0 ? static_cast<uint32_t>(group_env) : 8u;
   if (p.M == 0 || p.N == 0 || p.batch0 * p.batch1 == 0) return 0;
   if (p.in_dtype != T_BF16 && p.in_dtype != T_F16) return -3;
   int dev = 0;
