@@ -35,6 +35,8 @@ NVCC_FLAGS = [
     "--jump-table-density=20",
     "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall,-Wno-unused-function",
 ]
+# extra nvcc flags for experiments, e.g. DVM_B200_NVCC_EXTRA="--jump-table-density=101" (later flags win)
+NVCC_FLAGS += os.environ.get("DVM_B200_NVCC_EXTRA", "").split()
 
 
 def _nvcc():

@@ -116,8 +116,9 @@ struct Insn {
 //   [7:0] handler   [15:8] aux   [31:16] arg16   [63:32] imm32
 enum UopHandler : uint32_t {
   UH_END = 0,
-  // operand fetches; aux[1:0] = destination (UD_B / UD_ACC / UD_C), aux[5:2] = tensor slot
-  UH_LDR_F32, UH_LDR_F16, UH_LDR_BF16, UH_LDR_U8,   // from the ring stage, arg16 = ring offset / 16
+  // operand fetches; aux[1:0] = destination (UD_B / UD_ACC), aux[5:2] = tensor slot
+  UH_LDR_F32, UH_LDR_F16, UH_LDR_BF16, UH_LDR_U8,   // from the ring stage into b, arg16 = ring offset / 16
+  UH_LDRA_F32, UH_LDRA_F16, UH_LDRA_BF16, UH_LDRA_U8,   // the same into acc (one handler per destination: no test on the way)
   UH_LDG,                                           // from global memory through the tensor descriptor
   UH_LDT,                                           // thread-private temporary arg16
   UH_LDS,                                           // scalar register arg16, splat
@@ -133,16 +134,20 @@ enum UopHandler : uint32_t {
   UH_UN_FIRST,
   UH_UN_LAST = UH_UN_FIRST + U_NOP,
   UH_RND_F16, UH_RND_BF16,
-  // compares: aux[2:0] = CmpKind; the _S forms take aux bit7 = scalar register arg16, else imm32
+  // compares: aux[2:0] = CmpKind; the _S forms take UA_CMP_SREG = scalar register arg16, else imm32
   UH_CMP_F_V, UH_CMP_F_S, UH_CMP_I_V, UH_CMP_I_S,
-  UH_SEL_F, UH_SEL_I,                               // acc <- cond(acc) ? b : c
+  UH_PRED_F, UH_PRED_I,                             // lane mask <- acc != 0
+  UH_SELM,                                          // acc <- lane mask ? acc : b
   UH_CVT_F2I, UH_CVT_I2F, UH_CVT_NEZ_F, UH_CVT_NEZ_I,
   UH_RACC_SUM, UH_RACC_MAX, UH_RACC_MIN,            // arg16 = partial slot
   UH_ST_F32, UH_ST_F16, UH_ST_BF16, UH_ST_U8,       // dense, aligned tensor arg16: vector stores
   UH_STG,                                           // any tensor arg16
   UH_COUNT
 };
-enum UopDest : uint32_t { UD_B = 0, UD_ACC = 1, UD_C = 2 };
+enum UopDest : uint32_t { UD_B = 0, UD_ACC = 1 };
+enum UopAux : uint32_t {
+  UA_CMP_SREG = 0x08   // scalar compares: the scalar is register arg16, else imm32
+};
 
 constexpr uint64_t MakeUop(uint32_t handler, uint32_t aux, uint32_t arg16, uint32_t imm) {
   return (uint64_t)(handler & 0xff) | ((uint64_t)(aux & 0xff) << 8) | ((uint64_t)(arg16 & 0xffff) << 16) |

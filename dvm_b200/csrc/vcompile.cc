@@ -1167,7 +1167,7 @@ void LowerStage(VectorStage *st) {
         const uint32_t aux = dest | (idx << 2);
         if (td.ring_off != kNoRing) {
           static const uint32_t by_dtype[] = {UH_LDR_U8, UH_LDR_F16, UH_LDR_BF16, UH_LDR_F32, UH_LDR_F32};
-          push(MakeUop(by_dtype[td.dtype], aux, td.ring_off >> 4, 0));
+          push(MakeUop(by_dtype[td.dtype] + (dest == UD_ACC ? UH_LDRA_F32 - UH_LDR_F32 : 0u), aux, td.ring_off >> 4, 0));
         } else {
           push(MakeUop(UH_LDG, aux, 0, 0));
         }
@@ -1219,22 +1219,38 @@ void LowerStage(VectorStage *st) {
           break;
         case OP_CMP:
           if (splat) {
-            push(MakeUop(DVMB_ISINT(w) ? UH_CMP_I_S : UH_CMP_F_S, sub | (okind == K_SREG ? 0x80u : 0u), oidx, DVMB_IMM(w)));
+            push(MakeUop(DVMB_ISINT(w) ? UH_CMP_I_S : UH_CMP_F_S, sub | (okind == K_SREG ? UA_CMP_SREG : 0u), oidx, DVMB_IMM(w)));
           } else {
             fetch(okind, oidx, 0, UD_B);
             push(MakeUop(DVMB_ISINT(w) ? UH_CMP_I_V : UH_CMP_F_V, sub, 0, 0));
           }
           break;
         case OP_SEL: {
-          const bool inv = (DVMB_DST(w) & 1u) != 0;
-          fetch(okind, oidx, DVMB_IMM(w), inv ? UD_C : UD_B);   // the free-form alternative
-          fetch(sub >> 4, sub & 15u, 0, inv ? UD_B : UD_C);      // the register-like alternative
-          push(MakeUop(DVMB_ISINT(w) ? UH_SEL_I : UH_SEL_F, 0, 0, 0));
+          // acc holds the condition: keep its lane mask, then false value -> b, true value -> acc
+          const bool inv = (DVMB_DST(w) & 1u) != 0;   // the free-form operand is the false value
+          push(MakeUop(DVMB_ISINT(w) ? UH_PRED_I : UH_PRED_F, 0, 0, 0));
+          if (inv) {
+            fetch(okind, oidx, DVMB_IMM(w), UD_B);
+            fetch(sub >> 4, sub & 15u, 0, UD_ACC);
+          } else {
+            fetch(sub >> 4, sub & 15u, 0, UD_B);
+            fetch(okind, oidx, DVMB_IMM(w), UD_ACC);
+          }
+          push(MakeUop(UH_SELM, 0, 0, 0));
           break;
         }
         case OP_CVT: {
           static const uint32_t by_kind[] = {UH_CVT_F2I, UH_CVT_I2F, UH_CVT_NEZ_F, UH_CVT_NEZ_I};
           if (sub != V_RND) push(MakeUop(by_kind[sub], 0, 0, 0));
+          if (sub == V_RND && DVMB_OPC(st->bytecode[pc + 1]) == OP_ST) {
+            // a store of the same 16-bit type rounds the same way: no separate rounding when nothing else reads acc
+            const TensorDesc &td = P.tensor[DVMB_SUB(st->bytecode[pc + 1])];
+            const uint32_t after = DVMB_OPC(st->bytecode[pc + 2]);
+            const uint32_t rnd = DVMB_RND(w);
+            if ((after == OP_END || after == OP_COPY) &&
+                ((rnd == RN_F16 && td.dtype == kFloat16) || (rnd == RN_BF16 && td.dtype == kBFloat16)))
+              break;
+          }
           round(DVMB_RND(w));
           break;
         }

@@ -278,7 +278,7 @@ namespace {
 template <bool kResident, bool kCoords>
 __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
   asm volatile(DV_DECLARE);
-  asm volatile(DV_LN(DV_SPLATLANE, "va") DV_LN(DV_SPLATLANE, "vb") DV_LN(DV_SPLATLANE, "vc")
+  asm volatile(DV_LN(DV_SPLATLANE, "va") DV_LN(DV_SPLATLANE, "vb")
                "mov.b32 vp0, %0;\n\tmov.b32 vp1, %0;\n\tmov.b32 vp2, %0;\n\tmov.b32 vp3, %0;" ::"r"(0u));
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
@@ -296,6 +296,10 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
   const uint32_t ch_begin = flat ? blockIdx.x : rank * P.cpc, ch_step = flat ? gridDim.x : 1u;
   const uint32_t ch_end = flat ? P.chunks : min(P.chunks, (rank + 1u) * P.cpc);
 
+  // the program and the tensor table are read from shared memory in the loops below
+  for (uint32_t i = tid; i < P.n_code; i += blockDim.x) reinterpret_cast<uint64_t *>(smem + kVmSmemCode)[i] = P.code[i];
+  for (uint32_t i = tid; i < P.n_tensors * (sizeof(TensorDesc) / 4u); i += blockDim.x)
+    reinterpret_cast<uint32_t *>(smem + kVmSmemTensors)[i] = reinterpret_cast<const uint32_t *>(P.tensor)[i];
   if (tid == 0) {
     for (uint32_t s = 0; s < S; ++s) {
       mbar_init(smem_base + kVmSmemBarriers + 8 * s, 1);        // full: one arrival (the producer) + tx bytes
@@ -312,8 +316,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
   }
 
   // =============================== producer warp ===============================
-  // Lane j of the producer warp owns ring stage j: it walks the same tile sequence as the consumers and
-  // serves every S-th tile, so the address arithmetic of S tiles proceeds in parallel.
+  // One warp feeds the ring: it walks the same tile sequence as the consumers, one stage after the other.
   if (tid >= T) {
     const uint32_t plane = tid - T;
     if (resident) {
@@ -360,46 +363,65 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
       }
       return;
     }
-    if (plane >= S) return;
-    const uint32_t full = smem_base + kVmSmemBarriers + 8 * plane;
-    const uint32_t stage_saddr = smem_base + kVmSmemStages + plane * P.stage_bytes;
-    uint32_t next = plane, seq = 0, parity = 1;   // first wait on a fresh "empty" barrier passes at once
+    // Streaming ring.  The warp walks the consumers' tile sequence in step: every lane waits for the stage to be
+    // released, lane 0 posts the byte count, and lane t issues the bulk copy of the t-th staged tensor.  Each lane
+    // keeps its tensor's base, strides and element size in registers; the chunk coordinates advance incrementally.
+    uint32_t umask = 0;
+    for (uint32_t ph = 0; ph < P.num_body; ++ph) umask |= P.body_ring_mask[ph];
+    if (umask == 0) return;
+    const bool has = plane < (uint32_t)__popc(umask);
+    const uint32_t my_t = has ? (uint32_t)__fns(umask, 0, plane + 1) : (uint32_t)(__ffs(umask) - 1);
+    const TensorDesc &td = P.tensor[my_t];
+    const uint32_t sh = item_shift(td.dtype);
+    const uint32_t my_ring = td.ring_off;
+    const uint8_t *my_base = reinterpret_cast<const uint8_t *>(td.ptr);
+    uint32_t es[kMaxEnum];
+#pragma unroll
+    for (int j = 0; j < kMaxEnum; ++j) es[j] = td.estride[j];
+    const uint32_t step_elems = ch_step * P.chunk_elems;
+    uint32_t stage = 0, parity = 1;   // first wait on a fresh "empty" barrier passes at once
     for (uint32_t gb = gb_begin; gb < ngb; gb += gb_step) {
       uint32_t k[kMaxKept];
-      bool have_k = false;
+      decompose_group(P, gb, k);   // groups_per_cta == 1 whenever the ring is on
+      const uint32_t koff = kept_offset(td, k);
       for (uint32_t ph = 0; ph < P.num_body; ++ph) {
         const uint32_t mask = P.body_ring_mask[ph];
         if (mask == 0) continue;
-        for (uint32_t ch = ch_begin; ch < ch_end; ch += ch_step, ++seq) {
-          if (seq != next) continue;
-          next += S;
-          if (!have_k) {
-            decompose_group(P, gb, k);   // groups_per_cta == 1 whenever the ring is on
-            have_k = true;
-          }
-          mbar_wait(smem_base + kVmSmemEmpty + 8 * plane, parity, 1);
-          parity ^= 1u;
-          const uint32_t e_start = ch * P.chunk_elems;
+        const bool mine = has && ((mask >> my_t) & 1u);
+        uint32_t c[kMaxEnum] = {0, 0, 0, ch_begin * P.chunk_elems};
+        if (P.need_coords) split_enum(P, c[3], c);
+        uint32_t e_start = ch_begin * P.chunk_elems;
+        for (uint32_t ch = ch_begin; ch < ch_end; ch += ch_step, e_start += step_elems) {
+          const uint32_t full = smem_base + kVmSmemBarriers + 8 * stage;
+          mbar_wait(smem_base + kVmSmemEmpty + 8 * stage, parity, 1);
           const uint32_t valid = min(P.chunk_elems, P.group_elems - e_start);
-          uint32_t c[kMaxEnum] = {0, 0, 0, e_start};
-          if (P.need_coords) split_enum(P, e_start, c);
-          uint32_t total = 0;
-          for (uint32_t m = mask; m; m &= m - 1) {
-            const TensorDesc &td = P.tensor[__ffs(m) - 1];
-            total += (valid << item_shift(td.dtype)) & ~15u;
+          const uint32_t bytes = mine ? ((valid << sh) & ~15u) : 0u;
+          const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
+          if (plane == 0) {
+            if (total == 0) {
+              mbar_arrive(full);
+            } else {
+              mbar_arrive_expect_tx(full, total);
+            }
           }
-          if (total == 0) {
-            mbar_arrive(full);
-            continue;
+          __syncwarp();
+          if (bytes != 0) {
+            const uint32_t off = koff + c[0] * es[0] + c[1] * es[1] + c[2] * es[2] + c[3] * es[3];
+            bulk_g2s(smem_base + kVmSmemStages + stage * P.stage_bytes + my_ring, my_base + ((size_t)off << sh), bytes, full);
           }
-          mbar_arrive_expect_tx(full, total);
-          for (uint32_t m = mask; m; m &= m - 1) {
-            const TensorDesc &td = P.tensor[__ffs(m) - 1];
-            const uint32_t sh = item_shift(td.dtype);
-            const uint32_t bytes = (valid << sh) & ~15u;
-            if (bytes == 0) continue;
-            const uint32_t off = kept_offset(td, k) + enum_offset(td, c);
-            bulk_g2s(stage_saddr + td.ring_off, reinterpret_cast<const uint8_t *>(td.ptr) + ((size_t)off << sh), bytes, full);
+          // next chunk of this CTA: advance the innermost coordinate and carry
+          c[3] += step_elems;
+          if (P.need_coords) {
+#pragma unroll
+            for (int j = kMaxEnum - 1; j > 0; --j)
+              while (c[j] >= P.enum_size[j]) {
+                c[j] -= P.enum_size[j];
+                c[j - 1] += 1u;
+              }
+          }
+          if (++stage == S) {
+            stage = 0;
+            parity ^= 1u;
           }
         }
       }
@@ -408,7 +430,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
   }
 
   // =============================== consumer warps ===============================
-  // The vector state (accumulator va, operand registers vb / vc, reduction partials vp) lives in PTX
+  // The vector state (accumulator va, operand register vb, reduction partials vp) lives in PTX
   // registers that only inline assembly names.  The compiler therefore carries no vector state across
   // the dispatch loop (nothing to copy at the switch merge), and ptxas keeps each one in a fixed register.
   float *red_buf = reinterpret_cast<float *>(smem + kVmSmemRed);
@@ -419,6 +441,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
   const uint32_t group_in_cta = flat ? 0 : tid / tg;
 
   uint32_t sacc[1] = {0};
+  uint32_t sel_mask = 0;   // lanes whose select condition held
   uint32_t red_par = 0;
   uint32_t ring_stage = 0, ring_parity = 0;
   uint32_t xphase = 0, xpar = 0;       // cluster-combine phase and buffer
@@ -431,6 +454,16 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
 
   auto temp_addr = [&](uint32_t k, uint32_t g) { return temps_saddr + ((k * kGranules + g) * T + tid) * 16u; };
   auto sreg_addr = [&](uint32_t k) { return sregs_saddr + (k * T + tid) * 4u; };
+  const uint32_t code_saddr = smem_base + kVmSmemCode;
+  const TensorDesc *const tdesc = reinterpret_cast<const TensorDesc *>(smem + kVmSmemTensors);
+  auto lds64 = [](uint32_t a) {
+    uint64_t v;
+    asm volatile("ld.shared.u64 %0, [%1];" : "=l"(v) : "r"(a));
+    return v;
+  };
+  auto lds64x2 = [](uint32_t a, uint32_t &lo, uint32_t &hi) {
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(lo), "=r"(hi) : "r"(a));
+  };
   auto lds32 = [](uint32_t a) {
     uint32_t v;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
@@ -470,7 +503,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
     for (uint32_t ph = 0; ph <= P.num_body; ++ph) {
       // ---------------- scalar side: PRO_ph ----------------
       for (uint32_t pc = P.sec[2 * ph];;) {
-        const uint64_t w = P.code[pc++];
+        const uint64_t w = lds64(code_saddr + 8u * pc++);
         const uint32_t opc = DVMB_OPC(w);
         if (opc == OP_END) break;
         const uint32_t sub = DVMB_SUB(w);
@@ -482,7 +515,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
           } else if (okind == K_IMM) {
             sb = DVMB_IMM(w);
           } else if (okind == K_TENSOR) {
-            const TensorDesc &td = P.tensor[oidx];
+            const TensorDesc &td = tdesc[oidx];
             sb = load_elem(td.dtype, reinterpret_cast<const uint8_t *>(td.ptr), kept_offset(td, pos.k));
           } else {
             sb = sacc[0];
@@ -491,7 +524,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
         const SplatOperand bo{sb};
         switch (opc) {
           case OP_ST: {
-            const TensorDesc &td = P.tensor[sub];
+            const TensorDesc &td = tdesc[sub];
             if (lane_in_group == 0 && pos.gvalid && rank == 0 && (!flat || blockIdx.x == 0))
               store_elem(td.dtype, reinterpret_cast<uint8_t *>(td.ptr), kept_offset(td, pos.k), sacc[0]);
             break;
@@ -589,43 +622,39 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
         const bool full_tile = pos.gvalid && pos.in_chunk0 + 3u * pos.gstep + 4u <= pos.chunk_valid;
         // a thread without a single lane inside the chunk has nothing to fetch, add or store
         const bool lane_active = pos.gvalid && 4u * lane_in_group < pos.chunk_valid;
-        for (uint32_t pc = lane_active ? body_pc : P.n_code - 1u;; ++pc) {
-          const uint64_t u = P.code[pc];
-          const uint32_t uh = DVMB_UH(u);
-          const uint32_t aux = DVMB_UAUX(u);
-          const uint32_t arg = DVMB_UARG(u);
-          if (uh == UH_END) break;
+        uint32_t pc_saddr = code_saddr + 8u * (lane_active ? body_pc : P.n_code - 1u);
+        uint32_t ulo, uhi, nlo, nhi;   // the current micro-op and the next one, already on its way
+        lds64x2(pc_saddr, ulo, uhi);
+        for (;; ulo = nlo, uhi = nhi) {
+          const uint32_t uh = ulo & 0xffu;
+          const uint32_t aux = (ulo >> 8) & 0xffu;
+          const uint32_t arg = ulo >> 16;
+          if (uh == UH_END) break;   // (kept out of the switch: a compare is cheaper than the indexed jump)
+          pc_saddr += 8u;
+          lds64x2(pc_saddr, nlo, nhi);
           uint32_t slot;
           switch (uh) {
             // ---------------- operand fetches ----------------
-            case UH_LDR_F32: {
-              slot = aux >> 2;
-              if (!full_tile) goto fetch_generic;
-              const uint32_t a0 = stage_saddr + (arg << 4) + (pos.in_chunk0 << 2), gs = pos.gstep << 2;
-              DV_BY_DEST(aux & 3u, DV_LDR32, a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)
-              continue;
-            }
-            case UH_LDR_F16: {
-              slot = aux >> 2;
-              if (!full_tile) goto fetch_generic;
-              const uint32_t a0 = stage_saddr + (arg << 4) + (pos.in_chunk0 << 1), gs = pos.gstep << 1;
-              DV_BY_DEST(aux & 3u, DV_LDR_F16, a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)
-              continue;
-            }
-            case UH_LDR_BF16: {
-              slot = aux >> 2;
-              if (!full_tile) goto fetch_generic;
-              const uint32_t a0 = stage_saddr + (arg << 4) + (pos.in_chunk0 << 1), gs = pos.gstep << 1;
-              DV_BY_DEST(aux & 3u, DV_LDR_BF16, a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)
-              continue;
-            }
-            case UH_LDR_U8: {
-              slot = aux >> 2;
-              if (!full_tile) goto fetch_generic;
-              const uint32_t a0 = stage_saddr + (arg << 4) + pos.in_chunk0, gs = pos.gstep;
-              DV_BY_DEST(aux & 3u, DV_LDR_U8, a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)
-              continue;
-            }
+#define DV_LDR_CASE(H, REG, MACRO, SHL)                                                                        \
+  case H: {                                                                                                 \
+    slot = aux >> 2;                                                                                        \
+    if (!full_tile) goto fetch_generic;                                                                     \
+    const uint32_t a0 = stage_saddr + (arg << 4) + (SHL(pos.in_chunk0)), gs = SHL(pos.gstep);               \
+    MACRO(REG, a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)                                                      \
+    continue;                                                                                               \
+  }
+#define DV_SHL0(x) (x)
+#define DV_SHL1(x) ((x) << 1)
+#define DV_SHL2(x) ((x) << 2)
+            DV_LDR_CASE(UH_LDR_F32, "vb", DV_LDR32, DV_SHL2)
+            DV_LDR_CASE(UH_LDR_F16, "vb", DV_LDR_F16, DV_SHL1)
+            DV_LDR_CASE(UH_LDR_BF16, "vb", DV_LDR_BF16, DV_SHL1)
+            DV_LDR_CASE(UH_LDR_U8, "vb", DV_LDR_U8, DV_SHL0)
+            DV_LDR_CASE(UH_LDRA_F32, "va", DV_LDR32, DV_SHL2)
+            DV_LDR_CASE(UH_LDRA_F16, "va", DV_LDR_F16, DV_SHL1)
+            DV_LDR_CASE(UH_LDRA_BF16, "va", DV_LDR_BF16, DV_SHL1)
+            DV_LDR_CASE(UH_LDRA_U8, "va", DV_LDR_U8, DV_SHL0)
+#undef DV_LDR_CASE
             case UH_LDG: {
               slot = aux >> 2;
             fetch_generic:
@@ -641,12 +670,12 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             }
             case UH_LDS:
             case UH_LDI: {
-              const uint32_t v = uh == UH_LDS ? lds32(sreg_addr(arg)) : DVMB_UIMM(u);
+              const uint32_t v = uh == UH_LDS ? lds32(sreg_addr(arg)) : uhi;
               DV_BY_DEST(aux & 3u, DV_SPLAT, v)
               continue;
             }
             case UH_MOVA:
-              if ((aux & 3u) == UD_B) { asm volatile(DV_LN(DV_MOV_LANE, "vb", "va")); } else { asm volatile(DV_LN(DV_MOV_LANE, "vc", "va")); }
+              asm volatile(DV_LN(DV_MOV_LANE, "vb", "va"));
               continue;
             case UH_STT: {
               const uint32_t a0 = temp_addr(arg, 0), gs = T * 16u;
@@ -672,17 +701,17 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             DV_BIN_CASES(B_MIN_I, DV_BINV_LANE, DV_BINS_LANE, "min.s32")
             DV_BIN_CASES(B_RSUB_I, DV_RBINV_LANE, DV_RBINS_LANE, "sub.s32")
             // float max / min keep the reference's `a > b ? a : b` / `a < b ? a : b`
-            case UH_BINV_FIRST + B_MAX: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_PICKV_LANE, "setp.gt.f32") "}"); continue;
-            case UH_BINV_FIRST + B_MIN: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_PICKV_LANE, "setp.lt.f32") "}"); continue;
+            case UH_BINV_FIRST + B_MAX: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_PICKV_LANE, "setp.gt.f32") "}"); break;
+            case UH_BINV_FIRST + B_MIN: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_PICKV_LANE, "setp.lt.f32") "}"); break;
             case UH_BINS_FIRST + B_MAX: {
-              const uint32_t sv = (aux & 1u) ? lds32(sreg_addr(arg)) : DVMB_UIMM(u);
+              const uint32_t sv = (aux & 1u) ? lds32(sreg_addr(arg)) : uhi;
               asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_PICKS_LANE, "setp.gt.f32") "}" ::"r"(sv));
-              continue;
+              break;
             }
             case UH_BINS_FIRST + B_MIN: {
-              const uint32_t sv = (aux & 1u) ? lds32(sreg_addr(arg)) : DVMB_UIMM(u);
+              const uint32_t sv = (aux & 1u) ? lds32(sreg_addr(arg)) : uhi;
               asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_PICKS_LANE, "setp.lt.f32") "}" ::"r"(sv));
-              continue;
+              break;
             }
             case UH_BINV_FIRST + B_POW:
             case UH_BINS_FIRST + B_POW: {
@@ -691,26 +720,26 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
               if (uh == UH_BINV_FIRST + B_POW) {
                 DV_GET("vb", y)
               } else {
-                const uint32_t sv = (aux & 1u) ? lds32(sreg_addr(arg)) : DVMB_UIMM(u);
+                const uint32_t sv = (aux & 1u) ? lds32(sreg_addr(arg)) : uhi;
 #pragma unroll
                 for (int i = 0; i < kLanes; ++i) y[i] = sv;
               }
 #pragma unroll
               for (int i = 0; i < kLanes; ++i) x[i] = f2u(powf(u2f(x[i]), u2f(y[i])));
               DV_SET("va", x)
-              continue;
+              break;
             }
             // ---------------- unary ----------------
-            case UH_UN_FIRST + U_SQRT: asm volatile(DV_LN(DV_UN_LANE, "sqrt.rn.f32")); continue;
-            case UH_UN_FIRST + U_ABS: asm volatile(DV_LN(DV_UN_LANE, "abs.f32")); continue;
-            case UH_UN_FIRST + U_ROUND: asm volatile(DV_LN(DV_UN_LANE, "cvt.rni.f32.f32")); continue;
-            case UH_UN_FIRST + U_FLOOR: asm volatile(DV_LN(DV_UN_LANE, "cvt.rmi.f32.f32")); continue;
-            case UH_UN_FIRST + U_CEIL: asm volatile(DV_LN(DV_UN_LANE, "cvt.rpi.f32.f32")); continue;
-            case UH_UN_FIRST + U_TRUNC: asm volatile(DV_LN(DV_UN_LANE, "cvt.rzi.f32.f32")); continue;
-            case UH_UN_FIRST + U_ABS_I: asm volatile(DV_LN(DV_UN_LANE, "abs.s32")); continue;
+            case UH_UN_FIRST + U_SQRT: asm volatile(DV_LN(DV_UN_LANE, "sqrt.rn.f32")); break;
+            case UH_UN_FIRST + U_ABS: asm volatile(DV_LN(DV_UN_LANE, "abs.f32")); break;
+            case UH_UN_FIRST + U_ROUND: asm volatile(DV_LN(DV_UN_LANE, "cvt.rni.f32.f32")); break;
+            case UH_UN_FIRST + U_FLOOR: asm volatile(DV_LN(DV_UN_LANE, "cvt.rmi.f32.f32")); break;
+            case UH_UN_FIRST + U_CEIL: asm volatile(DV_LN(DV_UN_LANE, "cvt.rpi.f32.f32")); break;
+            case UH_UN_FIRST + U_TRUNC: asm volatile(DV_LN(DV_UN_LANE, "cvt.rzi.f32.f32")); break;
+            case UH_UN_FIRST + U_ABS_I: asm volatile(DV_LN(DV_UN_LANE, "abs.s32")); break;
             case UH_UN_FIRST + U_ISFINITE:
               asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_ISFIN_LANE, "") "}");
-              continue;
+              break;
             case UH_UN_FIRST + U_LOG:
             case UH_UN_FIRST + U_EXP: {
               uint32_t x[kLanes];
@@ -723,10 +752,10 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
                 for (int i = 0; i < kLanes; ++i) x[i] = f2u(logf(u2f(x[i])));
               }
               DV_SET("va", x)
-              continue;
+              break;
             }
-            case UH_UN_FIRST + U_EXP_FAST: asm volatile(DV_LN(DV_EXPF_LANE, "")); continue;
-            case UH_UN_FIRST + U_NOP: continue;
+            case UH_UN_FIRST + U_EXP_FAST: asm volatile(DV_LN(DV_EXPF_LANE, "")); break;
+            case UH_UN_FIRST + U_NOP: break;
             case UH_RND_F16: asm volatile("{\n\t.reg .b16 h;\n\t" DV_LN(DV_RNDH_LANE, "") "}"); continue;
             case UH_RND_BF16:
               asm volatile("{\n\t.reg .b32 t;\n\t" DV_PAIRS(DV_RNDB_PAIR, "") "}");
@@ -738,7 +767,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             case UH_CMP_I_S: {
               const bool is_int = uh == UH_CMP_I_V || uh == UH_CMP_I_S;
               if (uh == UH_CMP_F_S || uh == UH_CMP_I_S) {
-                const uint32_t sv = (aux & 0x80u) ? lds32(sreg_addr(arg)) : DVMB_UIMM(u);
+                const uint32_t sv = (aux & UA_CMP_SREG) ? lds32(sreg_addr(arg)) : uhi;
                 DV_SPLAT("vb", sv)
               }
               switch ((aux & 7u) | (is_int ? 8u : 0u)) {
@@ -757,10 +786,17 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
               }
               continue;
             }
-            case UH_SEL_F: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_SEL_LANE, "setp.neu.f32 p, va", ", 0f00000000") "}"); continue;
-            case UH_SEL_I: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_SEL_LANE, "setp.ne.s32 p, va", ", 0") "}"); continue;
-            case UH_CVT_F2I: asm volatile(DV_LN(DV_UN_LANE, "cvt.rzi.s32.f32")); continue;
-            case UH_CVT_I2F: asm volatile(DV_LN(DV_UN_LANE, "cvt.rn.f32.s32")); continue;
+            case UH_PRED_F:
+              sel_mask = 0;
+              asm volatile("{\n\t.reg .pred p;\n\t.reg .b32 t;\n\t" DV_LN(DV_PRED_LANE, "setp.neu.f32 p, va", ", 0f00000000") "}" : "+r"(sel_mask));
+              continue;
+            case UH_PRED_I:
+              sel_mask = 0;
+              asm volatile("{\n\t.reg .pred p;\n\t.reg .b32 t;\n\t" DV_LN(DV_PRED_LANE, "setp.ne.s32 p, va", ", 0") "}" : "+r"(sel_mask));
+              continue;
+            case UH_SELM: asm volatile("{\n\t.reg .pred p;\n\t.reg .b32 t;\n\t" DV_LN(DV_SELM_LANE, "") "}" ::"r"(sel_mask)); continue;
+            case UH_CVT_F2I: asm volatile(DV_LN(DV_UN_LANE, "cvt.rzi.s32.f32")); break;
+            case UH_CVT_I2F: asm volatile(DV_LN(DV_UN_LANE, "cvt.rn.f32.s32")); break;
             case UH_CVT_NEZ_F: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_NEZ_LANE, "setp.neu.f32 p, va", ", 0f00000000") "}"); continue;
             case UH_CVT_NEZ_I: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_NEZ_LANE, "setp.ne.s32 p, va", ", 0") "}"); continue;
             // ---------------- reductions ----------------
@@ -796,7 +832,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             // ---------------- stores ----------------
             case UH_ST_F32: {
               if (!full_tile) goto store_generic;
-              const TensorDesc &td = P.tensor[arg];
+              const TensorDesc &td = tdesc[arg];
               uint32_t *p0 = reinterpret_cast<uint32_t *>(td.ptr) + kept_offset(td, pos.k) + (!kCoords || td.mode == AM_DENSE ? pos.e_start : enum_offset(td, cc)) + pos.in_chunk0;
               const uint32_t gs = pos.gstep;
               asm volatile("st.global.v4.b32 [%0], {va0,va1,va2,va3};\n\tst.global.v4.b32 [%1], {va4,va5,va6,va7};\n\t"
@@ -808,7 +844,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             case UH_ST_F16:
             case UH_ST_BF16: {
               if (!full_tile) goto store_generic;
-              const TensorDesc &td = P.tensor[arg];
+              const TensorDesc &td = tdesc[arg];
               unsigned short *p0 = reinterpret_cast<unsigned short *>(td.ptr) + kept_offset(td, pos.k) + (!kCoords || td.mode == AM_DENSE ? pos.e_start : enum_offset(td, cc)) + pos.in_chunk0;
               const uint32_t gs = pos.gstep;
 #define DV_ST16(CVT)                                                                                          \
@@ -835,7 +871,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
               store_tensor(P, arg, pos, x);
               continue;
             }
-            default: continue;
+            default: __builtin_unreachable();
           }
         }
         if (staged_body && release_slots) {

@@ -1,6 +1,6 @@
 // Inline-PTX building blocks of the vector interpreter's hidden register file.
 //
-// The vector state of a consumer thread - accumulator va0..15, operand registers vb0..15 / vc0..15 and the
+// The vector state of a consumer thread - accumulator va0..15, operand register vb0..15 and the
 // reduction partials vp0..3 - is held in PTX registers that are declared once at the top of the kernel and
 // are named only inside inline assembly.  The C++ compiler therefore carries no vector value across the
 // dispatch loop (nothing to copy where the handlers' control flow merges) and ptxas keeps each register
@@ -18,7 +18,7 @@
   M("0", "1", __VA_ARGS__) M("2", "3", __VA_ARGS__) M("4", "5", __VA_ARGS__) M("6", "7", __VA_ARGS__) \
   M("8", "9", __VA_ARGS__) M("10", "11", __VA_ARGS__) M("12", "13", __VA_ARGS__) M("14", "15", __VA_ARGS__)
 
-#define DV_DECLARE ".reg .b32 va<16>, vb<16>, vc<16>, vp<4>;"
+#define DV_DECLARE ".reg .b32 va<16>, vb<16>, vp<4>;"
 
 // ---- lane templates ----------------------------------------------------------------------------------
 #define DV_BINV_LANE(i, OP) OP " va" #i ", va" #i ", vb" #i ";\n\t"
@@ -34,7 +34,8 @@
 #define DV_RNDB_PAIR(a, b, X) "cvt.rn.bf16x2.f32 t, va" b ", va" a ";\n\tshl.b32 va" a ", t, 16;\n\tand.b32 va" b ", t, 0xffff0000;\n\t"
 #define DV_CMPF_LANE(i, SETP) SETP " p, va" #i ", vb" #i ";\n\tselp.b32 va" #i ", 0x3f800000, 0, p;\n\t"
 #define DV_CMPI_LANE(i, SETP) SETP " p, va" #i ", vb" #i ";\n\tselp.b32 va" #i ", 1, 0, p;\n\t"
-#define DV_SEL_LANE(i, TEST, ZERO) TEST #i ZERO ";\n\tselp.b32 va" #i ", vb" #i ", vc" #i ", p;\n\t"
+#define DV_PRED_LANE(i, TEST, ZERO) TEST #i ZERO ";\n\tselp.u32 t, 1, 0, p;\n\tbfi.b32 %0, t, %0, " #i ", 1;\n\t"
+#define DV_SELM_LANE(i, X) "bfe.u32 t, %0, " #i ", 1;\n\tsetp.ne.u32 p, t, 0;\n\tselp.b32 va" #i ", va" #i ", vb" #i ", p;\n\t"
 #define DV_NEZ_LANE(i, TEST, ZERO) TEST #i ZERO ";\n\tselp.b32 va" #i ", 1, 0, p;\n\t"
 #define DV_MOV_LANE(i, D, S_) "mov.b32 " D #i ", " S_ #i ";\n\t"
 #define DV_GETLANE(i, R) "mov.b32 %" #i ", " R #i ";\n\t"
@@ -92,18 +93,18 @@
                "r"(A1), "r"(A2), "r"(A3)                                                                         \
                : "memory");
 
-// run FN("va" | "vb" | "vc", args...) for destination code D
+// run FN("va" | "vb", args...) for destination code D
 #define DV_BY_DEST(D, FN, ...)                \
   {                                           \
     const uint32_t d_ = (D);                  \
-    if (d_ == UD_ACC) { FN("va", __VA_ARGS__) } else if (d_ == UD_B) { FN("vb", __VA_ARGS__) } else { FN("vc", __VA_ARGS__) } \
+    if (d_ == UD_ACC) { FN("va", __VA_ARGS__) } else { FN("vb", __VA_ARGS__) } \
   }
 #define DV_BIN_CASES(K, VLANE, SLANE, OP)                                      \
-  case UH_BINV_FIRST + K: asm volatile(DV_LN(VLANE, OP)); continue;            \
+  case UH_BINV_FIRST + K: asm volatile(DV_LN(VLANE, OP)); break;               \
   case UH_BINS_FIRST + K: {                                                    \
-    const uint32_t sv_ = (aux & 1u) ? lds32(sreg_addr(arg)) : DVMB_UIMM(u);    \
+    const uint32_t sv_ = (aux & 1u) ? lds32(sreg_addr(arg)) : uhi;            \
     asm volatile(DV_LN(SLANE, OP)::"r"(sv_));                                  \
-    continue;                                                                  \
+    break;                                                                     \
   }
 #define DV_CMP_ASM(LANE, SETP) asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(LANE, SETP) "}")
 
