@@ -17,7 +17,7 @@
 
 namespace dvm {
 
-constexpr int kMaxRank = 8;
+constexpr int kMaxRank = 10;   // the reference's DimArray limit (src/ops.h:165)
 
 struct Shape {
   int64_t d[kMaxRank];

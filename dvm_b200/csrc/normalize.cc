@@ -33,7 +33,7 @@ namespace {
 
 Shape FromRef(const NDObject *n, const IntArrayRef *ref) {
   if (ref == nullptr || (ref->size > 0 && ref->data == nullptr)) Fail(n, "missing shape");
-  if (ref->size > static_cast<size_t>(kMaxRank)) Fail(n, "rank above 8");
+  if (ref->size > static_cast<size_t>(kMaxRank)) Fail(n, "rank above 10");
   Shape s;
   s.rank = static_cast<int>(ref->size);
   for (int i = 0; i < s.rank; ++i) s.d[i] = ref->data[i];

@@ -48,6 +48,8 @@ struct Planner {
   std::unordered_set<const NDObject *> done;
   // where a computed value lives in memory once its stage has run: a planner-made Load
   std::unordered_map<const NDObject *, NDObject *> mem;
+  // reductions over an empty extent with a non-empty result: the constant (the reduction's identity) readers see instead
+  std::unordered_map<const NDObject *, NDObject *> subst;
   std::vector<NDObject *> cur;   // open vector area, program order
   std::unordered_set<const NDObject *> in_cur;
   size_t ws_top = 0;
@@ -114,7 +116,9 @@ struct Planner {
     auto it = b.clone.find(v);
     if (it != b.clone.end()) return it->second;
     NDObject *c = nullptr;
-    if (InMemory(v)) {
+    if (subst.count(v)) {
+      c = Synth(subst.at(v));
+    } else if (InMemory(v)) {
       c = MemLoad(v);
     } else if (v->kind == N_BROADCAST_S) {
       c = Synth(v);
@@ -245,9 +249,53 @@ struct Planner {
     in_cur.insert(n);
   }
 
+  // The constant that stands for reduction `n` over an empty extent.
+  NDObject *EmptyReduce(const NDObject *n) {
+    auto c = new NDObject();
+    vk->synth_.push_back(c);
+    c->kind = N_BROADCAST_S;
+    c->dtype = n->dtype;
+    c->shape = n->shape;
+    c->id = n->id;
+    const bool is_int = n->dtype == kInt32;
+    if (n->sub == kMax) c->scalar_bits = is_int ? 0x80000000u : 0xff800000u;
+    if (n->sub == kMin) c->scalar_bits = is_int ? 0x7fffffffu : 0x7f800000u;
+    return c;
+  }
+
+  // Write a broadcast out to the workspace in a stage of its own, so that later stages can address it as memory.
+  void Materialize(NDObject *v) {
+    CloseCur();
+    Build b;
+    NDObject *c = InputFor(b, v);
+    auto st = new NDObject();
+    vk->synth_.push_back(st);
+    st->kind = N_STORE;
+    st->dtype = v->dtype;
+    st->shape = v->shape;
+    st->in[0] = c;
+    st->id = v->id;
+    st->ws_off = static_cast<int64_t>(AllocWs(v));
+    b.list.push_back(st);
+    b.temps.emplace_back(v, st);
+    auto stage = std::make_unique<Stage>();
+    stage->kind = STAGE_VECTOR;
+    std::string why;
+    if (!CompileVectorStage(b.list, &stage->vec, &why)) {
+      std::string msg = "cannot write a broadcast out to memory: " + why;
+      DvmException(msg.c_str());
+    }
+    Publish(b);
+    vk->stages_.push_back(std::move(stage));
+  }
+
   // Make sure `v` is addressable in memory before a tensor-core stage reads it.
   void RequireInMemory(NDObject *v, const char *what) {
     if (InMemory(v)) return;
+    if (v->kind == N_BROADCAST || v->kind == N_BROADCAST_S) {
+      Materialize(v);
+      return;
+    }
     if (in_cur.count(v)) {
       CloseCur();
       if (InMemory(v)) return;
@@ -508,13 +556,22 @@ struct Planner {
   void Run() {
     for (auto n : ops) {
       if (done.count(n)) continue;
+      if (n->shape.numel() == 0) {   // nothing to compute or to write
+        done.insert(n);
+        continue;
+      }
+      if (n->kind == N_REDUCE && n->in[0]->shape.numel() == 0) {
+        subst[n] = EmptyReduce(n);
+        done.insert(n);
+        continue;
+      }
       switch (n->kind) {
         case N_LOAD:
         case N_BROADCAST_S:
         case N_BROADCAST: break;
         case N_STORE: {
           NDObject *v = n->in[0];
-          if (IsLazy(v) || mem.count(v)) AddVector(n);   // a plain copy of something already in memory
+          if (IsLazy(v) || mem.count(v) || subst.count(v)) AddVector(n);   // a plain copy of something already in memory
           break;
         }
         case N_RESHAPE: {
@@ -531,11 +588,25 @@ struct Planner {
             CloseCur();
           }
           if (!InMemory(src)) {
-            if (src->kind == N_BROADCAST || src->kind == N_BROADCAST_S) {
-              AddVector(n);
+            if (src->kind != N_BROADCAST && src->kind != N_BROADCAST_S)
+              DvmException("stage planner: reshape of a value that is not in memory");
+            // a broadcast is re-created by its readers: a reshape that only adds or drops unit dims joins an area,
+            // any other one needs the broadcast written out first
+            std::string why;
+            cur.push_back(n);
+            if (TryVector(cur, false, &why)) {
+              in_cur.insert(n);
               break;
             }
-            DvmException("stage planner: reshape of a value that is not in memory");
+            cur.pop_back();
+            CloseCur();
+            cur.push_back(n);
+            if (TryVector(cur, false, &why)) {
+              in_cur.insert(n);
+              break;
+            }
+            cur.pop_back();
+            Materialize(src);
           }
           // a view of memory: same bytes, new shape
           NDObject *ld = MemLoad(src);

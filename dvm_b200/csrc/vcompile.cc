@@ -84,7 +84,7 @@ struct Compiler {
   void AlignAxes() {
     R = 0;
     for (auto n : ops) R = std::max(R, n->shape.rank);
-    if (R > kMaxRank) throw Fail{"domain rank above 8"};
+    if (R > kMaxRank) throw Fail{"domain rank above 10"};
     for (auto n : ops) {
       Info &fi = I(n);
       const int r = n->shape.rank;
@@ -832,6 +832,12 @@ struct Compiler {
         if (v->kind != N_LOAD && v->kind != N_BROADCAST_S) EmitNode(vs, v);
         flush_roots(v);
       }
+      // roots fed by a constant or by a value of the scalar side (a `full`, a broadcast group scalar) have no body node
+      for (size_t i = 0; i < pending.size(); ++i)
+        if (pending[i] != nullptr) {
+          const NDObject *v = Canon(pending[i]->in[0]);
+          if (I(v).scalar_space || v->kind == N_BROADCAST_S) flush_roots(v);
+        }
       for (auto r : pending)
         if (r != nullptr) throw Fail{"internal: a store or reduction lost its value"};
       vs.Push0(OP_END, 0);

@@ -72,9 +72,12 @@ size_t VKernel::Compile() {
     compiled_ = true;
     return 0;
   }
-  bool has_matmul = false;
-  for (auto n : ops) has_matmul |= n->kind == N_MATMUL;
-  if (!has_matmul) {
+  bool has_matmul = false, has_empty = false;
+  for (auto n : ops) {
+    has_matmul |= n->kind == N_MATMUL;
+    has_empty |= n->shape.numel() == 0;   // the planner drops empty tensors and keeps what still has elements
+  }
+  if (!has_matmul && !has_empty) {
     // the common case: the whole graph is one launch of the vector interpreter
     auto st = std::make_unique<Stage>();
     std::string why;

@@ -144,6 +144,7 @@ class Kernel:
     def __init__(self, kernel_type=0, flags=0):
         self._lib = _capi.load()
         self._k = check_ptr(self._lib.dvm_kernel_new(int(kernel_type), int(flags)), "kernel")
+        self._ktype = int(kernel_type)
         self._flags = int(flags)
         self._keep = []  # shape / scalar holders the graph borrows
 
@@ -261,6 +262,11 @@ class Kernel:
                                               bias._h if bias is not None else None), "matmul")
 
     # -- text
+    def tile(self, start, end, num, factor=0):
+        """Tiling hint of the reference's runner (src/pybind_api.cc:1093); the tile geometry here follows from the shapes
+        alone, so the hint is accepted and has no effect."""
+        return None
+
     def das(self):
         return self._lib.dvm_das(self._k).decode()
 
@@ -487,6 +493,17 @@ class PyKernel(Kernel):
 
     def jit_us(self):
         return float(self._lib.dvm_last_jit_us(self._k))
+
+    def reset(self):
+        """RtKernelPy::Reset (src/pybind_api.cc:909-922): an eager kernel drops its graph, loads and stores so that the
+        next graph can be built on the same object; other kernel types keep theirs."""
+        if self._ktype != Kernel.K_EAGER:
+            return
+        self.release_io()
+        check_rc(self._lib.dvm_kernel_reset(self._k, self._ktype, self._flags), "reset")
+        self._loads = []
+        self._stores = []
+        self._keep = []
 
     def release_io(self):
         for rec in self._loads + self._stores:

@@ -98,6 +98,11 @@ class Tester(PyKernel):
         self.run(verbose)
         return all(self.check(op, e, eps, verbose) for op, e, eps in self.expects)
 
+    def reset(self):
+        PyKernel.reset(self)
+        self.is_codegen = False
+        self.expects = []
+
     def run_perf(self):
         self.codegen()
         return self.perf()

@@ -57,6 +57,9 @@ class RefKernel:
     def cast(self, x, dtype):
         return self.k.cast(x, self._dt(dtype))
 
+    def full(self, scalar, shape, dtype):
+        return self.k.full(scalar, list(shape), self._dt(dtype))
+
     def store(self, x):
         s = self.k.store(x)
         self._stores.append(s)
