@@ -139,7 +139,9 @@ enum UopHandler : uint32_t {
   UH_PRED_F, UH_PRED_I,                             // lane mask <- acc != 0
   UH_SELM,                                          // acc <- lane mask ? acc : b
   UH_CVT_F2I, UH_CVT_I2F, UH_CVT_NEZ_F, UH_CVT_NEZ_I,
-  UH_RACC_SUM, UH_RACC_MAX, UH_RACC_MIN,            // arg16 = partial slot
+  UH_RACC_SUM, UH_RACC_MAX, UH_RACC_MIN,            // arg16 = partial slot; any chunk (lanes past the end are masked)
+  UH_RACCF_FIRST,                                   // full chunks: handler = first + kind * 4 + partial slot
+  UH_RACCF_LAST = UH_RACCF_FIRST + 11,
   UH_ST_F32, UH_ST_F16, UH_ST_BF16, UH_ST_U8,       // dense, aligned tensor arg16: vector stores
   UH_STG,                                           // any tensor arg16
   UH_COUNT
@@ -209,6 +211,9 @@ struct VmParam {
   // word offset of PRO_0, BODY_0, PRO_1, ..., PRO_n in code[]: PRO sections hold instruction words ending
   // with OP_END, BODY sections hold micro-ops ending with UH_END
   uint16_t sec[2 * kMaxPhases + 2];
+  // BODY sections come twice: the one in sec[] assumes a chunk in which every lane of every thread is valid
+  // (ring loads, vector stores, unmasked reductions), this one takes any chunk
+  uint16_t sec_any[kMaxPhases];
   uint32_t n_tensors;
   uint32_t n_code;
   TensorDesc tensor[kMaxTensors];

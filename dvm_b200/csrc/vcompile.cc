@@ -1157,21 +1157,29 @@ bool CompileEpilogue(const std::vector<NDObject *> &ops, const NDObject *mma_src
   }
 }
 
-void LowerStage(VectorStage *st) {
+namespace {
+// `dual`: every BODY is lowered twice, once for chunks in which every lane is valid and once for any chunk; without it
+// (programs too long to carry both) the any-chunk variant serves both.  Returns false when the words do not fit.
+bool LowerStageAs(VectorStage *st, bool dual) {
   using namespace dvmb;
   VmParam &P = st->param;
   uint32_t n = 0;
+  bool overflow = false;
   auto push = [&](uint64_t w) {
-    if (n >= static_cast<uint32_t>(kMaxCodeWords)) DvmException("lowered program exceeds the launch capacity");
+    if (n >= static_cast<uint32_t>(kMaxCodeWords)) {
+      overflow = true;
+      return;
+    }
     P.code[n++] = w;
   };
   // fetch of an operand into destination `dest`
+  bool full = true;   // lowering the variant for full chunks
   auto fetch = [&](uint32_t kind, uint32_t idx, uint32_t imm, uint32_t dest) {
     switch (kind) {
       case K_TENSOR: {
         const TensorDesc &td = P.tensor[idx];
         const uint32_t aux = dest | (idx << 2);
-        if (td.ring_off != kNoRing) {
+        if (full && td.ring_off != kNoRing) {
           static const uint32_t by_dtype[] = {UH_LDR_U8, UH_LDR_F16, UH_LDR_BF16, UH_LDR_F32, UH_LDR_F32};
           push(MakeUop(by_dtype[td.dtype] + (dest == UD_ACC ? UH_LDRA_F32 - UH_LDR_F32 : 0u), aux, td.ring_off >> 4, 0));
         } else {
@@ -1191,8 +1199,18 @@ void LowerStage(VectorStage *st) {
     if (rnd == RN_F16) push(MakeUop(UH_RND_F16, 0, 0, 0));
     if (rnd == RN_BF16) push(MakeUop(UH_RND_BF16, 0, 0, 0));
   };
-  for (uint32_t sidx = 0; sidx <= 2 * P.num_body; ++sidx) {
-    P.sec[sidx] = static_cast<uint16_t>(n);
+  // every BODY is lowered twice (full chunks, any chunk); PRO sections once
+  for (uint32_t pass = 0; pass <= 3 * P.num_body; ++pass) {
+    const bool second = pass > 2 * P.num_body;
+    const uint32_t sidx = second ? 2 * (pass - 2 * P.num_body - 1) + 1 : pass;
+    if (second && !dual) break;
+    full = dual && !second;
+    if (second) {
+      P.sec_any[sidx >> 1] = static_cast<uint16_t>(n);
+    } else {
+      P.sec[sidx] = static_cast<uint16_t>(n);
+      if ((sidx & 1u) && !dual) P.sec_any[sidx >> 1] = static_cast<uint16_t>(n);
+    }
     const bool body = (sidx & 1u) != 0;
     for (uint32_t pc = st->bsec[sidx];; ++pc) {
       const uint64_t w = st->bytecode[pc];
@@ -1260,11 +1278,17 @@ void LowerStage(VectorStage *st) {
           round(DVMB_RND(w));
           break;
         }
-        case OP_RACC: push(MakeUop(UH_RACC_SUM + (sub >> 4), 0, sub & 3u, 0)); break;
+        case OP_RACC:
+          if (full) {
+            push(MakeUop(UH_RACCF_FIRST + (sub >> 4) * 4u + (sub & 3u), 0, 0, 0));
+          } else {
+            push(MakeUop(UH_RACC_SUM + (sub >> 4), 0, sub & 3u, 0));
+          }
+          break;
         case OP_ST: {
           const TensorDesc &td = P.tensor[sub];
           static const uint32_t by_dtype[] = {UH_ST_U8, UH_ST_F16, UH_ST_BF16, UH_ST_F32, UH_ST_F32};
-          push(MakeUop(td.chunk_contig && td.vec_ok ? by_dtype[td.dtype] : UH_STG, 0, sub, 0));
+          push(MakeUop(full && td.chunk_contig && td.vec_ok ? by_dtype[td.dtype] : UH_STG, 0, sub, 0));
           break;
         }
         default: break;
@@ -1272,6 +1296,13 @@ void LowerStage(VectorStage *st) {
     }
   }
   P.n_code = n;
+  return !overflow;
+}
+}  // namespace
+
+void LowerStage(VectorStage *st) {
+  if (LowerStageAs(st, true)) return;
+  if (!LowerStageAs(st, false)) DvmException("lowered program exceeds the launch capacity");
 }
 
 

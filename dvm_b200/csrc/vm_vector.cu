@@ -580,7 +580,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
       }
       if (ph == P.num_body) break;
       // ---------------- vector side: BODY_ph over the chunks ----------------
-      const uint32_t body_pc = P.sec[2 * ph + 1];
+      const uint32_t body_pc = P.sec[2 * ph + 1], body_pc_any = P.sec_any[ph];
       const bool staged_body = ring && (resident || P.body_ring_mask[ph] != 0);
       const bool release_slots = !resident || ph + 1 == P.num_body;
       for (uint32_t ch = ch_begin; ch < ch_end; ch += ch_step) {
@@ -622,7 +622,8 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
         const bool full_tile = pos.gvalid && pos.in_chunk0 + 3u * pos.gstep + 4u <= pos.chunk_valid;
         // a thread without a single lane inside the chunk has nothing to fetch, add or store
         const bool lane_active = pos.gvalid && 4u * lane_in_group < pos.chunk_valid;
-        uint32_t pc_saddr = code_saddr + 8u * (lane_active ? body_pc : P.n_code - 1u);
+        // full chunks run the variant without per-lane tests; a thread with nothing to do starts at the final END
+        uint32_t pc_saddr = code_saddr + 8u * (full_tile ? body_pc : (lane_active ? body_pc_any : P.n_code - 1u));
         uint32_t ulo, uhi, nlo, nhi;   // the current micro-op and the next one, already on its way
         lds64x2(pc_saddr, ulo, uhi);
         for (;; ulo = nlo, uhi = nhi) {
@@ -632,13 +633,10 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
           if (uh == UH_END) break;   // (kept out of the switch: a compare is cheaper than the indexed jump)
           pc_saddr += 8u;
           lds64x2(pc_saddr, nlo, nhi);
-          uint32_t slot;
           switch (uh) {
             // ---------------- operand fetches ----------------
 #define DV_LDR_CASE(H, REG, MACRO, SHL)                                                                        \
   case H: {                                                                                                 \
-    slot = aux >> 2;                                                                                        \
-    if (!full_tile) goto fetch_generic;                                                                     \
     const uint32_t a0 = stage_saddr + (arg << 4) + (SHL(pos.in_chunk0)), gs = SHL(pos.gstep);               \
     MACRO(REG, a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)                                                      \
     continue;                                                                                               \
@@ -656,10 +654,8 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             DV_LDR_CASE(UH_LDRA_U8, "va", DV_LDR_U8, DV_SHL0)
 #undef DV_LDR_CASE
             case UH_LDG: {
-              slot = aux >> 2;
-            fetch_generic:
               uint32_t t[kLanes];
-              fetch_tensor(P, slot, pos, stage_saddr, t);
+              fetch_tensor(P, aux >> 2, pos, stage_saddr, t);
               DV_BY_DEST(aux & 3u, DV_SET, t)
               continue;
             }
@@ -803,35 +799,29 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             case UH_RACC_SUM:
             case UH_RACC_MAX:
             case UH_RACC_MIN: {
+              // any chunk: lanes past the end of the chunk do not take part
               const uint32_t kind = uh - UH_RACC_SUM;
-              float v;
-              if (full_tile) {
-                // reduce the 16 lanes in registers, in lane order
-                uint32_t r;
-                if (kind == R_SUM) {
-                  asm volatile("{\n\t.reg .b32 s;\n\tmov.b32 s, 0;\n\t" DV_LN(DV_SUMLANE, "") "mov.b32 %0, s;\n\t}" : "=r"(r));
-                } else if (kind == R_MAX) {
-                  asm volatile("{\n\t.reg .b32 s;\n\t.reg .pred p;\n\tmov.b32 s, 0xff800000;\n\t" DV_LN(DV_MAXLANE, "") "mov.b32 %0, s;\n\t}" : "=r"(r));
-                } else {
-                  asm volatile("{\n\t.reg .b32 s;\n\t.reg .pred p;\n\tmov.b32 s, 0x7f800000;\n\t" DV_LN(DV_MINLANE, "") "mov.b32 %0, s;\n\t}" : "=r"(r));
-                }
-                v = u2f(r);
-              } else {
-                uint32_t x[kLanes];
-                DV_GET("va", x)
-                v = red_identity(kind);
+              uint32_t x[kLanes];
+              DV_GET("va", x)
+              float v = red_identity(kind);
 #pragma unroll
-                for (int i = 0; i < kLanes; ++i) {
-                  const int32_t left = (int32_t)pos.chunk_valid - (int32_t)(pos.in_chunk0 + (uint32_t)(i >> 2) * pos.gstep);
-                  if (pos.gvalid && (i & 3) < left) v = red_combine(kind, v, u2f(x[i]));
-                }
+              for (int i = 0; i < kLanes; ++i) {
+                const int32_t left = (int32_t)pos.chunk_valid - (int32_t)(pos.in_chunk0 + (uint32_t)(i >> 2) * pos.gstep);
+                if (pos.gvalid && (i & 3) < left) v = red_combine(kind, v, u2f(x[i]));
               }
               set_part(arg & 3u, red_combine(kind, get_part(arg & 3u), v));
               continue;
             }
+            // full chunks: the 16 lanes are combined as a tree, one handler per partial register
+#define DV_RACCF(KIND, SLOT, TREE) case UH_RACCF_FIRST + KIND * 4 + SLOT: asm volatile(TREE(#SLOT)); continue;
+#define DV_RACCF4(KIND, TREE) DV_RACCF(KIND, 0, TREE) DV_RACCF(KIND, 1, TREE) DV_RACCF(KIND, 2, TREE) DV_RACCF(KIND, 3, TREE)
+            DV_RACCF4(R_SUM, DV_SUM_TREE)
+            DV_RACCF4(R_MAX, DV_MAX_TREE)
+            DV_RACCF4(R_MIN, DV_MIN_TREE)
+#undef DV_RACCF4
+#undef DV_RACCF
             // ---------------- stores ----------------
             case UH_ST_F32: {
-              if (!full_tile) goto store_generic;
               const TensorDesc &td = tdesc[arg];
               uint32_t *p0 = reinterpret_cast<uint32_t *>(td.ptr) + kept_offset(td, pos.k) + (!kCoords || td.mode == AM_DENSE ? pos.e_start : enum_offset(td, cc)) + pos.in_chunk0;
               const uint32_t gs = pos.gstep;
@@ -843,7 +833,6 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             }
             case UH_ST_F16:
             case UH_ST_BF16: {
-              if (!full_tile) goto store_generic;
               const TensorDesc &td = tdesc[arg];
               unsigned short *p0 = reinterpret_cast<unsigned short *>(td.ptr) + kept_offset(td, pos.k) + (!kCoords || td.mode == AM_DENSE ? pos.e_start : enum_offset(td, cc)) + pos.in_chunk0;
               const uint32_t gs = pos.gstep;
@@ -865,7 +854,6 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             }
             case UH_ST_U8:
             case UH_STG: {
-            store_generic:
               uint32_t x[kLanes];
               DV_GET("va", x)
               store_tensor(P, arg, pos, x);

@@ -41,9 +41,19 @@
 #define DV_GETLANE(i, R) "mov.b32 %" #i ", " R #i ";\n\t"
 #define DV_SETLANE(i, R) "mov.b32 " R #i ", %" #i ";\n\t"
 #define DV_SPLATLANE(i, R) "mov.b32 " R #i ", %0;\n\t"
-#define DV_SUMLANE(i, X) "add.f32 s, s, va" #i ";\n\t"
-#define DV_MAXLANE(i, X) "setp.gt.f32 p, s, va" #i ";\n\tselp.b32 s, s, va" #i ", p;\n\t"
-#define DV_MINLANE(i, X) "setp.lt.f32 p, s, va" #i ";\n\tselp.b32 s, s, va" #i ", p;\n\t"
+// tree reductions of the 16 accumulator lanes into partial register vp<SLOT>
+#define DV_TREE16(OP2, SLOT)                                                                                       \
+  "{\n\t.reg .b32 r<8>;\n\t.reg .pred p;\n\t"                                                                      \
+  OP2("r0", "va0", "va1") OP2("r1", "va2", "va3") OP2("r2", "va4", "va5") OP2("r3", "va6", "va7")                  \
+  OP2("r4", "va8", "va9") OP2("r5", "va10", "va11") OP2("r6", "va12", "va13") OP2("r7", "va14", "va15")            \
+  OP2("r0", "r0", "r1") OP2("r2", "r2", "r3") OP2("r4", "r4", "r5") OP2("r6", "r6", "r7")                          \
+  OP2("r0", "r0", "r2") OP2("r4", "r4", "r6") OP2("r0", "r0", "r4") OP2("vp" SLOT, "vp" SLOT, "r0") "}"
+#define DV_ADD2(D, A, B) "add.f32 " D ", " A ", " B ";\n\t"
+#define DV_MAX2(D, A, B) "setp.gt.f32 p, " A ", " B ";\n\tselp.b32 " D ", " A ", " B ", p;\n\t"
+#define DV_MIN2(D, A, B) "setp.lt.f32 p, " A ", " B ";\n\tselp.b32 " D ", " A ", " B ", p;\n\t"
+#define DV_SUM_TREE(SLOT) DV_TREE16(DV_ADD2, SLOT)
+#define DV_MAX_TREE(SLOT) DV_TREE16(DV_MAX2, SLOT)
+#define DV_MIN_TREE(SLOT) DV_TREE16(DV_MIN2, SLOT)
 
 // ---- whole-register operations ---------------------------------------------------------------------------
 #define DV_OUT16(X)                                                                                                   \
