@@ -179,6 +179,12 @@ struct Compiler {
           break;
         }
       }
+      // two dims of one value on the same axis: a reshape moved a dim across its partner's position, which only a
+      // view of memory can express (the planner then gives the reshape a stage boundary)
+      for (int i = 0; i < r; ++i)
+        for (int j = i + 1; j < r; ++j)
+          if (fi.axis[i] >= 0 && fi.axis[i] == fi.axis[j] && n->shape.d[i] != 1 && n->shape.d[j] != 1)
+            throw Fail{"general reshape inside a stage"};
     }
     // domain sizes
     for (int a = 0; a < R; ++a) dom[a] = 1;

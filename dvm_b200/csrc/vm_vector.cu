@@ -547,7 +547,10 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             float v = get_part(sub & 3u);
             set_part(sub & 3u, red_identity(kind));
             if (tg <= 32) {
-              for (uint32_t o = tg >> 1; o > 0; o >>= 1) v = red_combine(kind, v, __shfl_xor_sync(0xffffffffu, v, o));
+              // several groups per warp: tg is a power of two; one group per CTA: tg may be any size up to a warp, and
+              // the lanes past it hold the identity
+              for (uint32_t o = P.groups_per_cta == 1 ? 16u : tg >> 1; o > 0; o >>= 1)
+                v = red_combine(kind, v, __shfl_xor_sync(0xffffffffu, v, o));
             } else {
 #pragma unroll
               for (uint32_t o = 16; o > 0; o >>= 1) v = red_combine(kind, v, __shfl_xor_sync(0xffffffffu, v, o));
