@@ -1,4 +1,5 @@
-"""Records the reference's own GPU-marked unit tests (mindspore-ai/dvm, tests/ut, `-m gpu`) as replayable fixtures.
+"""Records the reference's own unit tests for this path (mindspore-ai/dvm, tests/ut: every test marked `gpu`, plus the
+unmarked MatMul / reduce / speculative-vector / tiling tests of the same files) as replayable fixtures.
 
 The reference's tests build a graph through `dvm.tester.Tester`, feed NumPy inputs and compare the device result with a
 NumPy expectation under a stated tolerance; they hold no stored vectors.  This script runs those test functions in THIS
@@ -29,6 +30,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 CASE_CAP_BYTES = 96 * 1024       # arrays of one test
 TOTAL_CAP_BYTES = 6 * 1024 * 1024
+IN_SCOPE_FILES = ["test_matmul.py", "test_reduce.py", "test_spec_vector.py", "test_tiling.py", "test_reshape.py",
+                  "test_broadcast.py", "test_unalign.py", "test_composite_ops.py", "test_dynamic_shape.py", "test_codegen.py"]
 SPEC_CAP_BYTES = 96 * 1024 * 1024   # a test recorded without its arrays still has to replay in seconds
 
 
@@ -265,9 +268,13 @@ def main(ref="/root/reference"):
     sys.modules["tests.mark_utils"] = marks
     plugin = Plugin()
     os.chdir(ref)
-    pytest.main(["tests/ut", "-m", "gpu", "-q", "-p", "no:cacheprovider", "--no-header", "--continue-on-collection-errors"],
-                plugins=[plugin])
-    header = {"source": "mindspore-ai/dvm tests/ut, -m gpu", "recorded": len(plugin.cases),
+    common = ["-q", "-p", "no:cacheprovider", "--no-header", "--continue-on-collection-errors"]
+    pytest.main(["tests/ut", "-m", "gpu"] + common, plugins=[plugin])
+    # the reference's CUDA backend has no MatMul and no max / min reduction, so its tests of those (and of the
+    # speculative vector kernels and tilings on the same path) carry no gpu mark: take them from the files of this path
+    pytest.main(["tests/ut/" + f for f in IN_SCOPE_FILES] + ["-m", "not gpu"] + common, plugins=[plugin])
+    header = {"source": "mindspore-ai/dvm tests/ut: every test marked gpu, and the unmarked tests of " + ", ".join(IN_SCOPE_FILES),
+              "recorded": len(plugin.cases),
               "with_arrays": sum(1 for c in plugin.cases if not c.get("spec")), "left_out": plugin.skipped}
     with open(os.path.join(HERE, "reference_suite.json"), "w") as f:
         json.dump({"header": header, "cases": plugin.cases}, f, separators=(",", ":"))
