@@ -57,9 +57,22 @@ enum Opcode : uint32_t {
   OP_COUNT
 };
 
+// Scalar sections of a lowered program: the host replaces the opcode byte of the common forms (no rounding, operand an
+// immediate, a scalar register or the accumulator) by one of these flat handler ids, so that the device dispatches once
+// per word; every other word keeps its opcode (< SOP_FIRST) and takes the general decode path.
+enum ScalarOp : uint32_t {
+  SOP_FIRST = 16,
+  SOP_COPY = SOP_FIRST, SOP_MOV, SOP_RINIT, SOP_RFIN,
+  SOP_UN_FIRST,                      // + UnKind
+  SOP_BIN_FIRST = SOP_UN_FIRST + 12, // + BinKind
+  SOP_CVT_FIRST = SOP_BIN_FIRST + 17,   // + CvtKind (V_F2I .. V_NEZ_I)
+  SOP_COUNT = SOP_CVT_FIRST + 4
+};
+
 enum UnKind : uint32_t { U_SQRT = 0, U_ABS, U_LOG, U_EXP, U_ROUND, U_FLOOR, U_CEIL, U_TRUNC, U_ISFINITE, U_ABS_I,
                          U_EXP_FAST,   // exp through ex2.approx (relative error about 1e-6): values that never reach an exact-class op
                          U_NOP };
+static_assert(U_NOP + 1 == 12, "ScalarOp numbering follows UnKind");
 
 enum BinKind : uint32_t {
   B_ADD = 0, B_SUB, B_MUL, B_DIV, B_MAX, B_MIN, B_POW, B_RSUB, B_RDIV,
@@ -67,6 +80,7 @@ enum BinKind : uint32_t {
   B_DIV_FAST, B_RDIV_FAST,   // 2-ulp full-range division, same eligibility rule as U_EXP_FAST
   B_COUNT
 };
+static_assert(B_COUNT == 17, "ScalarOp numbering follows BinKind");
 
 enum CmpKind : uint32_t { C_EQ = 0, C_NE, C_GT, C_GE, C_LT, C_LE };
 

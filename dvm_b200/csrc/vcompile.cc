@@ -1221,8 +1221,22 @@ bool LowerStageAs(VectorStage *st, bool dual) {
     for (uint32_t pc = st->bsec[sidx];; ++pc) {
       const uint64_t w = st->bytecode[pc];
       const uint32_t opc = DVMB_OPC(w), sub = DVMB_SUB(w), okind = DVMB_OKIND(w), oidx = DVMB_OIDX(w);
-      if (!body) {   // scalar sections run from the instruction words as they are
-        push(w);
+      if (!body) {
+        // scalar sections keep the instruction-word format; the common forms get a flat handler id as opcode
+        uint32_t flat = opc;
+        const bool plain_operand = okind == K_SREG || okind == K_IMM || okind == K_ACC;
+        const bool no_round = DVMB_RND(w) == RN_NONE;
+        switch (opc) {
+          case OP_COPY: if (plain_operand) flat = SOP_COPY; break;
+          case OP_MOV: flat = SOP_MOV; break;
+          case OP_RINIT: flat = SOP_RINIT; break;
+          case OP_RFIN: flat = SOP_RFIN; break;
+          case OP_UN: if (no_round && sub <= U_NOP) flat = SOP_UN_FIRST + sub; break;
+          case OP_BIN: if (no_round && plain_operand && sub < B_COUNT) flat = SOP_BIN_FIRST + sub; break;
+          case OP_CVT: if (no_round && sub <= V_NEZ_I) flat = SOP_CVT_FIRST + sub; break;
+          default: break;
+        }
+        push((w & ~(0xffull << 32)) | (static_cast<uint64_t>(flat) << 32));
         if (opc == OP_END) break;
         continue;
       }

@@ -502,83 +502,118 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
     }
     for (uint32_t ph = 0; ph <= P.num_body; ++ph) {
       // ---------------- scalar side: PRO_ph ----------------
-      for (uint32_t pc = P.sec[2 * ph];;) {
-        const uint64_t w = lds64(code_saddr + 8u * pc++);
-        const uint32_t opc = DVMB_OPC(w);
-        if (opc == OP_END) break;
-        const uint32_t sub = DVMB_SUB(w);
-        uint32_t sb = 0;
-        if (opc == OP_COPY || opc == OP_BIN || opc == OP_CMP || opc == OP_SEL) {
-          const uint32_t okind = DVMB_OKIND(w), oidx = DVMB_OIDX(w);
-          if (okind == K_SREG) {
-            sb = lds32(sreg_addr(oidx));
-          } else if (okind == K_IMM) {
-            sb = DVMB_IMM(w);
-          } else if (okind == K_TENSOR) {
-            const TensorDesc &td = tdesc[oidx];
-            sb = load_elem(td.dtype, reinterpret_cast<const uint8_t *>(td.ptr), kept_offset(td, pos.k));
-          } else {
-            sb = sacc[0];
-          }
-        }
-        const SplatOperand bo{sb};
-        switch (opc) {
-          case OP_ST: {
-            const TensorDesc &td = tdesc[sub];
-            if (lane_in_group == 0 && pos.gvalid && rank == 0 && (!flat || blockIdx.x == 0))
-              store_elem(td.dtype, reinterpret_cast<uint8_t *>(td.ptr), kept_offset(td, pos.k), sacc[0]);
-            break;
-          }
-          case OP_COPY: sacc[0] = sb; break;
-          case OP_MOV: asm volatile("st.shared.u32 [%0], %1;" ::"r"(sreg_addr(DVMB_DST(w))), "r"(sacc[0]) : "memory"); break;
-          case OP_UN: apply_un<1>(sub, sacc); apply_round<1>(DVMB_RND(w), sacc); break;
-          case OP_BIN: apply_bin<1>(sub, sacc, bo); apply_round<1>(DVMB_RND(w), sacc); break;
-          case OP_CMP: apply_cmp<1>(sub, DVMB_ISINT(w), sacc, bo); break;
-          case OP_SEL: {
-            uint32_t sc[1];
-            sc[0] = lds32(sreg_addr(sub & 15u));
-            apply_sel<1>(DVMB_ISINT(w), DVMB_DST(w) & 1u, sacc, bo, sc);
-            break;
-          }
-          case OP_CVT: apply_cvt<1>(sub, sacc); apply_round<1>(DVMB_RND(w), sacc); break;
-          case OP_RINIT: set_part(sub & 3u, red_identity(sub >> 4)); break;
-          case OP_RFIN: {
-            const uint32_t kind = sub >> 4;
-            float v = get_part(sub & 3u);
-            set_part(sub & 3u, red_identity(kind));
-            if (tg <= 32) {
-              // several groups per warp: tg is a power of two; one group per CTA: tg may be any size up to a warp, and
-              // the lanes past it hold the identity
-              for (uint32_t o = P.groups_per_cta == 1 ? 16u : tg >> 1; o > 0; o >>= 1)
-                v = red_combine(kind, v, __shfl_xor_sync(0xffffffffu, v, o));
-            } else {
+      {
+        uint32_t spc = code_saddr + 8u * P.sec[2 * ph];
+        uint32_t wlo, whi, xlo, xhi;   // the current word and the next one, already on its way
+        lds64x2(spc, wlo, whi);
+        for (;; wlo = xlo, whi = xhi) {
+          const uint32_t sop = whi & 0xffu;   // a flat ScalarOp id, or the opcode of a word that takes the general path
+          if (sop == OP_END) break;
+          spc += 8u;
+          lds64x2(spc, xlo, xhi);
+          const uint32_t sub = (whi >> 8) & 0xffu;
+          const uint32_t okind = (whi >> 16) & 0xfu, oidx = (whi >> 20) & 0xfu;
+          // operand of the flat forms (immediate, scalar register, accumulator), fetched without a branch
+          const uint32_t sv = lds32(okind == K_SREG ? sreg_addr(oidx) : code_saddr);
+          const uint32_t sb = okind == K_SREG ? sv : (okind == K_ACC ? sacc[0] : wlo);
+          switch (sop) {
+            case SOP_COPY: sacc[0] = sb; break;
+            case SOP_MOV: asm volatile("st.shared.u32 [%0], %1;" ::"r"(sreg_addr((whi >> 24) & 0xfu)), "r"(sacc[0]) : "memory"); break;
+            case SOP_RINIT: set_part(sub & 3u, red_identity(sub >> 4)); break;
+            case SOP_RFIN: {
+              const uint32_t kind = sub >> 4;
+              float v = get_part(sub & 3u);
+              set_part(sub & 3u, red_identity(kind));
+              if (tg <= 32) {
+                // several groups per warp: tg is a power of two; one group per CTA: tg may be any size up to a warp, and
+                // the lanes past it hold the identity
+                for (uint32_t o = P.groups_per_cta == 1 ? 16u : tg >> 1; o > 0; o >>= 1)
+                  v = red_combine(kind, v, __shfl_xor_sync(0xffffffffu, v, o));
+              } else {
 #pragma unroll
-              for (uint32_t o = 16; o > 0; o >>= 1) v = red_combine(kind, v, __shfl_xor_sync(0xffffffffu, v, o));
-              if ((tid & 31u) == 0) red_buf[red_par * 32 + (tid >> 5)] = v;
-              asm volatile("bar.sync 1, %0;" ::"r"(T) : "memory");   // consumer warps only
-              const uint32_t nw = T >> 5;
-              v = red_buf[red_par * 32];
-              for (uint32_t wi = 1; wi < nw; ++wi) v = red_combine(kind, v, red_buf[red_par * 32 + wi]);
-              red_par ^= 1u;
-            }
-            if (cluster > 1) {
-              // combine the CTA totals of the cluster in rank order: publish ours, signal every CTA, read all
-              float *xpart = reinterpret_cast<float *>(smem + kVmSmemXPart);
-              if (tid == 0) {
-                xpart[xpar] = v;
-                for (uint32_t r = 0; r < cluster; ++r) mbar_arrive_remote_release(map_shared_rank(smem_base + kVmSmemXBar, r));
+                for (uint32_t o = 16; o > 0; o >>= 1) v = red_combine(kind, v, __shfl_xor_sync(0xffffffffu, v, o));
+                if ((tid & 31u) == 0) red_buf[red_par * 32 + (tid >> 5)] = v;
+                asm volatile("bar.sync 1, %0;" ::"r"(T) : "memory");   // consumer warps only
+                // every warp's partial (at most 16 warps) is read at once and combined as a tree
+                const uint32_t nw = T >> 5;
+                float pv[16];
+#pragma unroll
+                for (uint32_t wi = 0; wi < 16; ++wi) pv[wi] = wi < nw ? red_buf[red_par * 32 + wi] : red_identity(kind);
+                if (kind == R_SUM) {
+#pragma unroll
+                  for (int h = 8; h > 0; h >>= 1)
+#pragma unroll
+                    for (int i = 0; i < h; ++i) pv[i] += pv[i + h];
+                } else {
+#pragma unroll
+                  for (int h = 8; h > 0; h >>= 1)
+#pragma unroll
+                    for (int i = 0; i < h; ++i) pv[i] = red_combine(kind, pv[i], pv[i + h]);
+                }
+                v = pv[0];
+                red_par ^= 1u;
               }
-              mbar_wait_cluster(smem_base + kVmSmemXBar, xphase);
-              xphase ^= 1u;
-              v = ld_shared_cluster_f32(map_shared_rank(smem_base + kVmSmemXPart + 4u * xpar, 0));
-              for (uint32_t r = 1; r < cluster; ++r)
-                v = red_combine(kind, v, ld_shared_cluster_f32(map_shared_rank(smem_base + kVmSmemXPart + 4u * xpar, r)));
-              xpar ^= 1u;
+              if (cluster > 1) {
+                // combine the CTA totals of the cluster in rank order: publish ours, signal every CTA, read all
+                float *xpart = reinterpret_cast<float *>(smem + kVmSmemXPart);
+                if (tid == 0) {
+                  xpart[xpar] = v;
+                  for (uint32_t r = 0; r < cluster; ++r) mbar_arrive_remote_release(map_shared_rank(smem_base + kVmSmemXBar, r));
+                }
+                mbar_wait_cluster(smem_base + kVmSmemXBar, xphase);
+                xphase ^= 1u;
+                v = ld_shared_cluster_f32(map_shared_rank(smem_base + kVmSmemXPart + 4u * xpar, 0));
+                for (uint32_t r = 1; r < cluster; ++r)
+                  v = red_combine(kind, v, ld_shared_cluster_f32(map_shared_rank(smem_base + kVmSmemXPart + 4u * xpar, r)));
+                xpar ^= 1u;
+              }
+              sacc[0] = f2u(v);
+              break;
             }
-            sacc[0] = f2u(v);
-            break;
+#define DV_SUN(K) case SOP_UN_FIRST + K: apply_un<1>(K, sacc); break;
+            DV_SUN(U_SQRT) DV_SUN(U_ABS) DV_SUN(U_LOG) DV_SUN(U_EXP) DV_SUN(U_ROUND) DV_SUN(U_FLOOR) DV_SUN(U_CEIL)
+            DV_SUN(U_TRUNC) DV_SUN(U_ISFINITE) DV_SUN(U_ABS_I) DV_SUN(U_EXP_FAST) DV_SUN(U_NOP)
+#undef DV_SUN
+#define DV_SBIN(K) case SOP_BIN_FIRST + K: apply_bin<1>(K, sacc, SplatOperand{sb}); break;
+            DV_SBIN(B_ADD) DV_SBIN(B_SUB) DV_SBIN(B_MUL) DV_SBIN(B_DIV) DV_SBIN(B_MAX) DV_SBIN(B_MIN) DV_SBIN(B_POW)
+            DV_SBIN(B_RSUB) DV_SBIN(B_RDIV) DV_SBIN(B_ADD_I) DV_SBIN(B_SUB_I) DV_SBIN(B_MUL_I) DV_SBIN(B_MAX_I)
+            DV_SBIN(B_MIN_I) DV_SBIN(B_RSUB_I) DV_SBIN(B_DIV_FAST) DV_SBIN(B_RDIV_FAST)
+#undef DV_SBIN
+#define DV_SCVT(K) case SOP_CVT_FIRST + K: apply_cvt<1>(K, sacc); break;
+            DV_SCVT(V_F2I) DV_SCVT(V_I2F) DV_SCVT(V_NEZ_F) DV_SCVT(V_NEZ_I)
+#undef DV_SCVT
+            default: {
+              // general path: the word keeps its opcode (tensor operands, rounding to 16 bit, compares, selects, stores)
+              const uint64_t w = ((uint64_t)whi << 32) | wlo;
+              uint32_t gb_ = sb;
+              if (okind == K_TENSOR && (sop == OP_COPY || sop == OP_BIN || sop == OP_CMP || sop == OP_SEL)) {
+                const TensorDesc &td = tdesc[oidx];
+                gb_ = load_elem(td.dtype, reinterpret_cast<const uint8_t *>(td.ptr), kept_offset(td, pos.k));
+              }
+              const SplatOperand bo{gb_};
+              switch (sop) {
+                case OP_ST: {
+                  const TensorDesc &td = tdesc[sub];
+                  if (lane_in_group == 0 && pos.gvalid && rank == 0 && (!flat || blockIdx.x == 0))
+                    store_elem(td.dtype, reinterpret_cast<uint8_t *>(td.ptr), kept_offset(td, pos.k), sacc[0]);
+                  break;
+                }
+                case OP_COPY: sacc[0] = gb_; break;
+                case OP_UN: apply_un<1>(sub, sacc); apply_round<1>(DVMB_RND(w), sacc); break;
+                case OP_BIN: apply_bin<1>(sub, sacc, bo); apply_round<1>(DVMB_RND(w), sacc); break;
+                case OP_CMP: apply_cmp<1>(sub, DVMB_ISINT(w), sacc, bo); break;
+                case OP_SEL: {
+                  uint32_t sc[1];
+                  sc[0] = lds32(sreg_addr(sub & 15u));
+                  apply_sel<1>(DVMB_ISINT(w), DVMB_DST(w) & 1u, sacc, bo, sc);
+                  break;
+                }
+                case OP_CVT: apply_cvt<1>(sub, sacc); apply_round<1>(DVMB_RND(w), sacc); break;
+                default: break;
+              }
+              break;
+            }
           }
-          default: break;
         }
       }
       if (ph == P.num_body) break;
