@@ -597,7 +597,10 @@ def main():
                     lo_r, hi_r, mean_r = got[0].perf()
                     ref[other] = {"us_per_run": mean_r, "rate": work_of(other, got[1], got[2]) / (mean_r * 1e-6) / unit_scale(other),
                                   "unit": unit_of(other), "kernels": got[0].k.das().count("vmain")}
-                    got[0].k.release_io()
+                    try:
+                        got[0].k.release_io()   # frees its device buffers now (its split kernels refuse and free on destruction)
+                    except RuntimeError:
+                        pass
                 del got
             line["reference_cuda_backend"] = ref or "not available"
     if rank == 0:

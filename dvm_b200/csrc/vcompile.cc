@@ -1000,7 +1000,7 @@ struct Compiler {
     const uint32_t fixed = kVmSmemStages + P.num_temps * T * (4u * kLanes) + P.num_sregs * T * 4u;
     uint32_t stages = 0;
     if (stage_bytes != 0) {
-      uint32_t budget = 100 * 1024;   // two CTAs of this size fit one SM
+      uint32_t budget = 106 * 1024;   // two CTAs of this size fit one SM
       if (const char *env = getenv("DVM_B200_RING_KB")) budget = static_cast<uint32_t>(atoi(env)) * 1024u;
       // enough stages to keep about 48 KB per CTA in flight (small tiles need a deep ring to cover the memory
       // latency), at least three; beyond that deeper read-ahead measured slower on large tiles
