@@ -89,6 +89,8 @@ struct VectorStage {
   uint32_t grid = 0, threads = 0, smem_bytes = 0;
   uint32_t body_tensor_mask[dvmb::kMaxPhases] = {0, 0, 0, 0};   // tensor slots each BODY reads
   bool idle = false;                       // zero-size domain: nothing to launch
+  uint32_t sregs_used = 0;                 // scalar registers the program names; the rest up to param.num_sregs hold
+                                           // reciprocals of group scalars that the lowering turns fast divisions into
   std::vector<uint64_t> bytecode;          // instruction words of every section (what Das() prints)
   uint16_t bsec[2 * dvmb::kMaxPhases + 2] = {0};   // section offsets inside `bytecode`
   std::vector<NDObject *> slot_obj;        // tensor slot -> load/store node (relocation sites)

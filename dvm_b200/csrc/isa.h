@@ -138,6 +138,8 @@ enum UopHandler : uint32_t {
   UH_LDS,                                           // scalar register arg16, splat
   UH_LDI,                                           // imm32, splat
   UH_MOVA,                                          // destination <- acc
+  UH_SQR,                                           // acc <- acc * acc (a product whose operand is the accumulator itself)
+  UH_RCP,                                           // acc <- 1 / acc, 1 ulp (the fast form of an immediate 1.0 divided by acc)
   UH_STT,                                           // temporary arg16 <- acc
   // acc <- op(acc, b)
   UH_BINV_FIRST,
@@ -209,6 +211,7 @@ struct VmParam {
   uint32_t tcons;            // consumer threads of the CTA: tg * groups_per_cta rounded up to a multiple of 32
   uint32_t chunks;           // chunks per group
   uint32_t chunk_elems;      // elements per chunk (<= 16 * tg; threads past the end idle)
+  uint32_t stages_off;       // byte offset of the first ring stage in shared memory (behind the program copy)
   uint32_t stage_bytes;      // bytes of one ring stage (0: no bulk staging in this launch)
   uint32_t num_stages;
   // resident groups: every chunk of a group keeps its own ring slot from the first phase to the last, so the

@@ -18,6 +18,8 @@
 
 namespace dvm {
 
+void LowerStage(VectorStage *st);
+
 uint32_t EncodeScalarRefNow(const ScalarRef *ref, DataType dtype);
 
 namespace {
@@ -1001,8 +1003,21 @@ struct Compiler {
     }
     // ---- shared memory plan
     P.num_temps = static_cast<uint32_t>(max_temp);
+    // a fast division of the vector side by a group scalar becomes a multiplication by its reciprocal, kept in a
+    // scalar register of its own (one per distinct divisor register, as far as registers are left)
+    {
+      uint32_t divisors = 0;
+      for (uint64_t w : code)
+        if (!DVMB_SCALAR(w) && DVMB_OPC(w) == OP_BIN && DVMB_SUB(w) == B_DIV_FAST && DVMB_OKIND(w) == K_SREG)
+          divisors |= 1u << DVMB_OIDX(w);
+      out->sregs_used = static_cast<uint32_t>(max_sreg);
+      max_sreg = std::min<int>(kNumSRegs, max_sreg + __builtin_popcount(divisors));
+    }
     P.num_sregs = static_cast<uint32_t>(max_sreg);
-    const uint32_t fixed = kVmSmemStages + P.num_temps * T * (4u * kLanes) + P.num_sregs * T * 4u;
+    // the lowered program's length does not depend on the addresses bound later: lower once now to size its copy
+    LowerStage(out);
+    P.stages_off = VmStagesOffset(P.n_code);
+    const uint32_t fixed = P.stages_off + P.num_temps * T * (4u * kLanes) + P.num_sregs * T * 4u;
     uint32_t stages = 0;
     if (stage_bytes != 0) {
       uint32_t budget = 106 * 1024;   // two CTAs of this size fit one SM
@@ -1185,6 +1200,17 @@ bool LowerStageAs(VectorStage *st, bool dual) {
     P.code[n++] = w;
   };
   // fetch of an operand into destination `dest`
+  // reciprocal registers: divisor register -> register that holds 1 / divisor (computed at the end of the scalar
+  // section in front of every body that divides by it)
+  int recip_of[16];
+  for (int i = 0; i < 16; ++i) recip_of[i] = -1;
+  {
+    uint32_t next = st->sregs_used;
+    for (uint64_t w : st->bytecode)
+      if (!DVMB_SCALAR(w) && DVMB_OPC(w) == OP_BIN && DVMB_SUB(w) == B_DIV_FAST && DVMB_OKIND(w) == K_SREG &&
+          recip_of[DVMB_OIDX(w)] < 0 && next < P.num_sregs)
+        recip_of[DVMB_OIDX(w)] = static_cast<int>(next++);
+  }
   bool full = true;   // lowering the variant for full chunks
   auto fetch = [&](uint32_t kind, uint32_t idx, uint32_t imm, uint32_t dest) {
     switch (kind) {
@@ -1242,6 +1268,21 @@ bool LowerStageAs(VectorStage *st, bool dual) {
           case OP_CVT: if (no_round && sub <= V_NEZ_I) flat = SOP_CVT_FIRST + sub; break;
           default: break;
         }
+        if (opc == OP_END && sidx < 2 * P.num_body) {
+          // reciprocals of the group scalars the next body divides by
+          uint32_t done_mask = 0;
+          for (uint32_t q = st->bsec[sidx + 1];; ++q) {
+            const uint64_t b = st->bytecode[q];
+            if (DVMB_OPC(b) == OP_END) break;
+            if (DVMB_OPC(b) != OP_BIN || DVMB_SUB(b) != B_DIV_FAST || DVMB_OKIND(b) != K_SREG) continue;
+            const uint32_t d = DVMB_OIDX(b);
+            if (recip_of[d] < 0 || ((done_mask >> d) & 1u)) continue;
+            done_mask |= 1u << d;
+            push(Insn::make(SOP_COPY, 0, K_SREG, d, 0, 0, 0, 1, 0));
+            push(Insn::make(SOP_BIN_FIRST + B_RDIV_FAST, 0, K_IMM, 0, 0, 0, 0, 1, 0x3f800000u));
+            push(Insn::make(SOP_MOV, 0, 0, 0, static_cast<uint32_t>(recip_of[d]), 0, 0, 1, 0));
+          }
+        }
         push((w & ~(0xffull << 32)) | (static_cast<uint64_t>(flat) << 32));
         if (opc == OP_END) break;
         continue;
@@ -1259,8 +1300,14 @@ bool LowerStageAs(VectorStage *st, bool dual) {
           round(DVMB_RND(w));
           break;
         case OP_BIN:
-          if (splat) {
+          if (splat && sub == B_RDIV_FAST && okind == K_IMM && DVMB_IMM(w) == 0x3f800000u) {
+            push(MakeUop(UH_RCP, 0, 0, 0));
+          } else if (splat && sub == B_DIV_FAST && okind == K_SREG && recip_of[oidx] >= 0) {
+            push(MakeUop(UH_BINS_FIRST + B_MUL, 1, static_cast<uint32_t>(recip_of[oidx]), 0));
+          } else if (splat) {
             push(MakeUop(UH_BINS_FIRST + sub, okind == K_SREG ? 1 : 0, oidx, DVMB_IMM(w)));
+          } else if (okind == K_ACC && sub == B_MUL) {
+            push(MakeUop(UH_SQR, 0, 0, 0));
           } else {
             fetch(okind, oidx, 0, UD_B);
             push(MakeUop(UH_BINV_FIRST + sub, 0, 0, 0));

@@ -21,9 +21,10 @@ constexpr uint32_t kVmSmemEmpty = 512;
 constexpr uint32_t kVmSmemRed = 1024;         // float[2][32]: warp partials of a CTA-wide reduction
 constexpr uint32_t kVmSmemXPart = 1280;       // float[2]: this CTA's partial for the cluster-wide combine
 constexpr uint32_t kVmSmemXBar = 1296;        // mbarrier of the cluster-wide combine
-constexpr uint32_t kVmSmemCode = 1536;        // copy of the program words (shared-memory fetch is faster than indexed parameter reads)
-constexpr uint32_t kVmSmemTensors = kVmSmemCode + 8 * dvmb::kMaxCodeWords;          // copy of the tensor table
-constexpr uint32_t kVmSmemStages = (kVmSmemTensors + sizeof(dvmb::TensorDesc) * dvmb::kMaxTensors + 127u) & ~127u;
+constexpr uint32_t kVmSmemTensors = 1536;     // copy of the tensor table (shared-memory reads are faster than indexed parameter reads)
+constexpr uint32_t kVmSmemCode = kVmSmemTensors + sizeof(dvmb::TensorDesc) * dvmb::kMaxTensors;   // copy of the program words
+// the ring stages follow the program at VmParam::stages_off (the program's capacity is fixed at compile time)
+constexpr uint32_t VmStagesOffset(uint32_t code_words) { return (kVmSmemCode + 8u * code_words + 127u) & ~127u; }
 
 // Enqueue the vector interpreter. Returns the cudaError_t of the launch (0 = ok).
 int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, uint32_t smem_bytes, void *stream);   // param.cluster > 1 launches clusters

@@ -352,7 +352,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             const uint32_t bytes = (valid << sh) & ~15u;
             if (bytes == 0) continue;
             const uint32_t off = kept_offset(td, k) + enum_offset(td, c);
-            bulk_g2s(smem_base + kVmSmemStages + slot * P.stage_bytes + td.ring_off,
+            bulk_g2s(smem_base + P.stages_off + slot * P.stage_bytes + td.ring_off,
                      reinterpret_cast<const uint8_t *>(td.ptr) + ((size_t)off << sh), bytes, full);
           }
         }
@@ -407,7 +407,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
           __syncwarp();
           if (bytes != 0) {
             const uint32_t off = koff + c[0] * es[0] + c[1] * es[1] + c[2] * es[2] + c[3] * es[3];
-            bulk_g2s(smem_base + kVmSmemStages + stage * P.stage_bytes + my_ring, my_base + ((size_t)off << sh), bytes, full);
+            bulk_g2s(smem_base + P.stages_off + stage * P.stage_bytes + my_ring, my_base + ((size_t)off << sh), bytes, full);
           }
           // next chunk of this CTA: advance the innermost coordinate and carry
           c[3] += step_elems;
@@ -434,7 +434,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
   // registers that only inline assembly names.  The compiler therefore carries no vector state across
   // the dispatch loop (nothing to copy at the switch merge), and ptxas keeps each one in a fixed register.
   float *red_buf = reinterpret_cast<float *>(smem + kVmSmemRed);
-  const uint32_t temps_saddr = smem_base + kVmSmemStages + S * P.stage_bytes;
+  const uint32_t temps_saddr = smem_base + P.stages_off + S * P.stage_bytes;
   const uint32_t sregs_saddr = temps_saddr + P.num_temps * T * (4u * kLanes);
   const uint32_t tg = P.tg;
   const uint32_t lane_in_group = flat ? tid : tid % tg;
@@ -643,11 +643,11 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
           if (resident) {
             // the chunk's own slot: filled once per group, waited for in the first phase only
             const uint32_t slot = res_set * P.cpc + (ch - ch_begin);
-            stage_saddr = smem_base + kVmSmemStages + slot * P.stage_bytes;
+            stage_saddr = smem_base + P.stages_off + slot * P.stage_bytes;
             empty_bar = smem_base + kVmSmemEmpty + 8 * slot;
             if (ph == 0) mbar_wait(smem_base + kVmSmemBarriers + 8 * slot, res_use & 1u, 2);
           } else {
-            stage_saddr = smem_base + kVmSmemStages + ring_stage * P.stage_bytes;
+            stage_saddr = smem_base + P.stages_off + ring_stage * P.stage_bytes;
             empty_bar = smem_base + kVmSmemEmpty + 8 * ring_stage;
             mbar_wait(smem_base + kVmSmemBarriers + 8 * ring_stage, ring_parity, 2);
             if (++ring_stage == S) {
@@ -711,6 +711,8 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             case UH_MOVA:
               asm volatile(DV_LN(DV_MOV_LANE, "vb", "va"));
               continue;
+            case UH_SQR: asm volatile(DV_LN(DV_SQR_LANE, "")); continue;
+            case UH_RCP: asm volatile(DV_LN(DV_UN_LANE, "rcp.approx.f32")); continue;
             case UH_STT: {
               const uint32_t a0 = temp_addr(arg, 0), gs = T * 16u;
               asm volatile("st.shared.v4.b32 [%0], {va0,va1,va2,va3};\n\tst.shared.v4.b32 [%1], {va4,va5,va6,va7};\n\t"
@@ -916,8 +918,9 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
 }
 }  // namespace
 
-// Two register budgets of the same interpreter: up to 256 consumer threads with two CTAs per SM (the
-// streaming shapes), and up to 512 consumer threads (long reduction rows) with one.
+// Two register budgets of the same interpreter: up to 256 consumer threads per CTA (two CTAs of that size per SM, four
+// of the 128-thread ones that reduce graphs with many groups use), and up to 512 (few long groups) with one CTA per SM.
+// A third budget of 72 registers (five 128-thread CTAs per SM) was measured 50 % slower: its spills sit in the loop.
 #define DVMB_VM_KERNEL(NAME, THREADS, BLOCKS, RES, COORDS)                                                       \
   __global__ void __launch_bounds__(THREADS, BLOCKS) NAME(const __grid_constant__ VmParam P) {                    \
     vm_vector_body<RES, COORDS>(P);                                                                                \

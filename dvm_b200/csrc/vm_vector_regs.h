@@ -27,6 +27,7 @@
 #define DV_RBINS_LANE(i, OP) OP " va" #i ", %0, va" #i ";\n\t"
 #define DV_PICKV_LANE(i, SETP) SETP " p, va" #i ", vb" #i ";\n\tselp.b32 va" #i ", va" #i ", vb" #i ", p;\n\t"
 #define DV_PICKS_LANE(i, SETP) SETP " p, va" #i ", %0;\n\tselp.b32 va" #i ", va" #i ", %0, p;\n\t"
+#define DV_SQR_LANE(i, X) "mul.f32 va" #i ", va" #i ", va" #i ";\n\t"
 #define DV_UN_LANE(i, OP) OP " va" #i ", va" #i ";\n\t"
 #define DV_EXPF_LANE(i, X) "mul.f32 va" #i ", va" #i ", 0f3FB8AA3B;\n\tex2.approx.ftz.f32 va" #i ", va" #i ";\n\t"
 #define DV_ISFIN_LANE(i, X) "testp.finite.f32 p, va" #i ";\n\tselp.b32 va" #i ", 0x3f800000, 0, p;\n\t"
