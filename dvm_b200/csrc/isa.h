@@ -224,6 +224,7 @@ struct VmParam {
   uint32_t kept_size[kMaxKept];
   uint32_t enum_size[kMaxEnum];   // right-aligned, unused outer slots are 1
   uint32_t need_coords;      // some tensor uses AM_GRANULE or is staged per segment
+  uint32_t body_coords_mask; // BODY sections whose vector stores address a strided tensor through the chunk coordinates
   uint32_t num_body;         // number of BODY sections
   // word offset of PRO_0, BODY_0, PRO_1, ..., PRO_n in code[]: PRO sections hold instruction words ending
   // with OP_END, BODY sections hold micro-ops ending with UH_END

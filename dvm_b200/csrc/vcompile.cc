@@ -1211,6 +1211,7 @@ bool LowerStageAs(VectorStage *st, bool dual) {
           recip_of[DVMB_OIDX(w)] < 0 && next < P.num_sregs)
         recip_of[DVMB_OIDX(w)] = static_cast<int>(next++);
   }
+  P.body_coords_mask = 0;
   bool full = true;   // lowering the variant for full chunks
   auto fetch = [&](uint32_t kind, uint32_t idx, uint32_t imm, uint32_t dest) {
     switch (kind) {
@@ -1361,7 +1362,9 @@ bool LowerStageAs(VectorStage *st, bool dual) {
         case OP_ST: {
           const TensorDesc &td = P.tensor[sub];
           static const uint32_t by_dtype[] = {UH_ST_U8, UH_ST_F16, UH_ST_BF16, UH_ST_F32, UH_ST_F32};
-          push(MakeUop(full && td.chunk_contig && td.vec_ok ? by_dtype[td.dtype] : UH_STG, 0, sub, 0));
+          const bool vec_store = full && td.chunk_contig && td.vec_ok;
+          if (vec_store && td.mode != AM_DENSE) P.body_coords_mask |= 1u << (sidx >> 1);
+          push(MakeUop(vec_store ? by_dtype[td.dtype] : UH_STG, 0, sub, 0));
           break;
         }
         default: break;

@@ -620,11 +620,12 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
       // ---------------- vector side: BODY_ph over the chunks ----------------
       const uint32_t body_pc = P.sec[2 * ph + 1], body_pc_any = P.sec_any[ph];
       const bool staged_body = ring && (resident || P.body_ring_mask[ph] != 0);
+      const bool body_coords = ((P.body_coords_mask >> ph) & 1u) != 0;   // only vector stores to strided tensors read cc
       const bool release_slots = !resident || ph + 1 == P.num_body;
       for (uint32_t ch = ch_begin; ch < ch_end; ch += ch_step) {
         pos.e_start = ch * P.chunk_elems;
         pos.chunk_valid = min(P.chunk_elems, P.group_elems - pos.e_start);
-        if (kCoords && P.need_coords) {
+        if (kCoords && body_coords) {
           if (ch == ch_begin) {
             split_enum(P, pos.e_start, cc);
           } else {
