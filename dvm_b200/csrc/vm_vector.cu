@@ -639,6 +639,14 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
               }
           }
         }
+        // every lane of this thread lies inside the chunk: the vector fast paths apply
+        const bool full_tile = pos.gvalid && pos.in_chunk0 + 3u * pos.gstep + 4u <= pos.chunk_valid;
+        // a thread without a single lane inside the chunk has nothing to fetch, add or store
+        const bool lane_active = pos.gvalid && 4u * lane_in_group < pos.chunk_valid;
+        // full chunks run the variant without per-lane tests; a thread with nothing to do starts at the final END
+        uint32_t pc_saddr = code_saddr + 8u * (full_tile ? body_pc : (lane_active ? body_pc_any : P.n_code - 1u));
+        uint32_t ulo, uhi, nlo, nhi;   // the current micro-op and the next one, already on its way
+        lds64x2(pc_saddr, ulo, uhi);   // (issued ahead of the wait for the chunk's data)
         uint32_t stage_saddr = 0, empty_bar = 0;
         if (staged_body) {
           if (resident) {
@@ -657,14 +665,6 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             }
           }
         }
-        // every lane of this thread lies inside the chunk: the vector fast paths apply
-        const bool full_tile = pos.gvalid && pos.in_chunk0 + 3u * pos.gstep + 4u <= pos.chunk_valid;
-        // a thread without a single lane inside the chunk has nothing to fetch, add or store
-        const bool lane_active = pos.gvalid && 4u * lane_in_group < pos.chunk_valid;
-        // full chunks run the variant without per-lane tests; a thread with nothing to do starts at the final END
-        uint32_t pc_saddr = code_saddr + 8u * (full_tile ? body_pc : (lane_active ? body_pc_any : P.n_code - 1u));
-        uint32_t ulo, uhi, nlo, nhi;   // the current micro-op and the next one, already on its way
-        lds64x2(pc_saddr, ulo, uhi);
         for (;; ulo = nlo, uhi = nhi) {
           const uint32_t uh = ulo & 0xffu;
           const uint32_t aux = (ulo >> 8) & 0xffu;
