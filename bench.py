@@ -557,6 +557,12 @@ def main():
     peak, peak_src = measured_peak(name)
     achieved = work / (mean * 1e-6) / unit_scale(name)
     tensor = name in ("c4", "c5")
+    # DRAM bytes per full-size launch from the ncu captures summarised under profiles/ (dram__bytes_read + write; the
+    # quarter-size captures of c1, c3, c4, c5 are scaled by 4: their traffic grows with the leading dimension)
+    traffic = {"c1": 4 * (135.8e6 + 40.0e6), "c2": 283.3e6 + 63.0e6, "c3": 4 * (135.1e6 + 42.0e6),
+               "c4": 4 * (101.0e6 + 13.0e6), "c5": 4 * (523.6e6 + 55.8e6)}.get(name)
+    if traffic is not None and args.scale != 1.0:
+        traffic *= args.scale
     line = {
         "metric": metric_of(name), "value": value, "unit": unit_of(name), "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
@@ -565,7 +571,8 @@ def main():
                    "l2": "inputs larger than L2 (no flush)", "sharding": "each rank runs a full-size shard (batch x N)",
                    "scale": args.scale},
         "roofline": {"bound": "tensor" if tensor else "hbm", "achieved": achieved, "peak": peak, "unit": unit_of(name),
-                     "frac": achieved / peak, "traffic": None, "peak_source": peak_src, "kernel": KERNEL_NAME[name],
+                     "frac": achieved / peak, "traffic": traffic, "traffic_source": "ncu capture (profiles/), bytes per launch",
+                     "peak_source": peak_src, "kernel": KERNEL_NAME[name],
                      "us_per_launch": {"min": lo, "mean": mean, "max": hi},
                      "frac_of_nominal": achieved / (2250.0 if tensor else 8000.0)},
         "gpu_launches": args.steps * wl.launches_per_step,
