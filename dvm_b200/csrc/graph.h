@@ -89,6 +89,7 @@ struct VectorStage {
   uint32_t grid = 0, threads = 0, smem_bytes = 0;
   uint32_t body_tensor_mask[dvmb::kMaxPhases] = {0, 0, 0, 0};   // tensor slots each BODY reads
   bool idle = false;                       // zero-size domain: nothing to launch
+  uint64_t lowered_for = ~0ull;            // per-tensor (vector access, ring slot) flags the micro-ops in `param` were lowered for
   uint32_t sregs_used = 0;                 // scalar registers the program names; the rest up to param.num_sregs hold
                                            // reciprocals of group scalars that the lowering turns fast divisions into
   std::vector<uint64_t> bytecode;          // instruction words of every section (what Das() prints)
@@ -167,6 +168,13 @@ std::string DisassembleStage(const VectorStage &st);
 // Turn the stage's instruction words into the launch program (scalar sections + micro-ops) for the tensor
 // addresses now in the descriptors; called whenever addresses are (re)bound.
 void LowerStage(VectorStage *st);
+// The per-tensor properties the lowering depends on, packed: a rebind that leaves them unchanged keeps the micro-ops.
+inline uint64_t LoweringKey(const VectorStage &st) {
+  uint64_t key = 0;
+  for (uint32_t s = 0; s < st.param.n_tensors; ++s)
+    key |= (static_cast<uint64_t>(st.param.tensor[s].vec_ok ? 1 : 0) | (st.param.tensor[s].ring_off != dvmb::kNoRing ? 2ull : 0ull)) << (2 * s);
+  return key;
+}
 
 // normalize.cc
 void InferShape(NDObject *n);

@@ -1015,7 +1015,9 @@ struct Compiler {
     }
     P.num_sregs = static_cast<uint32_t>(max_sreg);
     // the lowered program's length does not depend on the addresses bound later: lower once now to size its copy
+    for (uint32_t t = 0; t < P.n_tensors; ++t) P.tensor[t].vec_ok = P.tensor[t].layout_vec;   // as for aligned addresses
     LowerStage(out);
+    out->lowered_for = LoweringKey(*out);
     P.stages_off = VmStagesOffset(P.n_code);
     const uint32_t fixed = P.stages_off + P.num_temps * T * (4u * kLanes) + P.num_sregs * T * 4u;
     uint32_t stages = 0;

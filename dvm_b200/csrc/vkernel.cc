@@ -129,7 +129,10 @@ void VKernel::Bind(const RelocEntry *relocs, size_t n, void *workspace) {
       }
     }
     for (uint32_t q = 0; q < P.num_body; ++q) P.body_ring_mask[q] = st.body_tensor_mask[q] & staged;
-    LowerStage(&st);
+    if (LoweringKey(st) != st.lowered_for) {   // (an unaligned address took a tensor off its fast path)
+      LowerStage(&st);
+      st.lowered_for = LoweringKey(st);
+    }
   }
 }
 
