@@ -1,7 +1,7 @@
 """Builds the reference's own CUDA backend (mindspore-ai/dvm, `DVM_ARCH=gpu`) into oracle/_ref/ for cross-checking.
 
-TEST INFRASTRUCTURE ONLY.  The sources are compiled where they lie (the read-only reference tree, by default
-/root/reference); nothing is copied into this repository and every output goes to oracle/_ref/, which is git-ignored.
+TEST INFRASTRUCTURE ONLY.  The sources are compiled where they lie (the read-only reference tree: the directory given on the
+command line or in DVM_REFERENCE_DIR); nothing is copied into this repository and every output goes to oracle/_ref/, which is git-ignored.
 The recipe restates the GPU branch of the reference's Makefile (Makefile:7-14, 84-103): g++ on the host sources with
 -DDVM_ARCH_GPU, nvcc on src/vm_gpu.cu for sm_100a, one shared pybind11 module `_dvm_py`.  The reference's GPU backend
 executes vector kernels only (src/system.cc:290-294), so it cross-checks the elementwise / reduce graphs, not MatMul.
@@ -26,7 +26,10 @@ def module_path():
     return os.path.join(OUT, "_dvm_py" + suffix)
 
 
-def build(ref="/root/reference", force=False):
+DEFAULT_REFERENCE = os.environ.get("DVM_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))
+
+
+def build(ref=DEFAULT_REFERENCE, force=False):
     """Returns the path of the built module, or None when the reference tree or a toolchain piece is missing."""
     src = os.path.join(ref, "src")
     if not os.path.isdir(src):
@@ -69,4 +72,4 @@ def build(ref="/root/reference", force=False):
 
 
 if __name__ == "__main__":
-    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", force="--force" in sys.argv))
+    print(build(sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("-") else DEFAULT_REFERENCE, force="--force" in sys.argv))

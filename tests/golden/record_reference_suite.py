@@ -16,7 +16,8 @@ its shape, dtype and value range, the replay draws seeded inputs from that descr
 the same events, takes the place of the recorded expectation.  Tests that check through a Python callback or that use
 builder methods this backend does not offer are left out and counted in the json header.
 
-Usage (from the repository root, with the reference tree at /root/reference):  python -m tests.golden.record_reference_suite
+Usage (from the repository root; the reference tree is found as oracle/build_ref.py finds it):
+    python -m tests.golden.record_reference_suite
 """
 import json
 import os
@@ -248,7 +249,9 @@ class Plugin:
         self.cases.append({"name": TRACE.name, "array_base": base, "array_kinds": kinds, "events": TRACE.events})
 
 
-def main(ref="/root/reference"):
+def main(ref=None):
+    from oracle.build_ref import DEFAULT_REFERENCE
+    ref = ref or DEFAULT_REFERENCE
     import pytest
     sys.path[:0] = [ROOT, ref]
     shim = types.ModuleType("dvm")

@@ -1,5 +1,5 @@
 """The multi-GPU host logic on CPU: two gloo ranks cut a MatMul along K, all-reduce their fp32 partial products and
-finish with the bias + GeLU epilogue (the K-split path of the benchmark, SURVEY 8(e) / src/ops_c.cc:366-645 in the
+finish with the bias + GeLU epilogue (the K-split path of the benchmark, src/ops_c.cc:366-645 in the
 reference), and shard the other workloads along their leading dimension.  The oracle evaluates each rank's graph."""
 import os
 import socket
