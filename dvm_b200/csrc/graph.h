@@ -67,6 +67,7 @@ class NDObject {
   bool trans_a = false, trans_b = false;
   bool store_temp = false;
   int id = 0;
+  mutable int cidx = -1;   // position in the op list of the vector compiler that is looking at this node (scratch)
   NDObject *in[3] = {nullptr, nullptr, nullptr};
   // scalar operand: fixed code (already encoded in `dtype`, widened to the 32-bit register form) or a
   // borrowed ScalarRef re-read at code generation

@@ -49,7 +49,6 @@ enum LocKind { L_NONE, L_ACC, L_REG, L_IMM };
 struct Compiler {
   const std::vector<NDObject *> &ops;
   VectorStage *out;
-  std::unordered_map<const NDObject *, int> index;
   std::vector<Info> info;
   int R = 0;                       // domain rank
   int64_t dom[kMaxRank];
@@ -80,7 +79,11 @@ struct Compiler {
 
   Compiler(const std::vector<NDObject *> &o, VectorStage *st) : ops(o), out(st) {}
 
-  Info &I(const NDObject *n) { return info[index.at(n)]; }
+  int IndexOf(const NDObject *n) const {
+    if (n->cidx < 0 || static_cast<size_t>(n->cidx) >= ops.size() || ops[n->cidx] != n) throw Fail{"internal: node outside the stage"};
+    return n->cidx;
+  }
+  Info &I(const NDObject *n) { return info[IndexOf(n)]; }
 
   // ---- step 1: align every node's dims to domain axes -------------------------------------------
   void AlignAxes() {
@@ -289,7 +292,7 @@ struct Compiler {
       for (int k = 0; k < 3; ++k) {
         if (!n->in[k]) continue;
         const bool cond = n->kind == N_SELECT && k == 0;
-        if (sink || cond || exact[i]) exact[index.at(n->in[k])] = 1;
+        if (sink || cond || exact[i]) exact[IndexOf(n->in[k])] = 1;
       }
     }
   }
@@ -377,8 +380,16 @@ struct Compiler {
     int section;
     const NDObject *acc_val = nullptr;
     std::vector<const NDObject *> reg_val;
-    std::unordered_map<const NDObject *, int> uses;      // remaining uses inside this section
-    std::unordered_map<const NDObject *, int> vreg_of;   // vector side only
+    std::vector<int> uses_;      // by node position: remaining uses inside this section
+    std::vector<int> vreg_of_;   // by node position: register holding the value, or -1 (vector side only)
+    int &uses(const NDObject *v) {
+      if (uses_.empty()) uses_.assign(c->ops.size(), 0);
+      return uses_[c->IndexOf(v)];
+    }
+    int &vreg_of(const NDObject *v) {
+      if (vreg_of_.empty()) vreg_of_.assign(c->ops.size(), -1);
+      return vreg_of_[c->IndexOf(v)];
+    }
 
     void Push(uint32_t opc, uint32_t sub, Operand o, uint32_t dst, uint32_t rnd, uint32_t isint) {
       c->code.push_back(Insn::make(opc, sub, o.kind, o.idx, dst, rnd, isint, scalar ? 1 : 0, o.imm));
@@ -389,13 +400,11 @@ struct Compiler {
 
     int RegOf(const NDObject *v) {
       if (scalar) return c->I(v).sreg;
-      auto it = vreg_of.find(v);
-      return it == vreg_of.end() ? -1 : it->second;
+      return vreg_of(v);
     }
 
     bool NeededLater(const NDObject *v) {
-      auto it = uses.find(v);
-      if (it != uses.end() && it->second > 0) return true;
+      if (uses(v) > 0) return true;
       if (scalar && c->I(v).last_section > section) return true;
       return false;
     }
@@ -410,7 +419,7 @@ struct Compiler {
             c->I(v).sreg = i;
             c->max_sreg = std::max(c->max_sreg, i + 1);
           } else {
-            vreg_of[v] = i;
+            vreg_of(v) = i;
             c->max_temp = std::max(c->max_temp, i + 1);
           }
           return i;
@@ -427,7 +436,7 @@ struct Compiler {
         if (scalar) {
           c->I(v).sreg = -1;
         } else {
-          vreg_of.erase(v);
+          vreg_of(v) = -1;
         }
       }
     }
@@ -489,8 +498,7 @@ struct Compiler {
     }
 
     void Consume(const NDObject *v) {
-      auto it = uses.find(v);
-      if (it != uses.end() && it->second > 0) --it->second;
+      if (uses(v) > 0) --uses(v);
     }
 
     void Release(const NDObject *v) {
@@ -523,7 +531,7 @@ struct Compiler {
         static const uint32_t map[] = {U_SQRT, U_ABS, U_LOG, U_EXP, U_NOP, U_ISFINITE, U_NOP, U_ROUND, U_FLOOR, U_CEIL, U_TRUNC};
         uint32_t kind = map[n->sub];
         if (n->sub == kAbs && isint) kind = U_ABS_I;
-        if (kind == U_EXP && !exact[index.at(n)]) kind = U_EXP_FAST;
+        if (kind == U_EXP && !exact[IndexOf(n)]) kind = U_EXP_FAST;
         const bool noround = n->sub == kAbs || n->sub == kIsFinite || n->sub >= kRound;
         s.Push0(OP_UN, kind, 0, noround ? RN_NONE : rnd);
         s.acc_val = n;
@@ -565,7 +573,7 @@ struct Compiler {
           static const uint32_t imap[] = {B_ADD_I, B_MUL_I, B_COUNT, B_COUNT, B_MAX_I, B_MIN_I};
           uint32_t kind = isint ? imap[n->sub] : fmap[n->sub];
           if (kind == B_COUNT) throw Fail{"integer division is not supported"};
-          if (!exact[index.at(n)]) kind = kind == B_DIV ? B_DIV_FAST : (kind == B_RDIV ? B_RDIV_FAST : kind);
+          if (!exact[IndexOf(n)]) kind = kind == B_DIV ? B_DIV_FAST : (kind == B_RDIV ? B_RDIV_FAST : kind);
           const bool noround = n->sub == SB_MAX || n->sub == SB_MIN;
           s.Push(OP_BIN, kind, o, 0, noround ? RN_NONE : rnd, 0);
         }
@@ -587,7 +595,7 @@ struct Compiler {
             case kDiv:
               if (isint) throw Fail{"integer division is not supported"};
               kind = B_DIV; rkind = B_RDIV;
-              if (!exact[index.at(n)]) { kind = B_DIV_FAST; rkind = B_RDIV_FAST; }
+              if (!exact[IndexOf(n)]) { kind = B_DIV_FAST; rkind = B_RDIV_FAST; }
               break;
             case kPow:
               if (isint) throw Fail{"integer pow is not supported"};
@@ -697,7 +705,7 @@ struct Compiler {
       const NDObject *v = stack.back();
       stack.pop_back();
       if (I(v).scalar_space || v->kind == N_BROADCAST_S) continue;
-      int idx = index.at(v);
+      int idx = IndexOf(v);
       if (need[idx]) continue;
       need[idx] = 1;
       for (int k = 0; k < 3; ++k)
@@ -712,8 +720,8 @@ struct Compiler {
   void CountUses(Side &s, const std::vector<const NDObject *> &order, const std::vector<const NDObject *> &roots) {
     for (auto v : order)
       for (int k = 0; k < 3; ++k)
-        if (v->in[k]) s.uses[Canon(v->in[k])]++;
-    for (auto r : roots) s.uses[Canon(r->in[0])]++;
+        if (v->in[k]) s.uses(Canon(v->in[k]))++;
+    for (auto r : roots) s.uses(Canon(r->in[0]))++;
   }
 
   void Emit() {
@@ -785,7 +793,7 @@ struct Compiler {
         }
       for (auto n : pro_order[p])
         for (int k = 0; k < 3; ++k)
-          if (n->in[k] && n->kind != N_REDUCE) ss.uses[Canon(n->in[k])]++;
+          if (n->in[k] && n->kind != N_REDUCE) ss.uses(Canon(n->in[k]))++;
       for (auto n : pro_order[p]) {
         if (n->kind == N_STORE) {
           const NDObject *v = Canon(n->in[0]);
@@ -1155,7 +1163,7 @@ struct Compiler {
   }
 
   void Run(MatMulStage *mm = nullptr) {
-    for (size_t i = 0; i < ops.size(); ++i) index[ops[i]] = static_cast<int>(i);
+    for (size_t i = 0; i < ops.size(); ++i) ops[i]->cidx = static_cast<int>(i);
     info.assign(ops.size(), Info());
     for (auto n : ops)
       if (n->kind == N_MATMUL) throw Fail{"MatMul inside a vector stage"};
