@@ -24,7 +24,8 @@ constexpr uint32_t kVmSmemXBar = 1296;        // mbarrier of the cluster-wide co
 constexpr uint32_t kVmSmemTensors = 1536;     // copy of the tensor table (shared-memory reads are faster than indexed parameter reads)
 constexpr uint32_t kVmSmemCode = kVmSmemTensors + sizeof(dvmb::TensorDesc) * dvmb::kMaxTensors;   // copy of the program words
 // the ring stages follow the program at VmParam::stages_off (the program's capacity is fixed at compile time)
-constexpr uint32_t VmStagesOffset(uint32_t code_words) { return (kVmSmemCode + 8u * code_words + 127u) & ~127u; }
+// (one word more than the program: the dispatch loops fetch the word after the one they run, also behind the last END)
+constexpr uint32_t VmStagesOffset(uint32_t code_words) { return (kVmSmemCode + 8u * (code_words + 1u) + 127u) & ~127u; }
 
 // Enqueue the vector interpreter. Returns the cudaError_t of the launch (0 = ok).
 int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, uint32_t smem_bytes, void *stream);   // param.cluster > 1 launches clusters

@@ -508,7 +508,6 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
         lds64x2(spc, wlo, whi);
         for (;; wlo = xlo, whi = xhi) {
           const uint32_t sop = whi & 0xffu;   // a flat ScalarOp id, or the opcode of a word that takes the general path
-          if (sop == OP_END) break;
           spc += 8u;
           lds64x2(spc, xlo, xhi);
           const uint32_t sub = (whi >> 8) & 0xffu;
@@ -517,6 +516,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
           const uint32_t sv = lds32(okind == K_SREG ? sreg_addr(oidx) : code_saddr);
           const uint32_t sb = okind == K_SREG ? sv : (okind == K_ACC ? sacc[0] : wlo);
           switch (sop) {
+            case OP_END: goto scalar_done;   // (inside the switch: one indexed jump per word and no test in front of it)
             case SOP_COPY: sacc[0] = sb; break;
             case SOP_MOV: asm volatile("st.shared.u32 [%0], %1;" ::"r"(sreg_addr((whi >> 24) & 0xfu)), "r"(sacc[0]) : "memory"); break;
             case SOP_RINIT: set_part(sub & 3u, red_identity(sub >> 4)); break;
@@ -616,6 +616,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
           }
         }
       }
+    scalar_done:
       if (ph == P.num_body) break;
       // ---------------- vector side: BODY_ph over the chunks ----------------
       const uint32_t body_pc = P.sec[2 * ph + 1], body_pc_any = P.sec_any[ph];
@@ -669,10 +670,10 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
           const uint32_t uh = ulo & 0xffu;
           const uint32_t aux = (ulo >> 8) & 0xffu;
           const uint32_t arg = ulo >> 16;
-          if (uh == UH_END) break;   // (kept out of the switch: a compare is cheaper than the indexed jump)
           pc_saddr += 8u;
           lds64x2(pc_saddr, nlo, nhi);
           switch (uh) {
+            case UH_END: goto body_done;
             // ---------------- operand fetches ----------------
 #define DV_LDR_CASE(H, REG, MACRO, SHL)                                                                        \
   case H: {                                                                                                 \
@@ -903,6 +904,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             default: __builtin_unreachable();
           }
         }
+      body_done:
         if (staged_body && release_slots) {
           __syncwarp();
           if ((tid & 31u) == 0) mbar_arrive(empty_bar);
