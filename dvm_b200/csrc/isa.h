@@ -144,9 +144,12 @@ enum UopHandler : uint32_t {
   // acc <- op(acc, b)
   UH_BINV_FIRST,
   UH_BINV_LAST = UH_BINV_FIRST + B_COUNT - 1,
-  // acc <- op(acc, scalar); aux bit0: scalar register arg16, else imm32
+  // acc <- op(acc, imm32)
   UH_BINS_FIRST,
   UH_BINS_LAST = UH_BINS_FIRST + B_COUNT - 1,
+  // acc <- op(acc, scalar register arg16)
+  UH_BINR_FIRST,
+  UH_BINR_LAST = UH_BINR_FIRST + B_COUNT - 1,
   UH_UN_FIRST,
   UH_UN_LAST = UH_UN_FIRST + U_NOP,
   UH_RND_F16, UH_RND_BF16,

@@ -1337,9 +1337,9 @@ bool LowerStageAs(VectorStage *st, bool dual) {
           if (splat && sub == B_RDIV_FAST && okind == K_IMM && DVMB_IMM(w) == 0x3f800000u) {
             push(MakeUop(UH_RCP, 0, 0, 0));
           } else if (splat && sub == B_DIV_FAST && okind == K_SREG && recip_of[oidx] >= 0) {
-            push(MakeUop(UH_BINS_FIRST + B_MUL, 1, static_cast<uint32_t>(recip_of[oidx]), 0));
+            push(MakeUop(UH_BINR_FIRST + B_MUL, 0, static_cast<uint32_t>(recip_of[oidx]), 0));
           } else if (splat) {
-            push(MakeUop(UH_BINS_FIRST + sub, okind == K_SREG ? 1 : 0, oidx, DVMB_IMM(w)));
+            push(MakeUop((okind == K_SREG ? UH_BINR_FIRST : UH_BINS_FIRST) + sub, 0, oidx, DVMB_IMM(w)));
           } else if (okind == K_ACC && sub == B_MUL) {
             push(MakeUop(UH_SQR, 0, 0, 0));
           } else {

@@ -741,24 +741,27 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             // float max / min keep the reference's `a > b ? a : b` / `a < b ? a : b`
             case UH_BINV_FIRST + B_MAX: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_PICKV_LANE, "setp.gt.f32") "}"); break;
             case UH_BINV_FIRST + B_MIN: asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_PICKV_LANE, "setp.lt.f32") "}"); break;
-            case UH_BINS_FIRST + B_MAX: {
-              const uint32_t sv = (aux & 1u) ? lds32(sreg_addr(arg)) : uhi;
+            case UH_BINS_FIRST + B_MAX:
+            case UH_BINR_FIRST + B_MAX: {
+              const uint32_t sv = uh == UH_BINR_FIRST + B_MAX ? lds32(sreg_addr(arg)) : uhi;
               asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_PICKS_LANE, "setp.gt.f32") "}" ::"r"(sv));
               break;
             }
-            case UH_BINS_FIRST + B_MIN: {
-              const uint32_t sv = (aux & 1u) ? lds32(sreg_addr(arg)) : uhi;
+            case UH_BINS_FIRST + B_MIN:
+            case UH_BINR_FIRST + B_MIN: {
+              const uint32_t sv = uh == UH_BINR_FIRST + B_MIN ? lds32(sreg_addr(arg)) : uhi;
               asm volatile("{\n\t.reg .pred p;\n\t" DV_LN(DV_PICKS_LANE, "setp.lt.f32") "}" ::"r"(sv));
               break;
             }
             case UH_BINV_FIRST + B_POW:
+            case UH_BINR_FIRST + B_POW:
             case UH_BINS_FIRST + B_POW: {
               uint32_t x[kLanes], y[kLanes];
               DV_GET("va", x)
               if (uh == UH_BINV_FIRST + B_POW) {
                 DV_GET("vb", y)
               } else {
-                const uint32_t sv = (aux & 1u) ? lds32(sreg_addr(arg)) : uhi;
+                const uint32_t sv = uh == UH_BINR_FIRST + B_POW ? lds32(sreg_addr(arg)) : uhi;
 #pragma unroll
                 for (int i = 0; i < kLanes; ++i) y[i] = sv;
               }

@@ -112,8 +112,9 @@
   }
 #define DV_BIN_CASES(K, VLANE, SLANE, OP)                                      \
   case UH_BINV_FIRST + K: asm volatile(DV_LN(VLANE, OP)); break;               \
-  case UH_BINS_FIRST + K: {                                                    \
-    const uint32_t sv_ = (aux & 1u) ? lds32(sreg_addr(arg)) : uhi;            \
+  case UH_BINS_FIRST + K: asm volatile(DV_LN(SLANE, OP)::"r"(uhi)); break;     \
+  case UH_BINR_FIRST + K: {                                                    \
+    const uint32_t sv_ = lds32(sreg_addr(arg));                                \
     asm volatile(DV_LN(SLANE, OP)::"r"(sv_));                                  \
     break;                                                                     \
   }
