@@ -456,7 +456,7 @@ def measured_peak(name):
     return fallback, "fallback (earlier measurement on this pool)"
 
 
-KERNEL_NAME = {"c1": "dvm_b200_vm_vector", "c2": "dvm_b200_vm_vector", "c3": "dvm_b200_vm_vector",
+KERNEL_NAME = {"c1": "dvm_b200_vm_vector", "c2": "dvm_b200_vm_vector_nd", "c3": "dvm_b200_vm_vector",
                "c4": "dvm_b200_attention_bf16_sf", "c5": "dvm_b200_mm_tcgen05_pair"}
 
 
