@@ -900,7 +900,8 @@ struct Compiler {
     bool packed = false;           // several small groups share a CTA
     if (!has_reduce) {
       P.mode = VM_FLAT;
-      P.tg = kVmFlatThreads;
+      // enough chunks for four CTAs per SM: the 128-thread geometry (measured 139 -> 135 us on 2 x 256 MiB of fp32)
+      P.tg = G >= 4ll * sms * (kLanes * kVmFlatThreads / 2) ? kVmFlatThreads / 2 : kVmFlatThreads;
       if (const char *env = getenv("DVM_B200_FLAT_THREADS")) P.tg = static_cast<uint32_t>(atoi(env));
       P.groups_per_cta = 1;
       P.chunk_elems = kLanes * P.tg;
@@ -1051,15 +1052,15 @@ struct Compiler {
     uint32_t stages = 0;
     if (stage_bytes != 0) {
       uint32_t budget = 106 * 1024;   // two CTAs of this size fit one SM
-      if (P.mode == VM_GROUP && !packed && T <= 128) budget = 52 * 1024;   // four
+      if (!packed && T <= 128) budget = 52 * 1024;   // four
       if (const char *env = getenv("DVM_B200_RING_KB")) budget = static_cast<uint32_t>(atoi(env)) * 1024u;
       // enough stages to keep about 48 KB per CTA in flight (small tiles need a deep ring to cover the memory
       // latency), at least three; beyond that deeper read-ahead measured slower on large tiles
       const uint32_t want = std::max<uint32_t>(3u, (48u * 1024u + stage_bytes - 1) / stage_bytes + 1);
       stages = fixed + 2 * stage_bytes > budget ? 2 : std::min<uint32_t>(std::min<uint32_t>(want, kVmMaxStages), (budget - fixed) / stage_bytes);
-      // the 128-thread CTAs of many-group reduce graphs run fastest on two stages (a third, when it fits, measured
+      // the 128-thread CTAs (many-group reduce graphs, long reduce-free ones) run fastest on two stages (a third, when it fits, measured
       // 397 us against 339 us on 16384 rows of 4096)
-      if (P.mode == VM_GROUP && !packed && T <= 128) stages = std::min<uint32_t>(stages, 2u);
+      if (!packed && T <= 128) stages = std::min<uint32_t>(stages, 2u);
       if (const char *env = getenv("DVM_B200_STAGES")) stages = static_cast<uint32_t>(atoi(env));
       if (fixed + stages * stage_bytes > kVmMaxSmemBytes) {
         // too large to stage even twice: fall back to direct global loads
@@ -1107,7 +1108,7 @@ struct Compiler {
     out->threads = T + (stage_bytes != 0 ? 32u : 0u);
 
     // ---- grid: persistent CTAs, as many as fit per SM
-    uint32_t per_sm_cap = P.mode == VM_GROUP && !packed && T <= 128 ? 4u : 2u;
+    uint32_t per_sm_cap = !packed && T <= 128 ? 4u : 2u;
     if (const char *env = getenv("DVM_B200_CTAS_PER_SM")) per_sm_cap = static_cast<uint32_t>(atoi(env));
     uint32_t per_sm = std::max<uint32_t>(1u, std::min<uint32_t>(per_sm_cap, (226u * 1024u) / std::max<uint32_t>(out->smem_bytes + 1024u, 1u)));
     if (T > static_cast<uint32_t>(kVmFlatThreads)) per_sm = 1;
