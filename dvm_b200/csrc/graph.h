@@ -93,6 +93,8 @@ struct VectorStage {
   uint64_t lowered_for = ~0ull;            // per-tensor (vector access, ring slot) flags the micro-ops in `param` were lowered for
   uint32_t sregs_used = 0;                 // scalar registers the program names; the rest up to param.num_sregs hold
                                            // reciprocals of group scalars that the lowering turns fast divisions into
+  uint32_t fused_away = 0;                 // micro-ops the last lowering's peephole pass merged into fused handlers (a
+                                           // rebind that drops a ring slot can lengthen the program by up to this much)
   std::vector<uint64_t> bytecode;          // instruction words of every section (what Das() prints)
   uint16_t bsec[2 * dvmb::kMaxPhases + 2] = {0};   // section offsets inside `bytecode`
   std::vector<NDObject *> slot_obj;        // tensor slot -> load/store node (relocation sites)

@@ -163,11 +163,27 @@ enum UopHandler : uint32_t {
   UH_RACCF_LAST = UH_RACCF_FIRST + 11,
   UH_ST_F32, UH_ST_F16, UH_ST_BF16, UH_ST_U8,       // dense, aligned tensor arg16: vector stores
   UH_STG,                                           // any tensor arg16
+  // ---- fused forms (full chunks only): the host's peephole pass replaces frequent neighbours by one handler, so that
+  // the pair costs one dispatch; each computes exactly what its parts compute, in the same order and rounding
+  UH_LDOP_FIRST,                                    // b <- ring operand; acc <- acc (add | sub | mul) b:
+  UH_LDOP_LAST = UH_LDOP_FIRST + 8,                 //   handler = first + FusedOp * 3 + FusedType, arg16 = ring offset / 16
+  UH_LDSUM_FIRST,                                   // acc <- ring operand; partial 0 += lanes of acc: first + FusedType
+  UH_LDSUM_LAST = UH_LDSUM_FIRST + 2,
+  UH_LDSUBR_FIRST,                                  // acc <- ring operand - scalar register imm32: first + FusedType
+  UH_LDSUBR_LAST = UH_LDSUBR_FIRST + 2,
+  UH_SQRSUM0, UH_SQRSUM1,                           // acc <- acc * acc; partial 0 / 1 += lanes of acc
+  UH_SUBR_MULR, UH_MULR_ADDR, UH_MULR_MULR,         // two scalar-register operands: arg16 = first | second << 8
+  UH_SIGMOID_FAST,                                  // acc <- 1 / (1 + exp(-acc)) in the fast forms (mul -1, EXP_FAST, add 1, RCP)
   UH_COUNT
 };
+enum FusedOp : uint32_t { FO_ADD = 0, FO_SUB = 1, FO_MUL = 2 };
+enum FusedType : uint32_t { FT_F32 = 0, FT_F16 = 1, FT_BF16 = 2 };   // the order of UH_LDR_F32 .. UH_LDR_BF16
+static_assert(UH_COUNT <= 256, "handler ids are one byte");
 enum UopDest : uint32_t { UD_B = 0, UD_ACC = 1 };
 enum UopAux : uint32_t {
-  UA_CMP_SREG = 0x08   // scalar compares: the scalar is register arg16, else imm32
+  UA_CMP_SREG = 0x08,  // scalar compares: the scalar is register arg16, else imm32
+  UA_LAST = 0x80       // vector stores and full-chunk reduce accumulations (plain or fused): the body ends here (no UH_END
+                       // word follows, which saves its dispatch)
 };
 
 constexpr uint64_t MakeUop(uint32_t handler, uint32_t aux, uint32_t arg16, uint32_t imm) {

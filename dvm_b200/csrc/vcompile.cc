@@ -1047,7 +1047,8 @@ struct Compiler {
     for (uint32_t t = 0; t < P.n_tensors; ++t) P.tensor[t].vec_ok = P.tensor[t].layout_vec;   // as for aligned addresses
     LowerStage(out);
     out->lowered_for = LoweringKey(*out);
-    P.stages_off = VmStagesOffset(P.n_code);
+    // (sized for the program without fused handlers: a rebind that takes a tensor off the ring undoes its fusions)
+    P.stages_off = VmStagesOffset(P.n_code + out->fused_away);
     const uint32_t fixed = P.stages_off + P.num_temps * T * (4u * kLanes) + P.num_sregs * T * 4u;
     uint32_t stages = 0;
     if (stage_bytes != 0) {
@@ -1272,6 +1273,59 @@ bool LowerStageAs(VectorStage *st, bool dual) {
     if (rnd == RN_F16) push(MakeUop(UH_RND_F16, 0, 0, 0));
     if (rnd == RN_BF16) push(MakeUop(UH_RND_BF16, 0, 0, 0));
   };
+  // Peephole over the micro-ops [begin, n) of a full-chunk body: frequent neighbours become one fused handler (one
+  // dispatch instead of two to four).  A fused handler performs its parts' operations in their order, each rounded
+  // on its own, so the result is the unfused program's bit for bit.
+  uint32_t fused_away = 0;
+  auto fuse = [&](uint32_t begin) {
+    static const bool off = getenv("DVM_B200_NO_FUSE") != nullptr;
+    if (off || overflow) return;
+    uint32_t o = begin;
+    auto fused_op = [](uint32_t h) -> int {
+      if (h == UH_BINV_FIRST + B_ADD) return FO_ADD;
+      if (h == UH_BINV_FIRST + B_SUB) return FO_SUB;
+      if (h == UH_BINV_FIRST + B_MUL) return FO_MUL;
+      return -1;
+    };
+    for (uint32_t i = begin; i < n;) {
+      const uint64_t a = P.code[i];
+      const uint32_t ha = DVMB_UH(a), left = n - i;
+      const uint64_t b = left >= 2 ? P.code[i + 1] : 0;
+      const uint32_t hb = left >= 2 ? DVMB_UH(b) : static_cast<uint32_t>(UH_COUNT);
+      uint64_t f = 0;
+      uint32_t take = 1;
+      if (ha >= UH_LDR_F32 && ha <= UH_LDR_BF16 && fused_op(hb) >= 0) {
+        f = MakeUop(UH_LDOP_FIRST + static_cast<uint32_t>(fused_op(hb)) * 3u + (ha - UH_LDR_F32), 0, DVMB_UARG(a), 0);
+        take = 2;
+      } else if (ha >= UH_LDRA_F32 && ha <= UH_LDRA_BF16 && hb == UH_RACCF_FIRST + R_SUM * 4u) {
+        f = MakeUop(UH_LDSUM_FIRST + (ha - UH_LDRA_F32), 0, DVMB_UARG(a), 0);
+        take = 2;
+      } else if (ha >= UH_LDRA_F32 && ha <= UH_LDRA_BF16 && hb == UH_BINR_FIRST + B_SUB) {
+        f = MakeUop(UH_LDSUBR_FIRST + (ha - UH_LDRA_F32), 0, DVMB_UARG(a), DVMB_UARG(b));
+        take = 2;
+      } else if (ha == UH_SQR && (hb == UH_RACCF_FIRST + R_SUM * 4u || hb == UH_RACCF_FIRST + R_SUM * 4u + 1u)) {
+        f = MakeUop(hb == UH_RACCF_FIRST + R_SUM * 4u ? UH_SQRSUM0 : UH_SQRSUM1, 0, 0, 0);
+        take = 2;
+      } else if (left >= 4 && ha == UH_BINS_FIRST + B_MUL && DVMB_UIMM(a) == 0xbf800000u && hb == UH_UN_FIRST + U_EXP_FAST &&
+                 DVMB_UH(P.code[i + 2]) == UH_BINS_FIRST + B_ADD && DVMB_UIMM(P.code[i + 2]) == 0x3f800000u &&
+                 DVMB_UH(P.code[i + 3]) == UH_RCP) {
+        f = MakeUop(UH_SIGMOID_FAST, 0, 0, 0);
+        take = 4;
+      } else if (ha >= UH_BINR_FIRST && ha <= UH_BINR_LAST && hb >= UH_BINR_FIRST && hb <= UH_BINR_LAST) {
+        const uint32_t ka = ha - UH_BINR_FIRST, kb = hb - UH_BINR_FIRST;
+        const uint32_t h = ka == B_SUB && kb == B_MUL ? UH_SUBR_MULR : ka == B_MUL && kb == B_ADD ? UH_MULR_ADDR
+                           : ka == B_MUL && kb == B_MUL ? UH_MULR_MULR : 0u;
+        if (h != 0) {
+          f = MakeUop(h, 0, (DVMB_UARG(a) & 0xffu) | ((DVMB_UARG(b) & 0xffu) << 8), 0);
+          take = 2;
+        }
+      }
+      P.code[o++] = take > 1 ? f : a;
+      i += take;
+      fused_away += take - 1;
+    }
+    n = o;
+  };
   // every BODY is lowered twice (full chunks, any chunk); PRO sections once
   for (uint32_t pass = 0; pass <= 3 * P.num_body; ++pass) {
     const bool second = pass > 2 * P.num_body;
@@ -1323,6 +1377,19 @@ bool LowerStageAs(VectorStage *st, bool dual) {
         continue;
       }
       if (opc == OP_END) {
+        if (full) {
+          fuse(P.sec[sidx]);
+          // a body that ends in a vector store or a reduce accumulation ends inside that handler
+          static const bool no_tail = getenv("DVM_B200_NO_TAIL") != nullptr;
+          const uint32_t last = n > P.sec[sidx] ? DVMB_UH(P.code[n - 1]) : static_cast<uint32_t>(UH_END);
+          const bool ends_body = (last >= UH_ST_F32 && last <= UH_ST_BF16) || (last >= UH_RACCF_FIRST && last <= UH_RACCF_LAST) ||
+                                 (last >= UH_LDSUM_FIRST && last <= UH_LDSUM_LAST) || last == UH_SQRSUM0 || last == UH_SQRSUM1;
+          if (ends_body && !no_tail && !overflow) {
+            P.code[n - 1] |= static_cast<uint64_t>(UA_LAST) << 8;
+            ++fused_away;
+            break;
+          }
+        }
         push(MakeUop(UH_END, 0, 0, 0));
         break;
       }
@@ -1406,6 +1473,7 @@ bool LowerStageAs(VectorStage *st, bool dual) {
     }
   }
   P.n_code = n;
+  st->fused_away = fused_away;
   return !overflow;
 }
 }  // namespace
@@ -1515,6 +1583,60 @@ std::string DisassembleStage(const VectorStage &st) {
         o += buf;
       }
     o += InsnLine(pc, st.bytecode[pc], dt, ptr);
+  }
+  // the micro-ops the launch carries for full chunks (what the instruction words above were lowered to)
+  auto uop_name = [](uint32_t h) -> std::string {
+    static const char *ty[] = {"fp32", "fp16", "bf16", "u8"};
+    static const char *fo[] = {"Add", "Sub", "Mul"};
+    if (h == UH_END) return "end";
+    if (h >= UH_LDR_F32 && h <= UH_LDR_U8) return std::string("ldb.") + ty[h - UH_LDR_F32];
+    if (h >= UH_LDRA_F32 && h <= UH_LDRA_U8) return std::string("lda.") + ty[h - UH_LDRA_F32];
+    if (h >= UH_BINV_FIRST && h <= UH_BINV_LAST) return std::string(kBinNames[h - UH_BINV_FIRST]) + ".b";
+    if (h >= UH_BINS_FIRST && h <= UH_BINS_LAST) return std::string(kBinNames[h - UH_BINS_FIRST]) + ".imm";
+    if (h >= UH_BINR_FIRST && h <= UH_BINR_LAST) return std::string(kBinNames[h - UH_BINR_FIRST]) + ".s";
+    if (h >= UH_UN_FIRST && h <= UH_UN_LAST) return kUnNames[h - UH_UN_FIRST];
+    if (h >= UH_RACCF_FIRST && h <= UH_RACCF_LAST)
+      return std::string("Reduce") + kRedNames[(h - UH_RACCF_FIRST) / 4] + ".p" + std::to_string((h - UH_RACCF_FIRST) % 4);
+    if (h >= UH_RACC_SUM && h <= UH_RACC_MIN) return std::string("Reduce") + kRedNames[h - UH_RACC_SUM] + ".any";
+    if (h >= UH_ST_F32 && h <= UH_ST_U8) return std::string("st.") + ty[h - UH_ST_F32];
+    if (h >= UH_LDOP_FIRST && h <= UH_LDOP_LAST)
+      return std::string("ldb.") + ty[(h - UH_LDOP_FIRST) % 3] + "+" + fo[(h - UH_LDOP_FIRST) / 3] + ".b";
+    if (h >= UH_LDSUM_FIRST && h <= UH_LDSUM_LAST) return std::string("lda.") + ty[h - UH_LDSUM_FIRST] + "+ReduceSum.p0";
+    if (h >= UH_LDSUBR_FIRST && h <= UH_LDSUBR_LAST) return std::string("lda.") + ty[h - UH_LDSUBR_FIRST] + "+Sub.s";
+    switch (h) {
+      case UH_LDG: return "ldg";
+      case UH_LDT: return "ldt";
+      case UH_LDS: return "lds";
+      case UH_LDI: return "ldi";
+      case UH_MOVA: return "mova";
+      case UH_SQR: return "Sqr";
+      case UH_RCP: return "Rcp";
+      case UH_STT: return "stt";
+      case UH_RND_F16: return "rnd.fp16";
+      case UH_RND_BF16: return "rnd.bf16";
+      case UH_SELM: return "selm";
+      case UH_STG: return "stg";
+      case UH_SQRSUM0: return "Sqr+ReduceSum.p0";
+      case UH_SQRSUM1: return "Sqr+ReduceSum.p1";
+      case UH_SUBR_MULR: return "Sub.s+Mul.s";
+      case UH_MULR_ADDR: return "Mul.s+Add.s";
+      case UH_MULR_MULR: return "Mul.s+Mul.s";
+      case UH_SIGMOID_FAST: return "SigmoidFast";
+      default: return "u" + std::to_string(h);
+    }
+  };
+  for (uint32_t q = 0; q < P.num_body; ++q) {
+    o += "  // body_" + std::to_string(q) + " micro-ops:";
+    for (uint32_t pc = P.sec[2 * q + 1]; pc < P.n_code; ++pc) {
+      const uint32_t h = DVMB_UH(P.code[pc]);
+      if (h == UH_END) break;
+      o += " " + uop_name(h);
+      if (DVMB_UAUX(P.code[pc]) & UA_LAST) {
+        o += " (ends the body)";
+        break;
+      }
+    }
+    o += "\n";
   }
   o += "}\n";
   return o;

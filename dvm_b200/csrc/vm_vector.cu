@@ -693,6 +693,49 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             DV_LDR_CASE(UH_LDRA_BF16, "va", DV_LDR_BF16, DV_SHL1)
             DV_LDR_CASE(UH_LDRA_U8, "va", DV_LDR_U8, DV_SHL0)
 #undef DV_LDR_CASE
+            // ---------------- fused forms: ring operand + the operation that follows it ----------------
+#define DV_LDX_CASE(H, REG, MACRO, SHL, ...)                                                                   \
+  case H: {                                                                                                 \
+    const uint32_t a0 = stage_saddr + (arg << 4) + (SHL(pos.in_chunk0)), gs = SHL(pos.gstep);               \
+    MACRO(REG, a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)                                                      \
+    __VA_ARGS__                                                                                             \
+    continue;                                                                                               \
+  }
+#define DV_LDX_TYPES(FIRST, REG, ...)                                              \
+  DV_LDX_CASE(FIRST + FT_F32, REG, DV_LDR32, DV_SHL2, __VA_ARGS__)                 \
+  DV_LDX_CASE(FIRST + FT_F16, REG, DV_LDR_F16, DV_SHL1, __VA_ARGS__)               \
+  DV_LDX_CASE(FIRST + FT_BF16, REG, DV_LDR_BF16, DV_SHL1, __VA_ARGS__)
+            DV_LDX_TYPES(UH_LDOP_FIRST + FO_ADD * 3, "vb", asm volatile(DV_LN(DV_BINVRN_LANE, "add.rn.f32"));)
+            DV_LDX_TYPES(UH_LDOP_FIRST + FO_SUB * 3, "vb", asm volatile(DV_LN(DV_BINVRN_LANE, "sub.rn.f32"));)
+            DV_LDX_TYPES(UH_LDOP_FIRST + FO_MUL * 3, "vb", asm volatile(DV_LN(DV_BINVRN_LANE, "mul.rn.f32"));)
+            DV_LDX_TYPES(UH_LDSUM_FIRST, "va", asm volatile(DV_SUMRN_TREE("0")); if (aux & UA_LAST) goto body_done;)
+            DV_LDX_TYPES(UH_LDSUBR_FIRST, "va", {
+              const uint32_t sv_ = lds32(sreg_addr(uhi));
+              asm volatile(DV_LN(DV_BINS_LANE, "sub.rn.f32")::"r"(sv_));
+            })
+#undef DV_LDX_TYPES
+#undef DV_LDX_CASE
+            case UH_SQRSUM0:
+              asm volatile(DV_LN(DV_SQRRN_LANE, ""));
+              asm volatile(DV_SUMRN_TREE("0"));
+              if (aux & UA_LAST) goto body_done;
+              continue;
+            case UH_SQRSUM1:
+              asm volatile(DV_LN(DV_SQRRN_LANE, ""));
+              asm volatile(DV_SUMRN_TREE("1"));
+              if (aux & UA_LAST) goto body_done;
+              continue;
+#define DV_RR_CASE(H, OP1, OP2)                                                       \
+  case H: {                                                                        \
+    const uint32_t s1_ = lds32(sreg_addr(arg & 0xffu)), s2_ = lds32(sreg_addr(arg >> 8)); \
+    asm volatile(DV_LN(DV_BINS2_LANE, OP1, OP2)::"r"(s1_), "r"(s2_));              \
+    continue;                                                                      \
+  }
+            DV_RR_CASE(UH_SUBR_MULR, "sub.rn.f32", "mul.rn.f32")
+            DV_RR_CASE(UH_MULR_ADDR, "mul.rn.f32", "add.rn.f32")
+            DV_RR_CASE(UH_MULR_MULR, "mul.rn.f32", "mul.rn.f32")
+#undef DV_RR_CASE
+            case UH_SIGMOID_FAST: asm volatile(DV_LN(DV_SIGM_LANE, "")); continue;
             case UH_LDG: {
               uint32_t t[kLanes];
               fetch_tensor(P, aux >> 2, pos, stage_saddr, t);
@@ -858,7 +901,11 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
               continue;
             }
             // full chunks: the 16 lanes are combined as a tree, one handler per partial register
-#define DV_RACCF(KIND, SLOT, TREE) case UH_RACCF_FIRST + KIND * 4 + SLOT: asm volatile(TREE(#SLOT)); continue;
+#define DV_RACCF(KIND, SLOT, TREE)         \
+  case UH_RACCF_FIRST + KIND * 4 + SLOT:   \
+    asm volatile(TREE(#SLOT));             \
+    if (aux & UA_LAST) goto body_done;     \
+    continue;
 #define DV_RACCF4(KIND, TREE) DV_RACCF(KIND, 0, TREE) DV_RACCF(KIND, 1, TREE) DV_RACCF(KIND, 2, TREE) DV_RACCF(KIND, 3, TREE)
             DV_RACCF4(R_SUM, DV_SUM_TREE)
             DV_RACCF4(R_MAX, DV_MAX_TREE)
@@ -874,6 +921,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
                            "st.global.v4.b32 [%2], {va8,va9,va10,va11};\n\tst.global.v4.b32 [%3], {va12,va13,va14,va15};" ::"l"(p0),
                            "l"(p0 + gs), "l"(p0 + 2u * gs), "l"(p0 + 3u * gs)
                            : "memory");
+              if (aux & UA_LAST) goto body_done;
               continue;
             }
             case UH_ST_F16:
@@ -895,6 +943,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
                 DV_ST16("cvt.rn.f16x2.f32")
               }
 #undef DV_ST16
+              if (aux & UA_LAST) goto body_done;
               continue;
             }
             case UH_ST_U8:

@@ -42,6 +42,13 @@
 #define DV_GETLANE(i, R) "mov.b32 %" #i ", " R #i ";\n\t"
 #define DV_SETLANE(i, R) "mov.b32 " R #i ", %" #i ";\n\t"
 #define DV_SPLATLANE(i, R) "mov.b32 " R #i ", %0;\n\t"
+// fused handlers: two operations on a lane, each rounded on its own (.rn keeps ptxas from contracting them into an fma)
+#define DV_BINS2_LANE(i, OP1, OP2) OP1 " va" #i ", va" #i ", %0;\n\t" OP2 " va" #i ", va" #i ", %1;\n\t"
+#define DV_BINVRN_LANE(i, OP) OP " va" #i ", va" #i ", vb" #i ";\n\t"
+#define DV_SQRRN_LANE(i, X) "mul.rn.f32 va" #i ", va" #i ", va" #i ";\n\t"
+#define DV_SIGM_LANE(i, X)                                                                                  \
+  "mul.rn.f32 va" #i ", va" #i ", 0fBF800000;\n\tmul.rn.f32 va" #i ", va" #i ", 0f3FB8AA3B;\n\t"            \
+  "ex2.approx.ftz.f32 va" #i ", va" #i ";\n\tadd.rn.f32 va" #i ", va" #i ", 0f3F800000;\n\trcp.approx.f32 va" #i ", va" #i ";\n\t"
 // tree reductions of the 16 accumulator lanes into partial register vp<SLOT>
 #define DV_TREE16(OP2, SLOT)                                                                                       \
   "{\n\t.reg .b32 r<8>;\n\t.reg .pred p;\n\t"                                                                      \
@@ -52,7 +59,9 @@
 #define DV_ADD2(D, A, B) "add.f32 " D ", " A ", " B ";\n\t"
 #define DV_MAX2(D, A, B) "setp.gt.f32 p, " A ", " B ";\n\tselp.b32 " D ", " A ", " B ", p;\n\t"
 #define DV_MIN2(D, A, B) "setp.lt.f32 p, " A ", " B ";\n\tselp.b32 " D ", " A ", " B ", p;\n\t"
+#define DV_ADDRN2(D, A, B) "add.rn.f32 " D ", " A ", " B ";\n\t"
 #define DV_SUM_TREE(SLOT) DV_TREE16(DV_ADD2, SLOT)
+#define DV_SUMRN_TREE(SLOT) DV_TREE16(DV_ADDRN2, SLOT)
 #define DV_MAX_TREE(SLOT) DV_TREE16(DV_MAX2, SLOT)
 #define DV_MIN_TREE(SLOT) DV_TREE16(DV_MIN2, SLOT)
 
