@@ -174,6 +174,9 @@ enum UopHandler : uint32_t {
   UH_SQRSUM0, UH_SQRSUM1,                           // acc <- acc * acc; partial 0 / 1 += lanes of acc
   UH_SUBR_MULR, UH_MULR_ADDR, UH_MULR_MULR,         // two scalar-register operands: arg16 = first | second << 8
   UH_SIGMOID_FAST,                                  // acc <- 1 / (1 + exp(-acc)) in the fast forms (mul -1, EXP_FAST, add 1, RCP)
+  UH_LD2OP_FIRST,                                   // acc <- ring operand arg16; b <- ring operand imm32 (same type); acc <- acc
+  UH_LD2OP_LAST = UH_LD2OP_FIRST + 8,               //   (add | sub | mul) b: first + FusedOp * 3 + FusedType
+  UH_MULR_MULR_ADDR,                                // three scalar registers: arg16 = first | second << 4 | third << 8
   UH_COUNT
 };
 enum FusedOp : uint32_t { FO_ADD = 0, FO_SUB = 1, FO_MUL = 2 };

@@ -1294,7 +1294,21 @@ bool LowerStageAs(VectorStage *st, bool dual) {
       const uint32_t hb = left >= 2 ? DVMB_UH(b) : static_cast<uint32_t>(UH_COUNT);
       uint64_t f = 0;
       uint32_t take = 1;
-      if (ha >= UH_LDR_F32 && ha <= UH_LDR_BF16 && fused_op(hb) >= 0) {
+      const uint32_t hc = left >= 3 ? DVMB_UH(P.code[i + 2]) : static_cast<uint32_t>(UH_COUNT);
+      if (((ha == UH_RND_F16 && hb == UH_ST_F16) || (ha == UH_RND_BF16 && hb == UH_ST_BF16)) &&
+          (left == 2 || (hc >= UH_LDRA_F32 && hc <= UH_LDRA_U8))) {
+        // the vector store rounds the same way, and nothing reads the accumulator before it is loaded again
+        ++i;
+        ++fused_away;
+        continue;
+      }
+      if (ha >= UH_LDRA_F32 && ha <= UH_LDRA_BF16 && hb == ha - UH_LDRA_F32 + UH_LDR_F32 && fused_op(hc) >= 0) {
+        f = MakeUop(UH_LD2OP_FIRST + static_cast<uint32_t>(fused_op(hc)) * 3u + (ha - UH_LDRA_F32), 0, DVMB_UARG(a), DVMB_UARG(b));
+        take = 3;
+      } else if (ha == UH_BINR_FIRST + B_MUL && hb == UH_BINR_FIRST + B_MUL && hc == UH_BINR_FIRST + B_ADD) {
+        f = MakeUop(UH_MULR_MULR_ADDR, 0, (DVMB_UARG(a) & 0xfu) | ((DVMB_UARG(b) & 0xfu) << 4) | ((DVMB_UARG(P.code[i + 2]) & 0xfu) << 8), 0);
+        take = 3;
+      } else if (ha >= UH_LDR_F32 && ha <= UH_LDR_BF16 && fused_op(hb) >= 0) {
         f = MakeUop(UH_LDOP_FIRST + static_cast<uint32_t>(fused_op(hb)) * 3u + (ha - UH_LDR_F32), 0, DVMB_UARG(a), 0);
         take = 2;
       } else if (ha >= UH_LDRA_F32 && ha <= UH_LDRA_BF16 && hb == UH_RACCF_FIRST + R_SUM * 4u) {
@@ -1601,6 +1615,8 @@ std::string DisassembleStage(const VectorStage &st) {
     if (h >= UH_ST_F32 && h <= UH_ST_U8) return std::string("st.") + ty[h - UH_ST_F32];
     if (h >= UH_LDOP_FIRST && h <= UH_LDOP_LAST)
       return std::string("ldb.") + ty[(h - UH_LDOP_FIRST) % 3] + "+" + fo[(h - UH_LDOP_FIRST) / 3] + ".b";
+    if (h >= UH_LD2OP_FIRST && h <= UH_LD2OP_LAST)
+      return std::string("lda.") + ty[(h - UH_LD2OP_FIRST) % 3] + "+ldb+" + fo[(h - UH_LD2OP_FIRST) / 3] + ".b";
     if (h >= UH_LDSUM_FIRST && h <= UH_LDSUM_LAST) return std::string("lda.") + ty[h - UH_LDSUM_FIRST] + "+ReduceSum.p0";
     if (h >= UH_LDSUBR_FIRST && h <= UH_LDSUBR_LAST) return std::string("lda.") + ty[h - UH_LDSUBR_FIRST] + "+Sub.s";
     switch (h) {
@@ -1621,6 +1637,7 @@ std::string DisassembleStage(const VectorStage &st) {
       case UH_SUBR_MULR: return "Sub.s+Mul.s";
       case UH_MULR_ADDR: return "Mul.s+Add.s";
       case UH_MULR_MULR: return "Mul.s+Mul.s";
+      case UH_MULR_MULR_ADDR: return "Mul.s+Mul.s+Add.s";
       case UH_SIGMOID_FAST: return "SigmoidFast";
       default: return "u" + std::to_string(h);
     }

@@ -713,6 +713,30 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
               const uint32_t sv_ = lds32(sreg_addr(uhi));
               asm volatile(DV_LN(DV_BINS_LANE, "sub.rn.f32")::"r"(sv_));
             })
+            // two ring operands of one type and their sum / difference / product
+#define DV_LD2_CASE(H, MACRO, SHL, OPASM)                                                                      \
+  case H: {                                                                                                 \
+    const uint32_t o0 = stage_saddr + (SHL(pos.in_chunk0)), gs = SHL(pos.gstep);                            \
+    const uint32_t a0 = o0 + (arg << 4), b0 = o0 + (uhi << 4);                                              \
+    MACRO("va", a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)                                                     \
+    MACRO("vb", b0, b0 + gs, b0 + 2u * gs, b0 + 3u * gs)                                                     \
+    asm volatile(DV_LN(DV_BINVRN_LANE, OPASM));                                                             \
+    continue;                                                                                               \
+  }
+#define DV_LD2_TYPES(FO, OPASM)                                                   \
+  DV_LD2_CASE(UH_LD2OP_FIRST + FO * 3 + FT_F32, DV_LDR32, DV_SHL2, OPASM)         \
+  DV_LD2_CASE(UH_LD2OP_FIRST + FO * 3 + FT_F16, DV_LDR_F16, DV_SHL1, OPASM)       \
+  DV_LD2_CASE(UH_LD2OP_FIRST + FO * 3 + FT_BF16, DV_LDR_BF16, DV_SHL1, OPASM)
+            DV_LD2_TYPES(FO_ADD, "add.rn.f32")
+            DV_LD2_TYPES(FO_SUB, "sub.rn.f32")
+            DV_LD2_TYPES(FO_MUL, "mul.rn.f32")
+#undef DV_LD2_TYPES
+#undef DV_LD2_CASE
+            case UH_MULR_MULR_ADDR: {
+              const uint32_t s1_ = lds32(sreg_addr(arg & 0xfu)), s2_ = lds32(sreg_addr((arg >> 4) & 0xfu)), s3_ = lds32(sreg_addr(arg >> 8));
+              asm volatile(DV_LN(DV_BINS3_LANE, "mul.rn.f32", "mul.rn.f32", "add.rn.f32")::"r"(s1_), "r"(s2_), "r"(s3_));
+              continue;
+            }
 #undef DV_LDX_TYPES
 #undef DV_LDX_CASE
             case UH_SQRSUM0:

@@ -44,6 +44,8 @@
 #define DV_SPLATLANE(i, R) "mov.b32 " R #i ", %0;\n\t"
 // fused handlers: two operations on a lane, each rounded on its own (.rn keeps ptxas from contracting them into an fma)
 #define DV_BINS2_LANE(i, OP1, OP2) OP1 " va" #i ", va" #i ", %0;\n\t" OP2 " va" #i ", va" #i ", %1;\n\t"
+#define DV_BINS3_LANE(i, OP1, OP2, OP3) \
+  OP1 " va" #i ", va" #i ", %0;\n\t" OP2 " va" #i ", va" #i ", %1;\n\t" OP3 " va" #i ", va" #i ", %2;\n\t"
 #define DV_BINVRN_LANE(i, OP) OP " va" #i ", va" #i ", vb" #i ";\n\t"
 #define DV_SQRRN_LANE(i, X) "mul.rn.f32 va" #i ", va" #i ", va" #i ";\n\t"
 #define DV_SIGM_LANE(i, X)                                                                                  \

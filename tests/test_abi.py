@@ -93,3 +93,53 @@ def test_dynamic_shape_recompile_is_stateless():
         fresh, _ = build(shape)
         fresh.codegen()
         assert k.das() == fresh.das()
+
+
+def _micro_ops(das):
+    """The per-body micro-op listings of a disassembly, as lists of names."""
+    return [line.split("micro-ops:")[1].split() for line in das.splitlines() if "micro-ops:" in line]
+
+
+def test_peephole_fuses_frequent_neighbours():
+    # the launch program of a full chunk: neighbours the peephole pass knows become one micro-op, and a body that ends
+    # in a vector store or a reduce accumulation carries no END word
+    from dvm_b200 import workloads as W
+    k = dvm.PyKernel("vector", "das", 0)
+    x = k.load([64, 256, 56, 56], dvm.float16)
+    g = k.load([1, 256, 1, 1], dvm.float32)
+    b = k.load([1, 256, 1, 1], dvm.float32)
+    for o in W.batchnorm_train(k, x, g, b, 64 * 56 * 56):
+        k.store(o)
+    k.codegen()
+    bodies = _micro_ops(k.das())
+    assert len(bodies) == 3
+    assert bodies[0][0] == "lda.fp16+ReduceSum.p0"
+    assert bodies[1][:2] == ["lda.fp16+Sub.s", "Sqr+ReduceSum.p1"]
+    assert bodies[2][:3] == ["lda.fp16+Sub.s", "Mul.s+Mul.s+Add.s", "st.fp16"]
+    assert all(body[-3:] == ["(ends", "the", "body)"] for body in bodies)
+
+    k = dvm.PyKernel("vector", "das", 0)
+    T = 256
+    h, r, gg, u = (k.load([T, 4096], dvm.bfloat16) for _ in range(4))
+    w = k.load([4096], dvm.bfloat16)
+    for o in W.rmsnorm_swiglu(k, h, r, w, gg, u, 4096):
+        k.store(o)
+    k.codegen()
+    bodies = _micro_ops(k.das())
+    assert bodies[0][:2] == ["lda.bf16+ldb+Add.b", "Sqr+ReduceSum.p0"] and "SigmoidFast" in bodies[0]
+    assert bodies[1][0] == "lda.bf16+ldb+Add.b"
+
+
+def test_peephole_can_be_switched_off(monkeypatch):
+    # the unfused program is what the fused one must equal bit for bit; the switch keeps it reachable for comparison
+    import subprocess, sys
+    code = ("import dvm_b200 as dvm\n"
+            "k = dvm.PyKernel('vector', 'das', 0)\n"
+            "a = k.load([64, 4096], dvm.float32); b = k.load([64, 4096], dvm.float32)\n"
+            "k.store(k.add(a, b)); k.codegen(); print(k.das())\n")
+    env = dict(os.environ, DVM_B200_NO_FUSE="1", DVM_B200_NO_TAIL="1", PYTHONPATH=ROOT)
+    plain = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, check=True).stdout
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    fused = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, check=True).stdout
+    assert _micro_ops(plain)[0] == ["lda.fp32", "ldb.fp32", "Add.b", "st.fp32"]
+    assert _micro_ops(fused)[0][:2] == ["lda.fp32+ldb+Add.b", "st.fp32"]
