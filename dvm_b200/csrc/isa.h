@@ -177,6 +177,12 @@ enum UopHandler : uint32_t {
   UH_LD2OP_FIRST,                                   // acc <- ring operand arg16; b <- ring operand imm32 (same type); acc <- acc
   UH_LD2OP_LAST = UH_LD2OP_FIRST + 8,               //   (add | sub | mul) b: first + FusedOp * 3 + FusedType
   UH_MULR_MULR_ADDR,                                // three scalar registers: arg16 = first | second << 4 | third << 8
+  // the two passes of a normalisation over a ring operand x (arg16 = ring offset / 16, scalar registers in imm32, four
+  // bits each): the sum of (x - s0)^2 into partial 0 / 1, and ((x - s0) * s1) * s2 + s3
+  UH_LDVAR_FIRST,                                   // first + slot * 3 + FusedType
+  UH_LDVAR_LAST = UH_LDVAR_FIRST + 5,
+  UH_LDNORM_FIRST,                                  // first + FusedType
+  UH_LDNORM_LAST = UH_LDNORM_FIRST + 2,
   UH_COUNT
 };
 enum FusedOp : uint32_t { FO_ADD = 0, FO_SUB = 1, FO_MUL = 2 };

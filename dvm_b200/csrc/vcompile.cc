@@ -1302,7 +1302,18 @@ bool LowerStageAs(VectorStage *st, bool dual) {
         ++fused_away;
         continue;
       }
-      if (ha >= UH_LDRA_F32 && ha <= UH_LDRA_BF16 && hb == ha - UH_LDRA_F32 + UH_LDR_F32 && fused_op(hc) >= 0) {
+      const uint32_t hd = left >= 4 ? DVMB_UH(P.code[i + 3]) : static_cast<uint32_t>(UH_COUNT);
+      const uint32_t he = left >= 5 ? DVMB_UH(P.code[i + 4]) : static_cast<uint32_t>(UH_COUNT);
+      const bool centred = ha >= UH_LDRA_F32 && ha <= UH_LDRA_BF16 && hb == UH_BINR_FIRST + B_SUB;
+      if (centred && hc == UH_SQR && (hd == UH_RACCF_FIRST + R_SUM * 4u || hd == UH_RACCF_FIRST + R_SUM * 4u + 1u)) {
+        f = MakeUop(UH_LDVAR_FIRST + (hd - (UH_RACCF_FIRST + R_SUM * 4u)) * 3u + (ha - UH_LDRA_F32), 0, DVMB_UARG(a), DVMB_UARG(b) & 0xfu);
+        take = 4;
+      } else if (centred && hc == UH_BINR_FIRST + B_MUL && hd == UH_BINR_FIRST + B_MUL && he == UH_BINR_FIRST + B_ADD) {
+        f = MakeUop(UH_LDNORM_FIRST + (ha - UH_LDRA_F32), 0, DVMB_UARG(a),
+                    (DVMB_UARG(b) & 0xfu) | ((DVMB_UARG(P.code[i + 2]) & 0xfu) << 4) | ((DVMB_UARG(P.code[i + 3]) & 0xfu) << 8) |
+                      ((DVMB_UARG(P.code[i + 4]) & 0xfu) << 12));
+        take = 5;
+      } else if (ha >= UH_LDRA_F32 && ha <= UH_LDRA_BF16 && hb == ha - UH_LDRA_F32 + UH_LDR_F32 && fused_op(hc) >= 0) {
         f = MakeUop(UH_LD2OP_FIRST + static_cast<uint32_t>(fused_op(hc)) * 3u + (ha - UH_LDRA_F32), 0, DVMB_UARG(a), DVMB_UARG(b));
         take = 3;
       } else if (ha == UH_BINR_FIRST + B_MUL && hb == UH_BINR_FIRST + B_MUL && hc == UH_BINR_FIRST + B_ADD) {
@@ -1397,7 +1408,8 @@ bool LowerStageAs(VectorStage *st, bool dual) {
           static const bool no_tail = getenv("DVM_B200_NO_TAIL") != nullptr;
           const uint32_t last = n > P.sec[sidx] ? DVMB_UH(P.code[n - 1]) : static_cast<uint32_t>(UH_END);
           const bool ends_body = (last >= UH_ST_F32 && last <= UH_ST_BF16) || (last >= UH_RACCF_FIRST && last <= UH_RACCF_LAST) ||
-                                 (last >= UH_LDSUM_FIRST && last <= UH_LDSUM_LAST) || last == UH_SQRSUM0 || last == UH_SQRSUM1;
+                                 (last >= UH_LDSUM_FIRST && last <= UH_LDSUM_LAST) || last == UH_SQRSUM0 || last == UH_SQRSUM1 ||
+                                 (last >= UH_LDVAR_FIRST && last <= UH_LDVAR_LAST);
           if (ends_body && !no_tail && !overflow) {
             P.code[n - 1] |= static_cast<uint64_t>(UA_LAST) << 8;
             ++fused_away;
@@ -1617,6 +1629,9 @@ std::string DisassembleStage(const VectorStage &st) {
       return std::string("ldb.") + ty[(h - UH_LDOP_FIRST) % 3] + "+" + fo[(h - UH_LDOP_FIRST) / 3] + ".b";
     if (h >= UH_LD2OP_FIRST && h <= UH_LD2OP_LAST)
       return std::string("lda.") + ty[(h - UH_LD2OP_FIRST) % 3] + "+ldb+" + fo[(h - UH_LD2OP_FIRST) / 3] + ".b";
+    if (h >= UH_LDVAR_FIRST && h <= UH_LDVAR_LAST)
+      return std::string("lda.") + ty[(h - UH_LDVAR_FIRST) % 3] + "+Sub.s+Sqr+ReduceSum.p" + std::to_string((h - UH_LDVAR_FIRST) / 3);
+    if (h >= UH_LDNORM_FIRST && h <= UH_LDNORM_LAST) return std::string("lda.") + ty[h - UH_LDNORM_FIRST] + "+Sub.s+Mul.s+Mul.s+Add.s";
     if (h >= UH_LDSUM_FIRST && h <= UH_LDSUM_LAST) return std::string("lda.") + ty[h - UH_LDSUM_FIRST] + "+ReduceSum.p0";
     if (h >= UH_LDSUBR_FIRST && h <= UH_LDSUBR_LAST) return std::string("lda.") + ty[h - UH_LDSUBR_FIRST] + "+Sub.s";
     switch (h) {

@@ -737,6 +737,23 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
               asm volatile(DV_LN(DV_BINS3_LANE, "mul.rn.f32", "mul.rn.f32", "add.rn.f32")::"r"(s1_), "r"(s2_), "r"(s3_));
               continue;
             }
+            DV_LDX_TYPES(UH_LDVAR_FIRST, "va", {
+              const uint32_t sv_ = lds32(sreg_addr(uhi));
+              asm volatile(DV_LN(DV_CSQR_LANE, "")::"r"(sv_));
+              asm volatile(DV_SUMRN_TREE("0"));
+              if (aux & UA_LAST) goto body_done;
+            })
+            DV_LDX_TYPES(UH_LDVAR_FIRST + 3, "va", {
+              const uint32_t sv_ = lds32(sreg_addr(uhi));
+              asm volatile(DV_LN(DV_CSQR_LANE, "")::"r"(sv_));
+              asm volatile(DV_SUMRN_TREE("1"));
+              if (aux & UA_LAST) goto body_done;
+            })
+            DV_LDX_TYPES(UH_LDNORM_FIRST, "va", {
+              const uint32_t s0_ = lds32(sreg_addr(uhi & 0xfu)), s1_ = lds32(sreg_addr((uhi >> 4) & 0xfu));
+              const uint32_t s2_ = lds32(sreg_addr((uhi >> 8) & 0xfu)), s3_ = lds32(sreg_addr((uhi >> 12) & 0xfu));
+              asm volatile(DV_LN(DV_NORM_LANE, "")::"r"(s0_), "r"(s1_), "r"(s2_), "r"(s3_));
+            })
 #undef DV_LDX_TYPES
 #undef DV_LDX_CASE
             case UH_SQRSUM0:

@@ -46,6 +46,10 @@
 #define DV_BINS2_LANE(i, OP1, OP2) OP1 " va" #i ", va" #i ", %0;\n\t" OP2 " va" #i ", va" #i ", %1;\n\t"
 #define DV_BINS3_LANE(i, OP1, OP2, OP3) \
   OP1 " va" #i ", va" #i ", %0;\n\t" OP2 " va" #i ", va" #i ", %1;\n\t" OP3 " va" #i ", va" #i ", %2;\n\t"
+#define DV_NORM_LANE(i, X)                                                                                  \
+  "sub.rn.f32 va" #i ", va" #i ", %0;\n\tmul.rn.f32 va" #i ", va" #i ", %1;\n\tmul.rn.f32 va" #i ", va" #i ", %2;\n\t" \
+  "add.rn.f32 va" #i ", va" #i ", %3;\n\t"
+#define DV_CSQR_LANE(i, X) "sub.rn.f32 va" #i ", va" #i ", %0;\n\tmul.rn.f32 va" #i ", va" #i ", va" #i ";\n\t"
 #define DV_BINVRN_LANE(i, OP) OP " va" #i ", va" #i ", vb" #i ";\n\t"
 #define DV_SQRRN_LANE(i, X) "mul.rn.f32 va" #i ", va" #i ", va" #i ";\n\t"
 #define DV_SIGM_LANE(i, X)                                                                                  \
