@@ -17,6 +17,7 @@
 #include <math_constants.h>
 
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
 
 #include "isa.h"
@@ -1027,6 +1028,10 @@ DVMB_VM_KERNEL(dvm_b200_vm_vector_wide, kVmMaxThreads + 32, 1, false, false)
 // strided layouts: chunk starts follow from the chunk's coordinates along the iterated axes
 DVMB_VM_KERNEL(dvm_b200_vm_vector_nd, kVmFlatThreads + 32, 2, false, true)
 DVMB_VM_KERNEL(dvm_b200_vm_vector_nd_wide, kVmMaxThreads + 32, 1, false, true)
+// CTAs of at most 256 threads that run two per SM (groups of up to 224 consumer threads plus the producer warp): the
+// bound lets ptxas use up to 128 registers, which keeps the dispatch loop free of spills
+DVMB_VM_KERNEL(dvm_b200_vm_vector_r128, 256, 2, false, false)
+DVMB_VM_KERNEL(dvm_b200_vm_vector_nd_r128, 256, 2, false, true)
 // resident groups (and clusters): every chunk of a group keeps a shared-memory slot for all phases
 DVMB_VM_KERNEL(dvm_b200_vm_vector_res, kVmFlatThreads + 32, 2, true, true)
 DVMB_VM_KERNEL(dvm_b200_vm_vector_res_wide, kVmMaxThreads + 32, 1, true, true)
@@ -1039,7 +1044,7 @@ int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, uint32_t
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
     cudaError_t e = cudaSuccess;
     for (auto fn : {dvm_b200_vm_vector, dvm_b200_vm_vector_wide, dvm_b200_vm_vector_nd, dvm_b200_vm_vector_nd_wide,
-                    dvm_b200_vm_vector_res, dvm_b200_vm_vector_res_wide})
+                    dvm_b200_vm_vector_res, dvm_b200_vm_vector_res_wide, dvm_b200_vm_vector_r128, dvm_b200_vm_vector_nd_r128})
       if (e == cudaSuccess) e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kVmMaxSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set[dev] = true;
@@ -1066,6 +1071,10 @@ int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, uint32_t
   } else if (param.need_coords) {
     kernel = narrow ? dvm_b200_vm_vector_nd : dvm_b200_vm_vector_nd_wide;
   }
+  // (the 160-thread CTAs run four per SM and need the 96-register build for that)
+  static const bool no_r128 = getenv("DVM_B200_NO_R128") != nullptr;
+  if (!param.resident && threads > 160 && threads <= 256 && !no_r128)
+    kernel = param.need_coords ? dvm_b200_vm_vector_nd_r128 : dvm_b200_vm_vector_r128;
   const cudaError_t le = cudaLaunchKernelEx(&cfg, kernel, param);
   if (le != cudaSuccess) return static_cast<int>(le);
   return static_cast<int>(cudaGetLastError());
