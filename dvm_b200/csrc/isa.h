@@ -183,6 +183,10 @@ enum UopHandler : uint32_t {
   UH_LDVAR_LAST = UH_LDVAR_FIRST + 5,
   UH_LDNORM_FIRST,                                  // first + FusedType
   UH_LDNORM_LAST = UH_LDNORM_FIRST + 2,
+  UH_LDSIGM_FIRST,                                  // acc <- fast sigmoid of ring operand arg16: first + FusedType
+  UH_LDSIGM_LAST = UH_LDSIGM_FIRST + 2,
+  UH_LDMUL2_FIRST,                                  // acc <- (acc * ring operand arg16) * ring operand imm32 (one type; b keeps
+  UH_LDMUL2_LAST = UH_LDMUL2_FIRST + 2,             //   the second): first + FusedType
   UH_COUNT
 };
 enum FusedOp : uint32_t { FO_ADD = 0, FO_SUB = 1, FO_MUL = 2 };

@@ -1313,6 +1313,13 @@ bool LowerStageAs(VectorStage *st, bool dual) {
                     (DVMB_UARG(b) & 0xfu) | ((DVMB_UARG(P.code[i + 2]) & 0xfu) << 4) | ((DVMB_UARG(P.code[i + 3]) & 0xfu) << 8) |
                       ((DVMB_UARG(P.code[i + 4]) & 0xfu) << 12));
         take = 5;
+      } else if (ha >= UH_LDRA_F32 && ha <= UH_LDRA_BF16 && hb == UH_BINS_FIRST + B_MUL && DVMB_UIMM(b) == 0xbf800000u &&
+                 hc == UH_UN_FIRST + U_EXP_FAST && hd == UH_BINS_FIRST + B_ADD && DVMB_UIMM(P.code[i + 3]) == 0x3f800000u && he == UH_RCP) {
+        f = MakeUop(UH_LDSIGM_FIRST + (ha - UH_LDRA_F32), 0, DVMB_UARG(a), 0);
+        take = 5;
+      } else if (ha >= UH_LDR_F32 && ha <= UH_LDR_BF16 && hb == UH_BINV_FIRST + B_MUL && hc == ha && hd == UH_BINV_FIRST + B_MUL) {
+        f = MakeUop(UH_LDMUL2_FIRST + (ha - UH_LDR_F32), 0, DVMB_UARG(a), DVMB_UARG(P.code[i + 2]));
+        take = 4;
       } else if (ha >= UH_LDRA_F32 && ha <= UH_LDRA_BF16 && hb == ha - UH_LDRA_F32 + UH_LDR_F32 && fused_op(hc) >= 0) {
         f = MakeUop(UH_LD2OP_FIRST + static_cast<uint32_t>(fused_op(hc)) * 3u + (ha - UH_LDRA_F32), 0, DVMB_UARG(a), DVMB_UARG(b));
         take = 3;
@@ -1632,6 +1639,8 @@ std::string DisassembleStage(const VectorStage &st) {
     if (h >= UH_LDVAR_FIRST && h <= UH_LDVAR_LAST)
       return std::string("lda.") + ty[(h - UH_LDVAR_FIRST) % 3] + "+Sub.s+Sqr+ReduceSum.p" + std::to_string((h - UH_LDVAR_FIRST) / 3);
     if (h >= UH_LDNORM_FIRST && h <= UH_LDNORM_LAST) return std::string("lda.") + ty[h - UH_LDNORM_FIRST] + "+Sub.s+Mul.s+Mul.s+Add.s";
+    if (h >= UH_LDSIGM_FIRST && h <= UH_LDSIGM_LAST) return std::string("lda.") + ty[h - UH_LDSIGM_FIRST] + "+SigmoidFast";
+    if (h >= UH_LDMUL2_FIRST && h <= UH_LDMUL2_LAST) return std::string("ldb.") + ty[h - UH_LDMUL2_FIRST] + "+Mul.b+ldb+Mul.b";
     if (h >= UH_LDSUM_FIRST && h <= UH_LDSUM_LAST) return std::string("lda.") + ty[h - UH_LDSUM_FIRST] + "+ReduceSum.p0";
     if (h >= UH_LDSUBR_FIRST && h <= UH_LDSUBR_LAST) return std::string("lda.") + ty[h - UH_LDSUBR_FIRST] + "+Sub.s";
     switch (h) {

@@ -755,6 +755,21 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
               const uint32_t s2_ = lds32(sreg_addr((uhi >> 8) & 0xfu)), s3_ = lds32(sreg_addr((uhi >> 12) & 0xfu));
               asm volatile(DV_LN(DV_NORM_LANE, "")::"r"(s0_), "r"(s1_), "r"(s2_), "r"(s3_));
             })
+            DV_LDX_TYPES(UH_LDSIGM_FIRST, "va", asm volatile(DV_LN(DV_SIGM_LANE, ""));)
+#define DV_LDMUL2_CASE(H, MACRO, SHL)                                                                          \
+  case H: {                                                                                                 \
+    const uint32_t o0 = stage_saddr + (SHL(pos.in_chunk0)), gs = SHL(pos.gstep);                            \
+    const uint32_t a0 = o0 + (arg << 4), b0 = o0 + (uhi << 4);                                              \
+    MACRO("vb", a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)                                                     \
+    asm volatile(DV_LN(DV_BINVRN_LANE, "mul.rn.f32"));                                                      \
+    MACRO("vb", b0, b0 + gs, b0 + 2u * gs, b0 + 3u * gs)                                                     \
+    asm volatile(DV_LN(DV_BINVRN_LANE, "mul.rn.f32"));                                                      \
+    continue;                                                                                               \
+  }
+            DV_LDMUL2_CASE(UH_LDMUL2_FIRST + FT_F32, DV_LDR32, DV_SHL2)
+            DV_LDMUL2_CASE(UH_LDMUL2_FIRST + FT_F16, DV_LDR_F16, DV_SHL1)
+            DV_LDMUL2_CASE(UH_LDMUL2_FIRST + FT_BF16, DV_LDR_BF16, DV_SHL1)
+#undef DV_LDMUL2_CASE
 #undef DV_LDX_TYPES
 #undef DV_LDX_CASE
             case UH_SQRSUM0:

@@ -126,7 +126,7 @@ def test_peephole_fuses_frequent_neighbours():
         k.store(o)
     k.codegen()
     bodies = _micro_ops(k.das())
-    assert bodies[0][:2] == ["lda.bf16+ldb+Add.b", "Sqr+ReduceSum.p0"] and "SigmoidFast" in bodies[0]
+    assert bodies[0][:4] == ["lda.bf16+ldb+Add.b", "Sqr+ReduceSum.p0", "lda.bf16+SigmoidFast", "ldb.bf16+Mul.b+ldb+Mul.b"]
     assert bodies[1][0] == "lda.bf16+ldb+Add.b"
 
 
