@@ -66,7 +66,9 @@ enum ScalarOp : uint32_t {
   SOP_UN_FIRST,                      // + UnKind
   SOP_BIN_FIRST = SOP_UN_FIRST + 12, // + BinKind
   SOP_CVT_FIRST = SOP_BIN_FIRST + 17,   // + CvtKind (V_F2I .. V_NEZ_I)
-  SOP_COUNT = SOP_CVT_FIRST + 4
+  SOP_MOV_END = SOP_CVT_FIRST + 4,   // SOP_MOV / SOP_RINIT as the last word of a section: the section ends inside the
+  SOP_RINIT_END,                     // handler (no END word follows, which saves its dispatch)
+  SOP_COUNT
 };
 
 enum UnKind : uint32_t { U_SQRT = 0, U_ABS, U_LOG, U_EXP, U_ROUND, U_FLOOR, U_CEIL, U_TRUNC, U_ISFINITE, U_ABS_I,

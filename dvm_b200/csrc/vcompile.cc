@@ -1404,6 +1404,16 @@ bool LowerStageAs(VectorStage *st, bool dual) {
             push(Insn::make(SOP_MOV, 0, 0, 0, static_cast<uint32_t>(recip_of[d]), 0, 0, 1, 0));
           }
         }
+        if (opc == OP_END && n > P.sec[sidx] && !overflow) {
+          // a section whose last word stores a scalar register or resets a partial ends inside that word's handler
+          static const bool no_tail = getenv("DVM_B200_NO_TAIL") != nullptr;
+          const uint32_t last = DVMB_OPC(P.code[n - 1]);
+          if (!no_tail && (last == SOP_MOV || last == SOP_RINIT)) {
+            P.code[n - 1] = (P.code[n - 1] & ~(0xffull << 32)) | (static_cast<uint64_t>(last == SOP_MOV ? SOP_MOV_END : SOP_RINIT_END) << 32);
+            ++fused_away;
+            break;
+          }
+        }
         push((w & ~(0xffull << 32)) | (static_cast<uint64_t>(flat) << 32));
         if (opc == OP_END) break;
         continue;

@@ -521,6 +521,10 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             case SOP_COPY: sacc[0] = sb; break;
             case SOP_MOV: asm volatile("st.shared.u32 [%0], %1;" ::"r"(sreg_addr((whi >> 24) & 0xfu)), "r"(sacc[0]) : "memory"); break;
             case SOP_RINIT: set_part(sub & 3u, red_identity(sub >> 4)); break;
+            case SOP_MOV_END:
+              asm volatile("st.shared.u32 [%0], %1;" ::"r"(sreg_addr((whi >> 24) & 0xfu)), "r"(sacc[0]) : "memory");
+              goto scalar_done;
+            case SOP_RINIT_END: set_part(sub & 3u, red_identity(sub >> 4)); goto scalar_done;
             case SOP_RFIN: {
               const uint32_t kind = sub >> 4;
               float v = get_part(sub & 3u);
