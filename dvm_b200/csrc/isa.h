@@ -68,6 +68,8 @@ enum ScalarOp : uint32_t {
   SOP_CVT_FIRST = SOP_BIN_FIRST + 17,   // + CvtKind (V_F2I .. V_NEZ_I)
   SOP_MOV_END = SOP_CVT_FIRST + 4,   // SOP_MOV / SOP_RINIT as the last word of a section: the section ends inside the
   SOP_RINIT_END,                     // handler (no END word follows, which saves its dispatch)
+  SOP_RSTD_FAST,                     // sacc <- 1 / sqrt(sacc * imm + imm'), fast division: the four words Mul #imm, Add #imm',
+                                     // Sqrt, RDivFast #1.0 as one; imm' is read from the following word, which is skipped
   SOP_COUNT
 };
 

@@ -1404,6 +1404,23 @@ bool LowerStageAs(VectorStage *st, bool dual) {
             push(Insn::make(SOP_MOV, 0, 0, 0, static_cast<uint32_t>(recip_of[d]), 0, 0, 1, 0));
           }
         }
+        if (opc == OP_END && !overflow) {
+          // the reciprocal standard deviation chain of a normalisation becomes one word (plus the word that keeps its
+          // second immediate); the arithmetic and its order stay the same
+          static const bool no_fuse = getenv("DVM_B200_NO_FUSE") != nullptr;
+          for (uint32_t q = P.sec[sidx]; !no_fuse && q + 4 <= n; ++q) {
+            const uint64_t w0 = P.code[q], w1 = P.code[q + 1], w2 = P.code[q + 2], w3 = P.code[q + 3];
+            if (DVMB_OPC(w0) == SOP_BIN_FIRST + B_MUL && DVMB_OKIND(w0) == K_IMM && DVMB_OPC(w1) == SOP_BIN_FIRST + B_ADD &&
+                DVMB_OKIND(w1) == K_IMM && DVMB_OPC(w2) == SOP_UN_FIRST + U_SQRT && DVMB_OPC(w3) == SOP_BIN_FIRST + B_RDIV_FAST &&
+                DVMB_OKIND(w3) == K_IMM && DVMB_IMM(w3) == 0x3f800000u) {
+              P.code[q] = (w0 & ~(0xffull << 32)) | (static_cast<uint64_t>(SOP_RSTD_FAST) << 32);
+              for (uint32_t r = q + 4; r < n; ++r) P.code[r - 2] = P.code[r];
+              n -= 2;
+              fused_away += 2;
+              break;
+            }
+          }
+        }
         if (opc == OP_END && n > P.sec[sidx] && !overflow) {
           // a section whose last word stores a scalar register or resets a partial ends inside that word's handler
           static const bool no_tail = getenv("DVM_B200_NO_TAIL") != nullptr;

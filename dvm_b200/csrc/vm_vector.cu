@@ -525,6 +525,14 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
               asm volatile("st.shared.u32 [%0], %1;" ::"r"(sreg_addr((whi >> 24) & 0xfu)), "r"(sacc[0]) : "memory");
               goto scalar_done;
             case SOP_RINIT_END: set_part(sub & 3u, red_identity(sub >> 4)); goto scalar_done;
+            case SOP_RSTD_FAST: {
+              // each operation rounded on its own, as in the four separate words
+              const float v = __fadd_rn(__fmul_rn(u2f(sacc[0]), u2f(wlo)), u2f(xlo));
+              sacc[0] = f2u(fast_div(1.0f, sqrtf(v)));
+              spc += 8u;   // the next word only carried the second immediate
+              lds64x2(spc, xlo, xhi);
+              break;
+            }
             case SOP_RFIN: {
               const uint32_t kind = sub >> 4;
               float v = get_part(sub & 3u);
