@@ -262,6 +262,7 @@ struct VmParam {
   uint32_t need_coords;      // some tensor uses AM_GRANULE or is staged per segment
   uint32_t body_coords_mask; // BODY sections whose vector stores address a strided tensor through the chunk coordinates
   uint32_t num_body;         // number of BODY sections
+  uint32_t pro_skip_mask;    // PRO sections that hold nothing but their END word (not entered at all)
   // word offset of PRO_0, BODY_0, PRO_1, ..., PRO_n in code[]: PRO sections hold instruction words ending
   // with OP_END, BODY sections hold micro-ops ending with UH_END
   uint16_t sec[2 * kMaxPhases + 2];

@@ -1247,6 +1247,7 @@ bool LowerStageAs(VectorStage *st, bool dual) {
         recip_of[DVMB_OIDX(w)] = static_cast<int>(next++);
   }
   P.body_coords_mask = 0;
+  P.pro_skip_mask = 0;
   bool full = true;   // lowering the variant for full chunks
   auto fetch = [&](uint32_t kind, uint32_t idx, uint32_t imm, uint32_t dest) {
     switch (kind) {
@@ -1375,6 +1376,10 @@ bool LowerStageAs(VectorStage *st, bool dual) {
       const uint64_t w = st->bytecode[pc];
       const uint32_t opc = DVMB_OPC(w), sub = DVMB_SUB(w), okind = DVMB_OKIND(w), oidx = DVMB_OIDX(w);
       if (!body) {
+        // a sum partial is zero at kernel start and every ReduceSum.fin leaves it at zero again: its init does nothing
+        static const bool keep_init = getenv("DVM_B200_NO_FUSE") != nullptr;
+        if (opc == OP_RINIT && (sub >> 4) == R_SUM && !keep_init) continue;
+        if (opc == OP_END && n == P.sec[sidx]) P.pro_skip_mask |= 1u << (sidx >> 1);
         // scalar sections keep the instruction-word format; the common forms get a flat handler id as opcode
         uint32_t flat = opc;
         const bool plain_operand = okind == K_SREG || okind == K_IMM || okind == K_ACC;

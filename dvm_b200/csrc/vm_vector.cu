@@ -503,7 +503,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
     }
     for (uint32_t ph = 0; ph <= P.num_body; ++ph) {
       // ---------------- scalar side: PRO_ph ----------------
-      {
+      if (!((P.pro_skip_mask >> ph) & 1u)) {
         uint32_t spc = code_saddr + 8u * P.sec[2 * ph];
         uint32_t wlo, whi, xlo, xhi;   // the current word and the next one, already on its way
         lds64x2(spc, wlo, whi);
