@@ -56,6 +56,10 @@ SIGNATURES = {
     "dvm_reshape": (c_void_p, [c_void_p, c_void_p, c_void_p]),
     "dvm_copy": (c_void_p, [c_void_p, c_void_p]),
     "dvm_matmul": (c_void_p, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "dvm_sequence_add": (c_int, [c_void_p, c_int, ctypes.c_uint32]),
+    "dvm_parallel_add": (c_int, [c_void_p, c_int, ctypes.c_uint32, c_size_t]),
+    "dvm_spec_next": (c_int, [c_void_p]),
+    "dvm_set_store_inplace": (c_int, [c_void_p, c_void_p]),
     "dvm_normalize": (c_int, [c_void_p]),
     "dvm_pre_codegen": (c_int, [c_void_p, ctypes.POINTER(c_size_t)]),
     "dvm_codegen": (c_int, [c_void_p, ctypes.POINTER(Reloc), c_size_t, WS_ALLOC_FN, c_void_p]),
@@ -80,6 +84,8 @@ SIGNATURES = {
     "dvm_rt_memcpy_d2h": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
     "dvm_rt_memset": (c_int, [c_void_p, c_int, c_size_t, c_void_p]),
     "dvm_rt_sync": (c_int, [c_void_p]),
+    "dvm_rt_check_status": (c_int, []),
+    "dvm_rt_selftest_wait_expiry": (c_int, [ctypes.c_uint, c_void_p]),
     "dvm_rt_host_alloc": (c_void_p, [c_size_t]),
     "dvm_rt_host_free": (c_int, [c_void_p]),
     "dvm_perf": (c_int, [c_void_p, c_int, c_int, c_void_p, ctypes.POINTER(ctypes.c_float),

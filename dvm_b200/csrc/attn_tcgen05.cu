@@ -30,7 +30,7 @@
 
 namespace dvmb {
 
-__device__ unsigned int g_attn_status = 0;
+__device__ WaitStatus g_attn_status = {0u, 0u};
 
 namespace {
 
@@ -127,7 +127,7 @@ __device__ __forceinline__ uint32_t pack_pair(uint32_t dtype, float lo, float hi
 
 namespace {
 template <uint32_t DT, bool SCALE_FIRST>
-__device__ __forceinline__ void attention_body(const AttnParam &P, const AttnMaps &maps) {
+__device__ __forceinline__ void attention_body(const AttnParam &P, const AttnMaps &maps, const uint32_t epoch) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -179,7 +179,7 @@ __device__ __forceinline__ void attention_body(const AttnParam &P, const AttnMap
         const bool is_v = p != 0 && ((p & 1u) == 0 || p == ntiles - 1);
         const uint32_t j = p == 0 ? 0u : (is_v ? (p == ntiles - 1 ? nkv - 1 : (p - 2) / 2) : (p + 1) / 2);
         const CUtensorMap *map = is_v ? &maps.v : &maps.k;
-        mbar_wait(base + kBarKvEmpty + 8 * slot, parity, 1, &g_attn_status);
+        mbar_wait(base + kBarKvEmpty + 8 * slot, parity, 1, &g_attn_status, epoch);
         mbar_expect_tx(base + kBarKvFull + 8 * slot, tile_bytes);
         for (uint32_t h = 0; h < dhalves; ++h)
           tma_load_3d(base + kOffRing + slot * kTileBytes + h * kHalfBytes, map, base + kBarKvFull + 8 * slot, (int)(h * 64),
@@ -223,9 +223,9 @@ __device__ __forceinline__ void attention_body(const AttnParam &P, const AttnMap
       auto v_pos = [&](uint32_t j) { return j + 1 < nkv ? 2 * j + 2 : ntiles - 1; };
       auto full_ready = [&](uint32_t pos) { return mbar_try_wait(base + kBarKvFull + 8 * (pos % kRingSlots), (pos / kRingSlots) & 1u); };
       auto release = [&](uint32_t pos) { umma_commit_cta1(base + kBarKvEmpty + 8 * (pos % kRingSlots)); };
-      mbar_wait(base + kBarQ, 0, 2, &g_attn_status);
+      mbar_wait(base + kBarQ, 0, 2, &g_attn_status, epoch);
       // prologue: scores of key tile 0 for both row tiles
-      mbar_wait(base + kBarKvFull, 0, 3, &g_attn_status);
+      mbar_wait(base + kBarKvFull, 0, 3, &g_attn_status, epoch);
       tcgen05_after_sync();
       issue_s(0, 0);
       issue_s(1, 0);
@@ -264,9 +264,10 @@ __device__ __forceinline__ void attention_body(const AttnParam &P, const AttnMap
           idle = 0;
           unsigned long long t_now;
           asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_now));
-          if (*reinterpret_cast<volatile unsigned int *>(&g_attn_status) != 0u) break;
-          if (idle == 0 && t_now - t_last > 2000000000ull) {
-            atomicCAS(&g_attn_status, 0u, (11u << 24) | (blockIdx.x & 0xffffffu));
+          if (*reinterpret_cast<volatile unsigned int *>(&g_attn_status.abort_epoch) == epoch) break;
+          if (idle == 0 && t_now - t_last > kWaitLimitNs) {
+            atomicCAS(&g_attn_status.first_error, 0u, (11u << 24) | (blockIdx.x & 0xffffffu));
+            atomicExch(&g_attn_status.abort_epoch, epoch);
             break;
           }
         }
@@ -286,7 +287,7 @@ __device__ __forceinline__ void attention_body(const AttnParam &P, const AttnMap
     float m_used = -CUDART_INF_F, l = 0.0f;
     const uint32_t p_row = base + kOffP + g * kTileBytes + (r >> 3) * 1024 + (r & 7u) * 128;
     for (uint32_t j = 0; j < nkv; ++j) {
-      mbar_wait(base + kBarSFull + 8 * g, j & 1u, 8, &g_attn_status);
+      mbar_wait(base + kBarSFull + 8 * g, j & 1u, 8, &g_attn_status, epoch);
       tcgen05_after_sync();
       uint32_t s[128];
 #pragma unroll
@@ -379,7 +380,7 @@ __device__ __forceinline__ void attention_body(const AttnParam &P, const AttnMap
       }
       // P_g and O_g are free once the previous P V of this tile has completed
       if (j != 0) {
-        mbar_wait(base + kBarPvDone + 8 * g, (j - 1) & 1u, 9, &g_attn_status);
+        mbar_wait(base + kBarPvDone + 8 * g, (j - 1) & 1u, 9, &g_attn_status, epoch);
         tcgen05_after_sync();
       }
       if (__any_sync(0xffffffffu, rescale)) {
@@ -406,7 +407,7 @@ __device__ __forceinline__ void attention_body(const AttnParam &P, const AttnMap
       if (lane == 0) mbar_arrive(base + kBarPReady + 8 * g);
     }
     // ---- result: O / l, rounded to the operand type
-    mbar_wait(base + kBarPvDone + 8 * g, (nkv - 1) & 1u, 10, &g_attn_status);
+    mbar_wait(base + kBarPvDone + 8 * g, (nkv - 1) & 1u, 10, &g_attn_status, epoch);
     tcgen05_after_sync();
     const float inv = 1.0f / l;
     uint8_t *orow = reinterpret_cast<uint8_t *>(P.o_ptr) + ((size_t)bz * P.sq + row) * P.d * 2;
@@ -434,8 +435,8 @@ __device__ __forceinline__ void attention_body(const AttnParam &P, const AttnMap
 
 #define DVMB_ATTN_KERNEL(NAME, DT, SF)                                                                              \
   __global__ void __launch_bounds__(kThreads, 1) NAME(const __grid_constant__ AttnParam P,                          \
-                                                      const __grid_constant__ AttnMaps maps) {                      \
-    attention_body<DT, SF>(P, maps);                                                                                \
+                                                      const __grid_constant__ AttnMaps maps, const uint32_t epoch) { \
+    attention_body<DT, SF>(P, maps, epoch);                                                                         \
   }
 DVMB_ATTN_KERNEL(dvm_b200_attention_bf16, T_BF16, false)
 DVMB_ATTN_KERNEL(dvm_b200_attention_bf16_sf, T_BF16, true)
@@ -485,7 +486,7 @@ int LaunchAttention(const AttnParam &p, void *stream) {
   if ((p.q_ptr | p.k_ptr | p.v_ptr | p.o_ptr) & 15u) return -2;
   int dev = 0;
   cudaGetDevice(&dev);
-  using KernelFn = void (*)(const AttnParam, const AttnMaps);
+  using KernelFn = void (*)(const AttnParam, const AttnMaps, const uint32_t);
   static const KernelFn kernels[4] = {dvm_b200_attention_bf16, dvm_b200_attention_bf16_sf, dvm_b200_attention_f16,
                                       dvm_b200_attention_f16_sf};
   static bool attr_set[64] = {false};
@@ -503,15 +504,16 @@ int LaunchAttention(const AttnParam &p, void *stream) {
   if (rc == 0) rc = EncodeRows(&maps.v, p.v_ptr, p.d, p.skv, p.batch);
   if (rc != 0) return rc;
   const uint32_t qblocks = (p.sq + kTileQ * kQTilesPerCta - 1) / (kTileQ * kQTilesPerCta);
-  kernel<<<p.batch * qblocks, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p, maps);
+  kernel<<<p.batch * qblocks, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p, maps, NextLaunchEpoch());
   return static_cast<int>(cudaGetLastError());
 }
 
 unsigned int ReadAttentionStatus() {
-  unsigned int v = 0, zero = 0;
+  WaitStatus v = {0u, 0u};
+  const unsigned int zero = 0;
   if (cudaMemcpyFromSymbol(&v, g_attn_status, sizeof(v)) != cudaSuccess) return 0xffffffffu;
-  if (v != 0) cudaMemcpyToSymbol(g_attn_status, &zero, sizeof(zero));
-  return v;
+  if (v.first_error != 0) cudaMemcpyToSymbol(g_attn_status, &zero, sizeof(zero), offsetof(WaitStatus, first_error));
+  return v.first_error;
 }
 
 }  // namespace dvmb

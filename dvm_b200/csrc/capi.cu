@@ -32,7 +32,6 @@ struct dvm_scalar {
 struct dvm_kernel {
   dvm::Kernel kernel;
   double last_jit_us = 0.0;
-  size_t ws_bytes = 0;   // workspace the current program needs (set by dvm_pre_codegen / dvm_codegen)
 };
 
 namespace {
@@ -182,6 +181,19 @@ dvm_object *dvm_matmul(dvm_kernel *k, dvm_object *lhs, dvm_object *rhs, int tran
   return DVM_OBJ_GUARD(k->kernel.MatMul(N(lhs), N(rhs), trans_a != 0, trans_b != 0, bias ? N(bias) : nullptr));
 }
 
+int dvm_sequence_add(dvm_kernel *k, int kernel_type, uint32_t flags) {
+  return Guard([&]() { k->kernel.SequenceAdd(static_cast<dvm::KernelType>(kernel_type), flags); return 0; }, 1);
+}
+int dvm_parallel_add(dvm_kernel *k, int kernel_type, uint32_t flags, size_t thread_limit) {
+  return Guard([&]() { k->kernel.ParallelAdd(static_cast<dvm::KernelType>(kernel_type), flags, thread_limit); return 0; }, 1);
+}
+int dvm_spec_next(dvm_kernel *k) {
+  return Guard([&]() { k->kernel.SpecNext(); return 0; }, 1);
+}
+int dvm_set_store_inplace(dvm_kernel *k, dvm_object *store) {
+  return Guard([&]() { k->kernel.SetStoreInplace(N(store)); return 0; }, 1);
+}
+
 int dvm_normalize(dvm_kernel *k) {
   return Guard([&]() { k->kernel.Normalize(); return 0; }, 1);
 }
@@ -192,7 +204,6 @@ int dvm_pre_codegen(dvm_kernel *k, size_t *workspace_bytes) {
       auto t0 = std::chrono::steady_clock::now();
       size_t ws = k->kernel.PreCodeGen();
       k->last_jit_us = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count();
-      k->ws_bytes = ws;
       if (workspace_bytes) *workspace_bytes = ws;
       return 0;
     },
@@ -210,7 +221,6 @@ int dvm_codegen(dvm_kernel *k, const dvm_reloc *relocs, size_t reloc_size, dvm_w
       k->kernel.Normalize();
       k->kernel.CodeGen(reinterpret_cast<const dvm::RelocEntry *>(relocs), reloc_size, &cb);
       k->last_jit_us = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count();
-      k->ws_bytes = cb.asked;
       return 0;
     },
     1);
@@ -231,9 +241,16 @@ size_t dvm_static_scratch_capacity(void) { return kStaticScratchBytes; }
 int dvm_launch_static_scratch(dvm_kernel *k, const dvm_reloc *relocs, size_t reloc_size, void *stream) {
   return Guard(
     [&]() {
-      if (k->ws_bytes > kStaticScratchBytes) {
+      // the workspace the program compiled for the CURRENT shapes needs (any call that compiles - code generation, a
+      // listing, an inspection after a shape update - may have changed it, so it is read here and never cached)
+      const dvm::VKernel *vk = k->kernel.GetImpl();
+      if (vk == nullptr || !vk->compiled_) {
+        g_error = "dvm_launch_static_scratch needs dvm_pre_codegen() or dvm_codegen() for the current shapes first";
+        return -5;
+      }
+      if (vk->ws_bytes_ > kStaticScratchBytes) {
         char buf[160];
-        snprintf(buf, sizeof(buf), "this kernel needs %zu bytes of workspace; the static scratch holds %zu", k->ws_bytes,
+        snprintf(buf, sizeof(buf), "this kernel needs %zu bytes of workspace; the static scratch holds %zu", vk->ws_bytes_,
                  kStaticScratchBytes);
         g_error = buf;
         return -2;
@@ -298,11 +315,9 @@ int dvm_rt_memcpy_d2h(void *dst, const void *src, size_t bytes, void *stream) {
 int dvm_rt_memset(void *dst, int value, size_t bytes, void *stream) {
   return CudaCheck(cudaMemsetAsync(dst, value, bytes, static_cast<cudaStream_t>(stream)), "memset");
 }
-// Waits for the stream, then reads the status words of the device interpreters: a bounded device wait that
-// expired (the kernel then ran to its end with wrong results) is reported here as an error.
-int dvm_rt_sync(void *stream) {
-  int rc = CudaCheck(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)), "stream sync");
-  if (rc != 0) return rc;
+// Reads (and clears) the status records of the device interpreters: a bounded device wait that expired (the kernel
+// then ran to its end with wrong results) is reported here as an error.  Does not wait for anything.
+int dvm_rt_check_status(void) {
   const unsigned int sv = dvmb::ReadVectorStatus(), sm = dvmb::ReadMatMulStatus(), sa = dvmb::ReadAttentionStatus();
   if ((sv | sm | sa) != 0) {
     char buf[160];
@@ -311,6 +326,20 @@ int dvm_rt_sync(void *stream) {
     return -1;
   }
   return 0;
+}
+// Waits for the stream, then reports like dvm_rt_check_status().
+int dvm_rt_sync(void *stream) {
+  int rc = CudaCheck(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)), "stream sync");
+  if (rc != 0) return rc;
+  return dvm_rt_check_status();
+}
+int dvm_rt_selftest_wait_expiry(unsigned int limit_ms, void *stream) {
+  return Guard(
+    [&]() {
+      dvmb::Runtime::Get().EnsureInit();
+      return dvmb::LaunchWaitSelfTest(limit_ms, stream);
+    },
+    -1);
 }
 void *dvm_rt_host_alloc(size_t bytes) {
   void *p = nullptr;

@@ -392,7 +392,13 @@ NDObject *Kernel::Store(void *addr, NDObject *input, IntArrayRef *stride) {
   return Store(addr, input);
 }
 NDObject *Kernel::PadStore(void *, NDObject *, int64_t) { Unsupported("PadStore"); }
-void Kernel::SetStoreInplace(NDObject *) {}
+// ref: src/dvm.cc:1578-1580, src/xkernel.h:322.  The reference's flag keeps its workspace pool from handing the store's
+// buffer to another temporary.  Workspace temporaries here are bump-allocated once per compile and never reused, and a
+// user's buffer is never used as workspace, so the mark needs no action beyond being recorded (listed by DumpR).
+void Kernel::SetStoreInplace(NDObject *store) {
+  if (store == nullptr || store->kind != N_STORE) DvmException("SetStoreInplace expects a Store operation");
+  store->store_inplace = true;
+}
 void Kernel::SetStoreTemp(NDObject *store) { store->store_temp = true; }
 void Kernel::SetLoadBind(NDObject *, NDObject *) { Unsupported("SetLoadBind"); }
 
@@ -589,9 +595,31 @@ NDObject *Kernel::AllGather(NDObject *, const Comm *) { Unsupported("AllGather")
 NDObject *Kernel::AllGatherV2(NDObject *, const Comm *) { Unsupported("AllGatherV2"); }
 NDObject *Kernel::ReduceScatter(NDObject *, const Comm *) { Unsupported("ReduceScatter"); }
 NDObject *Kernel::ExtOut(NDObject *, int) { Unsupported("ExtOut"); }
-void Kernel::SpecNext() {}
-void Kernel::ParallelAdd(KernelType, uint32_t, size_t) { Unsupported("ParallelAdd"); }
-void Kernel::SequenceAdd(KernelType, uint32_t) {}
+// ref: src/dvm.cc:1721-1725 (kernel.h:405).  In the reference the call moves a speculative vector kernel to its next
+// fallback stage: a hint where to cut if the graph cannot stay one kernel.  It never changes what the graph computes.
+// The stage planner here finds its cuts from the graph alone, so the hint is accepted and not needed; on any other
+// kernel type the call is an error, as it is undefined in the reference.
+void Kernel::SpecNext() {
+  auto vk = Impl(this);
+  if (vk->type_ != kVector || !(vk->flags_ & kSpeculate)) DvmException("SpecNext needs a kVector kernel with the kSpeculate flag");
+}
+// ref: src/dvm.cc:1704-1707, ParallelKernel::AddKernel src/xkernel.cc:1009-1151.  Sub-kernels are independent graphs;
+// each becomes launches of its own on the caller's stream (the reference packs them into one launch through a per-core
+// program table, src/vm_gpu.cu:1567-1583 - same results, one launch more per sub-kernel here).
+void Kernel::ParallelAdd(KernelType type, uint32_t, size_t) {
+  auto vk = Impl(this);
+  if (vk->type_ != kParallel) DvmException("ParallelAdd needs a kParallel kernel");
+  if (type != kVector) DvmException("ParallelAdd: only kVector sub-kernels are supported");
+  vk->cur_sub_ += 1;
+}
+// ref: src/dvm.cc:1709-1719, SequenceKernel::AddStage src/xkernel.cc:1226-1468.  Ops appended from here on form the
+// next stage: it is launched after the previous ones and reads their results through the workspace.
+void Kernel::SequenceAdd(KernelType type, uint32_t) {
+  auto vk = Impl(this);
+  if (vk->type_ != kSequence) DvmException("SequenceAdd needs a kSequence kernel");
+  if (type >= kSequence) DvmException("invalid sequence add kernel type");
+  vk->cur_sub_ += 1;
+}
 
 void Kernel::Normalize() { Impl(this)->Normalize(); }
 

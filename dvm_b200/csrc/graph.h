@@ -66,6 +66,8 @@ class NDObject {
   bool keepdims = false;
   bool trans_a = false, trans_b = false;
   bool store_temp = false;
+  bool store_inplace = false;   // Kernel::SetStoreInplace: the caller's buffer also feeds this kernel (see dvm_api.cc)
+  int sub_kernel = 0;           // sub-kernel of a kSequence / kParallel kernel this op was appended to (0 before the first add)
   int id = 0;
   mutable int cidx = -1;   // position in the op list of the vector compiler that is looking at this node (scratch)
   NDObject *in[3] = {nullptr, nullptr, nullptr};
@@ -99,6 +101,10 @@ struct VectorStage {
   uint16_t bsec[2 * dvmb::kMaxPhases + 2] = {0};   // section offsets inside `bytecode`
   std::vector<NDObject *> slot_obj;        // tensor slot -> load/store node (relocation sites)
   std::vector<int64_t> slot_ws_off;        // >= 0: slot is a workspace temporary at this byte offset
+  // byte offset inside a ring stage that the compiler planned for each bulk-staged tensor (kNoRing otherwise).  Bind()
+  // writes it into the descriptor when the bound address is 16-byte aligned and kNoRing when it is not, so a later
+  // rebind to an aligned address gets the planned offset back
+  uint32_t ring_plan_off[dvmb::kMaxTensors] = {0};
   uint64_t algo_bytes = 0;
 };
 
@@ -153,6 +159,7 @@ class VKernel {
   std::vector<std::unique_ptr<Stage>> stages_;
   std::vector<NDObject *> synth_;          // planner-made nodes (clones, workspace temporaries), owned
   size_t ws_bytes_ = 0;
+  int cur_sub_ = 0;                        // sub-kernel that NewNode() tags ops with (SequenceAdd / ParallelAdd advance it)
   void *workspace_ = nullptr;
   bool normalized_ = false;
   bool compiled_ = false;

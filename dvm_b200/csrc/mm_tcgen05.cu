@@ -32,7 +32,7 @@
 
 namespace dvmb {
 
-__device__ unsigned int g_mm_status = 0;
+__device__ WaitStatus g_mm_status = {0u, 0u};
 
 namespace {
 
@@ -97,7 +97,7 @@ __device__ __forceinline__ void finish_strip(const MmParam &P, const EpiPos &pos
 }
 
 template <int CTAS>
-__device__ __forceinline__ void mm_body(const MmParam &P, const MmMaps &maps) {
+__device__ __forceinline__ void mm_body(const MmParam &P, const MmMaps &maps, const uint32_t epoch) {
   using G = Geo<CTAS>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // 1024-byte alignment of the stage area (required by the 128-byte swizzle pattern)
@@ -157,7 +157,7 @@ __device__ __forceinline__ void mm_body(const MmParam &P, const MmMaps &maps) {
         const int row0 = (int)((mb * CTAS + rank) * BM);
         const int col0 = (int)(nb * BN + rank * (BN / CTAS));
         for (uint32_t kb = 0; kb < kblocks; ++kb) {
-          mbar_wait(bar_empty + 8 * stage, parity, 1, &g_mm_status);
+          mbar_wait(bar_empty + 8 * stage, parity, 1, &g_mm_status, epoch);
           const uint32_t sa = stages + stage * G::kStageBytes, sb = sa + kABytes;
           // the pair's first CTA counts the bytes of both CTAs on its barrier
           uint32_t full = bar_full + 8 * stage;
@@ -204,11 +204,11 @@ __device__ __forceinline__ void mm_body(const MmParam &P, const MmMaps &maps) {
                              ((P.b_kmajor ? 0u : 1u) << 16) | ((BN >> 3) << 17) | (((BM * CTAS) >> 4) << 24);
       uint32_t stage = 0, parity = 0, acc = 0, acc_parity = 1;
       for (uint32_t t = unit; t < num_tiles; t += num_units) {
-        mbar_wait(bar_tempty + 8 * acc, acc_parity, 2, &g_mm_status);
+        mbar_wait(bar_tempty + 8 * acc, acc_parity, 2, &g_mm_status, epoch);
         tcgen05_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (uint32_t kb = 0; kb < kblocks; ++kb) {
-          mbar_wait(bar_full + 8 * stage, parity, 3, &g_mm_status);
+          mbar_wait(bar_full + 8 * stage, parity, 3, &g_mm_status, epoch);
           tcgen05_after_sync();
           const uint32_t sa = stages + stage * G::kStageBytes, sb = sa + kABytes;
 #pragma unroll
@@ -254,7 +254,7 @@ __device__ __forceinline__ void mm_body(const MmParam &P, const MmMaps &maps) {
     for (uint32_t t = unit; t < num_tiles; t += num_units) {
       uint32_t bz, mb, nb;
       tile_coords(t, mblocks, nblocks, P.group_m, bz, mb, nb);
-      mbar_wait(bar_tfull + 8 * acc, acc_parity, 4, &g_mm_status);
+      mbar_wait(bar_tfull + 8 * acc, acc_parity, 4, &g_mm_status, epoch);
       tcgen05_after_sync();
       EpiPos pos;
       pos.b0 = bz / P.batch1;
@@ -303,13 +303,14 @@ __device__ __forceinline__ void mm_body(const MmParam &P, const MmMaps &maps) {
 }  // namespace
 
 __global__ void __launch_bounds__(kThreads, 1) dvm_b200_mm_tcgen05(const __grid_constant__ MmParam P,
-                                                                   const __grid_constant__ MmMaps maps) {
-  mm_body<1>(P, maps);
+                                                                   const __grid_constant__ MmMaps maps,
+                                                                   const uint32_t epoch) {
+  mm_body<1>(P, maps, epoch);
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-  dvm_b200_mm_tcgen05_pair(const __grid_constant__ MmParam P, const __grid_constant__ MmMaps maps) {
-  mm_body<2>(P, maps);
+  dvm_b200_mm_tcgen05_pair(const __grid_constant__ MmParam P, const __grid_constant__ MmMaps maps, const uint32_t epoch) {
+  mm_body<2>(P, maps, epoch);
 }
 
 // General SIMT MatMul for problems the copy engine cannot address: one thread per 16-column strip of a row,
@@ -434,20 +435,21 @@ int LaunchMatMul(const MmParam &p_in, void *stream) {
   if (pair) {
     const uint32_t tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN) * batch;
     const uint32_t units = tiles < static_cast<uint32_t>(sms / 2) ? tiles : static_cast<uint32_t>(sms / 2);
-    dvm_b200_mm_tcgen05_pair<<<units * 2, kThreads, Geo<2>::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p, maps);
+    dvm_b200_mm_tcgen05_pair<<<units * 2, kThreads, Geo<2>::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p, maps, NextLaunchEpoch());
   } else {
     const uint32_t tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * batch;
     const uint32_t grid = tiles < static_cast<uint32_t>(sms) ? tiles : static_cast<uint32_t>(sms);
-    dvm_b200_mm_tcgen05<<<grid, kThreads, Geo<1>::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p, maps);
+    dvm_b200_mm_tcgen05<<<grid, kThreads, Geo<1>::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p, maps, NextLaunchEpoch());
   }
   return static_cast<int>(cudaGetLastError());
 }
 
 unsigned int ReadMatMulStatus() {
-  unsigned int v = 0, zero = 0;
+  WaitStatus v = {0u, 0u};
+  const unsigned int zero = 0;
   if (cudaMemcpyFromSymbol(&v, g_mm_status, sizeof(v)) != cudaSuccess) return 0xffffffffu;
-  if (v != 0) cudaMemcpyToSymbol(g_mm_status, &zero, sizeof(zero));
-  return v;
+  if (v.first_error != 0) cudaMemcpyToSymbol(g_mm_status, &zero, sizeof(zero), offsetof(WaitStatus, first_error));
+  return v.first_error;
 }
 
 }  // namespace dvmb

@@ -326,6 +326,7 @@ struct Planner {
     for (size_t i = pos.at(m) + 1; i < ops.size(); ++i) {
       NDObject *v = ops[i];
       if (done.count(v) || !IsElementwise(v->kind) || !(v->shape == m->shape)) continue;
+      if (v->sub_kernel != m->sub_kernel) continue;   // a later sub-kernel of a stacked kernel is a launch of its own
       bool touches = false, ok = true;
       for (int j = 0; j < 3; ++j) {
         if (!v->in[j]) continue;
@@ -554,7 +555,16 @@ struct Planner {
 
   // ---- driver ------------------------------------------------------------------------------------------------
   void Run() {
+    // Sub-kernels of a kSequence / kParallel kernel (Kernel::SequenceAdd / ParallelAdd; the reference's SequenceKernel
+    // and ParallelKernel, src/xkernel.cc:1226-1468, 1009-1151): the open vector area is closed where the sub-kernel
+    // changes, so each sub-kernel becomes launches of its own, enqueued in the order of the adds, and a value that a
+    // later sub-kernel reads crosses through the workspace.
+    int sub = ops.empty() ? 0 : ops.front()->sub_kernel;
     for (auto n : ops) {
+      if (n->sub_kernel != sub) {
+        CloseCur();
+        sub = n->sub_kernel;
+      }
       if (done.count(n)) continue;
       if (n->shape.numel() == 0) {   // nothing to compute or to write
         done.insert(n);

@@ -2,11 +2,20 @@
 
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <string>
 
 #include "../../include/dvm.h"
+#include "bounded_wait.cuh"
 
 namespace dvmb {
+
+uint32_t NextLaunchEpoch() {
+  static std::atomic<uint32_t> counter{0};
+  uint32_t e = counter.fetch_add(1, std::memory_order_relaxed) + 1;
+  if (e == 0) e = counter.fetch_add(1, std::memory_order_relaxed) + 1;   // 0 means "no launch has failed yet"
+  return e;
+}
 
 Runtime &Runtime::Get() {
   static Runtime rt;

@@ -8,6 +8,8 @@
 
 #include <cstdint>
 
+#include "bounded_wait.cuh"
+
 namespace dvmb {
 namespace {
 
@@ -34,28 +36,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t addr, uint32_t parity) {
     : "memory");
   return ok != 0;
 }
-// Bounded wait (about two seconds).  On expiry the status word receives (code << 24 | block index); once it
-// is non-zero every later wait of the launch returns at once, so the kernel always runs to its end and the
-// host reports the failure instead of the GPU hanging.
-__device__ __noinline__ void mbar_wait_slow(uint32_t addr, uint32_t parity, uint32_t code, unsigned int *status) {
-  for (int i = 0; i < 4096; ++i)
-    if (mbar_try_wait(addr, parity)) return;
-  unsigned long long t0, t1;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-  for (;;) {
-    if (*reinterpret_cast<volatile unsigned int *>(status) != 0u) return;
-    for (int i = 0; i < 1024; ++i)
-      if (mbar_try_wait(addr, parity)) return;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-    if (t1 - t0 > 2000000000ull) {
-      atomicCAS(status, 0u, (code << 24) | (blockIdx.x & 0xffffffu));
-      return;
-    }
-  }
+// Bounded wait (bounded_wait.cuh, about two seconds).  On expiry the status record receives (code << 24 | block
+// index) and the launch's epoch; the other waits of the same launch then return from their slow path at once, so the
+// kernel always runs to its end and the host reports the failure instead of the GPU hanging.
+__device__ __noinline__ void mbar_wait_slow(uint32_t addr, uint32_t parity, uint32_t code, WaitStatus *status, uint32_t epoch) {
+  bounded_spin([&]() { return mbar_try_wait(addr, parity); }, code, status, epoch, kWaitLimitNs);
 }
-__device__ __forceinline__ void mbar_wait(uint32_t addr, uint32_t parity, uint32_t code, unsigned int *status) {
+__device__ __forceinline__ void mbar_wait(uint32_t addr, uint32_t parity, uint32_t code, WaitStatus *status, uint32_t epoch) {
   if (mbar_try_wait(addr, parity)) return;
-  mbar_wait_slow(addr, parity, code, status);
+  mbar_wait_slow(addr, parity, code, status, epoch);
 }
 
 // TMA tile loads (no multicast), completion counted in bytes on an mbarrier of this CTA.

@@ -1102,6 +1102,8 @@ struct Compiler {
     }
     P.stage_bytes = stage_bytes;
     P.num_stages = stages;
+    for (int t = 0; t < kMaxTensors; ++t)
+      out->ring_plan_off[t] = static_cast<uint32_t>(t) < P.n_tensors ? P.tensor[t].ring_off : kNoRing;
     for (int q = 0; q < kMaxPhases; ++q) P.body_ring_mask[q] = 0;
     out->smem_bytes = fixed + stages * stage_bytes;
     if (out->smem_bytes > kVmMaxSmemBytes) throw Fail{"stage needs more shared memory than one SM has"};
@@ -1638,6 +1640,15 @@ std::string DisassembleStage(const VectorStage &st) {
              td.kstride[2], td.estride[0], td.estride[1], td.estride[2], td.estride[3],
              static_cast<unsigned long long>(td.ptr));
     o += buf;
+  }
+  if (P.stage_bytes != 0) {
+    // tensor slots the producer warp stages for each BODY (what Bind() derived from the bound addresses)
+    o += "  // staged:";
+    for (uint32_t q = 0; q < P.num_body; ++q) {
+      snprintf(buf, sizeof(buf), " body_%u=0x%x", q, P.body_ring_mask[q]);
+      o += buf;
+    }
+    o += "\n";
   }
   auto dt = [&](uint32_t slot) { return static_cast<uint32_t>(P.tensor[slot].dtype); };
   auto ptr = [&](uint32_t slot) { return P.tensor[slot].ptr; };

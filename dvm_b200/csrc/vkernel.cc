@@ -35,6 +35,7 @@ NDObject *VKernel::NewNode(NodeKind kind, DataType dtype) {
   n->kind = kind;
   n->dtype = dtype;
   n->id = static_cast<int>(nodes_.size());
+  n->sub_kernel = cur_sub_;
   nodes_.push_back(n);
   normalized_ = false;
   compiled_ = false;
@@ -72,12 +73,13 @@ size_t VKernel::Compile() {
     compiled_ = true;
     return 0;
   }
-  bool has_matmul = false, has_empty = false;
+  bool has_matmul = false, has_empty = false, stacked = false;
   for (auto n : ops) {
     has_matmul |= n->kind == N_MATMUL;
     has_empty |= n->shape.numel() == 0;   // the planner drops empty tensors and keeps what still has elements
+    stacked |= n->sub_kernel != ops.front()->sub_kernel;   // kSequence / kParallel: every sub-kernel gets launches of its own
   }
-  if (!has_matmul && !has_empty) {
+  if (!has_matmul && !has_empty && !stacked) {
     // the common case: the whole graph is one launch of the vector interpreter
     auto st = std::make_unique<Stage>();
     std::string why;
@@ -122,11 +124,9 @@ void VKernel::Bind(const RelocEntry *relocs, size_t n, void *workspace) {
       const uint64_t align = 4ull * ItemSize(static_cast<DataType>(td.dtype));
       td.vec_ok = (td.layout_vec && td.ptr != 0 && td.ptr % align == 0) ? 1 : 0;
       // a tensor planned for bulk staging keeps its ring slot only if its address is 16-byte aligned
-      if (td.ring_layout && td.ptr % 16 == 0) {
-        staged |= 1u << s;
-      } else if (td.ring_layout) {
-        td.ring_off = dvmb::kNoRing;
-      }
+      const bool on_ring = td.ring_layout && st.ring_plan_off[s] != dvmb::kNoRing && td.ptr % 16 == 0;
+      td.ring_off = on_ring ? st.ring_plan_off[s] : dvmb::kNoRing;
+      if (on_ring) staged |= 1u << s;
     }
     for (uint32_t q = 0; q < P.num_body; ++q) P.body_ring_mask[q] = st.body_tensor_mask[q] & staged;
     if (LoweringKey(st) != st.lowered_for) {   // (an unaligned address took a tensor off its fast path)

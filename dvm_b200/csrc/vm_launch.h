@@ -31,6 +31,8 @@ constexpr uint32_t VmStagesOffset(uint32_t code_words) { return (kVmSmemCode + 8
 int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, uint32_t smem_bytes, void *stream);   // param.cluster > 1 launches clusters
 // Device status word (0 = ok); reading clears it.
 unsigned int ReadVectorStatus();
+// Enqueue a one-thread kernel whose bounded wait must expire after `limit_ms` (at most 1000) with status code 15.
+int LaunchWaitSelfTest(unsigned int limit_ms, void *stream);
 
 }  // namespace dvmb
 

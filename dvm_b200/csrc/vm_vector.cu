@@ -16,10 +16,12 @@
 #include <cuda_runtime.h>
 #include <math_constants.h>
 
+#include <cstddef>
 #include <cstdint>
 #include <cstdlib>
 #include <cstring>
 
+#include "bounded_wait.cuh"
 #include "isa.h"
 #include "vm_launch.h"
 #include "vm_ops.cuh"
@@ -27,7 +29,7 @@
 
 namespace dvmb {
 
-__device__ unsigned int g_vm_status = 0;   // 0 = ok; else (code << 24 | blockIdx)
+__device__ WaitStatus g_vm_status = {0u, 0u};
 
 namespace {
 
@@ -53,28 +55,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t addr, uint32_t parity) {
     : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after about two seconds and records `code` in the status word.  Once any wait
-// of the launch has expired every later wait returns at once, so the kernel always runs to its end (with
-// wrong results, which the host reports through the status word) instead of hanging.
-__device__ __noinline__ void mbar_wait_slow(uint32_t addr, uint32_t parity, uint32_t code) {
-  for (int i = 0; i < 4096; ++i)
-    if (mbar_try_wait(addr, parity)) return;
-  unsigned long long t0, t1;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-  for (;;) {
-    if (*reinterpret_cast<volatile unsigned int *>(&g_vm_status) != 0u) return;
-    for (int i = 0; i < 1024; ++i)
-      if (mbar_try_wait(addr, parity)) return;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-    if (t1 - t0 > 2000000000ull) {
-      atomicCAS(&g_vm_status, 0u, (code << 24) | (blockIdx.x & 0xffffffu));
-      return;
-    }
-  }
+// Bounded wait (bounded_wait.cuh): gives up after about two seconds and records `code` in the status record.
+__device__ __noinline__ void mbar_wait_slow(uint32_t addr, uint32_t parity, uint32_t code, uint32_t epoch) {
+  bounded_spin([&]() { return mbar_try_wait(addr, parity); }, code, &g_vm_status, epoch, kWaitLimitNs);
 }
-__device__ __forceinline__ void mbar_wait(uint32_t addr, uint32_t parity, uint32_t code) {
+__device__ __forceinline__ void mbar_wait(uint32_t addr, uint32_t parity, uint32_t code, uint32_t epoch) {
   if (mbar_try_wait(addr, parity)) return;
-  mbar_wait_slow(addr, parity, code);
+  mbar_wait_slow(addr, parity, code, epoch);
 }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t mbar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
@@ -101,21 +88,8 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t addr, uint32_t pa
   return ok != 0;
 }
 // Bounded like every other wait of the kernel (status code 3).
-__device__ __noinline__ void mbar_wait_cluster(uint32_t addr, uint32_t parity) {
-  for (int i = 0; i < 4096; ++i)
-    if (mbar_try_wait_cluster(addr, parity)) return;
-  unsigned long long t0, t1;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-  for (;;) {
-    if (*reinterpret_cast<volatile unsigned int *>(&g_vm_status) != 0u) return;
-    for (int i = 0; i < 1024; ++i)
-      if (mbar_try_wait_cluster(addr, parity)) return;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-    if (t1 - t0 > 2000000000ull) {
-      atomicCAS(&g_vm_status, 0u, (3u << 24) | (blockIdx.x & 0xffffffu));
-      return;
-    }
-  }
+__device__ __noinline__ void mbar_wait_cluster(uint32_t addr, uint32_t parity, uint32_t epoch) {
+  bounded_spin([&]() { return mbar_try_wait_cluster(addr, parity); }, 3u, &g_vm_status, epoch, kWaitLimitNs);
 }
 __device__ __forceinline__ float ld_shared_cluster_f32(uint32_t cluster_addr) {
   float v;
@@ -277,7 +251,7 @@ __device__ __forceinline__ void decompose_group(const VmParam &P, uint32_t gi, u
 
 namespace {
 template <bool kResident, bool kCoords>
-__device__ __forceinline__ void vm_vector_body(const VmParam &P) {
+__device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t epoch) {
   asm volatile(DV_DECLARE);
   asm volatile(DV_LN(DV_SPLATLANE, "va") DV_LN(DV_SPLATLANE, "vb")
                "mov.b32 vp0, %0;\n\tmov.b32 vp1, %0;\n\tmov.b32 vp2, %0;\n\tmov.b32 vp3, %0;" ::"r"(0u));
@@ -332,7 +306,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
         for (uint32_t ch = ch_begin + plane; ch < ch_end; ch += 32u) {
           const uint32_t slot = set * P.cpc + (ch - ch_begin);
           const uint32_t full = smem_base + kVmSmemBarriers + 8 * slot;
-          mbar_wait(smem_base + kVmSmemEmpty + 8 * slot, (use & 1u) ^ 1u, 1);
+          mbar_wait(smem_base + kVmSmemEmpty + 8 * slot, (use & 1u) ^ 1u, 1, epoch);
           const uint32_t e_start = ch * P.chunk_elems;
           const uint32_t valid = min(P.chunk_elems, P.group_elems - e_start);
           uint32_t c[kMaxEnum] = {0, 0, 0, e_start};
@@ -394,7 +368,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
         uint32_t e_start = ch_begin * P.chunk_elems;
         for (uint32_t ch = ch_begin; ch < ch_end; ch += ch_step, e_start += step_elems) {
           const uint32_t full = smem_base + kVmSmemBarriers + 8 * stage;
-          mbar_wait(smem_base + kVmSmemEmpty + 8 * stage, parity, 1);
+          mbar_wait(smem_base + kVmSmemEmpty + 8 * stage, parity, 1, epoch);
           const uint32_t valid = min(P.chunk_elems, P.group_elems - e_start);
           const uint32_t bytes = mine ? ((valid << sh) & ~15u) : 0u;
           const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
@@ -573,7 +547,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
                   xpart[xpar] = v;
                   for (uint32_t r = 0; r < cluster; ++r) mbar_arrive_remote_release(map_shared_rank(smem_base + kVmSmemXBar, r));
                 }
-                mbar_wait_cluster(smem_base + kVmSmemXBar, xphase);
+                mbar_wait_cluster(smem_base + kVmSmemXBar, xphase, epoch);
                 xphase ^= 1u;
                 v = ld_shared_cluster_f32(map_shared_rank(smem_base + kVmSmemXPart + 4u * xpar, 0));
                 for (uint32_t r = 1; r < cluster; ++r)
@@ -668,11 +642,11 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
             const uint32_t slot = res_set * P.cpc + (ch - ch_begin);
             stage_saddr = smem_base + P.stages_off + slot * P.stage_bytes;
             empty_bar = smem_base + kVmSmemEmpty + 8 * slot;
-            if (ph == 0) mbar_wait(smem_base + kVmSmemBarriers + 8 * slot, res_use & 1u, 2);
+            if (ph == 0) mbar_wait(smem_base + kVmSmemBarriers + 8 * slot, res_use & 1u, 2, epoch);
           } else {
             stage_saddr = smem_base + P.stages_off + ring_stage * P.stage_bytes;
             empty_bar = smem_base + kVmSmemEmpty + 8 * ring_stage;
-            mbar_wait(smem_base + kVmSmemBarriers + 8 * ring_stage, ring_parity, 2);
+            mbar_wait(smem_base + kVmSmemBarriers + 8 * ring_stage, ring_parity, 2, epoch);
             if (++ring_stage == S) {
               ring_stage = 0;
               ring_parity ^= 1u;
@@ -1037,7 +1011,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
     // no CTA leaves while a peer may still read its partials
     if (tid == 0)
       for (uint32_t r = 0; r < cluster; ++r) mbar_arrive_remote_release(map_shared_rank(smem_base + kVmSmemXBar, r));
-    mbar_wait_cluster(smem_base + kVmSmemXBar, xphase);
+    mbar_wait_cluster(smem_base + kVmSmemXBar, xphase, epoch);
   }
 }
 }  // namespace
@@ -1046,8 +1020,9 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P) {
 // of the 128-thread ones that reduce graphs with many groups use), and up to 512 (few long groups) with one CTA per SM.
 // A third budget of 72 registers (five 128-thread CTAs per SM) was measured 50 % slower: its spills sit in the loop.
 #define DVMB_VM_KERNEL(NAME, THREADS, BLOCKS, RES, COORDS)                                                       \
-  __global__ void __launch_bounds__(THREADS, BLOCKS) NAME(const __grid_constant__ VmParam P) {                    \
-    vm_vector_body<RES, COORDS>(P);                                                                                \
+  __global__ void __launch_bounds__(THREADS, BLOCKS) NAME(const __grid_constant__ VmParam P,  \
+                                                                  const uint32_t epoch) {                         \
+    vm_vector_body<RES, COORDS>(P, epoch);                                                                         \
   }
 // dense layouts (every chunk starts at group offset + element index)
 DVMB_VM_KERNEL(dvm_b200_vm_vector, kVmFlatThreads + 32, 2, false, false)
@@ -1102,17 +1077,35 @@ int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, uint32_t
   static const bool no_r128 = getenv("DVM_B200_NO_R128") != nullptr;
   if (!param.resident && threads > 160 && threads <= 256 && !no_r128)
     kernel = param.need_coords ? dvm_b200_vm_vector_nd_r128 : dvm_b200_vm_vector_r128;
-  const cudaError_t le = cudaLaunchKernelEx(&cfg, kernel, param);
+  const cudaError_t le = cudaLaunchKernelEx(&cfg, kernel, param, NextLaunchEpoch());
   if (le != cudaSuccess) return static_cast<int>(le);
   return static_cast<int>(cudaGetLastError());
 }
 
-// Read (and clear) the device status word of the vector interpreter; 0 means every bounded wait succeeded.
+// A launch whose only wait can never succeed: one thread spins on an mbarrier that nothing arrives at, through the same
+// bounded wait as the interpreter, with a caller-chosen limit.  It exists so that a test can watch the expiry path end
+// to end (status recorded, reported by the host, cleared, later launches unaffected) without hanging or faulting the GPU.
+__global__ void dvm_b200_wait_selftest(const uint32_t epoch, const unsigned long long limit_ns) {
+  __shared__ __align__(8) uint64_t bar;
+  const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(&bar));
+  mbar_init(addr, 1);
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  bounded_spin([&]() { return mbar_try_wait(addr, 0u); }, 15u, &g_vm_status, epoch, limit_ns);
+}
+
+int LaunchWaitSelfTest(unsigned int limit_ms, void *stream) {
+  if (limit_ms > 1000u) limit_ms = 1000u;
+  dvm_b200_wait_selftest<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(NextLaunchEpoch(), 1000000ull * limit_ms);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Read (and clear) the first recorded expiry of the vector interpreter; 0 means every bounded wait succeeded.
 unsigned int ReadVectorStatus() {
-  unsigned int v = 0, zero = 0;
+  WaitStatus v = {0u, 0u};
+  const unsigned int zero = 0;
   if (cudaMemcpyFromSymbol(&v, g_vm_status, sizeof(v)) != cudaSuccess) return 0xffffffffu;
-  if (v != 0) cudaMemcpyToSymbol(g_vm_status, &zero, sizeof(zero));
-  return v;
+  if (v.first_error != 0) cudaMemcpyToSymbol(g_vm_status, &zero, sizeof(zero), offsetof(WaitStatus, first_error));
+  return v.first_error;
 }
 
 }  // namespace dvmb

@@ -280,7 +280,20 @@ class Kernel:
         return self._lib.dvm_inspect(self._k).decode()
 
     def spec_next(self):
-        pass
+        """Stage hint of a speculative vector kernel (KernelPy::SpecNext, include/dvm_py.h)."""
+        check_rc(self._lib.dvm_spec_next(self._k), "spec_next")
+
+    def seq_add(self, ktype, flags=0):
+        """Start the next stage of a "seq" kernel (KernelPy::SequenceAdd, include/dvm_py.h:371)."""
+        check_rc(self._lib.dvm_sequence_add(self._k, int(ktype), int(flags)), "seq_add")
+
+    def parallel_add(self, ktype, flags=0, core_limit=0):
+        """Start the next independent sub-kernel of a "parallel" kernel (KernelPy::ParallelAdd, include/dvm_py.h:214)."""
+        check_rc(self._lib.dvm_parallel_add(self._k, int(ktype), int(flags), int(core_limit)), "parallel_add")
+
+    def set_store_inplace(self, store):
+        """Mark a store whose buffer also feeds the kernel (KernelPy::SetStoreInplace, include/dvm_py.h:206)."""
+        check_rc(self._lib.dvm_set_store_inplace(self._k, store._h), "set_store_inplace")
 
     @staticmethod
     def set_deterministic(enable):

@@ -82,6 +82,16 @@ DVM_C_API dvm_object *dvm_copy(dvm_kernel *k, dvm_object *input);               
 DVM_C_API dvm_object *dvm_matmul(dvm_kernel *k, dvm_object *lhs, dvm_object *rhs, int trans_a, int trans_b,
                                  dvm_object *bias);                                           /* dvm.h:509 */
 
+/* ---- stacked kernels and marks ---- */
+/* start the next stage of a kSequence kernel (Kernel::SequenceAdd, dvm.h:559; KernelPy::SeqAdd, include/dvm_py.h) */
+DVM_C_API int dvm_sequence_add(dvm_kernel *k, int kernel_type, uint32_t flags);
+/* start the next independent sub-kernel of a kParallel kernel (Kernel::ParallelAdd, dvm.h:552) */
+DVM_C_API int dvm_parallel_add(dvm_kernel *k, int kernel_type, uint32_t flags, size_t thread_limit);
+/* stage hint of a speculative vector kernel (Kernel::SpecNext, dvm.h:544) */
+DVM_C_API int dvm_spec_next(dvm_kernel *k);
+/* mark a store whose buffer also feeds the kernel (Kernel::SetStoreInplace, dvm.h:350) */
+DVM_C_API int dvm_set_store_inplace(dvm_kernel *k, dvm_object *store);
+
 /* ---- shape inference, code generation, launch ---- */
 DVM_C_API int dvm_normalize(dvm_kernel *k);                                                   /* dvm.h:566 */
 DVM_C_API int dvm_pre_codegen(dvm_kernel *k, size_t *workspace_bytes);                        /* dvm.h:590 */
@@ -102,7 +112,9 @@ DVM_C_API int dvm_launch_reloc(dvm_kernel *k, const dvm_reloc *relocs, size_t re
  *     non-zero return and a message in dvm_last_error(); nothing is launched.
  *   - Every GPU that loads the library holds the array until the process exits.
  *   - The first call on a device resolves the array's device address (cudaGetSymbolAddress, with that device
- *     current); make that first call before starting any stream capture.
+ *     current) and, like the first launch of any kernel of this library, sets function attributes; make that first call
+ *     before starting any stream capture, and from one thread (the per-device address is cached without a lock; later
+ *     calls only read it).
  *   - All calls share the one array, which keeps whatever the last call left in it.  A kernel's temporaries are
  *     always written before they are read, so nothing needs clearing; but two such launches that overlap on the
  *     GPU (different streams) race on the array - serialise them. */
@@ -129,7 +141,20 @@ DVM_C_API int dvm_rt_free(void *p);
 DVM_C_API int dvm_rt_memcpy_h2d(void *dst, const void *src, size_t bytes, void *stream);
 DVM_C_API int dvm_rt_memcpy_d2h(void *dst, const void *src, size_t bytes, void *stream);
 DVM_C_API int dvm_rt_memset(void *dst, int value, size_t bytes, void *stream);
+/* Waits for `stream`, then reports like dvm_rt_check_status(). */
 DVM_C_API int dvm_rt_sync(void *stream);
+/* No counterpart in the reference (its device waits are unbounded).  Every wait inside the device kernels is bounded
+ * (about two seconds); a kernel whose wait ran out records that, finishes with wrong results and leaves the context
+ * usable.  This call reads and clears the record of the current device without waiting for anything: 0 = no wait has
+ * expired since the last check, -1 = one has (details in dvm_last_error()).  Callers that synchronise their own streams
+ * (cudaStreamSynchronize, events) instead of dvm_rt_sync() - C++ clients of include/dvm.h link the same symbol - call it
+ * after they have synchronised.  An expiry is tied to the launch it happened in: it does not shorten the waits of later
+ * launches or of launches on other streams. */
+DVM_C_API int dvm_rt_check_status(void);
+/* No counterpart in the reference.  Enqueues a one-thread kernel whose only wait can never be satisfied and gives up
+ * after `limit_ms` milliseconds (clamped to 1000), so that the reporting path above can be exercised without a hang or
+ * a fault: after a synchronisation dvm_rt_check_status() returns -1 once and 0 afterwards. */
+DVM_C_API int dvm_rt_selftest_wait_expiry(unsigned int limit_ms, void *stream);
 DVM_C_API void *dvm_rt_host_alloc(size_t bytes);   /* pinned host memory */
 DVM_C_API int dvm_rt_host_free(void *p);
 /* warmup launches, then `reps` launches timed one by one with device events on `stream`

@@ -1,7 +1,7 @@
 """Builds the reference's own CUDA backend (mindspore-ai/dvm, `DVM_ARCH=gpu`) into oracle/_ref/ for cross-checking.
 
 TEST INFRASTRUCTURE ONLY.  The sources are compiled where they lie (the read-only reference tree: the directory given on the
-command line or in DVM_REFERENCE_DIR); nothing is copied into this repository and every output goes to oracle/_ref/, which is git-ignored.
+command line, else DVM_REFERENCE_DIR, else a directory named `reference` beside this repository); nothing is copied into this repository and every output goes to oracle/_ref/, which is git-ignored.
 The recipe restates the GPU branch of the reference's Makefile (Makefile:7-14, 84-103): g++ on the host sources with
 -DDVM_ARCH_GPU, nvcc on src/vm_gpu.cu for sm_100a, one shared pybind11 module `_dvm_py`.  The reference's GPU backend
 executes vector kernels only (src/system.cc:290-294), so it cross-checks the elementwise / reduce graphs, not MatMul.
@@ -26,7 +26,15 @@ def module_path():
     return os.path.join(OUT, "_dvm_py" + suffix)
 
 
-DEFAULT_REFERENCE = os.environ.get("DVM_REFERENCE_DIR", os.path.join(os.sep, "root", "reference"))
+def find_reference():
+    """The reference tree: DVM_REFERENCE_DIR when set, else a directory named `reference` beside this repository."""
+    env = os.environ.get("DVM_REFERENCE_DIR")
+    if env:
+        return env
+    return os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+DEFAULT_REFERENCE = find_reference()
 
 
 def build(ref=DEFAULT_REFERENCE, force=False):

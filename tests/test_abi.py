@@ -143,3 +143,112 @@ def test_peephole_can_be_switched_off(monkeypatch):
     fused = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, check=True).stdout
     assert _micro_ops(plain)[0] == ["lda.fp32", "ldb.fp32", "Add.b", "st.fp32"]
     assert _micro_ops(fused)[0][:2] == ["lda.fp32+ldb+Add.b", "st.fp32"]
+
+
+def _reloc_array(pairs):
+    arr = (_capi.Reloc * len(pairs))()
+    for i, (op, addr) in enumerate(pairs):
+        arr[i].io = op._h
+        arr[i].addr = addr
+    return arr
+
+
+def test_ring_slot_comes_back_after_an_unaligned_rebind(lib):
+    # a tensor planned for bulk staging loses its ring slot while it is bound to an address that is not 16-byte aligned,
+    # and gets the planned slot back (not a stale marker) when it is bound to an aligned address again
+    k = dvm.PyKernel("vector", "das", 0)
+    a = k.load([64, 4096], dvm.float32)
+    b = k.load([64, 4096], dvm.float32)
+    s = k.store(k.add(a, b))
+    ws = ctypes_size_t()
+    assert lib.dvm_pre_codegen(k._k, ws) == 0
+
+    def listing(addr_a):
+        rel = _reloc_array([(a, addr_a), (b, 0x20000000), (s, 0x30000000)])
+        lib.dvm_launch_reloc(k._k, rel, len(rel), None, None)   # binds, then fails to launch without a device
+        return k.das()
+
+    aligned = listing(0x10000000)
+    assert "t0: fp32 dense vec=1 ring=1" in aligned and "staged: body_0=0x3" in aligned
+    unaligned = listing(0x10000004)
+    assert "t0: fp32 dense vec=0 ring=0" in unaligned and "staged: body_0=0x2" in unaligned
+    again = listing(0x10000000)
+    assert again == aligned
+
+
+def ctypes_size_t():
+    import ctypes
+    return ctypes.byref(ctypes.c_size_t(0))
+
+
+def test_static_scratch_launch_reads_the_workspace_of_the_current_program(lib):
+    # the capacity check must see the program compiled for the shapes of NOW, also when the last compile was triggered
+    # by a listing after a shape update and not by dvm_pre_codegen / dvm_codegen
+    k = dvm.PyKernel("split:dyn", "das", 0)
+    sa, sb = dvm.IntArrayRef([128, 64]), dvm.IntArrayRef([128, 64])
+    a, b = k.load(sa, dvm.bfloat16), k.load(sb, dvm.bfloat16)
+    prod = k.cast(k.matmul(a, b, False, True), dvm.float32)
+    s1, s2 = k.store(k.sum(prod, (1,), True)), k.store(k.mul(prod, 2.0))
+    ws = ctypes_size_t()
+    assert lib.dvm_pre_codegen(k._k, ws) == 0
+    small = ws._obj.value
+    assert 0 < small <= lib.dvm_static_scratch_capacity()
+    sa.update([4096, 64])
+    sb.update([2048, 64])           # fp32 product of 4096 x 2048: 32 MiB of workspace
+    assert lib.dvm_normalize(k._k) == 0
+    k.das()                         # compiles for the new shapes
+    rel = _reloc_array([(a, 0x10000000), (b, 0x20000000), (s1, 0x30000000), (s2, 0x40000000)])
+    rc = lib.dvm_launch_static_scratch(k._k, rel, len(rel), None)
+    assert rc == -2 and "static scratch" in _capi.last_error()
+    # and a kernel that was never compiled for its current shapes is refused outright
+    sa.update([256, 64])
+    sb.update([256, 64])
+    assert lib.dvm_normalize(k._k) == 0
+    assert lib.dvm_launch_static_scratch(k._k, rel, len(rel), None) == -5
+
+
+def test_sequence_kernel_cuts_a_stage_at_every_seq_add():
+    # Kernel::SequenceAdd (include/dvm.h:559): ops after the call form the next stage, launched after the previous one
+    k = dvm.PyKernel("seq", "das", 0)
+    k.seq_add(k.K_VEC)
+    a = k.load([1024, 128], dvm.float32)
+    c = k.mul(a, k.add(a, 0.2))
+    k.seq_add(k.K_VEC)
+    k.store(k.mul(c, 0.7))
+    k.codegen()
+    das = k.das()
+    assert das.count("vmain") == 2
+    assert "workspace_bytes=%d" % (1024 * 128 * 4) in k.inspect()
+    with pytest.raises(RuntimeError):
+        k.seq_add(k.K_SEQ)          # "invalid sequence add kernel type"
+    with pytest.raises(RuntimeError):
+        dvm.PyKernel("vector", "das", 0).seq_add(0)
+
+
+def test_parallel_kernel_keeps_its_sub_kernels_apart():
+    # Kernel::ParallelAdd (include/dvm.h:552): independent sub-kernels, one set of launches each
+    k = dvm.PyKernel("parallel", "das", 0)
+    for n, f in ((256, 0.3), (8192, 0.5), (1024, 0.7)):
+        k.parallel_add(k.K_VEC)
+        k.store(k.mul(k.load([n], dvm.float32), f))
+    k.codegen()
+    assert k.das().count("vmain") == 3
+    with pytest.raises(RuntimeError):
+        dvm.PyKernel("vector", "das", 0).parallel_add(0)
+    with pytest.raises(RuntimeError):
+        k.parallel_add(k.K_MIX)
+
+
+def test_spec_next_and_inplace_mark_are_checked():
+    k = dvm.PyKernel("vector:spec", "das", 0)
+    a = k.load([10, 6000], dvm.float32)
+    r = k.sum(k.add(a, 0.02), (0,), True)
+    k.spec_next()                                   # a stage hint: accepted, the result does not depend on it
+    s = k.store(k.mul(r, a))
+    k.set_store_inplace(s)
+    k.codegen()
+    assert k.das().count("vmain") == 1
+    with pytest.raises(RuntimeError):
+        dvm.PyKernel("vector", "das", 0).spec_next()   # only speculative vector kernels have stages to advance
+    with pytest.raises(RuntimeError):
+        k.set_store_inplace(a)                      # not a store

@@ -45,13 +45,20 @@ def test_static_scratch_launch_matches_the_regular_path_twice():
     assert t.das().count("main") >= 2         # two launches, so the workspace is in use
     want = [t.output(s).copy() for s in stores]
     relocs = _relocs(t, loads + stores)
+    import torch
     for call in range(2):
         for s in stores:                      # wipe the outputs so that a launch that did nothing cannot pass
             host = t.output(s)
             assert lib.dvm_rt_memset(t.device_ptr(s), 0, host.nbytes, None) == 0
+        assert lib.dvm_rt_sync(None) == 0, _capi.last_error()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = lib.dvm_launch_static_scratch(t._k, relocs, len(relocs), None)
         assert rc == 0, _capi.last_error()
         assert lib.dvm_rt_sync(None) == 0, _capi.last_error()
+        if call == 1:
+            # the first call on a device may trigger one-time set-up inside the CUDA runtime (function attributes, the
+            # symbol lookup); from the second call on the device's free memory must not move at all
+            assert torch.cuda.mem_get_info()[0] == free_before, "the launch changed the device's free memory"
         for s, w in zip(stores, want):
             assert_close(t.output(s), w, 0.0, "static-scratch launch, call %d" % call)
 
