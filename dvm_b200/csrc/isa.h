@@ -4,9 +4,10 @@
 // `group_elems` elements.  A reduce-free graph is one group spanning the whole (coalesced) domain and its
 // chunks are dealt round-robin to the CTAs ("flat" mode).  A graph with reductions makes one group per
 // kept (non-reduced) coordinate; a CTA, or a power-of-two slice of a warp, owns a group and loops over
-// its chunks ("group" mode).  A chunk is up to `16 * tg` consecutive elements of a group: thread `t` of the
-// group owns four 4-element granules at `4*t + g*4*tg` (g = 0..3) inside the chunk, so every global access
-// is a coalesced 16-byte (fp32), 8-byte (fp16/bf16) or 4-byte (bool) vector.
+// its chunks ("group" mode).  A chunk is one or more rounds of up to `16 * tg` consecutive elements of a group: in a
+// round thread `t` of the group owns four 4-element granules at `4*t + g*4*tg` (g = 0..3), so every global access
+// is a coalesced 16-byte (fp32), 8-byte (fp16/bf16) or 4-byte (bool) vector.  Chunks of several rounds spread the
+// per-chunk work (barrier waits, bookkeeping, for single-micro-op bodies also the dispatch) over more elements.
 //
 // The machine is an accumulator machine.  The 16-lane accumulator is the only vector state in registers;
 // every other operand is read where it already lives: an input tensor's chunk in the shared-memory ring
@@ -199,6 +200,7 @@ static_assert(UH_COUNT <= 256, "handler ids are one byte");
 enum UopDest : uint32_t { UD_B = 0, UD_ACC = 1 };
 enum UopAux : uint32_t {
   UA_CMP_SREG = 0x08,  // scalar compares: the scalar is register arg16, else imm32
+  UA_LOOP = 0x40,      // load + reduce forms that are a body's only micro-op: the handler runs all remaining full rounds of the chunk
   UA_LAST = 0x80       // vector stores and full-chunk reduce accumulations (plain or fused): the body ends here (no UH_END
                        // word follows, which saves its dispatch)
 };
@@ -246,7 +248,11 @@ struct VmParam {
   uint32_t groups_per_cta;   // groups a CTA works on at a time
   uint32_t tcons;            // consumer threads of the CTA: tg * groups_per_cta rounded up to a multiple of 32
   uint32_t chunks;           // chunks per group
-  uint32_t chunk_elems;      // elements per chunk (<= 16 * tg; threads past the end idle)
+  uint32_t chunk_elems;      // elements per chunk = rounds * round_elems
+  uint32_t rounds;           // a chunk is this many rounds, back to back in its ring stage: the unit the producer stages and
+                             // the consumers wait for is the chunk, the unit a body's micro-ops work on is the round
+  uint32_t round_elems;      // elements per round (<= 16 * tg; threads past the end idle); every round is one contiguous run
+                             // of each staged tensor
   uint32_t stages_off;       // byte offset of the first ring stage in shared memory (behind the program copy)
   uint32_t stage_bytes;      // bytes of one ring stage (0: no bulk staging in this launch)
   uint32_t num_stages;

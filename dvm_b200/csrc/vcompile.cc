@@ -942,6 +942,31 @@ struct Compiler {
         P.chunks = static_cast<uint32_t>((G + P.chunk_elems - 1) / P.chunk_elems);
       }
     }
+    // ---- rounds: a long group's chunk holds several rounds (the chunk sized so far), so that the per-chunk work of
+    // the device loop (barrier waits, bookkeeping, the dispatch of single-micro-op bodies) is spread over more elements
+    P.rounds = 1;
+    P.round_elems = P.chunk_elems;
+    // (only the kernels built with the larger register budget carry the round loop: CTAs of 161..256 threads, producer
+    // warp included; the many-group geometry keeps its short chunks)
+    static const bool no_r128 = getenv("DVM_B200_NO_R128") != nullptr;
+    const uint32_t threads_planned = (P.tg * P.groups_per_cta + 31u) / 32u * 32u + 32u;
+    if (P.mode == VM_GROUP && !packed && P.chunks >= 2 && K < 4ll * sms && threads_planned > 160 && threads_planned <= 256 && !no_r128) {
+      uint64_t round_bytes = 0;
+      uint32_t n_in = 0, reads = 0;
+      for (int q = 0; q < num_body; ++q) reads |= body_tensor_mask[q];
+      for (size_t sidx = 0; sidx < slot_nodes.size(); ++sidx)
+        if (slot_nodes[sidx]->kind == N_LOAD && ((reads >> sidx) & 1u) && !I(slot_nodes[sidx]).scalar_space) {
+          round_bytes += static_cast<uint64_t>(P.round_elems) * ItemSize(slot_nodes[sidx]->dtype);
+          ++n_in;
+        }
+      uint32_t r = 1;
+      // (one producer lane per staged tensor and round; a stage of at most 32 KB leaves room for three of them)
+      while (r < 8 && 2 * r <= P.chunks && 2 * r * std::max(n_in, 1u) <= 32 && 2 * r * round_bytes <= 32u * 1024u) r *= 2;
+      if (const char *env = getenv("DVM_B200_ROUNDS")) r = std::max(1, std::min(32 / static_cast<int>(std::max(n_in, 1u)), atoi(env)));
+      P.rounds = r;
+      P.chunk_elems = r * P.round_elems;
+      P.chunks = static_cast<uint32_t>((G + P.chunk_elems - 1) / P.chunk_elems);
+    }
     const uint32_t T = (P.tg * P.groups_per_cta + 31u) / 32u * 32u;
     P.tcons = T;
 
@@ -1007,7 +1032,7 @@ struct Compiler {
       const bool contiguous_chunk = inner_stride == 1 && (dense || (td.mode == AM_GRANULE && chunk_in_inner));
       td.chunk_contig = contiguous_chunk ? 1 : 0;
       const bool is_input = n->kind == N_LOAD && ((read_mask >> sidx) & 1u);
-      if (is_input && !packed && contiguous_chunk && layout_bulk && (static_cast<int64_t>(P.chunk_elems) * isz) % 16 == 0 &&
+      if (is_input && !packed && contiguous_chunk && layout_bulk && (static_cast<int64_t>(P.round_elems) * isz) % 16 == 0 &&
           (dense ? true : chunk_in_inner)) {
         td.ring_layout = 1;
         // provisional (Bind() drops it when the address is not 16-byte aligned).  Tensors that no BODY reads together
@@ -1453,6 +1478,9 @@ bool LowerStageAs(VectorStage *st, bool dual) {
                                  (last >= UH_LDVAR_FIRST && last <= UH_LDVAR_LAST);
           if (ends_body && !no_tail && !overflow) {
             P.code[n - 1] |= static_cast<uint64_t>(UA_LAST) << 8;
+            // a body that is one load + reduce micro-op runs all full rounds of a chunk in a single dispatch
+            const bool load_reduce = (last >= UH_LDSUM_FIRST && last <= UH_LDSUM_LAST) || (last >= UH_LDVAR_FIRST && last <= UH_LDVAR_LAST);
+            if (load_reduce && n - P.sec[sidx] == 1 && P.rounds > 1) P.code[n - 1] |= static_cast<uint64_t>(UA_LOOP) << 8;
             ++fused_away;
             break;
           }
@@ -1627,9 +1655,9 @@ std::string DisassembleStage(const VectorStage &st) {
   std::string o;
   char buf[256];
   snprintf(buf, sizeof(buf),
-           "vmain.sm100(mode=%s, groups=%u, group_elems=%u, tg=%u, groups_per_cta=%u, chunk_elems=%u, chunks=%u, grid=%u, "
+           "vmain.sm100(mode=%s, groups=%u, group_elems=%u, tg=%u, groups_per_cta=%u, chunk_elems=%u, rounds=%u, chunks=%u, grid=%u, "
            "threads=%u, smem=%u, stages=%u x %u B%s, cluster=%u) {\n",
-           P.mode == VM_FLAT ? "flat" : "group", P.num_groups, P.group_elems, P.tg, P.groups_per_cta, P.chunk_elems, P.chunks,
+           P.mode == VM_FLAT ? "flat" : "group", P.num_groups, P.group_elems, P.tg, P.groups_per_cta, P.chunk_elems, P.rounds, P.chunks,
            st.grid, st.threads, st.smem_bytes, P.num_stages, P.stage_bytes, P.resident ? " resident" : "", P.cluster);
   o += buf;
   for (uint32_t t = 0; t < P.n_tensors; ++t) {
@@ -1716,7 +1744,7 @@ std::string DisassembleStage(const VectorStage &st) {
       if (h == UH_END) break;
       o += " " + uop_name(h);
       if (DVMB_UAUX(P.code[pc]) & UA_LAST) {
-        o += " (ends the body)";
+        o += (DVMB_UAUX(P.code[pc]) & UA_LOOP) ? " (ends the body, loops over the chunk's rounds)" : " (ends the body)";
         break;
       }
     }

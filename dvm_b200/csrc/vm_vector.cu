@@ -18,6 +18,7 @@
 
 #include <cstddef>
 #include <cstdint>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 
@@ -106,9 +107,9 @@ constexpr int kGranules = kLanes / 4;
 struct Pos {
   uint32_t k[kMaxKept];   // kept coordinates of this thread's group
   uint32_t e_start;       // first element (inside the group) of the current chunk
-  uint32_t in_chunk0;     // element index of granule 0 inside its chunk
+  uint32_t in_chunk0;     // element index of granule 0 inside its chunk (the current round's offset included)
   uint32_t gstep;         // 4 * tg
-  uint32_t chunk_valid;   // valid elements of the current chunk
+  uint32_t chunk_valid;   // valid elements of the current chunk up to the end of the current round
   bool gvalid;
 };
 
@@ -250,7 +251,9 @@ __device__ __forceinline__ void decompose_group(const VmParam &P, uint32_t gi, u
 }  // namespace
 
 namespace {
-template <bool kResident, bool kCoords>
+// kRounds: chunks may hold several rounds (VmParam::rounds > 1).  Only the instantiations with the larger register budget
+// carry the round bookkeeping; the others run one round per chunk and the compiler folds the round loop away.
+template <bool kResident, bool kCoords, bool kRounds>
 __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t epoch) {
   asm volatile(DV_DECLARE);
   asm volatile(DV_LN(DV_SPLATLANE, "va") DV_LN(DV_SPLATLANE, "vb")
@@ -309,26 +312,30 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
           mbar_wait(smem_base + kVmSmemEmpty + 8 * slot, (use & 1u) ^ 1u, 1, epoch);
           const uint32_t e_start = ch * P.chunk_elems;
           const uint32_t valid = min(P.chunk_elems, P.group_elems - e_start);
-          uint32_t c[kMaxEnum] = {0, 0, 0, e_start};
-          if (P.need_coords) split_enum(P, e_start, c);
+          // one copy per staged tensor and round of the chunk (a round is one contiguous run of every tensor)
           uint32_t total = 0;
-          for (uint32_t m = mask; m; m &= m - 1) {
-            const TensorDesc &td = P.tensor[__ffs(m) - 1];
-            total += (valid << item_shift(td.dtype)) & ~15u;
+          for (uint32_t r = 0; r * P.round_elems < valid; ++r) {
+            const uint32_t rv = min(P.round_elems, valid - r * P.round_elems);
+            for (uint32_t m = mask; m; m &= m - 1) total += (rv << item_shift(P.tensor[__ffs(m) - 1].dtype)) & ~15u;
           }
           if (total == 0) {
             mbar_arrive(full);
             continue;
           }
           mbar_arrive_expect_tx(full, total);
-          for (uint32_t m = mask; m; m &= m - 1) {
-            const TensorDesc &td = P.tensor[__ffs(m) - 1];
-            const uint32_t sh = item_shift(td.dtype);
-            const uint32_t bytes = (valid << sh) & ~15u;
-            if (bytes == 0) continue;
-            const uint32_t off = kept_offset(td, k) + enum_offset(td, c);
-            bulk_g2s(smem_base + P.stages_off + slot * P.stage_bytes + td.ring_off,
-                     reinterpret_cast<const uint8_t *>(td.ptr) + ((size_t)off << sh), bytes, full);
+          for (uint32_t r = 0; r * P.round_elems < valid; ++r) {
+            const uint32_t rv = min(P.round_elems, valid - r * P.round_elems);
+            uint32_t c[kMaxEnum] = {0, 0, 0, e_start + r * P.round_elems};
+            if (P.need_coords) split_enum(P, c[3], c);
+            for (uint32_t m = mask; m; m &= m - 1) {
+              const TensorDesc &td = P.tensor[__ffs(m) - 1];
+              const uint32_t sh = item_shift(td.dtype);
+              const uint32_t bytes = (rv << sh) & ~15u;
+              if (bytes == 0) continue;
+              const uint32_t off = kept_offset(td, k) + enum_offset(td, c);
+              bulk_g2s(smem_base + P.stages_off + slot * P.stage_bytes + td.ring_off + ((r * P.round_elems) << sh),
+                       reinterpret_cast<const uint8_t *>(td.ptr) + ((size_t)off << sh), bytes, full);
+            }
           }
         }
         if (++set == P.sets) {
@@ -339,16 +346,19 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
       return;
     }
     // Streaming ring.  The warp walks the consumers' tile sequence in step: every lane waits for the stage to be
-    // released, lane 0 posts the byte count, and lane t issues the bulk copy of the t-th staged tensor.  Each lane
-    // keeps its tensor's base, strides and element size in registers; the chunk coordinates advance incrementally.
+    // released, lane 0 posts the byte count, and lane (t * rounds + r) issues the bulk copy of round r of the t-th staged
+    // tensor (a round is one contiguous run of the tensor; the rounds of a chunk lie back to back in the stage).  Each
+    // lane keeps its tensor's base, strides and element size in registers; its coordinates advance incrementally.
     uint32_t umask = 0;
     for (uint32_t ph = 0; ph < P.num_body; ++ph) umask |= P.body_ring_mask[ph];
     if (umask == 0) return;
-    const bool has = plane < (uint32_t)__popc(umask);
-    const uint32_t my_t = has ? (uint32_t)__fns(umask, 0, plane + 1) : (uint32_t)(__ffs(umask) - 1);
+    const uint32_t R = P.rounds;
+    const uint32_t my_ti = plane / R, my_r = plane - my_ti * R;
+    const bool has = my_ti < (uint32_t)__popc(umask);
+    const uint32_t my_t = has ? (uint32_t)__fns(umask, 0, my_ti + 1) : (uint32_t)(__ffs(umask) - 1);
     const TensorDesc &td = P.tensor[my_t];
     const uint32_t sh = item_shift(td.dtype);
-    const uint32_t my_ring = td.ring_off;
+    const uint32_t my_ring = td.ring_off + ((my_r * P.round_elems) << sh);
     const uint8_t *my_base = reinterpret_cast<const uint8_t *>(td.ptr);
     uint32_t es[kMaxEnum];
 #pragma unroll
@@ -363,13 +373,14 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
         const uint32_t mask = P.body_ring_mask[ph];
         if (mask == 0) continue;
         const bool mine = has && ((mask >> my_t) & 1u);
-        uint32_t c[kMaxEnum] = {0, 0, 0, ch_begin * P.chunk_elems};
+        // this lane's round starts my_r * round_elems into the chunk
+        uint32_t r_start = ch_begin * P.chunk_elems + my_r * P.round_elems;
+        uint32_t c[kMaxEnum] = {0, 0, 0, r_start};
         if (P.need_coords) split_enum(P, c[3], c);
-        uint32_t e_start = ch_begin * P.chunk_elems;
-        for (uint32_t ch = ch_begin; ch < ch_end; ch += ch_step, e_start += step_elems) {
+        for (uint32_t ch = ch_begin; ch < ch_end; ch += ch_step, r_start += step_elems) {
           const uint32_t full = smem_base + kVmSmemBarriers + 8 * stage;
           mbar_wait(smem_base + kVmSmemEmpty + 8 * stage, parity, 1, epoch);
-          const uint32_t valid = min(P.chunk_elems, P.group_elems - e_start);
+          const uint32_t valid = r_start < P.group_elems ? min(P.round_elems, P.group_elems - r_start) : 0u;
           const uint32_t bytes = mine ? ((valid << sh) & ~15u) : 0u;
           const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
           if (plane == 0) {
@@ -425,7 +436,8 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
   Pos pos;
   uint32_t cc[kMaxEnum] = {0, 0, 0, 0};   // coordinates of the chunk's first element (only when some tensor needs them)
   pos.gstep = 4u * tg;
-  pos.in_chunk0 = 4u * lane_in_group;
+  const uint32_t lane4 = 4u * lane_in_group;   // the thread's first element inside a round
+  pos.in_chunk0 = lane4;
 
   auto temp_addr = [&](uint32_t k, uint32_t g) { return temps_saddr + ((k * kGranules + g) * T + tid) * 16u; };
   auto sreg_addr = [&](uint32_t k) { return sregs_saddr + (k * T + tid) * 4u; };
@@ -612,13 +624,13 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
       const bool release_slots = !resident || ph + 1 == P.num_body;
       for (uint32_t ch = ch_begin; ch < ch_end; ch += ch_step) {
         pos.e_start = ch * P.chunk_elems;
-        pos.chunk_valid = min(P.chunk_elems, P.group_elems - pos.e_start);
+        const uint32_t chunk_total = min(P.chunk_elems, P.group_elems - pos.e_start);
         if (kCoords && body_coords) {
           if (ch == ch_begin) {
             split_enum(P, pos.e_start, cc);
-          } else {
-            // chunks follow one another: advance the innermost coordinate and carry
-            cc[3] += ch_step * P.chunk_elems;
+          } else if (ch_step > 1u) {
+            // the rounds of the previous chunk advanced the coordinates by one chunk; skip the other CTAs' chunks
+            cc[3] += (ch_step - 1u) * P.chunk_elems;
 #pragma unroll
             for (int j = kMaxEnum - 1; j > 0; --j)
               while (cc[j] >= P.enum_size[j]) {
@@ -627,14 +639,6 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
               }
           }
         }
-        // every lane of this thread lies inside the chunk: the vector fast paths apply
-        const bool full_tile = pos.gvalid && pos.in_chunk0 + 3u * pos.gstep + 4u <= pos.chunk_valid;
-        // a thread without a single lane inside the chunk has nothing to fetch, add or store
-        const bool lane_active = pos.gvalid && 4u * lane_in_group < pos.chunk_valid;
-        // full chunks run the variant without per-lane tests; a thread with nothing to do starts at the final END
-        uint32_t pc_saddr = code_saddr + 8u * (full_tile ? body_pc : (lane_active ? body_pc_any : P.n_code - 1u));
-        uint32_t ulo, uhi, nlo, nhi;   // the current micro-op and the next one, already on its way
-        lds64x2(pc_saddr, ulo, uhi);   // (issued ahead of the wait for the chunk's data)
         uint32_t stage_saddr = 0, empty_bar = 0;
         if (staged_body) {
           if (resident) {
@@ -653,6 +657,22 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
             }
           }
         }
+        // A chunk is `rounds` rounds of round_elems elements, back to back in the stage; the body runs once per round on
+        // the thread's 16 lanes of it.  Rounds in which every lane of every thread is valid: the first n_full ones.
+        const uint32_t n_full = kRounds ? chunk_total / P.round_elems : 1u;
+        const uint32_t n_rounds = kRounds ? n_full + (n_full * P.round_elems < chunk_total ? 1u : 0u) : 1u;
+        for (uint32_t rnd = 0; rnd < n_rounds; ++rnd) {
+        pos.in_chunk0 = kRounds ? lane4 + rnd * P.round_elems : lane4;
+        pos.chunk_valid = kRounds ? min(chunk_total, (rnd + 1u) * P.round_elems) : chunk_total;
+        // every lane of this thread lies inside the round: the vector fast paths apply
+        const bool full_tile = pos.gvalid && pos.in_chunk0 + 3u * pos.gstep + 4u <= pos.chunk_valid;
+        // a thread without a single lane inside the round has nothing to fetch, add or store
+        const bool lane_active = pos.gvalid && pos.in_chunk0 < pos.chunk_valid;
+        // full rounds run the variant without per-lane tests; a thread with nothing to do starts at the final END
+        uint32_t pc_saddr = code_saddr + 8u * (full_tile ? body_pc : (lane_active ? body_pc_any : P.n_code - 1u));
+        uint32_t ulo, uhi, nlo, nhi;   // the current micro-op and the next one, already on its way
+        lds64x2(pc_saddr, ulo, uhi);
+        const uint32_t rnd_begin = rnd;
         for (;; ulo = nlo, uhi = nhi) {
           const uint32_t uh = ulo & 0xffu;
           const uint32_t aux = (ulo >> 8) & 0xffu;
@@ -695,7 +715,28 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
             DV_LDX_TYPES(UH_LDOP_FIRST + FO_ADD * 3, "vb", asm volatile(DV_LN(DV_BINVRN_LANE, "add.rn.f32"));)
             DV_LDX_TYPES(UH_LDOP_FIRST + FO_SUB * 3, "vb", asm volatile(DV_LN(DV_BINVRN_LANE, "sub.rn.f32"));)
             DV_LDX_TYPES(UH_LDOP_FIRST + FO_MUL * 3, "vb", asm volatile(DV_LN(DV_BINVRN_LANE, "mul.rn.f32"));)
-            DV_LDX_TYPES(UH_LDSUM_FIRST, "va", asm volatile(DV_SUMRN_TREE("0")); if (aux & UA_LAST) goto body_done;)
+            // load + reduce forms: as the only micro-op of a body (UA_LOOP) they run every remaining full round of the
+            // chunk inside one dispatch; the partial grows round by round exactly as it does with one dispatch per round
+#define DV_LDRED_CASE(H, MACRO, SHL, PRE, ...)                                                                \
+  case H: {                                                                                                 \
+    uint32_t a0 = stage_saddr + (arg << 4) + (SHL(pos.in_chunk0));                                          \
+    const uint32_t gs = SHL(pos.gstep);                                                                     \
+    PRE                                                                                                     \
+    for (;;) {                                                                                              \
+      MACRO("va", a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)                                                   \
+      __VA_ARGS__                                                                                           \
+      if (!kRounds || !(aux & UA_LOOP) || rnd + 1u >= n_full) break;                                        \
+      ++rnd;                                                                                                \
+      a0 += SHL(P.round_elems);                                                                             \
+    }                                                                                                       \
+    if (aux & UA_LAST) goto body_done;                                                                      \
+    continue;                                                                                               \
+  }
+#define DV_LDRED_TYPES(FIRST, PRE, ...)                                            \
+  DV_LDRED_CASE(FIRST + FT_F32, DV_LDR32, DV_SHL2, PRE, __VA_ARGS__)               \
+  DV_LDRED_CASE(FIRST + FT_F16, DV_LDR_F16, DV_SHL1, PRE, __VA_ARGS__)             \
+  DV_LDRED_CASE(FIRST + FT_BF16, DV_LDR_BF16, DV_SHL1, PRE, __VA_ARGS__)
+            DV_LDRED_TYPES(UH_LDSUM_FIRST, , asm volatile(DV_SUMRN_TREE("0"));)
             DV_LDX_TYPES(UH_LDSUBR_FIRST, "va", {
               const uint32_t sv_ = lds32(sreg_addr(uhi));
               asm volatile(DV_LN(DV_BINS_LANE, "sub.rn.f32")::"r"(sv_));
@@ -724,18 +765,12 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
               asm volatile(DV_LN(DV_BINS3_LANE, "mul.rn.f32", "mul.rn.f32", "add.rn.f32")::"r"(s1_), "r"(s2_), "r"(s3_));
               continue;
             }
-            DV_LDX_TYPES(UH_LDVAR_FIRST, "va", {
-              const uint32_t sv_ = lds32(sreg_addr(uhi));
-              asm volatile(DV_LN(DV_CSQR_LANE, "")::"r"(sv_));
-              asm volatile(DV_SUMRN_TREE("0"));
-              if (aux & UA_LAST) goto body_done;
-            })
-            DV_LDX_TYPES(UH_LDVAR_FIRST + 3, "va", {
-              const uint32_t sv_ = lds32(sreg_addr(uhi));
-              asm volatile(DV_LN(DV_CSQR_LANE, "")::"r"(sv_));
-              asm volatile(DV_SUMRN_TREE("1"));
-              if (aux & UA_LAST) goto body_done;
-            })
+            DV_LDRED_TYPES(UH_LDVAR_FIRST, const uint32_t sv_ = lds32(sreg_addr(uhi));,
+                           asm volatile(DV_LN(DV_CSQR_LANE, "")::"r"(sv_)); asm volatile(DV_SUMRN_TREE("0"));)
+            DV_LDRED_TYPES(UH_LDVAR_FIRST + 3, const uint32_t sv_ = lds32(sreg_addr(uhi));,
+                           asm volatile(DV_LN(DV_CSQR_LANE, "")::"r"(sv_)); asm volatile(DV_SUMRN_TREE("1"));)
+#undef DV_LDRED_TYPES
+#undef DV_LDRED_CASE
             DV_LDX_TYPES(UH_LDNORM_FIRST, "va", {
               const uint32_t s0_ = lds32(sreg_addr(uhi & 0xfu)), s1_ = lds32(sreg_addr((uhi >> 4) & 0xfu));
               const uint32_t s2_ = lds32(sreg_addr((uhi >> 8) & 0xfu)), s3_ = lds32(sreg_addr((uhi >> 12) & 0xfu));
@@ -958,7 +993,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
             // ---------------- stores ----------------
             case UH_ST_F32: {
               const TensorDesc &td = tdesc[arg];
-              uint32_t *p0 = reinterpret_cast<uint32_t *>(td.ptr) + kept_offset(td, pos.k) + (!kCoords || td.mode == AM_DENSE ? pos.e_start : enum_offset(td, cc)) + pos.in_chunk0;
+              uint32_t *p0 = reinterpret_cast<uint32_t *>(td.ptr) + kept_offset(td, pos.k) + (!kCoords || td.mode == AM_DENSE ? pos.e_start + pos.in_chunk0 : enum_offset(td, cc) + lane4);
               const uint32_t gs = pos.gstep;
               asm volatile("st.global.v4.b32 [%0], {va0,va1,va2,va3};\n\tst.global.v4.b32 [%1], {va4,va5,va6,va7};\n\t"
                            "st.global.v4.b32 [%2], {va8,va9,va10,va11};\n\tst.global.v4.b32 [%3], {va12,va13,va14,va15};" ::"l"(p0),
@@ -970,7 +1005,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
             case UH_ST_F16:
             case UH_ST_BF16: {
               const TensorDesc &td = tdesc[arg];
-              unsigned short *p0 = reinterpret_cast<unsigned short *>(td.ptr) + kept_offset(td, pos.k) + (!kCoords || td.mode == AM_DENSE ? pos.e_start : enum_offset(td, cc)) + pos.in_chunk0;
+              unsigned short *p0 = reinterpret_cast<unsigned short *>(td.ptr) + kept_offset(td, pos.k) + (!kCoords || td.mode == AM_DENSE ? pos.e_start + pos.in_chunk0 : enum_offset(td, cc) + lane4);
               const uint32_t gs = pos.gstep;
 #define DV_ST16(CVT)                                                                                          \
   asm volatile("{\n\t.reg .b32 t0, t1;\n\t"                                                                   \
@@ -1000,6 +1035,17 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
           }
         }
       body_done:
+        if (kCoords && body_coords) {
+          // the coordinates follow the rounds (a looping handler may have run several)
+          cc[3] += (rnd - rnd_begin + 1u) * P.round_elems;
+#pragma unroll
+          for (int j = kMaxEnum - 1; j > 0; --j)
+            while (cc[j] >= P.enum_size[j]) {
+              cc[j] -= P.enum_size[j];
+              cc[j - 1] += 1u;
+            }
+        }
+        }   // rounds
         if (staged_body && release_slots) {
           __syncwarp();
           if ((tid & 31u) == 0) mbar_arrive(empty_bar);
@@ -1016,27 +1062,27 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
 }
 }  // namespace
 
-// Two register budgets of the same interpreter: up to 256 consumer threads per CTA (two CTAs of that size per SM, four
+// Register budgets of the same interpreter: up to 256 consumer threads per CTA (two CTAs of that size per SM, four
 // of the 128-thread ones that reduce graphs with many groups use), and up to 512 (few long groups) with one CTA per SM.
 // A third budget of 72 registers (five 128-thread CTAs per SM) was measured 50 % slower: its spills sit in the loop.
-#define DVMB_VM_KERNEL(NAME, THREADS, BLOCKS, RES, COORDS)                                                       \
-  __global__ void __launch_bounds__(THREADS, BLOCKS) NAME(const __grid_constant__ VmParam P,  \
-                                                                  const uint32_t epoch) {                         \
-    vm_vector_body<RES, COORDS>(P, epoch);                                                                         \
+#define DVMB_VM_KERNEL(NAME, THREADS, BLOCKS, RES, COORDS, ROUNDS)                                               \
+  __global__ void __launch_bounds__(THREADS, BLOCKS) NAME(const __grid_constant__ VmParam P,                      \
+                                                          const uint32_t epoch) {                                 \
+    vm_vector_body<RES, COORDS, ROUNDS>(P, epoch);                                                                \
   }
 // dense layouts (every chunk starts at group offset + element index)
-DVMB_VM_KERNEL(dvm_b200_vm_vector, kVmFlatThreads + 32, 2, false, false)
-DVMB_VM_KERNEL(dvm_b200_vm_vector_wide, kVmMaxThreads + 32, 1, false, false)
+DVMB_VM_KERNEL(dvm_b200_vm_vector, kVmFlatThreads + 32, 2, false, false, false)
+DVMB_VM_KERNEL(dvm_b200_vm_vector_wide, kVmMaxThreads + 32, 1, false, false, false)
 // strided layouts: chunk starts follow from the chunk's coordinates along the iterated axes
-DVMB_VM_KERNEL(dvm_b200_vm_vector_nd, kVmFlatThreads + 32, 2, false, true)
-DVMB_VM_KERNEL(dvm_b200_vm_vector_nd_wide, kVmMaxThreads + 32, 1, false, true)
+DVMB_VM_KERNEL(dvm_b200_vm_vector_nd, kVmFlatThreads + 32, 2, false, true, false)
+DVMB_VM_KERNEL(dvm_b200_vm_vector_nd_wide, kVmMaxThreads + 32, 1, false, true, false)
 // CTAs of at most 256 threads that run two per SM (groups of up to 224 consumer threads plus the producer warp): the
-// bound lets ptxas use up to 128 registers, which keeps the dispatch loop free of spills
-DVMB_VM_KERNEL(dvm_b200_vm_vector_r128, 256, 2, false, false)
-DVMB_VM_KERNEL(dvm_b200_vm_vector_nd_r128, 256, 2, false, true)
+// bound lets ptxas use up to 128 registers, which keeps the dispatch loop free of spills and pays for the round loop
+DVMB_VM_KERNEL(dvm_b200_vm_vector_r128, 256, 2, false, false, true)
+DVMB_VM_KERNEL(dvm_b200_vm_vector_nd_r128, 256, 2, false, true, true)
 // resident groups (and clusters): every chunk of a group keeps a shared-memory slot for all phases
-DVMB_VM_KERNEL(dvm_b200_vm_vector_res, kVmFlatThreads + 32, 2, true, true)
-DVMB_VM_KERNEL(dvm_b200_vm_vector_res_wide, kVmMaxThreads + 32, 1, true, true)
+DVMB_VM_KERNEL(dvm_b200_vm_vector_res, 256, 2, true, true, true)
+DVMB_VM_KERNEL(dvm_b200_vm_vector_res_wide, kVmMaxThreads + 32, 1, true, true, true)
 #undef DVMB_VM_KERNEL
 
 int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, uint32_t smem_bytes, void *stream) {
@@ -1069,14 +1115,24 @@ int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, uint32_t
   const bool narrow = threads <= kVmFlatThreads + 32;
   auto kernel = narrow ? dvm_b200_vm_vector : dvm_b200_vm_vector_wide;
   if (param.resident) {
-    kernel = narrow ? dvm_b200_vm_vector_res : dvm_b200_vm_vector_res_wide;
+    kernel = threads <= 256 ? dvm_b200_vm_vector_res : dvm_b200_vm_vector_res_wide;
   } else if (param.need_coords) {
     kernel = narrow ? dvm_b200_vm_vector_nd : dvm_b200_vm_vector_nd_wide;
   }
   // (the 160-thread CTAs run four per SM and need the 96-register build for that)
   static const bool no_r128 = getenv("DVM_B200_NO_R128") != nullptr;
-  if (!param.resident && threads > 160 && threads <= 256 && !no_r128)
-    kernel = param.need_coords ? dvm_b200_vm_vector_nd_r128 : dvm_b200_vm_vector_r128;
+  const bool r128 = !param.resident && threads > 160 && threads <= 256 && !no_r128;
+  if (r128) kernel = param.need_coords ? dvm_b200_vm_vector_nd_r128 : dvm_b200_vm_vector_r128;
+  if (param.rounds > 1 && !r128 && !param.resident) return -4;   // (the compiler only plans rounds for these kernels)
+  static const bool debug_launch = getenv("DVM_B200_DEBUG_LAUNCH") != nullptr;
+  if (debug_launch) {
+    // the launch configuration and what the driver says about its residency (a diagnostic; off by default)
+    int per_sm = 0, clusters = 0;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, static_cast<int>(threads), smem_bytes);
+    if (param.cluster > 1) cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg);
+    fprintf(stderr, "dvm_b200 launch: grid=%u threads=%u smem=%u cluster=%u resident=%u blocks/SM=%d active clusters=%d\n", grid,
+            threads, smem_bytes, param.cluster, param.resident, per_sm, clusters);
+  }
   const cudaError_t le = cudaLaunchKernelEx(&cfg, kernel, param, NextLaunchEpoch());
   if (le != cudaSuccess) return static_cast<int>(le);
   return static_cast<int>(cudaGetLastError());
