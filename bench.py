@@ -13,8 +13,10 @@ timed region is bracketed by a barrier + synchronize and the maximum over ranks 
 Output: one JSON line (rank 0) with the whole-job throughput in GB/s of algorithmic bytes, the roofline of
 the dominant kernel against the measured HBM peak, the end-to-end figure through the public API with host
 buffers, and the NumPy evaluation of the same graph on the host cores as the CPU baseline.
-``--impl reference`` times only that NumPy evaluation (the reference has no CPU executor of its own; its
-tests evaluate every graph with NumPy).
+``--impl reference`` runs the unmodified reference instead: its own CUDA backend (built from the reference tree into
+oracle/_ref) through its own Python module for c1-c3, with `value` = its kernels on resident inputs and `e2e` = its own
+host-buffer path (input / run / output per step); for c4/c5, which its GPU backend cannot run, and when no GPU or module
+is there, the NumPy evaluation of the same graph on the host cores (the evaluator of the reference's own tests).
 """
 import argparse
 import json
@@ -233,8 +235,21 @@ def reference_cuda(name, scale=1.0):
         return None
 
 
+def config_of(name, **extra):
+    """The `config` object of a bench line: both arms fill the same keys."""
+    cfg = {"workload": WORKLOADS[name], "algorithmic_bytes_per_step_per_gpu": ALGO_BYTES[name],
+           "l2": "inputs larger than L2 (no flush)", "sharding": "each rank runs a full-size shard (batch x N)", "scale": 1.0}
+    if name in ALGO_FLOPS:
+        cfg["algorithmic_flops_per_step_per_gpu"] = float(ALGO_FLOPS[name])
+    cfg.update(extra)
+    return cfg
+
+
 def run_reference_cuda(args, name):
-    """Reference arm on the reference's own CUDA backend: K launches of its kernels for the same graph and inputs."""
+    """Reference arm on the reference's own CUDA backend.  `value`: K runs of its kernels with the inputs resident
+    (its run() launches every kernel of the split graph and waits for the stream).  `e2e`: the same K steps through
+    its own host-buffer path - input() of every load, run(), output() of every store - which is what a user of its
+    Python module executes per call."""
     import torch
     got = reference_cuda(name)
     if got is None:
@@ -251,16 +266,30 @@ def run_reference_cuda(args, name):
     work = work_of(name, arrays, outs)
     v = work * args.steps / dt / unit_scale(name)
     lo, hi, mean = k.perf()
+    e2e_steps = max(2, min(args.steps, 5))
+    k.step_from_host()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        up, down = k.step_from_host()
+    torch.cuda.synchronize()
+    dt_e2e = time.perf_counter() - t0
     print(json.dumps({
         "impl": "reference", "metric": metric_of(name), "value": v, "unit": unit_of(name), "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": DTYPE[name], "data": "synthetic",
-        "config": {"workload": WORKLOADS[name], "note": "the reference's own CUDA backend (src/vm_gpu.cu compiled for sm_100a "
-                   "from the reference tree), same graph through its Python module, inputs resident; kernel time by its perf(): "
-                   "%.1f us mean" % mean},
-        "cpu_baseline": {"value": v, "unit": unit_of(name), "cores": 1, "kind": "reference",
-                         "sample": "the full workload on the GPU through the reference's CUDA backend"},
-        "e2e": {"value": v, "unit": unit_of(name), "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "config": config_of(name),
+        "note": "the reference's own CUDA backend (src/vm_gpu.cu compiled for sm_100a from the reference tree), same graph "
+                "through its Python module; value = inputs resident, wall clock around K run() calls; kernel time by its "
+                "perf(): %.1f us mean (device events)" % mean,
+        "kernel_us_by_perf": {"min": lo, "max": hi, "mean": mean},
+        "cpu_baseline": {"value": v, "unit": unit_of(name), "cores": 0, "kind": "reference",
+                         "sample": "not a CPU run: the full workload on the GPU through the reference's CUDA backend "
+                                   "(the reference has no CPU executor)"},
+        "e2e": {"value": work * e2e_steps / dt_e2e / unit_scale(name), "unit": unit_of(name), "h2d_bytes_per_step": int(up),
+                "d2h_bytes_per_step": int(down), "ms_per_step": dt_e2e / e2e_steps * 1e3,
+                "how": "the reference's own host-buffer path per step: input() of every load (device allocation + synchronous "
+                       "upload from pageable NumPy memory), run(), output() of every store"},
     }))
     return True
 
@@ -289,8 +318,9 @@ def run_reference(args, rank):
         "impl": "reference", "metric": metric_of(name), "value": v, "unit": unit_of(name), "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": DTYPE[name], "data": "synthetic",
-        "config": {"workload": WORKLOADS[name], "note": "NumPy evaluation of the same graph on host cores; the "
-                   "reference ships no CPU executor and its tests use NumPy as the evaluator"},
+        "config": config_of(name),
+        "note": "NumPy evaluation of the same graph on host cores (a bounded sample per step); the reference ships no CPU "
+                "executor and its tests use NumPy as the evaluator",
         "cpu_baseline": {"value": v, "unit": unit_of(name), "cores": cores, "kind": "port", "sample": what + " per step"},
         "e2e": {"value": v, "unit": unit_of(name), "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -504,50 +534,50 @@ def dynamic_shape_jit():
     return out
 
 
-def run_c5tp(args, rank, world, local_rank, dist):
-    """K-split tensor-parallel MatMul: every rank multiplies its K slice, the fp32 partial products are all-reduced
-    with NCCL, then the fused bias + GeLU kernel runs on the sum (strong scaling: the whole product is one unit)."""
-    import torch
+def init_product_comm(rank, world, dist):
+    """The library's own NCCL communicator for this process: rank 0 makes the rendezvous id, torch.distributed carries it."""
+    from dvm_b200 import frontend
+    box = [frontend.comm_unique_id() if rank == 0 else None]
+    if dist is not None:
+        dist.broadcast_object_list(box, src=0)
+    frontend.init_comm_with_id(rank, world, box[0])
+
+
+def c5tp_workload(rank, world, local_rank, scale=1.0):
+    """The K-split tensor-parallel MatMul as ONE kernel of the library: MatMul of the rank's K slice, all-reduce of the fp32
+    partial products (Kernel::AllReduce on the library's NCCL communicator), bias + GeLU, bf16 result."""
     import dvm_b200 as dvm
     from dvm_b200 import sharding, workloads as W
-    a, b, bias = make_inputs("c5", scale=args.scale)
+    a, b, bias = make_inputs("c5", scale=scale)
     m, n, kdim = a.shape[0], b.shape[1], a.shape[1]
     ar, br = sharding.ksplit_operands(a, b, rank, world)
     del a, b
-    partial = torch.empty((m, n), dtype=torch.float32, device="cuda")
-    k1 = dvm.PyKernel("mix", "dev", local_rank)
-    la, lb = k1.load(list(ar.shape), dvm.bfloat16), k1.load(list(br.shape), dvm.bfloat16)
-    k1.input(la, ar)
-    k1.input(lb, br)
-    s1 = k1.store(k1.cast(k1.matmul(la, lb, False, False), dvm.float32))
-    k1.bind_device(s1, partial.data_ptr(), partial.numel() * 4)
-    k1.codegen()
-    k2 = dvm.PyKernel("vector", "dev", local_rank)
-    lt, lbias = k2.load([m, n], dvm.float32), k2.load([n], dvm.bfloat16)
-    k2.bind_device(lt, partial.data_ptr(), partial.numel() * 4)
-    k2.input(lbias, bias)
-    s2 = k2.store(k2.cast(W.gelu_tanh(k2, k2.add(lt, k2.cast(lbias, dvm.float32))), dvm.bfloat16))
-    k2.codegen()
+    k = dvm.PyKernel("mix", "dev", local_rank)
+    la, lb, lbias = k.load(list(ar.shape), dvm.bfloat16), k.load(list(br.shape), dvm.bfloat16), k.load([n], dvm.bfloat16)
+    k.input(la, ar)
+    k.input(lb, br)
+    k.input(lbias, bias)
+    total = k.allreduce("sum", k.cast(k.matmul(la, lb, False, False), dvm.float32))
+    out = k.store(k.cast(W.gelu_tanh(k, k.add(total, k.cast(lbias, dvm.float32))), dvm.bfloat16))
+    k.codegen()
+    return k, out, (m, n, kdim)
 
-    def step():
-        k1.launch()
-        if dist is not None:
-            dist.all_reduce(partial)
-        k2.launch()
 
-    for _ in range(args.warmup):
-        step()
+def time_launches(k, steps, warmup, dist):
+    """Device milliseconds of `steps` launches of `k`, bracketed by barriers, maximum over the ranks."""
+    import torch
+    for _ in range(warmup):
+        k.launch()
     torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clocks:
-        e0.record()
-        for _ in range(args.steps):
-            step()
-        e1.record()
-        torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        k.launch()
+    e1.record()
+    torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
     ms = e0.elapsed_time(e1)
@@ -555,25 +585,65 @@ def run_c5tp(args, rank, world, local_rank, dist):
         t = torch.tensor([ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+    return ms
+
+
+def c5tp_record(args, rank, world, local_rank, dist, steps):
+    """Figures of the K-split variant on `world` ranks (strong scaling: the whole product is one unit)."""
+    k, out, (m, n, kdim) = c5tp_workload(rank, world, local_rank, args.scale)
+    ms = time_launches(k, steps, max(args.warmup, 3), dist)
+    stages = k.perf_stages(warmup=2, reps=5)
+    das = k.das()
+    names = [ln.split("(")[0] + ("(" + ln.split("(")[1].split(",")[0] + ")" if ln.startswith("cmain") else "")
+             for ln in das.splitlines() if ln[:5] in ("mmain", "vmain", "cmain", "amain")]
+    wire = sum(int(w) for w in __import__("re").findall(r"wire_bytes=(\d+)", das))
+    coll_us = sum(us for nm, us in zip(names, stages) if nm.startswith("cmain"))
     flops = 2.0 * m * n * kdim
-    lo, hi, mean = k1.perf(warmup=2, reps=10)
+    rec = {"ms_per_step": ms / steps, "value": flops * steps / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+           "scaling": "strong", "stages": names, "stage_us_serialised": [round(float(u), 1) for u in stages],
+           "collective_share_of_stage_time": coll_us / max(sum(stages), 1e-9), "wire_bytes_per_rank": wire,
+           "workspace_bytes_per_rank": m * n * 4}
+    k.release_io()
+    return rec
+
+
+def run_c5tp(args, rank, world, local_rank, dist):
+    """`--workload c5tp`: the K-split tensor-parallel MatMul as the headline line."""
+    init_product_comm(rank, world, dist)
+    with ClockSampler(local_rank) as clocks:
+        rec = c5tp_record(args, rank, world, local_rank, dist, args.steps)
     peak, peak_src = measured_peak("c5")
-    achieved = flops / world / (mean * 1e-6) / 1e12
+    per_gpu = rec["value"] / world
     if rank == 0:
         print(json.dumps({
-            "metric": "matmul_post_fusion_tflops", "value": flops * args.steps / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "metric": "matmul_post_fusion_tflops", "value": rec["value"], "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": rec["ms_per_step"],
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": DTYPE["c5"], "data": "synthetic",
-            "config": {"workload": WORKLOADS["c5"] + "; K split over %d ranks, fp32 partial products all-reduced with NCCL" % world,
-                       "l2": "inputs larger than L2 (no flush)", "exchange_bytes_per_rank": m * n * 4, "scale": args.scale},
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": peak_src, "kernel": "dvm_b200_mm_tcgen05_pair",
-                         "us_per_launch": {"min": lo, "mean": mean, "max": hi}},
-            "gpu_launches": args.steps * 2, "clocks": clocks.summary(),
+            "config": config_of("c5", workload=WORKLOADS["c5"] + "; K split over %d ranks, fp32 partial products combined over NCCL "
+                                "inside the kernel's plan" % world, sharding="K / N per rank, one product", scale=args.scale),
+            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s", "frac": per_gpu / peak,
+                         "traffic": None, "peak_source": peak_src, "kernel": "dvm_b200_mm_tcgen05_pair"},
+            "c5tp": rec, "gpu_launches": args.steps * len(rec["stages"]), "clocks": clocks.summary(),
         }))
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def strong_scaling_record(name, rank, world, local_rank, dist, steps=10):
+    """One BASELINE workload cut into `world` parts along its leading dimension (no collective): whole-job rate and the
+    per-GPU roofline fraction."""
+    wl = DeviceWorkload(name, seed_offset=1000 * rank, scale=1.0 / world)
+    outs = [np.empty(s.shape(), wl.k.output(s).dtype) for s in wl.stores]
+    work = work_of(name, wl.arrays, outs)
+    ms = time_launches(wl.k, steps, 3, dist)
+    peak, _ = measured_peak(name)
+    per_gpu = work * steps / (ms * 1e-3) / unit_scale(name)
+    rec = {"partition": {"c1": "rows", "c3": "tokens", "c4": "batch", "c5": "rows of A"}[name] + " / %d per GPU" % world,
+           "us_per_step": ms / steps * 1e3, "value": per_gpu * world, "unit": unit_of(name), "scaling": "strong",
+           "per_gpu_frac_of_measured_peak": per_gpu / peak}
+    wl.k.release_io()
+    return rec
 
 
 def main():
@@ -617,8 +687,10 @@ def main():
 
     with ClockSampler(local_rank) as clocks:
         ms = time_steps(wl, args.steps, args.warmup, dist)
-        # per-launch duration of the dominant kernel, device events on the launch stream
-        lo, hi, mean = wl.k.perf(warmup=3, reps=max(20, min(args.steps, 200)))
+        # per-launch duration of the dominant kernel, device events on the launch stream; the loop runs for about 1.5 s so
+        # that the clock sampler (one nvidia-smi query per ~0.1 s) sees the same kernel under load more than once
+        reps = int(min(10000, max(20, 1500.0 / max(ms / args.steps, 1e-3))))
+        lo, hi, mean = wl.k.perf(warmup=3, reps=reps)
     value = work * args.steps * world / (ms * 1e-3) / unit_scale(name)
     peak, peak_src = measured_peak(name)
     achieved = work / (mean * 1e-6) / unit_scale(name)
@@ -633,9 +705,7 @@ def main():
         "metric": metric_of(name), "value": value, "unit": unit_of(name), "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": DTYPE[name], "data": "synthetic",
-        "config": {"workload": WORKLOADS[name], "algorithmic_bytes_per_step_per_gpu": nbytes,
-                   "l2": "inputs larger than L2 (no flush)", "sharding": "each rank runs a full-size shard (batch x N)",
-                   "scale": args.scale},
+        "config": config_of(name, algorithmic_bytes_per_step_per_gpu=nbytes, scale=args.scale),
         "roofline": {"bound": "tensor" if tensor else "hbm", "achieved": achieved, "peak": peak, "unit": unit_of(name),
                      "frac": achieved / peak, "traffic": traffic, "traffic_source": "ncu capture (profiles/), bytes per launch",
                      "peak_source": peak_src, "kernel": KERNEL_NAME[name],
@@ -646,7 +716,7 @@ def main():
         "clocks": clocks.summary(),
     }
     if tensor:
-        line["config"]["algorithmic_flops_per_step_per_gpu"] = work
+        line["config"]["algorithmic_flops_per_step_per_gpu"] = float(work)
     if not args.no_extras:
         e2e_steps = max(3, min(args.steps, 10))
         dt, h2d, d2h = time_e2e(wl, e2e_steps, 1, dist)
@@ -684,6 +754,24 @@ def main():
                         pass
                 del got
             line["reference_cuda_backend"] = ref or "not available"
+    if dist is not None and not args.no_extras:
+        # what only exists on several GPUs: the K-split MatMul with its collective, and the BASELINE shapes cut N ways
+        try:
+            wl.k.release_io()
+        except Exception:
+            pass
+        multi = {}
+        try:
+            init_product_comm(rank, world, dist)
+            multi["c5tp"] = c5tp_record(args, rank, world, local_rank, dist, steps=10)
+        except Exception as e:   # the headline line must survive a failure here
+            multi["c5tp"] = {"error": str(e)[:300]}
+        for other in ("c1", "c3", "c4", "c5"):
+            try:
+                multi[other] = strong_scaling_record(other, rank, world, local_rank, dist)
+            except Exception as e:
+                multi[other] = {"error": str(e)[:300]}
+        line["multi_gpu"] = multi
     if rank == 0:
         print(json.dumps(line))
     if dist is not None:

@@ -56,6 +56,16 @@ SIGNATURES = {
     "dvm_reshape": (c_void_p, [c_void_p, c_void_p, c_void_p]),
     "dvm_copy": (c_void_p, [c_void_p, c_void_p]),
     "dvm_matmul": (c_void_p, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "dvm_comm_new": (c_void_p, []),
+    "dvm_comm_free": (None, [c_void_p]),
+    "dvm_comm_id_bytes": (c_size_t, []),
+    "dvm_comm_unique_id": (c_int, [c_void_p, c_size_t]),
+    "dvm_comm_init_rank": (c_int, [c_void_p, c_void_p, c_size_t, c_int, c_int]),
+    "dvm_comm_init_dummy": (c_int, [c_void_p, c_int, c_int]),
+    "dvm_comm_adopt": (c_int, [c_void_p, c_void_p]),
+    "dvm_comm_rank": (c_int, [c_void_p]),
+    "dvm_comm_size": (c_int, [c_void_p]),
+    "dvm_allreduce": (c_void_p, [c_void_p, c_int, c_void_p, c_void_p]),
     "dvm_sequence_add": (c_int, [c_void_p, c_int, ctypes.c_uint32]),
     "dvm_parallel_add": (c_int, [c_void_p, c_int, ctypes.c_uint32, c_size_t]),
     "dvm_spec_next": (c_int, [c_void_p]),
@@ -90,6 +100,8 @@ SIGNATURES = {
     "dvm_rt_host_free": (c_int, [c_void_p]),
     "dvm_perf": (c_int, [c_void_p, c_int, c_int, c_void_p, ctypes.POINTER(ctypes.c_float),
                          ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_float)]),
+    "dvm_perf_stages": (c_int, [c_void_p, c_int, c_int, c_void_p, ctypes.POINTER(ctypes.c_float), c_size_t,
+                                ctypes.POINTER(c_size_t)]),
 }
 
 _lib = None

@@ -20,6 +20,7 @@ SOURCES = [
     "vcompile.cc",
     "vkernel.cc",
     "partition.cc",
+    "comm.cc",
     "runtime.cu",
     "capi.cu",
     "vm_vector.cu",
@@ -85,7 +86,7 @@ def build(force=False, verbose=False):
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             list(ex.map(run, jobs))
     if jobs or not os.path.exists(LIB_PATH):
-        run([_nvcc(), "-shared", "-o", LIB_PATH] + objs + ["-lcudart"])
+        run([_nvcc(), "-shared", "-o", LIB_PATH] + objs + ["-lcudart", "-ldl"])
     return LIB_PATH
 
 

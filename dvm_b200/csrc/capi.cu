@@ -11,6 +11,7 @@
 
 #include "../../include/dvm.h"
 #include "../../include/dvm_c.h"
+#include "comm.h"
 #include "graph.h"
 #include "runtime.h"
 #include "vm_launch.h"
@@ -27,6 +28,10 @@ struct dvm_int_array {
 
 struct dvm_scalar {
   dvm::ScalarRef ref;
+};
+
+struct dvm_comm : dvm::Comm {
+  dvm::Communicator *&impl() { return comm_; }   // (comm_ is the protected member of dvm::Comm)
 };
 
 struct dvm_kernel {
@@ -179,6 +184,38 @@ dvm_object *dvm_reshape(dvm_kernel *k, dvm_object *input, dvm_int_array *shape) 
 dvm_object *dvm_copy(dvm_kernel *k, dvm_object *input) { return DVM_OBJ_GUARD(k->kernel.Copy(N(input))); }
 dvm_object *dvm_matmul(dvm_kernel *k, dvm_object *lhs, dvm_object *rhs, int trans_a, int trans_b, dvm_object *bias) {
   return DVM_OBJ_GUARD(k->kernel.MatMul(N(lhs), N(rhs), trans_a != 0, trans_b != 0, bias ? N(bias) : nullptr));
+}
+
+dvm_comm *dvm_comm_new(void) { return new dvm_comm(); }
+void dvm_comm_free(dvm_comm *c) { delete c; }
+size_t dvm_comm_id_bytes(void) { return dvmb::kCommIdBytes; }
+int dvm_comm_unique_id(void *id, size_t bytes) {
+  if (bytes < dvmb::kCommIdBytes) {
+    g_error = "the id buffer is smaller than dvm_comm_id_bytes()";
+    return 1;
+  }
+  g_error.clear();
+  return dvmb::CommUniqueId(id, &g_error);
+}
+int dvm_comm_init_rank(dvm_comm *c, const void *id, size_t bytes, int rank, int size) {
+  if (bytes < dvmb::kCommIdBytes || rank < 0 || rank >= size) {
+    g_error = "dvm_comm_init_rank: bad id size or rank";
+    return 1;
+  }
+  g_error.clear();
+  if (c->impl() == nullptr) c->impl() = new dvm::Communicator();
+  return dvmb::CommInitRank(c->impl(), id, rank, size, &g_error);
+}
+int dvm_comm_init_dummy(dvm_comm *c, int rank, int size) {
+  return Guard([&]() { return c->Init(rank, size, dvm::Comm::kDummy) ? 0 : 1; }, 1);
+}
+int dvm_comm_adopt(dvm_comm *c, void *nccl_comm) {
+  return Guard([&]() { c->Init(nccl_comm); return 0; }, 1);
+}
+int dvm_comm_rank(const dvm_comm *c) { return c->GetImpl() ? c->GetImpl()->rank : 0; }
+int dvm_comm_size(const dvm_comm *c) { return c->GetImpl() ? c->GetImpl()->size : 1; }
+dvm_object *dvm_allreduce(dvm_kernel *k, int reduce_type, dvm_object *input, dvm_comm *c) {
+  return DVM_OBJ_GUARD(k->kernel.AllReduce(reduce_type, N(input), c));
 }
 
 int dvm_sequence_add(dvm_kernel *k, int kernel_type, uint32_t flags) {
@@ -377,6 +414,42 @@ int dvm_perf(dvm_kernel *k, int warmup, int reps, void *stream, float *min_us, f
       if (min_us) *min_us = lo;
       if (max_us) *max_us = hi;
       if (mean_us) *mean_us = reps > 0 ? sum / reps : 0.0f;
+      return 0;
+    },
+    1);
+}
+
+// Per-stage device times of one kernel: every launch / collective of the plan bracketed by its own pair of events.
+int dvm_perf_stages(dvm_kernel *k, int warmup, int reps, void *stream, float *mean_us, size_t capacity, size_t *stages) {
+  return Guard(
+    [&]() {
+      dvm::VKernel *vk = k->kernel.GetImpl();
+      if (vk == nullptr || !vk->compiled_) dvm::DvmException("dvm_perf_stages needs a generated kernel");
+      const size_t n = vk->stages_.size();
+      if (stages) *stages = n;
+      if (n > capacity) dvm::DvmException("dvm_perf_stages: the output array is too small");
+      cudaStream_t s = static_cast<cudaStream_t>(stream);
+      std::vector<cudaEvent_t> ev(n + 1);
+      for (auto &e : ev)
+        if (CudaCheck(cudaEventCreate(&e), "event")) return 1;
+      std::vector<double> sum(n, 0.0);
+      for (int it = 0; it < warmup + reps; ++it) {
+        cudaEventRecord(ev[0], s);
+        for (size_t i = 0; i < n; ++i) {
+          int rc = vk->LaunchStage(i, stream);
+          if (rc != 0) return rc;
+          cudaEventRecord(ev[i + 1], s);
+        }
+        if (CudaCheck(cudaEventSynchronize(ev[n]), "event sync")) return 1;
+        if (it < warmup) continue;
+        for (size_t i = 0; i < n; ++i) {
+          float ms = 0.0f;
+          cudaEventElapsedTime(&ms, ev[i], ev[i + 1]);
+          sum[i] += ms * 1000.0;
+        }
+      }
+      for (auto &e : ev) cudaEventDestroy(e);
+      for (size_t i = 0; i < n; ++i) mean_us[i] = reps > 0 ? static_cast<float>(sum[i] / reps) : 0.0f;
       return 0;
     },
     1);

@@ -9,6 +9,7 @@
 #include <stdexcept>
 #include <string>
 
+#include "comm.h"
 #include "graph.h"
 #include "numeric.h"
 #include "runtime.h"
@@ -29,25 +30,7 @@ BFloat16::BFloat16(int32_t v) : value_(F32ToBF16Bits(static_cast<float>(v))) {}
 BFloat16::operator float() const { return BF16BitsToF32(value_); }
 BFloat16::operator int32_t() const { return static_cast<int32_t>(BF16BitsToF32(value_)); }
 
-// ---- Comm / Config --------------------------------------------------------------------------------
-class Communicator {
- public:
-  int rank = 0, size = 1, type = Comm::kDummy;
-  void *nccl = nullptr;
-};
-Comm::~Comm() { delete comm_; }
-bool Comm::Init(int rank_id, int rank_size, int comm_type, const uint32_t *) {
-  if (comm_ == nullptr) comm_ = new Communicator();
-  comm_->rank = rank_id;
-  comm_->size = rank_size;
-  comm_->type = comm_type;
-  return true;
-}
-void Comm::Init(void *nccl_comm) {
-  if (comm_ == nullptr) comm_ = new Communicator();
-  comm_->nccl = nccl_comm;
-}
-
+// ---- Config (Comm lives in comm.cc) --------------------------------------------------------------
 namespace {
 class ConfigImpl : public Config {
  public:
@@ -590,7 +573,18 @@ NDObject *Kernel::MatMul(NDObject *lhs, NDObject *rhs, bool trans_a, bool trans_
 NDObject *Kernel::GroupedMatMul(NDObject *, NDObject *, bool, bool, NDObject *, NDObject *, GmmSplitType, GmmListType) {
   Unsupported("GroupedMatMul");
 }
-NDObject *Kernel::_AllReduce(int, NDObject *, const Comm *) { Unsupported("AllReduce inside a vector kernel"); }
+// ref: Kernel::_AllReduce, src/dvm.cc:1646-1655 (AllReduceOp, src/ops_c.h:124-132): the value of `input` combined over
+// the ranks of `comm`.  Sum and max / min on fp32, fp16, bf16 and int32 tensors.
+NDObject *Kernel::_AllReduce(int op_type, NDObject *input, const Comm *comm) {
+  if (op_type < 0 || op_type >= kReduceTypeEnd) DvmException("invalid all-reduce type");
+  if (comm == nullptr || comm->GetImpl() == nullptr) DvmException("AllReduce needs an initialised Comm");
+  if (input->dtype == kBool || input->dtype == kInt64) DvmException("AllReduce of bool / int64 tensors is not supported");
+  auto n = Impl(this)->NewNode(N_ALLREDUCE, input->dtype);
+  n->sub = static_cast<uint8_t>(op_type);
+  n->in[0] = input;
+  n->comm = comm->GetImpl();
+  return n;
+}
 NDObject *Kernel::AllGather(NDObject *, const Comm *) { Unsupported("AllGather"); }
 NDObject *Kernel::AllGatherV2(NDObject *, const Comm *) { Unsupported("AllGatherV2"); }
 NDObject *Kernel::ReduceScatter(NDObject *, const Comm *) { Unsupported("ReduceScatter"); }

@@ -51,6 +51,7 @@ enum NodeKind : uint8_t {
   N_COPY,
   N_REDUCE,     // sub = ReduceType
   N_MATMUL,
+  N_ALLREDUCE,  // sub = ReduceType; the value of in[0] combined over the ranks of `comm`
 };
 
 // Scalar-operand arithmetic kinds (the reference's BinaryScalarOp opcodes ADDS/MULS/DIVS/SDIV/MAXS/MINS,
@@ -81,6 +82,8 @@ class NDObject {
   // temporary in the kernel's workspace (`ws_off` >= 0, bytes from the workspace base)
   NDObject *origin = nullptr;
   int64_t ws_off = -1;
+  int64_t addr_off = 0;               // bytes added to the address above (a rank's row block of a tensor)
+  const Communicator *comm = nullptr; // N_ALLREDUCE: the communicator (borrowed from the caller's Comm)
   // results of Normalize()
   Shape shape;
   IntArrayRef out_ref;                // view of `shape` handed out by Kernel::GetShape
@@ -126,13 +129,27 @@ struct AttnStage {
   uint64_t algo_bytes = 0, flops = 0;
 };
 
-enum StageKind : uint8_t { STAGE_VECTOR = 0, STAGE_MATMUL, STAGE_ATTENTION };
+// One collective on the launch stream (comm.h): all-reduce, or the reduce-scatter / all-gather halves it is split
+// into when the ops behind it can run on a rank's own row block.
+struct CollStage {
+  uint32_t kind = 0;                       // dvmb::CollKind
+  int reduce_type = 0, dtype = 0;
+  const Communicator *comm = nullptr;
+  NDObject *send = nullptr, *recv = nullptr;   // nodes whose addresses feed the call
+  int64_t send_off = 0, recv_off = 0;      // bytes added to them
+  uint64_t count = 0;                      // elements per NCCL's definition of the call
+  uint64_t send_ptr = 0, recv_ptr = 0;     // bound addresses
+  uint64_t wire_bytes = 0;                 // bytes this rank sends over the links
+};
+
+enum StageKind : uint8_t { STAGE_VECTOR = 0, STAGE_MATMUL, STAGE_ATTENTION, STAGE_COLLECTIVE };
 
 struct Stage {
   StageKind kind = STAGE_VECTOR;
   VectorStage vec;
   MatMulStage mm;
   AttnStage attn;
+  CollStage coll;
 };
 
 class VKernel {
@@ -147,6 +164,7 @@ class VKernel {
   size_t Compile();   // build stages for the current shapes; returns workspace bytes
   void Bind(const RelocEntry *relocs, size_t n, void *workspace);
   int Launch(void *stream);
+  int LaunchStage(size_t index, void *stream);   // one launch (or collective) of the plan, for per-stage timing
 
   const char *Dump();
   const char *DumpR();

@@ -114,6 +114,7 @@ void InferShape(NDObject *n) {
       n->shape = o;
       break;
     }
+    case N_ALLREDUCE: n->shape = n->in[0]->shape; break;
     case N_MATMUL: {
       const Shape &a = n->in[0]->shape, &b = n->in[1]->shape;
       if (a.rank < 2 || b.rank < 2) Fail(n, "matmul operands need rank >= 2");

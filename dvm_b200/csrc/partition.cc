@@ -9,11 +9,13 @@
 // takes every following elementwise op of its own shape into its epilogue, and the
 // MatMul -> softmax -> MatMul pattern becomes one attention launch.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <unordered_map>
 #include <unordered_set>
 
+#include "comm.h"
 #include "graph.h"
 #include "runtime.h"
 
@@ -553,6 +555,184 @@ struct Planner {
     return true;
   }
 
+  // ---- collectives -----------------------------------------------------------------------------------------
+  void PushCollective(uint32_t kind, const NDObject *n, NDObject *send, int64_t send_off, NDObject *recv, int64_t recv_off,
+                      uint64_t count, uint64_t wire_bytes) {
+    auto st = std::make_unique<Stage>();
+    st->kind = STAGE_COLLECTIVE;
+    CollStage &c = st->coll;
+    c.kind = kind;
+    c.reduce_type = n->kind == N_ALLREDUCE ? n->sub : 0;
+    c.dtype = static_cast<int>(send->dtype);
+    c.comm = n->comm;
+    c.send = send;
+    c.recv = recv;
+    c.send_off = send_off;
+    c.recv_off = recv_off;
+    c.count = count;
+    c.wire_bytes = wire_bytes;
+    vk->stages_.push_back(std::move(st));
+  }
+
+  // True when `x` (not yet computed) can be recomputed inside a row-block stage: an elementwise chain without a row axis
+  // (or with a row extent of 1) over scalars and tensors in memory.  Collects the chain in `extra`.
+  bool PullRowFree(const NDObject *x, std::unordered_set<const NDObject *> &extra) {
+    while (x->kind == N_BROADCAST) x = x->in[0];
+    if (x->kind == N_BROADCAST_S || InMemory(x) || extra.count(x)) return true;
+    if (done.count(x) || !IsElementwise(x->kind)) return false;
+    const Shape &xs = x->shape;
+    if (!(xs.rank < 2 || xs.d[xs.rank - 2] == 1)) return false;
+    for (int j = 0; j < 3; ++j)
+      if (x->in[j] && !PullRowFree(x->in[j], extra)) return false;
+    extra.insert(x);
+    return true;
+  }
+
+  // All transitive users of `root`, in program order, when they form a tail that can run on a row block: elementwise ops
+  // and stores only, every other operand a scalar, a row-free value (no row axis or a row extent of 1: a tensor in memory
+  // or an elementwise chain over such, which the stage then computes itself) or a full [M, N] tensor in memory.  Empty
+  // when the tail does not qualify.
+  std::vector<NDObject *> RowBlockTail(const NDObject *root) {
+    const Shape &rs = root->shape;
+    std::unordered_set<const NDObject *> in_tail{root}, extra;
+    for (size_t i = pos.at(root) + 1; i < ops.size(); ++i) {
+      NDObject *v = ops[i];
+      bool touches = false;
+      for (int j = 0; j < 3; ++j)
+        if (v->in[j] && in_tail.count(v->in[j])) touches = true;
+      if (!touches) continue;
+      if (done.count(v)) return {};
+      if (v->kind == N_STORE) {
+        if (!(v->shape == rs)) return {};
+      } else if (!IsElementwise(v->kind) || !(v->shape == rs)) {
+        return {};
+      }
+      for (int j = 0; j < 3; ++j) {
+        const NDObject *x = v->in[j];
+        if (!x || in_tail.count(x)) continue;
+        while (x->kind == N_BROADCAST) x = x->in[0];
+        if (x->kind == N_BROADCAST_S) continue;
+        if (InMemory(x)) {
+          const Shape &xs = x->shape;
+          const bool row_free = xs.rank < 2 || xs.d[xs.rank - 2] == 1;
+          if (!row_free && !(xs == rs)) return {};
+        } else if (!PullRowFree(x, extra)) {
+          return {};
+        }
+      }
+      in_tail.insert(v);
+    }
+    std::vector<NDObject *> nodes;
+    bool stores = false;
+    for (size_t i = 0; i < ops.size(); ++i) {
+      NDObject *v = ops[i];
+      if (v == root || (!in_tail.count(v) && !extra.count(v))) continue;
+      nodes.push_back(v);
+      stores |= v->kind == N_STORE && in_tail.count(v);
+    }
+    // (every user of a tail value is in the tail by construction; a tail that stores nothing is not worth a special plan)
+    return stores ? nodes : std::vector<NDObject *>();
+  }
+
+  // Clone of load-like node `x` (a Load or a value in memory) restricted to the rank's row block.
+  void ToRowBlock(NDObject *c, int64_t rows_all, int64_t rows, int rank_id) {
+    Shape &s = c->shape;
+    if (s.rank < 2 || s.d[s.rank - 2] != rows_all) return;
+    int64_t row_bytes = ItemSize(c->dtype);
+    for (int i = s.rank - 1; i < s.rank; ++i) row_bytes *= s.d[i];
+    s.d[s.rank - 2] = rows;
+    if (c->kind == N_LOAD || c->kind == N_STORE) c->addr_off += rank_id * rows * row_bytes;
+  }
+
+  // AllReduce(sum) of an [M, N] value that sits in a workspace temporary of its own, followed by a row-independent tail:
+  // reduce-scatter in place (each rank ends up with the sum of its own M / size rows), the tail on that row block only,
+  // all-gather of every stored result.  Same results on every rank as all-reduce + tail everywhere, with the second half of
+  // the exchange in the (narrower) result type and the tail's work divided by the number of ranks (src/ops_c.cc:366-645 is
+  // the reference's fused MatMul + all-reduce this stands in for).
+  bool TryShardedTail(NDObject *n) {
+    static const bool off = getenv("DVM_B200_NO_SHARDED_TAIL") != nullptr;
+    const Communicator *comm = n->comm;
+    const Shape &rs = n->shape;
+    if (off || comm->size <= 1 || n->sub != kSum || rs.rank != 2 || rs.d[0] % comm->size != 0 || rs.numel() == 0) return false;
+    NDObject *v = n->in[0];
+    auto where = mem.find(v);
+    if (where == mem.end() || where->second->ws_off < 0) return false;   // (a caller's buffer must not be overwritten)
+    auto uv = users.find(v);
+    if (uv == users.end() || uv->second.size() != 1) return false;
+    std::vector<NDObject *> tail = RowBlockTail(n);
+    if (tail.empty()) return false;
+    const int64_t rows_all = rs.d[0], rows = rows_all / comm->size;
+    const int64_t blk_elems = rows * rs.d[1];
+    const int64_t isz = ItemSize(n->dtype);
+    // 1. reduce-scatter, in place on the temporary
+    NDObject *w = MemLoad(v);
+    PushCollective(dvmb::COLL_REDUCE_SCATTER, n, w, 0, w, comm->rank * blk_elems * isz, static_cast<uint64_t>(blk_elems),
+                   static_cast<uint64_t>(blk_elems * isz) * (comm->size - 1));
+    // 2. the tail on the rank's rows
+    Build b;
+    NDObject *src = MemLoad(v);
+    src->shape = rs;
+    b.clone[n] = src;
+    b.list.push_back(src);
+    std::unordered_set<const NDObject *> area(tail.begin(), tail.end());
+    area.insert(n);
+    const size_t first_clone = vk->synth_.size() - 1;
+    CloneArea(b, tail, area, true);
+    for (size_t i = first_clone; i < vk->synth_.size(); ++i) ToRowBlock(vk->synth_[i], rows_all, rows, comm->rank);
+    auto st = std::make_unique<Stage>();
+    st->kind = STAGE_VECTOR;
+    std::string why;
+    if (!CompileVectorStage(b.list, &st->vec, &why)) {
+      std::string msg = "cannot compile the row-block tail of an all-reduce: " + why;
+      DvmException(msg.c_str());
+    }
+    vk->stages_.push_back(std::move(st));
+    // 3. all-gather of every result, in place on the caller's buffer
+    for (auto t : tail) {
+      // (a recomputed row-free chain that something else reads as well stays open for the stage that needs it)
+      bool inside = true;
+      auto ut = users.find(t);
+      if (ut != users.end())
+        for (auto u : ut->second) inside &= area.count(u) != 0;
+      if (inside) done.insert(t);
+      if (t->kind != N_STORE) continue;
+      NDObject *whole = Synth(t);
+      whole->origin = t;
+      whole->in[0] = nullptr;
+      const int64_t osz = ItemSize(t->dtype);
+      PushCollective(dvmb::COLL_ALL_GATHER, n, whole, comm->rank * blk_elems * osz, whole, 0, static_cast<uint64_t>(blk_elems),
+                     static_cast<uint64_t>(blk_elems * osz) * (comm->size - 1));
+      vk->stages_.back()->coll.dtype = static_cast<int>(t->dtype);
+    }
+    done.insert(n);
+    return true;
+  }
+
+  void PlaceAllReduce(NDObject *n) {
+    NDObject *v = n->in[0];
+    if (!InMemory(v)) {
+      if (v->kind == N_BROADCAST || v->kind == N_BROADCAST_S) {
+        Materialize(v);
+      } else {
+        CloseCur();   // the open area stores v to the workspace: this node reads it from outside the area
+      }
+      if (!InMemory(v)) DvmException("AllReduce of a value that is not in memory");
+    } else {
+      CloseCur();
+    }
+    if (TryShardedTail(n)) return;
+    // general form: all ranks receive the whole combined tensor in a workspace temporary
+    NDObject *src = MemLoad(v);
+    NDObject *dst = SynthLoad(n, n->shape);
+    dst->ws_off = static_cast<int64_t>(AllocWs(n));
+    const uint64_t count = static_cast<uint64_t>(n->shape.numel());
+    const uint64_t bytes = count * ItemSize(n->dtype);
+    PushCollective(dvmb::COLL_ALL_REDUCE, n, src, 0, dst, 0, count,
+                   n->comm->size > 1 ? 2 * bytes * (n->comm->size - 1) / n->comm->size : 0);
+    mem[n] = dst;
+    done.insert(n);
+  }
+
   // ---- driver ------------------------------------------------------------------------------------------------
   void Run() {
     // Sub-kernels of a kSequence / kParallel kernel (Kernel::SequenceAdd / ParallelAdd; the reference's SequenceKernel
@@ -628,6 +808,7 @@ struct Planner {
         case N_MATMUL:
           if (!TryAttention(n)) PlaceMatMul(n);
           break;
+        case N_ALLREDUCE: PlaceAllReduce(n); break;
         default: AddVector(n); break;
       }
     }

@@ -1194,8 +1194,10 @@ struct Compiler {
   void Run(MatMulStage *mm = nullptr) {
     for (size_t i = 0; i < ops.size(); ++i) ops[i]->cidx = static_cast<int>(i);
     info.assign(ops.size(), Info());
-    for (auto n : ops)
+    for (auto n : ops) {
       if (n->kind == N_MATMUL) throw Fail{"MatMul inside a vector stage"};
+      if (n->kind == N_ALLREDUCE) throw Fail{"a collective inside a vector stage"};
+    }
     AlignAxes();
     Classify();
     MarkExact();

@@ -5,6 +5,7 @@
 #include <cstring>
 #include <string>
 
+#include "comm.h"
 #include "graph.h"
 #include "runtime.h"
 #include "vm_launch.h"
@@ -25,9 +26,13 @@ void VKernel::ClearStages() {
 
 // Device address of a load/store node: a workspace temporary, a clone of a user's node, or the node itself.
 static void *AddrOf(const NDObject *n, void *workspace) {
-  if (n->ws_off >= 0) return workspace ? static_cast<char *>(workspace) + n->ws_off : nullptr;
-  if (n->origin) return n->origin->addr;
-  return n->addr;
+  void *base = n->addr;
+  if (n->ws_off >= 0) {
+    base = workspace ? static_cast<char *>(workspace) + n->ws_off : nullptr;
+  } else if (n->origin) {
+    base = n->origin->addr;
+  }
+  return base ? static_cast<char *>(base) + n->addr_off : nullptr;
 }
 
 NDObject *VKernel::NewNode(NodeKind kind, DataType dtype) {
@@ -75,7 +80,7 @@ size_t VKernel::Compile() {
   }
   bool has_matmul = false, has_empty = false, stacked = false;
   for (auto n : ops) {
-    has_matmul |= n->kind == N_MATMUL;
+    has_matmul |= n->kind == N_MATMUL || n->kind == N_ALLREDUCE;   // (anything that needs the stage planner)
     has_empty |= n->shape.numel() == 0;   // the planner drops empty tensors and keeps what still has elements
     stacked |= n->sub_kernel != ops.front()->sub_kernel;   // kSequence / kParallel: every sub-kernel gets launches of its own
   }
@@ -105,6 +110,13 @@ void VKernel::Bind(const RelocEntry *relocs, size_t n, void *workspace) {
       mm.param.bias_ptr = mm.bias ? reinterpret_cast<uint64_t>(AddrOf(mm.bias, workspace)) : 0;
       for (size_t s = 0; s < mm.slot_obj.size(); ++s)
         if (mm.slot_obj[s]) mm.param.tensor[s].ptr = reinterpret_cast<uint64_t>(AddrOf(mm.slot_obj[s], workspace));
+      continue;
+    }
+    if (stp->kind == STAGE_COLLECTIVE) {
+      CollStage &co = stp->coll;
+      void *sp = AddrOf(co.send, workspace), *rp = AddrOf(co.recv, workspace);
+      co.send_ptr = sp ? reinterpret_cast<uint64_t>(sp) + co.send_off : 0;
+      co.recv_ptr = rp ? reinterpret_cast<uint64_t>(rp) + co.recv_off : 0;
       continue;
     }
     if (stp->kind == STAGE_ATTENTION) {
@@ -139,34 +151,50 @@ void VKernel::Bind(const RelocEntry *relocs, size_t n, void *workspace) {
 int VKernel::Launch(void *stream) {
   if (!compiled_) DvmException("Launch before CodeGen");
   dvmb::Runtime::Get().EnsureInit();
-  for (auto &stp : stages_) {
-    if (stp->kind == STAGE_MATMUL) {
-      MatMulStage &mm = stp->mm;
-      if (mm.idle) continue;
-      if (mm.param.a_ptr == 0 || mm.param.b_ptr == 0) DvmException("Launch with an unbound tensor address");
-      for (size_t s = 0; s < mm.slot_obj.size(); ++s)
-        if (mm.slot_obj[s] && mm.param.tensor[s].ptr == 0) DvmException("Launch with an unbound tensor address");
-      int err = dvmb::LaunchMatMul(mm.param, stream);
-      if (err != 0) return err;
-      continue;
-    }
-    if (stp->kind == STAGE_ATTENTION) {
-      AttnStage &at = stp->attn;
-      if (at.idle) continue;
-      if (!at.param.q_ptr || !at.param.k_ptr || !at.param.v_ptr || !at.param.o_ptr)
-        DvmException("Launch with an unbound tensor address");
-      int err = dvmb::LaunchAttention(at.param, stream);
-      if (err != 0) return err;
-      continue;
-    }
-    VectorStage &st = stp->vec;
-    if (st.idle) continue;
-    for (size_t s = 0; s < st.slot_obj.size(); ++s)
-      if (st.param.tensor[s].ptr == 0) DvmException("Launch with an unbound tensor address");
-    int err = dvmb::LaunchVector(st.param, st.grid, st.threads, st.smem_bytes, stream);
+  for (size_t i = 0; i < stages_.size(); ++i) {
+    int err = LaunchStage(i, stream);
     if (err != 0) return err;
   }
   return 0;
+}
+
+int VKernel::LaunchStage(size_t index, void *stream) {
+  if (!compiled_ || index >= stages_.size()) DvmException("LaunchStage: no such stage");
+  dvmb::Runtime::Get().EnsureInit();
+  {
+    auto &stp = stages_[index];
+    if (stp->kind == STAGE_MATMUL) {
+      MatMulStage &mm = stp->mm;
+      if (mm.idle) return 0;
+      if (mm.param.a_ptr == 0 || mm.param.b_ptr == 0) DvmException("Launch with an unbound tensor address");
+      for (size_t s = 0; s < mm.slot_obj.size(); ++s)
+        if (mm.slot_obj[s] && mm.param.tensor[s].ptr == 0) DvmException("Launch with an unbound tensor address");
+      return dvmb::LaunchMatMul(mm.param, stream);
+    }
+    if (stp->kind == STAGE_COLLECTIVE) {
+      CollStage &co = stp->coll;
+      if (co.count == 0) return 0;
+      if (co.send_ptr == 0 || co.recv_ptr == 0) DvmException("Launch with an unbound tensor address");
+      std::string err;
+      int rc = dvmb::RunCollective(co.comm, static_cast<dvmb::CollKind>(co.kind), co.reduce_type, co.dtype,
+                                   reinterpret_cast<const void *>(co.send_ptr), reinterpret_cast<void *>(co.recv_ptr), co.count,
+                                   stream, &err);
+      if (rc != 0) DvmException(("collective failed: " + err).c_str());
+      return 0;
+    }
+    if (stp->kind == STAGE_ATTENTION) {
+      AttnStage &at = stp->attn;
+      if (at.idle) return 0;
+      if (!at.param.q_ptr || !at.param.k_ptr || !at.param.v_ptr || !at.param.o_ptr)
+        DvmException("Launch with an unbound tensor address");
+      return dvmb::LaunchAttention(at.param, stream);
+    }
+    VectorStage &st = stp->vec;
+    if (st.idle) return 0;
+    for (size_t s = 0; s < st.slot_obj.size(); ++s)
+      if (st.param.tensor[s].ptr == 0) DvmException("Launch with an unbound tensor address");
+    return dvmb::LaunchVector(st.param, st.grid, st.threads, st.smem_bytes, stream);
+  }
 }
 
 // ---- text dumps -------------------------------------------------------------------------------------
@@ -191,6 +219,7 @@ static const char *KindName(const NDObject *n) {
     case N_RESHAPE: return "Reshape";
     case N_COPY: return "Copy";
     case N_REDUCE: return red[n->sub];
+    case N_ALLREDUCE: return n->sub == kSum ? "AllReduceSum" : (n->sub == kMax ? "AllReduceMax" : "AllReduceMin");
     default: return "MatMul";
   }
 }
@@ -247,6 +276,17 @@ const char *VKernel::Das() {
   for (auto &st : stages_) {
     if (st->kind == STAGE_MATMUL) {
       text_ += DisassembleEpilogue(st->mm);
+    } else if (st->kind == STAGE_COLLECTIVE) {
+      const CollStage &c = st->coll;
+      static const char *names[] = {"all_reduce", "reduce_scatter", "all_gather"};
+      static const char *ops[] = {"sum", "max", "min"};
+      char buf[320];
+      snprintf(buf, sizeof(buf), "cmain.nccl(%s%s%s, %s, count=%llu, rank=%d of %d, wire_bytes=%llu) {\n  %s 0x%llx, load(0x%llx)\n}\n",
+               names[c.kind], c.kind == dvmb::COLL_ALL_GATHER ? "" : ".", c.kind == dvmb::COLL_ALL_GATHER ? "" : ops[c.reduce_type],
+               DTypeName(static_cast<DataType>(c.dtype)), static_cast<unsigned long long>(c.count), c.comm ? c.comm->rank : 0,
+               c.comm ? c.comm->size : 1, static_cast<unsigned long long>(c.wire_bytes), names[c.kind],
+               static_cast<unsigned long long>(c.recv_ptr), static_cast<unsigned long long>(c.send_ptr));
+      text_ += buf;
     } else if (st->kind == STAGE_ATTENTION) {
       const dvmb::AttnParam &a = st->attn.param;
       char buf[256];
@@ -272,6 +312,9 @@ const char *VKernel::Inspect() {
       snprintf(buf, sizeof(buf), "stage %d: matmul flops=%llu algorithmic_bytes=%llu%s\n", i++,
                static_cast<unsigned long long>(stp->mm.flops), static_cast<unsigned long long>(stp->mm.algo_bytes),
                stp->mm.idle ? " (idle: zero-size result)" : "");
+    } else if (stp->kind == STAGE_COLLECTIVE) {
+      snprintf(buf, sizeof(buf), "stage %d: collective kind=%u count=%llu wire_bytes=%llu\n", i++, stp->coll.kind,
+               static_cast<unsigned long long>(stp->coll.count), static_cast<unsigned long long>(stp->coll.wire_bytes));
     } else if (stp->kind == STAGE_ATTENTION) {
       snprintf(buf, sizeof(buf), "stage %d: attention flops=%llu algorithmic_bytes=%llu\n", i++,
                static_cast<unsigned long long>(stp->attn.flops), static_cast<unsigned long long>(stp->attn.algo_bytes));

@@ -352,8 +352,77 @@ class _ExternalBuf:
         self.ptr = None
 
 
+class _ProcessComm:
+    """The process-wide communicator of the Python runner (g_mpc.comm, src/pybind_api.cc:675-687)."""
+    handle = None
+    rank = 0
+    size = 1
+
+
+def comm_unique_id():
+    """A fresh rendezvous id (bytes): rank 0 makes it, every rank passes the same bytes to init_comm_with_id()."""
+    lib = _capi.load()
+    n = lib.dvm_comm_id_bytes()
+    buf = ctypes.create_string_buffer(n)
+    check_rc(lib.dvm_comm_unique_id(buf, n), "comm_unique_id")
+    return buf.raw
+
+
+def init_comm_with_id(rank_id, rank_size, id_bytes):
+    """Create this process's NCCL communicator from a rendezvous id the ranks have shared by their own means
+    (collective over all ranks; the device this rank launches on must be current)."""
+    lib = _capi.load()
+    if _ProcessComm.handle is None:
+        _ProcessComm.handle = check_ptr(lib.dvm_comm_new(), "comm")
+    check_rc(lib.dvm_comm_init_rank(_ProcessComm.handle, id_bytes, len(id_bytes), int(rank_id), int(rank_size)), "init_comm")
+    _ProcessComm.rank, _ProcessComm.size = int(rank_id), int(rank_size)
+
+
 class PyKernel(Kernel):
     """Kernel plus a device runner (RtKernelPy, src/pybind_api.h:27-119)."""
+
+    @staticmethod
+    def init_comm(rank_id, rank_size, comm_type="memory"):
+        """RtKernelPy::InitComm (src/pybind_api.cc:675-687).  "dummy" records rank and size only (plans and listings);
+        any other type creates an NCCL communicator, the ranks meeting through the file named by DVM_B200_COMM_ID_FILE
+        (rank 0 writes the rendezvous id there)."""
+        lib = _capi.load()
+        if _ProcessComm.handle is None:
+            _ProcessComm.handle = check_ptr(lib.dvm_comm_new(), "comm")
+        if comm_type == "dummy":
+            check_rc(lib.dvm_comm_init_dummy(_ProcessComm.handle, int(rank_id), int(rank_size)), "init_comm")
+        else:
+            import os
+            path = os.environ.get("DVM_B200_COMM_ID_FILE")
+            if int(rank_size) > 1 and not path:
+                raise DvmError("init_comm: set DVM_B200_COMM_ID_FILE to a path all ranks share, or use init_comm_with_id()")
+            if int(rank_id) == 0 or int(rank_size) == 1:
+                uid = comm_unique_id()
+                if int(rank_size) > 1:
+                    with open(path + ".tmp", "wb") as f:
+                        f.write(uid)
+                    os.replace(path + ".tmp", path)
+            else:
+                import time
+                deadline = time.time() + 60
+                while not os.path.exists(path):
+                    if time.time() > deadline:
+                        raise DvmError("init_comm: no rendezvous id appeared at %s" % path)
+                    time.sleep(0.01)
+                with open(path, "rb") as f:
+                    uid = f.read()
+            init_comm_with_id(rank_id, rank_size, uid)
+            return
+        _ProcessComm.rank, _ProcessComm.size = int(rank_id), int(rank_size)
+
+    def allreduce(self, type, input):
+        """RtKernelPy::AllReduce (src/pybind_api.cc:562-572): "sum" or "max" over the ranks of the process's communicator."""
+        codes = {"sum": 0, "max": 1}
+        if type not in codes:
+            raise ValueError("Unsupported AllReduce type: " + str(type))
+        if _ProcessComm.handle is None:
+            raise DvmError("allreduce before init_comm()")
+        return self._obj(self._lib.dvm_allreduce(self._k, codes[type], input._h, _ProcessComm.handle), "allreduce")
 
     def __init__(self, ker_type="", run_type="dev", dev_id=0):
         ktype, flags = parse_kernel_type(ker_type)
@@ -503,6 +572,14 @@ class PyKernel(Kernel):
         check_rc(self._lib.dvm_perf(self._k, warmup, reps, None, ctypes.byref(lo), ctypes.byref(hi),
                                     ctypes.byref(mean)), "perf")
         return (lo.value, hi.value, mean.value)
+
+    def perf_stages(self, warmup=1, reps=10):
+        """Mean device microseconds of every launch / collective of the plan, in the order of das()."""
+        cap = 64
+        arr = (ctypes.c_float * cap)()
+        n = ctypes.c_size_t(0)
+        check_rc(self._lib.dvm_perf_stages(self._k, warmup, reps, None, arr, cap, ctypes.byref(n)), "perf_stages")
+        return [arr[i] for i in range(n.value)]
 
     def jit_us(self):
         return float(self._lib.dvm_last_jit_us(self._k))

@@ -82,6 +82,26 @@ DVM_C_API dvm_object *dvm_copy(dvm_kernel *k, dvm_object *input);               
 DVM_C_API dvm_object *dvm_matmul(dvm_kernel *k, dvm_object *lhs, dvm_object *rhs, int trans_a, int trans_b,
                                  dvm_object *bias);                                           /* dvm.h:509 */
 
+/* ---- collectives (Comm, include/dvm.h:219-231; Kernel::AllReduce, dvm.h:531) ----
+ * The communicator is NCCL's; it is bound at run time, so a host without NCCL can still use everything else.
+ * Rank 0 makes a rendezvous id (dvm_comm_id_bytes() bytes) and hands it to the other ranks by any means the job has
+ * (a torch.distributed / MPI broadcast, a file); then every rank calls dvm_comm_init_rank with the device it will launch
+ * on current.  dvm_comm_adopt uses an ncclComm_t the caller owns (Comm::Init(void *), dvm.h:228).  A dummy communicator
+ * (Comm::kDummy) carries rank and size for planning and listings and cannot launch. */
+typedef struct dvm_comm dvm_comm;
+DVM_C_API dvm_comm *dvm_comm_new(void);
+DVM_C_API void dvm_comm_free(dvm_comm *c);
+DVM_C_API size_t dvm_comm_id_bytes(void);
+DVM_C_API int dvm_comm_unique_id(void *id, size_t bytes);
+DVM_C_API int dvm_comm_init_rank(dvm_comm *c, const void *id, size_t bytes, int rank, int size);
+DVM_C_API int dvm_comm_init_dummy(dvm_comm *c, int rank, int size);
+DVM_C_API int dvm_comm_adopt(dvm_comm *c, void *nccl_comm);
+DVM_C_API int dvm_comm_rank(const dvm_comm *c);
+DVM_C_API int dvm_comm_size(const dvm_comm *c);
+/* the value of `input` combined (reduce_type: 0 sum, 1 max, 2 min) over the ranks of `c` (KernelPy::AllReduce,
+ * include/dvm_py.h; python/dvm/_dvm_py.pyi:166) */
+DVM_C_API dvm_object *dvm_allreduce(dvm_kernel *k, int reduce_type, dvm_object *input, dvm_comm *c);
+
 /* ---- stacked kernels and marks ---- */
 /* start the next stage of a kSequence kernel (Kernel::SequenceAdd, dvm.h:559; KernelPy::SeqAdd, include/dvm_py.h) */
 DVM_C_API int dvm_sequence_add(dvm_kernel *k, int kernel_type, uint32_t flags);
@@ -161,6 +181,12 @@ DVM_C_API int dvm_rt_host_free(void *p);
  * (RtKernelPy::Perf, src/pybind_api.cc:751-767: 1 warm-up + 10 timed runs, min/max/mean in us). */
 DVM_C_API int dvm_perf(dvm_kernel *k, int warmup, int reps, void *stream, float *min_us, float *max_us,
                        float *mean_us);
+
+/* No counterpart in the reference.  Like dvm_perf(), but with one pair of device events around every launch or
+ * collective of the kernel's plan (the order of dvm_das()): mean_us[i] is the mean device time of stage i over `reps`
+ * runs; *stages receives the number of stages, which must not exceed `capacity`. */
+DVM_C_API int dvm_perf_stages(dvm_kernel *k, int warmup, int reps, void *stream, float *mean_us, size_t capacity,
+                              size_t *stages);
 
 #ifdef __cplusplus
 }

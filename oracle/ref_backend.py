@@ -32,6 +32,7 @@ class RefKernel:
         self.m = module()
         self.k = self.m.PyKernel(ker_type, "dev", int(os.environ.get("DEVICE_ID", "0")))
         self._stores = []
+        self._inputs = []   # (load op, host array in the form the reference's input() takes)
 
     def _dt(self, code):
         return getattr(self.m.DataType, _NAMES[int(code)])
@@ -52,6 +53,7 @@ class RefKernel:
             array = array.astype(np.float16)
         op = self.k.load(list(array.shape), self._dt(code))
         self.k.input(op, array)
+        self._inputs.append((op, array))
         return op
 
     def cast(self, x, dtype):
@@ -75,6 +77,19 @@ class RefKernel:
 
     def perf(self):
         return self.k.perf()
+
+    def step_from_host(self):
+        """One step of the reference's own host-buffer path: input() of every load (its device allocation and
+        synchronous upload, src/pybind_api.cc:217-223, 819-842), run() (launch and stream wait, :689-701) and output()
+        of every store (download, :856-865).  Returns (bytes uploaded, bytes downloaded)."""
+        up = down = 0
+        for op, array in self._inputs:
+            self.k.input(op, array)
+            up += array.nbytes
+        self.k.run()
+        for s in self._stores:
+            down += self.k.output(s).nbytes
+        return up, down
 
     def __getattr__(self, name):   # every other builder method goes straight to the reference
         return getattr(self.k, name)
