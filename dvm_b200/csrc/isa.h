@@ -192,6 +192,11 @@ enum UopHandler : uint32_t {
   UH_LDSIGM_LAST = UH_LDSIGM_FIRST + 2,
   UH_LDMUL2_FIRST,                                  // acc <- (acc * ring operand arg16) * ring operand imm32 (one type; b keeps
   UH_LDMUL2_LAST = UH_LDMUL2_FIRST + 2,             //   the second): first + FusedType
+  // a whole normalisation body: ((x - s0) * s1) * s2 + s3 over ring operand x (arg16 = ring offset / 16; imm32 = the four
+  // scalar registers, four bits each, and the result tensor's slot in bits 16-19), stored as a vector of the operand's
+  // own type; with UA_LOOP the handler runs every remaining full round of the chunk
+  UH_LDNORMST_FIRST,                                // first + FusedType
+  UH_LDNORMST_LAST = UH_LDNORMST_FIRST + 2,
   UH_COUNT
 };
 enum FusedOp : uint32_t { FO_ADD = 0, FO_SUB = 1, FO_MUL = 2 };
@@ -200,7 +205,8 @@ static_assert(UH_COUNT <= 256, "handler ids are one byte");
 enum UopDest : uint32_t { UD_B = 0, UD_ACC = 1 };
 enum UopAux : uint32_t {
   UA_CMP_SREG = 0x08,  // scalar compares: the scalar is register arg16, else imm32
-  UA_LOOP = 0x40,      // load + reduce forms that are a body's only micro-op: the handler runs all remaining full rounds of the chunk
+  UA_LOOP = 0x40,      // load + reduce and load + normalise + store forms that are a body's only micro-op: the handler runs all
+                       // remaining full rounds of the chunk
   UA_LAST = 0x80       // vector stores and full-chunk reduce accumulations (plain or fused): the body ends here (no UH_END
                        // word follows, which saves its dispatch)
 };

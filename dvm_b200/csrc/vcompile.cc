@@ -1386,7 +1386,24 @@ bool LowerStageAs(VectorStage *st, bool dual) {
       i += take;
       fused_away += take - 1;
     }
-    n = o;
+    // second pass: a normalisation whose result goes straight into a vector store of the operand's own type
+    uint32_t o2 = begin;
+    for (uint32_t i = begin; i < o; ++i) {
+      const uint32_t h = DVMB_UH(P.code[i]);
+      if (h >= UH_LDNORM_FIRST && h <= UH_LDNORM_LAST && i + 1 < o) {
+        static const uint32_t store_of[] = {UH_ST_F32, UH_ST_F16, UH_ST_BF16};   // by FusedType
+        const uint64_t st_op = P.code[i + 1];
+        if (DVMB_UH(st_op) == store_of[h - UH_LDNORM_FIRST] && DVMB_UARG(st_op) < 16u) {
+          P.code[o2++] = MakeUop(UH_LDNORMST_FIRST + (h - UH_LDNORM_FIRST), 0, DVMB_UARG(P.code[i]),
+                                 (DVMB_UIMM(P.code[i]) & 0xffffu) | (DVMB_UARG(st_op) << 16));
+          ++i;
+          ++fused_away;
+          continue;
+        }
+      }
+      P.code[o2++] = P.code[i];
+    }
+    n = o2;
   };
   // every BODY is lowered twice (full chunks, any chunk); PRO sections once
   for (uint32_t pass = 0; pass <= 3 * P.num_body; ++pass) {
@@ -1477,11 +1494,13 @@ bool LowerStageAs(VectorStage *st, bool dual) {
           const uint32_t last = n > P.sec[sidx] ? DVMB_UH(P.code[n - 1]) : static_cast<uint32_t>(UH_END);
           const bool ends_body = (last >= UH_ST_F32 && last <= UH_ST_BF16) || (last >= UH_RACCF_FIRST && last <= UH_RACCF_LAST) ||
                                  (last >= UH_LDSUM_FIRST && last <= UH_LDSUM_LAST) || last == UH_SQRSUM0 || last == UH_SQRSUM1 ||
-                                 (last >= UH_LDVAR_FIRST && last <= UH_LDVAR_LAST);
+                                 (last >= UH_LDVAR_FIRST && last <= UH_LDVAR_LAST) ||
+                                 (last >= UH_LDNORMST_FIRST && last <= UH_LDNORMST_LAST);
           if (ends_body && !no_tail && !overflow) {
             P.code[n - 1] |= static_cast<uint64_t>(UA_LAST) << 8;
             // a body that is one load + reduce micro-op runs all full rounds of a chunk in a single dispatch
-            const bool load_reduce = (last >= UH_LDSUM_FIRST && last <= UH_LDSUM_LAST) || (last >= UH_LDVAR_FIRST && last <= UH_LDVAR_LAST);
+            const bool load_reduce = (last >= UH_LDSUM_FIRST && last <= UH_LDSUM_LAST) || (last >= UH_LDVAR_FIRST && last <= UH_LDVAR_LAST) ||
+                                     (last >= UH_LDNORMST_FIRST && last <= UH_LDNORMST_LAST);
             if (load_reduce && n - P.sec[sidx] == 1 && P.rounds > 1) P.code[n - 1] |= static_cast<uint64_t>(UA_LOOP) << 8;
             ++fused_away;
             break;
@@ -1735,6 +1754,9 @@ std::string DisassembleStage(const VectorStage &st) {
       case UH_MULR_ADDR: return "Mul.s+Add.s";
       case UH_MULR_MULR: return "Mul.s+Mul.s";
       case UH_MULR_MULR_ADDR: return "Mul.s+Mul.s+Add.s";
+      case UH_LDNORMST_FIRST + FT_F32: return "lda.fp32+Sub.s+Mul.s+Mul.s+Add.s+st.fp32";
+      case UH_LDNORMST_FIRST + FT_F16: return "lda.fp16+Sub.s+Mul.s+Mul.s+Add.s+st.fp16";
+      case UH_LDNORMST_FIRST + FT_BF16: return "lda.bf16+Sub.s+Mul.s+Mul.s+Add.s+st.bf16";
       case UH_SIGMOID_FAST: return "SigmoidFast";
       default: return "u" + std::to_string(h);
     }

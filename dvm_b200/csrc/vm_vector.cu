@@ -672,7 +672,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
         uint32_t pc_saddr = code_saddr + 8u * (full_tile ? body_pc : (lane_active ? body_pc_any : P.n_code - 1u));
         uint32_t ulo, uhi, nlo, nhi;   // the current micro-op and the next one, already on its way
         lds64x2(pc_saddr, ulo, uhi);
-        const uint32_t rnd_begin = rnd;
+        uint32_t rnd_begin = rnd;
         for (;; ulo = nlo, uhi = nhi) {
           const uint32_t uh = ulo & 0xffu;
           const uint32_t aux = (ulo >> 8) & 0xffu;
@@ -777,6 +777,60 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
               asm volatile(DV_LN(DV_NORM_LANE, "")::"r"(s0_), "r"(s1_), "r"(s2_), "r"(s3_));
             })
             DV_LDX_TYPES(UH_LDSIGM_FIRST, "va", asm volatile(DV_LN(DV_SIGM_LANE, ""));)
+            // a whole normalisation body in one micro-op: ring operand -> ((x - s0) * s1) * s2 + s3 -> vector store in the
+            // operand's own type, for every remaining full round of the chunk when it is the body's only micro-op
+#define DV_STV32(P0, GS)                                                                                              \
+  asm volatile("st.global.v4.b32 [%0], {va0,va1,va2,va3};\n\tst.global.v4.b32 [%1], {va4,va5,va6,va7};\n\t"            \
+               "st.global.v4.b32 [%2], {va8,va9,va10,va11};\n\tst.global.v4.b32 [%3], {va12,va13,va14,va15};" ::"l"(P0), \
+               "l"(P0 + GS), "l"(P0 + 2u * GS), "l"(P0 + 3u * GS)                                                      \
+               : "memory");
+#define DV_STV16(CVT, P0, GS)                                                                                 \
+  asm volatile("{\n\t.reg .b32 t0, t1;\n\t"                                                                   \
+               CVT " t0, va1, va0;\n\t" CVT " t1, va3, va2;\n\tst.global.v2.b32 [%0], {t0,t1};\n\t"           \
+               CVT " t0, va5, va4;\n\t" CVT " t1, va7, va6;\n\tst.global.v2.b32 [%1], {t0,t1};\n\t"           \
+               CVT " t0, va9, va8;\n\t" CVT " t1, va11, va10;\n\tst.global.v2.b32 [%2], {t0,t1};\n\t"         \
+               CVT " t0, va13, va12;\n\t" CVT " t1, va15, va14;\n\tst.global.v2.b32 [%3], {t0,t1};\n\t}" ::"l"(P0), \
+               "l"(P0 + GS), "l"(P0 + 2u * GS), "l"(P0 + 3u * GS)                                            \
+               : "memory");
+#define DV_LDNORMST_CASE(H, MACRO, SHL, ELEM, STORE)                                                          \
+  case H: {                                                                                                 \
+    const TensorDesc &td = tdesc[(uhi >> 16) & 0xfu];                                                       \
+    const uint32_t s0_ = lds32(sreg_addr(uhi & 0xfu)), s1_ = lds32(sreg_addr((uhi >> 4) & 0xfu));           \
+    const uint32_t s2_ = lds32(sreg_addr((uhi >> 8) & 0xfu)), s3_ = lds32(sreg_addr((uhi >> 12) & 0xfu));   \
+    uint32_t a0 = stage_saddr + (arg << 4) + (SHL(pos.in_chunk0));                                          \
+    const uint32_t gs = SHL(pos.gstep), ge = pos.gstep;                                                     \
+    const bool by_coords = kCoords && td.mode != AM_DENSE;                                                  \
+    ELEM *const base = reinterpret_cast<ELEM *>(td.ptr) + kept_offset(td, pos.k);                           \
+    ELEM *p0 = base + (by_coords ? enum_offset(td, cc) + lane4 : pos.e_start + pos.in_chunk0);              \
+    for (;;) {                                                                                              \
+      MACRO("va", a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)                                                   \
+      asm volatile(DV_LN(DV_NORM_LANE, "")::"r"(s0_), "r"(s1_), "r"(s2_), "r"(s3_));                        \
+      STORE                                                                                                 \
+      if (!kRounds || !(aux & UA_LOOP) || rnd + 1u >= n_full) break;                                        \
+      ++rnd;                                                                                                \
+      a0 += SHL(P.round_elems);                                                                             \
+      if (by_coords) {                                                                                      \
+        /* the coordinates move on by one round; the code behind the body adds the last one */              \
+        rnd_begin = rnd;                                                                                    \
+        cc[3] += P.round_elems;                                                                             \
+        _Pragma("unroll") for (int j = kMaxEnum - 1; j > 0; --j) while (cc[j] >= P.enum_size[j]) {          \
+          cc[j] -= P.enum_size[j];                                                                          \
+          cc[j - 1] += 1u;                                                                                  \
+        }                                                                                                   \
+        p0 = base + enum_offset(td, cc) + lane4;                                                            \
+      } else {                                                                                              \
+        p0 += P.round_elems;                                                                                \
+      }                                                                                                     \
+    }                                                                                                       \
+    if (aux & UA_LAST) goto body_done;                                                                      \
+    continue;                                                                                               \
+  }
+            DV_LDNORMST_CASE(UH_LDNORMST_FIRST + FT_F32, DV_LDR32, DV_SHL2, uint32_t, DV_STV32(p0, ge))
+            DV_LDNORMST_CASE(UH_LDNORMST_FIRST + FT_F16, DV_LDR_F16, DV_SHL1, unsigned short, DV_STV16("cvt.rn.f16x2.f32", p0, ge))
+            DV_LDNORMST_CASE(UH_LDNORMST_FIRST + FT_BF16, DV_LDR_BF16, DV_SHL1, unsigned short, DV_STV16("cvt.rn.bf16x2.f32", p0, ge))
+#undef DV_LDNORMST_CASE
+#undef DV_STV16
+#undef DV_STV32
 #define DV_LDMUL2_CASE(H, MACRO, SHL)                                                                          \
   case H: {                                                                                                 \
     const uint32_t o0 = stage_saddr + (SHL(pos.in_chunk0)), gs = SHL(pos.gstep);                            \
@@ -1124,6 +1178,32 @@ int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, uint32_t
   const bool r128 = !param.resident && threads > 160 && threads <= 256 && !no_r128;
   if (r128) kernel = param.need_coords ? dvm_b200_vm_vector_nd_r128 : dvm_b200_vm_vector_r128;
   if (param.rounds > 1 && !r128 && !param.resident) return -4;   // (the compiler only plans rounds for these kernels)
+  if (param.cluster > 1) {
+    // A persistent grid of clusters must be resident as a whole: a cluster that has to wait for another one to leave
+    // would start its share of the groups only then.  The driver knows how many clusters of this shape fit (fewer than
+    // SMs x CTAs per SM / cluster size, since a cluster may not straddle GPCs); the answer is cached per launch shape.
+    struct Fit { const void *fn; uint32_t threads, smem, cluster; int dev, clusters; };
+    static Fit cache[16];
+    static int cached = 0;
+    int fit = -1;
+    for (int i = 0; i < cached; ++i)
+      if (cache[i].fn == reinterpret_cast<const void *>(kernel) && cache[i].threads == threads && cache[i].smem == smem_bytes &&
+          cache[i].cluster == param.cluster && cache[i].dev == dev)
+        fit = cache[i].clusters;
+    if (fit < 0) {
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        n = static_cast<int>(grid / param.cluster);
+      }
+      fit = n;
+      if (cached < 16) cache[cached++] = Fit{reinterpret_cast<const void *>(kernel), threads, smem_bytes, param.cluster, dev, n};
+    }
+    if (grid / param.cluster > static_cast<uint32_t>(fit)) {
+      grid = static_cast<uint32_t>(fit) * param.cluster;
+      cfg.gridDim = dim3(grid, 1, 1);
+    }
+  }
   static const bool debug_launch = getenv("DVM_B200_DEBUG_LAUNCH") != nullptr;
   if (debug_launch) {
     // the launch configuration and what the driver says about its residency (a diagnostic; off by default)
