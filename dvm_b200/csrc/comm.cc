@@ -42,11 +42,20 @@ NcclApi *Api(std::string *err) {
   static NcclApi api;
   static std::once_flag once;
   std::call_once(once, []() {
-    // a copy that the process already holds (a framework's) is found first: same SONAME
+    // A copy that the process already holds (a framework's own build) is used first: two NCCL builds in one process
+    // clash, because the loader resolves a later library's dependency on "libnccl.so.2" to whichever copy came first.
+    // For the same reason a process that will load such a framework later must load it before its first communicator
+    // (the Python front-end does that for torch).  DVM_B200_NCCL_LIB names a specific library file.
     const char *names[] = {"libnccl.so.2", "libnccl.so"};
     for (const char *n : names) {
-      api.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+      api.handle = dlopen(n, RTLD_NOW | RTLD_NOLOAD);
       if (api.handle) break;
+    }
+    if (!api.handle)
+      if (const char *path = getenv("DVM_B200_NCCL_LIB")) api.handle = dlopen(path, RTLD_NOW | RTLD_LOCAL);
+    for (const char *n : names) {
+      if (api.handle) break;
+      api.handle = dlopen(n, RTLD_NOW | RTLD_LOCAL);
     }
     if (!api.handle) {
       api.why = std::string("NCCL is not available: ") + dlerror();

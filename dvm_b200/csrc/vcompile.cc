@@ -960,8 +960,10 @@ struct Compiler {
           ++n_in;
         }
       uint32_t r = 1;
-      // (one producer lane per staged tensor and round; a stage of at most 32 KB leaves room for three of them)
-      while (r < 8 && 2 * r <= P.chunks && 2 * r * std::max(n_in, 1u) <= 32 && 2 * r * round_bytes <= 32u * 1024u) r *= 2;
+      // (one producer lane per staged tensor and round; two stages of up to 50 KB fit a CTA that shares its SM with
+      // another one; measured on 256 groups of 64 x 6272 B, three passes: 165 us with 1 round per chunk, 133 with 2, 115
+      // with 4, 107 with 8)
+      while (r < 8 && 2 * r <= P.chunks && 2 * r * std::max(n_in, 1u) <= 32 && 2 * r * round_bytes <= 50u * 1024u) r *= 2;
       if (const char *env = getenv("DVM_B200_ROUNDS")) r = std::max(1, std::min(32 / static_cast<int>(std::max(n_in, 1u)), atoi(env)));
       P.rounds = r;
       P.chunk_elems = r * P.round_elems;
@@ -1124,6 +1126,23 @@ struct Compiler {
         P.sets = sets;
         stages = sets * cpc;
       }
+    }
+    // ---- a long group shared by a cluster, streaming: with every CTA on a group of its own, all groups are in flight at
+    // once and a pass over a group has left the L2 by the time the next pass comes back to it.  A cluster of CTAs per
+    // group (each takes a run of the group's chunks, reductions combined through distributed shared memory) cuts the bytes
+    // in flight by the cluster size, so that the later passes of a multi-pass graph are served by the L2.
+    if (!P.resident && P.mode == VM_GROUP && !packed && P.rounds > 1 && stage_bytes != 0 && num_body >= 2) {
+      const uint64_t group_bytes = static_cast<uint64_t>(P.chunks) * stage_bytes;
+      const uint64_t slots = std::min<uint64_t>(static_cast<uint64_t>(K), 2ull * sms);
+      // (measured on 256 groups of 400 KB, three passes: 115 us with one CTA per group, 123 us with clusters of two, 147 us
+      // with four - the CTAs of a cluster wait for their slowest member at every reduction - so the split is opt-in)
+      (void)group_bytes;
+      (void)slots;
+      uint32_t cl = 1;
+      if (const char *env = getenv("DVM_B200_CLUSTER")) cl = static_cast<uint32_t>(std::max(1, std::min(8, atoi(env))));
+      while (cl > 1 && P.chunks < 2 * cl) cl /= 2;
+      P.cluster = cl;
+      P.cpc = (P.chunks + cl - 1) / cl;
     }
     P.stage_bytes = stage_bytes;
     P.num_stages = stages;

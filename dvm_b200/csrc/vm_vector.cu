@@ -267,8 +267,8 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
   const bool ring = P.stage_bytes != 0;
   const uint32_t ngb = flat ? 1u : (P.num_groups + P.groups_per_cta - 1) / P.groups_per_cta;
   // CTAs of a cluster share a group: CTA `rank` of unit `blockIdx.x / cluster` owns chunks [rank * cpc, ...)
-  // (only the resident instantiation carries the cluster / slot bookkeeping: the streaming one keeps its registers)
-  const uint32_t cluster = kResident ? P.cluster : 1u, rank = cluster > 1 ? blockIdx.x % cluster : 0u;
+  // (only the instantiations with the larger register budget carry the cluster bookkeeping)
+  const uint32_t cluster = (kResident || kRounds) ? P.cluster : 1u, rank = cluster > 1 ? blockIdx.x % cluster : 0u;
   const bool resident = kResident;
   const uint32_t gb_begin = flat ? 0u : blockIdx.x / cluster, gb_step = flat ? 1u : gridDim.x / cluster;
   const uint32_t ch_begin = flat ? blockIdx.x : rank * P.cpc, ch_step = flat ? gridDim.x : 1u;
@@ -779,17 +779,18 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
             DV_LDX_TYPES(UH_LDSIGM_FIRST, "va", asm volatile(DV_LN(DV_SIGM_LANE, ""));)
             // a whole normalisation body in one micro-op: ring operand -> ((x - s0) * s1) * s2 + s3 -> vector store in the
             // operand's own type, for every remaining full round of the chunk when it is the body's only micro-op
+#define DVMB_ST "st.global"   /* (a cache-streaming form, st.global.cs, measured the same on a three-pass normalisation) */
 #define DV_STV32(P0, GS)                                                                                              \
-  asm volatile("st.global.v4.b32 [%0], {va0,va1,va2,va3};\n\tst.global.v4.b32 [%1], {va4,va5,va6,va7};\n\t"            \
-               "st.global.v4.b32 [%2], {va8,va9,va10,va11};\n\tst.global.v4.b32 [%3], {va12,va13,va14,va15};" ::"l"(P0), \
+  asm volatile(DVMB_ST ".v4.b32 [%0], {va0,va1,va2,va3};\n\t" DVMB_ST ".v4.b32 [%1], {va4,va5,va6,va7};\n\t"            \
+               DVMB_ST ".v4.b32 [%2], {va8,va9,va10,va11};\n\t" DVMB_ST ".v4.b32 [%3], {va12,va13,va14,va15};" ::"l"(P0), \
                "l"(P0 + GS), "l"(P0 + 2u * GS), "l"(P0 + 3u * GS)                                                      \
                : "memory");
 #define DV_STV16(CVT, P0, GS)                                                                                 \
   asm volatile("{\n\t.reg .b32 t0, t1;\n\t"                                                                   \
-               CVT " t0, va1, va0;\n\t" CVT " t1, va3, va2;\n\tst.global.v2.b32 [%0], {t0,t1};\n\t"           \
-               CVT " t0, va5, va4;\n\t" CVT " t1, va7, va6;\n\tst.global.v2.b32 [%1], {t0,t1};\n\t"           \
-               CVT " t0, va9, va8;\n\t" CVT " t1, va11, va10;\n\tst.global.v2.b32 [%2], {t0,t1};\n\t"         \
-               CVT " t0, va13, va12;\n\t" CVT " t1, va15, va14;\n\tst.global.v2.b32 [%3], {t0,t1};\n\t}" ::"l"(P0), \
+               CVT " t0, va1, va0;\n\t" CVT " t1, va3, va2;\n\t" DVMB_ST ".v2.b32 [%0], {t0,t1};\n\t"           \
+               CVT " t0, va5, va4;\n\t" CVT " t1, va7, va6;\n\t" DVMB_ST ".v2.b32 [%1], {t0,t1};\n\t"           \
+               CVT " t0, va9, va8;\n\t" CVT " t1, va11, va10;\n\t" DVMB_ST ".v2.b32 [%2], {t0,t1};\n\t"         \
+               CVT " t0, va13, va12;\n\t" CVT " t1, va15, va14;\n\t" DVMB_ST ".v2.b32 [%3], {t0,t1};\n\t}" ::"l"(P0), \
                "l"(P0 + GS), "l"(P0 + 2u * GS), "l"(P0 + 3u * GS)                                            \
                : "memory");
 #define DV_LDNORMST_CASE(H, MACRO, SHL, ELEM, STORE)                                                          \
@@ -831,6 +832,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
 #undef DV_LDNORMST_CASE
 #undef DV_STV16
 #undef DV_STV32
+#undef DVMB_ST
 #define DV_LDMUL2_CASE(H, MACRO, SHL)                                                                          \
   case H: {                                                                                                 \
     const uint32_t o0 = stage_saddr + (SHL(pos.in_chunk0)), gs = SHL(pos.gstep);                            \
@@ -1177,7 +1179,7 @@ int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, uint32_t
   static const bool no_r128 = getenv("DVM_B200_NO_R128") != nullptr;
   const bool r128 = !param.resident && threads > 160 && threads <= 256 && !no_r128;
   if (r128) kernel = param.need_coords ? dvm_b200_vm_vector_nd_r128 : dvm_b200_vm_vector_r128;
-  if (param.rounds > 1 && !r128 && !param.resident) return -4;   // (the compiler only plans rounds for these kernels)
+  if ((param.rounds > 1 || param.cluster > 1) && !r128 && !param.resident) return -4;   // (the compiler only plans rounds and clusters for these kernels)
   if (param.cluster > 1) {
     // A persistent grid of clusters must be resident as a whole: a cluster that has to wait for another one to leave
     // would start its share of the groups only then.  The driver knows how many clusters of this shape fit (fewer than

@@ -359,8 +359,19 @@ class _ProcessComm:
     size = 1
 
 
+def _framework_nccl_first():
+    """Two NCCL builds in one process clash (the loader hands the copy that came first to every later library that asks
+    for "libnccl.so.2").  torch ships its own build, so when torch is installed it is imported before this library binds
+    NCCL; the library then finds and uses the copy torch loaded."""
+    import importlib.util
+    import sys
+    if "torch" not in sys.modules and importlib.util.find_spec("torch") is not None:
+        import torch  # noqa: F401
+
+
 def comm_unique_id():
     """A fresh rendezvous id (bytes): rank 0 makes it, every rank passes the same bytes to init_comm_with_id()."""
+    _framework_nccl_first()
     lib = _capi.load()
     n = lib.dvm_comm_id_bytes()
     buf = ctypes.create_string_buffer(n)
@@ -371,6 +382,7 @@ def comm_unique_id():
 def init_comm_with_id(rank_id, rank_size, id_bytes):
     """Create this process's NCCL communicator from a rendezvous id the ranks have shared by their own means
     (collective over all ranks; the device this rank launches on must be current)."""
+    _framework_nccl_first()
     lib = _capi.load()
     if _ProcessComm.handle is None:
         _ProcessComm.handle = check_ptr(lib.dvm_comm_new(), "comm")

@@ -116,8 +116,8 @@ def test_peephole_fuses_frequent_neighbours():
     assert bodies[0][0] == "lda.fp16+ReduceSum.p0"
     assert bodies[1][0] == "lda.fp16+Sub.s+Sqr+ReduceSum.p1"
     assert bodies[2][0] == "lda.fp16+Sub.s+Mul.s+Mul.s+Add.s+st.fp16"
-    # every body is one micro-op that runs all four rounds of a chunk in one dispatch
-    assert "rounds=4" in k.das()
+    # every body is one micro-op that runs all eight rounds of a chunk in one dispatch
+    assert "rounds=8" in k.das()
     assert all(len(body) == 9 and " ".join(body).endswith("(ends the body, loops over the chunk's rounds)") for body in bodies)
 
     k = dvm.PyKernel("vector", "das", 0)
