@@ -497,8 +497,12 @@ def device_summary(name, reps=30):
     work = work_of(name, wl.arrays, outs)
     lo, hi, mean = wl.k.perf(warmup=3, reps=reps)
     peak, _ = measured_peak(name)
+    # K launches back to back between two events (what the headline workload's figure is, too); `us_single` is one event
+    # pair per launch, which adds the launch latency
+    single = mean
+    mean = time_launches(wl.k, reps, 3, None) / reps * 1e3
     rate = work / (mean * 1e-6) / unit_scale(name)
-    out = {"workload": WORKLOADS[name], "us_per_launch": mean, "us_min": lo, "rate": rate, "unit": unit_of(name),
+    out = {"workload": WORKLOADS[name], "us_per_launch": mean, "us_single": single, "us_min": lo, "rate": rate, "unit": unit_of(name),
            "frac_of_measured_peak": rate / peak, "jit_us": wl.jit_us, "launches": wl.launches_per_step}
     wl.k.release_io()
     return out
@@ -528,8 +532,19 @@ def dynamic_shape_jit():
             k.input(op, a)
         k.codegen()
         jit = k.jit_us()
+        # from "the shape is known" to "the kernel is enqueued", on the host: the shape update, shape inference + planning +
+        # emission + binding, and the launch call (device buffers exist already; every codegen call plans from scratch)
+        lib_sync = k._lib.dvm_rt_sync
+        lib_sync(None)
+        t0 = time.perf_counter()
+        t_ref.update([t, 4096])
+        k.codegen()
+        k.launch()
+        enq = (time.perf_counter() - t0) * 1e6
+        lib_sync(None)
         lo, hi, mean = k.perf(warmup=2, reps=10)
-        out[str(t)] = {"jit_us": jit, "kernel_us": mean}
+        b2b = time_launches(k, 20, 2, None) / 20 * 1e3
+        out[str(t)] = {"jit_us": jit, "shape_to_enqueued_us": enq, "kernel_us": b2b, "kernel_us_single_launch": mean}
     k.release_io()
     return out
 
@@ -693,7 +708,10 @@ def main():
         lo, hi, mean = wl.k.perf(warmup=3, reps=reps)
     value = work * args.steps * world / (ms * 1e-3) / unit_scale(name)
     peak, peak_src = measured_peak(name)
-    achieved = work / (mean * 1e-6) / unit_scale(name)
+    # the kernel's average launch duration over the timed region: K launches back to back between two events on the launch
+    # stream (one launch per step); a pair of events around every single launch adds the launch latency to each (`us_per_launch`)
+    kernel_us = ms / args.steps * 1e3 / max(1, wl.launches_per_step)
+    achieved = work / (ms / args.steps * 1e-3) / unit_scale(name)
     tensor = name in ("c4", "c5")
     # DRAM bytes per full-size launch from the ncu captures summarised under profiles/ (dram__bytes_read + write; the
     # quarter-size captures of c1, c3, c4, c5 are scaled by 4: their traffic grows with the leading dimension)
@@ -709,7 +727,8 @@ def main():
         "roofline": {"bound": "tensor" if tensor else "hbm", "achieved": achieved, "peak": peak, "unit": unit_of(name),
                      "frac": achieved / peak, "traffic": traffic, "traffic_source": "ncu capture (profiles/), bytes per launch",
                      "peak_source": peak_src, "kernel": KERNEL_NAME[name],
-                     "us_per_launch": {"min": lo, "mean": mean, "max": hi},
+                     "kernel_us": kernel_us, "us_per_launch": {"min": lo, "mean": mean, "max": hi,
+                                                               "how": "one event pair per launch (includes the launch latency)"},
                      "frac_of_nominal": achieved / (2250.0 if tensor else 8000.0)},
         "gpu_launches": args.steps * wl.launches_per_step,
         "jit_us": wl.jit_us,

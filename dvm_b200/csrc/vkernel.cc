@@ -48,6 +48,11 @@ NDObject *VKernel::NewNode(NodeKind kind, DataType dtype) {
 }
 
 void VKernel::Normalize() {
+  // a Store handed to a later op as an operand stands for the value it stores (the reference's sequence kernels read a
+  // stage's stored result back in a later stage, tests/ut/test_sequence_fusion.py:170-205)
+  for (auto n : nodes_)
+    for (int k = 0; k < 3; ++k)
+      while (n->in[k] && n->in[k]->kind == N_STORE && n->in[k]->in[0]) n->in[k] = n->in[k]->in[0];
   for (auto n : nodes_) InferShape(n);
   normalized_ = true;
   compiled_ = false;

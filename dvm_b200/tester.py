@@ -33,6 +33,17 @@ class Tester(PyKernel):
         self.is_codegen = False
         self.expects = []  # [store op, expectation, eps]
 
+    @staticmethod
+    def fast_random_normal(mean, std, shape):
+        """Normal samples of `shape` (python/dvm/tester.py: a faster stand-in for np.random.normal on large shapes)."""
+        return np.random.default_rng().standard_normal(tuple(shape), dtype=np.float32) * np.float32(std) + np.float32(mean)
+
+    @staticmethod
+    def bf16_random_normal(loc, scale, shape):
+        """fp32 normal samples whose values are exactly representable in bfloat16 (python/dvm/tester.py:93-99)."""
+        x = np.random.normal(loc, scale, shape).astype(np.float32)
+        return (x.view(np.uint32) & np.uint32(0xFFFF0000)).view(np.float32)
+
     def load(self, shape_arr, dtype=None):
         if not isinstance(shape_arr, np.ndarray):
             return PyKernel.load(self, shape_arr, _normalize_dtype(dtype))   # dynamic-shape declaration

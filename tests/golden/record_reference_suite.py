@@ -200,6 +200,8 @@ def make_recording_tester():
         return method
 
     for name in dir(RealTester):
+        if not name.startswith("_") and not callable(getattr(RealTester, name)):
+            setattr(Tester, name, getattr(RealTester, name))   # class constants the tests name (Tester.K_VEC, ...)
         if name.startswith("_") or not callable(getattr(RealTester, name)) or name in ("fast_random_normal",):
             continue
         if name in ("das", "dump", "dump_r", "inspect", "convert_to_bf16", "convert_from_bf16", "is_dynamic"):
