@@ -645,6 +645,37 @@ def run_c5tp(args, rank, world, local_rank, dist):
         dist.destroy_process_group()
 
 
+def c2_by_channels_record(rank, world, local_rank, dist, steps=10):
+    """The BatchNorm workload cut by channels (each channel's statistics are independent, so no collective): every rank
+    holds the full NCHW tensors and normalises its 256 / N channels through strided loads and stores."""
+    import dvm_b200 as dvm
+    from dvm_b200 import workloads as W
+    x, gamma, beta = make_inputs("c2")
+    n, c, h, w = x.shape
+    per = c // world
+    first = rank * per
+    stride = [c * h * w, h * w, w, 1]
+    k = dvm.PyKernel("vector", "dev", local_rank)
+    lx = k.view_load([n, per, h, w], stride, dvm.float16)
+    lg, lb = k.load([1, per, 1, 1], dvm.float32), k.load([1, per, 1, 1], dvm.float32)
+    k.input(lx, x, offset=first * h * w)
+    k.input(lg, np.ascontiguousarray(gamma[:, first:first + per]))
+    k.input(lb, np.ascontiguousarray(beta[:, first:first + per]))
+    y, mean, var = W.batchnorm_train(k, lx, lg, lb, n * h * w)
+    sy = k.view_store(y, stride)
+    k.set_output(sy, np.zeros_like(x), offset=first * h * w)
+    k.store(mean)
+    k.store(var)
+    k.codegen()
+    ms = time_launches(k, steps, 3, dist)
+    peak, _ = measured_peak("c2")
+    per_gpu = ALGO_BYTES["c2"] / world * steps / (ms * 1e-3) / 1e9
+    rec = {"partition": "channels / %d per GPU (strided slab of NCHW)" % world, "us_per_step": ms / steps * 1e3,
+           "value": per_gpu * world, "unit": "GB/s", "scaling": "strong", "per_gpu_frac_of_measured_peak": per_gpu / peak}
+    k.release_io()
+    return rec
+
+
 def strong_scaling_record(name, rank, world, local_rank, dist, steps=10):
     """One BASELINE workload cut into `world` parts along its leading dimension (no collective): whole-job rate and the
     per-GPU roofline fraction."""
@@ -785,9 +816,10 @@ def main():
             multi["c5tp"] = c5tp_record(args, rank, world, local_rank, dist, steps=10)
         except Exception as e:   # the headline line must survive a failure here
             multi["c5tp"] = {"error": str(e)[:300]}
-        for other in ("c1", "c3", "c4", "c5"):
+        for other in ("c1", "c2", "c3", "c4", "c5"):
             try:
-                multi[other] = strong_scaling_record(other, rank, world, local_rank, dist)
+                multi[other] = (c2_by_channels_record(rank, world, local_rank, dist) if other == "c2"
+                                else strong_scaling_record(other, rank, world, local_rank, dist))
             except Exception as e:
                 multi[other] = {"error": str(e)[:300]}
         line["multi_gpu"] = multi

@@ -41,6 +41,8 @@ SIGNATURES = {
     "dvm_set_name_hint": (c_int, [c_void_p, c_char_p]),
     "dvm_load": (c_void_p, [c_void_p, c_void_p, c_void_p, c_int]),
     "dvm_store": (c_void_p, [c_void_p, c_void_p, c_void_p]),
+    "dvm_load_strided": (c_void_p, [c_void_p, c_void_p, c_void_p, c_void_p, c_int]),
+    "dvm_store_strided": (c_void_p, [c_void_p, c_void_p, c_void_p, c_void_p]),
     "dvm_unary": (c_void_p, [c_void_p, c_int, c_void_p]),
     "dvm_binary": (c_void_p, [c_void_p, c_int, c_void_p, c_void_p]),
     "dvm_binary_f32": (c_void_p, [c_void_p, c_int, c_void_p, ctypes.c_float, c_int]),

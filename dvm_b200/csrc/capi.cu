@@ -142,6 +142,12 @@ dvm_object *dvm_load(dvm_kernel *k, void *addr, dvm_int_array *shape, int dtype)
   return DVM_OBJ_GUARD(k->kernel.Load(addr, &shape->ref, static_cast<dvm::DataType>(dtype)));
 }
 dvm_object *dvm_store(dvm_kernel *k, void *addr, dvm_object *input) { return DVM_OBJ_GUARD(k->kernel.Store(addr, N(input))); }
+dvm_object *dvm_load_strided(dvm_kernel *k, void *addr, dvm_int_array *shape, dvm_int_array *stride, int dtype) {
+  return DVM_OBJ_GUARD(k->kernel.Load(addr, &shape->ref, &stride->ref, static_cast<dvm::DataType>(dtype)));
+}
+dvm_object *dvm_store_strided(dvm_kernel *k, void *addr, dvm_object *input, dvm_int_array *stride) {
+  return DVM_OBJ_GUARD(k->kernel.Store(addr, N(input), &stride->ref));
+}
 dvm_object *dvm_unary(dvm_kernel *k, int unary_type, dvm_object *input) {
   return DVM_OBJ_GUARD(k->kernel.Unary(unary_type, N(input)));
 }

@@ -351,9 +351,12 @@ NDObject *Kernel::Load(void *addr, IntArrayRef *shape, DataType type) {
   n->shape_ref = shape;
   return n;
 }
+// ref: include/dvm.h:286-294 - a tensor that is not contiguous in memory: `stride` gives the element stride of every dim
+// of `shape` (re-read at every Normalize, like the shape)
 NDObject *Kernel::Load(void *addr, IntArrayRef *shape, IntArrayRef *stride, DataType type) {
-  if (stride != nullptr) Unsupported("strided (view) Load");
-  return Load(addr, shape, type);
+  NDObject *n = Load(addr, shape, type);
+  n->stride_ref = stride;
+  return n;
 }
 NDObject *Kernel::GlobalAccess(void *, IntArrayRef *, DataType) { Unsupported("GlobalAccess"); }
 NDObject *Kernel::GatherLoad(void *, IntArrayRef *, NDObject *, int, DataType, GatherMode) { Unsupported("GatherLoad"); }
@@ -370,9 +373,11 @@ NDObject *Kernel::Store(void *addr, NDObject *input) {
   n->addr = addr;
   return n;
 }
+// ref: include/dvm.h:332-339 - the result written with the element strides `stride` (what lies between is left as it is)
 NDObject *Kernel::Store(void *addr, NDObject *input, IntArrayRef *stride) {
-  if (stride != nullptr) Unsupported("strided (view) Store");
-  return Store(addr, input);
+  NDObject *n = Store(addr, input);
+  n->stride_ref = stride;
+  return n;
 }
 NDObject *Kernel::PadStore(void *, NDObject *, int64_t) { Unsupported("PadStore"); }
 // ref: src/dvm.cc:1578-1580, src/xkernel.h:322.  The reference's flag keeps its workspace pool from handing the store's

@@ -77,6 +77,9 @@ class NDObject {
   uint32_t scalar_bits = 0;
   ScalarRef *scalar_ref = nullptr;
   IntArrayRef *shape_ref = nullptr;   // Load/Broadcast/Reshape target shape, Reduce dims (borrowed)
+  IntArrayRef *stride_ref = nullptr;  // strided (view) Load / Store: element strides of the tensor in memory (borrowed)
+  bool strided = false;               // results of Normalize() for a view: `stride` holds one element stride per dim
+  int64_t stride[kMaxRank] = {0};
   void *addr = nullptr;               // Load/Store device address
   // nodes the stage planner makes: a clone of a user's Load/Store (`origin` supplies the address) or a
   // temporary in the kernel's workspace (`ws_off` >= 0, bytes from the workspace base)

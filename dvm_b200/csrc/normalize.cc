@@ -54,14 +54,35 @@ Shape BroadcastShapes(const NDObject *n, const Shape &a, const Shape &b) {
 
 }  // namespace
 
+// A view's element strides, one per dim of the node's shape (borrowed reference, re-read at every Normalize).
+static void ReadStrides(NDObject *n) {
+  n->strided = false;
+  if (n->stride_ref == nullptr) return;
+  if (static_cast<int>(n->stride_ref->size) != n->shape.rank) Fail(n, "a view needs one stride per dimension");
+  int64_t dense = 1;
+  bool same = true;
+  for (int i = n->shape.rank - 1; i >= 0; --i) {
+    const int64_t st = n->stride_ref->data[i];
+    if (st < 0) Fail(n, "negative strides are not supported");
+    n->stride[i] = st;
+    if (n->shape.d[i] != 1 && st != dense) same = false;
+    dense *= n->shape.d[i];
+  }
+  n->strided = !same;   // (strides that describe a contiguous tensor need no special handling)
+}
+
 void InferShape(NDObject *n) {
   switch (n->kind) {
     case N_LOAD:
       n->shape = FromRef(n, n->shape_ref);
       for (int i = 0; i < n->shape.rank; ++i)
         if (n->shape.d[i] < 0) Fail(n, "negative dimension");
+      ReadStrides(n);
       break;
     case N_STORE:
+      n->shape = n->in[0]->shape;
+      ReadStrides(n);
+      break;
     case N_UNARY:
     case N_BINARY_S:
     case N_COMPARE_S:

@@ -91,10 +91,13 @@ struct Planner {
 
   // True when `n` is already addressable in global memory (a user's Load, a view of one, a stored temporary).
   bool InMemory(const NDObject *n) const { return n->kind == N_LOAD || mem.count(n) != 0; }
+  // ... and as one contiguous tensor (what the tensor-core stages, collectives and reshapes-as-views need): a strided
+  // Load only after it has been copied out to the workspace
+  bool InPlainMemory(const NDObject *n) const { return mem.count(n) != 0 || (n->kind == N_LOAD && !n->strided); }
 
   // A Load node (planner-made) reading value `n`, which must be InMemory().
   NDObject *MemLoad(const NDObject *n) {
-    if (n->kind == N_LOAD) {
+    if (n->kind == N_LOAD && mem.count(n) == 0) {
       NDObject *c = Synth(n);
       c->origin = n->origin ? n->origin : const_cast<NDObject *>(n);
       c->ws_off = n->ws_off;
@@ -293,8 +296,8 @@ struct Planner {
 
   // Make sure `v` is addressable in memory before a tensor-core stage reads it.
   void RequireInMemory(NDObject *v, const char *what) {
-    if (InMemory(v)) return;
-    if (v->kind == N_BROADCAST || v->kind == N_BROADCAST_S) {
+    if (InPlainMemory(v)) return;
+    if (v->kind == N_BROADCAST || v->kind == N_BROADCAST_S || v->kind == N_LOAD) {   // (a strided Load is copied out)
       Materialize(v);
       return;
     }
@@ -525,7 +528,7 @@ struct Planner {
     // every operand must be addressable; only then commit
     NDObject *ins[3] = {m1->in[0], m1->in[1], m2->in[1]};
     for (auto v : ins)
-      if (!InMemory(v) && !in_cur.count(v)) return false;
+      if (!InPlainMemory(v) && !in_cur.count(v) && v->kind != N_LOAD) return false;
     for (auto v : ins) RequireInMemory(v, "attention operand");
     auto st = std::make_unique<Stage>();
     st->kind = STAGE_ATTENTION;
@@ -710,8 +713,8 @@ struct Planner {
 
   void PlaceAllReduce(NDObject *n) {
     NDObject *v = n->in[0];
-    if (!InMemory(v)) {
-      if (v->kind == N_BROADCAST || v->kind == N_BROADCAST_S) {
+    if (!InPlainMemory(v)) {
+      if (v->kind == N_BROADCAST || v->kind == N_BROADCAST_S || v->kind == N_LOAD) {
         Materialize(v);
       } else {
         CloseCur();   // the open area stores v to the workspace: this node reads it from outside the area
@@ -777,8 +780,8 @@ struct Planner {
             cur.pop_back();
             CloseCur();
           }
-          if (!InMemory(src)) {
-            if (src->kind != N_BROADCAST && src->kind != N_BROADCAST_S)
+          if (!InPlainMemory(src)) {
+            if (src->kind != N_BROADCAST && src->kind != N_BROADCAST_S && src->kind != N_LOAD)
               DvmException("stage planner: reshape of a value that is not in memory");
             // a broadcast is re-created by its readers: a reshape that only adds or drops unit dims joins an area,
             // any other one needs the broadcast written out first

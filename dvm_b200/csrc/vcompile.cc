@@ -301,6 +301,11 @@ struct Compiler {
   // Element stride of tensor node `n` (contiguous in its own API shape) along domain axis `a`.
   int64_t StrideOn(const NDObject *n, int a) {
     const Info &fi = I(n);
+    if (n->strided) {   // a view: the strides the caller gave
+      for (int i = n->shape.rank - 1; i >= 0; --i)
+        if (fi.axis[i] == a && n->shape.d[i] != 1) return n->stride[i];
+      return 0;
+    }
     int64_t st = 1;
     for (int i = n->shape.rank - 1; i >= 0; --i) {
       if (fi.axis[i] == a && n->shape.d[i] != 1) return st;

@@ -185,6 +185,20 @@ class Kernel:
             obj = self.cast(obj, type)
         return self._obj(self._lib.dvm_store(self._k, None, obj._h), "store")
 
+    def view_load(self, shape, stride, type):
+        """A tensor that is not contiguous in memory: one element stride per dim (KernelPy::ViewLoad, include/dvm_py.h:104)."""
+        ref, sref = self._shape_ref(shape), self._shape_ref(stride)
+        op = self._obj(self._lib.dvm_load_strided(self._k, None, ref._h, sref._h, int(type)), "view_load")
+        op._shape_ref = ref
+        return op
+
+    def view_store(self, obj, stride, type=None):
+        """Store with element strides; what lies between the written elements keeps its content (KernelPy::ViewStore,
+        include/dvm_py.h:107)."""
+        if type is not None and int(type) < len(DataType._names):
+            obj = self.cast(obj, type)
+        return self._obj(self._lib.dvm_store_strided(self._k, None, obj._h, self._shape_ref(stride)._h), "view_store")
+
     def scalar(self, dtype=None):
         ref = ScalarRef(dtype)
         self._keep.append(ref)
@@ -461,6 +475,26 @@ class PyKernel(Kernel):
         self._stores.append([op, None, None])
         return op
 
+    def view_load(self, shape, stride, type):
+        op = Kernel.view_load(self, shape, stride, type)
+        self._loads.append([op, None, None])
+        return op
+
+    def view_store(self, obj, stride, type=None):
+        op = Kernel.view_store(self, obj, stride, type)
+        self._stores.append([op, None, None])
+        return op
+
+    def set_output(self, store, array, offset=0):
+        """The host array a store's result lives in (RtKernelPy::SetOutput, src/pybind_api.cc:867-872): its size is the
+        size of the device buffer and its content is what the buffer holds before the kernel runs - a strided store writes
+        only some of the elements.  `offset` (elements; not in the reference) is where in the array the stored tensor
+        starts, the counterpart of input()'s offset."""
+        rec = self._find(self._stores, store)
+        rec[2] = np.ascontiguousarray(array)
+        self._preset = getattr(self, "_preset", {})
+        self._preset[store._h] = (rec[2], int(offset) * rec[2].dtype.itemsize)
+
     def _find(self, table, op):
         for rec in table:
             if rec[0] is op or rec[0]._h == op._h:
@@ -503,6 +537,8 @@ class PyKernel(Kernel):
                 rec[1].free()
             rec[1] = _DevBuf(max(arr.nbytes, 1))
         rec[2] = arr
+        self._load_offset = getattr(self, "_load_offset", {})
+        self._load_offset[obj._h] = int(offset) * arr.dtype.itemsize   # the tensor starts `offset` elements into the array
         if arr.nbytes:
             check_rc(self._lib.dvm_rt_memcpy_h2d(rec[1].ptr, arr.ctypes.data, arr.nbytes, None), "H2D copy")
 
@@ -526,20 +562,27 @@ class PyKernel(Kernel):
             shape = op.shape()
             dt = np_dtype_of(op.dtype())
             nbytes = int(np.prod(shape, dtype=np.int64)) * dt.itemsize if len(shape) else dt.itemsize
-            rec[2] = np.empty(shape, dtype=dt)
+            preset, preset_off = getattr(self, "_preset", {}).get(op._h, (None, 0))
+            if preset is not None:
+                rec[2] = preset
+                nbytes = preset.nbytes
+            else:
+                rec[2] = np.empty(shape, dtype=dt)
             if self._run_type == "dev":
                 if rec[1] is None or rec[1].nbytes < nbytes:
                     if rec[1] is not None:
                         rec[1].free()
                     rec[1] = _DevBuf(max(nbytes, 1))
-                relocs.append((op._h, rec[1].ptr))
+                if preset is not None and nbytes:
+                    check_rc(self._lib.dvm_rt_memcpy_h2d(rec[1].ptr, preset.ctypes.data, nbytes, None), "H2D copy")
+                relocs.append((op._h, rec[1].ptr + preset_off))
             else:
                 relocs.append((op._h, 0x1000 * (len(relocs) + 1)))
         for rec in self._loads:
             if self._run_type == "dev":
                 if rec[1] is None:
                     raise DvmError("load has no input bound; call input() first")
-                relocs.append((rec[0]._h, rec[1].ptr))
+                relocs.append((rec[0]._h, rec[1].ptr + getattr(self, "_load_offset", {}).get(rec[0]._h, 0)))
             else:
                 relocs.append((rec[0]._h, 0x1000 * (len(relocs) + 1)))
         arr = (_capi.Reloc * max(1, len(relocs)))()

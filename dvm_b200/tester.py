@@ -58,6 +58,27 @@ class Tester(PyKernel):
         self.input(op, shape_arr)
         return op
 
+    def view_load(self, shape, stride, arr_dtype, offset=0, real_dtype=None):
+        """python/dvm/tester.py:120-132: a strided window of an array (or, given a dtype, of a dynamic-shape input)."""
+        if not isinstance(arr_dtype, np.ndarray):
+            return PyKernel.view_load(self, shape, stride, _normalize_dtype(arr_dtype))
+        arr = arr_dtype
+        dtype_id = _normalize_dtype(arr.dtype)
+        if real_dtype is not None:
+            dtype_id = _normalize_dtype(real_dtype)
+            if dtype_id == DataType.bfloat16:
+                arr = PyKernel.convert_to_bf16(arr)
+        op = PyKernel.view_load(self, shape, stride, dtype_id)
+        self.input(op, arr, offset)
+        return op
+
+    def view_store_expect(self, x, stride, e, eps=None):
+        """python/dvm/tester.py:205-209: a strided store into a zero-filled buffer of the expectation's size."""
+        op = PyKernel.view_store(self, x, stride)
+        self.expects.append([op, e, eps])
+        self.set_output(op, np.ascontiguousarray(np.zeros_like(e)))
+        return op
+
     def cast(self, x, dtype):
         return PyKernel.cast(self, x, _normalize_dtype(dtype))
 

@@ -62,6 +62,9 @@ DVM_C_API int dvm_set_name_hint(dvm_kernel *k, const char *name);               
 /* ---- graph building ---- */
 DVM_C_API dvm_object *dvm_load(dvm_kernel *k, void *addr, dvm_int_array *shape, int dtype);  /* dvm.h:276 */
 DVM_C_API dvm_object *dvm_store(dvm_kernel *k, void *addr, dvm_object *input);               /* dvm.h:331 */
+/* views: a tensor that is not contiguous in memory, one element stride per dim of its shape (dvm.h:294, 339) */
+DVM_C_API dvm_object *dvm_load_strided(dvm_kernel *k, void *addr, dvm_int_array *shape, dvm_int_array *stride, int dtype);
+DVM_C_API dvm_object *dvm_store_strided(dvm_kernel *k, void *addr, dvm_object *input, dvm_int_array *stride);
 DVM_C_API dvm_object *dvm_unary(dvm_kernel *k, int unary_type, dvm_object *input);           /* dvm.h:372 */
 DVM_C_API dvm_object *dvm_binary(dvm_kernel *k, int binary_type, dvm_object *lhs, dvm_object *rhs); /* dvm.h:381 */
 /* tensor (op) scalar; scalar_is_lhs selects `scalar op tensor` (KernelPy::Binary, include/dvm_py.h:113-133) */

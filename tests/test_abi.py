@@ -254,3 +254,22 @@ def test_spec_next_and_inplace_mark_are_checked():
         dvm.PyKernel("vector", "das", 0).spec_next()   # only speculative vector kernels have stages to advance
     with pytest.raises(RuntimeError):
         k.set_store_inplace(a)                      # not a store
+
+
+def test_views_carry_their_strides_into_the_tensor_table():
+    # Kernel::Load(addr, shape, stride, type) / Store(addr, input, stride): include/dvm.h:294, 339
+    k = dvm.PyKernel("vector", "das", 0)
+    x = k.view_load([64, 32, 56, 56], [256 * 3136, 3136, 56, 1], dvm.float16)     # 32 channels of an NCHW [64,256,56,56]
+    k.view_store(k.mul(x, 2.0), [256 * 3136, 3136, 56, 1])
+    k.codegen()
+    das = k.das()
+    assert das.count("estride=[0,802816,3136,1]") + das.count("estride=[0,0,802816,1]") >= 2, das[:600]
+    # strides that describe a contiguous tensor are an ordinary load
+    k = dvm.PyKernel("vector", "das", 0)
+    k.store(k.add(k.view_load([8, 16], [16, 1], dvm.float32), 1.0))
+    k.codegen()
+    assert "mode=flat" in k.das() and "fp32 dense" in k.das()
+    with pytest.raises(RuntimeError):
+        k = dvm.PyKernel("vector", "das", 0)
+        k.store(k.view_load([8, 16], [16], dvm.float32))      # one stride per dim
+        k.codegen()

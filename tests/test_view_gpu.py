@@ -1,0 +1,104 @@
+"""Strided (view) loads and stores on the device: Kernel::Load(addr, shape, stride, type) / Store(addr, input, stride)
+(include/dvm.h:286-294, 332-339).  Cases follow the reference's tests/ut/test_view.py (2-d and 3-d windows of a larger
+array, a strided store into a zero-filled buffer), plus the channel slab of an NCHW tensor that the BatchNorm graph
+is partitioned by, an element offset into the source array, and a view that feeds a MatMul (copied out first)."""
+import numpy as np
+import pytest
+
+from dvm_b200 import workloads as W
+from dvm_b200.tester import Tester
+from tests.util import TOL_FP32, TOL_HALF, TOL_REDUCE, assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("in_shape,window", [([30, 1000], [20, 500]), ([30, 500], [20, 200]), ([30, 4000], [20, 3000]),
+                                             ([43, 1000], [40, 500]), ([7, 13], [5, 11])])
+def test_window_of_a_matrix(in_shape, window):
+    rng = np.random.default_rng(1)
+    a = rng.normal(0, 1, in_shape).astype(np.float32)
+    t = Tester("vector")
+    x = t.view_load(window, [in_shape[1], 1], a)
+    s = t.store(t.add(x, 0.1))
+    t.run()
+    assert_close(t.output(s), a[:window[0], :window[1]] + np.float32(0.1), TOL_FP32, "2-d window")
+
+
+@pytest.mark.parametrize("in_shape,window", [([24, 20, 100], [20, 10, 60]), ([24, 20, 1000], [20, 10, 600]),
+                                             ([24, 20, 1000], [20, 20, 600]), ([24, 20, 64], [20, 15, 64]),
+                                             ([200, 20, 100], [200, 20, 30]), ([200, 20, 20], [200, 10, 20])])
+def test_window_of_a_3d_tensor(in_shape, window):
+    rng = np.random.default_rng(2)
+    a = rng.normal(0, 1, in_shape).astype(np.float32)
+    t = Tester("vector")
+    x = t.view_load(window, [in_shape[1] * in_shape[2], in_shape[2], 1], a)
+    s = t.store(t.add(x, 0.1))
+    t.run()
+    assert_close(t.output(s), a[:window[0], :window[1], :window[2]] + np.float32(0.1), TOL_FP32, "3-d window")
+
+
+def test_strided_store_leaves_the_rest_of_the_buffer_alone():
+    rng = np.random.default_rng(3)
+    data = rng.normal(0, 0.2, (4, 96, 7, 7)).astype(np.float32)
+    stride = [96 * 49, 49, 7, 1]
+    t = Tester("vector")
+    x = t.view_load([4, 32, 7, 7], stride, data)
+    expected = np.zeros_like(data)
+    expected[:, :32] = data[:, :32]
+    t.view_store_expect(x, stride, expected)
+    assert t.run_check()
+
+
+def test_element_offset_and_transposed_view():
+    rng = np.random.default_rng(4)
+    a = rng.normal(0, 1, (64, 48)).astype(np.float32)
+    t = Tester("vector")
+    x = t.view_load([40, 16], [48, 1], a, offset=3 * 48 + 5)   # rows 3.., columns 5..20
+    y = t.view_load([48, 64], [1, 48], a)                       # the transpose, read through its strides
+    s1, s2 = t.store(t.mul(x, 2.0)), t.store(t.sum(y, (1,), True))
+    t.run()
+    assert_close(t.output(s1), a[3:43, 5:21] * 2, TOL_FP32, "offset window")
+    assert_close(t.output(s2), a.T.sum(axis=1, keepdims=True), 1e-4, "row sums of the transposed view")
+
+
+@pytest.mark.parametrize("first,count", [(0, 8), (24, 8), (5, 3)])
+def test_batchnorm_on_a_channel_slab_of_nchw(first, count):
+    """The partitioning of the BatchNorm graph over GPUs: a rank normalises channels [first, first + count) of an NCHW
+    tensor in place in the full-size buffers, through strided loads and stores."""
+    rng = np.random.default_rng(5)
+    n, c, h, w = 16, 32, 14, 14
+    x = rng.normal(size=(n, c, h, w)).astype(np.float16)
+    gamma = rng.normal(1, 0.1, (1, c, 1, 1)).astype(np.float32)
+    beta = rng.normal(0, 0.1, (1, c, 1, 1)).astype(np.float32)
+    stride = [c * h * w, h * w, w, 1]
+    t = Tester("vector")
+    xs = t.view_load([n, count, h, w], stride, x, offset=first * h * w)
+    g, b = t.load(gamma[:, first:first + count]), t.load(beta[:, first:first + count])
+    y, mean, var = W.batchnorm_train(t, xs, g, b, n * h * w)
+    ys = t.view_store(y, stride)
+    t.set_output(ys, np.zeros_like(x), offset=first * h * w)   # the slab starts `first` channels into the result
+    sm, sv = t.store(mean), t.store(var)
+    t.run()
+    xf = x[:, first:first + count].astype(np.float32)
+    m, v = xf.mean(axis=(0, 2, 3), keepdims=True), xf.var(axis=(0, 2, 3), keepdims=True)
+    want = (xf - m) / np.sqrt(v + 1e-5) * gamma[:, first:first + count] + beta[:, first:first + count]
+    got = t.output(ys)
+    assert_close(got[:, first:first + count], want, TOL_HALF, "normalised slab")
+    outside = got.copy()
+    outside[:, first:first + count] = 0
+    assert not outside.any(), "elements outside the slab were written"
+    assert_close(t.output(sm), m, TOL_REDUCE, "slab mean")
+    assert_close(t.output(sv), v, TOL_REDUCE, "slab variance")
+
+
+def test_view_feeding_a_matmul_is_copied_out_first():
+    rng = np.random.default_rng(6)
+    big = rng.normal(0, 0.1, (256, 512)).astype(np.float32)
+    b = rng.normal(0, 0.1, (128, 192)).astype(np.float32)
+    t = Tester("split")
+    a = t.view_load([256, 128], [512, 1], big.astype(np.float16))
+    s = t.store(t.matmul(a, t.load(b.astype(np.float16)), False, False))
+    t.run()
+    assert t.das().count("vmain") == 1 and t.das().count("mmain") == 1
+    want = big[:, :128].astype(np.float16).astype(np.float32) @ b.astype(np.float16).astype(np.float32)
+    assert_close(t.output(s), want, TOL_HALF, "MatMul of a window")
