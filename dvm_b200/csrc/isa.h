@@ -197,6 +197,18 @@ enum UopHandler : uint32_t {
   // own type; with UA_LOOP the handler runs every remaining full round of the chunk
   UH_LDNORMST_FIRST,                                // first + FusedType
   UH_LDNORMST_LAST = UH_LDNORMST_FIRST + 2,
+  // the pieces of a residual RMSNorm + gated-activation graph, one dispatch each.  Ring offsets / 16 are 12 bits wide here.
+  //   sum of squares of a sum:  acc <- (ring A + ring B)^2; partial 0 / 1 += lanes.  arg16 = A, imm32 = B
+  UH_LD2ADDSQRSUM_FIRST,                            // first + slot * 3 + FusedType
+  UH_LD2ADDSQRSUM_LAST = UH_LD2ADDSQRSUM_FIRST + 5,
+  //   scaled sum times a weight, stored:  ((ring A + ring B) * sreg) * ring W -> vector store in the operands' type.
+  //   arg16 = A, imm32 = B | W << 12 | result slot << 24 | sreg << 28
+  UH_LD2ADDMULRMULST_FIRST,                         // first + FusedType
+  UH_LD2ADDMULRMULST_LAST = UH_LD2ADDMULRMULST_FIRST + 2,
+  //   gated activation, stored:  (sigmoid(ring G) * ring X) * ring Y -> vector store (fast sigmoid forms).
+  //   arg16 = G, imm32 = X | Y << 12 | result slot << 24
+  UH_LDSIGMMUL2ST_FIRST,                            // first + FusedType
+  UH_LDSIGMMUL2ST_LAST = UH_LDSIGMMUL2ST_FIRST + 2,
   UH_COUNT
 };
 enum FusedOp : uint32_t { FO_ADD = 0, FO_SUB = 1, FO_MUL = 2 };

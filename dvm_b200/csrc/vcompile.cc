@@ -1425,6 +1425,39 @@ bool LowerStageAs(VectorStage *st, bool dual) {
           continue;
         }
       }
+      // the pieces of a residual RMSNorm + gated activation (ring offsets must fit 12 bits)
+      const uint64_t c0 = P.code[i];
+      const uint64_t c1 = i + 1 < o ? P.code[i + 1] : 0, c2 = i + 2 < o ? P.code[i + 2] : 0, c3 = i + 3 < o ? P.code[i + 3] : 0;
+      const uint32_t h1 = i + 1 < o ? DVMB_UH(c1) : static_cast<uint32_t>(UH_COUNT), h2 = i + 2 < o ? DVMB_UH(c2) : static_cast<uint32_t>(UH_COUNT);
+      const uint32_t h3 = i + 3 < o ? DVMB_UH(c3) : static_cast<uint32_t>(UH_COUNT);
+      static const uint32_t store_for[] = {UH_ST_F32, UH_ST_F16, UH_ST_BF16};   // by FusedType
+      auto small = [](uint32_t off) { return off < 4096u; };
+      if (h >= UH_LD2OP_FIRST + FO_ADD * 3u && h <= UH_LD2OP_FIRST + FO_ADD * 3u + 2u && small(DVMB_UARG(c0)) && small(DVMB_UIMM(c0))) {
+        const uint32_t ft = h - (UH_LD2OP_FIRST + FO_ADD * 3u);
+        if (h1 == UH_SQRSUM0 || h1 == UH_SQRSUM1) {
+          P.code[o2++] = MakeUop(UH_LD2ADDSQRSUM_FIRST + (h1 == UH_SQRSUM1 ? 3u : 0u) + ft, 0, DVMB_UARG(c0), DVMB_UIMM(c0));
+          i += 1;
+          fused_away += 1;
+          continue;
+        }
+        if (h1 == UH_BINR_FIRST + B_MUL && h2 == UH_LDOP_FIRST + FO_MUL * 3u + ft && h3 == store_for[ft] && small(DVMB_UARG(c2)) &&
+            DVMB_UARG(c3) < 16u && DVMB_UARG(c1) < 16u) {
+          P.code[o2++] = MakeUop(UH_LD2ADDMULRMULST_FIRST + ft, 0, DVMB_UARG(c0),
+                                 DVMB_UIMM(c0) | (DVMB_UARG(c2) << 12) | (DVMB_UARG(c3) << 24) | (DVMB_UARG(c1) << 28));
+          i += 3;
+          fused_away += 3;
+          continue;
+        }
+      }
+      if (h >= UH_LDSIGM_FIRST && h <= UH_LDSIGM_LAST && small(DVMB_UARG(c0))) {
+        const uint32_t ft = h - UH_LDSIGM_FIRST;
+        if (h1 == UH_LDMUL2_FIRST + ft && h2 == store_for[ft] && small(DVMB_UARG(c1)) && small(DVMB_UIMM(c1)) && DVMB_UARG(c2) < 16u) {
+          P.code[o2++] = MakeUop(UH_LDSIGMMUL2ST_FIRST + ft, 0, DVMB_UARG(c0), DVMB_UARG(c1) | (DVMB_UIMM(c1) << 12) | (DVMB_UARG(c2) << 24));
+          i += 2;
+          fused_away += 2;
+          continue;
+        }
+      }
       P.code[o2++] = P.code[i];
     }
     n = o2;
@@ -1519,12 +1552,14 @@ bool LowerStageAs(VectorStage *st, bool dual) {
           const bool ends_body = (last >= UH_ST_F32 && last <= UH_ST_BF16) || (last >= UH_RACCF_FIRST && last <= UH_RACCF_LAST) ||
                                  (last >= UH_LDSUM_FIRST && last <= UH_LDSUM_LAST) || last == UH_SQRSUM0 || last == UH_SQRSUM1 ||
                                  (last >= UH_LDVAR_FIRST && last <= UH_LDVAR_LAST) ||
-                                 (last >= UH_LDNORMST_FIRST && last <= UH_LDNORMST_LAST);
+                                 (last >= UH_LDNORMST_FIRST && last <= UH_LDNORMST_LAST) ||
+                                 (last >= UH_LD2ADDSQRSUM_FIRST && last <= UH_LDSIGMMUL2ST_LAST);
           if (ends_body && !no_tail && !overflow) {
             P.code[n - 1] |= static_cast<uint64_t>(UA_LAST) << 8;
             // a body that is one load + reduce micro-op runs all full rounds of a chunk in a single dispatch
             const bool load_reduce = (last >= UH_LDSUM_FIRST && last <= UH_LDSUM_LAST) || (last >= UH_LDVAR_FIRST && last <= UH_LDVAR_LAST) ||
-                                     (last >= UH_LDNORMST_FIRST && last <= UH_LDNORMST_LAST);
+                                     (last >= UH_LDNORMST_FIRST && last <= UH_LDNORMST_LAST) ||
+                                 (last >= UH_LD2ADDSQRSUM_FIRST && last <= UH_LDSIGMMUL2ST_LAST);
             if (load_reduce && n - P.sec[sidx] == 1 && P.rounds > 1) P.code[n - 1] |= static_cast<uint64_t>(UA_LOOP) << 8;
             ++fused_away;
             break;
@@ -1778,6 +1813,14 @@ std::string DisassembleStage(const VectorStage &st) {
       case UH_MULR_ADDR: return "Mul.s+Add.s";
       case UH_MULR_MULR: return "Mul.s+Mul.s";
       case UH_MULR_MULR_ADDR: return "Mul.s+Mul.s+Add.s";
+      case UH_LD2ADDSQRSUM_FIRST + 0: case UH_LD2ADDSQRSUM_FIRST + 1: case UH_LD2ADDSQRSUM_FIRST + 2:
+        return std::string("lda.") + ty[h - UH_LD2ADDSQRSUM_FIRST] + "+ldb+Add.b+Sqr+ReduceSum.p0";
+      case UH_LD2ADDSQRSUM_FIRST + 3: case UH_LD2ADDSQRSUM_FIRST + 4: case UH_LD2ADDSQRSUM_FIRST + 5:
+        return std::string("lda.") + ty[h - UH_LD2ADDSQRSUM_FIRST - 3] + "+ldb+Add.b+Sqr+ReduceSum.p1";
+      case UH_LD2ADDMULRMULST_FIRST + 0: case UH_LD2ADDMULRMULST_FIRST + 1: case UH_LD2ADDMULRMULST_FIRST + 2:
+        return std::string("lda.") + ty[h - UH_LD2ADDMULRMULST_FIRST] + "+ldb+Add.b+Mul.s+ldb+Mul.b+st." + ty[h - UH_LD2ADDMULRMULST_FIRST];
+      case UH_LDSIGMMUL2ST_FIRST + 0: case UH_LDSIGMMUL2ST_FIRST + 1: case UH_LDSIGMMUL2ST_FIRST + 2:
+        return std::string("lda.") + ty[h - UH_LDSIGMMUL2ST_FIRST] + "+SigmoidFast+ldb+Mul.b+ldb+Mul.b+st." + ty[h - UH_LDSIGMMUL2ST_FIRST];
       case UH_LDNORMST_FIRST + FT_F32: return "lda.fp32+Sub.s+Mul.s+Mul.s+Add.s+st.fp32";
       case UH_LDNORMST_FIRST + FT_F16: return "lda.fp16+Sub.s+Mul.s+Mul.s+Add.s+st.fp16";
       case UH_LDNORMST_FIRST + FT_BF16: return "lda.bf16+Sub.s+Mul.s+Mul.s+Add.s+st.bf16";

@@ -830,6 +830,74 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
             DV_LDNORMST_CASE(UH_LDNORMST_FIRST + FT_F16, DV_LDR_F16, DV_SHL1, unsigned short, DV_STV16("cvt.rn.f16x2.f32", p0, ge))
             DV_LDNORMST_CASE(UH_LDNORMST_FIRST + FT_BF16, DV_LDR_BF16, DV_SHL1, unsigned short, DV_STV16("cvt.rn.bf16x2.f32", p0, ge))
 #undef DV_LDNORMST_CASE
+            // ---- the pieces of a residual RMSNorm + gated activation, one dispatch each (same operations, order and
+            // rounding as the micro-ops they replace)
+#define DV_RING3(SHL)                                                                                       \
+    const uint32_t o0 = stage_saddr + (SHL(pos.in_chunk0)), gs = SHL(pos.gstep);                            \
+    const uint32_t a0 = o0 + (arg << 4), b0 = o0 + ((uhi & 0xfffu) << 4), c0 = o0 + (((uhi >> 12) & 0xfffu) << 4);
+#define DV_STORE_PTR(ELEM)                                                                                  \
+    const TensorDesc &td = tdesc[(uhi >> 24) & 0xfu];                                                       \
+    ELEM *const p0 = reinterpret_cast<ELEM *>(td.ptr) + kept_offset(td, pos.k) +                            \
+                     ((kCoords && td.mode != AM_DENSE) ? enum_offset(td, cc) + lane4 : pos.e_start + pos.in_chunk0); \
+    const uint32_t ge = pos.gstep;
+#define DV_LD2ADDSQRSUM_CASE(H, MACRO, SHL, SLOT)                                                           \
+  case H: {                                                                                                 \
+    const uint32_t o0 = stage_saddr + (SHL(pos.in_chunk0)), gs = SHL(pos.gstep);                            \
+    const uint32_t a0 = o0 + (arg << 4), b0 = o0 + (uhi << 4);                                              \
+    MACRO("va", a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)                                                     \
+    MACRO("vb", b0, b0 + gs, b0 + 2u * gs, b0 + 3u * gs)                                                     \
+    asm volatile(DV_LN(DV_BINVRN_LANE, "add.rn.f32"));                                                      \
+    asm volatile(DV_LN(DV_SQRRN_LANE, ""));                                                                 \
+    asm volatile(DV_SUMRN_TREE(SLOT));                                                                      \
+    if (aux & UA_LAST) goto body_done;                                                                      \
+    continue;                                                                                               \
+  }
+            DV_LD2ADDSQRSUM_CASE(UH_LD2ADDSQRSUM_FIRST + FT_F32, DV_LDR32, DV_SHL2, "0")
+            DV_LD2ADDSQRSUM_CASE(UH_LD2ADDSQRSUM_FIRST + FT_F16, DV_LDR_F16, DV_SHL1, "0")
+            DV_LD2ADDSQRSUM_CASE(UH_LD2ADDSQRSUM_FIRST + FT_BF16, DV_LDR_BF16, DV_SHL1, "0")
+            DV_LD2ADDSQRSUM_CASE(UH_LD2ADDSQRSUM_FIRST + 3 + FT_F32, DV_LDR32, DV_SHL2, "1")
+            DV_LD2ADDSQRSUM_CASE(UH_LD2ADDSQRSUM_FIRST + 3 + FT_F16, DV_LDR_F16, DV_SHL1, "1")
+            DV_LD2ADDSQRSUM_CASE(UH_LD2ADDSQRSUM_FIRST + 3 + FT_BF16, DV_LDR_BF16, DV_SHL1, "1")
+#undef DV_LD2ADDSQRSUM_CASE
+#define DV_LD2ADDMULRMULST_CASE(H, MACRO, SHL, ELEM, STORE)                                                   \
+  case H: {                                                                                                 \
+    DV_RING3(SHL)                                                                                           \
+    const uint32_t sv_ = lds32(sreg_addr(uhi >> 28));                                                       \
+    DV_STORE_PTR(ELEM)                                                                                      \
+    MACRO("va", a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)                                                     \
+    MACRO("vb", b0, b0 + gs, b0 + 2u * gs, b0 + 3u * gs)                                                     \
+    asm volatile(DV_LN(DV_BINVRN_LANE, "add.rn.f32"));                                                      \
+    asm volatile(DV_LN(DV_BINS_LANE, "mul.rn.f32")::"r"(sv_));                                              \
+    MACRO("vb", c0, c0 + gs, c0 + 2u * gs, c0 + 3u * gs)                                                     \
+    asm volatile(DV_LN(DV_BINVRN_LANE, "mul.rn.f32"));                                                      \
+    STORE                                                                                                   \
+    if (aux & UA_LAST) goto body_done;                                                                      \
+    continue;                                                                                               \
+  }
+            DV_LD2ADDMULRMULST_CASE(UH_LD2ADDMULRMULST_FIRST + FT_F32, DV_LDR32, DV_SHL2, uint32_t, DV_STV32(p0, ge))
+            DV_LD2ADDMULRMULST_CASE(UH_LD2ADDMULRMULST_FIRST + FT_F16, DV_LDR_F16, DV_SHL1, unsigned short, DV_STV16("cvt.rn.f16x2.f32", p0, ge))
+            DV_LD2ADDMULRMULST_CASE(UH_LD2ADDMULRMULST_FIRST + FT_BF16, DV_LDR_BF16, DV_SHL1, unsigned short, DV_STV16("cvt.rn.bf16x2.f32", p0, ge))
+#undef DV_LD2ADDMULRMULST_CASE
+#define DV_LDSIGMMUL2ST_CASE(H, MACRO, SHL, ELEM, STORE)                                                      \
+  case H: {                                                                                                 \
+    DV_RING3(SHL)                                                                                           \
+    DV_STORE_PTR(ELEM)                                                                                      \
+    MACRO("va", a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)                                                     \
+    asm volatile(DV_LN(DV_SIGM_LANE, ""));                                                                  \
+    MACRO("vb", b0, b0 + gs, b0 + 2u * gs, b0 + 3u * gs)                                                     \
+    asm volatile(DV_LN(DV_BINVRN_LANE, "mul.rn.f32"));                                                      \
+    MACRO("vb", c0, c0 + gs, c0 + 2u * gs, c0 + 3u * gs)                                                     \
+    asm volatile(DV_LN(DV_BINVRN_LANE, "mul.rn.f32"));                                                      \
+    STORE                                                                                                   \
+    if (aux & UA_LAST) goto body_done;                                                                      \
+    continue;                                                                                               \
+  }
+            DV_LDSIGMMUL2ST_CASE(UH_LDSIGMMUL2ST_FIRST + FT_F32, DV_LDR32, DV_SHL2, uint32_t, DV_STV32(p0, ge))
+            DV_LDSIGMMUL2ST_CASE(UH_LDSIGMMUL2ST_FIRST + FT_F16, DV_LDR_F16, DV_SHL1, unsigned short, DV_STV16("cvt.rn.f16x2.f32", p0, ge))
+            DV_LDSIGMMUL2ST_CASE(UH_LDSIGMMUL2ST_FIRST + FT_BF16, DV_LDR_BF16, DV_SHL1, unsigned short, DV_STV16("cvt.rn.bf16x2.f32", p0, ge))
+#undef DV_LDSIGMMUL2ST_CASE
+#undef DV_STORE_PTR
+#undef DV_RING3
 #undef DV_STV16
 #undef DV_STV32
 #undef DVMB_ST

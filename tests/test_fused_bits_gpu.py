@@ -45,11 +45,31 @@ x = rng.standard_normal((8, 24, 28, 28), dtype=np.float32).astype(np.float16)
 g = rng.normal(1, 0.1, (1, 24, 1, 1)).astype(np.float32)
 b = rng.normal(0, 0.1, (1, 24, 1, 1)).astype(np.float32)
 run("bn", lambda k, a, c, d: W.batchnorm_train(k, a, c, d, 8 * 28 * 28), [x, g, b])
+# the same on planes of 56 x 56 (chunks of several rounds, every body one looping micro-op), with a last chunk that is
+# not full (19 planes, 8 per chunk)
+x = rng.standard_normal((19, 6, 56, 56), dtype=np.float32).astype(np.float16)
+run("bn_rounds", lambda k, a, c, d: W.batchnorm_train(k, a, c, d, 19 * 56 * 56), [x, g[:, :6], b[:, :6]])
 # residual + RMSNorm + SwiGLU in bf16 (two ring operands + add, ring operand + mul, fast sigmoid), rows with a ragged tail
 for rows, hidden in ((37, 4096), (5, 1000)):
     h, r, gg, u = (rng.standard_normal((rows, hidden), dtype=np.float32).astype(BF16) for _ in range(4))
     w = rng.normal(1, 0.02, (hidden,)).astype(np.float32).astype(BF16)
     run("rms%d" % hidden, lambda k, a, c, d, e, f, n=hidden: W.rmsnorm_swiglu(k, a, c, d, e, f, n), [h, r, w, gg, u])
+# the same graph on fp16 and fp32 storage (the fused sum-of-squares, scaled-sum and gated-activation forms of each type)
+
+
+def rms_any(k, a, c, d, e, f, n, dt):
+    s = k.add(k.cast(a, 3), k.cast(c, 3))
+    inv = k.div(1.0, k.sqrt(k.add(k.mul(k.sum(k.mul(s, s), (1,), True), 1.0 / n), 1e-6)))
+    o1 = k.cast(k.mul(k.mul(s, inv), k.cast(d, 3)), dt)
+    ef = k.cast(e, 3)
+    o2 = k.cast(k.mul(k.mul(ef, k.div(1.0, k.add(k.exp(k.mul(ef, -1.0)), 1.0))), k.cast(f, 3)), dt)
+    return o1, o2
+
+
+for dt, code, tag in ((np.float16, 1, "f16"), (np.float32, 3, "f32")):
+    h, r, gg, u = (rng.standard_normal((21, 2048), dtype=np.float32).astype(dt) for _ in range(4))
+    w = rng.normal(1, 0.02, (2048,)).astype(dt)
+    run("rms_" + tag, lambda k, a, c, d, e, f, c_=code: rms_any(k, a, c, d, e, f, 2048, c_), [h, r, w, gg, u])
 # reduce-free chains in the three storage types
 for dt, tag in ((np.float32, "f32"), (np.float16, "f16")):
     p = rng.uniform(-2, 2, (333, 2048)).astype(dt)
