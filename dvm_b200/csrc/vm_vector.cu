@@ -717,14 +717,27 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
             DV_LDX_TYPES(UH_LDOP_FIRST + FO_MUL * 3, "vb", asm volatile(DV_LN(DV_BINVRN_LANE, "mul.rn.f32"));)
             // load + reduce forms: as the only micro-op of a body (UA_LOOP) they run every remaining full round of the
             // chunk inside one dispatch; the partial grows round by round exactly as it does with one dispatch per round
-#define DV_LDRED_CASE(H, MACRO, SHL, PRE, ...)                                                                \
+#define DV_LDRED_CASE(H, MACRO, SHL, PRE, OPS)                                                                \
   case H: {                                                                                                 \
     uint32_t a0 = stage_saddr + (arg << 4) + (SHL(pos.in_chunk0));                                          \
     const uint32_t gs = SHL(pos.gstep);                                                                     \
     PRE                                                                                                     \
     for (;;) {                                                                                              \
+      if (kRounds && (aux & UA_LOOP) && rnd + 1u < n_full) {                                                \
+        /* two rounds at a time, one per vector register; the partial takes them in their order */          \
+        const uint32_t a1 = a0 + SHL(P.round_elems);                                                        \
+        MACRO("va", a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)                                                 \
+        MACRO("vb", a1, a1 + gs, a1 + 2u * gs, a1 + 3u * gs)                                                 \
+        OPS("va")                                                                                           \
+        OPS("vb")                                                                                           \
+        ++rnd;                                                                                              \
+        if (rnd + 1u >= n_full) break;                                                                      \
+        ++rnd;                                                                                              \
+        a0 = a1 + SHL(P.round_elems);                                                                       \
+        continue;                                                                                           \
+      }                                                                                                     \
       MACRO("va", a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)                                                   \
-      __VA_ARGS__                                                                                           \
+      OPS("va")                                                                                             \
       if (!kRounds || !(aux & UA_LOOP) || rnd + 1u >= n_full) break;                                        \
       ++rnd;                                                                                                \
       a0 += SHL(P.round_elems);                                                                             \
@@ -732,11 +745,14 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
     if (aux & UA_LAST) goto body_done;                                                                      \
     continue;                                                                                               \
   }
-#define DV_LDRED_TYPES(FIRST, PRE, ...)                                            \
-  DV_LDRED_CASE(FIRST + FT_F32, DV_LDR32, DV_SHL2, PRE, __VA_ARGS__)               \
-  DV_LDRED_CASE(FIRST + FT_F16, DV_LDR_F16, DV_SHL1, PRE, __VA_ARGS__)             \
-  DV_LDRED_CASE(FIRST + FT_BF16, DV_LDR_BF16, DV_SHL1, PRE, __VA_ARGS__)
-            DV_LDRED_TYPES(UH_LDSUM_FIRST, , asm volatile(DV_SUMRN_TREE("0"));)
+#define DV_LDRED_TYPES(FIRST, PRE, OPS)                                            \
+  DV_LDRED_CASE(FIRST + FT_F32, DV_LDR32, DV_SHL2, PRE, OPS)                       \
+  DV_LDRED_CASE(FIRST + FT_F16, DV_LDR_F16, DV_SHL1, PRE, OPS)                     \
+  DV_LDRED_CASE(FIRST + FT_BF16, DV_LDR_BF16, DV_SHL1, PRE, OPS)
+#define DV_OPS_SUM0(R) asm volatile(DV_TREE16R(DV_ADDRN2, "0", R));
+#define DV_OPS_VAR0(R) asm volatile(DV_LNR(DV_CSQR_LANE_R, R, "")::"r"(sv_)); asm volatile(DV_TREE16R(DV_ADDRN2, "0", R));
+#define DV_OPS_VAR1(R) asm volatile(DV_LNR(DV_CSQR_LANE_R, R, "")::"r"(sv_)); asm volatile(DV_TREE16R(DV_ADDRN2, "1", R));
+            DV_LDRED_TYPES(UH_LDSUM_FIRST, , DV_OPS_SUM0)
             DV_LDX_TYPES(UH_LDSUBR_FIRST, "va", {
               const uint32_t sv_ = lds32(sreg_addr(uhi));
               asm volatile(DV_LN(DV_BINS_LANE, "sub.rn.f32")::"r"(sv_));
@@ -765,10 +781,11 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
               asm volatile(DV_LN(DV_BINS3_LANE, "mul.rn.f32", "mul.rn.f32", "add.rn.f32")::"r"(s1_), "r"(s2_), "r"(s3_));
               continue;
             }
-            DV_LDRED_TYPES(UH_LDVAR_FIRST, const uint32_t sv_ = lds32(sreg_addr(uhi));,
-                           asm volatile(DV_LN(DV_CSQR_LANE, "")::"r"(sv_)); asm volatile(DV_SUMRN_TREE("0"));)
-            DV_LDRED_TYPES(UH_LDVAR_FIRST + 3, const uint32_t sv_ = lds32(sreg_addr(uhi));,
-                           asm volatile(DV_LN(DV_CSQR_LANE, "")::"r"(sv_)); asm volatile(DV_SUMRN_TREE("1"));)
+            DV_LDRED_TYPES(UH_LDVAR_FIRST, const uint32_t sv_ = lds32(sreg_addr(uhi));, DV_OPS_VAR0)
+            DV_LDRED_TYPES(UH_LDVAR_FIRST + 3, const uint32_t sv_ = lds32(sreg_addr(uhi));, DV_OPS_VAR1)
+#undef DV_OPS_SUM0
+#undef DV_OPS_VAR0
+#undef DV_OPS_VAR1
 #undef DV_LDRED_TYPES
 #undef DV_LDRED_CASE
             DV_LDX_TYPES(UH_LDNORM_FIRST, "va", {
@@ -780,19 +797,21 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
             // a whole normalisation body in one micro-op: ring operand -> ((x - s0) * s1) * s2 + s3 -> vector store in the
             // operand's own type, for every remaining full round of the chunk when it is the body's only micro-op
 #define DVMB_ST "st.global"   /* (a cache-streaming form, st.global.cs, measured the same on a three-pass normalisation) */
-#define DV_STV32(P0, GS)                                                                                              \
-  asm volatile(DVMB_ST ".v4.b32 [%0], {va0,va1,va2,va3};\n\t" DVMB_ST ".v4.b32 [%1], {va4,va5,va6,va7};\n\t"            \
-               DVMB_ST ".v4.b32 [%2], {va8,va9,va10,va11};\n\t" DVMB_ST ".v4.b32 [%3], {va12,va13,va14,va15};" ::"l"(P0), \
+#define DV_STV32R(R, P0, GS)                                                                                          \
+  asm volatile(DVMB_ST ".v4.b32 [%0], {" R "0," R "1," R "2," R "3};\n\t" DVMB_ST ".v4.b32 [%1], {" R "4," R "5," R "6," R "7};\n\t" \
+               DVMB_ST ".v4.b32 [%2], {" R "8," R "9," R "10," R "11};\n\t" DVMB_ST ".v4.b32 [%3], {" R "12," R "13," R "14," R "15};" ::"l"(P0), \
                "l"(P0 + GS), "l"(P0 + 2u * GS), "l"(P0 + 3u * GS)                                                      \
                : "memory");
-#define DV_STV16(CVT, P0, GS)                                                                                 \
+#define DV_STV16R(CVT, R, P0, GS)                                                                             \
   asm volatile("{\n\t.reg .b32 t0, t1;\n\t"                                                                   \
-               CVT " t0, va1, va0;\n\t" CVT " t1, va3, va2;\n\t" DVMB_ST ".v2.b32 [%0], {t0,t1};\n\t"           \
-               CVT " t0, va5, va4;\n\t" CVT " t1, va7, va6;\n\t" DVMB_ST ".v2.b32 [%1], {t0,t1};\n\t"           \
-               CVT " t0, va9, va8;\n\t" CVT " t1, va11, va10;\n\t" DVMB_ST ".v2.b32 [%2], {t0,t1};\n\t"         \
-               CVT " t0, va13, va12;\n\t" CVT " t1, va15, va14;\n\t" DVMB_ST ".v2.b32 [%3], {t0,t1};\n\t}" ::"l"(P0), \
+               CVT " t0, " R "1, " R "0;\n\t" CVT " t1, " R "3, " R "2;\n\t" DVMB_ST ".v2.b32 [%0], {t0,t1};\n\t"           \
+               CVT " t0, " R "5, " R "4;\n\t" CVT " t1, " R "7, " R "6;\n\t" DVMB_ST ".v2.b32 [%1], {t0,t1};\n\t"           \
+               CVT " t0, " R "9, " R "8;\n\t" CVT " t1, " R "11, " R "10;\n\t" DVMB_ST ".v2.b32 [%2], {t0,t1};\n\t"         \
+               CVT " t0, " R "13, " R "12;\n\t" CVT " t1, " R "15, " R "14;\n\t" DVMB_ST ".v2.b32 [%3], {t0,t1};\n\t}" ::"l"(P0), \
                "l"(P0 + GS), "l"(P0 + 2u * GS), "l"(P0 + 3u * GS)                                            \
                : "memory");
+#define DV_STV32(P0, GS) DV_STV32R("va", P0, GS)
+#define DV_STV16(CVT, P0, GS) DV_STV16R(CVT, "va", P0, GS)
 #define DV_LDNORMST_CASE(H, MACRO, SHL, ELEM, STORE)                                                          \
   case H: {                                                                                                 \
     const TensorDesc &td = tdesc[(uhi >> 16) & 0xfu];                                                       \
@@ -803,32 +822,55 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
     const bool by_coords = kCoords && td.mode != AM_DENSE;                                                  \
     ELEM *const base = reinterpret_cast<ELEM *>(td.ptr) + kept_offset(td, pos.k);                           \
     ELEM *p0 = base + (by_coords ? enum_offset(td, cc) + lane4 : pos.e_start + pos.in_chunk0);              \
+    /* the result pointer of the round after the one at p0 (the coordinates move on by one round) */       \
+    auto next_round = [&](ELEM *p) -> ELEM * {                                                              \
+      if (!by_coords) return p + P.round_elems;                                                             \
+      rnd_begin += 1u;   /* (the code behind the body adds one round to the coordinates itself) */          \
+      cc[3] += P.round_elems;                                                                               \
+      _Pragma("unroll") for (int j = kMaxEnum - 1; j > 0; --j) while (cc[j] >= P.enum_size[j]) {            \
+        cc[j] -= P.enum_size[j];                                                                            \
+        cc[j - 1] += 1u;                                                                                    \
+      }                                                                                                     \
+      return base + enum_offset(td, cc) + lane4;                                                            \
+    };                                                                                                      \
     for (;;) {                                                                                              \
+      if (kRounds && (aux & UA_LOOP) && rnd + 1u < n_full) {                                                \
+        /* two rounds at a time, one per vector register */                                                 \
+        const uint32_t a1 = a0 + SHL(P.round_elems);                                                        \
+        ELEM *const p1 = next_round(p0);                                                                    \
+        MACRO("va", a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)                                                 \
+        MACRO("vb", a1, a1 + gs, a1 + 2u * gs, a1 + 3u * gs)                                                 \
+        asm volatile(DV_LNR(DV_NORM_LANE_R, "va", "")::"r"(s0_), "r"(s1_), "r"(s2_), "r"(s3_));             \
+        asm volatile(DV_LNR(DV_NORM_LANE_R, "vb", "")::"r"(s0_), "r"(s1_), "r"(s2_), "r"(s3_));             \
+        STORE("va", p0)                                                                                     \
+        STORE("vb", p1)                                                                                     \
+        ++rnd;                                                                                              \
+        if (rnd + 1u >= n_full) break;                                                                      \
+        ++rnd;                                                                                              \
+        a0 = a1 + SHL(P.round_elems);                                                                       \
+        p0 = next_round(p1);                                                                                \
+        continue;                                                                                           \
+      }                                                                                                     \
       MACRO("va", a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)                                                   \
-      asm volatile(DV_LN(DV_NORM_LANE, "")::"r"(s0_), "r"(s1_), "r"(s2_), "r"(s3_));                        \
-      STORE                                                                                                 \
+      asm volatile(DV_LNR(DV_NORM_LANE_R, "va", "")::"r"(s0_), "r"(s1_), "r"(s2_), "r"(s3_));               \
+      STORE("va", p0)                                                                                       \
       if (!kRounds || !(aux & UA_LOOP) || rnd + 1u >= n_full) break;                                        \
       ++rnd;                                                                                                \
       a0 += SHL(P.round_elems);                                                                             \
-      if (by_coords) {                                                                                      \
-        /* the coordinates move on by one round; the code behind the body adds the last one */              \
-        rnd_begin = rnd;                                                                                    \
-        cc[3] += P.round_elems;                                                                             \
-        _Pragma("unroll") for (int j = kMaxEnum - 1; j > 0; --j) while (cc[j] >= P.enum_size[j]) {          \
-          cc[j] -= P.enum_size[j];                                                                          \
-          cc[j - 1] += 1u;                                                                                  \
-        }                                                                                                   \
-        p0 = base + enum_offset(td, cc) + lane4;                                                            \
-      } else {                                                                                              \
-        p0 += P.round_elems;                                                                                \
-      }                                                                                                     \
+      p0 = next_round(p0);                                                                                  \
     }                                                                                                       \
     if (aux & UA_LAST) goto body_done;                                                                      \
     continue;                                                                                               \
   }
-            DV_LDNORMST_CASE(UH_LDNORMST_FIRST + FT_F32, DV_LDR32, DV_SHL2, uint32_t, DV_STV32(p0, ge))
-            DV_LDNORMST_CASE(UH_LDNORMST_FIRST + FT_F16, DV_LDR_F16, DV_SHL1, unsigned short, DV_STV16("cvt.rn.f16x2.f32", p0, ge))
-            DV_LDNORMST_CASE(UH_LDNORMST_FIRST + FT_BF16, DV_LDR_BF16, DV_SHL1, unsigned short, DV_STV16("cvt.rn.bf16x2.f32", p0, ge))
+#define DV_ST_NORM32(R, P) DV_STV32R(R, P, ge)
+#define DV_ST_NORMF16(R, P) DV_STV16R("cvt.rn.f16x2.f32", R, P, ge)
+#define DV_ST_NORMBF16(R, P) DV_STV16R("cvt.rn.bf16x2.f32", R, P, ge)
+            DV_LDNORMST_CASE(UH_LDNORMST_FIRST + FT_F32, DV_LDR32, DV_SHL2, uint32_t, DV_ST_NORM32)
+            DV_LDNORMST_CASE(UH_LDNORMST_FIRST + FT_F16, DV_LDR_F16, DV_SHL1, unsigned short, DV_ST_NORMF16)
+            DV_LDNORMST_CASE(UH_LDNORMST_FIRST + FT_BF16, DV_LDR_BF16, DV_SHL1, unsigned short, DV_ST_NORMBF16)
+#undef DV_ST_NORM32
+#undef DV_ST_NORMF16
+#undef DV_ST_NORMBF16
 #undef DV_LDNORMST_CASE
             // ---- the pieces of a residual RMSNorm + gated activation, one dispatch each (same operations, order and
             // rounding as the micro-ops they replace)
@@ -900,6 +942,8 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
 #undef DV_RING3
 #undef DV_STV16
 #undef DV_STV32
+#undef DV_STV16R
+#undef DV_STV32R
 #undef DVMB_ST
 #define DV_LDMUL2_CASE(H, MACRO, SHL)                                                                          \
   case H: {                                                                                                 \

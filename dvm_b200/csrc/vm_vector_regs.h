@@ -19,6 +19,23 @@
   M("8", "9", __VA_ARGS__) M("10", "11", __VA_ARGS__) M("12", "13", __VA_ARGS__) M("14", "15", __VA_ARGS__)
 
 #define DV_DECLARE ".reg .b32 va<16>, vb<16>, vp<4>;"
+// lane templates that name their register (R = "va" or "vb"): the looping handlers work on two rounds at a time, one in
+// each vector register, so that the loads and the arithmetic of the two overlap
+#define DV_LNR(M, R, ...)                                                                                         \
+  M(0, R, __VA_ARGS__) M(1, R, __VA_ARGS__) M(2, R, __VA_ARGS__) M(3, R, __VA_ARGS__) M(4, R, __VA_ARGS__)         \
+  M(5, R, __VA_ARGS__) M(6, R, __VA_ARGS__) M(7, R, __VA_ARGS__) M(8, R, __VA_ARGS__) M(9, R, __VA_ARGS__)         \
+  M(10, R, __VA_ARGS__) M(11, R, __VA_ARGS__) M(12, R, __VA_ARGS__) M(13, R, __VA_ARGS__) M(14, R, __VA_ARGS__)    \
+  M(15, R, __VA_ARGS__)
+#define DV_CSQR_LANE_R(i, R, X) "sub.rn.f32 " R #i ", " R #i ", %0;\n\tmul.rn.f32 " R #i ", " R #i ", " R #i ";\n\t"
+#define DV_NORM_LANE_R(i, R, X)                                                                                \
+  "sub.rn.f32 " R #i ", " R #i ", %0;\n\tmul.rn.f32 " R #i ", " R #i ", %1;\n\tmul.rn.f32 " R #i ", " R #i ", %2;\n\t" \
+  "add.rn.f32 " R #i ", " R #i ", %3;\n\t"
+#define DV_TREE16R(OP2, SLOT, R)                                                                                   \
+  "{\n\t.reg .b32 r<8>;\n\t.reg .pred p;\n\t"                                                                      \
+  OP2("r0", R "0", R "1") OP2("r1", R "2", R "3") OP2("r2", R "4", R "5") OP2("r3", R "6", R "7")                  \
+  OP2("r4", R "8", R "9") OP2("r5", R "10", R "11") OP2("r6", R "12", R "13") OP2("r7", R "14", R "15")            \
+  OP2("r0", "r0", "r1") OP2("r2", "r2", "r3") OP2("r4", "r4", "r5") OP2("r6", "r6", "r7")                          \
+  OP2("r0", "r0", "r2") OP2("r4", "r4", "r6") OP2("r0", "r0", "r4") OP2("vp" SLOT, "vp" SLOT, "r0") "}"
 
 // ---- lane templates ----------------------------------------------------------------------------------
 #define DV_BINV_LANE(i, OP) OP " va" #i ", va" #i ", vb" #i ";\n\t"
