@@ -600,7 +600,16 @@ class PyKernel(Kernel):
             return self._ws.ptr
 
         self._ws_cb = _capi.WS_ALLOC_FN(alloc)
+        self._reloc_args = (arr, len(relocs))   # what the last code generation was given (kept for repeat_codegen_launch)
         check_rc(self._lib.dvm_codegen(self._k, arr, len(relocs), self._ws_cb, None), "codegen")
+
+    def repeat_codegen_launch(self, stream=None):
+        """Shape inference + planning + emission + binding + launch once more, with the addresses of the last codegen():
+        the three C calls a framework makes when a new shape arrives (dvm_normalize is part of dvm_codegen), without this
+        front-end's own bookkeeping around them."""
+        arr, n = self._reloc_args
+        check_rc(self._lib.dvm_codegen(self._k, arr, n, self._ws_cb, None), "codegen")
+        check_rc(self._lib.dvm_launch(self._k, stream), "launch")
 
     def run(self):
         if self._run_type != "dev":
