@@ -56,6 +56,10 @@ SIGNATURES = {
     "dvm_full_i64": (c_void_p, [c_void_p, c_int64, c_void_p, c_int]),
     "dvm_full_ref": (c_void_p, [c_void_p, c_void_p, c_void_p, c_int]),
     "dvm_reshape": (c_void_p, [c_void_p, c_void_p, c_void_p]),
+    "dvm_permute": (c_void_p, [c_void_p, c_void_p, c_void_p]),
+    "dvm_slice": (c_void_p, [c_void_p, c_void_p, c_void_p, c_void_p]),
+    "dvm_slice_dim": (c_void_p, [c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "dvm_split_chunk": (c_void_p, [c_void_p, c_void_p, c_int, c_int64, c_size_t, c_size_t]),
     "dvm_copy": (c_void_p, [c_void_p, c_void_p]),
     "dvm_matmul": (c_void_p, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "dvm_comm_new": (c_void_p, []),
@@ -68,6 +72,8 @@ SIGNATURES = {
     "dvm_comm_rank": (c_int, [c_void_p]),
     "dvm_comm_size": (c_int, [c_void_p]),
     "dvm_allreduce": (c_void_p, [c_void_p, c_int, c_void_p, c_void_p]),
+    "dvm_allgather": (c_void_p, [c_void_p, c_void_p, c_void_p]),
+    "dvm_reducescatter": (c_void_p, [c_void_p, c_void_p, c_void_p]),
     "dvm_sequence_add": (c_int, [c_void_p, c_int, ctypes.c_uint32]),
     "dvm_parallel_add": (c_int, [c_void_p, c_int, ctypes.c_uint32, c_size_t]),
     "dvm_spec_next": (c_int, [c_void_p]),

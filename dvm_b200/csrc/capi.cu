@@ -187,6 +187,24 @@ dvm_object *dvm_full_ref(dvm_kernel *k, dvm_scalar *v, dvm_int_array *shape, int
 dvm_object *dvm_reshape(dvm_kernel *k, dvm_object *input, dvm_int_array *shape) {
   return DVM_OBJ_GUARD(k->kernel.Reshape(N(input), &shape->ref));
 }
+dvm_object *dvm_permute(dvm_kernel *k, dvm_object *input, dvm_int_array *dims) {
+  return DVM_OBJ_GUARD(k->kernel.Permute(N(input), &dims->ref));
+}
+dvm_object *dvm_slice(dvm_kernel *k, dvm_object *input, dvm_int_array *start, dvm_int_array *size) {
+  return DVM_OBJ_GUARD(k->kernel.Slice(N(input), &start->ref, &size->ref));
+}
+dvm_object *dvm_slice_dim(dvm_kernel *k, dvm_object *input, int dim, dvm_scalar *begin, dvm_scalar *end) {
+  return DVM_OBJ_GUARD(k->kernel.Slice(N(input), dim, &begin->ref, &end->ref));
+}
+dvm_object *dvm_split_chunk(dvm_kernel *k, dvm_object *input, int dim, int64_t split_size, size_t split_num, size_t index) {
+  return Guard(
+    [&]() {
+      if (index >= split_num) dvm::DvmException("dvm_split_chunk: index outside the split");
+      // one Kernel::Split call per distinct (input, dim, size, num) would do; a front-end asks chunk by chunk
+      return O(k->kernel.Split(N(input), dim, split_size, split_num)[index]);
+    },
+    static_cast<dvm_object *>(nullptr));
+}
 dvm_object *dvm_copy(dvm_kernel *k, dvm_object *input) { return DVM_OBJ_GUARD(k->kernel.Copy(N(input))); }
 dvm_object *dvm_matmul(dvm_kernel *k, dvm_object *lhs, dvm_object *rhs, int trans_a, int trans_b, dvm_object *bias) {
   return DVM_OBJ_GUARD(k->kernel.MatMul(N(lhs), N(rhs), trans_a != 0, trans_b != 0, bias ? N(bias) : nullptr));
@@ -222,6 +240,11 @@ int dvm_comm_rank(const dvm_comm *c) { return c->GetImpl() ? c->GetImpl()->rank 
 int dvm_comm_size(const dvm_comm *c) { return c->GetImpl() ? c->GetImpl()->size : 1; }
 dvm_object *dvm_allreduce(dvm_kernel *k, int reduce_type, dvm_object *input, dvm_comm *c) {
   return DVM_OBJ_GUARD(k->kernel.AllReduce(reduce_type, N(input), c));
+}
+
+dvm_object *dvm_allgather(dvm_kernel *k, dvm_object *input, dvm_comm *c) { return DVM_OBJ_GUARD(k->kernel.AllGather(N(input), c)); }
+dvm_object *dvm_reducescatter(dvm_kernel *k, dvm_object *input, dvm_comm *c) {
+  return DVM_OBJ_GUARD(k->kernel.ReduceScatter(N(input), c));
 }
 
 int dvm_sequence_add(dvm_kernel *k, int kernel_type, uint32_t flags) {

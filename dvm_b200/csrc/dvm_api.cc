@@ -535,11 +535,48 @@ NDObject *Kernel::Reshape(NDObject *input, IntArrayRef *shape) {
   return n;
 }
 
-NDObject *Kernel::Permute(NDObject *, IntArrayRef *) { Unsupported("Permute"); }
-NDObject *Kernel::Slice(NDObject *, IntArrayRef *, IntArrayRef *) { Unsupported("Slice"); }
-NDObject *Kernel::Slice(NDObject *, int, ScalarRef *, ScalarRef *) { Unsupported("Slice"); }
+// Views (ref: include/dvm.h:428-453, 470-479; the reference's view schedules src/schedule.h:23-167): the input's memory
+// seen through another shape, strides and offset.  No data moves where the input is a tensor in memory (a Load, another
+// view); a computed input is written to the workspace first and viewed there.
+static NDObject *View(VKernel *vk, uint8_t kind, NDObject *input) {
+  auto n = vk->NewNode(N_VIEW, input->dtype);
+  n->sub = kind;
+  n->in[0] = input;
+  return n;
+}
+NDObject *Kernel::Permute(NDObject *input, IntArrayRef *dims) {
+  auto n = View(Impl(this), VIEW_PERMUTE, input);
+  n->shape_ref = dims;
+  return n;
+}
+NDObject *Kernel::Slice(NDObject *input, IntArrayRef *start, IntArrayRef *size) {
+  auto n = View(Impl(this), VIEW_SLICE, input);
+  n->shape_ref = start;
+  n->aux_ref = size;
+  return n;
+}
+NDObject *Kernel::Slice(NDObject *input, int dim, ScalarRef *begin, ScalarRef *end) {
+  auto n = View(Impl(this), VIEW_SLICE_DIM, input);
+  n->view_dim = dim;
+  n->scalar_ref = begin;
+  n->scalar_ref2 = end;
+  return n;
+}
 NDObject *Kernel::Concat(NDObject **, size_t, int) { Unsupported("Concat"); }
-NDObject **Kernel::Split(NDObject *, int, int64_t, size_t) { Unsupported("Split"); }
+// ref: include/dvm.h:470-479 - equal chunks along `dim` (the last may be smaller); the returned array is owned by the kernel
+NDObject **Kernel::Split(NDObject *input, int dim, int64_t split_size, size_t split_num) {
+  auto vk = Impl(this);
+  vk->split_outs_.emplace_back(split_num);
+  auto &outs = vk->split_outs_.back();
+  for (size_t i = 0; i < split_num; ++i) {
+    auto n = View(vk, VIEW_SPLIT, input);
+    n->view_dim = dim;
+    n->view_arg = split_size;
+    n->view_index = static_cast<int64_t>(i);
+    outs[i] = n;
+  }
+  return outs.data();
+}
 template <typename T>
 NDObject *Kernel::OneHot(NDObject *, IntArrayRef *, int, T, T) {
   Unsupported("OneHot");
@@ -590,9 +627,20 @@ NDObject *Kernel::_AllReduce(int op_type, NDObject *input, const Comm *comm) {
   n->comm = comm->GetImpl();
   return n;
 }
-NDObject *Kernel::AllGather(NDObject *, const Comm *) { Unsupported("AllGather"); }
+// ref: Kernel::AllGather / ReduceScatter, src/dvm.cc:1657-1677 (AllGatherOp, ReduceScatterOp: src/ops_c.cc:951-962, 90-111)
+static NDObject *Collective(VKernel *vk, uint8_t coll, NDObject *input, const Comm *comm) {
+  if (comm == nullptr || comm->GetImpl() == nullptr) DvmException("a collective needs an initialised Comm");
+  if (input->dtype == kBool || input->dtype == kInt64) DvmException("collectives on bool / int64 tensors are not supported");
+  auto n = vk->NewNode(N_ALLREDUCE, input->dtype);
+  n->sub = kSum;
+  n->coll = coll;
+  n->in[0] = input;
+  n->comm = comm->GetImpl();
+  return n;
+}
+NDObject *Kernel::AllGather(NDObject *input, const Comm *comm) { return Collective(Impl(this), 2, input, comm); }
 NDObject *Kernel::AllGatherV2(NDObject *, const Comm *) { Unsupported("AllGatherV2"); }
-NDObject *Kernel::ReduceScatter(NDObject *, const Comm *) { Unsupported("ReduceScatter"); }
+NDObject *Kernel::ReduceScatter(NDObject *input, const Comm *comm) { return Collective(Impl(this), 1, input, comm); }
 NDObject *Kernel::ExtOut(NDObject *, int) { Unsupported("ExtOut"); }
 // ref: src/dvm.cc:1721-1725 (kernel.h:405).  In the reference the call moves a speculative vector kernel to its next
 // fallback stage: a hint where to cut if the graph cannot stay one kernel.  It never changes what the graph computes.

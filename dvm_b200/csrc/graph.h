@@ -51,11 +51,15 @@ enum NodeKind : uint8_t {
   N_COPY,
   N_REDUCE,     // sub = ReduceType
   N_MATMUL,
-  N_ALLREDUCE,  // sub = ReduceType; the value of in[0] combined over the ranks of `comm`
+  N_VIEW,       // Permute / Slice / Split: the input's memory seen through another shape, strides and offset
+  N_ALLREDUCE,  // a collective over the ranks of `comm`: `coll` 0 all-reduce (sub = ReduceType), 1 reduce-scatter (sum),
+                // 2 all-gather along the leading dim
 };
 
 // Scalar-operand arithmetic kinds (the reference's BinaryScalarOp opcodes ADDS/MULS/DIVS/SDIV/MAXS/MINS,
 // src/vm_gpu.cu:1178-1297).
+enum ViewKind : uint8_t { VIEW_PERMUTE = 0, VIEW_SLICE, VIEW_SLICE_DIM, VIEW_SPLIT };
+
 enum ScalarBin : uint8_t { SB_ADD = 0, SB_MUL, SB_DIV, SB_SDIV, SB_MAX, SB_MIN };
 
 class NDObject {
@@ -87,6 +91,16 @@ class NDObject {
   int64_t ws_off = -1;
   int64_t addr_off = 0;               // bytes added to the address above (a rank's row block of a tensor)
   const Communicator *comm = nullptr; // N_ALLREDUCE: the communicator (borrowed from the caller's Comm)
+  uint8_t coll = 0;                   // N_ALLREDUCE: which collective (see NodeKind)
+  // N_VIEW: sub = ViewKind.  Permute: shape_ref = dims.  Slice: shape_ref = start, aux_ref = size.  Slice along one dim:
+  // view_dim, scalar_ref = begin, scalar_ref2 = end.  Split: view_dim, view_arg = chunk size, view_index = which chunk.
+  IntArrayRef *aux_ref = nullptr;
+  ScalarRef *scalar_ref2 = nullptr;
+  int view_dim = 0;
+  int64_t view_arg = 0, view_index = 0;
+  // results of Normalize() for a view: per result dim the input dim it walks and the element offset into the input
+  int view_from[kMaxRank] = {0};
+  int64_t view_start[kMaxRank] = {0};   // per INPUT dim: first index taken
   // results of Normalize()
   Shape shape;
   IntArrayRef out_ref;                // view of `shape` handed out by Kernel::GetShape
@@ -179,6 +193,7 @@ class VKernel {
   std::vector<NDObject *> nodes_;          // append (= topological) order
   std::vector<std::unique_ptr<Stage>> stages_;
   std::vector<NDObject *> synth_;          // planner-made nodes (clones, workspace temporaries), owned
+  std::vector<std::vector<NDObject *>> split_outs_;   // arrays handed out by Kernel::Split (valid for the kernel's life)
   size_t ws_bytes_ = 0;
   int cur_sub_ = 0;                        // sub-kernel that NewNode() tags ops with (SequenceAdd / ParallelAdd advance it)
   void *workspace_ = nullptr;

@@ -4,6 +4,9 @@
 // (outermost first); NumPy right-aligned broadcasting rules apply.
 #include <string>
 
+#include <algorithm>
+
+#include "comm.h"
 #include "graph.h"
 
 namespace dvm {
@@ -135,7 +138,91 @@ void InferShape(NDObject *n) {
       n->shape = o;
       break;
     }
-    case N_ALLREDUCE: n->shape = n->in[0]->shape; break;
+    case N_VIEW: {
+      const Shape &in = n->in[0]->shape;
+      Shape o = in;
+      for (int i = 0; i < in.rank; ++i) {
+        n->view_from[i] = i;
+        n->view_start[i] = 0;
+      }
+      auto norm_dim = [&](int d) {
+        if (d < 0) d += in.rank;
+        if (d < 0 || d >= in.rank) Fail(n, "view dimension out of range");
+        return d;
+      };
+      auto scalar_int = [&](const ScalarRef *r) -> int64_t {
+        if (r == nullptr) Fail(n, "slice bound missing");
+        return r->type == kFloat32 ? static_cast<int64_t>(r->f32) : (r->type == kInt32 ? r->i32 : r->i64);
+      };
+      switch (n->sub) {
+        case VIEW_PERMUTE: {   // result dim i walks input dim dims[i] (ref: include/dvm.h:428-434)
+          if (n->shape_ref == nullptr || static_cast<int>(n->shape_ref->size) != in.rank) Fail(n, "permute needs one axis per dim");
+          bool seen[kMaxRank] = {false};
+          for (int i = 0; i < in.rank; ++i) {
+            const int d = norm_dim(static_cast<int>(n->shape_ref->data[i]));
+            if (seen[d]) Fail(n, "permute axes repeat");
+            seen[d] = true;
+            n->view_from[i] = d;
+            o.d[i] = in.d[d];
+          }
+          break;
+        }
+        case VIEW_SLICE: {     // ref: include/dvm.h:436-443
+          if (n->shape_ref == nullptr || n->aux_ref == nullptr || static_cast<int>(n->shape_ref->size) != in.rank ||
+              static_cast<int>(n->aux_ref->size) != in.rank)
+            Fail(n, "slice needs a start and a size per dim");
+          for (int i = 0; i < in.rank; ++i) {
+            const int64_t st = n->shape_ref->data[i], sz = n->aux_ref->data[i];
+            if (st < 0 || sz < 0 || st + sz > in.d[i]) Fail(n, "slice outside its input");
+            n->view_start[i] = st;
+            o.d[i] = sz;
+          }
+          break;
+        }
+        case VIEW_SLICE_DIM: { // begin / end along one dim, negative indices count from the end (ref: include/dvm.h:445-453)
+          const int d = norm_dim(n->view_dim);
+          int64_t b = scalar_int(n->scalar_ref), e = scalar_int(n->scalar_ref2);
+          if (b < 0) b += in.d[d];
+          if (e < 0) e += in.d[d];
+          b = std::min<int64_t>(std::max<int64_t>(b, 0), in.d[d]);
+          e = std::min<int64_t>(std::max<int64_t>(e, b), in.d[d]);
+          n->view_start[d] = b;
+          o.d[d] = e - b;
+          break;
+        }
+        default: {             // VIEW_SPLIT: chunk `view_index` of size `view_arg` along a dim, the last one may be smaller
+          const int d = norm_dim(n->view_dim);
+          const int64_t b = n->view_index * n->view_arg;
+          if (n->view_arg <= 0 || b >= in.d[d]) Fail(n, "split chunk outside its input");
+          n->view_start[d] = b;
+          o.d[d] = std::min<int64_t>(n->view_arg, in.d[d] - b);
+          break;
+        }
+      }
+      n->shape = o;
+      break;
+    }
+    case N_ALLREDUCE: {
+      n->shape = n->in[0]->shape;
+      const int ranks = n->comm ? n->comm->size : 1;
+      Shape &s = n->shape;
+      if (n->coll == 2) {   // all-gather: the ranks' tensors stacked along the leading dim (src/ops_c.cc:951-962)
+        if (s.rank < 1) Fail(n, "all-gather of a scalar");
+        s.d[0] *= ranks;
+      } else if (n->coll == 1) {   // reduce-scatter: rank r keeps block r of the leading dim (src/ops_c.cc:90-111)
+        if (s.rank < 1 || s.d[0] % ranks != 0) Fail(n, "reduce-scatter needs a leading dim divisible by the number of ranks");
+        if (s.d[0] == ranks) {
+          s.d[0] = 1;
+        } else {
+          if (s.rank >= kMaxRank) Fail(n, "reduce-scatter result exceeds the rank limit");
+          for (int i = s.rank; i > 1; --i) s.d[i] = s.d[i - 1];
+          s.d[1] = s.d[0] / ranks;
+          s.d[0] = 1;
+          s.rank += 1;
+        }
+      }
+      break;
+    }
     case N_MATMUL: {
       const Shape &a = n->in[0]->shape, &b = n->in[1]->shape;
       if (a.rank < 2 || b.rank < 2) Fail(n, "matmul operands need rank >= 2");

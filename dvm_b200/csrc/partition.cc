@@ -93,7 +93,11 @@ struct Planner {
   bool InMemory(const NDObject *n) const { return n->kind == N_LOAD || mem.count(n) != 0; }
   // ... and as one contiguous tensor (what the tensor-core stages, collectives and reshapes-as-views need): a strided
   // Load only after it has been copied out to the workspace
-  bool InPlainMemory(const NDObject *n) const { return mem.count(n) != 0 || (n->kind == N_LOAD && !n->strided); }
+  bool InPlainMemory(const NDObject *n) const {
+    auto it = mem.find(n);
+    if (it != mem.end()) return !it->second->strided;
+    return n->kind == N_LOAD && !n->strided;
+  }
 
   // A Load node (planner-made) reading value `n`, which must be InMemory().
   NDObject *MemLoad(const NDObject *n) {
@@ -297,7 +301,7 @@ struct Planner {
   // Make sure `v` is addressable in memory before a tensor-core stage reads it.
   void RequireInMemory(NDObject *v, const char *what) {
     if (InPlainMemory(v)) return;
-    if (v->kind == N_BROADCAST || v->kind == N_BROADCAST_S || v->kind == N_LOAD) {   // (a strided Load is copied out)
+    if (v->kind == N_BROADCAST || v->kind == N_BROADCAST_S || InMemory(v)) {   // (a strided Load or view is copied out)
       Materialize(v);
       return;
     }
@@ -528,7 +532,7 @@ struct Planner {
     // every operand must be addressable; only then commit
     NDObject *ins[3] = {m1->in[0], m1->in[1], m2->in[1]};
     for (auto v : ins)
-      if (!InPlainMemory(v) && !in_cur.count(v) && v->kind != N_LOAD) return false;
+      if (!InPlainMemory(v) && !in_cur.count(v) && !InMemory(v)) return false;
     for (auto v : ins) RequireInMemory(v, "attention operand");
     auto st = std::make_unique<Stage>();
     st->kind = STAGE_ATTENTION;
@@ -556,6 +560,38 @@ struct Planner {
     for (auto n : chain) done.insert(n);
     done.insert(m2);
     return true;
+  }
+
+  // ---- views ------------------------------------------------------------------------------------------------
+  // Permute / Slice / Split: no stage, the result is the input's memory read through other strides.  A computed input
+  // is stored to the workspace first (closing the open area), a broadcast is written out.
+  void PlaceView(NDObject *n) {
+    NDObject *src = n->in[0];
+    if (!InMemory(src)) {
+      if (src->kind == N_BROADCAST || src->kind == N_BROADCAST_S) {
+        Materialize(src);
+      } else if (in_cur.count(src)) {
+        CloseCur();   // the view reads the value from outside the area, so the area stores it to the workspace
+      }
+      if (!InMemory(src)) DvmException("stage planner: view of a value that is not in memory");
+    }
+    NDObject *ld = MemLoad(src);
+    const Shape &ps = src->shape;
+    int64_t pstride[kMaxRank];
+    int64_t dense = 1;
+    for (int i = ps.rank - 1; i >= 0; --i) {
+      pstride[i] = ld->strided ? ld->stride[i] : dense;
+      dense *= ps.d[i];
+    }
+    int64_t off = 0;
+    for (int i = 0; i < ps.rank; ++i) off += n->view_start[i] * pstride[i];
+    ld->shape = n->shape;
+    for (int i = 0; i < n->shape.rank; ++i) ld->stride[i] = pstride[n->view_from[i]];
+    ld->strided = true;
+    ld->stride_ref = nullptr;
+    ld->addr_off += off * ItemSize(n->dtype);
+    mem[n] = ld;
+    done.insert(n);
   }
 
   // ---- collectives -----------------------------------------------------------------------------------------
@@ -714,7 +750,7 @@ struct Planner {
   void PlaceAllReduce(NDObject *n) {
     NDObject *v = n->in[0];
     if (!InPlainMemory(v)) {
-      if (v->kind == N_BROADCAST || v->kind == N_BROADCAST_S || v->kind == N_LOAD) {
+      if (v->kind == N_BROADCAST || v->kind == N_BROADCAST_S || InMemory(v)) {
         Materialize(v);
       } else {
         CloseCur();   // the open area stores v to the workspace: this node reads it from outside the area
@@ -723,15 +759,23 @@ struct Planner {
     } else {
       CloseCur();
     }
-    if (TryShardedTail(n)) return;
-    // general form: all ranks receive the whole combined tensor in a workspace temporary
+    if (n->coll == 0 && TryShardedTail(n)) return;
+    // general form: the result goes to a workspace temporary
     NDObject *src = MemLoad(v);
     NDObject *dst = SynthLoad(n, n->shape);
     dst->ws_off = static_cast<int64_t>(AllocWs(n));
-    const uint64_t count = static_cast<uint64_t>(n->shape.numel());
-    const uint64_t bytes = count * ItemSize(n->dtype);
-    PushCollective(dvmb::COLL_ALL_REDUCE, n, src, 0, dst, 0, count,
-                   n->comm->size > 1 ? 2 * bytes * (n->comm->size - 1) / n->comm->size : 0);
+    const uint64_t ranks = static_cast<uint64_t>(n->comm->size);
+    if (n->coll == 1) {   // reduce-scatter: this rank's block of the sum
+      const uint64_t blk = static_cast<uint64_t>(n->shape.numel());
+      PushCollective(dvmb::COLL_REDUCE_SCATTER, n, src, 0, dst, 0, blk, blk * ItemSize(n->dtype) * (ranks - 1));
+    } else if (n->coll == 2) {   // all-gather: every rank's tensor, stacked
+      const uint64_t blk = static_cast<uint64_t>(v->shape.numel());
+      PushCollective(dvmb::COLL_ALL_GATHER, n, src, 0, dst, 0, blk, blk * ItemSize(n->dtype) * (ranks - 1));
+    } else {
+      const uint64_t count = static_cast<uint64_t>(n->shape.numel());
+      const uint64_t bytes = count * ItemSize(n->dtype);
+      PushCollective(dvmb::COLL_ALL_REDUCE, n, src, 0, dst, 0, count, ranks > 1 ? 2 * bytes * (ranks - 1) / ranks : 0);
+    }
     mem[n] = dst;
     done.insert(n);
   }
@@ -781,7 +825,7 @@ struct Planner {
             CloseCur();
           }
           if (!InPlainMemory(src)) {
-            if (src->kind != N_BROADCAST && src->kind != N_BROADCAST_S && src->kind != N_LOAD)
+            if (src->kind != N_BROADCAST && src->kind != N_BROADCAST_S && !InMemory(src))
               DvmException("stage planner: reshape of a value that is not in memory");
             // a broadcast is re-created by its readers: a reshape that only adds or drops unit dims joins an area,
             // any other one needs the broadcast written out first
@@ -812,6 +856,7 @@ struct Planner {
           if (!TryAttention(n)) PlaceMatMul(n);
           break;
         case N_ALLREDUCE: PlaceAllReduce(n); break;
+        case N_VIEW: PlaceView(n); break;
         default: AddVector(n); break;
       }
     }

@@ -1221,6 +1221,7 @@ struct Compiler {
     for (auto n : ops) {
       if (n->kind == N_MATMUL) throw Fail{"MatMul inside a vector stage"};
       if (n->kind == N_ALLREDUCE) throw Fail{"a collective inside a vector stage"};
+      if (n->kind == N_VIEW) throw Fail{"a view inside a vector stage"};
     }
     AlignAxes();
     Classify();

@@ -85,7 +85,7 @@ size_t VKernel::Compile() {
   }
   bool has_matmul = false, has_empty = false, stacked = false;
   for (auto n : ops) {
-    has_matmul |= n->kind == N_MATMUL || n->kind == N_ALLREDUCE;   // (anything that needs the stage planner)
+    has_matmul |= n->kind == N_MATMUL || n->kind == N_ALLREDUCE || n->kind == N_VIEW;   // (anything that needs the stage planner)
     has_empty |= n->shape.numel() == 0;   // the planner drops empty tensors and keeps what still has elements
     stacked |= n->sub_kernel != ops.front()->sub_kernel;   // kSequence / kParallel: every sub-kernel gets launches of its own
   }
@@ -224,7 +224,14 @@ static const char *KindName(const NDObject *n) {
     case N_RESHAPE: return "Reshape";
     case N_COPY: return "Copy";
     case N_REDUCE: return red[n->sub];
-    case N_ALLREDUCE: return n->sub == kSum ? "AllReduceSum" : (n->sub == kMax ? "AllReduceMax" : "AllReduceMin");
+    case N_VIEW: {
+      static const char *views[] = {"Permute", "Slice", "Slice", "Split"};
+      return views[n->sub & 3];
+    }
+    case N_ALLREDUCE:
+      if (n->coll == 1) return "ReduceScatter";
+      if (n->coll == 2) return "AllGather";
+      return n->sub == kSum ? "AllReduceSum" : (n->sub == kMax ? "AllReduceMax" : "AllReduceMin");
     default: return "MatMul";
   }
 }

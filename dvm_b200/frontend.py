@@ -255,6 +255,30 @@ class Kernel:
     def reshape(self, input, shape):
         return self._obj(self._lib.dvm_reshape(self._k, input._h, self._shape_ref(shape)._h), "reshape")
 
+    # -- views of the input's memory (KernelPy::Permute / Slice / SliceDim / Split, include/dvm_py.h:163-186)
+    def permute(self, input, dims):
+        return self._obj(self._lib.dvm_permute(self._k, input._h, self._shape_ref(list(dims))._h), "permute")
+
+    def slice(self, input, begin, size):
+        return self._obj(self._lib.dvm_slice(self._k, input._h, self._shape_ref(list(begin))._h,
+                                             self._shape_ref(list(size))._h), "slice")
+
+    def _index_ref(self, v):
+        if isinstance(v, ScalarRef):
+            return v
+        ref = ScalarRef()
+        ref.update(int(v))
+        self._keep.append(ref)
+        return ref
+
+    def slice_dim(self, input, dim, begin, end):
+        return self._obj(self._lib.dvm_slice_dim(self._k, input._h, int(dim), self._index_ref(begin)._h,
+                                                 self._index_ref(end)._h), "slice_dim")
+
+    def split(self, input, dim, split_size, split_num):
+        return [self._obj(self._lib.dvm_split_chunk(self._k, input._h, int(dim), int(split_size), int(split_num), i), "split")
+                for i in range(int(split_num))]
+
     def copy(self, input):
         return self._obj(self._lib.dvm_copy(self._k, input._h), "copy")
 
@@ -449,6 +473,18 @@ class PyKernel(Kernel):
         if _ProcessComm.handle is None:
             raise DvmError("allreduce before init_comm()")
         return self._obj(self._lib.dvm_allreduce(self._k, codes[type], input._h, _ProcessComm.handle), "allreduce")
+
+    def allgather(self, input):
+        """RtKernelPy::AllGather (src/pybind_api.cc:578): every rank's tensor stacked along the leading dim."""
+        if _ProcessComm.handle is None:
+            raise DvmError("allgather before init_comm()")
+        return self._obj(self._lib.dvm_allgather(self._k, input._h, _ProcessComm.handle), "allgather")
+
+    def reducescatter(self, input):
+        """RtKernelPy::ReduceScatter (src/pybind_api.cc:574-576): this rank's block of the sum over the ranks."""
+        if _ProcessComm.handle is None:
+            raise DvmError("reducescatter before init_comm()")
+        return self._obj(self._lib.dvm_reducescatter(self._k, input._h, _ProcessComm.handle), "reducescatter")
 
     def __init__(self, ker_type="", run_type="dev", dev_id=0):
         ktype, flags = parse_kernel_type(ker_type)

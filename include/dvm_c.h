@@ -81,6 +81,12 @@ DVM_C_API dvm_object *dvm_full_f32(dvm_kernel *k, float v, dvm_int_array *shape,
 DVM_C_API dvm_object *dvm_full_i64(dvm_kernel *k, int64_t v, dvm_int_array *shape, int dtype);
 DVM_C_API dvm_object *dvm_full_ref(dvm_kernel *k, dvm_scalar *v, dvm_int_array *shape, int dtype);
 DVM_C_API dvm_object *dvm_reshape(dvm_kernel *k, dvm_object *input, dvm_int_array *shape);    /* dvm.h:434 */
+/* views of the input's memory: Kernel::Permute (dvm.h:434), Slice (:443, :453), one chunk of Kernel::Split (:479) */
+DVM_C_API dvm_object *dvm_permute(dvm_kernel *k, dvm_object *input, dvm_int_array *dims);
+DVM_C_API dvm_object *dvm_slice(dvm_kernel *k, dvm_object *input, dvm_int_array *start, dvm_int_array *size);
+DVM_C_API dvm_object *dvm_slice_dim(dvm_kernel *k, dvm_object *input, int dim, dvm_scalar *begin, dvm_scalar *end);
+DVM_C_API dvm_object *dvm_split_chunk(dvm_kernel *k, dvm_object *input, int dim, int64_t split_size, size_t split_num,
+                                      size_t index);
 DVM_C_API dvm_object *dvm_copy(dvm_kernel *k, dvm_object *input);                             /* dvm.h:466 */
 DVM_C_API dvm_object *dvm_matmul(dvm_kernel *k, dvm_object *lhs, dvm_object *rhs, int trans_a, int trans_b,
                                  dvm_object *bias);                                           /* dvm.h:509 */
@@ -104,6 +110,10 @@ DVM_C_API int dvm_comm_size(const dvm_comm *c);
 /* the value of `input` combined (reduce_type: 0 sum, 1 max, 2 min) over the ranks of `c` (KernelPy::AllReduce,
  * include/dvm_py.h; python/dvm/_dvm_py.pyi:166) */
 DVM_C_API dvm_object *dvm_allreduce(dvm_kernel *k, int reduce_type, dvm_object *input, dvm_comm *c);
+/* every rank's tensor stacked along the leading dim (Kernel::AllGather, dvm.h:225); this rank's block of the sum along the
+ * leading dim, shape [1, d0 / ranks, ...] or [1, d1, ...] when d0 equals the number of ranks (Kernel::ReduceScatter, :227) */
+DVM_C_API dvm_object *dvm_allgather(dvm_kernel *k, dvm_object *input, dvm_comm *c);
+DVM_C_API dvm_object *dvm_reducescatter(dvm_kernel *k, dvm_object *input, dvm_comm *c);
 
 /* ---- stacked kernels and marks ---- */
 /* start the next stage of a kSequence kernel (Kernel::SequenceAdd, dvm.h:559; KernelPy::SeqAdd, include/dvm_py.h) */

@@ -62,15 +62,32 @@ int main(int argc, char **argv) {
   try {
     dvm::Kernel bad;
     bad.Reset(dvm::kVector, 0);
-    std::vector<int64_t> perm{1, 0};
-    dvm::IntArrayRef perm_ref(perm);
-    bad.Permute(bad.Load(nullptr, &shape_ref, dvm::kFloat32), &perm_ref);
+    dvm::NDObject *parts[2] = {bad.Load(nullptr, &shape_ref, dvm::kFloat32), bad.Load(nullptr, &shape_ref, dvm::kFloat32)};
+    bad.Concat(parts, 2, 0);
   } catch (const std::runtime_error &e) {
     threw = std::strstr(e.what(), "DVM EXCEPTION") != nullptr;
   }
   if (!threw) {
-    std::printf("FAIL: Permute did not raise DvmException\n");
+    std::printf("FAIL: Concat did not raise DvmException\n");
     return 1;
+  }
+  {
+    // a view: the transpose of a Load is its memory read through permuted strides (no copy, no workspace)
+    dvm::Kernel v;
+    v.Reset(dvm::kVector, 0);
+    std::vector<int64_t> perm{1, 0};
+    dvm::IntArrayRef perm_ref(perm);
+    auto t = v.Permute(v.Load(nullptr, &shape_ref, dvm::kFloat32), &perm_ref);
+    v.Store(nullptr, v.Binary<dvm::kAdd>(t, 1.0f));
+    if (v.PreCodeGen() != 0) {
+      std::printf("FAIL: a permuted Load needed a workspace\n");
+      return 1;
+    }
+    dvm::IntArrayRef *ts = v.GetShape(t);
+    if (ts->size != 2 || ts->data[0] != cols || ts->data[1] != rows) {
+      std::printf("FAIL: inferred shape of the transpose\n");
+      return 1;
+    }
   }
 
   std::vector<float> hx(rows * cols), hy(rows * cols), hz(rows * cols), hs(rows);

@@ -274,3 +274,23 @@ def test_views_carry_their_strides_into_the_tensor_table():
         k = dvm.PyKernel("vector", "das", 0)
         k.store(k.view_load([8, 16], [16], dvm.float32))      # one stride per dim
         k.codegen()
+
+
+def test_view_ops_infer_shapes_and_plan_without_a_copy():
+    # Kernel::Permute / Slice / Split are views of a tensor in memory (include/dvm.h:428-453, 470-479)
+    k = dvm.PyKernel("vector", "das", 0)
+    x = k.load([6, 40, 96], dvm.float32)
+    p = k.permute(x, [2, 0, 1])
+    s = k.slice(x, [1, 8, 16], [4, 20, 64])
+    d = k.slice_dim(x, 1, -10, 40)
+    chunks = k.split(x, 2, 40, 3)
+    for v in [p, s, d] + chunks:
+        k.store(k.add(v, 1.0))
+    k.codegen()
+    assert p.shape() == (96, 6, 40) and s.shape() == (4, 20, 64) and d.shape() == (6, 10, 96)
+    assert [c.shape() for c in chunks] == [(6, 40, 40), (6, 40, 40), (6, 40, 16)]
+    assert "workspace_bytes=0" in k.inspect()          # no copies: every view reads the Load's own memory
+    with pytest.raises(RuntimeError):
+        bad = dvm.PyKernel("vector", "das", 0)
+        bad.store(bad.slice(bad.load([4, 4], dvm.float32), [2, 2], [4, 4]))
+        bad.codegen()

@@ -50,12 +50,30 @@ def _run_rank(rank, world, uid, m, n, k):
     return t.output(y), t.das()
 
 
+def _check_scatter_gather(rank, world):
+    """ReduceScatter, AllGather and AllReduce(max) as graph ops, against NumPy on every rank's inputs."""
+    from dvm_b200.tester import Tester
+    rows = 4 * world
+    xs = [np.random.default_rng(100 + r).normal(size=(rows, 96)).astype(np.float32) for r in range(world)]
+    t = Tester("vector", run_mode="dev")
+    x = t.load(xs[rank])
+    s_rs = t.store(t.add(t.reducescatter(x), 1.0))
+    s_ag = t.store(t.allgather(t.mul(x, 0.5)))
+    s_mx = t.store(t.allreduce("max", x))
+    t.run()
+    total = np.sum(xs, axis=0)
+    assert_close(t.output(s_rs), total[rank * 4:(rank + 1) * 4][None] + 1.0, 1e-5, "reduce-scatter")
+    assert_close(t.output(s_ag), np.concatenate([a * np.float32(0.5) for a in xs], axis=0), 0.0, "all-gather")
+    assert_close(t.output(s_mx), np.max(xs, axis=0), 0.0, "all-reduce max")
+
+
 def test_one_rank_communicator_runs_the_all_reduce_stage():
     from dvm_b200 import frontend
     m, n, k = 256, 512, 128
     got, das = _run_rank(0, 1, frontend.comm_unique_id(), m, n, k)
     assert "cmain.nccl(all_reduce.sum" in das
     assert_close(got, _oracle(*_inputs(m, n, k)), TOL_HALF, "K-split graph on one rank")
+    _check_scatter_gather(0, 1)
 
 
 _CHILD = """
@@ -75,6 +93,7 @@ got, das = T._run_rank(rank, world, box[0], m, n, k)
 assert "reduce_scatter" in das and "all_gather" in das, das
 want = T._oracle(*T._inputs(m, n, k))
 T.assert_close(got, want, T.TOL_HALF, "rank %d of %d" % (rank, world))
+T._check_scatter_gather(rank, world)
 dist.barrier()
 print("RANK_OK", rank)
 """

@@ -77,6 +77,26 @@ def test_all_reduce_needs_a_communicator_and_a_supported_type():
         kk.allreduce("sum", kk.greater(x, 0.0))   # bool
 
 
+def test_reduce_scatter_and_all_gather_shapes_and_plans():
+    # Kernel::ReduceScatter / AllGather (include/dvm.h:225-227; shapes: src/ops_c.cc:90-111, 951-962)
+    dvm.PyKernel.init_comm(2, 4, "dummy")
+    kk = dvm.PyKernel("vector", "das", 0)
+    x = kk.load([64, 48], dvm.float32)
+    rs = kk.reducescatter(kk.mul(x, 2.0))
+    ag = kk.allgather(kk.add(x, 1.0))
+    one = kk.reducescatter(kk.load([4, 48], dvm.float32))      # leading dim == ranks: one row per rank
+    s1, s2, s3 = kk.store(kk.add(rs, 1.0)), kk.store(ag), kk.store(one)
+    kk.codegen()
+    assert rs.shape() == (1, 16, 48) and ag.shape() == (256, 48) and one.shape() == (1, 48)
+    plan = _collectives(kk.das())
+    kinds = sorted((c["kind"], c["count"]) for c in plan)
+    assert kinds == [("all_gather", 64 * 48), ("reduce_scatter", 48), ("reduce_scatter", 16 * 48)], kinds
+    with pytest.raises(RuntimeError):
+        bad = dvm.PyKernel("vector", "das", 0)
+        bad.store(bad.reducescatter(bad.load([10, 8], dvm.float32)))   # 10 rows over 4 ranks
+        bad.codegen()
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))

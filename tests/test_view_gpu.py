@@ -102,3 +102,38 @@ def test_view_feeding_a_matmul_is_copied_out_first():
     assert t.das().count("vmain") == 1 and t.das().count("mmain") == 1
     want = big[:, :128].astype(np.float16).astype(np.float32) @ b.astype(np.float16).astype(np.float32)
     assert_close(t.output(s), want, TOL_HALF, "MatMul of a window")
+
+
+def test_permute_slice_and_split_of_a_tensor_in_memory():
+    """Kernel::Permute / Slice / Split (include/dvm.h:428-453, 470-479) of a Load: pure views, no copy."""
+    rng = np.random.default_rng(7)
+    a = rng.normal(size=(6, 40, 96)).astype(np.float32)
+    t = Tester("vector")
+    x = t.load(a)
+    p = t.permute(x, [2, 0, 1])
+    s1 = t.store(t.add(p, 1.0))
+    s2 = t.store(t.mul(t.slice(x, [1, 8, 16], [4, 20, 64]), 2.0))
+    s3 = t.store(t.sum(t.slice_dim(x, 1, -10, 40), (2,), True))
+    chunks = t.split(x, 2, 40, 3)                       # 40 + 40 + 16 columns
+    s4 = [t.store(t.mul(c, 3.0)) for c in chunks]
+    t.run()
+    assert_close(t.output(s1), a.transpose(2, 0, 1) + 1.0, TOL_FP32, "permute")
+    assert_close(t.output(s2), a[1:5, 8:28, 16:80] * 2.0, TOL_FP32, "slice")
+    assert_close(t.output(s3), a[:, 30:40].sum(axis=2, keepdims=True), 1e-4, "slice along one dim")
+    for i, s in enumerate(s4):
+        assert_close(t.output(s), a[:, :, 40 * i:40 * (i + 1)] * 3.0, TOL_FP32, "split chunk %d" % i)
+
+
+def test_views_of_computed_values_and_of_views():
+    rng = np.random.default_rng(8)
+    a = rng.normal(size=(64, 128)).astype(np.float32)
+    b = rng.normal(size=(128, 64)).astype(np.float32)
+    t = Tester("split")
+    y = t.add(t.load(a), 1.0)                            # computed: written to the workspace, then viewed
+    yt = t.permute(y, [1, 0])
+    s1 = t.store(t.mul(yt, t.load(b)))
+    s2 = t.store(t.exp(t.slice(yt, [16, 8], [32, 40])))  # a view of a view
+    t.run()
+    want = (a + 1.0).T
+    assert_close(t.output(s1), want * b, TOL_FP32, "permute of a computed value")
+    assert_close(t.output(s2), np.exp(want[16:48, 8:48]), TOL_FP32, "slice of a permuted value")
