@@ -560,7 +560,9 @@ def dynamic_shape_jit():
         lib_sync(None)
         lo, hi, mean = k.perf(warmup=2, reps=10)
         b2b = time_launches(k, 20, 2, None) / 20 * 1e3
-        out[str(t)] = {"jit_us": jit, "shape_to_enqueued_us": enq, "kernel_us": b2b, "kernel_us_single_launch": mean}
+        nbytes = 49152 * t + 8192   # h, r, g, u in, two results out (bf16 [t, 4096] each) and the weight row
+        out[str(t)] = {"jit_us": jit, "shape_to_enqueued_us": enq, "kernel_us": b2b, "kernel_us_single_launch": mean,
+                       "gbs": nbytes / (b2b * 1e-6) / 1e9, "frac_of_measured_peak": nbytes / (b2b * 1e-6) / 1e9 / measured_peak("c3")[0]}
     k.release_io()
     return out
 
