@@ -40,6 +40,8 @@ struct MmParam {
   uint32_t mma_slot;
   uint32_t num_temps;
   uint32_t group_m;         // row blocks swept together over all column blocks (L2 reuse of the A panel); set by the launcher
+  uint32_t fast_store_slot; // set by the launcher: the post-fusion program is just "store the product to tensor <slot>" (in the
+                            // operand type or widened to fp32), which the kernel does without interpreting; 0xffffffff otherwise
   EpiTensor tensor[kMmMaxEpiTensors];
   uint64_t epilogue[kMmMaxEpilogueWords];
 };

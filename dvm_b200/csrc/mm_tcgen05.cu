@@ -87,11 +87,93 @@ __device__ __forceinline__ void tile_coords(uint32_t t, uint32_t mblocks, uint32
 
 // Bias, rounding to the operand type and the post-fusion program for one 16-column strip of one row.
 __device__ __forceinline__ void finish_strip(const MmParam &P, const EpiPos &pos, uint32_t (&r)[16]) {
+  const bool whole = pos.valid == 16u;
+  if (P.bias_ptr != 0) {
+    const uint32_t bsh = P.bias_dtype == T_F32 ? 2u : 1u;
+    if (whole && ((P.bias_ptr + ((uint64_t)pos.col << bsh)) & 15u) == 0) {
+      // sixteen bias values as 16-byte loads
+      if (bsh == 2u) {
+        const uint4 *bp = reinterpret_cast<const uint4 *>(P.bias_ptr) + (pos.col >> 2);
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    float x = __uint_as_float(r[i]);
-    if (P.bias_ptr != 0 && (uint32_t)i < pos.valid) x += load_bias(P, pos.col + i);
-    r[i] = __float_as_uint(round_operand_type(P.in_dtype, x));
+        for (int g = 0; g < 4; ++g) {
+          const uint4 b = __ldg(bp + g);
+          r[4 * g + 0] = __float_as_uint(__uint_as_float(r[4 * g + 0]) + __uint_as_float(b.x));
+          r[4 * g + 1] = __float_as_uint(__uint_as_float(r[4 * g + 1]) + __uint_as_float(b.y));
+          r[4 * g + 2] = __float_as_uint(__uint_as_float(r[4 * g + 2]) + __uint_as_float(b.z));
+          r[4 * g + 3] = __float_as_uint(__uint_as_float(r[4 * g + 3]) + __uint_as_float(b.w));
+        }
+      } else {
+        const uint4 *bp = reinterpret_cast<const uint4 *>(P.bias_ptr) + (pos.col >> 3);
+        const uint4 b0 = __ldg(bp), b1 = __ldg(bp + 1);
+        const uint32_t w[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float lo, hi;
+          if (P.bias_dtype == T_BF16) {
+            lo = __uint_as_float(w[i] << 16);
+            hi = __uint_as_float(w[i] & 0xffff0000u);
+          } else {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+            lo = f.x;
+            hi = f.y;
+          }
+          r[2 * i] = __float_as_uint(__uint_as_float(r[2 * i]) + lo);
+          r[2 * i + 1] = __float_as_uint(__uint_as_float(r[2 * i + 1]) + hi);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        if ((uint32_t)i < pos.valid) r[i] = __float_as_uint(__uint_as_float(r[i]) + load_bias(P, pos.col + i));
+    }
+  }
+  // The product in the operand type: packed two at a time (hardware round to nearest even, NaN kept).
+  uint32_t pk[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    if (P.in_dtype == T_BF16) {
+      pk[i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+    } else {
+      const __half2 h = __floats2half2_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+      pk[i] = *reinterpret_cast<const uint32_t *>(&h);
+    }
+  }
+  if (P.fast_store_slot != 0xffffffffu && whole) {
+    // the whole post-fusion program is one store of the product: write it without interpreting
+    const EpiTensor &t = P.tensor[P.fast_store_slot];
+    const size_t off = epi_offset(t, pos);
+    if (t.dtype == P.in_dtype) {
+      uint8_t *dst = reinterpret_cast<uint8_t *>(t.ptr) + (off << 1);
+      if ((reinterpret_cast<uint64_t>(dst) & 15u) == 0) {
+        *reinterpret_cast<uint4 *>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+        return;
+      }
+    }
+  }
+  // back to the 32-bit register form of the rounded product
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    if (P.in_dtype == T_BF16) {
+      r[2 * i] = pk[i] << 16;
+      r[2 * i + 1] = pk[i] & 0xffff0000u;
+    } else {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&pk[i]));
+      r[2 * i] = __float_as_uint(f.x);
+      r[2 * i + 1] = __float_as_uint(f.y);
+    }
+  }
+  if (P.fast_store_slot != 0xffffffffu && whole) {
+    const EpiTensor &t = P.tensor[P.fast_store_slot];
+    if (t.dtype == T_F32) {
+      uint8_t *dst = reinterpret_cast<uint8_t *>(t.ptr) + (epi_offset(t, pos) << 2);
+      if ((reinterpret_cast<uint64_t>(dst) & 15u) == 0) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          *reinterpret_cast<uint4 *>(dst + 16 * g) = make_uint4(r[4 * g], r[4 * g + 1], r[4 * g + 2], r[4 * g + 3]);
+        return;
+      }
+    }
   }
   run_epilogue(P, pos, r);
 }
@@ -399,6 +481,16 @@ int LaunchMatMul(const MmParam &p_in, void *stream) {
   MmParam p = p_in;
   static const int group_env = getenv("DVM_B200_MM_GROUP_M") ? atoi(getenv("DVM_B200_MM_GROUP_M")) : 0;
   p.group_m = group_env > 0 ? static_cast<uint32_t>(group_env) : 8u;
+  // "copy acc, product; store tensor s; end" with a dense row layout: the kernel stores the product directly
+  p.fast_store_slot = 0xffffffffu;
+  {
+    const uint64_t w0 = p.epilogue[0], w1 = p.epilogue[1], w2 = p.epilogue[2];
+    if (DVMB_OPC(w0) == OP_COPY && DVMB_OKIND(w0) == K_TENSOR && DVMB_OIDX(w0) == p.mma_slot && DVMB_OPC(w1) == OP_ST &&
+        DVMB_OPC(w2) == OP_END && DVMB_SUB(w1) < p.n_tensors) {
+      const EpiTensor &t = p.tensor[DVMB_SUB(w1)];
+      if (t.sn == 1 && (t.dtype == p.in_dtype || t.dtype == T_F32)) p.fast_store_slot = DVMB_SUB(w1);
+    }
+  }
   if (p.M == 0 || p.N == 0 || p.batch0 * p.batch1 == 0) return 0;
   if (p.in_dtype != T_BF16 && p.in_dtype != T_F16) return -3;
   int dev = 0;

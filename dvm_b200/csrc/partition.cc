@@ -655,6 +655,7 @@ struct Planner {
           const Shape &xs = x->shape;
           const bool row_free = xs.rank < 2 || xs.d[xs.rank - 2] == 1;
           if (!row_free && !(xs == rs)) return {};
+          if (!row_free && !InPlainMemory(x)) return {};   // (the row block of a strided tensor is not a plain offset)
         } else if (!PullRowFree(x, extra)) {
           return {};
         }
