@@ -379,10 +379,14 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
         if (P.need_coords) split_enum(P, c[3], c);
         for (uint32_t ch = ch_begin; ch < ch_end; ch += ch_step, r_start += step_elems) {
           const uint32_t full = smem_base + kVmSmemBarriers + 8 * stage;
-          mbar_wait(smem_base + kVmSmemEmpty + 8 * stage, parity, 1, epoch);
+          // everything the copy needs is worked out before the wait, so that the copy leaves right after the release
           const uint32_t valid = r_start < P.group_elems ? min(P.round_elems, P.group_elems - r_start) : 0u;
           const uint32_t bytes = mine ? ((valid << sh) & ~15u) : 0u;
           const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
+          const uint32_t off = koff + c[0] * es[0] + c[1] * es[1] + c[2] * es[2] + c[3] * es[3];
+          const uint32_t dst = smem_base + P.stages_off + stage * P.stage_bytes + my_ring;
+          const uint8_t *const src = my_base + ((size_t)off << sh);
+          mbar_wait(smem_base + kVmSmemEmpty + 8 * stage, parity, 1, epoch);
           if (plane == 0) {
             if (total == 0) {
               mbar_arrive(full);
@@ -391,10 +395,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
             }
           }
           __syncwarp();
-          if (bytes != 0) {
-            const uint32_t off = koff + c[0] * es[0] + c[1] * es[1] + c[2] * es[2] + c[3] * es[3];
-            bulk_g2s(smem_base + P.stages_off + stage * P.stage_bytes + my_ring, my_base + ((size_t)off << sh), bytes, full);
-          }
+          if (bytes != 0) bulk_g2s(dst, src, bytes, full);
           // next chunk of this CTA: advance the innermost coordinate and carry
           c[3] += step_elems;
           if (P.need_coords) {
@@ -661,7 +662,10 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
         // the thread's 16 lanes of it.  Rounds in which every lane of every thread is valid: the first n_full ones.
         const uint32_t n_full = kRounds ? chunk_total / P.round_elems : 1u;
         const uint32_t n_rounds = kRounds ? n_full + (n_full * P.round_elems < chunk_total ? 1u : 0u) : 1u;
-        for (uint32_t rnd = 0; rnd < n_rounds; ++rnd) {
+        // A thread outside every group of this CTA (the tail of the last warp of a group that does not fill it) has no
+        // round to run.  It goes straight to the release, where its warp meets again: walking the rounds to their END
+        // word beside the warp's working threads made that warp the last one to release every stage.
+        for (uint32_t rnd = (kRounds && !pos.gvalid) ? n_rounds : 0u; rnd < n_rounds; ++rnd) {
         pos.in_chunk0 = kRounds ? lane4 + rnd * P.round_elems : lane4;
         pos.chunk_valid = kRounds ? min(chunk_total, (rnd + 1u) * P.round_elems) : chunk_total;
         // every lane of this thread lies inside the round: the vector fast paths apply
