@@ -20,6 +20,7 @@ SOURCES = [
     "vcompile.cc",
     "vkernel.cc",
     "partition.cc",
+    "stat_fusion.cc",
     "comm.cc",
     "runtime.cu",
     "capi.cu",

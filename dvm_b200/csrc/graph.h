@@ -173,6 +173,8 @@ class VKernel {
  public:
   VKernel(KernelType type, uint32_t flags) : type_(type), flags_(flags) {}
   void ClearStages();
+  // stat_fusion.cc: the op list with sums of squared deviations folded into the pass that makes their mean
+  std::vector<NDObject *> FuseDeviationSums(const std::vector<NDObject *> &ops);
   void PlanStages(const std::vector<NDObject *> &ops);   // partition.cc: general multi-stage planner
   ~VKernel();
 

@@ -209,6 +209,11 @@ enum UopHandler : uint32_t {
   //   arg16 = G, imm32 = X | Y << 12 | result slot << 24
   UH_LDSIGMMUL2ST_FIRST,                            // first + FusedType
   UH_LDSIGMMUL2ST_LAST = UH_LDSIGMMUL2ST_FIRST + 2,
+  // first pass of a normalisation that needs no second one: d = x - s over ring operand x (arg16 = ring offset / 16,
+  // imm32 = the scalar register of s), partial 0 += lanes of d, partial 1 += lanes of d * d; loops like the other
+  // load + reduce forms
+  UH_LDSTATS_FIRST,                                 // first + FusedType
+  UH_LDSTATS_LAST = UH_LDSTATS_FIRST + 2,
   UH_COUNT
 };
 enum FusedOp : uint32_t { FO_ADD = 0, FO_SUB = 1, FO_MUL = 2 };

@@ -1360,7 +1360,10 @@ bool LowerStageAs(VectorStage *st, bool dual) {
       const uint32_t hd = left >= 4 ? DVMB_UH(P.code[i + 3]) : static_cast<uint32_t>(UH_COUNT);
       const uint32_t he = left >= 5 ? DVMB_UH(P.code[i + 4]) : static_cast<uint32_t>(UH_COUNT);
       const bool centred = ha >= UH_LDRA_F32 && ha <= UH_LDRA_BF16 && hb == UH_BINR_FIRST + B_SUB;
-      if (centred && hc == UH_SQR && (hd == UH_RACCF_FIRST + R_SUM * 4u || hd == UH_RACCF_FIRST + R_SUM * 4u + 1u)) {
+      if (centred && hc == UH_RACCF_FIRST + R_SUM * 4u && hd == UH_SQR && he == UH_RACCF_FIRST + R_SUM * 4u + 1u) {
+        f = MakeUop(UH_LDSTATS_FIRST + (ha - UH_LDRA_F32), 0, DVMB_UARG(a), DVMB_UARG(b) & 0xfu);
+        take = 5;
+      } else if (centred && hc == UH_SQR && (hd == UH_RACCF_FIRST + R_SUM * 4u || hd == UH_RACCF_FIRST + R_SUM * 4u + 1u)) {
         f = MakeUop(UH_LDVAR_FIRST + (hd - (UH_RACCF_FIRST + R_SUM * 4u)) * 3u + (ha - UH_LDRA_F32), 0, DVMB_UARG(a), DVMB_UARG(b) & 0xfu);
         take = 4;
       } else if (centred && hc == UH_BINR_FIRST + B_MUL && hd == UH_BINR_FIRST + B_MUL && he == UH_BINR_FIRST + B_ADD) {
@@ -1554,13 +1557,15 @@ bool LowerStageAs(VectorStage *st, bool dual) {
                                  (last >= UH_LDSUM_FIRST && last <= UH_LDSUM_LAST) || last == UH_SQRSUM0 || last == UH_SQRSUM1 ||
                                  (last >= UH_LDVAR_FIRST && last <= UH_LDVAR_LAST) ||
                                  (last >= UH_LDNORMST_FIRST && last <= UH_LDNORMST_LAST) ||
-                                 (last >= UH_LD2ADDSQRSUM_FIRST && last <= UH_LDSIGMMUL2ST_LAST);
+                                 (last >= UH_LD2ADDSQRSUM_FIRST && last <= UH_LDSIGMMUL2ST_LAST) ||
+                                 (last >= UH_LDSTATS_FIRST && last <= UH_LDSTATS_LAST);
           if (ends_body && !no_tail && !overflow) {
             P.code[n - 1] |= static_cast<uint64_t>(UA_LAST) << 8;
             // a body that is one load + reduce micro-op runs all full rounds of a chunk in a single dispatch
             const bool load_reduce = (last >= UH_LDSUM_FIRST && last <= UH_LDSUM_LAST) || (last >= UH_LDVAR_FIRST && last <= UH_LDVAR_LAST) ||
                                      (last >= UH_LDNORMST_FIRST && last <= UH_LDNORMST_LAST) ||
-                                 (last >= UH_LD2ADDSQRSUM_FIRST && last <= UH_LDSIGMMUL2ST_LAST);
+                                     (last >= UH_LD2ADDSQRSUM_FIRST && last <= UH_LDSIGMMUL2ST_LAST) ||
+                                     (last >= UH_LDSTATS_FIRST && last <= UH_LDSTATS_LAST);
             if (load_reduce && n - P.sec[sidx] == 1 && P.rounds > 1) P.code[n - 1] |= static_cast<uint64_t>(UA_LOOP) << 8;
             ++fused_away;
             break;
@@ -1790,6 +1795,8 @@ std::string DisassembleStage(const VectorStage &st) {
       return std::string("lda.") + ty[(h - UH_LD2OP_FIRST) % 3] + "+ldb+" + fo[(h - UH_LD2OP_FIRST) / 3] + ".b";
     if (h >= UH_LDVAR_FIRST && h <= UH_LDVAR_LAST)
       return std::string("lda.") + ty[(h - UH_LDVAR_FIRST) % 3] + "+Sub.s+Sqr+ReduceSum.p" + std::to_string((h - UH_LDVAR_FIRST) / 3);
+    if (h >= UH_LDSTATS_FIRST && h <= UH_LDSTATS_LAST)
+      return std::string("lda.") + ty[h - UH_LDSTATS_FIRST] + "+Sub.s+ReduceSum.p0+Sqr+ReduceSum.p1";
     if (h >= UH_LDNORM_FIRST && h <= UH_LDNORM_LAST) return std::string("lda.") + ty[h - UH_LDNORM_FIRST] + "+Sub.s+Mul.s+Mul.s+Add.s";
     if (h >= UH_LDSIGM_FIRST && h <= UH_LDSIGM_LAST) return std::string("lda.") + ty[h - UH_LDSIGM_FIRST] + "+SigmoidFast";
     if (h >= UH_LDMUL2_FIRST && h <= UH_LDMUL2_LAST) return std::string("ldb.") + ty[h - UH_LDMUL2_FIRST] + "+Mul.b+ldb+Mul.b";

@@ -91,8 +91,17 @@ size_t VKernel::Compile() {
   }
   if (!has_matmul && !has_empty && !stacked) {
     // the common case: the whole graph is one launch of the vector interpreter
-    auto st = std::make_unique<Stage>();
     std::string why;
+    const std::vector<NDObject *> folded = FuseDeviationSums(ops);
+    if (folded != ops) {
+      auto st = std::make_unique<Stage>();
+      if (CompileVectorStage(folded, &st->vec, &why)) {
+        stages_.push_back(std::move(st));
+        compiled_ = true;
+        return 0;
+      }
+    }
+    auto st = std::make_unique<Stage>();
     if (CompileVectorStage(ops, &st->vec, &why)) {
       stages_.push_back(std::move(st));
       compiled_ = true;

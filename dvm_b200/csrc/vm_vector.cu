@@ -787,6 +787,14 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
             }
             DV_LDRED_TYPES(UH_LDVAR_FIRST, const uint32_t sv_ = lds32(sreg_addr(uhi));, DV_OPS_VAR0)
             DV_LDRED_TYPES(UH_LDVAR_FIRST + 3, const uint32_t sv_ = lds32(sreg_addr(uhi));, DV_OPS_VAR1)
+            // deviations from a group scalar, their sum and the sum of their squares in one pass
+#define DV_OPS_STATS(R)                                                                                  \
+  asm volatile(DV_LNR(DV_SUBS_LANE_R, R, "")::"r"(sv_));                                                   \
+  asm volatile(DV_TREE16R(DV_ADDRN2, "0", R));                                                             \
+  asm volatile(DV_LNR(DV_SQRRN_LANE_R, R, ""));                                                            \
+  asm volatile(DV_TREE16R(DV_ADDRN2, "1", R));
+            DV_LDRED_TYPES(UH_LDSTATS_FIRST, const uint32_t sv_ = lds32(sreg_addr(uhi));, DV_OPS_STATS)
+#undef DV_OPS_STATS
 #undef DV_OPS_SUM0
 #undef DV_OPS_VAR0
 #undef DV_OPS_VAR1

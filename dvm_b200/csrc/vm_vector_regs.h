@@ -26,6 +26,8 @@
   M(5, R, __VA_ARGS__) M(6, R, __VA_ARGS__) M(7, R, __VA_ARGS__) M(8, R, __VA_ARGS__) M(9, R, __VA_ARGS__)         \
   M(10, R, __VA_ARGS__) M(11, R, __VA_ARGS__) M(12, R, __VA_ARGS__) M(13, R, __VA_ARGS__) M(14, R, __VA_ARGS__)    \
   M(15, R, __VA_ARGS__)
+#define DV_SUBS_LANE_R(i, R, X) "sub.rn.f32 " R #i ", " R #i ", %0;\n\t"
+#define DV_SQRRN_LANE_R(i, R, X) "mul.rn.f32 " R #i ", " R #i ", " R #i ";\n\t"
 #define DV_CSQR_LANE_R(i, R, X) "sub.rn.f32 " R #i ", " R #i ", %0;\n\tmul.rn.f32 " R #i ", " R #i ", " R #i ";\n\t"
 #define DV_NORM_LANE_R(i, R, X)                                                                                \
   "sub.rn.f32 " R #i ", " R #i ", %0;\n\tmul.rn.f32 " R #i ", " R #i ", %1;\n\tmul.rn.f32 " R #i ", " R #i ", %2;\n\t" \

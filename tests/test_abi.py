@@ -112,10 +112,11 @@ def test_peephole_fuses_frequent_neighbours():
         k.store(o)
     k.codegen()
     bodies = _micro_ops(k.das())
-    assert len(bodies) == 3
-    assert bodies[0][0] == "lda.fp16+ReduceSum.p0"
-    assert bodies[1][0] == "lda.fp16+Sub.s+Sqr+ReduceSum.p1"
-    assert bodies[2][0] == "lda.fp16+Sub.s+Mul.s+Mul.s+Add.s+st.fp16"
+    # the variance of a 16-bit tensor needs no pass of its own: sum and sum of squares of the deviations from each
+    # channel's first element are taken together, so the tensor is read twice instead of three times
+    assert len(bodies) == 2
+    assert bodies[0][0] == "lda.fp16+Sub.s+ReduceSum.p0+Sqr+ReduceSum.p1"
+    assert bodies[1][0] == "lda.fp16+Sub.s+Mul.s+Mul.s+Add.s+st.fp16"
     # every body is one micro-op that runs all eight rounds of a chunk in one dispatch
     assert "rounds=8" in k.das()
     assert all(len(body) == 9 and " ".join(body).endswith("(ends the body, loops over the chunk's rounds)") for body in bodies)
@@ -146,6 +147,28 @@ def test_peephole_can_be_switched_off(monkeypatch):
     fused = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, check=True).stdout
     assert _micro_ops(plain)[0] == ["lda.fp32", "ldb.fp32", "Add.b", "st.fp32"]
     assert _micro_ops(fused)[0][:2] == ["lda.fp32+ldb+Add.b", "st.fp32"]
+
+
+def test_deviation_sums_keep_their_own_pass_on_request():
+    # DVM_B200_EXACT_MATH=1 keeps a graph's reductions as written: mean, then the squared deviations from it, then the
+    # result (three passes); a fp32 input is never rewritten either
+    import subprocess, sys
+    code = ("import sys, dvm_b200 as dvm\n"
+            "from dvm_b200 import workloads as W\n"
+            "dt = dvm.float16 if sys.argv[1] == 'f16' else dvm.float32\n"
+            "k = dvm.PyKernel('vector', 'das', 0)\n"
+            "x = k.load([8, 32, 14, 14], dt); g = k.load([1, 32, 1, 1], dvm.float32); b = k.load([1, 32, 1, 1], dvm.float32)\n"
+            "[k.store(o) for o in W.batchnorm_train(k, x, g, b, 8 * 14 * 14)]\n"
+            "k.codegen(); print(k.das())\n")
+
+    def bodies(dtype, **extra):
+        env = dict(os.environ, PYTHONPATH=ROOT, **extra)
+        out = subprocess.run([sys.executable, "-c", code, dtype], env=env, capture_output=True, text=True, check=True).stdout
+        return sum(1 for line in out.splitlines() if line.strip().startswith("body_") and line.strip().endswith(":"))
+
+    assert bodies("f16") == 2
+    assert bodies("f16", DVM_B200_EXACT_MATH="1") == 3
+    assert bodies("f32") == 3
 
 
 def _reloc_array(pairs):
