@@ -8,10 +8,12 @@
 //     sum(x)          = T + n s
 //     sum((x - m)^2)  = Q - 2 e T + n e^2          with e = m - s   (exact in real arithmetic)
 //
-// so the second pass disappears: one read of the tensor less.  In fp32 the identity costs a little accuracy where
-// (m - s)^2 is large against the variance (cancellation between Q and n e^2); for a 16-bit input, whose values are a
-// few thousand steps apart at most, the relative error of the result stays near 1e-6 * (1 + (m - s)^2 / var), far
-// inside the 1e-2 / 1e-3 tolerance class of reductions over 16-bit data.  The rewrite is therefore applied only to a
+// so the second pass disappears: one read of the tensor less.  Where m is the mean itself, m = sum(x) / n (the usual
+// case), the two collapse to  m = s + T / n  and  sum((x - m)^2) = Q - T (T / n).
+// In fp32 the identity costs a little accuracy where (m - s)^2 is large against the variance (cancellation between Q
+// and n e^2); for a 16-bit input, whose values are a few thousand steps apart at most, the relative error of the
+// result stays near 1e-6 * (1 + (m - s)^2 / var), far inside the 1e-2 / 1e-3 tolerance class of reductions over
+// 16-bit data.  The rewrite is therefore applied only to a
 // 16-bit tensor widened to fp32, and DVM_B200_EXACT_MATH=1 (which also keeps exact divisions) switches it off.
 //
 // No counterpart in the reference, whose vector kernels run each reduction as written (src/vm_gpu.cu:1552-1617: seven
@@ -69,6 +71,7 @@ uint32_t FloatBits(float f) {
 struct Match {
   NDObject *r1, *r2, *sq, *m, *x, *load;
   int64_t n;
+  bool mean_form;   // m = r1 * (1 / n) and nothing else reads r1
 };
 
 }  // namespace
@@ -105,7 +108,9 @@ std::vector<NDObject *> VKernel::FuseDeviationSums(const std::vector<NDObject *>
     const int64_t n = x->shape.numel() / groups;
     if (n < 2 || n > (1 << 24)) continue;
     taken.insert(r1);
-    found.push_back(Match{r1, r2, sq, m, x, load, n});
+    const bool mean_form = m->kind == N_BINARY_S && m->sub == SB_MUL && m->in[0] == r1 && m->scalar_ref == nullptr &&
+                           m->scalar_bits == FloatBits(static_cast<float>(1.0 / static_cast<double>(n))) && users[r1].size() == 1;
+    found.push_back(Match{r1, r2, sq, m, x, load, n, mean_form});
   }
   if (found.empty()) return ops;
 
@@ -137,8 +142,11 @@ std::vector<NDObject *> VKernel::FuseDeviationSums(const std::vector<NDObject *>
     dead.insert(mt.sq);
   }
   struct Sums {
-    NDObject *s, *t, *q;
+    NDObject *s, *t, *q, *tn;   // tn = T / n (mean form only)
   };
+  std::unordered_map<const NDObject *, const Match *> at_mean;
+  for (auto &mt : found)
+    if (mt.mean_form) at_mean[mt.m] = &mt;
   std::unordered_map<const Match *, Sums> sums;
   std::vector<NDObject *> out;
   auto mapped = [&](NDObject *v) {
@@ -170,17 +178,42 @@ std::vector<NDObject *> VKernel::FuseDeviationSums(const std::vector<NDObject *>
       NDObject *sq0 = make(N_BINARY, mt->x, kMul, d0, d0);
       NDObject *q = copy_of(mt->r2);
       q->in[0] = sq0;
+      for (NDObject *v : {sl, s, d0, t, sq0, q}) out.push_back(v);
+      if (mt->mean_form) {
+        sums[mt] = Sums{s, t, q, nullptr};   // the mean itself is made where the graph makes it
+        continue;
+      }
       NDObject *ns = make(N_BINARY_S, mt->r1, SB_MUL, s, nullptr);
       ns->scalar_bits = FloatBits(static_cast<float>(mt->n));
       NDObject *sum = make(N_BINARY, mt->r1, kAdd, t, ns);
-      for (NDObject *v : {sl, s, d0, t, sq0, q, ns, sum}) out.push_back(v);
+      out.push_back(ns);
+      out.push_back(sum);
       repl[n] = sum;
-      sums[mt] = Sums{s, t, q};
+      sums[mt] = Sums{s, t, q, nullptr};
+      continue;
+    }
+    if (at_mean.count(n)) {
+      const Match *mt = at_mean.at(n);
+      Sums &sm = sums.at(mt);
+      sm.tn = make(N_BINARY_S, mt->r1, SB_MUL, sm.t, nullptr);
+      sm.tn->scalar_bits = n->scalar_bits;
+      NDObject *mean = make(N_BINARY, mt->r1, kAdd, sm.tn, sm.s);
+      out.push_back(sm.tn);
+      out.push_back(mean);
+      repl[n] = mean;
       continue;
     }
     if (at_r2.count(n)) {
       const Match *mt = at_r2.at(n);
       const Sums &sm = sums.at(mt);
+      if (mt->mean_form) {
+        NDObject *ttn = make(N_BINARY, mt->r2, kMul, sm.t, sm.tn);
+        NDObject *res = make(N_BINARY, mt->r2, kSub, sm.q, ttn);
+        out.push_back(ttn);
+        out.push_back(res);
+        repl[n] = res;
+        continue;
+      }
       NDObject *e = make(N_BINARY, mt->r2, kSub, mapped(mt->m), sm.s);
       NDObject *et = make(N_BINARY, mt->r2, kMul, e, sm.t);
       NDObject *et2 = make(N_BINARY_S, mt->r2, SB_MUL, et, nullptr);
