@@ -42,6 +42,12 @@ struct MmParam {
   uint32_t group_m;         // row blocks swept together over all column blocks (L2 reuse of the A panel); set by the launcher
   uint32_t fast_store_slot; // set by the launcher: the post-fusion program is just "store the product to tensor <slot>" (in the
                             // operand type or widened to fp32), which the kernel does without interpreting; 0xffffffff otherwise
+  // set by the launcher: the post-fusion program is the gated form  y = x / (c2 + exp(c1 * (x + c0 * x^3)))  of the
+  // rounded product x (tanh-GeLU written through the exponential, c0 = 0.044715, c1 = -2 sqrt(2/pi), c2 = 1), rounded to
+  // the operand type and stored to tensor <gate_slot>: the kernel computes it in registers with the interpreter's own
+  // operations in the interpreter's order (same bits) instead of interpreting eleven words per strip; 0xffffffff otherwise
+  uint32_t gate_slot;
+  uint32_t gate_c[3];
   EpiTensor tensor[kMmMaxEpiTensors];
   uint64_t epilogue[kMmMaxEpilogueWords];
 };

@@ -163,6 +163,40 @@ __device__ __forceinline__ void finish_strip(const MmParam &P, const EpiPos &pos
       r[2 * i + 1] = __float_as_uint(f.y);
     }
   }
+  if (P.gate_slot != 0xffffffffu && whole) {
+    // y = x / (c2 + exp(c1 * (x + c0 * x^3))): each step rounded on its own, as the interpreter's words are
+    const EpiTensor &t = P.tensor[P.gate_slot];
+    uint8_t *dst = reinterpret_cast<uint8_t *>(t.ptr) + (epi_offset(t, pos) << 1);
+    if ((reinterpret_cast<uint64_t>(dst) & 15u) == 0) {
+      const float c0 = __uint_as_float(P.gate_c[0]), c1 = __uint_as_float(P.gate_c[1]), c2 = __uint_as_float(P.gate_c[2]);
+      float y[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float x = __uint_as_float(r[i]);
+        float a = __fmul_rn(x, x);
+        a = __fmul_rn(a, x);
+        a = __fmul_rn(a, c0);
+        a = __fadd_rn(a, x);
+        a = __fmul_rn(a, c1);
+        a = fast_exp(a);
+        a = __fadd_rn(a, c2);
+        y[i] = fast_div(x, a);
+      }
+      uint32_t o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (P.in_dtype == T_BF16) {
+          o[i] = pack_bf16x2(y[2 * i], y[2 * i + 1]);
+        } else {
+          const __half2 h = __floats2half2_rn(y[2 * i], y[2 * i + 1]);
+          o[i] = *reinterpret_cast<const uint32_t *>(&h);
+        }
+      }
+      *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+      *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(o[4], o[5], o[6], o[7]);
+      return;
+    }
+  }
   if (P.fast_store_slot != 0xffffffffu && whole) {
     const EpiTensor &t = P.tensor[P.fast_store_slot];
     if (t.dtype == T_F32) {
@@ -489,6 +523,30 @@ int LaunchMatMul(const MmParam &p_in, void *stream) {
         DVMB_OPC(w2) == OP_END && DVMB_SUB(w1) < p.n_tensors) {
       const EpiTensor &t = p.tensor[DVMB_SUB(w1)];
       if (t.sn == 1 && (t.dtype == p.in_dtype || t.dtype == T_F32)) p.fast_store_slot = DVMB_SUB(w1);
+    }
+  }
+  // the gated form x / (c2 + exp(c1 * (x + c0 * x^3))) of the product, rounded to the operand type and stored
+  p.gate_slot = 0xffffffffu;
+  {
+    static const bool off = getenv("DVM_B200_NO_FUSE") != nullptr;
+    const uint64_t *w = p.epilogue;
+    auto is = [&](int i, uint32_t opc, uint32_t sub, uint32_t okind) {
+      return DVMB_OPC(w[i]) == opc && DVMB_SUB(w[i]) == sub && DVMB_OKIND(w[i]) == okind && DVMB_RND(w[i]) == RN_NONE &&
+             (okind != K_TENSOR || DVMB_OIDX(w[i]) == p.mma_slot);
+    };
+    const uint32_t rnd_out = p.in_dtype == T_BF16 ? RN_BF16 : RN_F16;
+    if (!off && DVMB_OPC(w[0]) == OP_COPY && DVMB_OKIND(w[0]) == K_TENSOR && DVMB_OIDX(w[0]) == p.mma_slot &&
+        is(1, OP_BIN, B_MUL, K_ACC) && is(2, OP_BIN, B_MUL, K_TENSOR) && is(3, OP_BIN, B_MUL, K_IMM) && is(4, OP_BIN, B_ADD, K_TENSOR) &&
+        is(5, OP_BIN, B_MUL, K_IMM) && DVMB_OPC(w[6]) == OP_UN && DVMB_SUB(w[6]) == U_EXP_FAST && DVMB_RND(w[6]) == RN_NONE &&
+        is(7, OP_BIN, B_ADD, K_IMM) && is(8, OP_BIN, B_RDIV_FAST, K_TENSOR) && DVMB_OPC(w[9]) == OP_CVT && DVMB_SUB(w[9]) == V_RND &&
+        DVMB_RND(w[9]) == rnd_out && DVMB_OPC(w[10]) == OP_ST && DVMB_OPC(w[11]) == OP_END && DVMB_SUB(w[10]) < p.n_tensors) {
+      const EpiTensor &t = p.tensor[DVMB_SUB(w[10])];
+      if (t.sn == 1 && t.dtype == p.in_dtype) {
+        p.gate_slot = DVMB_SUB(w[10]);
+        p.gate_c[0] = DVMB_IMM(w[3]);
+        p.gate_c[1] = DVMB_IMM(w[5]);
+        p.gate_c[2] = DVMB_IMM(w[7]);
+      }
     }
   }
   if (p.M == 0 || p.N == 0 || p.batch0 * p.batch1 == 0) return 0;

@@ -77,6 +77,20 @@ for dt, tag in ((np.float32, "f32"), (np.float16, "f16")):
     run("chain_" + tag, lambda k, a, c: (k.add(k.mul(k.sub(a, c), c), a), k.mul(k.add(a, c), k.sub(a, c))), [p, q])
 run("exp_f32", W.fused_elementwise, [rng.uniform(-1, 1, (1024, 4096)).astype(np.float32),
                                       rng.uniform(-1, 1, (1024, 4096)).astype(np.float32)])
+# MatMul + bias + tanh-GeLU: the launcher recognises the post-fusion program and the kernel computes it in registers
+# instead of interpreting it; rows / columns that do not fill a tile take the interpreter in both runs
+for dt, code, tag in ((BF16, 2, "bf16"), (np.float16, 1, "f16")):
+    for (m, n, kk) in ((256, 512, 128), (200, 264, 96)):
+        a_ = rng.normal(0, 0.5, (m, kk)).astype(np.float32).astype(dt)
+        b_ = rng.normal(0, 0.5, (kk, n)).astype(np.float32).astype(dt)
+        bias_ = rng.normal(0, 0.5, (n,)).astype(np.float32).astype(dt)
+        t = Tester("mix")
+        la, lb, lbias = t.load(a_), t.load(b_), t.load(bias_)
+        c = t.matmul(la, lb, False, False, lbias)
+        st = t.store(t.cast(W.gelu_tanh(t, t.cast(c, 3)), code))
+        t.run()
+        o = np.asarray(t.output(st))
+        out["mm_gelu_%s_%d" % (tag, m)] = o.view(np.uint16)
 np.savez(sys.argv[1], fused_seen=np.int64(fused_seen), **out)
 """
 
