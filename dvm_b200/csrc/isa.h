@@ -71,6 +71,9 @@ enum ScalarOp : uint32_t {
   SOP_RINIT_END,                     // handler (no END word follows, which saves its dispatch)
   SOP_RSTD_FAST,                     // sacc <- 1 / sqrt(sacc * imm + imm'), fast division: the four words Mul #imm, Add #imm',
                                      // Sqrt, RDivFast #1.0 as one; imm' is read from the following word, which is skipped
+  SOP_RFIN2,                         // two sum reductions finished behind one CTA barrier: partial (sub & 3) -> scalar register dst,
+                                     // partial (sub >> 2 & 3) -> scalar register oidx and sacc (the words RFIN, MOV, RFIN, MOV as one;
+                                     // each sum is combined in the order of a single RFIN)
   SOP_COUNT
 };
 

@@ -764,12 +764,22 @@ struct Compiler {
     if (max_level > num_body) throw Fail{"internal: scalar work beyond the last phase"};
     const int num_pro = num_body + 1;
     std::vector<std::vector<const NDObject *>> pro_order(num_pro);
+    int deferred_stores = 0;
     for (auto n : ops) {
       const Info &fi = I(n);
       if (!fi.scalar_space) continue;
       if (n->kind == N_STORE) {
-        pro_order[fi.level].push_back(n);
-        touch(Canon(n->in[0]), 2 * fi.level);
+        // A group scalar that is only stored (a mean, a variance) leaves for memory in the last scalar section instead
+        // of the one that makes it: the section between two bodies is where every CTA of a normalisation waits at the
+        // same time, and each store there costs two words and a global write in front of the next body.  (At most four
+        // values wait this way: each keeps its scalar register until the end.)
+        int at = fi.level;
+        if (at < num_body && deferred_stores < 4) {
+          at = num_body;
+          ++deferred_stores;
+        }
+        pro_order[at].push_back(n);
+        touch(Canon(n->in[0]), 2 * at);
         continue;
       }
       if (fi.canon != n || n->kind == N_BROADCAST_S) continue;
@@ -1529,6 +1539,23 @@ bool LowerStageAs(VectorStage *st, bool dual) {
               for (uint32_t r = q + 4; r < n; ++r) P.code[r - 2] = P.code[r];
               n -= 2;
               fused_away += 2;
+              break;
+            }
+          }
+        }
+        if (opc == OP_END && !overflow && P.mode == VM_GROUP && P.tg > 32) {
+          // two sums finished one after the other share their CTA barrier (not with clusters or resident groups,
+          // whose finish also talks to the other CTAs)
+          static const bool plain = getenv("DVM_B200_NO_FUSE") == nullptr && getenv("DVM_B200_CLUSTER") == nullptr &&
+                                    getenv("DVM_B200_RESIDENT") == nullptr;
+          for (uint32_t q = P.sec[sidx]; plain && q + 4 <= n; ++q) {
+            const uint64_t w0 = P.code[q], w1 = P.code[q + 1], w2 = P.code[q + 2], w3 = P.code[q + 3];
+            if (DVMB_OPC(w0) == SOP_RFIN && DVMB_OPC(w1) == SOP_MOV && DVMB_OPC(w2) == SOP_RFIN && DVMB_OPC(w3) == SOP_MOV &&
+                (DVMB_SUB(w0) >> 4) == R_SUM && (DVMB_SUB(w2) >> 4) == R_SUM) {
+              P.code[q] = Insn::make(SOP_RFIN2, (DVMB_SUB(w0) & 3u) | ((DVMB_SUB(w2) & 3u) << 2), K_IMM, DVMB_DST(w3), DVMB_DST(w1), 0, 0, 1, 0);
+              for (uint32_t r = q + 4; r < n; ++r) P.code[r - 3] = P.code[r];
+              n -= 3;
+              fused_away += 3;
               break;
             }
           }

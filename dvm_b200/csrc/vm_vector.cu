@@ -570,6 +570,42 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
               sacc[0] = f2u(v);
               break;
             }
+            case SOP_RFIN2: {
+              // (sums only, more than one warp per group: the lowering sees to both)
+              const uint32_t pa = sub & 3u, pb = (sub >> 2) & 3u;
+              float v0 = get_part(pa), v1 = get_part(pb);
+              set_part(pa, 0.0f);
+              set_part(pb, 0.0f);
+#pragma unroll
+              for (uint32_t o = 16; o > 0; o >>= 1) {
+                v0 += __shfl_xor_sync(0xffffffffu, v0, o);
+                v1 += __shfl_xor_sync(0xffffffffu, v1, o);
+              }
+              if ((tid & 31u) == 0) {
+                red_buf[red_par * 32 + (tid >> 5)] = v0;
+                red_buf[red_par * 32 + 16 + (tid >> 5)] = v1;
+              }
+              asm volatile("bar.sync 1, %0;" ::"r"(T) : "memory");   // consumer warps only
+              const uint32_t nw = T >> 5;
+              float pv[16], pw[16];
+#pragma unroll
+              for (uint32_t wi = 0; wi < 16; ++wi) {
+                pv[wi] = wi < nw ? red_buf[red_par * 32 + wi] : 0.0f;
+                pw[wi] = wi < nw ? red_buf[red_par * 32 + 16 + wi] : 0.0f;
+              }
+#pragma unroll
+              for (int h = 8; h > 0; h >>= 1)
+#pragma unroll
+                for (int i = 0; i < h; ++i) {
+                  pv[i] += pv[i + h];
+                  pw[i] += pw[i + h];
+                }
+              red_par ^= 1u;
+              asm volatile("st.shared.u32 [%0], %1;" ::"r"(sreg_addr((whi >> 24) & 0xfu)), "r"(f2u(pv[0])) : "memory");
+              asm volatile("st.shared.u32 [%0], %1;" ::"r"(sreg_addr(oidx)), "r"(f2u(pw[0])) : "memory");
+              sacc[0] = f2u(pw[0]);
+              break;
+            }
 #define DV_SUN(K) case SOP_UN_FIRST + K: apply_un<1>(K, sacc); break;
             DV_SUN(U_SQRT) DV_SUN(U_ABS) DV_SUN(U_LOG) DV_SUN(U_EXP) DV_SUN(U_ROUND) DV_SUN(U_FLOOR) DV_SUN(U_CEIL)
             DV_SUN(U_TRUNC) DV_SUN(U_ISFINITE) DV_SUN(U_ABS_I) DV_SUN(U_EXP_FAST) DV_SUN(U_NOP)
