@@ -163,6 +163,11 @@ enum StageKind : uint8_t { STAGE_VECTOR = 0, STAGE_MATMUL, STAGE_ATTENTION, STAG
 
 struct Stage {
   StageKind kind = STAGE_VECTOR;
+  // A pipelined plan (the row chunks of a K-split MatMul whose exchange overlaps the next chunk's product): stages are
+  // enqueued in list order, lane 0 on the launch stream, lane 1 (the collectives) on a second stream of the kernel's own;
+  // a stage first waits for the stage `after` (an index into the plan, -1: none) where that one ran on the other lane.
+  int lane = 0;
+  int after = -1;
   VectorStage vec;
   MatMulStage mm;
   AttnStage attn;
@@ -184,6 +189,10 @@ class VKernel {
   void Bind(const RelocEntry *relocs, size_t n, void *workspace);
   int Launch(void *stream);
   int LaunchStage(size_t index, void *stream);   // one launch (or collective) of the plan, for per-stage timing
+  int LaunchPipelined(void *stream);             // a plan with two lanes (see Stage::lane)
+  void *side_stream_ = nullptr;                  // lane 1; created at the first pipelined launch
+  std::vector<void *> stage_events_;             // one event per stage that another lane waits for
+  void *join_event_ = nullptr;
 
   const char *Dump();
   const char *DumpR();

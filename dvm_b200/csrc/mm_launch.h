@@ -48,6 +48,7 @@ struct MmParam {
   // operations in the interpreter's order (same bits) instead of interpreting eleven words per strip; 0xffffffff otherwise
   uint32_t gate_slot;
   uint32_t gate_c[3];
+  uint32_t leave_sms;       // set by the planner: SMs this launch leaves free (a collective runs beside it); 0 = none
   EpiTensor tensor[kMmMaxEpiTensors];
   uint64_t epilogue[kMmMaxEpilogueWords];
 };

@@ -562,6 +562,7 @@ int LaunchMatMul(const MmParam &p_in, void *stream) {
     dvm_b200_mm_simt<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(p);
     return static_cast<int>(cudaGetLastError());
   }
+  if (p.leave_sms != 0 && static_cast<int>(p.leave_sms) + 32 <= sms) sms -= static_cast<int>(p.leave_sms);
   static bool attr_set[64] = {false};
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
     cudaError_t e = cudaFuncSetAttribute(dvm_b200_mm_tcgen05, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<1>::kSmemBytes);

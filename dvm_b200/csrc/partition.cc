@@ -701,48 +701,142 @@ struct Planner {
     if (uv == users.end() || uv->second.size() != 1) return false;
     std::vector<NDObject *> tail = RowBlockTail(n);
     if (tail.empty()) return false;
-    const int64_t rows_all = rs.d[0], rows = rows_all / comm->size;
-    const int64_t blk_elems = rows * rs.d[1];
+    const int64_t rows_all = rs.d[0];
     const int64_t isz = ItemSize(n->dtype);
-    // 1. reduce-scatter, in place on the temporary
-    NDObject *w = MemLoad(v);
-    PushCollective(dvmb::COLL_REDUCE_SCATTER, n, w, 0, w, comm->rank * blk_elems * isz, static_cast<uint64_t>(blk_elems),
-                   static_cast<uint64_t>(blk_elems * isz) * (comm->size - 1));
-    // 2. the tail on the rank's rows
-    Build b;
-    NDObject *src = MemLoad(v);
-    src->shape = rs;
-    b.clone[n] = src;
-    b.list.push_back(src);
+    // Row chunks (DVM_B200_TP_CHUNKS=n).  When the stage in front is the MatMul that makes the temporary (and nothing
+    // else), the product can be cut into row chunks: chunk c's reduce-scatter, tail and all-gather run while the MatMul works on chunk c + 1, the
+    // collectives on a second stream (Stage::lane).  Rank r then owns rows [c Mc + r Mc / size, ...) of every chunk instead
+    // of one block of M / size rows: the same results, since the tail is row-independent.
+    int chunks = 1;
+    Stage *mm_stage = nullptr;
+    int ws_slot = -1;
+    if (!vk->stages_.empty() && vk->stages_.back()->kind == STAGE_MATMUL) {
+      MatMulStage &m0 = vk->stages_.back()->mm;
+      bool other = false;
+      for (size_t sl = 0; sl < m0.slot_obj.size(); ++sl) {
+        NDObject *o = m0.slot_obj[sl];
+        if (!o) continue;
+        if (o->kind == N_STORE && o->ws_off >= 0 && o->ws_off == where->second->ws_off && o->shape == rs) {
+          ws_slot = static_cast<int>(sl);
+        } else {
+          other = true;
+        }
+      }
+      const dvmb::MmParam &mp = m0.param;
+      if (ws_slot >= 0 && !other && !mp.a_mmajor && mp.batch0 * mp.batch1 == 1 && mp.M == static_cast<uint32_t>(rows_all) &&
+          m0.a->shape.rank == 2 && !m0.idle)
+        mm_stage = vk->stages_.back().get();
+    }
+    if (mm_stage) {
+      // (off unless asked for: on 8 GPUs the [16384, 8192] product measured 1.57 ms in one chunk, 1.57 in two and 1.65-1.71
+      // in four - the collectives lose more by sharing the GPU with the MatMul and by their smaller messages than the
+      // overlap wins; on 2 GPUs, where the MatMul is the longer part, four chunks measured 1.81 against 1.89 ms)
+      int want = 1;
+      if (const char *env = getenv("DVM_B200_TP_CHUNKS")) want = std::max(1, atoi(env));
+      // every chunk keeps whole MatMul tiles (256 rows per CTA pair) and whole rows per rank
+      while (want > 1 && (rows_all % (static_cast<int64_t>(want) * comm->size) != 0 || (rows_all / want) % 256 != 0)) --want;
+      chunks = want;
+    }
+    const int64_t rows_chunk = rows_all / chunks, rows = rows_chunk / comm->size;   // rows of a chunk, of a rank's block in it
+    const int64_t blk_elems = rows * rs.d[1];
+    auto copy_node = [&](const NDObject *like) {
+      auto c = new NDObject(*like);
+      vk->synth_.push_back(c);
+      return c;
+    };
+    // the stages of every chunk, pushed in pipeline order further down
+    std::vector<std::unique_ptr<Stage>> mm_c, rs_c, tail_c;
+    std::vector<std::vector<std::unique_ptr<Stage>>> ag_c(chunks);
+    std::unique_ptr<Stage> mm_base;
+    if (chunks > 1) {
+      mm_base = std::move(vk->stages_.back());
+      vk->stages_.pop_back();
+      for (int c = 0; c < chunks; ++c) {
+        auto st = std::make_unique<Stage>(*mm_base);
+        MatMulStage &mc = st->mm;
+        mc.a = copy_node(mm_base->mm.a);
+        ToRowBlock(mc.a, rows_all, rows_chunk, c);
+        mc.slot_obj[ws_slot] = copy_node(mm_base->mm.slot_obj[ws_slot]);
+        ToRowBlock(mc.slot_obj[ws_slot], rows_all, rows_chunk, c);
+        mc.param.M = static_cast<uint32_t>(rows_chunk);
+        mc.param.leave_sms = 16;   // room for the collective that runs beside this launch
+        mc.flops = mm_base->mm.flops / chunks;
+        mc.algo_bytes = mm_base->mm.algo_bytes / chunks;
+        mm_c.push_back(std::move(st));
+      }
+    }
+    auto take_last = [&]() {
+      std::unique_ptr<Stage> st = std::move(vk->stages_.back());
+      vk->stages_.pop_back();
+      return st;
+    };
     std::unordered_set<const NDObject *> area(tail.begin(), tail.end());
     area.insert(n);
-    const size_t first_clone = vk->synth_.size() - 1;
-    CloneArea(b, tail, area, true);
-    for (size_t i = first_clone; i < vk->synth_.size(); ++i) ToRowBlock(vk->synth_[i], rows_all, rows, comm->rank);
-    auto st = std::make_unique<Stage>();
-    st->kind = STAGE_VECTOR;
-    std::string why;
-    if (!CompileVectorStage(b.list, &st->vec, &why)) {
-      std::string msg = "cannot compile the row-block tail of an all-reduce: " + why;
-      DvmException(msg.c_str());
+    for (int c = 0; c < chunks; ++c) {
+      const int64_t chunk_off = static_cast<int64_t>(c) * rows_chunk * rs.d[1];   // elements in front of the chunk
+      // 1. reduce-scatter, in place on the chunk's rows of the temporary
+      NDObject *w = MemLoad(v);
+      PushCollective(dvmb::COLL_REDUCE_SCATTER, n, w, chunk_off * isz, w, (chunk_off + comm->rank * blk_elems) * isz,
+                     static_cast<uint64_t>(blk_elems), static_cast<uint64_t>(blk_elems * isz) * (comm->size - 1));
+      rs_c.push_back(take_last());
+      // 2. the tail on the rank's rows of the chunk
+      Build b;
+      NDObject *src = MemLoad(v);
+      src->shape = rs;
+      b.clone[n] = src;
+      b.list.push_back(src);
+      const size_t first_clone = vk->synth_.size() - 1;
+      CloneArea(b, tail, area, c == 0);
+      if (c > 0 && !b.temps.empty()) DvmException("stage planner: a row-block tail with a temporary cannot be cut into chunks");
+      for (size_t i = first_clone; i < vk->synth_.size(); ++i)
+        ToRowBlock(vk->synth_[i], rows_all, rows, c * comm->size + comm->rank);
+      auto st = std::make_unique<Stage>();
+      st->kind = STAGE_VECTOR;
+      std::string why;
+      if (!CompileVectorStage(b.list, &st->vec, &why)) {
+        std::string msg = "cannot compile the row-block tail of an all-reduce: " + why;
+        DvmException(msg.c_str());
+      }
+      tail_c.push_back(std::move(st));
+      // 3. all-gather of every result, in place on the caller's buffer
+      for (auto t : tail) {
+        if (c == 0) {
+          // (a recomputed row-free chain that something else reads as well stays open for the stage that needs it)
+          bool inside = true;
+          auto ut = users.find(t);
+          if (ut != users.end())
+            for (auto u : ut->second) inside &= area.count(u) != 0;
+          if (inside) done.insert(t);
+        }
+        if (t->kind != N_STORE) continue;
+        NDObject *whole = Synth(t);
+        whole->origin = t;
+        whole->in[0] = nullptr;
+        const int64_t osz = ItemSize(t->dtype);
+        PushCollective(dvmb::COLL_ALL_GATHER, n, whole, (chunk_off + comm->rank * blk_elems) * osz, whole, chunk_off * osz,
+                       static_cast<uint64_t>(blk_elems), static_cast<uint64_t>(blk_elems * osz) * (comm->size - 1));
+        vk->stages_.back()->coll.dtype = static_cast<int>(t->dtype);
+        ag_c[c].push_back(take_last());
+      }
     }
-    vk->stages_.push_back(std::move(st));
-    // 3. all-gather of every result, in place on the caller's buffer
-    for (auto t : tail) {
-      // (a recomputed row-free chain that something else reads as well stays open for the stage that needs it)
-      bool inside = true;
-      auto ut = users.find(t);
-      if (ut != users.end())
-        for (auto u : ut->second) inside &= area.count(u) != 0;
-      if (inside) done.insert(t);
-      if (t->kind != N_STORE) continue;
-      NDObject *whole = Synth(t);
-      whole->origin = t;
-      whole->in[0] = nullptr;
-      const int64_t osz = ItemSize(t->dtype);
-      PushCollective(dvmb::COLL_ALL_GATHER, n, whole, comm->rank * blk_elems * osz, whole, 0, static_cast<uint64_t>(blk_elems),
-                     static_cast<uint64_t>(blk_elems * osz) * (comm->size - 1));
-      vk->stages_.back()->coll.dtype = static_cast<int>(t->dtype);
+    // pipeline order.  Launch stream: mm_0, mm_1, tail_0, mm_2, tail_1, ...; second stream: rs_0, rs_1, ag_0, rs_2, ag_1, ...
+    std::vector<int> at_mm(chunks, -1), at_rs(chunks, -1), at_tail(chunks, -1);
+    auto push = [&](std::unique_ptr<Stage> st, int lane, int after) {
+      st->lane = chunks > 1 ? lane : 0;
+      st->after = chunks > 1 ? after : -1;
+      vk->stages_.push_back(std::move(st));
+      return static_cast<int>(vk->stages_.size()) - 1;
+    };
+    if (chunks > 1) {
+      at_mm[0] = push(std::move(mm_c[0]), 0, -1);
+      at_mm[1] = push(std::move(mm_c[1]), 0, -1);
+    }
+    at_rs[0] = push(std::move(rs_c[0]), 1, chunks > 1 ? at_mm[0] : -1);
+    for (int c = 0; c < chunks; ++c) {
+      if (c + 1 < chunks) at_rs[c + 1] = push(std::move(rs_c[c + 1]), 1, at_mm[c + 1]);
+      at_tail[c] = push(std::move(tail_c[c]), 0, at_rs[c]);
+      if (c + 2 < chunks) at_mm[c + 2] = push(std::move(mm_c[c + 2]), 0, -1);
+      for (auto &ag : ag_c[c]) push(std::move(ag), 1, at_tail[c]);
     }
     done.insert(n);
     return true;

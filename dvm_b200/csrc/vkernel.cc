@@ -5,6 +5,8 @@
 #include <cstring>
 #include <string>
 
+#include <cuda_runtime.h>
+
 #include "comm.h"
 #include "graph.h"
 #include "runtime.h"
@@ -16,6 +18,10 @@ namespace dvm {
 VKernel::~VKernel() {
   ClearStages();
   for (auto n : nodes_) delete n;
+  for (void *e : stage_events_)
+    if (e) cudaEventDestroy(static_cast<cudaEvent_t>(e));
+  if (join_event_) cudaEventDestroy(static_cast<cudaEvent_t>(join_event_));
+  if (side_stream_) cudaStreamDestroy(static_cast<cudaStream_t>(side_stream_));
 }
 
 void VKernel::ClearStages() {
@@ -162,9 +168,61 @@ void VKernel::Bind(const RelocEntry *relocs, size_t n, void *workspace) {
   }
 }
 
+// A plan with two lanes: every stage goes to its lane's stream in list order; a stage whose `after` ran on the other lane
+// waits for that stage's event first.  The launch stream finally waits for the second stream, so that the caller sees
+// the usual contract (everything enqueued on `stream` is ordered behind the kernel).
+int VKernel::LaunchPipelined(void *stream) {
+  cudaStream_t main_s = static_cast<cudaStream_t>(stream);
+  if (side_stream_ == nullptr) {
+    cudaStream_t s = nullptr;
+    if (cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) DvmException("cannot create the second launch stream");
+    side_stream_ = s;
+    cudaEvent_t e = nullptr;
+    if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) DvmException("cannot create an event");
+    join_event_ = e;
+  }
+  cudaStream_t side_s = static_cast<cudaStream_t>(side_stream_);
+  if (stage_events_.size() < stages_.size()) stage_events_.resize(stages_.size(), nullptr);
+  std::vector<char> signals(stages_.size(), 0);
+  for (auto &st : stages_)
+    if (st->after >= 0 && stages_[st->after]->lane != st->lane) signals[st->after] = 1;
+  bool side_used = false;
+  for (size_t i = 0; i < stages_.size(); ++i) {
+    Stage &st = *stages_[i];
+    cudaStream_t s = st.lane ? side_s : main_s;
+    if (st.after >= 0 && stages_[st.after]->lane != st.lane) {
+      if (cudaStreamWaitEvent(s, static_cast<cudaEvent_t>(stage_events_[st.after]), 0) != cudaSuccess) return static_cast<int>(cudaGetLastError());
+    } else if (st.lane && !side_used) {
+      // the first stage of the second stream is ordered behind whatever the launch stream holds
+      if (cudaEventRecord(static_cast<cudaEvent_t>(join_event_), main_s) != cudaSuccess ||
+          cudaStreamWaitEvent(side_s, static_cast<cudaEvent_t>(join_event_), 0) != cudaSuccess)
+        return static_cast<int>(cudaGetLastError());
+    }
+    side_used |= st.lane != 0;
+    int err = LaunchStage(i, s);
+    if (err != 0) return err;
+    if (signals[i]) {
+      if (stage_events_[i] == nullptr) {
+        cudaEvent_t e = nullptr;
+        if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) DvmException("cannot create an event");
+        stage_events_[i] = e;
+      }
+      if (cudaEventRecord(static_cast<cudaEvent_t>(stage_events_[i]), s) != cudaSuccess) return static_cast<int>(cudaGetLastError());
+    }
+  }
+  if (side_used) {
+    if (cudaEventRecord(static_cast<cudaEvent_t>(join_event_), side_s) != cudaSuccess ||
+        cudaStreamWaitEvent(main_s, static_cast<cudaEvent_t>(join_event_), 0) != cudaSuccess)
+      return static_cast<int>(cudaGetLastError());
+  }
+  return 0;
+}
+
 int VKernel::Launch(void *stream) {
   if (!compiled_) DvmException("Launch before CodeGen");
   dvmb::Runtime::Get().EnsureInit();
+  for (auto &st : stages_)
+    if (st->lane != 0) return LaunchPipelined(stream);
   for (size_t i = 0; i < stages_.size(); ++i) {
     int err = LaunchStage(i, stream);
     if (err != 0) return err;

@@ -91,6 +91,7 @@ dist.broadcast_object_list(box, src=0)
 m, n, k = {m}, {n}, {k}
 got, das = T._run_rank(rank, world, box[0], m, n, k)
 assert "reduce_scatter" in das and "all_gather" in das, das
+assert das.count("mmain.") == int(os.environ["DVM_B200_TP_CHUNKS"]), das
 want = T._oracle(*T._inputs(m, n, k))
 T.assert_close(got, want, T.TOL_HALF, "rank %d of %d" % (rank, world))
 T._check_scatter_gather(rank, world)
@@ -99,7 +100,9 @@ print("RANK_OK", rank)
 """
 
 
-def test_k_split_over_all_visible_gpus_matches_the_unsplit_graph():
+@pytest.mark.parametrize("m,chunks", [(1024, 1), (2048, 4)])
+def test_k_split_over_all_visible_gpus_matches_the_unsplit_graph(m, chunks):
+    # (with four row chunks the collectives run on the kernel's second stream beside the next chunk's MatMul)
     import torch
     world = min(torch.cuda.device_count(), 8)
     if world < 2:
@@ -108,11 +111,11 @@ def test_k_split_over_all_visible_gpus_matches_the_unsplit_graph():
     s.bind(("127.0.0.1", 0))
     port = s.getsockname()[1]
     s.close()
-    m, n, k = 1024, 768, 128 * world
+    n, k = 768, 128 * world
     procs = []
     for r in range(world):
         env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
-                   NCCL_NVLS_ENABLE="0")
+                   NCCL_NVLS_ENABLE="0", DVM_B200_TP_CHUNKS=str(chunks))
         procs.append(subprocess.Popen([sys.executable, "-c", _CHILD.format(root=ROOT, m=m, n=n, k=k)], env=env,
                                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
     outs = [p.communicate(timeout=300)[0] for p in procs]

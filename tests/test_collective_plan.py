@@ -41,7 +41,8 @@ def _collectives(das):
     return out
 
 
-def test_row_independent_tail_becomes_reduce_scatter_tail_all_gather():
+def test_row_independent_tail_becomes_reduce_scatter_tail_all_gather(monkeypatch):
+    monkeypatch.setenv("DVM_B200_TP_CHUNKS", "1")   # (the plan of one chunk; the pipelined plan is checked below)
     m, n, k, world, rank = 16384, 8192, 1024, 8, 3
     kk = _tp_kernel(rank, world, m, n, k)
     das = kk.das()
@@ -57,6 +58,41 @@ def test_row_independent_tail_becomes_reduce_scatter_tail_all_gather():
     assert rs["wire"] == blk * 4 * (world - 1) and ag["wire"] == blk * 2 * (world - 1)
     assert "group_elems=%d" % blk in das                                    # the tail works on m / world rows
     assert "workspace_bytes=%d" % (m * n * 4) in kk.inspect()
+
+
+def test_products_can_be_cut_into_row_chunks_on_two_lanes(monkeypatch):
+    # DVM_B200_TP_CHUNKS=4: four row chunks; chunk c's reduce-scatter, tail and all-gather are enqueued so that the launch
+    # stream (MatMuls and tails) and the second stream (collectives) overlap, every rank in the same order
+    monkeypatch.setenv("DVM_B200_TP_CHUNKS", "4")
+    m, n, k, world, rank = 16384, 8192, 1024, 8, 3
+    kk = _tp_kernel(rank, world, m, n, k)
+    das = kk.das()
+    names = re.findall(r"^(\w+main)\.", das, re.M)
+    assert names == ["mmain", "mmain", "cmain", "cmain", "vmain", "mmain", "cmain", "cmain", "vmain", "mmain", "cmain", "cmain",
+                     "vmain", "cmain", "vmain", "cmain"], names
+    colls = _collectives(das)
+    kinds = [c["kind"] for c in colls]
+    assert kinds == ["reduce_scatter", "reduce_scatter", "all_gather", "reduce_scatter", "all_gather", "reduce_scatter",
+                     "all_gather", "all_gather"]
+    chunks, mc = 4, m // 4
+    blk = mc // world * n                                   # a rank's rows of one chunk
+    rs = [c for c in colls if c["kind"] == "reduce_scatter"]
+    ag = [c for c in colls if c["kind"] == "all_gather"]
+    for c in range(chunks):
+        assert rs[c]["count"] == blk and ag[c]["count"] == blk
+        assert rs[c]["send"] - rs[0]["send"] == c * mc * n * 4          # chunk c of the fp32 temporary ...
+        assert rs[c]["recv"] - rs[c]["send"] == rank * blk * 4          # ... reduced in place onto the rank's rows of it
+        assert ag[c]["recv"] - ag[0]["recv"] == c * mc * n * 2          # chunk c of the caller's bf16 result
+        assert ag[c]["send"] - ag[c]["recv"] == rank * blk * 2
+    assert das.count("m=%d, n=%d, k=%d" % (mc, n, k)) == chunks         # four MatMuls of a quarter of the rows
+    assert das.count("group_elems=%d" % blk) >= chunks or das.count("groups=%d" % (mc // world)) >= chunks
+    assert "workspace_bytes=%d" % (m * n * 4) in kk.inspect()
+    # chunks that would split a MatMul tile or a rank's rows are not made; without the switch the plan is one chunk
+    small = _tp_kernel(rank, world, 256, 512, 256)
+    assert re.findall(r"^(\w+main)\.", small.das(), re.M) == ["mmain", "cmain", "vmain", "cmain"]
+    monkeypatch.delenv("DVM_B200_TP_CHUNKS")
+    plain = _tp_kernel(rank, world, m, n, k)
+    assert re.findall(r"^(\w+main)\.", plain.das(), re.M) == ["mmain", "cmain", "vmain", "cmain"]
 
 
 def test_row_dependent_tail_keeps_the_plain_all_reduce():
