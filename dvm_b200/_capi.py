@@ -60,6 +60,7 @@ SIGNATURES = {
     "dvm_slice": (c_void_p, [c_void_p, c_void_p, c_void_p, c_void_p]),
     "dvm_slice_dim": (c_void_p, [c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "dvm_split_chunk": (c_void_p, [c_void_p, c_void_p, c_int, c_int64, c_size_t, c_size_t]),
+    "dvm_concat": (c_void_p, [c_void_p, ctypes.POINTER(c_void_p), c_size_t, c_int]),
     "dvm_copy": (c_void_p, [c_void_p, c_void_p]),
     "dvm_matmul": (c_void_p, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "dvm_comm_new": (c_void_p, []),

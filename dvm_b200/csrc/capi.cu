@@ -205,6 +205,15 @@ dvm_object *dvm_split_chunk(dvm_kernel *k, dvm_object *input, int dim, int64_t s
     },
     static_cast<dvm_object *>(nullptr));
 }
+dvm_object *dvm_concat(dvm_kernel *k, dvm_object **inputs, size_t input_num, int dim) {
+  return Guard(
+    [&]() {
+      std::vector<dvm::NDObject *> in(input_num);
+      for (size_t i = 0; i < input_num; ++i) in[i] = N(inputs[i]);
+      return O(k->kernel.Concat(in.data(), input_num, dim));
+    },
+    static_cast<dvm_object *>(nullptr));
+}
 dvm_object *dvm_copy(dvm_kernel *k, dvm_object *input) { return DVM_OBJ_GUARD(k->kernel.Copy(N(input))); }
 dvm_object *dvm_matmul(dvm_kernel *k, dvm_object *lhs, dvm_object *rhs, int trans_a, int trans_b, dvm_object *bias) {
   return DVM_OBJ_GUARD(k->kernel.MatMul(N(lhs), N(rhs), trans_a != 0, trans_b != 0, bias ? N(bias) : nullptr));

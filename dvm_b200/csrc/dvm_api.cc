@@ -562,7 +562,22 @@ NDObject *Kernel::Slice(NDObject *input, int dim, ScalarRef *begin, ScalarRef *e
   n->scalar_ref2 = end;
   return n;
 }
-NDObject *Kernel::Concat(NDObject **, size_t, int) { Unsupported("Concat"); }
+// ref: include/dvm.h:455-469 - the inputs one after the other along `dim` (same type, same extents elsewhere)
+NDObject *Kernel::Concat(NDObject **inputs, size_t input_num, int dim) {
+  if (inputs == nullptr || input_num == 0) DvmException("Concat needs at least one input");
+  auto vk = Impl(this);
+  NDObject *acc = inputs[0];
+  if (input_num == 1) return Copy(acc);
+  for (size_t i = 1; i < input_num; ++i) {
+    if (inputs[i]->dtype != acc->dtype) DvmException("Concat inputs must have one type");
+    auto n = vk->NewNode(N_CONCAT, acc->dtype);
+    n->in[0] = acc;
+    n->in[1] = inputs[i];
+    n->view_dim = dim;
+    acc = n;
+  }
+  return acc;
+}
 // ref: include/dvm.h:470-479 - equal chunks along `dim` (the last may be smaller); the returned array is owned by the kernel
 NDObject **Kernel::Split(NDObject *input, int dim, int64_t split_size, size_t split_num) {
   auto vk = Impl(this);

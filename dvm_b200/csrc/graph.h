@@ -52,6 +52,8 @@ enum NodeKind : uint8_t {
   N_REDUCE,     // sub = ReduceType
   N_MATMUL,
   N_VIEW,       // Permute / Slice / Split: the input's memory seen through another shape, strides and offset
+  N_CONCAT,     // in[0] followed by in[1] along dim `view_dim`; Kernel::Concat of n inputs is a chain of n - 1 of these, which
+                // the stage planner writes as n slabs of one workspace tensor
   N_ALLREDUCE,  // a collective over the ranks of `comm`: `coll` 0 all-reduce (sub = ReduceType), 1 reduce-scatter (sum),
                 // 2 all-gather along the leading dim
 };

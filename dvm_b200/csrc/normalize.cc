@@ -138,6 +138,20 @@ void InferShape(NDObject *n) {
       n->shape = o;
       break;
     }
+    case N_CONCAT: {
+      const Shape &a = n->in[0]->shape, &b = n->in[1]->shape;
+      if (a.rank != b.rank || a.rank == 0) Fail(n, "concat inputs must have one rank");
+      int d = n->view_dim;
+      if (d < 0) d += a.rank;
+      if (d < 0 || d >= a.rank) Fail(n, "concat dimension out of range");
+      Shape o = a;
+      for (int i = 0; i < a.rank; ++i)
+        if (i != d && a.d[i] != b.d[i]) Fail(n, "concat inputs differ outside the concatenated dimension");
+      o.d[d] = a.d[d] + b.d[d];
+      n->view_from[0] = d;   // (the normalised dimension, for the planner)
+      n->shape = o;
+      break;
+    }
     case N_VIEW: {
       const Shape &in = n->in[0]->shape;
       Shape o = in;

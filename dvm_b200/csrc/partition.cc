@@ -64,6 +64,8 @@ struct Planner {
     }
   }
 
+  std::unordered_set<const NDObject *> slabbed;   // values that a launch writes straight into their slab of a Concat result
+
   NDObject *Synth(const NDObject *like) {
     auto n = new NDObject(*like);
     n->origin = nullptr;
@@ -150,7 +152,13 @@ struct Planner {
       if (n->in[j]) in[j] = InputFor(b, n->in[j]);
     NDObject *c = Synth(n);
     for (int j = 0; j < 3; ++j) c->in[j] = in[j];
-    if (n->kind == N_STORE) c->origin = n;
+    if (n->kind == N_STORE) {
+      if (n->ws_off >= 0) {
+        c->ws_off = n->ws_off;   // (a store the planner made itself: a Concat slab in the workspace)
+      } else {
+        c->origin = n;
+      }
+    }
     b.clone[n] = c;
     b.list.push_back(c);
     return c;
@@ -161,6 +169,7 @@ struct Planner {
     if (it == users.end()) return false;
     for (auto u : it->second) {
       if (u->kind == N_STORE && !IsLazy(n)) continue;   // stores travel with their value
+      if (u->kind == N_CONCAT && slabbed.count(n)) continue;   // (the value goes to its slab of the Concat result instead)
       if (u->kind == N_BROADCAST) {
         if (HasOutsideUser(u, area)) return true;
         continue;
@@ -594,6 +603,108 @@ struct Planner {
     done.insert(n);
   }
 
+  // ---- Concat ----------------------------------------------------------------------------------------------
+  // Kernel::Concat arrives as a chain of two-input nodes along one dimension.  The chain's last node writes all its
+  // pieces as slabs of one workspace tensor (a strided store each, one launch per piece); the nodes inside the chain do
+  // nothing of their own.  Whatever reads the result reads that tensor.
+  bool InsideConcatChain(const NDObject *n) const {
+    auto it = users.find(n);
+    if (it == users.end() || it->second.size() != 1) return false;
+    const NDObject *u = it->second[0];
+    return u->kind == N_CONCAT && u->in[0] == n && u->in[1] != n && u->view_from[0] == n->view_from[0];
+  }
+
+  void PlaceConcat(NDObject *n) {
+    if (InsideConcatChain(n)) return;   // (placed with the end of its chain)
+    const int d = n->view_from[0];
+    std::vector<NDObject *> pieces, inner;
+    for (NDObject *c = n;;) {
+      pieces.insert(pieces.begin(), c->in[1]);
+      NDObject *a = c->in[0];
+      if (a->kind == N_CONCAT && InsideConcatChain(a) && !done.count(a)) {
+        inner.push_back(a);
+        c = a;
+        continue;
+      }
+      pieces.insert(pieces.begin(), a);
+      break;
+    }
+    NDObject *dst = SynthLoad(n, n->shape);
+    dst->ws_off = static_cast<int64_t>(AllocWs(n));
+    int64_t stride[kMaxRank];
+    int64_t dense = 1;
+    for (int i = n->shape.rank - 1; i >= 0; --i) {
+      stride[i] = dense;
+      dense *= n->shape.d[i];
+    }
+    auto slab_store = [&](NDObject *value, const Shape &shape, int64_t at) {
+      auto st = new NDObject();
+      vk->synth_.push_back(st);
+      st->kind = N_STORE;
+      st->dtype = n->dtype;
+      st->shape = shape;
+      st->in[0] = value;
+      st->id = n->id;
+      st->ws_off = dst->ws_off;
+      st->addr_off = at * stride[d] * static_cast<int64_t>(ItemSize(n->dtype));
+      st->strided = true;
+      for (int i = 0; i < n->shape.rank; ++i) st->stride[i] = stride[i];
+      return st;
+    };
+    // a piece the open area computes goes to its slab from the launch that makes it, when that launch can hold the
+    // strided store; anything else is copied from where it lives
+    std::vector<int64_t> starts;
+    int64_t at = 0;
+    for (auto p : pieces) {
+      starts.push_back(at);
+      at += p->shape.d[d];
+    }
+    std::vector<char> placed(pieces.size(), 0);
+    for (size_t i = 0; i < pieces.size(); ++i) {
+      NDObject *p = pieces[i];
+      if (!in_cur.count(p) || slabbed.count(p) || p->shape.numel() == 0) continue;
+      NDObject *st = slab_store(p, p->shape, starts[i]);
+      users[p].push_back(st);
+      slabbed.insert(p);
+      std::string why;
+      if (TryVector(cur, false, &why)) {
+        placed[i] = 1;
+      } else {
+        users[p].pop_back();
+        slabbed.erase(p);
+      }
+    }
+    for (size_t i = 0; i < pieces.size(); ++i) {
+      NDObject *p = pieces[i];
+      if (placed[i] || InMemory(p)) continue;
+      if (p->kind == N_BROADCAST || p->kind == N_BROADCAST_S) {
+        Materialize(p);
+      } else {
+        CloseCur();   // the open area stores the piece to the workspace: the chain reads it from outside the area
+      }
+      if (!InMemory(p)) DvmException("Concat of a value that is not in memory");
+    }
+    CloseCur();
+    for (size_t i = 0; i < pieces.size(); ++i) {
+      NDObject *p = pieces[i];
+      if (placed[i] || p->shape.numel() == 0) continue;
+      Build b;
+      NDObject *src = InputFor(b, p);
+      b.list.push_back(slab_store(src, p->shape, starts[i]));
+      auto stage = std::make_unique<Stage>();
+      stage->kind = STAGE_VECTOR;
+      std::string why;
+      if (!CompileVectorStage(b.list, &stage->vec, &why)) {
+        std::string msg = "cannot write a Concat input to its slab: " + why;
+        DvmException(msg.c_str());
+      }
+      vk->stages_.push_back(std::move(stage));
+    }
+    mem[n] = dst;
+    done.insert(n);
+    for (auto c : inner) done.insert(c);
+  }
+
   // ---- collectives -----------------------------------------------------------------------------------------
   void PushCollective(uint32_t kind, const NDObject *n, NDObject *send, int64_t send_off, NDObject *recv, int64_t recv_off,
                       uint64_t count, uint64_t wire_bytes) {
@@ -952,6 +1063,7 @@ struct Planner {
           break;
         case N_ALLREDUCE: PlaceAllReduce(n); break;
         case N_VIEW: PlaceView(n); break;
+        case N_CONCAT: PlaceConcat(n); break;
         default: AddVector(n); break;
       }
     }

@@ -1232,6 +1232,7 @@ struct Compiler {
       if (n->kind == N_MATMUL) throw Fail{"MatMul inside a vector stage"};
       if (n->kind == N_ALLREDUCE) throw Fail{"a collective inside a vector stage"};
       if (n->kind == N_VIEW) throw Fail{"a view inside a vector stage"};
+      if (n->kind == N_CONCAT) throw Fail{"a concatenation inside a vector stage"};
     }
     AlignAxes();
     Classify();

@@ -91,7 +91,7 @@ size_t VKernel::Compile() {
   }
   bool has_matmul = false, has_empty = false, stacked = false;
   for (auto n : ops) {
-    has_matmul |= n->kind == N_MATMUL || n->kind == N_ALLREDUCE || n->kind == N_VIEW;   // (anything that needs the stage planner)
+    has_matmul |= n->kind == N_MATMUL || n->kind == N_ALLREDUCE || n->kind == N_VIEW || n->kind == N_CONCAT;   // (anything that needs the stage planner)
     has_empty |= n->shape.numel() == 0;   // the planner drops empty tensors and keeps what still has elements
     stacked |= n->sub_kernel != ops.front()->sub_kernel;   // kSequence / kParallel: every sub-kernel gets launches of its own
   }
@@ -295,6 +295,7 @@ static const char *KindName(const NDObject *n) {
       static const char *views[] = {"Permute", "Slice", "Slice", "Split"};
       return views[n->sub & 3];
     }
+    case N_CONCAT: return "Concat";
     case N_ALLREDUCE:
       if (n->coll == 1) return "ReduceScatter";
       if (n->coll == 2) return "AllGather";

@@ -279,6 +279,12 @@ class Kernel:
         return [self._obj(self._lib.dvm_split_chunk(self._k, input._h, int(dim), int(split_size), int(split_num), i), "split")
                 for i in range(int(split_num))]
 
+    def concat(self, inputs, dim):
+        """KernelPy::Concat (include/dvm_py.h): the inputs one after the other along `dim`."""
+        import ctypes
+        arr = (ctypes.c_void_p * len(inputs))(*[x._h for x in inputs])
+        return self._obj(self._lib.dvm_concat(self._k, arr, len(inputs), int(dim)), "concat")
+
     def copy(self, input):
         return self._obj(self._lib.dvm_copy(self._k, input._h), "copy")
 

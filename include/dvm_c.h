@@ -87,6 +87,8 @@ DVM_C_API dvm_object *dvm_slice(dvm_kernel *k, dvm_object *input, dvm_int_array 
 DVM_C_API dvm_object *dvm_slice_dim(dvm_kernel *k, dvm_object *input, int dim, dvm_scalar *begin, dvm_scalar *end);
 DVM_C_API dvm_object *dvm_split_chunk(dvm_kernel *k, dvm_object *input, int dim, int64_t split_size, size_t split_num,
                                       size_t index);
+/* Kernel::Concat (dvm.h:469): the inputs one after the other along `dim` */
+DVM_C_API dvm_object *dvm_concat(dvm_kernel *k, dvm_object **inputs, size_t input_num, int dim);
 DVM_C_API dvm_object *dvm_copy(dvm_kernel *k, dvm_object *input);                             /* dvm.h:466 */
 DVM_C_API dvm_object *dvm_matmul(dvm_kernel *k, dvm_object *lhs, dvm_object *rhs, int trans_a, int trans_b,
                                  dvm_object *bias);                                           /* dvm.h:509 */

@@ -62,14 +62,31 @@ int main(int argc, char **argv) {
   try {
     dvm::Kernel bad;
     bad.Reset(dvm::kVector, 0);
-    dvm::NDObject *parts[2] = {bad.Load(nullptr, &shape_ref, dvm::kFloat32), bad.Load(nullptr, &shape_ref, dvm::kFloat32)};
-    bad.Concat(parts, 2, 0);
+    bad.ElemAny(bad.Load(nullptr, &shape_ref, dvm::kFloat32));
   } catch (const std::runtime_error &e) {
     threw = std::strstr(e.what(), "DVM EXCEPTION") != nullptr;
   }
   if (!threw) {
-    std::printf("FAIL: Concat did not raise DvmException\n");
+    std::printf("FAIL: ElemAny did not raise DvmException\n");
     return 1;
+  }
+  {
+    // Concat: two inputs one after the other along the rows (planned as two slabs of one workspace tensor)
+    dvm::Kernel c;
+    c.Reset(dvm::kVector, 0);
+    dvm::NDObject *parts[2] = {c.Load(nullptr, &shape_ref, dvm::kFloat32), c.Load(nullptr, &shape_ref, dvm::kFloat32)};
+    dvm::NDObject *cat = c.Concat(parts, 2, 0);
+    c.Store(nullptr, c.Binary<dvm::kAdd>(cat, 1.0f));
+    c.Normalize();
+    dvm::IntArrayRef *cs = dvm::Kernel::GetShape(cat);
+    if (cs->size != 2 || cs->data[0] != 2 * rows) {
+      std::printf("FAIL: inferred shape of a Concat\n");
+      return 1;
+    }
+    if (c.PreCodeGen() == 0) {
+      std::printf("FAIL: a Concat result needs a workspace\n");
+      return 1;
+    }
   }
   {
     // a view: the transpose of a Load is its memory read through permuted strides (no copy, no workspace)

@@ -317,3 +317,21 @@ def test_view_ops_infer_shapes_and_plan_without_a_copy():
         bad = dvm.PyKernel("vector", "das", 0)
         bad.store(bad.slice(bad.load([4, 4], dvm.float32), [2, 2], [4, 4]))
         bad.codegen()
+
+
+def test_concat_is_planned_as_slabs_of_one_workspace_tensor():
+    # Kernel::Concat: every input is written to its slab by a launch of its own (a strided store), the ops behind the result
+    # read the whole tensor; inputs must agree outside the concatenated dimension
+    k = dvm.PyKernel("vector", "das", 0)
+    a, b, c = k.load([8, 100], dvm.float32), k.load([8, 28], dvm.float32), k.load([8, 1], dvm.float32)
+    cat = k.concat([k.add(a, 1.0), b, c], 1)
+    k.store(k.mul(cat, 2.0))
+    k.codegen()
+    assert list(cat.shape()) == [8, 129]
+    das = k.das()
+    # the first input's add and its slab store are one launch; the workspace holds the concatenated tensor and nothing else
+    assert das.count("vmain.") == 4 and "workspace_bytes=%d" % ((8 * 129 * 4 + 255) // 256 * 256) in k.inspect()
+    bad = dvm.PyKernel("vector", "das", 0)
+    bad.store(bad.concat([bad.load([8, 100], dvm.float32), bad.load([7, 100], dvm.float32)], 1))
+    with pytest.raises(Exception, match="concat inputs differ"):
+        bad.codegen()
