@@ -145,6 +145,14 @@ dvm_object *dvm_store(dvm_kernel *k, void *addr, dvm_object *input) { return DVM
 dvm_object *dvm_load_strided(dvm_kernel *k, void *addr, dvm_int_array *shape, dvm_int_array *stride, int dtype) {
   return DVM_OBJ_GUARD(k->kernel.Load(addr, &shape->ref, &stride->ref, static_cast<dvm::DataType>(dtype)));
 }
+dvm_object *dvm_slice_load(dvm_kernel *k, void *addr, dvm_int_array *shape, dvm_int_array *start, dvm_int_array *size, int dtype) {
+  return DVM_OBJ_GUARD(k->kernel.SliceLoad(addr, &shape->ref, &start->ref, &size->ref, static_cast<dvm::DataType>(dtype)));
+}
+dvm_object *dvm_strided_slice_load(dvm_kernel *k, void *addr, dvm_int_array *shape, dvm_int_array *start, dvm_int_array *end,
+                                   dvm_int_array *step, int dtype) {
+  return DVM_OBJ_GUARD(
+    k->kernel.StridedSliceLoad(addr, &shape->ref, &start->ref, &end->ref, &step->ref, static_cast<dvm::DataType>(dtype)));
+}
 dvm_object *dvm_store_strided(dvm_kernel *k, void *addr, dvm_object *input, dvm_int_array *stride) {
   return DVM_OBJ_GUARD(k->kernel.Store(addr, N(input), &stride->ref));
 }

@@ -360,9 +360,23 @@ NDObject *Kernel::Load(void *addr, IntArrayRef *shape, IntArrayRef *stride, Data
 }
 NDObject *Kernel::GlobalAccess(void *, IntArrayRef *, DataType) { Unsupported("GlobalAccess"); }
 NDObject *Kernel::GatherLoad(void *, IntArrayRef *, NDObject *, int, DataType, GatherMode) { Unsupported("GatherLoad"); }
-NDObject *Kernel::SliceLoad(void *, IntArrayRef *, IntArrayRef *, IntArrayRef *, DataType) { Unsupported("SliceLoad"); }
-NDObject *Kernel::StridedSliceLoad(void *, IntArrayRef *, IntArrayRef *, IntArrayRef *, IntArrayRef *, DataType) {
-  Unsupported("StridedSliceLoad");
+// ref: include/dvm.h:305-317 - a window of a tensor in memory, given by start + size or by start / end / step per dim: a
+// strided load (the window is never copied)
+NDObject *Kernel::SliceLoad(void *addr, IntArrayRef *shape, IntArrayRef *start, IntArrayRef *size, DataType type) {
+  NDObject *n = Load(addr, shape, type);
+  n->slice_mode = 1;
+  n->slice_a = start;
+  n->slice_b = size;
+  return n;
+}
+NDObject *Kernel::StridedSliceLoad(void *addr, IntArrayRef *shape, IntArrayRef *start, IntArrayRef *end, IntArrayRef *step,
+                                   DataType type) {
+  NDObject *n = Load(addr, shape, type);
+  n->slice_mode = 2;
+  n->slice_a = start;
+  n->slice_b = end;
+  n->slice_c = step;
+  return n;
 }
 NDObject *Kernel::MultiLoad(void *, IntArrayRef *, DataType, const Comm *) { Unsupported("MultiLoad"); }
 

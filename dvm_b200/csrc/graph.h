@@ -86,6 +86,11 @@ class NDObject {
   IntArrayRef *stride_ref = nullptr;  // strided (view) Load / Store: element strides of the tensor in memory (borrowed)
   bool strided = false;               // results of Normalize() for a view: `stride` holds one element stride per dim
   int64_t stride[kMaxRank] = {0};
+  // SliceLoad / StridedSliceLoad: a window of the tensor at `addr` whose full shape is shape_ref.  slice_mode 1: start +
+  // size (slice_a, slice_b); 2: start, end, step (slice_a, slice_b, slice_c; indices as in Python slicing).  Normalize()
+  // turns it into a strided load: shape = the window, stride = the tensor's strides times the steps, addr_off = the start
+  uint8_t slice_mode = 0;
+  IntArrayRef *slice_a = nullptr, *slice_b = nullptr, *slice_c = nullptr;
   void *addr = nullptr;               // Load/Store device address
   // nodes the stage planner makes: a clone of a user's Load/Store (`origin` supplies the address) or a
   // temporary in the kernel's workspace (`ws_off` >= 0, bytes from the workspace base)

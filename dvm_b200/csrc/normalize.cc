@@ -80,6 +80,37 @@ void InferShape(NDObject *n) {
       n->shape = FromRef(n, n->shape_ref);
       for (int i = 0; i < n->shape.rank; ++i)
         if (n->shape.d[i] < 0) Fail(n, "negative dimension");
+      if (n->slice_mode != 0) {
+        const Shape full = n->shape;
+        const int r = full.rank;
+        if (n->slice_a == nullptr || n->slice_b == nullptr || static_cast<int>(n->slice_a->size) != r ||
+            static_cast<int>(n->slice_b->size) != r || (n->slice_mode == 2 && (n->slice_c == nullptr || static_cast<int>(n->slice_c->size) != r)))
+          Fail(n, "a slice load needs one start, one size (or end and step) per dimension");
+        int64_t dense = 1, off = 0;
+        for (int i = r - 1; i >= 0; --i) {
+          int64_t b = n->slice_a->data[i], len = 0, step = 1;
+          if (n->slice_mode == 1) {
+            len = n->slice_b->data[i];
+            if (b < 0 || len < 0 || b + len > full.d[i]) Fail(n, "slice outside its tensor");
+          } else {   // start / end as Python slices read them
+            int64_t e = n->slice_b->data[i];
+            step = n->slice_c->data[i];
+            if (step <= 0) Fail(n, "slice steps must be positive");
+            if (b < 0) b += full.d[i];
+            if (e < 0) e += full.d[i];
+            b = std::min<int64_t>(std::max<int64_t>(b, 0), full.d[i]);
+            e = std::min<int64_t>(std::max<int64_t>(e, b), full.d[i]);
+            len = (e - b + step - 1) / step;
+          }
+          n->shape.d[i] = len;
+          n->stride[i] = dense * step;
+          off += b * dense;
+          dense *= full.d[i];
+        }
+        n->strided = true;
+        n->addr_off = off * static_cast<int64_t>(ItemSize(n->dtype));
+        break;
+      }
       ReadStrides(n);
       break;
     case N_STORE:

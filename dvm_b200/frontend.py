@@ -192,6 +192,23 @@ class Kernel:
         op._shape_ref = ref
         return op
 
+    def slice_load(self, shape, start, size, type):
+        """A window (start + size per dim) of a tensor in memory whose whole shape is `shape` (KernelPy::SliceLoad)."""
+        ref = self._shape_ref(shape)
+        op = self._obj(self._lib.dvm_slice_load(self._k, None, ref._h, self._shape_ref(list(start))._h,
+                                                self._shape_ref(list(size))._h, int(type)), "slice_load")
+        op._shape_ref = ref
+        return op
+
+    def stridedslice_load(self, shape, start, end, step, type):
+        """The same with start / end / step per dim, read as Python slices are (KernelPy::StridedSliceLoad)."""
+        ref = self._shape_ref(shape)
+        op = self._obj(self._lib.dvm_strided_slice_load(self._k, None, ref._h, self._shape_ref(list(start))._h,
+                                                        self._shape_ref(list(end))._h, self._shape_ref(list(step))._h,
+                                                        int(type)), "stridedslice_load")
+        op._shape_ref = ref
+        return op
+
     def view_store(self, obj, stride, type=None):
         """Store with element strides; what lies between the written elements keeps its content (KernelPy::ViewStore,
         include/dvm_py.h:107)."""
@@ -519,6 +536,16 @@ class PyKernel(Kernel):
 
     def view_load(self, shape, stride, type):
         op = Kernel.view_load(self, shape, stride, type)
+        self._loads.append([op, None, None])
+        return op
+
+    def slice_load(self, shape, start, size, type):
+        op = Kernel.slice_load(self, shape, start, size, type)
+        self._loads.append([op, None, None])
+        return op
+
+    def stridedslice_load(self, shape, start, end, step, type):
+        op = Kernel.stridedslice_load(self, shape, start, end, step, type)
         self._loads.append([op, None, None])
         return op
 

@@ -58,6 +58,30 @@ class Tester(PyKernel):
         self.input(op, shape_arr)
         return op
 
+    def _whole_array(self, arr, dtype):
+        dtype_id = _normalize_dtype(arr.dtype if dtype is None else dtype)
+        if dtype_id == DataType.bfloat16 and (_BF16 is None or arr.dtype != _BF16):
+            arr = PyKernel.convert_to_bf16(arr)
+        return arr, dtype_id
+
+    def slice_load(self, shape_arr, start, size, dtype=None):
+        """python/dvm/tester.py:151-160: the window start + size of an array (or of a dynamic-shape input)."""
+        if not isinstance(shape_arr, np.ndarray):
+            return PyKernel.slice_load(self, shape_arr, start, size, _normalize_dtype(dtype))
+        arr, dtype_id = self._whole_array(shape_arr, dtype)
+        op = PyKernel.slice_load(self, list(arr.shape), start, size, dtype_id)
+        self.input(op, arr)
+        return op
+
+    def stridedslice_load(self, shape_arr, start, end, step, dtype=None):
+        """python/dvm/tester.py:162-171: the window start / end / step of an array, read as Python slices are."""
+        if not isinstance(shape_arr, np.ndarray):
+            return PyKernel.stridedslice_load(self, shape_arr, start, end, step, _normalize_dtype(dtype))
+        arr, dtype_id = self._whole_array(shape_arr, dtype)
+        op = PyKernel.stridedslice_load(self, list(arr.shape), start, end, step, dtype_id)
+        self.input(op, arr)
+        return op
+
     def view_load(self, shape, stride, arr_dtype, offset=0, real_dtype=None):
         """python/dvm/tester.py:120-132: a strided window of an array (or, given a dtype, of a dynamic-shape input)."""
         if not isinstance(arr_dtype, np.ndarray):

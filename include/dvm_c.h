@@ -81,6 +81,11 @@ DVM_C_API dvm_object *dvm_full_f32(dvm_kernel *k, float v, dvm_int_array *shape,
 DVM_C_API dvm_object *dvm_full_i64(dvm_kernel *k, int64_t v, dvm_int_array *shape, int dtype);
 DVM_C_API dvm_object *dvm_full_ref(dvm_kernel *k, dvm_scalar *v, dvm_int_array *shape, int dtype);
 DVM_C_API dvm_object *dvm_reshape(dvm_kernel *k, dvm_object *input, dvm_int_array *shape);    /* dvm.h:434 */
+/* a window of a tensor in memory (Kernel::SliceLoad dvm.h:312, StridedSliceLoad :317): `shape` is the whole tensor's */
+DVM_C_API dvm_object *dvm_slice_load(dvm_kernel *k, void *addr, dvm_int_array *shape, dvm_int_array *start,
+                                     dvm_int_array *size, int dtype);
+DVM_C_API dvm_object *dvm_strided_slice_load(dvm_kernel *k, void *addr, dvm_int_array *shape, dvm_int_array *start,
+                                             dvm_int_array *end, dvm_int_array *step, int dtype);
 /* views of the input's memory: Kernel::Permute (dvm.h:434), Slice (:443, :453), one chunk of Kernel::Split (:479) */
 DVM_C_API dvm_object *dvm_permute(dvm_kernel *k, dvm_object *input, dvm_int_array *dims);
 DVM_C_API dvm_object *dvm_slice(dvm_kernel *k, dvm_object *input, dvm_int_array *start, dvm_int_array *size);

@@ -335,3 +335,19 @@ def test_concat_is_planned_as_slabs_of_one_workspace_tensor():
     bad.store(bad.concat([bad.load([8, 100], dvm.float32), bad.load([7, 100], dvm.float32)], 1))
     with pytest.raises(Exception, match="concat inputs differ"):
         bad.codegen()
+
+
+def test_slice_loads_are_strided_loads_with_an_offset():
+    # Kernel::SliceLoad / StridedSliceLoad: the window's shape, the tensor's strides (times the steps) and the start as an
+    # address offset; a window outside the tensor is refused
+    k = dvm.PyKernel("vector", "das", 0)
+    x = k.slice_load([32, 64], [3, 8], [16, 32], dvm.float32)
+    y = k.stridedslice_load([32, 64], [-4, 0], [100, 64], [1, 2], dvm.float32)
+    k.store(k.mul(x, 2.0))
+    k.store(k.mul(y, 2.0))
+    k.codegen()
+    assert list(x.shape()) == [16, 32] and list(y.shape()) == [4, 32]
+    bad = dvm.PyKernel("vector", "das", 0)
+    bad.store(bad.mul(bad.slice_load([32, 64], [3, 40], [16, 32], dvm.float32), 2.0))
+    with pytest.raises(Exception, match="slice outside its tensor"):
+        bad.codegen()
