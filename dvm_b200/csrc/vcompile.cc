@@ -54,6 +54,11 @@ struct Compiler {
   int64_t dom[kMaxRank];
   bool reduced[kMaxRank];
   bool has_reduce = false;
+  // A reduce-free graph over more iterated axes than a tile walks (kMaxEnum after coalescing, e.g. a 5-d window of a
+  // larger tensor) is run like a reduction's: its outer axes become group axes (forced_outer) and the tile walks the
+  // rest.  There is no reduction, so the groups only serve as the outer loop.
+  bool forced_outer[kMaxRank] = {false};
+  int num_forced_outer = 0;
   std::vector<int> kept_axes, enum_axes;   // domain axes, outer -> inner
   // coalesced geometry
   struct CoAxis {
@@ -233,6 +238,10 @@ struct Compiler {
           if (reduced[a] != mine[a]) throw Fail{"reductions over different axes in one stage"};
       }
       has_reduce = true;
+    }
+    if (!has_reduce && num_forced_outer > 0) {
+      has_reduce = true;
+      for (int a = 0; a < R; ++a) reduced[a] = !forced_outer[a];
     }
     int nred = 0;
     for (int a = 0; a < R; ++a) nred += reduced[a] ? 1 : 0;
@@ -1237,7 +1246,25 @@ struct Compiler {
     AlignAxes();
     Classify();
     MarkExact();
-    Geometry();
+    const bool reduce_free = !has_reduce;
+    for (;;) {
+      try {
+        Geometry();
+        break;
+      } catch (const Fail &f) {
+        // too many iterated axes in a reduce-free graph: one more outer axis (of extent > 1) becomes a group axis
+        if (!reduce_free || epilogue || std::string(f.why).find("iterated axes") == std::string::npos) throw;
+        int next = -1;
+        for (int a = 0; a < R && next < 0; ++a)
+          if (!forced_outer[a] && dom[a] != 1) next = a;
+        if (next < 0 || num_forced_outer >= R - 1) throw;
+        forced_outer[next] = true;
+        ++num_forced_outer;
+        has_reduce = false;
+        Classify();
+        MarkExact();
+      }
+    }
     Emit();
     if (epilogue) {
       FillEpilogue(mm);

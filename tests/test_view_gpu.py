@@ -137,3 +137,46 @@ def test_views_of_computed_values_and_of_views():
     want = (a + 1.0).T
     assert_close(t.output(s1), want * b, TOL_FP32, "permute of a computed value")
     assert_close(t.output(s2), np.exp(want[16:48, 8:48]), TOL_FP32, "slice of a permuted value")
+
+
+def _dense_strides(shape):
+    st = [1] * len(shape)
+    for i in range(len(shape) - 1, 0, -1):
+        st[i - 1] = st[i] * shape[i]
+    return st
+
+
+@pytest.mark.parametrize("in_shape,window", [([4, 4, 5, 3, 16], [3, 2, 3, 2, 12]), ([4, 4, 4, 5, 6, 16], [3, 2, 3, 4, 5, 12])])
+def test_windows_of_five_and_six_dimensions(in_shape, window):
+    # more strided axes than a tile walks: the outer ones become the launch's groups (tests/ut/test_view.py:92-114)
+    rng = np.random.default_rng(51)
+    a = rng.normal(0, 1, in_shape).astype(np.float32)
+    t = Tester("vector")
+    s = t.store(t.add(t.view_load(window, _dense_strides(in_shape), a), 0.1))
+    t.run()
+    assert_close(t.output(s), a[tuple(slice(0, w) for w in window)] + np.float32(0.1), TOL_FP32, "%d-d window" % len(window))
+    assert "mode=group" in t.das()
+
+
+def test_high_rank_window_that_broadcasts_against_a_dense_tensor():
+    # tests/ut/test_view.py:217-233
+    rng = np.random.default_rng(52)
+    shape, sshape, bshape = [1, 10, 1, 20, 8, 32], [1, 6, 1, 18, 7, 32], [4, 6, 8, 18, 7, 32]
+    a = rng.normal(0, 1, shape).astype(np.float32)
+    b = rng.normal(0, 1, bshape).astype(np.float32)
+    t = Tester("vector")
+    s = t.store(t.add(t.view_load(sshape, _dense_strides(shape), a), t.load(b)))
+    t.run()
+    assert_close(t.output(s), a[:, :6, :, :18, :7, :] + b, TOL_FP32, "6-d window + dense tensor")
+
+
+def test_strided_store_of_five_dimensions():
+    # tests/ut/test_view.py:364-375
+    rng = np.random.default_rng(53)
+    out_shape, window = [4, 4, 5, 3, 16], [3, 2, 3, 2, 12]
+    a = rng.normal(0, 1, window).astype(np.float32)
+    t = Tester("vector")
+    want = np.zeros(out_shape, np.float32)
+    want[tuple(slice(0, w) for w in window)] = a + np.float32(0.1)
+    t.view_store_expect(t.add(t.load(a), 0.1), _dense_strides(out_shape), want)
+    assert t.run_check()
