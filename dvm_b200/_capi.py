@@ -62,6 +62,12 @@ SIGNATURES = {
     "dvm_slice": (c_void_p, [c_void_p, c_void_p, c_void_p, c_void_p]),
     "dvm_slice_dim": (c_void_p, [c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "dvm_split_chunk": (c_void_p, [c_void_p, c_void_p, c_int, c_int64, c_size_t, c_size_t]),
+    "dvm_clone_map_new": (c_void_p, []),
+    "dvm_clone_map_free": (None, [c_void_p]),
+    "dvm_clone_map_int_array": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "dvm_clone_map_scalar": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "dvm_kernel_clone": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "dvm_clone_map_object": (c_void_p, [c_void_p, c_void_p]),
     "dvm_concat": (c_void_p, [c_void_p, ctypes.POINTER(c_void_p), c_size_t, c_int]),
     "dvm_copy": (c_void_p, [c_void_p, c_void_p]),
     "dvm_matmul": (c_void_p, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),

@@ -7,6 +7,7 @@
 #include <exception>
 #include <memory>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "../../include/dvm.h"
@@ -37,6 +38,40 @@ struct dvm_comm : dvm::Comm {
 struct dvm_kernel {
   dvm::Kernel kernel;
   double last_jit_us = 0.0;
+};
+
+// Kernel::Clone's helper over the C handles: registered pairs first, copies owned by the map for everything else
+struct dvm_clone_map : dvm::CloneHelper {
+  std::unordered_map<const void *, void *> refs;
+  std::unordered_map<const dvm::NDObject *, dvm::NDObject *> ops;
+  std::vector<std::unique_ptr<dvm_int_array>> own_arrays;
+  std::vector<std::unique_ptr<dvm_scalar>> own_scalars;
+  dvm::IntArrayRef *GetClone(dvm::IntArrayRef *r) override {
+    auto it = refs.find(r);
+    if (it != refs.end()) return static_cast<dvm::IntArrayRef *>(it->second);
+    auto a = std::make_unique<dvm_int_array>();
+    a->data.assign(r->data, r->data + r->size);
+    a->sync();
+    dvm::IntArrayRef *out = &a->ref;
+    refs[r] = out;
+    own_arrays.push_back(std::move(a));
+    return out;
+  }
+  dvm::ScalarRef *GetClone(dvm::ScalarRef *r) override {
+    auto it = refs.find(r);
+    if (it != refs.end()) return static_cast<dvm::ScalarRef *>(it->second);
+    auto s = std::make_unique<dvm_scalar>();
+    s->ref = *r;
+    dvm::ScalarRef *out = &s->ref;
+    refs[r] = out;
+    own_scalars.push_back(std::move(s));
+    return out;
+  }
+  dvm::NDObject *GetClone(dvm::NDObject *op) override {
+    auto it = ops.find(op);
+    return it == ops.end() ? nullptr : it->second;
+  }
+  void SetClone(dvm::NDObject *op, dvm::NDObject *clone) override { ops[op] = clone; }
 };
 
 namespace {
@@ -213,6 +248,30 @@ dvm_object *dvm_split_chunk(dvm_kernel *k, dvm_object *input, int dim, int64_t s
     },
     static_cast<dvm_object *>(nullptr));
 }
+dvm_clone_map *dvm_clone_map_new(void) { return new (std::nothrow) dvm_clone_map(); }
+void dvm_clone_map_free(dvm_clone_map *m) { delete m; }
+int dvm_clone_map_int_array(dvm_clone_map *m, dvm_int_array *base, dvm_int_array *clone) {
+  return Guard([&]() {
+    clone->data = base->data;
+    clone->sync();
+    m->refs[&base->ref] = &clone->ref;
+    return 0;
+  }, 1);
+}
+int dvm_clone_map_scalar(dvm_clone_map *m, dvm_scalar *base, dvm_scalar *clone) {
+  return Guard([&]() {
+    clone->ref = base->ref;
+    m->refs[&base->ref] = &clone->ref;
+    return 0;
+  }, 1);
+}
+int dvm_kernel_clone(dvm_kernel *dst, dvm_kernel *base, dvm_clone_map *m) {
+  return Guard([&]() {
+    dst->kernel.Clone(base->kernel, *m);
+    return 0;
+  }, 1);
+}
+dvm_object *dvm_clone_map_object(dvm_clone_map *m, dvm_object *base) { return O(m->GetClone(N(base))); }
 dvm_object *dvm_concat(dvm_kernel *k, dvm_object **inputs, size_t input_num, int dim) {
   return Guard(
     [&]() {

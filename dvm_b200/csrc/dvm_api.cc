@@ -335,7 +335,42 @@ void Kernel::Clear() {
   kernel_ = new VKernel(type, flags);
 }
 
-void Kernel::Clone(const Kernel &, CloneHelper &) { Unsupported("Clone"); }
+// ref: include/dvm.h:255-259, src/dvm.cc:1183-1191 - this kernel becomes a copy of `base`'s graph: same type and flags, every
+// op copied in order with its operands mapped through the helper, every borrowed IntArrayRef / ScalarRef replaced by what the
+// helper maps it to (itself when the helper has nothing for it).  Addresses are not copied: the clone is bound by relocation.
+void Kernel::Clone(const Kernel &base, CloneHelper &helper) {
+  const VKernel *src = base.GetImpl();
+  if (src == nullptr) DvmException("Clone of a kernel that was never reset");
+  delete kernel_;
+  kernel_ = new VKernel(src->type_, src->flags_);
+  kernel_->name_ = src->name_;
+  for (const NDObject *n : src->nodes_) {
+    NDObject *c = kernel_->NewNode(n->kind, n->dtype);
+    const int id = c->id;
+    *c = *n;
+    c->id = id;
+    c->cidx = -1;
+    c->addr = nullptr;
+    c->origin = nullptr;
+    for (int k = 0; k < 3; ++k)
+      if (n->in[k]) {
+        c->in[k] = helper.GetClone(n->in[k]);
+        if (c->in[k] == nullptr) DvmException("Clone: an operand was not cloned before its user");
+      }
+    auto ints = [&](IntArrayRef *r) { return r ? helper.GetClone(r) : nullptr; };
+    auto scal = [&](ScalarRef *r) { return r ? helper.GetClone(r) : nullptr; };
+    c->shape_ref = ints(n->shape_ref);
+    c->stride_ref = ints(n->stride_ref);
+    c->aux_ref = ints(n->aux_ref);
+    c->slice_a = ints(n->slice_a);
+    c->slice_b = ints(n->slice_b);
+    c->slice_c = ints(n->slice_c);
+    c->scalar_ref = scal(n->scalar_ref);
+    c->scalar_ref2 = scal(n->scalar_ref2);
+    helper.SetClone(const_cast<NDObject *>(n), c);
+  }
+  kernel_->cur_sub_ = src->cur_sub_;
+}
 void Kernel::SetNameHint(const char *name, const char *) {
   if (kernel_ && name) kernel_->name_ = name;
 }
@@ -685,7 +720,7 @@ void Kernel::SpecNext() {
 void Kernel::ParallelAdd(KernelType type, uint32_t, size_t) {
   auto vk = Impl(this);
   if (vk->type_ != kParallel) DvmException("ParallelAdd needs a kParallel kernel");
-  if (type != kVector) DvmException("ParallelAdd: only kVector sub-kernels are supported");
+  if (type >= kParallel) DvmException("invalid parallel add kernel type");   // (kVector, kCube or kMix graphs)
   vk->cur_sub_ += 1;
 }
 // ref: src/dvm.cc:1709-1719, SequenceKernel::AddStage src/xkernel.cc:1226-1468.  Ops appended from here on form the

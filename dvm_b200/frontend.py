@@ -368,6 +368,14 @@ class Kernel:
     def set_vf_fusion(mode):
         pass
 
+    @staticmethod
+    def set_cube_store_type(type):
+        pass  # (a tuning switch of the reference's MatMul store path; results do not depend on it)
+
+    @staticmethod
+    def set_lazy_tuning(enable):
+        pass
+
 
 def _make_unary(code):
     def f(self, input):
@@ -522,6 +530,58 @@ class PyKernel(Kernel):
         self._ws_cb = None
         if run_type == "dev":
             check_rc(self._lib.dvm_rt_set_device(self._dev_id), "set device")
+
+    def clone(self, base, remap):
+        """RtKernelPy::Clone (src/pybind_api.cc:918-997): this kernel becomes a copy of `base`'s graph with its own
+        shapes and scalars.  `remap` lists ops, IntArrayRefs and ScalarRefs of `base`; their counterparts in the copy
+        come back in the same order."""
+        lib = self._lib
+        m = check_ptr(lib.dvm_clone_map_new(), "clone map")
+
+        class _Map:   # the copy borrows what the map owns: it lives as long as this kernel does
+            def __init__(self, h):
+                self.h = h
+
+            def __del__(self):
+                try:
+                    lib.dvm_clone_map_free(self.h)
+                except Exception:
+                    pass
+
+        self._keep.append(_Map(m))
+        load_refs = []
+        for rec in base._loads:
+            ref = IntArrayRef(rec[0]._shape_ref.shape())
+            check_rc(lib.dvm_clone_map_int_array(m, rec[0]._shape_ref._h, ref._h), "clone")
+            self._keep.append(ref)
+            load_refs.append(ref)
+        out = [None] * len(remap)
+        for i, x in enumerate(remap):
+            if isinstance(x, IntArrayRef):
+                ref = IntArrayRef(x.shape())
+                check_rc(lib.dvm_clone_map_int_array(m, x._h, ref._h), "clone")
+            elif isinstance(x, ScalarRef):
+                ref = ScalarRef()
+                check_rc(lib.dvm_clone_map_scalar(m, x._h, ref._h), "clone")
+            else:
+                continue
+            self._keep.append(ref)
+            out[i] = ref
+        check_rc(lib.dvm_kernel_clone(self._k, base._k, m), "clone")
+        self._ktype, self._flags = base._ktype, base._flags
+        self._loads, self._stores = [], []
+        for rec, ref in zip(base._loads, load_refs):
+            op = self._obj(lib.dvm_clone_map_object(m, rec[0]._h), "clone")
+            op._shape_ref = ref
+            self._loads.append([op, None, None])
+        for rec in base._stores:
+            self._stores.append([self._obj(lib.dvm_clone_map_object(m, rec[0]._h), "clone"), None, None])
+        known = {rec[0]._h: rec[0] for rec in self._loads + self._stores}
+        for i, x in enumerate(remap):
+            if isinstance(x, NDObject):
+                h = lib.dvm_clone_map_object(m, x._h)
+                out[i] = known.get(h) or self._obj(h, "clone")
+        return tuple(out)
 
     # bookkeeping wrappers
     def load(self, shape, type):

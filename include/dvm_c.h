@@ -98,6 +98,20 @@ DVM_C_API dvm_object *dvm_copy(dvm_kernel *k, dvm_object *input);               
 DVM_C_API dvm_object *dvm_matmul(dvm_kernel *k, dvm_object *lhs, dvm_object *rhs, int trans_a, int trans_b,
                                  dvm_object *bias);                                           /* dvm.h:509 */
 
+/* ---- Kernel::Clone (dvm.h:255-259, CloneHelper dvm.h:212-217) ----
+ * dvm_kernel_clone makes `dst` a copy of `base`'s graph (same kernel type and flags).  The map says what every borrowed
+ * dvm_int_array / dvm_scalar of `base` becomes in the copy: pairs registered beforehand are used as given (the caller
+ * keeps updating the clone's shapes and scalars through them), every other one is copied into an object the map owns -
+ * so the map must live as long as `dst` does.  After the call dvm_clone_map_object gives the copy of any op of `base`
+ * (its loads and stores, for binding), NULL for an op the base kernel does not hold. */
+typedef struct dvm_clone_map dvm_clone_map;
+DVM_C_API dvm_clone_map *dvm_clone_map_new(void);
+DVM_C_API void dvm_clone_map_free(dvm_clone_map *m);
+DVM_C_API int dvm_clone_map_int_array(dvm_clone_map *m, dvm_int_array *base, dvm_int_array *clone);
+DVM_C_API int dvm_clone_map_scalar(dvm_clone_map *m, dvm_scalar *base, dvm_scalar *clone);
+DVM_C_API int dvm_kernel_clone(dvm_kernel *dst, dvm_kernel *base, dvm_clone_map *m);
+DVM_C_API dvm_object *dvm_clone_map_object(dvm_clone_map *m, dvm_object *base);
+
 /* ---- collectives (Comm, include/dvm.h:219-231; Kernel::AllReduce, dvm.h:531) ----
  * The communicator is NCCL's; it is bound at run time, so a host without NCCL can still use everything else.
  * Rank 0 makes a rendezvous id (dvm_comm_id_bytes() bytes) and hands it to the other ranks by any means the job has

@@ -261,8 +261,14 @@ def test_parallel_kernel_keeps_its_sub_kernels_apart():
     assert k.das().count("vmain") == 3
     with pytest.raises(RuntimeError):
         dvm.PyKernel("vector", "das", 0).parallel_add(0)
+    # a sub-kernel may hold a MatMul (kCube / kMix); a stacked kernel type as sub-kernel is refused
+    k.parallel_add(k.K_MIX)
+    a, b = k.load([128, 64], dvm.float16), k.load([64, 256], dvm.float16)
+    k.store(k.matmul(a, b, False, False))
+    k.codegen()
+    assert k.das().count("vmain") == 3 and k.das().count("mmain") == 1
     with pytest.raises(RuntimeError):
-        k.parallel_add(k.K_MIX)
+        k.parallel_add(3)
 
 
 def test_spec_next_and_inplace_mark_are_checked():
@@ -351,3 +357,24 @@ def test_slice_loads_are_strided_loads_with_an_offset():
     bad.store(bad.mul(bad.slice_load([32, 64], [3, 40], [16, 32], dvm.float32), 2.0))
     with pytest.raises(Exception, match="slice outside its tensor"):
         bad.codegen()
+
+
+def test_a_cloned_kernel_is_the_same_program_with_its_own_shapes():
+    # Kernel::Clone (include/dvm.h:255-259): the copy compiles to the same program; its shapes and scalars are its own
+    base = dvm.PyKernel("vector:dyn", "das", 0)
+    x = base.load([-1, -1], dvm.float32)
+    dims = dvm.IntArrayRef([0])
+    s = base.store(base.sum(base.add(x, 0.01), dims, True))
+    base.input(x, np.zeros((10, 512), np.float32))
+    base.codegen()
+    copy = dvm.PyKernel("", "das", 0)
+    x2, s2, dims2 = copy.clone(base, [x, s, dims])
+    copy.input(x2, np.zeros((10, 512), np.float32))
+    copy.codegen()
+    strip = lambda das: re.sub(r"@0x[0-9a-f]+|0x[0-9a-f]{4,}", "@", das)
+    assert strip(copy.das()) == strip(base.das())
+    assert list(s2.shape()) == [1, 512]
+    dims2.update([1])                               # the copy's reduce dims are its own
+    copy.input(x2, np.zeros((64, 800), np.float32))
+    copy.codegen()
+    assert list(s2.shape()) == [64, 1] and list(s.shape()) == [1, 512]
