@@ -44,6 +44,8 @@ SIGNATURES = {
     "dvm_load_strided": (c_void_p, [c_void_p, c_void_p, c_void_p, c_void_p, c_int]),
     "dvm_slice_load": (c_void_p, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int]),
     "dvm_strided_slice_load": (c_void_p, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int]),
+    "dvm_elem_any": (c_void_p, [c_void_p, c_void_p]),
+    "dvm_pad_store": (c_void_p, [c_void_p, c_void_p, c_void_p, c_int64]),
     "dvm_store_strided": (c_void_p, [c_void_p, c_void_p, c_void_p, c_void_p]),
     "dvm_unary": (c_void_p, [c_void_p, c_int, c_void_p]),
     "dvm_binary": (c_void_p, [c_void_p, c_int, c_void_p, c_void_p]),

@@ -188,6 +188,10 @@ dvm_object *dvm_strided_slice_load(dvm_kernel *k, void *addr, dvm_int_array *sha
   return DVM_OBJ_GUARD(
     k->kernel.StridedSliceLoad(addr, &shape->ref, &start->ref, &end->ref, &step->ref, static_cast<dvm::DataType>(dtype)));
 }
+dvm_object *dvm_elem_any(dvm_kernel *k, dvm_object *input) { return DVM_OBJ_GUARD(k->kernel.ElemAny(N(input))); }
+dvm_object *dvm_pad_store(dvm_kernel *k, void *addr, dvm_object *input, int64_t pad_size) {
+  return DVM_OBJ_GUARD(k->kernel.PadStore(addr, N(input), pad_size));
+}
 dvm_object *dvm_store_strided(dvm_kernel *k, void *addr, dvm_object *input, dvm_int_array *stride) {
   return DVM_OBJ_GUARD(k->kernel.Store(addr, N(input), &stride->ref));
 }
@@ -417,7 +421,11 @@ int dvm_launch_static_scratch(dvm_kernel *k, const dvm_reloc *relocs, size_t rel
 double dvm_last_jit_us(const dvm_kernel *k) { return k->last_jit_us; }
 
 int dvm_object_rank(const dvm_object *o) { return reinterpret_cast<const dvm::NDObject *>(o)->shape.rank; }
-int64_t dvm_object_dim(const dvm_object *o, int i) { return reinterpret_cast<const dvm::NDObject *>(o)->shape.d[i]; }
+int64_t dvm_object_dim(const dvm_object *o, int i) {
+  const dvm::NDObject *n = reinterpret_cast<const dvm::NDObject *>(o);
+  // (a PadStore reports the shape of its buffer: rows longer by the pad)
+  return n->shape.d[i] + (n->kind == dvm::N_STORE && i == n->shape.rank - 1 ? n->pad_size : 0);
+}
 int dvm_object_dtype(const dvm_object *o) { return reinterpret_cast<const dvm::NDObject *>(o)->dtype; }
 
 const char *dvm_dump(dvm_kernel *k) { return Guard([&]() { return k->kernel.Dump(); }, ""); }

@@ -359,7 +359,7 @@ void Kernel::Clone(const Kernel &base, CloneHelper &helper) {
       }
     auto ints = [&](IntArrayRef *r) { return r ? helper.GetClone(r) : nullptr; };
     auto scal = [&](ScalarRef *r) { return r ? helper.GetClone(r) : nullptr; };
-    c->shape_ref = ints(n->shape_ref);
+    c->shape_ref = n->reduce_all ? nullptr : ints(n->shape_ref);   // (a reduce over every dim finds its dims at Normalize)
     c->stride_ref = ints(n->stride_ref);
     c->aux_ref = ints(n->aux_ref);
     c->slice_a = ints(n->slice_a);
@@ -428,7 +428,15 @@ NDObject *Kernel::Store(void *addr, NDObject *input, IntArrayRef *stride) {
   n->stride_ref = stride;
   return n;
 }
-NDObject *Kernel::PadStore(void *, NDObject *, int64_t) { Unsupported("PadStore"); }
+// ref: src/dvm.cc:1572-1576, NDPadStore::Normalize src/ops.cc:1399-1412 - the result in a buffer whose rows are `pad_size`
+// elements longer than the tensor's (dense strides of that longer shape; the padding is left as it is).  GetShape of the
+// store reports the padded shape, which is the buffer the caller provides.
+NDObject *Kernel::PadStore(void *addr, NDObject *input, int64_t pad_size) {
+  if (pad_size < 0) DvmException("PadStore: negative pad size");
+  NDObject *n = Store(addr, input);
+  n->pad_size = pad_size;
+  return n;
+}
 // ref: src/dvm.cc:1578-1580, src/xkernel.h:322.  The reference's flag keeps its workspace pool from handing the store's
 // buffer to another temporary.  Workspace temporaries here are bump-allocated once per compile and never reused, and a
 // user's buffer is never used as workspace, so the mark needs no action beyond being recorded (listed by DumpR).
@@ -649,7 +657,26 @@ template DVM_API NDObject *Kernel::OneHot<float>(NDObject *, IntArrayRef *, int,
 template DVM_API NDObject *Kernel::OneHot<int32_t>(NDObject *, IntArrayRef *, int, int32_t, int32_t);
 template DVM_API NDObject *Kernel::OneHot<Float16>(NDObject *, IntArrayRef *, int, Float16, Float16);
 template DVM_API NDObject *Kernel::OneHot<BFloat16>(NDObject *, IntArrayRef *, int, BFloat16, BFloat16);
-NDObject *Kernel::ElemAny(NDObject *) { Unsupported("ElemAny"); }
+// ref: include/dvm.h:493-496 (private in the reference; python element_any, tests/ut/test_element_any.py): one element
+// that is 1 when any element of the input differs from 0, else 0 - the maximum over every dim of (x != 0), in fp32
+NDObject *Kernel::ElemAny(NDObject *input) {
+  auto vk = Impl(this);
+  NDObject *x = input->dtype == kFloat32 ? input : Cast(input, kFloat32);
+  auto ne = vk->NewNode(N_COMPARE_S, kFloat32);
+  ne->sub = kNotEqual;
+  ne->in[0] = x;
+  ne->scalar_bits = 0;   // 0.0f
+  auto r = vk->NewNode(N_REDUCE, kFloat32);
+  r->sub = kMax;
+  r->in[0] = ne;
+  r->keepdims = false;
+  r->reduce_all = true;
+  static const int64_t kOne[1] = {1};
+  static IntArrayRef one_ref;
+  one_ref.data = kOne;
+  one_ref.size = 1;
+  return Reshape(r, &one_ref);
+}
 
 // ref: src/dvm.cc:1537-1544 - a sum of anything but fp32 is refused with a null result.
 NDObject *Kernel::_Reduce(int op_type, NDObject *input, IntArrayRef *dims, bool keepdims) {
@@ -764,6 +791,11 @@ int Kernel::Launch(const RelocEntry *relocs, size_t reloc_size, void *workspace,
 IntArrayRef *Kernel::GetShape(NDObject *op) {
   op->out_ref.data = op->shape.d;
   op->out_ref.size = static_cast<size_t>(op->shape.rank);
+  if (op->kind == N_STORE && op->pad_size > 0 && op->shape.rank > 0) {   // the buffer's shape: rows longer by the pad
+    for (int i = 0; i < op->shape.rank; ++i) op->out_dims[i] = op->shape.d[i];
+    op->out_dims[op->shape.rank - 1] += op->pad_size;
+    op->out_ref.data = op->out_dims;
+  }
   return &op->out_ref;
 }
 DataType Kernel::GetDType(NDObject *op) { return op->dtype; }

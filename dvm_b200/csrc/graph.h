@@ -89,6 +89,11 @@ class NDObject {
   // SliceLoad / StridedSliceLoad: a window of the tensor at `addr` whose full shape is shape_ref.  slice_mode 1: start +
   // size (slice_a, slice_b); 2: start, end, step (slice_a, slice_b, slice_c; indices as in Python slicing).  Normalize()
   // turns it into a strided load: shape = the window, stride = the tensor's strides times the steps, addr_off = the start
+  // a reduction over every dim of its input, whatever the rank turns out to be (ElemAny): Normalize() fills the dims
+  bool reduce_all = false;
+  int64_t all_dims[kMaxRank] = {0};
+  IntArrayRef all_ref;
+  int64_t pad_size = 0;               // PadStore: elements added behind every row of the result in memory (never written)
   uint8_t slice_mode = 0;
   IntArrayRef *slice_a = nullptr, *slice_b = nullptr, *slice_c = nullptr;
   void *addr = nullptr;               // Load/Store device address
@@ -111,6 +116,7 @@ class NDObject {
   // results of Normalize()
   Shape shape;
   IntArrayRef out_ref;                // view of `shape` handed out by Kernel::GetShape
+  int64_t out_dims[kMaxRank] = {0};   // ... of the padded shape for a PadStore
 };
 
 // One launch of the vector interpreter.

@@ -115,6 +115,15 @@ void InferShape(NDObject *n) {
       break;
     case N_STORE:
       n->shape = n->in[0]->shape;
+      if (n->pad_size > 0 && n->shape.rank > 0) {
+        int64_t dense = 1;
+        for (int i = n->shape.rank - 1; i >= 0; --i) {
+          n->stride[i] = dense;
+          dense *= n->shape.d[i] + (i == n->shape.rank - 1 ? n->pad_size : 0);
+        }
+        n->strided = true;
+        break;
+      }
       ReadStrides(n);
       break;
     case N_UNARY:
@@ -150,6 +159,12 @@ void InferShape(NDObject *n) {
     case N_REDUCE: {
       const Shape &s = n->in[0]->shape;
       bool red[kMaxRank] = {false};
+      if (n->reduce_all) {
+        for (int i = 0; i < s.rank; ++i) n->all_dims[i] = i;
+        n->all_ref.data = n->all_dims;
+        n->all_ref.size = static_cast<size_t>(s.rank);
+        n->shape_ref = &n->all_ref;
+      }
       if (n->shape_ref == nullptr) Fail(n, "missing reduce dims");
       for (size_t i = 0; i < n->shape_ref->size; ++i) {
         int64_t d = n->shape_ref->data[i];

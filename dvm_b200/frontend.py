@@ -192,6 +192,14 @@ class Kernel:
         op._shape_ref = ref
         return op
 
+    def element_any(self, input):
+        """KernelPy::ElementAny: one element, 1 when any element of the input differs from 0."""
+        return self._obj(self._lib.dvm_elem_any(self._k, input._h), "element_any")
+
+    def pad_store(self, obj, pad_size):
+        """KernelPy::PadStore: the result in a buffer whose rows are `pad_size` elements longer (shape() of the store)."""
+        return self._obj(self._lib.dvm_pad_store(self._k, None, obj._h, int(pad_size)), "pad_store")
+
     def slice_load(self, shape, start, size, type):
         """A window (start + size per dim) of a tensor in memory whose whole shape is `shape` (KernelPy::SliceLoad)."""
         ref = self._shape_ref(shape)
@@ -351,6 +359,11 @@ class Kernel:
     def parallel_add(self, ktype, flags=0, core_limit=0):
         """Start the next independent sub-kernel of a "parallel" kernel (KernelPy::ParallelAdd, include/dvm_py.h:214)."""
         check_rc(self._lib.dvm_parallel_add(self._k, int(ktype), int(flags), int(core_limit)), "parallel_add")
+
+    def clear_store_memory(self, store):
+        """RtKernelPy::ClearStoreMemory zeroes a buffer that the reference's kernels accumulate into; stores here write
+        every element of their result, so there is nothing to clear."""
+        self._find(self._stores, store)
 
     def set_store_inplace(self, store):
         """Mark a store whose buffer also feeds the kernel (KernelPy::SetStoreInplace, include/dvm_py.h:206)."""
@@ -597,6 +610,11 @@ class PyKernel(Kernel):
     def view_load(self, shape, stride, type):
         op = Kernel.view_load(self, shape, stride, type)
         self._loads.append([op, None, None])
+        return op
+
+    def pad_store(self, obj, pad_size):
+        op = Kernel.pad_store(self, obj, pad_size)
+        self._stores.append([op, None, None])
         return op
 
     def slice_load(self, shape, start, size, type):

@@ -81,6 +81,10 @@ DVM_C_API dvm_object *dvm_full_f32(dvm_kernel *k, float v, dvm_int_array *shape,
 DVM_C_API dvm_object *dvm_full_i64(dvm_kernel *k, int64_t v, dvm_int_array *shape, int dtype);
 DVM_C_API dvm_object *dvm_full_ref(dvm_kernel *k, dvm_scalar *v, dvm_int_array *shape, int dtype);
 DVM_C_API dvm_object *dvm_reshape(dvm_kernel *k, dvm_object *input, dvm_int_array *shape);    /* dvm.h:434 */
+/* Kernel::ElemAny (dvm.h:496): one fp32 element, 1 when any element of the input differs from 0 */
+DVM_C_API dvm_object *dvm_elem_any(dvm_kernel *k, dvm_object *input);
+/* Kernel::PadStore (dvm.h:344): rows of the result lie `pad_size` elements further apart than the tensor's own */
+DVM_C_API dvm_object *dvm_pad_store(dvm_kernel *k, void *addr, dvm_object *input, int64_t pad_size);
 /* a window of a tensor in memory (Kernel::SliceLoad dvm.h:312, StridedSliceLoad :317): `shape` is the whole tensor's */
 DVM_C_API dvm_object *dvm_slice_load(dvm_kernel *k, void *addr, dvm_int_array *shape, dvm_int_array *start,
                                      dvm_int_array *size, int dtype);

@@ -62,12 +62,12 @@ int main(int argc, char **argv) {
   try {
     dvm::Kernel bad;
     bad.Reset(dvm::kVector, 0);
-    bad.ElemAny(bad.Load(nullptr, &shape_ref, dvm::kFloat32));
+    bad.MultiLoad(nullptr, &shape_ref, dvm::kFloat32, nullptr);
   } catch (const std::runtime_error &e) {
     threw = std::strstr(e.what(), "DVM EXCEPTION") != nullptr;
   }
   if (!threw) {
-    std::printf("FAIL: ElemAny did not raise DvmException\n");
+    std::printf("FAIL: MultiLoad did not raise DvmException\n");
     return 1;
   }
   {

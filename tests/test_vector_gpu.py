@@ -188,3 +188,21 @@ def test_scalar_ref_and_relaunch():
         t.input(sc, v)
         t.run()
         assert_close(t.output(s), x * np.float32(v), TOL_EXACT, "scalar ref")
+
+
+@pytest.mark.parametrize("mask", [1, 0])
+@pytest.mark.parametrize("shape", [(1024, 32), (127,), (100, 100), (23, 23), (5231,)])
+def test_element_any(mask, shape):
+    # Kernel::ElemAny (include/dvm.h:496; tests/ut/test_element_any.py): 1 when any element differs from 0
+    from dvm_b200.tester import Tester
+    a = np.full(shape, mask, np.float32)
+    t = Tester("vector")
+    b = t.store(t.element_any(t.load(a)))
+    t.run()
+    assert t.output(b).shape == (1,) and t.output(b)[0] == mask
+    a = np.zeros(shape, np.float16)
+    a.reshape(-1)[a.size // 3] = -0.5 if mask else 0.0
+    t = Tester("vector")
+    b = t.store(t.element_any(t.abs(t.load(a))))
+    t.run()
+    assert t.output(b)[0] == mask

@@ -180,3 +180,19 @@ def test_strided_store_of_five_dimensions():
     want[tuple(slice(0, w) for w in window)] = a + np.float32(0.1)
     t.view_store_expect(t.add(t.load(a), 0.1), _dense_strides(out_shape), want)
     assert t.run_check()
+
+
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+@pytest.mark.parametrize("shape,pad", [((200, 100), 128), ((220, 100), 202), ((2000, 1), 1), ((1, 3, 200, 100), 128),
+                                       ((4, 5, 111, 1), 1), ((1024, 30), 15), ((7, 33), 0)])
+def test_pad_store_writes_rows_into_a_wider_buffer(dtype, shape, pad):
+    # Kernel::PadStore (include/dvm.h:344): the store's shape is the buffer's, rows longer by the pad, the padding untouched
+    # (tests/ut/test_pad.py)
+    rng = np.random.default_rng(71)
+    a = rng.normal(0, 1, shape).astype(dtype)
+    t = Tester("vector")
+    o = t.pad_store(t.abs(t.load(a)), pad)
+    t.run()
+    out = np.asarray(t.output(o))
+    assert out.shape == tuple(shape[:-1]) + (shape[-1] + pad,)
+    assert_close(out[..., :shape[-1]].astype(np.float32), np.abs(a).astype(np.float32), 0.0, "pad store")
