@@ -108,3 +108,29 @@ def test_folded_and_unfolded_kernels_agree(tmp_path):
     # the normalised fp16 result may differ by one unit in the last place where the fp32 value sits on a rounding edge
     diff = np.abs(y.astype(np.float32) - exact["y"].astype(np.float32))
     assert np.max(diff) <= 2e-3 and np.mean(diff > 0) < 0.01
+
+
+@pytest.mark.parametrize("shape,dims", [((64, 4096), (1,)), ((300, 777), (1,)), ((37, 5000), (1,)), ((48, 96, 64), (2,)),
+                                        ((48, 96, 64), (1, 2)), ((96, 64, 50), (0,)), ((7, 33), (0, 1)), ((2048, 16), (1,))])
+def test_folded_variance_over_other_axes(shape, dims):
+    # layer-norm style statistics (rows, trailing blocks, leading axis, everything): the same rewrite on every geometry
+    rng = np.random.default_rng(24)
+    x = (rng.normal(size=shape) * 1.5 + rng.normal(0, 2.0, size=[s if i not in dims else 1 for i, s in enumerate(shape)])).astype(np.float16)
+    n = int(np.prod([shape[d] for d in dims]))
+
+    def build(k, a):
+        xf = k.cast(a, 3)
+        mean = k.mul(k.sum(xf, dims, True), 1.0 / n)
+        xc = k.sub(xf, mean)
+        var = k.mul(k.sum(k.mul(xc, xc), dims, True), 1.0 / n)
+        y = k.cast(k.div(xc, k.sqrt(k.add(var, 1e-5))), 1)
+        return y, mean, var
+
+    dev, _, k = run_both(build, [x])
+    assert " body_1:" in k.das() and " body_2:" not in k.das()
+    xd = x.astype(np.float64)
+    m64 = xd.mean(axis=dims, keepdims=True)
+    v64 = ((xd - m64) ** 2).mean(axis=dims, keepdims=True)
+    assert np.max(np.abs(dev[1].astype(np.float64) - m64)) <= 1e-4 * (1.0 + np.max(np.abs(m64)))
+    assert np.max(np.abs(dev[2].astype(np.float64) - v64) / np.maximum(v64, 1e-12)) <= 2e-4
+    assert_close(np.asarray(dev[0]).astype(np.float32), ((xd - m64) / np.sqrt(v64 + 1e-5)).astype(np.float32), 2e-3, "normalised")
