@@ -253,7 +253,7 @@ __device__ __forceinline__ void decompose_group(const VmParam &P, uint32_t gi, u
 namespace {
 // kRounds: chunks may hold several rounds (VmParam::rounds > 1).  Only the instantiations with the larger register budget
 // carry the round bookkeeping; the others run one round per chunk and the compiler folds the round loop away.
-template <bool kResident, bool kCoords, bool kRounds>
+template <bool kResident, bool kCoords, bool kRounds, bool kFlatOnly = false>
 __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t epoch) {
   asm volatile(DV_DECLARE);
   asm volatile(DV_LN(DV_SPLATLANE, "va") DV_LN(DV_SPLATLANE, "vb")
@@ -262,7 +262,8 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
   const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
   const uint32_t tid = threadIdx.x;
   const uint32_t T = P.tcons;   // consumer threads (a multiple of 32; threads past tg * groups_per_cta idle)
-  const bool flat = P.mode == VM_FLAT;
+  // (kFlatOnly: an instantiation for reduce-free launches only, without the group loop and the reduction words)
+  const bool flat = kFlatOnly || P.mode == VM_FLAT;
   const uint32_t S = P.num_stages;
   const bool ring = P.stage_bytes != 0;
   const uint32_t ngb = flat ? 1u : (P.num_groups + P.groups_per_cta - 1) / P.groups_per_cta;
@@ -521,6 +522,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
               break;
             }
             case SOP_RFIN: {
+              if (kFlatOnly) break;   // (a reduce-free launch has no reductions to finish)
               const uint32_t kind = sub >> 4;
               float v = get_part(sub & 3u);
               set_part(sub & 3u, red_identity(kind));
@@ -571,6 +573,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
               break;
             }
             case SOP_RFIN2: {
+              if (kFlatOnly) break;
               // (sums only, more than one warp per group: the lowering sees to both)
               const uint32_t pa = sub & 3u, pb = (sub >> 2) & 3u;
               float v0 = get_part(pa), v1 = get_part(pb);
@@ -1281,14 +1284,16 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
 // Register budgets of the same interpreter: up to 256 consumer threads per CTA (two CTAs of that size per SM, four
 // of the 128-thread ones that reduce graphs with many groups use), and up to 512 (few long groups) with one CTA per SM.
 // A third budget of 72 registers (five 128-thread CTAs per SM) was measured 50 % slower: its spills sit in the loop.
-#define DVMB_VM_KERNEL(NAME, THREADS, BLOCKS, RES, COORDS, ROUNDS)                                               \
+#define DVMB_VM_KERNEL(NAME, THREADS, BLOCKS, ...)                                                              \
   __global__ void __launch_bounds__(THREADS, BLOCKS) NAME(const __grid_constant__ VmParam P,                      \
                                                           const uint32_t epoch) {                                 \
-    vm_vector_body<RES, COORDS, ROUNDS>(P, epoch);                                                                \
+    vm_vector_body<__VA_ARGS__>(P, epoch);                                                                        \
   }
 // dense layouts (every chunk starts at group offset + element index)
 DVMB_VM_KERNEL(dvm_b200_vm_vector, kVmFlatThreads + 32, 2, false, false, false)
 DVMB_VM_KERNEL(dvm_b200_vm_vector_wide, kVmMaxThreads + 32, 1, false, false, false)
+// ... of reduce-free (flat) launches only
+DVMB_VM_KERNEL(dvm_b200_vm_vector_flat, kVmFlatThreads + 32, 2, false, false, false, true)
 // strided layouts: chunk starts follow from the chunk's coordinates along the iterated axes
 DVMB_VM_KERNEL(dvm_b200_vm_vector_nd, kVmFlatThreads + 32, 2, false, true, false)
 DVMB_VM_KERNEL(dvm_b200_vm_vector_nd_wide, kVmMaxThreads + 32, 1, false, true, false)
@@ -1308,7 +1313,8 @@ int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, uint32_t
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
     cudaError_t e = cudaSuccess;
     for (auto fn : {dvm_b200_vm_vector, dvm_b200_vm_vector_wide, dvm_b200_vm_vector_nd, dvm_b200_vm_vector_nd_wide,
-                    dvm_b200_vm_vector_res, dvm_b200_vm_vector_res_wide, dvm_b200_vm_vector_r128, dvm_b200_vm_vector_nd_r128})
+                    dvm_b200_vm_vector_res, dvm_b200_vm_vector_res_wide, dvm_b200_vm_vector_r128, dvm_b200_vm_vector_nd_r128,
+                    dvm_b200_vm_vector_flat})
       if (e == cudaSuccess) e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kVmMaxSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set[dev] = true;
@@ -1329,7 +1335,8 @@ int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, uint32_t
     cfg.numAttrs = 1;
   }
   const bool narrow = threads <= kVmFlatThreads + 32;
-  auto kernel = narrow ? dvm_b200_vm_vector : dvm_b200_vm_vector_wide;
+  static const bool no_flat = getenv("DVM_B200_NO_FLAT_KERNEL") != nullptr;
+  auto kernel = narrow ? (param.mode == VM_FLAT && !no_flat ? dvm_b200_vm_vector_flat : dvm_b200_vm_vector) : dvm_b200_vm_vector_wide;
   if (param.resident) {
     kernel = threads <= 256 ? dvm_b200_vm_vector_res : dvm_b200_vm_vector_res_wide;
   } else if (param.need_coords) {
