@@ -494,7 +494,7 @@ def measured_sustained():
         return None
 
 
-KERNEL_NAME = {"c1": "dvm_b200_vm_vector_flat", "c2": "dvm_b200_vm_vector_nd_r128", "c3": "dvm_b200_vm_vector",
+KERNEL_NAME = {"c1": "dvm_b200_vm_vector_flat", "c2": "dvm_b200_vm_vector_nd_r128", "c3": "dvm_b200_vm_vector_group",
                "c4": "dvm_b200_attention_bf16_sf", "c5": "dvm_b200_mm_tcgen05_pair"}
 
 

@@ -253,7 +253,7 @@ __device__ __forceinline__ void decompose_group(const VmParam &P, uint32_t gi, u
 namespace {
 // kRounds: chunks may hold several rounds (VmParam::rounds > 1).  Only the instantiations with the larger register budget
 // carry the round bookkeeping; the others run one round per chunk and the compiler folds the round loop away.
-template <bool kResident, bool kCoords, bool kRounds, bool kFlatOnly = false>
+template <bool kResident, bool kCoords, bool kRounds, int kModeOnly = 0>
 __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t epoch) {
   asm volatile(DV_DECLARE);
   asm volatile(DV_LN(DV_SPLATLANE, "va") DV_LN(DV_SPLATLANE, "vb")
@@ -262,8 +262,10 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
   const uint32_t smem_base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
   const uint32_t tid = threadIdx.x;
   const uint32_t T = P.tcons;   // consumer threads (a multiple of 32; threads past tg * groups_per_cta idle)
-  // (kFlatOnly: an instantiation for reduce-free launches only, without the group loop and the reduction words)
-  const bool flat = kFlatOnly || P.mode == VM_FLAT;
+  // (kModeOnly 1: an instantiation for reduce-free launches only, without the group loop and the reduction words; 2: for
+  // group launches only)
+  constexpr bool kFlatOnly = kModeOnly == 1;
+  const bool flat = kFlatOnly || (kModeOnly != 2 && P.mode == VM_FLAT);
   const uint32_t S = P.num_stages;
   const bool ring = P.stage_bytes != 0;
   const uint32_t ngb = flat ? 1u : (P.num_groups + P.groups_per_cta - 1) / P.groups_per_cta;
@@ -1293,7 +1295,9 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
 DVMB_VM_KERNEL(dvm_b200_vm_vector, kVmFlatThreads + 32, 2, false, false, false)
 DVMB_VM_KERNEL(dvm_b200_vm_vector_wide, kVmMaxThreads + 32, 1, false, false, false)
 // ... of reduce-free (flat) launches only
-DVMB_VM_KERNEL(dvm_b200_vm_vector_flat, kVmFlatThreads + 32, 2, false, false, false, true)
+DVMB_VM_KERNEL(dvm_b200_vm_vector_flat, kVmFlatThreads + 32, 2, false, false, false, 1)
+// ... of group launches only
+DVMB_VM_KERNEL(dvm_b200_vm_vector_group, kVmFlatThreads + 32, 2, false, false, false, 2)
 // strided layouts: chunk starts follow from the chunk's coordinates along the iterated axes
 DVMB_VM_KERNEL(dvm_b200_vm_vector_nd, kVmFlatThreads + 32, 2, false, true, false)
 DVMB_VM_KERNEL(dvm_b200_vm_vector_nd_wide, kVmMaxThreads + 32, 1, false, true, false)
@@ -1314,7 +1318,7 @@ int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, uint32_t
     cudaError_t e = cudaSuccess;
     for (auto fn : {dvm_b200_vm_vector, dvm_b200_vm_vector_wide, dvm_b200_vm_vector_nd, dvm_b200_vm_vector_nd_wide,
                     dvm_b200_vm_vector_res, dvm_b200_vm_vector_res_wide, dvm_b200_vm_vector_r128, dvm_b200_vm_vector_nd_r128,
-                    dvm_b200_vm_vector_flat})
+                    dvm_b200_vm_vector_flat, dvm_b200_vm_vector_group})
       if (e == cudaSuccess) e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kVmMaxSmemBytes);
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set[dev] = true;
@@ -1336,7 +1340,10 @@ int LaunchVector(const VmParam &param, uint32_t grid, uint32_t threads, uint32_t
   }
   const bool narrow = threads <= kVmFlatThreads + 32;
   static const bool no_flat = getenv("DVM_B200_NO_FLAT_KERNEL") != nullptr;
-  auto kernel = narrow ? (param.mode == VM_FLAT && !no_flat ? dvm_b200_vm_vector_flat : dvm_b200_vm_vector) : dvm_b200_vm_vector_wide;
+  static const bool no_group = getenv("DVM_B200_NO_GROUP_KERNEL") != nullptr;
+  auto kernel = narrow ? (param.mode == VM_FLAT ? (no_flat ? dvm_b200_vm_vector : dvm_b200_vm_vector_flat)
+                                                : (no_group ? dvm_b200_vm_vector : dvm_b200_vm_vector_group))
+                       : dvm_b200_vm_vector_wide;
   if (param.resident) {
     kernel = threads <= 256 ? dvm_b200_vm_vector_res : dvm_b200_vm_vector_res_wide;
   } else if (param.need_coords) {
