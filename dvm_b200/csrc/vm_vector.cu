@@ -540,6 +540,16 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
                 asm volatile("bar.sync 1, %0;" ::"r"(T) : "memory");   // consumer warps only
                 // every warp's partial (at most 16 warps) is read at once and combined as a tree
                 const uint32_t nw = T >> 5;
+                if (nw == 4u) {
+                  // four warps: the same tree without its identity leaves, (p0 + p2) + (p1 + p3)
+                  const float4 q = *reinterpret_cast<const float4 *>(&red_buf[red_par * 32]);
+                  v = red_combine(kind, red_combine(kind, q.x, q.z), red_combine(kind, q.y, q.w));
+                  red_par ^= 1u;
+                  if (cluster == 1) {
+                    sacc[0] = f2u(v);
+                    break;
+                  }
+                } else {
                 float pv[16];
 #pragma unroll
                 for (uint32_t wi = 0; wi < 16; ++wi) pv[wi] = wi < nw ? red_buf[red_par * 32 + wi] : red_identity(kind);
@@ -556,6 +566,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
                 }
                 v = pv[0];
                 red_par ^= 1u;
+                }
               }
               if (cluster > 1) {
                 // combine the CTA totals of the cluster in rank order: publish ours, signal every CTA, read all
