@@ -47,12 +47,16 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t addr, uint32_t by
   asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(addr), "r"(bytes)
                : "memory");
 }
+// One try: the thread may sleep inside the instruction until the phase completes or the hint (nanoseconds) runs out.  The
+// hint matters: with the default limit a waiting warp came back some thirty times per microsecond, and the producer warps'
+// polling alone was a fifth of the instructions an issue-bound kernel executed.
+constexpr uint32_t kTryWaitHintNs = 2000;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t addr, uint32_t parity) {
   uint32_t ok;
   asm volatile(
-    "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+    "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
     : "=r"(ok)
-    : "r"(addr), "r"(parity)
+    : "r"(addr), "r"(parity), "r"(kTryWaitHintNs)
     : "memory");
   return ok != 0;
 }

@@ -73,7 +73,7 @@
 #define DV_SQRRN_LANE(i, X) "mul.rn.f32 va" #i ", va" #i ", va" #i ";\n\t"
 #define DV_SIGM_LANE(i, X)                                                                                  \
   "mul.rn.f32 va" #i ", va" #i ", 0fBF800000;\n\tmul.rn.f32 va" #i ", va" #i ", 0f3FB8AA3B;\n\t"            \
-  "ex2.approx.ftz.f32 va" #i ", va" #i ";\n\tadd.rn.f32 va" #i ", va" #i ", 0f3F800000;\n\trcp.approx.f32 va" #i ", va" #i ";\n\t"
+  "ex2.approx.ftz.f32 va" #i ", va" #i ";\n\tadd.rn.f32 va" #i ", va" #i ", 0f3F800000;\n\trcp.approx.ftz.f32 va" #i ", va" #i ";\n\t"
 // tree reductions of the 16 accumulator lanes into partial register vp<SLOT>
 #define DV_TREE16(OP2, SLOT)                                                                                       \
   "{\n\t.reg .b32 r<8>;\n\t.reg .pred p;\n\t"                                                                      \
