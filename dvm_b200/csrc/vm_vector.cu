@@ -47,22 +47,27 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t addr, uint32_t by
   asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(addr), "r"(bytes)
                : "memory");
 }
-// One try: the thread may sleep inside the instruction until the phase completes or the hint (nanoseconds) runs out.  The
-// hint matters: with the default limit a waiting warp came back some thirty times per microsecond, and the producer warps'
-// polling alone was a fifth of the instructions an issue-bound kernel executed.
-constexpr uint32_t kTryWaitHintNs = 2000;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t addr, uint32_t parity) {
   uint32_t ok;
   asm volatile(
-    "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+    "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
     : "=r"(ok)
-    : "r"(addr), "r"(parity), "r"(kTryWaitHintNs)
+    : "r"(addr), "r"(parity)
     : "memory");
   return ok != 0;
 }
 // Bounded wait (bounded_wait.cuh): gives up after about two seconds and records `code` in the status record.
+// (A warp that has to wait sleeps between its polls: polled back to back, the producer warps' waits alone were a fifth of
+// the instructions an issue-bound kernel executed.)
+constexpr uint32_t kPollSleepNs = 200;
 __device__ __noinline__ void mbar_wait_slow(uint32_t addr, uint32_t parity, uint32_t code, uint32_t epoch) {
-  bounded_spin([&]() { return mbar_try_wait(addr, parity); }, code, &g_vm_status, epoch, kWaitLimitNs);
+  bounded_spin(
+    [&]() {
+      if (mbar_try_wait(addr, parity)) return true;
+      __nanosleep(kPollSleepNs);
+      return false;
+    },
+    code, &g_vm_status, epoch, kWaitLimitNs);
 }
 __device__ __forceinline__ void mbar_wait(uint32_t addr, uint32_t parity, uint32_t code, uint32_t epoch) {
   if (mbar_try_wait(addr, parity)) return;
