@@ -518,6 +518,9 @@ def device_summary(name, reps=30):
         sustained = measured_sustained()
         out["rate_single_launch"] = work / (single * 1e-6) / unit_scale(name)
         out["frac_of_measured_burst_single_launch"] = out["rate_single_launch"] / peak
+        out["frac_back_to_back_of_burst"] = rate / peak
+        # like with like: the launch timed alone against the burst figure, the launches back to back against the sustained one
+        out["frac_of_measured_peak"] = out["frac_of_measured_burst_single_launch"]
         if sustained:
             out["frac_of_measured_sustained"] = rate / sustained
     wl.k.release_io()
