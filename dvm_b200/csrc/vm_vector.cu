@@ -885,11 +885,16 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
                : "memory");
 #define DV_STV32(P0, GS) DV_STV32R("va", P0, GS)
 #define DV_STV16(CVT, P0, GS) DV_STV16R(CVT, "va", P0, GS)
+#define DV_NORM_SCALARS                                                                                     \
+  const uint64_t s0w_ = (static_cast<uint64_t>(s0_) << 32) | s0_, s1w_ = (static_cast<uint64_t>(s1_) << 32) | s1_, \
+                 s2w_ = (static_cast<uint64_t>(s2_) << 32) | s2_;
+#define DV_NORM_APPLY(R) asm volatile(DV_NORM2_R(R)::"l"(s0w_), "l"(s1w_), "l"(s2w_), "r"(s3_));
 #define DV_LDNORMST_CASE(H, MACRO, SHL, ELEM, STORE)                                                          \
   case H: {                                                                                                 \
     const TensorDesc &td = tdesc[(uhi >> 16) & 0xfu];                                                       \
     const uint32_t s0_ = lds32(sreg_addr(uhi & 0xfu)), s1_ = lds32(sreg_addr((uhi >> 4) & 0xfu));           \
     const uint32_t s2_ = lds32(sreg_addr((uhi >> 8) & 0xfu)), s3_ = lds32(sreg_addr((uhi >> 12) & 0xfu));   \
+    DV_NORM_SCALARS                                                                                         \
     uint32_t a0 = stage_saddr + (arg << 4) + (SHL(pos.in_chunk0));                                          \
     const uint32_t gs = SHL(pos.gstep), ge = pos.gstep;                                                     \
     const bool by_coords = kCoords && td.mode != AM_DENSE;                                                  \
@@ -913,8 +918,8 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
         ELEM *const p1 = next_round(p0);                                                                    \
         MACRO("va", a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)                                                 \
         MACRO("vb", a1, a1 + gs, a1 + 2u * gs, a1 + 3u * gs)                                                 \
-        asm volatile(DV_LNR(DV_NORM_LANE_R, "va", "")::"r"(s0_), "r"(s1_), "r"(s2_), "r"(s3_));             \
-        asm volatile(DV_LNR(DV_NORM_LANE_R, "vb", "")::"r"(s0_), "r"(s1_), "r"(s2_), "r"(s3_));             \
+        DV_NORM_APPLY("va")                                                                                 \
+        DV_NORM_APPLY("vb")                                                                                 \
         STORE("va", p0)                                                                                     \
         STORE("vb", p1)                                                                                     \
         ++rnd;                                                                                              \
@@ -925,7 +930,7 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
         continue;                                                                                           \
       }                                                                                                     \
       MACRO("va", a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)                                                   \
-      asm volatile(DV_LNR(DV_NORM_LANE_R, "va", "")::"r"(s0_), "r"(s1_), "r"(s2_), "r"(s3_));               \
+      DV_NORM_APPLY("va")                                                                                   \
       STORE("va", p0)                                                                                       \
       if (!kRounds || !(aux & UA_LOOP) || rnd + 1u >= n_full) break;                                        \
       ++rnd;                                                                                                \
@@ -945,6 +950,8 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
 #undef DV_ST_NORMF16
 #undef DV_ST_NORMBF16
 #undef DV_LDNORMST_CASE
+#undef DV_NORM_APPLY
+#undef DV_NORM_SCALARS
             // ---- the pieces of a residual RMSNorm + gated activation, one dispatch each (same operations, order and
             // rounding as the micro-ops they replace)
 #define DV_RING3(SHL)                                                                                       \
@@ -955,14 +962,18 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
     ELEM *const p0 = reinterpret_cast<ELEM *>(td.ptr) + kept_offset(td, pos.k) +                            \
                      ((kCoords && td.mode != AM_DENSE) ? enum_offset(td, cc) + lane4 : pos.e_start + pos.in_chunk0); \
     const uint32_t ge = pos.gstep;
+// the arithmetic of the three handlers below in packed f32x2 form (two lanes per instruction)
+#define DV_C3_ADDSQR asm volatile(DV_PAIRS8V(DV_P2_ADDSQR, ""));
+#define DV_C3_ADDMULS asm volatile(DV_PAIRS8V(DV_P2_ADDMULS, "")::"l"((static_cast<uint64_t>(sv_) << 32) | sv_));
+#define DV_C3_MULV asm volatile(DV_PAIRS8V(DV_P2_BINV, "mul.rn.f32x2"));
+#define DV_C3_SIGM asm volatile(DV_PAIRS8V(DV_P2_SIGM, "")::"l"(0xbfb8aa3bbfb8aa3bull), "l"(0x3f8000003f800000ull));
 #define DV_LD2ADDSQRSUM_CASE(H, MACRO, SHL, SLOT)                                                           \
   case H: {                                                                                                 \
     const uint32_t o0 = stage_saddr + (SHL(pos.in_chunk0)), gs = SHL(pos.gstep);                            \
     const uint32_t a0 = o0 + (arg << 4), b0 = o0 + (uhi << 4);                                              \
     MACRO("va", a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)                                                     \
     MACRO("vb", b0, b0 + gs, b0 + 2u * gs, b0 + 3u * gs)                                                     \
-    asm volatile(DV_LN(DV_BINVRN_LANE, "add.rn.f32"));                                                      \
-    asm volatile(DV_LN(DV_SQRRN_LANE, ""));                                                                 \
+    DV_C3_ADDSQR                                                                                            \
     asm volatile(DV_SUMRN_TREE(SLOT));                                                                      \
     if (aux & UA_LAST) goto body_done;                                                                      \
     continue;                                                                                               \
@@ -981,10 +992,9 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
     DV_STORE_PTR(ELEM)                                                                                      \
     MACRO("va", a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)                                                     \
     MACRO("vb", b0, b0 + gs, b0 + 2u * gs, b0 + 3u * gs)                                                     \
-    asm volatile(DV_LN(DV_BINVRN_LANE, "add.rn.f32"));                                                      \
-    asm volatile(DV_LN(DV_BINS_LANE, "mul.rn.f32")::"r"(sv_));                                              \
+    DV_C3_ADDMULS                                                                                           \
     MACRO("vb", c0, c0 + gs, c0 + 2u * gs, c0 + 3u * gs)                                                     \
-    asm volatile(DV_LN(DV_BINVRN_LANE, "mul.rn.f32"));                                                      \
+    DV_C3_MULV                                                                                              \
     STORE                                                                                                   \
     if (aux & UA_LAST) goto body_done;                                                                      \
     continue;                                                                                               \
@@ -998,11 +1008,11 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
     DV_RING3(SHL)                                                                                           \
     DV_STORE_PTR(ELEM)                                                                                      \
     MACRO("va", a0, a0 + gs, a0 + 2u * gs, a0 + 3u * gs)                                                     \
-    asm volatile(DV_LN(DV_SIGM_LANE, ""));                                                                  \
+    DV_C3_SIGM                                                                                              \
     MACRO("vb", b0, b0 + gs, b0 + 2u * gs, b0 + 3u * gs)                                                     \
-    asm volatile(DV_LN(DV_BINVRN_LANE, "mul.rn.f32"));                                                      \
+    DV_C3_MULV                                                                                              \
     MACRO("vb", c0, c0 + gs, c0 + 2u * gs, c0 + 3u * gs)                                                     \
-    asm volatile(DV_LN(DV_BINVRN_LANE, "mul.rn.f32"));                                                      \
+    DV_C3_MULV                                                                                              \
     STORE                                                                                                   \
     if (aux & UA_LAST) goto body_done;                                                                      \
     continue;                                                                                               \
@@ -1011,6 +1021,10 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
             DV_LDSIGMMUL2ST_CASE(UH_LDSIGMMUL2ST_FIRST + FT_F16, DV_LDR_F16, DV_SHL1, unsigned short, DV_STV16("cvt.rn.f16x2.f32", p0, ge))
             DV_LDSIGMMUL2ST_CASE(UH_LDSIGMMUL2ST_FIRST + FT_BF16, DV_LDR_BF16, DV_SHL1, unsigned short, DV_STV16("cvt.rn.bf16x2.f32", p0, ge))
 #undef DV_LDSIGMMUL2ST_CASE
+#undef DV_C3_ADDSQR
+#undef DV_C3_ADDMULS
+#undef DV_C3_MULV
+#undef DV_C3_SIGM
 #undef DV_STORE_PTR
 #undef DV_RING3
 #undef DV_STV16

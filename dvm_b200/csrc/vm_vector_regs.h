@@ -29,9 +29,19 @@
 #define DV_SUBS_LANE_R(i, R, X) "sub.rn.f32 " R #i ", " R #i ", %0;\n\t"
 #define DV_SQRRN_LANE_R(i, R, X) "mul.rn.f32 " R #i ", " R #i ", " R #i ";\n\t"
 #define DV_CSQR_LANE_R(i, R, X) "sub.rn.f32 " R #i ", " R #i ", %0;\n\tmul.rn.f32 " R #i ", " R #i ", " R #i ";\n\t"
-#define DV_NORM_LANE_R(i, R, X)                                                                                \
-  "sub.rn.f32 " R #i ", " R #i ", %0;\n\tmul.rn.f32 " R #i ", " R #i ", %1;\n\tmul.rn.f32 " R #i ", " R #i ", %2;\n\t" \
-  "add.rn.f32 " R #i ", " R #i ", %3;\n\t"
+// ((x - %0) * %1) * %2 + %3 on two neighbouring lanes at a time: the subtraction and the two multiplications as packed
+// f32x2 operations (%0..%2 hold the scalar twice, as a 64-bit pair), the addition per lane - a packed addition behind a
+// packed multiplication is contracted into a fused multiply-add by the assembler, which would change the result (so is
+// a packed fused multiply-add by one in its place; a packed addition under an always-true predicate keeps its rounding
+// but measured slower than the two additions per lane)
+#define DV_NORM2_PAIR_R(a, b, R, D)                                                                              \
+  "mov.b64 " D ", {" R a ", " R b "};\n\tsub.rn.f32x2 " D ", " D ", %0;\n\tmul.rn.f32x2 " D ", " D ", %1;\n\t"        \
+  "mul.rn.f32x2 " D ", " D ", %2;\n\tmov.b64 {" R a ", " R b "}, " D ";\n\t"                                         \
+  "add.rn.f32 " R a ", " R a ", %3;\n\tadd.rn.f32 " R b ", " R b ", %3;\n\t"
+#define DV_NORM2_R(R)                                                                                            \
+  "{\n\t.reg .b64 d<8>;\n\t" DV_NORM2_PAIR_R("0", "1", R, "d0") DV_NORM2_PAIR_R("2", "3", R, "d1")                  \
+  DV_NORM2_PAIR_R("4", "5", R, "d2") DV_NORM2_PAIR_R("6", "7", R, "d3") DV_NORM2_PAIR_R("8", "9", R, "d4")          \
+  DV_NORM2_PAIR_R("10", "11", R, "d5") DV_NORM2_PAIR_R("12", "13", R, "d6") DV_NORM2_PAIR_R("14", "15", R, "d7") "}"
 #define DV_TREE16R(OP2, SLOT, R)                                                                                   \
   "{\n\t.reg .b32 r<8>;\n\t.reg .pred p;\n\t"                                                                      \
   OP2("r0", R "0", R "1") OP2("r1", R "2", R "3") OP2("r2", R "4", R "5") OP2("r3", R "6", R "7")                  \
@@ -74,6 +84,30 @@
 #define DV_SIGM_LANE(i, X)                                                                                  \
   "mul.rn.f32 va" #i ", va" #i ", 0fBF800000;\n\tmul.rn.f32 va" #i ", va" #i ", 0f3FB8AA3B;\n\t"            \
   "ex2.approx.ftz.f32 va" #i ", va" #i ";\n\tadd.rn.f32 va" #i ", va" #i ", 0f3F800000;\n\trcp.approx.ftz.f32 va" #i ", va" #i ";\n\t"
+// packed f32x2 forms of the fused handlers' arithmetic: two neighbouring lanes of va (and of vb) travel as one 64-bit
+// pair, one instruction works on both.  Only where no addition follows a multiplication directly in packed form (the
+// assembler contracts that pair into a fused multiply-add, which rounds once instead of twice).
+#define DV_PAIRS8V(M, X)                                                                                          \
+  "{\n\t.reg .b64 d<8>, e<8>;\n\t" M("0", "1", "d0", "e0", X) M("2", "3", "d1", "e1", X) M("4", "5", "d2", "e2", X)   \
+  M("6", "7", "d3", "e3", X) M("8", "9", "d4", "e4", X) M("10", "11", "d5", "e5", X) M("12", "13", "d6", "e6", X)    \
+  M("14", "15", "d7", "e7", X) "}"
+#define DV_P2_PACKAB(a, b, D, E) "mov.b64 " D ", {va" a ", va" b "};\n\tmov.b64 " E ", {vb" a ", vb" b "};\n\t"
+#define DV_P2_UNPACK(a, b, D) "mov.b64 {va" a ", va" b "}, " D ";\n\t"
+// va <- (va + vb)^2
+#define DV_P2_ADDSQR(a, b, D, E, X)                                                                               \
+  DV_P2_PACKAB(a, b, D, E) "add.rn.f32x2 " D ", " D ", " E ";\n\tmul.rn.f32x2 " D ", " D ", " D ";\n\t" DV_P2_UNPACK(a, b, D)
+// va <- (va + vb) * scalar pair %0
+#define DV_P2_ADDMULS(a, b, D, E, X)                                                                              \
+  DV_P2_PACKAB(a, b, D, E) "add.rn.f32x2 " D ", " D ", " E ";\n\tmul.rn.f32x2 " D ", " D ", %0;\n\t" DV_P2_UNPACK(a, b, D)
+// va <- va OP vb
+#define DV_P2_BINV(a, b, D, E, OP) DV_P2_PACKAB(a, b, D, E) OP " " D ", " D ", " E ";\n\t" DV_P2_UNPACK(a, b, D)
+// va <- 1 / (1 + 2^(va * -log2(e)))   (%0 = the pair of -log2(e), %1 = the pair of 1.0; x * -1 is exact, so one
+// multiplication by -log2(e) gives the bits of (x * -1) * log2(e))
+#define DV_P2_SIGM(a, b, D, E, X)                                                                                 \
+  "mov.b64 " D ", {va" a ", va" b "};\n\tmul.rn.f32x2 " D ", " D ", %0;\n\t" DV_P2_UNPACK(a, b, D)                     \
+  "ex2.approx.ftz.f32 va" a ", va" a ";\n\tex2.approx.ftz.f32 va" b ", va" b ";\n\t"                                 \
+  "mov.b64 " D ", {va" a ", va" b "};\n\tadd.rn.f32x2 " D ", " D ", %1;\n\t" DV_P2_UNPACK(a, b, D)                     \
+  "rcp.approx.ftz.f32 va" a ", va" a ";\n\trcp.approx.ftz.f32 va" b ", va" b ";\n\t"
 // tree reductions of the 16 accumulator lanes into partial register vp<SLOT>
 #define DV_TREE16(OP2, SLOT)                                                                                       \
   "{\n\t.reg .b32 r<8>;\n\t.reg .pred p;\n\t"                                                                      \
