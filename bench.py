@@ -769,7 +769,7 @@ def main():
     tensor = name in ("c4", "c5")
     # DRAM bytes per full-size launch from the ncu captures summarised under profiles/ (dram__bytes_read + write; the
     # quarter-size captures of c1, c3, c4, c5 are scaled by 4: their traffic grows with the leading dimension)
-    traffic = {"c1": 4 * (135.9e6 + 39.5e6), "c2": 195.7e6 + 55.8e6, "c3": 4 * (135.0e6 + 39.9e6),
+    traffic = {"c1": 4 * (135.2e6 + 36.0e6), "c2": 195.7e6 + 55.8e6, "c3": 4 * (135.0e6 + 39.9e6),
                "c4": 4 * (101.0e6 + 13.0e6), "c5": 4 * (520.3e6 + 62.0e6)}.get(name)
     if traffic is not None and args.scale != 1.0:
         traffic *= args.scale
