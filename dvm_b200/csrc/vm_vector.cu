@@ -555,6 +555,24 @@ __device__ __forceinline__ void vm_vector_body(const VmParam &P, const uint32_t 
                   v = red_combine(kind, red_combine(kind, q.x, q.z), red_combine(kind, q.y, q.w));
                   red_par ^= 1u;
                   if (cluster == 1) {
+                    if ((xhi & 0xffu) == SOP_RSTD_FAST) {
+                      // the word behind is the fused reciprocal root (its second immediate in the word after it): done
+                      // here, and so is a closing move behind that - a normalisation's scalar section in one dispatch
+                      // instead of three, with the operations and roundings of the separate words
+                      uint32_t dlo, dhi, mlo, mhi;
+                      lds64x2(spc + 8u, dlo, dhi);
+                      lds64x2(spc + 16u, mlo, mhi);
+                      const float t = __fadd_rn(__fmul_rn(v, u2f(xlo)), u2f(dlo));
+                      sacc[0] = f2u(fast_div(1.0f, sqrtf(t)));
+                      if ((mhi & 0xffu) == SOP_MOV_END) {
+                        asm volatile("st.shared.u32 [%0], %1;" ::"r"(sreg_addr((mhi >> 24) & 0xfu)), "r"(sacc[0]) : "memory");
+                        goto scalar_done;
+                      }
+                      spc += 16u;
+                      xlo = mlo;
+                      xhi = mhi;
+                      break;
+                    }
                     sacc[0] = f2u(v);
                     break;
                   }
